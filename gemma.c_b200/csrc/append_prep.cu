@@ -1,0 +1,337 @@
+// Per-head prep (RMSNorm + RoPE) fused into the paged KV append, the
+// whole-prompt prep, and the plain cache write of prepared rows.
+//
+// Replaces, with the same arithmetic order so that results are bit-identical:
+//   prep_weighted_rope_head_values / prep_scale_free_head_values /
+//   phase_decode_q_paged_kv_norm_rope   src/gemma4_flash_attention_decode.cu:216-375
+//   gemma4_rmsnorm_warp_scale_f32_device src/gemma4_rmsnorm.cu:90-101
+//   store_rotated_pair_bf16              src/gemma4_rope.cu:8-20
+//   phase_qkv_norm_rope                  src/gemma4_flash_attention_prefill.cu:1022-1081
+//   kv_cache_write_vec_kernel            src/gemma4_kv_cache.cu:11-71
+//
+// One warp owns one head; lane l holds elements l + 32*i (the reference's
+// ownership), the sum of squares is an fma chain per lane followed by the xor
+// butterfly 16,8,4,2,1 -- that order defines the bit pattern of the scale.
+#include "common.cuh"
+#include "kernels.cuh"
+
+#include <type_traits>
+
+namespace b200kv {
+
+namespace {
+
+constexpr float kRmsEps = 1.0e-6f;  // GEMMA4_RMS_NORM_EPS, src/gemma4.h:29
+
+// The reference compiles its prep call sites with flush-to-zero multiplies
+// and the shared norm/rope helpers without; the approx mode reproduces that
+// split, the IEEE mode uses plain round-to-nearest everywhere.
+template <bool kIeee>
+__device__ __forceinline__ float mul_prep(float a, float b) {
+  if constexpr (kIeee) {
+    return __fmul_rn(a, b);
+  } else {
+    float r;
+    asm("mul.ftz.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+    return r;
+  }
+}
+
+template <int D, bool kIeee>
+__device__ __forceinline__ float warp_rms_scale(const float (&x)[D / 32]) {
+  float ss = 0.0f;
+#pragma unroll
+  for (int i = 0; i < D / 32; ++i) ss = __fmaf_rn(x[i], x[i], ss);
+#pragma unroll
+  for (int offset = 16; offset > 0; offset /= 2) {
+    ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, offset));
+  }
+  const float t = __fadd_rn(__fdiv_rn(ss, float(D)), kRmsEps);
+  if constexpr (kIeee) {
+    return __fdiv_rn(1.0f, __fsqrt_rn(t));
+  } else {
+    return rsqrtf(t);
+  }
+}
+
+template <int D>
+__device__ __forceinline__ void load_head(const __nv_bfloat16 *in, int lane,
+                                          float (&x)[D / 32]) {
+#pragma unroll
+  for (int i = 0; i < D / 32; ++i) {
+    x[i] = __bfloat162float(in[lane + i * 32]);
+  }
+}
+
+// Learned-weight RMSNorm, then split-half RoPE on the first ROT dims.
+template <int D, int ROT, bool kIeee>
+__device__ __forceinline__ void prep_weighted_rope(
+    __nv_bfloat16 *out, const float (&x)[D / 32], const __nv_bfloat16 *weight,
+    const float *cos_row, const float *sin_row, int lane) {
+  constexpr int kHalf = ROT / 2;
+  constexpr int kPairs = kHalf / 32;
+  const float scale = warp_rms_scale<D, kIeee>(x);
+#pragma unroll
+  for (int i = 0; i < kPairs; ++i) {
+    const int dim = lane + i * 32;
+    const float lo = mul_prep<kIeee>(mul_prep<kIeee>(x[i], scale),
+                                     __bfloat162float(__ldg(weight + dim)));
+    const float hi =
+        mul_prep<kIeee>(mul_prep<kIeee>(x[i + kPairs], scale),
+                        __bfloat162float(__ldg(weight + kHalf + dim)));
+    const float c = __ldg(cos_row + dim);
+    const float s = __ldg(sin_row + dim);
+    out[dim] = __float2bfloat16_rn(__fmaf_rn(-hi, s, __fmul_rn(lo, c)));
+    out[kHalf + dim] = __float2bfloat16_rn(__fmaf_rn(lo, s, __fmul_rn(hi, c)));
+  }
+#pragma unroll
+  for (int i = 0; i < D / 32; ++i) {
+    const int dim = lane + i * 32;
+    if (dim >= ROT) {
+      const float value = mul_prep<kIeee>(mul_prep<kIeee>(x[i], scale),
+                                          __bfloat162float(__ldg(weight + dim)));
+      out[dim] = __float2bfloat16_rn(value);
+    }
+  }
+}
+
+// Scale-free RMSNorm (V rows): no weight, no rotation.
+template <int D, bool kIeee>
+__device__ __forceinline__ void prep_scale_free(__nv_bfloat16 *out,
+                                                const float (&x)[D / 32],
+                                                int lane) {
+  const float scale = warp_rms_scale<D, kIeee>(x);
+#pragma unroll
+  for (int i = 0; i < D / 32; ++i) {
+    out[lane + i * 32] = __float2bfloat16_rn(mul_prep<kIeee>(x[i], scale));
+  }
+}
+
+// grid (batch, kv_head); warps 0..G-1 prep the G query heads of the group,
+// warp G preps and stores K, warp G+1 (only when V has its own projection)
+// preps and stores V.
+template <int D, int ROT, bool kIeee>
+__global__ void decode_append_kernel(AppendArgs a) {
+  const int batch = int(blockIdx.x);
+  const int kv_head = int(blockIdx.y);
+  const int warp = int(threadIdx.x) >> 5;
+  const int lane = int(threadIdx.x) & 31;
+  const Gemma4KvCacheConfig &c = a.cfg;
+  const int G = a.q_heads / c.num_heads;
+  const bool has_v = a.v != nullptr;
+
+  const int position = __ldg(a.token_position + batch);
+  if (position < 0) return;
+  const float *cos_row = a.cos + int64_t(position) * (ROT / 2);
+  const float *sin_row = a.sin + int64_t(position) * (ROT / 2);
+
+  if (warp < G) {
+    const int64_t off = (int64_t(batch) * a.q_heads + kv_head * G + warp) * D;
+    float x[D / 32];
+    load_head<D>(a.q + off, lane, x);
+    prep_weighted_rope<D, ROT, kIeee>(a.q_prepared + off, x, a.q_norm_weight,
+                                      cos_row, sin_row, lane);
+    return;
+  }
+
+  // Row address, src/gemma4_flash_attention_decode.cu:285-303: the slot is
+  // the logical page modulo the table width; an unmapped page drops the row.
+  const int logical_page = position / c.page_size;
+  const int slot = logical_page % c.max_pages_per_seq;
+  const int physical =
+      __ldg(a.page_table + int64_t(batch) * c.max_pages_per_seq + slot);
+  if (physical < 0 || physical >= c.num_pages) return;
+  const int64_t dst = cache_offset(c, a.cache_layer, physical,
+                                   position - logical_page * c.page_size,
+                                   kv_head, 0);
+  const int64_t src = (int64_t(batch) * c.num_heads + kv_head) * D;
+
+  if (warp == G) {
+    float x[D / 32];
+    load_head<D>(a.k + src, lane, x);
+    prep_weighted_rope<D, ROT, kIeee>(a.cache_k + dst, x, a.k_norm_weight,
+                                      cos_row, sin_row, lane);
+    if (!has_v) prep_scale_free<D, kIeee>(a.cache_v + dst, x, lane);
+  } else if (has_v) {
+    float x[D / 32];
+    load_head<D>(a.v + src, lane, x);
+    prep_scale_free<D, kIeee>(a.cache_v + dst, x, lane);
+  }
+}
+
+// grid (rows); warp h preps query head h and, when h < kv_heads, K/V head h.
+template <int D, int ROT, bool kIeee>
+__global__ void prefill_prep_kernel(PrefillPrepArgs a) {
+  const int64_t row = blockIdx.x;
+  const int lane = int(threadIdx.x) & 31;
+  const int position = __ldg(a.token_position + row);
+  if (position < 0) return;
+  const float *cos_row = a.cos + int64_t(position) * (ROT / 2);
+  const float *sin_row = a.sin + int64_t(position) * (ROT / 2);
+  const int warps = int(blockDim.x) >> 5;
+  for (int head = int(threadIdx.x) >> 5; head < a.q_heads; head += warps) {
+    const int64_t q_off = (row * a.q_heads + head) * D;
+    float x[D / 32];
+    load_head<D>(a.q + q_off, lane, x);
+    prep_weighted_rope<D, ROT, kIeee>(a.q_prepared + q_off, x,
+                                      a.q_norm_weight, cos_row, sin_row, lane);
+    if (head < a.kv_heads) {
+      const int64_t kv_off = (row * a.kv_heads + head) * D;
+      float kx[D / 32];
+      load_head<D>(a.k + kv_off, lane, kx);
+      prep_weighted_rope<D, ROT, kIeee>(a.k_prepared + kv_off, kx,
+                                        a.k_norm_weight, cos_row, sin_row,
+                                        lane);
+      if (a.v != nullptr) {
+        float vx[D / 32];
+        load_head<D>(a.v + kv_off, lane, vx);
+        prep_scale_free<D, kIeee>(a.v_prepared + kv_off, vx, lane);
+      } else {
+        prep_scale_free<D, kIeee>(a.v_prepared + kv_off, kx, lane);
+      }
+    }
+  }
+}
+
+// One CTA per token: all heads of the token are one contiguous row in the
+// source and in the cache page, moved as 128-bit packs.
+__global__ __launch_bounds__(256) void kv_cache_write_kernel(
+    __nv_bfloat16 *cache_k, __nv_bfloat16 *cache_v, Gemma4KvCacheConfig c,
+    const int32_t *token_batch, const int32_t *token_position,
+    const int32_t *page_table, int32_t layer, const __nv_bfloat16 *k,
+    const __nv_bfloat16 *v) {
+  const int token = int(blockIdx.x);
+  const int batch = __ldg(token_batch + token);
+  const int position = __ldg(token_position + token);
+  // Guards of src/gemma4_kv_cache.cu:27-34.
+  if (batch < 0 || position < 0) return;
+  if (batch >= c.batch_size) return;
+  const int logical_page = position / c.page_size;
+  if (c.window_size == 0 && logical_page >= c.max_pages_per_seq) return;
+  const int slot = logical_page % c.max_pages_per_seq;
+  const int physical =
+      __ldg(page_table + int64_t(batch) * c.max_pages_per_seq + slot);
+  if (physical < 0 || physical >= c.num_pages) return;
+  const int page_offset = position - logical_page * c.page_size;
+
+  const int vecs = c.num_heads * c.head_dim / 8;
+  const uint4 *src_k =
+      reinterpret_cast<const uint4 *>(k) + int64_t(token) * vecs;
+  const uint4 *src_v =
+      reinterpret_cast<const uint4 *>(v) + int64_t(token) * vecs;
+  const int64_t dst = cache_offset(c, layer, physical, page_offset, 0, 0) / 8;
+  uint4 *dst_k = reinterpret_cast<uint4 *>(cache_k) + dst;
+  uint4 *dst_v = reinterpret_cast<uint4 *>(cache_v) + dst;
+  for (int i = int(threadIdx.x); i < vecs; i += int(blockDim.x)) {
+    const uint4 kk = __ldg(src_k + i);
+    const uint4 vv = __ldg(src_v + i);
+    dst_k[i] = kk;
+    dst_v[i] = vv;
+  }
+}
+
+template <typename Launch>
+cudaError_t dispatch_geometry(int head_dim, int rotary_dim, int norm_mode,
+                              Launch launch) {
+  const bool ieee = norm_mode == B200KV_NORM_IEEE;
+  if (head_dim == 256 && rotary_dim == 256) {
+    return ieee ? launch(std::integral_constant<int, 256>{},
+                         std::integral_constant<int, 256>{},
+                         std::true_type{})
+                : launch(std::integral_constant<int, 256>{},
+                         std::integral_constant<int, 256>{},
+                         std::false_type{});
+  }
+  if (head_dim == 512 && rotary_dim == 128) {
+    return ieee ? launch(std::integral_constant<int, 512>{},
+                         std::integral_constant<int, 128>{},
+                         std::true_type{})
+                : launch(std::integral_constant<int, 512>{},
+                         std::integral_constant<int, 128>{},
+                         std::false_type{});
+  }
+  return cudaErrorInvalidValue;  // geometry the kernels are not built for
+}
+
+}  // namespace
+
+cudaError_t decode_append_bf16(const AppendArgs &a, cudaStream_t stream) {
+  const Gemma4KvCacheConfig &c = a.cfg;
+  if (a.batch_count == 0) return cudaSuccess;
+  if (a.q_prepared == nullptr || a.cache_k == nullptr ||
+      a.cache_v == nullptr || a.page_table == nullptr ||
+      a.token_position == nullptr || a.q == nullptr || a.k == nullptr ||
+      a.q_norm_weight == nullptr || a.k_norm_weight == nullptr ||
+      a.cos == nullptr || a.sin == nullptr || a.batch_count < 0 ||
+      a.cache_layer < 0 || a.cache_layer >= c.num_layers ||
+      c.num_pages <= 0 || c.page_size <= 0 || c.max_pages_per_seq <= 0 ||
+      c.batch_size <= 0 || c.window_size < 0 || c.num_heads <= 0 ||
+      a.q_heads <= 0 || a.q_heads % c.num_heads != 0 ||
+      (a.norm_mode != B200KV_NORM_IEEE &&
+       a.norm_mode != B200KV_NORM_RSQRT_APPROX)) {
+    return cudaErrorInvalidValue;
+  }
+  const int G = a.q_heads / c.num_heads;
+  const int warps = G + (a.v != nullptr ? 2 : 1);
+  if (warps > 32 || c.num_heads > 65535) return cudaErrorInvalidValue;
+  const dim3 grid(a.batch_count, c.num_heads);
+  return dispatch_geometry(
+      c.head_dim, a.rotary_dim, a.norm_mode, [&](auto d, auto rot, auto ieee) {
+        decode_append_kernel<decltype(d)::value, decltype(rot)::value,
+                             decltype(ieee)::value>
+            <<<grid, warps * 32, 0, stream>>>(a);
+        return cudaGetLastError();
+      });
+}
+
+cudaError_t prefill_prep_bf16(const PrefillPrepArgs &a, cudaStream_t stream) {
+  if (a.rows == 0) return cudaSuccess;
+  if (a.q_prepared == nullptr || a.k_prepared == nullptr ||
+      a.v_prepared == nullptr || a.q == nullptr || a.k == nullptr ||
+      a.q_norm_weight == nullptr || a.k_norm_weight == nullptr ||
+      a.cos == nullptr || a.sin == nullptr || a.token_position == nullptr ||
+      a.rows < 0 || a.rows > 2147483647ll || a.q_heads <= 0 ||
+      a.kv_heads <= 0 || a.kv_heads > a.q_heads ||
+      (a.norm_mode != B200KV_NORM_IEEE &&
+       a.norm_mode != B200KV_NORM_RSQRT_APPROX)) {
+    return cudaErrorInvalidValue;
+  }
+  const int warps = a.q_heads < 16 ? a.q_heads : 16;
+  return dispatch_geometry(
+      a.head_dim, a.rotary_dim, a.norm_mode, [&](auto d, auto rot, auto ieee) {
+        prefill_prep_kernel<decltype(d)::value, decltype(rot)::value,
+                            decltype(ieee)::value>
+            <<<unsigned(a.rows), warps * 32, 0, stream>>>(a);
+        return cudaGetLastError();
+      });
+}
+
+cudaError_t kv_cache_write_bf16(__nv_bfloat16 *cache_k, __nv_bfloat16 *cache_v,
+                                Gemma4KvCacheConfig config,
+                                const int32_t *page_table,
+                                const int32_t *token_batch,
+                                const int32_t *token_position,
+                                int32_t token_count, int32_t layer,
+                                const __nv_bfloat16 *k, const __nv_bfloat16 *v,
+                                cudaStream_t stream) {
+  // Argument contract of src/gemma4_kv_cache.cu:149-180.
+  if (token_count == 0) return cudaSuccess;
+  if (token_count < 0 || layer < 0 || layer >= config.num_layers ||
+      config.num_pages <= 0 || config.page_size <= 0 ||
+      config.max_pages_per_seq <= 0 || config.batch_size <= 0 ||
+      config.window_size < 0 || config.num_heads <= 0 ||
+      config.head_dim <= 0 || config.head_dim % 8 != 0 ||
+      cache_k == nullptr || cache_v == nullptr || page_table == nullptr ||
+      token_batch == nullptr || token_position == nullptr || k == nullptr ||
+      v == nullptr) {
+    return cudaErrorInvalidValue;
+  }
+  const int vecs = config.num_heads * config.head_dim / 8;
+  const int threads = vecs >= 256 ? 256 : ((vecs + 31) / 32) * 32;
+  kv_cache_write_kernel<<<token_count, threads, 0, stream>>>(
+      cache_k, cache_v, config, token_batch, token_position, page_table, layer,
+      k, v);
+  return cudaGetLastError();
+}
+
+}  // namespace b200kv

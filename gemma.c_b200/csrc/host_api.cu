@@ -1,0 +1,740 @@
+// Host side of libgemma4_b200kv.so: geometry and page bookkeeping, the runtime
+// state that owns caches and per-step metadata, launch planning, and the
+// extern "C" boundary. The device work lives in append_prep.cu and
+// decode_attention.cu; nothing here computes on the CPU what a kernel is
+// meant to compute.
+#include "common.cuh"
+#include "kernels.cuh"
+
+#include <algorithm>
+#include <cmath>
+#include <new>
+#include <vector>
+
+namespace {
+
+// Model constants of the reference (src/gemma4.h:8-29).
+constexpr int kNumLayers = 48;
+constexpr int kGlobalLayerPeriod = 6;
+constexpr int kGlobalLayerCount =
+    kNumLayers / kGlobalLayerPeriod + (kNumLayers % kGlobalLayerPeriod ? 1 : 0);
+constexpr int kSlidingLayerCount = kNumLayers - kGlobalLayerCount;
+constexpr int kMaxPositions = 262144;
+
+constexpr bool is_global_layer(int32_t layer) {
+  return layer == kNumLayers - 1 || (layer + 1) % kGlobalLayerPeriod == 0;
+}
+
+B200KvRuntimeGeometry default_geometry() {
+  B200KvRuntimeGeometry g;
+  g.sliding_layers = kSlidingLayerCount;
+  g.sliding_kv_heads = 8;
+  g.sliding_head_dim = 256;
+  g.sliding_window = 1024;
+  g.sliding_rotary_dim = 256;
+  g.sliding_rope_theta = 10000.0f;
+  g.global_layers = kGlobalLayerCount;
+  g.global_kv_heads = 1;
+  g.global_head_dim = 512;
+  g.global_rotary_dim = 128;  // partial rotary factor 0.25
+  g.global_rope_theta = 1000000.0f;
+  g.global_rope_exponent_dim = 512;
+  return g;
+}
+
+size_t cache_elements(const Gemma4KvCacheConfig &c) {
+  return size_t(c.num_layers) * c.num_pages * c.page_size * c.num_heads *
+         c.head_dim;
+}
+
+int32_t sliding_pages(int32_t max_seq_len, int32_t page_size, int32_t window) {
+  // src/gemma4_runtime.cu:18-24: a live window may straddle one extra page.
+  if (max_seq_len <= window) return b200kv::div_up(max_seq_len, page_size);
+  return b200kv::div_up(window + page_size - 1, page_size);
+}
+
+void fill_rope(std::vector<float> &cos_t, std::vector<float> &sin_t,
+               int32_t max_seq_len, int32_t rotary_half, float theta,
+               int32_t exponent_dim) {
+  cos_t.resize(size_t(max_seq_len) * rotary_half);
+  sin_t.resize(cos_t.size());
+  b200kv_fill_rope_tables(cos_t.data(), sin_t.data(), max_seq_len, rotary_half,
+                          theta, exponent_dim);
+}
+
+template <typename T>
+cudaError_t upload(T *dst, const std::vector<T> &src, size_t count,
+                   cudaStream_t stream) {
+  if (count == 0) return cudaSuccess;
+  return cudaMemcpyAsync(dst, src.data(), count * sizeof(T),
+                         cudaMemcpyHostToDevice, stream);
+}
+
+#define B200KV_TRY(expr)                        \
+  do {                                          \
+    const cudaError_t b200kv_st__ = (expr);     \
+    if (b200kv_st__ != cudaSuccess) return b200kv_st__; \
+  } while (0)
+
+cudaError_t upload_all_metadata(Gemma4RuntimeState *s, size_t token_count,
+                                cudaStream_t stream) {
+  B200KV_TRY(upload(s->sliding_page_table, s->h_sliding_page_table,
+                    s->h_sliding_page_table.size(), stream));
+  B200KV_TRY(upload(s->global_page_table, s->h_global_page_table,
+                    s->h_global_page_table.size(), stream));
+  B200KV_TRY(upload(s->seq_lengths, s->h_seq_lengths, s->h_seq_lengths.size(),
+                    stream));
+  B200KV_TRY(upload(s->token_batch, s->h_token_batch, token_count, stream));
+  return upload(s->token_position, s->h_token_position, token_count, stream);
+}
+
+}  // namespace
+
+// ===========================================================================
+// C++ interface (names and behaviour of the reference's host functions)
+// ===========================================================================
+
+Gemma4KvCacheConfig gemma4_kv_cache_make_config(bool global, int32_t num_pages,
+                                                int32_t page_size,
+                                                int32_t max_pages_per_seq) {
+  const B200KvRuntimeGeometry g = default_geometry();
+  Gemma4KvCacheConfig c;
+  c.num_layers = global ? g.global_layers : g.sliding_layers;
+  c.num_pages = num_pages;
+  c.page_size = page_size;
+  c.max_pages_per_seq = max_pages_per_seq;
+  c.batch_size = num_pages / max_pages_per_seq;
+  c.num_heads = global ? g.global_kv_heads : g.sliding_kv_heads;
+  c.head_dim = global ? g.global_head_dim : g.sliding_head_dim;
+  c.window_size = global ? 0 : g.sliding_window;
+  return c;
+}
+
+int32_t gemma4_kv_cache_layer_index(int32_t model_layer, bool global_cache) {
+  if (model_layer < 0 || model_layer >= kNumLayers) return -1;
+  if (is_global_layer(model_layer) != global_cache) return -1;
+  int32_t index = 0;
+  for (int32_t layer = 0; layer < model_layer; ++layer) {
+    index += is_global_layer(layer) == global_cache ? 1 : 0;
+  }
+  return index;
+}
+
+int32_t gemma4_kv_cache_ensure_page(std::vector<int32_t> &page_table,
+                                    std::vector<int32_t> &slot_logical_pages,
+                                    const Gemma4KvCacheConfig &config,
+                                    int32_t batch, int32_t position) {
+  return b200kv_ensure_page(page_table.data(), slot_logical_pages.data(),
+                            &config, batch, position);
+}
+
+int32_t gemma4_kv_cache_ensure_range(std::vector<int32_t> &page_table,
+                                     std::vector<int32_t> &slot_logical_pages,
+                                     const Gemma4KvCacheConfig &config,
+                                     int32_t batch, int32_t first_position,
+                                     int32_t token_count) {
+  return b200kv_ensure_range(page_table.data(), slot_logical_pages.data(),
+                             &config, batch, first_position, token_count);
+}
+
+void gemma4_runtime_state_free(Gemma4RuntimeState *state) {
+  cudaFree(state->sliding_cache_k);
+  cudaFree(state->sliding_cache_v);
+  cudaFree(state->global_cache_k);
+  cudaFree(state->global_cache_v);
+  cudaFree(state->sliding_page_table);
+  cudaFree(state->global_page_table);
+  cudaFree(state->seq_lengths);
+  cudaFree(state->token_batch);
+  cudaFree(state->token_position);
+  cudaFree(state->sliding_cos);
+  cudaFree(state->sliding_sin);
+  cudaFree(state->global_cos);
+  cudaFree(state->global_sin);
+  *state = Gemma4RuntimeState();
+}
+
+cudaError_t gemma4_runtime_state_init_geometry(
+    Gemma4RuntimeState *state, int32_t batch_size, int32_t max_seq_len,
+    int32_t page_size, const B200KvRuntimeGeometry &g, cudaStream_t stream) {
+  if (state == nullptr || batch_size <= 0 || max_seq_len <= 0 ||
+      page_size <= 0 || max_seq_len > kMaxPositions ||
+      g.sliding_layers <= 0 || g.global_layers <= 0 ||
+      g.sliding_kv_heads <= 0 || g.global_kv_heads <= 0 ||
+      g.sliding_head_dim <= 0 || g.global_head_dim <= 0 ||
+      g.sliding_window <= 0 || g.sliding_rotary_dim <= 0 ||
+      g.global_rotary_dim <= 0 || g.global_rope_exponent_dim <= 0) {
+    return cudaErrorInvalidValue;
+  }
+  const int32_t global_pps = b200kv::div_up(max_seq_len, page_size);
+  const int32_t sliding_pps =
+      sliding_pages(max_seq_len, page_size, g.sliding_window);
+  const size_t token_rows = size_t(batch_size) * max_seq_len;
+
+  *state = Gemma4RuntimeState();
+  Gemma4RuntimeState &s = *state;
+  s.geometry = g;
+  s.batch_size = batch_size;
+  s.max_seq_len = max_seq_len;
+  s.page_size = page_size;
+  s.sliding_cache_config = {g.sliding_layers,
+                            batch_size * sliding_pps,
+                            page_size,
+                            sliding_pps,
+                            batch_size,
+                            g.sliding_kv_heads,
+                            g.sliding_head_dim,
+                            std::min(max_seq_len, g.sliding_window)};
+  s.global_cache_config = {g.global_layers, batch_size * global_pps,
+                           page_size,       global_pps,
+                           batch_size,      g.global_kv_heads,
+                           g.global_head_dim, 0};
+  s.h_sliding_page_table.assign(size_t(batch_size) * sliding_pps, -1);
+  s.h_global_page_table.assign(size_t(batch_size) * global_pps, -1);
+  s.h_sliding_slot_logical_pages.assign(s.h_sliding_page_table.size(), -1);
+  s.h_global_slot_logical_pages.assign(s.h_global_page_table.size(), -1);
+  s.h_seq_lengths.assign(batch_size, 0);
+  s.h_token_batch.resize(token_rows);
+  s.h_token_position.resize(token_rows);
+
+  auto body = [&]() -> cudaError_t {
+    const size_t sliding_bytes =
+        cache_elements(s.sliding_cache_config) * sizeof(__nv_bfloat16);
+    const size_t global_bytes =
+        cache_elements(s.global_cache_config) * sizeof(__nv_bfloat16);
+    B200KV_TRY(cudaMalloc(&s.sliding_cache_k, sliding_bytes));
+    B200KV_TRY(cudaMalloc(&s.sliding_cache_v, sliding_bytes));
+    B200KV_TRY(cudaMalloc(&s.global_cache_k, global_bytes));
+    B200KV_TRY(cudaMalloc(&s.global_cache_v, global_bytes));
+    B200KV_TRY(cudaMalloc(&s.sliding_page_table,
+                          s.h_sliding_page_table.size() * sizeof(int32_t)));
+    B200KV_TRY(cudaMalloc(&s.global_page_table,
+                          s.h_global_page_table.size() * sizeof(int32_t)));
+    B200KV_TRY(cudaMalloc(&s.seq_lengths, size_t(batch_size) * sizeof(int32_t)));
+    B200KV_TRY(cudaMalloc(&s.token_batch, token_rows * sizeof(int32_t)));
+    B200KV_TRY(cudaMalloc(&s.token_position, token_rows * sizeof(int32_t)));
+
+    std::vector<float> cos_t, sin_t;
+    fill_rope(cos_t, sin_t, max_seq_len, g.sliding_rotary_dim / 2,
+              g.sliding_rope_theta, g.sliding_head_dim);
+    B200KV_TRY(cudaMalloc(&s.sliding_cos, cos_t.size() * sizeof(float)));
+    B200KV_TRY(cudaMalloc(&s.sliding_sin, sin_t.size() * sizeof(float)));
+    B200KV_TRY(upload(s.sliding_cos, cos_t, cos_t.size(), stream));
+    B200KV_TRY(upload(s.sliding_sin, sin_t, sin_t.size(), stream));
+    // The tables are pageable host vectors about to go out of scope.
+    B200KV_TRY(cudaStreamSynchronize(stream));
+    fill_rope(cos_t, sin_t, max_seq_len, g.global_rotary_dim / 2,
+              g.global_rope_theta, g.global_rope_exponent_dim);
+    B200KV_TRY(cudaMalloc(&s.global_cos, cos_t.size() * sizeof(float)));
+    B200KV_TRY(cudaMalloc(&s.global_sin, sin_t.size() * sizeof(float)));
+    B200KV_TRY(upload(s.global_cos, cos_t, cos_t.size(), stream));
+    B200KV_TRY(upload(s.global_sin, sin_t, sin_t.size(), stream));
+    B200KV_TRY(cudaStreamSynchronize(stream));
+    return upload_all_metadata(&s, 0, stream);
+  };
+  const cudaError_t st = body();
+  if (st != cudaSuccess) gemma4_runtime_state_free(state);
+  return st;
+}
+
+cudaError_t gemma4_runtime_state_init(Gemma4RuntimeState *state,
+                                      int32_t batch_size, int32_t max_seq_len,
+                                      int32_t page_size, cudaStream_t stream) {
+  return gemma4_runtime_state_init_geometry(state, batch_size, max_seq_len,
+                                            page_size, default_geometry(),
+                                            stream);
+}
+
+cudaError_t gemma4_runtime_prepare_prefill(Gemma4RuntimeState *state,
+                                           int32_t seq_len,
+                                           cudaStream_t stream) {
+  Gemma4RuntimeState &s = *state;
+  if (seq_len < 0 || seq_len > s.max_seq_len) return cudaErrorInvalidValue;
+  std::fill(s.h_sliding_page_table.begin(), s.h_sliding_page_table.end(), -1);
+  std::fill(s.h_global_page_table.begin(), s.h_global_page_table.end(), -1);
+  std::fill(s.h_sliding_slot_logical_pages.begin(),
+            s.h_sliding_slot_logical_pages.end(), -1);
+  std::fill(s.h_global_slot_logical_pages.begin(),
+            s.h_global_slot_logical_pages.end(), -1);
+  for (int32_t b = 0; b < s.batch_size; ++b) {
+    if (gemma4_kv_cache_ensure_range(s.h_sliding_page_table,
+                                     s.h_sliding_slot_logical_pages,
+                                     s.sliding_cache_config, b, 0,
+                                     seq_len) < 0 ||
+        gemma4_kv_cache_ensure_range(s.h_global_page_table,
+                                     s.h_global_slot_logical_pages,
+                                     s.global_cache_config, b, 0,
+                                     seq_len) < 0) {
+      return cudaErrorInvalidValue;
+    }
+    s.h_seq_lengths[b] = seq_len;
+    for (int32_t pos = 0; pos < seq_len; ++pos) {
+      const size_t row = size_t(b) * seq_len + pos;  // batch-major rows
+      s.h_token_batch[row] = b;
+      s.h_token_position[row] = pos;
+    }
+  }
+  s.token_count = s.batch_size * seq_len;
+  return upload_all_metadata(&s, size_t(s.token_count), stream);
+}
+
+cudaError_t gemma4_runtime_prepare_decode_step(Gemma4RuntimeState *state,
+                                               cudaStream_t stream) {
+  Gemma4RuntimeState &s = *state;
+  // All-or-nothing: reject the step before touching any table
+  // (tests/test_runtime_state.cu:83-105).
+  for (int32_t b = 0; b < s.batch_size; ++b) {
+    const int32_t pos = s.h_seq_lengths[b];
+    if (pos < 0 || pos >= s.max_seq_len) return cudaErrorInvalidValue;
+  }
+  for (int32_t b = 0; b < s.batch_size; ++b) {
+    const int32_t pos = s.h_seq_lengths[b];
+    if (gemma4_kv_cache_ensure_page(s.h_sliding_page_table,
+                                    s.h_sliding_slot_logical_pages,
+                                    s.sliding_cache_config, b, pos) < 0 ||
+        gemma4_kv_cache_ensure_page(s.h_global_page_table,
+                                    s.h_global_slot_logical_pages,
+                                    s.global_cache_config, b, pos) < 0) {
+      return cudaErrorInvalidValue;
+    }
+    s.h_token_batch[b] = b;
+    s.h_token_position[b] = pos;
+    // Only the one entry per table that this position touches changes.
+    const size_t si = size_t(b) * s.sliding_cache_config.max_pages_per_seq +
+                      (pos / s.page_size) %
+                          s.sliding_cache_config.max_pages_per_seq;
+    const size_t gi = size_t(b) * s.global_cache_config.max_pages_per_seq +
+                      (pos / s.page_size) %
+                          s.global_cache_config.max_pages_per_seq;
+    B200KV_TRY(cudaMemcpyAsync(s.sliding_page_table + si,
+                               s.h_sliding_page_table.data() + si,
+                               sizeof(int32_t), cudaMemcpyHostToDevice,
+                               stream));
+    B200KV_TRY(cudaMemcpyAsync(s.global_page_table + gi,
+                               s.h_global_page_table.data() + gi,
+                               sizeof(int32_t), cudaMemcpyHostToDevice,
+                               stream));
+  }
+  for (int32_t b = 0; b < s.batch_size; ++b) ++s.h_seq_lengths[b];
+  s.token_count = s.batch_size;
+  B200KV_TRY(upload(s.seq_lengths, s.h_seq_lengths, s.h_seq_lengths.size(),
+                    stream));
+  B200KV_TRY(upload(s.token_batch, s.h_token_batch, size_t(s.token_count),
+                    stream));
+  return upload(s.token_position, s.h_token_position, size_t(s.token_count),
+                stream);
+}
+
+// ===========================================================================
+// extern "C" boundary
+// ===========================================================================
+
+struct B200KvRuntimeState {
+  Gemma4RuntimeState state;
+};
+
+extern "C" {
+
+cudaError_t gemma4_kv_cache_write_bf16(
+    __nv_bfloat16 *__restrict__ d_cache_k,
+    __nv_bfloat16 *__restrict__ d_cache_v, Gemma4KvCacheConfig config,
+    const int32_t *__restrict__ d_page_table,
+    const int32_t *__restrict__ d_token_batch,
+    const int32_t *__restrict__ d_token_position, int32_t token_count,
+    int32_t layer, const __nv_bfloat16 *__restrict__ d_k,
+    const __nv_bfloat16 *__restrict__ d_v, cudaStream_t stream) {
+  return b200kv::kv_cache_write_bf16(d_cache_k, d_cache_v, config,
+                                     d_page_table, d_token_batch,
+                                     d_token_position, token_count, layer, d_k,
+                                     d_v, stream);
+}
+
+int64_t b200kv_cache_offset(const Gemma4KvCacheConfig *config, int32_t layer,
+                            int32_t page, int32_t page_offset, int32_t head,
+                            int32_t dim) {
+  return gemma4_kv_cache_offset(*config, layer, page, page_offset, head, dim);
+}
+
+void b200kv_make_config(Gemma4KvCacheConfig *out, int32_t global,
+                        int32_t num_pages, int32_t page_size,
+                        int32_t max_pages_per_seq) {
+  *out = gemma4_kv_cache_make_config(global != 0, num_pages, page_size,
+                                     max_pages_per_seq);
+}
+
+int32_t b200kv_is_global_layer(int32_t model_layer) {
+  return is_global_layer(model_layer) ? 1 : 0;
+}
+
+int32_t b200kv_layer_index(int32_t model_layer, int32_t global_cache) {
+  return gemma4_kv_cache_layer_index(model_layer, global_cache != 0);
+}
+
+int32_t b200kv_ensure_page(int32_t *h_page_table, int32_t *h_slot_logical_pages,
+                           const Gemma4KvCacheConfig *config, int32_t batch,
+                           int32_t position) {
+  // Direct map: sequence b owns physical pages [b*width, (b+1)*width). A slot
+  // that already holds a later logical page is stale for this position.
+  const int32_t logical_page = position / config->page_size;
+  const int32_t slot = logical_page % config->max_pages_per_seq;
+  const int64_t index = int64_t(batch) * config->max_pages_per_seq + slot;
+  if (h_slot_logical_pages[index] > logical_page) return -1;
+  const int32_t physical = batch * config->max_pages_per_seq + slot;
+  h_page_table[index] = physical;
+  h_slot_logical_pages[index] = logical_page;
+  return physical;
+}
+
+int32_t b200kv_ensure_range(int32_t *h_page_table,
+                            int32_t *h_slot_logical_pages,
+                            const Gemma4KvCacheConfig *config, int32_t batch,
+                            int32_t first_position, int32_t token_count) {
+  if (token_count == 0) return 0;
+  const int32_t first_page = first_position / config->page_size;
+  const int32_t last_page =
+      (first_position + token_count - 1) / config->page_size;
+  for (int32_t page = first_page; page <= last_page; ++page) {
+    if (b200kv_ensure_page(h_page_table, h_slot_logical_pages, config, batch,
+                           page * config->page_size) < 0) {
+      return -1;
+    }
+  }
+  return 0;
+}
+
+int32_t b200kv_sliding_pages_per_sequence(int32_t max_seq_len,
+                                          int32_t page_size) {
+  return sliding_pages(max_seq_len, page_size, 1024);
+}
+
+void b200kv_fill_rope_tables(float *h_cos, float *h_sin, int32_t max_seq_len,
+                             int32_t rotary_half, float theta,
+                             int32_t exponent_dim) {
+  // fp32 throughout, as the reference's table builder: the angle is the fp32
+  // product of the position and powf(theta, -2i/exponent_dim).
+  for (int32_t pos = 0; pos < max_seq_len; ++pos) {
+    float *c = h_cos + size_t(pos) * rotary_half;
+    float *s = h_sin + size_t(pos) * rotary_half;
+    for (int32_t i = 0; i < rotary_half; ++i) {
+      const float exponent = -2.0f * float(i) / float(exponent_dim);
+      const float angle = float(pos) * std::pow(theta, exponent);
+      c[i] = std::cos(angle);
+      s[i] = std::sin(angle);
+    }
+  }
+}
+
+void b200kv_runtime_geometry_default(B200KvRuntimeGeometry *out) {
+  *out = default_geometry();
+}
+
+int b200kv_runtime_state_create(B200KvRuntimeState **out, int32_t batch_size,
+                                int32_t max_seq_len, int32_t page_size,
+                                const B200KvRuntimeGeometry *geometry,
+                                b200kv_stream stream) {
+  if (out == nullptr) return cudaErrorInvalidValue;
+  *out = nullptr;
+  B200KvRuntimeState *handle = new (std::nothrow) B200KvRuntimeState();
+  if (handle == nullptr) return cudaErrorMemoryAllocation;
+  const cudaError_t st = gemma4_runtime_state_init_geometry(
+      &handle->state, batch_size, max_seq_len, page_size,
+      geometry != nullptr ? *geometry : default_geometry(),
+      static_cast<cudaStream_t>(stream));
+  if (st != cudaSuccess) {
+    delete handle;
+    return st;
+  }
+  *out = handle;
+  return cudaSuccess;
+}
+
+void b200kv_runtime_state_destroy(B200KvRuntimeState *state) {
+  if (state == nullptr) return;
+  gemma4_runtime_state_free(&state->state);
+  delete state;
+}
+
+int b200kv_runtime_prepare_prefill(B200KvRuntimeState *state, int32_t seq_len,
+                                   b200kv_stream stream) {
+  if (state == nullptr) return cudaErrorInvalidValue;
+  return gemma4_runtime_prepare_prefill(&state->state, seq_len,
+                                        static_cast<cudaStream_t>(stream));
+}
+
+int b200kv_runtime_prepare_decode_step(B200KvRuntimeState *state,
+                                       b200kv_stream stream) {
+  if (state == nullptr) return cudaErrorInvalidValue;
+  return gemma4_runtime_prepare_decode_step(&state->state,
+                                            static_cast<cudaStream_t>(stream));
+}
+
+void b200kv_runtime_state_view(B200KvRuntimeState *state,
+                               B200KvRuntimeView *out) {
+  Gemma4RuntimeState &s = state->state;
+  out->batch_size = s.batch_size;
+  out->max_seq_len = s.max_seq_len;
+  out->page_size = s.page_size;
+  out->token_count = s.token_count;
+  out->sliding_cache_config = s.sliding_cache_config;
+  out->global_cache_config = s.global_cache_config;
+  out->sliding_cache_k = reinterpret_cast<b200kv_bf16 *>(s.sliding_cache_k);
+  out->sliding_cache_v = reinterpret_cast<b200kv_bf16 *>(s.sliding_cache_v);
+  out->global_cache_k = reinterpret_cast<b200kv_bf16 *>(s.global_cache_k);
+  out->global_cache_v = reinterpret_cast<b200kv_bf16 *>(s.global_cache_v);
+  out->sliding_page_table = s.sliding_page_table;
+  out->global_page_table = s.global_page_table;
+  out->seq_lengths = s.seq_lengths;
+  out->token_batch = s.token_batch;
+  out->token_position = s.token_position;
+  out->sliding_cos = s.sliding_cos;
+  out->sliding_sin = s.sliding_sin;
+  out->global_cos = s.global_cos;
+  out->global_sin = s.global_sin;
+  out->h_sliding_page_table = s.h_sliding_page_table.data();
+  out->h_global_page_table = s.h_global_page_table.data();
+  out->h_sliding_slot_logical_pages = s.h_sliding_slot_logical_pages.data();
+  out->h_global_slot_logical_pages = s.h_global_slot_logical_pages.data();
+  out->h_seq_lengths = s.h_seq_lengths.data();
+  out->h_token_batch = s.h_token_batch.data();
+  out->h_token_position = s.h_token_position.data();
+  out->h_sliding_page_table_size = int64_t(s.h_sliding_page_table.size());
+  out->h_global_page_table_size = int64_t(s.h_global_page_table.size());
+  out->h_token_rows = int64_t(s.h_token_batch.size());
+}
+
+int b200kv_prefill_prep_bf16(b200kv_bf16 *d_q_prepared,
+                             b200kv_bf16 *d_k_prepared,
+                             b200kv_bf16 *d_v_prepared, const b200kv_bf16 *d_q,
+                             const b200kv_bf16 *d_k, const b200kv_bf16 *d_v,
+                             const b200kv_bf16 *d_q_norm_weight,
+                             const b200kv_bf16 *d_k_norm_weight,
+                             const float *d_cos, const float *d_sin,
+                             const int32_t *d_token_position, int64_t rows,
+                             int32_t q_heads, int32_t kv_heads,
+                             int32_t head_dim, int32_t rotary_dim,
+                             int32_t norm_mode, b200kv_stream stream) {
+  using bf = __nv_bfloat16;
+  b200kv::PrefillPrepArgs a;
+  a.q_prepared = reinterpret_cast<bf *>(d_q_prepared);
+  a.k_prepared = reinterpret_cast<bf *>(d_k_prepared);
+  a.v_prepared = reinterpret_cast<bf *>(d_v_prepared);
+  a.q = reinterpret_cast<const bf *>(d_q);
+  a.k = reinterpret_cast<const bf *>(d_k);
+  a.v = reinterpret_cast<const bf *>(d_v);
+  a.q_norm_weight = reinterpret_cast<const bf *>(d_q_norm_weight);
+  a.k_norm_weight = reinterpret_cast<const bf *>(d_k_norm_weight);
+  a.cos = d_cos;
+  a.sin = d_sin;
+  a.token_position = d_token_position;
+  a.rows = rows;
+  a.q_heads = q_heads;
+  a.kv_heads = kv_heads;
+  a.head_dim = head_dim;
+  a.rotary_dim = rotary_dim;
+  a.norm_mode = norm_mode;
+  return b200kv::prefill_prep_bf16(a, static_cast<cudaStream_t>(stream));
+}
+
+int b200kv_decode_append_bf16(b200kv_bf16 *d_q_prepared,
+                              b200kv_bf16 *d_cache_k, b200kv_bf16 *d_cache_v,
+                              Gemma4KvCacheConfig cache_config,
+                              const int32_t *d_page_table,
+                              const int32_t *d_token_position,
+                              int32_t cache_layer, const b200kv_bf16 *d_q,
+                              const b200kv_bf16 *d_k, const b200kv_bf16 *d_v,
+                              const b200kv_bf16 *d_q_norm_weight,
+                              const b200kv_bf16 *d_k_norm_weight,
+                              const float *d_cos, const float *d_sin,
+                              int32_t batch_count, int32_t q_heads,
+                              int32_t rotary_dim, int32_t norm_mode,
+                              b200kv_stream stream) {
+  using bf = __nv_bfloat16;
+  b200kv::AppendArgs a;
+  a.q_prepared = reinterpret_cast<bf *>(d_q_prepared);
+  a.cache_k = reinterpret_cast<bf *>(d_cache_k);
+  a.cache_v = reinterpret_cast<bf *>(d_cache_v);
+  a.cfg = cache_config;
+  a.page_table = d_page_table;
+  a.token_position = d_token_position;
+  a.cache_layer = cache_layer;
+  a.q = reinterpret_cast<const bf *>(d_q);
+  a.k = reinterpret_cast<const bf *>(d_k);
+  a.v = reinterpret_cast<const bf *>(d_v);
+  a.q_norm_weight = reinterpret_cast<const bf *>(d_q_norm_weight);
+  a.k_norm_weight = reinterpret_cast<const bf *>(d_k_norm_weight);
+  a.cos = d_cos;
+  a.sin = d_sin;
+  a.batch_count = batch_count;
+  a.q_heads = q_heads;
+  a.rotary_dim = rotary_dim;
+  a.norm_mode = norm_mode;
+  return b200kv::decode_append_bf16(a, static_cast<cudaStream_t>(stream));
+}
+
+int b200kv_decode_attention_bf16(b200kv_bf16 *d_out, float *d_lse,
+                                 const b200kv_bf16 *d_q_prepared,
+                                 const b200kv_bf16 *d_cache_k,
+                                 const b200kv_bf16 *d_cache_v,
+                                 Gemma4KvCacheConfig cache_config,
+                                 const int32_t *d_page_table,
+                                 const int32_t *d_seq_lengths,
+                                 int32_t cache_layer, float softmax_scale,
+                                 int32_t split_size, int32_t num_splits,
+                                 int32_t batch_count, int32_t q_heads,
+                                 float *d_partial_m, float *d_partial_l,
+                                 float *d_partial_acc, int32_t *d_status,
+                                 b200kv_stream stream) {
+  using bf = __nv_bfloat16;
+  b200kv::DecodeArgs a;
+  a.out = reinterpret_cast<bf *>(d_out);
+  a.lse = d_lse;
+  a.q = reinterpret_cast<const bf *>(d_q_prepared);
+  a.cache_k = reinterpret_cast<const bf *>(d_cache_k);
+  a.cache_v = reinterpret_cast<const bf *>(d_cache_v);
+  a.cfg = cache_config;
+  a.page_table = d_page_table;
+  a.seq_lengths = d_seq_lengths;
+  a.layer = cache_layer;
+  a.softmax_scale = softmax_scale;
+  a.split_size = split_size;
+  a.num_splits = num_splits;
+  a.batch_count = batch_count;
+  a.q_heads = q_heads;
+  a.partial_m = d_partial_m;
+  a.partial_l = d_partial_l;
+  a.partial_acc = d_partial_acc;
+  a.status = d_status;
+  return b200kv::decode_attention_bf16(a, static_cast<cudaStream_t>(stream));
+}
+
+void b200kv_decode_workspace_bytes(int32_t batch_count, int32_t q_heads,
+                                   int32_t head_dim, int32_t num_splits,
+                                   size_t *partial_m_bytes,
+                                   size_t *partial_l_bytes,
+                                   size_t *partial_acc_bytes) {
+  const size_t rows = num_splits > 1
+                          ? size_t(batch_count) * q_heads * num_splits
+                          : 0;
+  if (partial_m_bytes) *partial_m_bytes = rows * sizeof(float);
+  if (partial_l_bytes) *partial_l_bytes = rows * sizeof(float);
+  if (partial_acc_bytes) *partial_acc_bytes = rows * head_dim * sizeof(float);
+}
+
+void b200kv_plan_splits(int32_t batch_count, int32_t max_live_keys,
+                        int32_t kv_heads, int32_t sm_count,
+                        int32_t *split_size, int32_t *num_splits) {
+  const int tile = b200kv::decode_stage_tokens(kv_heads);
+  const int64_t total = int64_t(std::max(batch_count, 1)) *
+                        std::max(max_live_keys, 1);
+  const int64_t target_ctas = int64_t(std::max(sm_count, 1)) * 4;
+  int64_t size = b200kv::div_up(total, target_ctas);
+  size = b200kv::div_up(size, int64_t(tile)) * tile;
+  size = std::min<int64_t>(std::max<int64_t>(size, tile), 32 * tile);
+  *split_size = int32_t(size);
+  *num_splits =
+      int32_t(std::max<int64_t>(1, b200kv::div_up(int64_t(max_live_keys), size)));
+}
+
+int b200kv_decode_layer_step_bf16(const B200KvLayerStepArgs *s,
+                                  b200kv_stream stream) {
+  if (s == nullptr) return cudaErrorInvalidValue;
+  using bf = __nv_bfloat16;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  b200kv::AppendArgs a;
+  a.q_prepared = reinterpret_cast<bf *>(s->q);
+  a.cache_k = reinterpret_cast<bf *>(s->cache_k);
+  a.cache_v = reinterpret_cast<bf *>(s->cache_v);
+  a.cfg = s->cache_config;
+  a.page_table = s->page_table;
+  a.token_position = s->token_position;
+  a.cache_layer = s->cache_layer;
+  a.q = reinterpret_cast<const bf *>(s->raw_q);
+  a.k = reinterpret_cast<const bf *>(s->raw_k);
+  a.v = reinterpret_cast<const bf *>(s->raw_v);
+  a.q_norm_weight = reinterpret_cast<const bf *>(s->q_norm_weight);
+  a.k_norm_weight = reinterpret_cast<const bf *>(s->k_norm_weight);
+  a.cos = s->cos;
+  a.sin = s->sin;
+  a.batch_count = s->batch_count;
+  a.q_heads = s->q_heads;
+  a.rotary_dim = s->rotary_dim;
+  a.norm_mode = s->norm_mode;
+
+  b200kv::DecodeArgs d;
+  d.out = reinterpret_cast<bf *>(s->out);
+  d.lse = s->lse;
+  d.q = reinterpret_cast<const bf *>(s->q);
+  d.cache_k = reinterpret_cast<const bf *>(s->cache_k);
+  d.cache_v = reinterpret_cast<const bf *>(s->cache_v);
+  d.cfg = s->cache_config;
+  d.page_table = s->page_table;
+  d.seq_lengths = s->seq_lengths;
+  d.layer = s->cache_layer;
+  d.softmax_scale = s->softmax_scale;
+  d.split_size = s->split_size;
+  d.num_splits = s->num_splits;
+  d.batch_count = s->batch_count;
+  d.q_heads = s->q_heads;
+  d.partial_m = s->partial_m;
+  d.partial_l = s->partial_l;
+  d.partial_acc = s->partial_acc;
+  d.status = s->status;
+
+  // Stream order makes the appended row visible to the attention kernel, the
+  // job the grid-wide barrier does inside the reference's fused layer kernel
+  // (src/gemma4_flash_attention_decode.cu:524).
+  const cudaError_t st_append = b200kv::decode_append_bf16(a, st);
+  if (st_append != cudaSuccess) return st_append;
+  if (s->event_before_attention != nullptr) {
+    B200KV_TRY(cudaEventRecord(
+        static_cast<cudaEvent_t>(s->event_before_attention), st));
+  }
+  const cudaError_t st_attn = b200kv::decode_attention_bf16(d, st);
+  if (st_attn != cudaSuccess) return st_attn;
+  if (s->event_after_attention != nullptr) {
+    B200KV_TRY(cudaEventRecord(
+        static_cast<cudaEvent_t>(s->event_after_attention), st));
+  }
+  return cudaSuccess;
+}
+
+int b200kv_decode_step_bf16(const B200KvLayerStepArgs *layers,
+                            int32_t layer_count, b200kv_stream stream) {
+  if (layers == nullptr || layer_count < 0) return cudaErrorInvalidValue;
+  for (int32_t i = 0; i < layer_count; ++i) {
+    const int st = b200kv_decode_layer_step_bf16(layers + i, stream);
+    if (st != cudaSuccess) return st;
+  }
+  return cudaSuccess;
+}
+
+int b200kv_timer_create(void **event) {
+  if (event == nullptr) return cudaErrorInvalidValue;
+  cudaEvent_t ev = nullptr;
+  const cudaError_t st = cudaEventCreate(&ev);
+  *event = ev;
+  return st;
+}
+
+int b200kv_timer_destroy(void *event) {
+  return event == nullptr ? cudaSuccess
+                          : cudaEventDestroy(static_cast<cudaEvent_t>(event));
+}
+
+int b200kv_timer_record(void *event, b200kv_stream stream) {
+  if (event == nullptr) return cudaErrorInvalidValue;
+  return cudaEventRecord(static_cast<cudaEvent_t>(event),
+                         static_cast<cudaStream_t>(stream));
+}
+
+int b200kv_timer_elapsed_ms(void *begin, void *end, float *ms) {
+  if (begin == nullptr || end == nullptr || ms == nullptr) {
+    return cudaErrorInvalidValue;
+  }
+  return cudaEventElapsedTime(ms, static_cast<cudaEvent_t>(begin),
+                              static_cast<cudaEvent_t>(end));
+}
+
+int32_t b200kv_compiled_arch(void) { return 1000; }
+
+}  // extern "C"

@@ -1,0 +1,94 @@
+// Internal C++ interface between the kernel translation units and the C ABI.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/gemma4_b200kv.hpp"
+
+namespace b200kv {
+
+struct DecodeArgs {
+  __nv_bfloat16 *out = nullptr;
+  float *lse = nullptr;
+  const __nv_bfloat16 *q = nullptr;
+  const __nv_bfloat16 *cache_k = nullptr;
+  const __nv_bfloat16 *cache_v = nullptr;
+  Gemma4KvCacheConfig cfg = {};
+  const int32_t *page_table = nullptr;
+  const int32_t *seq_lengths = nullptr;
+  int32_t layer = 0;
+  float softmax_scale = 0.0f;
+  int32_t split_size = 0;
+  int32_t num_splits = 0;
+  int32_t batch_count = 0;
+  int32_t q_heads = 0;
+  float *partial_m = nullptr;
+  float *partial_l = nullptr;
+  float *partial_acc = nullptr;
+  int32_t *status = nullptr;
+};
+
+cudaError_t decode_attention_bf16(const DecodeArgs &args, cudaStream_t stream);
+
+// Key tile of the split kernel for a given KV-head count: split sizes that
+// are multiples of it keep every shared-memory stage full.
+int decode_stage_tokens(int kv_heads);
+
+struct AppendArgs {
+  __nv_bfloat16 *q_prepared = nullptr;
+  __nv_bfloat16 *cache_k = nullptr;
+  __nv_bfloat16 *cache_v = nullptr;
+  Gemma4KvCacheConfig cfg = {};
+  const int32_t *page_table = nullptr;
+  const int32_t *token_position = nullptr;
+  int32_t cache_layer = 0;
+  const __nv_bfloat16 *q = nullptr;
+  const __nv_bfloat16 *k = nullptr;
+  const __nv_bfloat16 *v = nullptr;  // nullptr: V is derived from raw K
+  const __nv_bfloat16 *q_norm_weight = nullptr;
+  const __nv_bfloat16 *k_norm_weight = nullptr;
+  const float *cos = nullptr;
+  const float *sin = nullptr;
+  int32_t batch_count = 0;
+  int32_t q_heads = 0;
+  int32_t rotary_dim = 0;
+  int32_t norm_mode = B200KV_NORM_RSQRT_APPROX;
+};
+
+cudaError_t decode_append_bf16(const AppendArgs &args, cudaStream_t stream);
+
+struct PrefillPrepArgs {
+  __nv_bfloat16 *q_prepared = nullptr;
+  __nv_bfloat16 *k_prepared = nullptr;
+  __nv_bfloat16 *v_prepared = nullptr;
+  const __nv_bfloat16 *q = nullptr;
+  const __nv_bfloat16 *k = nullptr;
+  const __nv_bfloat16 *v = nullptr;  // nullptr: V is derived from raw K
+  const __nv_bfloat16 *q_norm_weight = nullptr;
+  const __nv_bfloat16 *k_norm_weight = nullptr;
+  const float *cos = nullptr;
+  const float *sin = nullptr;
+  const int32_t *token_position = nullptr;
+  int64_t rows = 0;
+  int32_t q_heads = 0;
+  int32_t kv_heads = 0;
+  int32_t head_dim = 0;
+  int32_t rotary_dim = 0;
+  int32_t norm_mode = B200KV_NORM_RSQRT_APPROX;
+};
+
+cudaError_t prefill_prep_bf16(const PrefillPrepArgs &args,
+                              cudaStream_t stream);
+
+cudaError_t kv_cache_write_bf16(__nv_bfloat16 *cache_k, __nv_bfloat16 *cache_v,
+                                Gemma4KvCacheConfig config,
+                                const int32_t *page_table,
+                                const int32_t *token_batch,
+                                const int32_t *token_position,
+                                int32_t token_count, int32_t layer,
+                                const __nv_bfloat16 *k, const __nv_bfloat16 *v,
+                                cudaStream_t stream);
+
+}  // namespace b200kv

@@ -1,0 +1,326 @@
+/*
+ * C ABI of libgemma4_b200kv.so: the B200 (sm_100a) implementation of gemma.c's
+ * KV-cache hot path -- per-layer K/V append with QK-norm + RoPE fused into the
+ * write, the paged ring / linear cache, and the GQA split-KV flash-decode.
+ *
+ * Conventions shared by every entry point (they are the reference's,
+ * src/gemma4_kv_cache.cu:149-180 and src/gemma4_flash_attention_decode.cu:1122-1157):
+ *   - plain pointers and sizes only; every buffer is owned by the caller;
+ *     nothing here allocates or frees device memory unless its name says
+ *     "runtime_state";
+ *   - device pointers unless the parameter name starts with h_;
+ *   - the return value is a cudaError_t carried as int: 0 = cudaSuccess,
+ *     1 = cudaErrorInvalidValue for rejected host arguments; launch errors
+ *     come from cudaGetLastError();
+ *   - rows whose page, batch or position is invalid on the device are
+ *     silently skipped (tests/test_kv_cache.cu:94-133 pins this);
+ *   - work is enqueued on `stream` and is asynchronous; no call synchronises.
+ *
+ * bf16 tensors are passed as uint16_t* (bit patterns of __nv_bfloat16), fp8
+ * e4m3 as uint8_t*; `stream` is a cudaStream_t passed as void*.
+ */
+#ifndef GEMMA4_B200KV_H_
+#define GEMMA4_B200KV_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef uint16_t b200kv_bf16;
+typedef void *b200kv_stream;
+
+/* Same layout as src/gemma4_kv_cache.cuh:9-18 (8 x int32, passed by value).
+ * Cache tensors are [num_layers, num_pages, page_size, num_heads, head_dim];
+ * window_size == 0 means a linear (global) cache, > 0 a sliding ring. */
+#ifndef GEMMA4_KV_CACHE_CONFIG_DEFINED
+#define GEMMA4_KV_CACHE_CONFIG_DEFINED
+typedef struct Gemma4KvCacheConfig {
+  int32_t num_layers;
+  int32_t num_pages;
+  int32_t page_size;
+  int32_t max_pages_per_seq;
+  int32_t batch_size;
+  int32_t num_heads;
+  int32_t head_dim;
+  int32_t window_size;
+} Gemma4KvCacheConfig;
+#endif
+
+/* How the RMSNorm scale 1/sqrt(mean(x^2)+eps) is evaluated in the prep. */
+enum {
+  /* rsqrt.approx.f32 as the reference's GPU code does
+   * (src/gemma4_rmsnorm.cu:100): bit-identical to the reference kernels on
+   * the same GPU. */
+  B200KV_NORM_RSQRT_APPROX = 0,
+  /* IEEE sqrt and divide, round-to-nearest: bit-identical to a host
+   * restatement. */
+  B200KV_NORM_IEEE = 1
+};
+
+/* ------------------------------------------------------------------ *
+ * Cache write of already prepared rows.
+ * Replaces gemma4_kv_cache_write_bf16, src/gemma4_kv_cache.cuh:55-66
+ * (same name, argument order and error behaviour).
+ * ------------------------------------------------------------------ */
+#ifndef GEMMA4_B200KV_TYPED_CACHE_WRITE /* the .hpp declares it with CUDA types */
+int gemma4_kv_cache_write_bf16(b200kv_bf16 *d_cache_k, b200kv_bf16 *d_cache_v,
+                               Gemma4KvCacheConfig config,
+                               const int32_t *d_page_table,
+                               const int32_t *d_token_batch,
+                               const int32_t *d_token_position,
+                               int32_t token_count, int32_t layer,
+                               const b200kv_bf16 *d_k, const b200kv_bf16 *d_v,
+                               b200kv_stream stream);
+#endif
+
+/* ------------------------------------------------------------------ *
+ * Host-side geometry and page bookkeeping.
+ * ------------------------------------------------------------------ */
+/* gemma4_kv_cache_offset, src/gemma4_kv_cache.cuh:28-38. */
+int64_t b200kv_cache_offset(const Gemma4KvCacheConfig *config, int32_t layer,
+                            int32_t page, int32_t page_offset, int32_t head,
+                            int32_t dim);
+/* gemma4_kv_cache_make_config, src/gemma4_kv_cache.cu:76-91. */
+void b200kv_make_config(Gemma4KvCacheConfig *out, int32_t global,
+                        int32_t num_pages, int32_t page_size,
+                        int32_t max_pages_per_seq);
+/* gemma4_is_global_layer, src/gemma4.h:105-108. */
+int32_t b200kv_is_global_layer(int32_t model_layer);
+/* gemma4_kv_cache_layer_index, src/gemma4_kv_cache.cu:94-105. */
+int32_t b200kv_layer_index(int32_t model_layer, int32_t global_cache);
+/* gemma4_kv_cache_ensure_page, src/gemma4_kv_cache.cu:108-123. Arrays are
+ * host int32 [batch_size * max_pages_per_seq]. Returns the physical page or -1. */
+int32_t b200kv_ensure_page(int32_t *h_page_table, int32_t *h_slot_logical_pages,
+                           const Gemma4KvCacheConfig *config, int32_t batch,
+                           int32_t position);
+/* gemma4_kv_cache_ensure_range, src/gemma4_kv_cache.cu:126-146. 0 or -1. */
+int32_t b200kv_ensure_range(int32_t *h_page_table,
+                            int32_t *h_slot_logical_pages,
+                            const Gemma4KvCacheConfig *config, int32_t batch,
+                            int32_t first_position, int32_t token_count);
+/* sliding_pages_per_sequence, src/gemma4_runtime.cu:18-24. */
+int32_t b200kv_sliding_pages_per_sequence(int32_t max_seq_len,
+                                          int32_t page_size);
+/* fill_rope_tables, src/gemma4_runtime.cu:27-45: host fp32 tables
+ * [max_seq_len, rotary_half]. */
+void b200kv_fill_rope_tables(float *h_cos, float *h_sin, int32_t max_seq_len,
+                             int32_t rotary_half, float theta,
+                             int32_t exponent_dim);
+
+/* ------------------------------------------------------------------ *
+ * Runtime state (owner of caches, page tables and per-step metadata).
+ * Replaces Gemma4RuntimeState and its four functions,
+ * src/gemma4_runtime.cuh:12-64. The C++ struct of the same name and field
+ * order is in gemma4_b200kv.hpp; these wrappers give C callers a handle.
+ * ------------------------------------------------------------------ */
+typedef struct B200KvRuntimeState B200KvRuntimeState;
+
+/* Geometry of the two caches the state owns. The reference fixes these as
+ * compile-time constants (src/gemma4.h:17-23); here they are arguments so the
+ * same owner serves 8 KV x 256 global layers as well as the 1 KV x 512 ones. */
+typedef struct B200KvRuntimeGeometry {
+  int32_t sliding_layers, sliding_kv_heads, sliding_head_dim, sliding_window;
+  int32_t sliding_rotary_dim;
+  float sliding_rope_theta;
+  int32_t global_layers, global_kv_heads, global_head_dim;
+  int32_t global_rotary_dim;
+  float global_rope_theta;
+  int32_t global_rope_exponent_dim;
+} B200KvRuntimeGeometry;
+
+/* Reference geometry (src/gemma4.h:8-29). */
+void b200kv_runtime_geometry_default(B200KvRuntimeGeometry *out);
+/* gemma4_runtime_state_init, src/gemma4_runtime.cu:95-234. geometry may be
+ * NULL for the reference geometry. *out is NULL on failure. */
+int b200kv_runtime_state_create(B200KvRuntimeState **out, int32_t batch_size,
+                                int32_t max_seq_len, int32_t page_size,
+                                const B200KvRuntimeGeometry *geometry,
+                                b200kv_stream stream);
+/* gemma4_runtime_state_free, src/gemma4_runtime.cu:77-92. */
+void b200kv_runtime_state_destroy(B200KvRuntimeState *state);
+/* gemma4_runtime_prepare_prefill, src/gemma4_runtime.cu:237-273. */
+int b200kv_runtime_prepare_prefill(B200KvRuntimeState *state, int32_t seq_len,
+                                   b200kv_stream stream);
+/* gemma4_runtime_prepare_decode_step, src/gemma4_runtime.cu:276-341: all
+ * sequences are validated before anything is changed. */
+int b200kv_runtime_prepare_decode_step(B200KvRuntimeState *state,
+                                       b200kv_stream stream);
+
+typedef struct B200KvRuntimeView {
+  int32_t batch_size, max_seq_len, page_size, token_count;
+  Gemma4KvCacheConfig sliding_cache_config, global_cache_config;
+  b200kv_bf16 *sliding_cache_k, *sliding_cache_v;
+  b200kv_bf16 *global_cache_k, *global_cache_v;
+  int32_t *sliding_page_table, *global_page_table;
+  int32_t *seq_lengths, *token_batch, *token_position;
+  float *sliding_cos, *sliding_sin, *global_cos, *global_sin;
+  /* host mirrors (read/write: the reference's tests edit h_seq_lengths) */
+  int32_t *h_sliding_page_table, *h_global_page_table;
+  int32_t *h_sliding_slot_logical_pages, *h_global_slot_logical_pages;
+  int32_t *h_seq_lengths, *h_token_batch, *h_token_position;
+  int64_t h_sliding_page_table_size, h_global_page_table_size;
+  int64_t h_token_rows;
+} B200KvRuntimeView;
+void b200kv_runtime_state_view(B200KvRuntimeState *state,
+                               B200KvRuntimeView *out);
+
+/* ------------------------------------------------------------------ *
+ * Prep (per-head RMSNorm + RoPE) for a whole prompt into contiguous tensors:
+ * the first stage of gemma4_flash_attention_{sliding,global}_fwd_bf16_norm_rope,
+ * src/gemma4_flash_attention.cuh:9-45 (kernel src/gemma4_flash_attention_prefill.cu:1022-1103).
+ * q/q_prepared are [rows, q_heads, head_dim]; k, v and their outputs
+ * [rows, kv_heads, head_dim]; d_v == NULL derives V from raw K (global
+ * layers). Rows with a negative position are left untouched.
+ * ------------------------------------------------------------------ */
+int b200kv_prefill_prep_bf16(b200kv_bf16 *d_q_prepared,
+                             b200kv_bf16 *d_k_prepared,
+                             b200kv_bf16 *d_v_prepared, const b200kv_bf16 *d_q,
+                             const b200kv_bf16 *d_k, const b200kv_bf16 *d_v,
+                             const b200kv_bf16 *d_q_norm_weight,
+                             const b200kv_bf16 *d_k_norm_weight,
+                             const float *d_cos, const float *d_sin,
+                             const int32_t *d_token_position, int64_t rows,
+                             int32_t q_heads, int32_t kv_heads,
+                             int32_t head_dim, int32_t rotary_dim,
+                             int32_t norm_mode, b200kv_stream stream);
+
+/* ------------------------------------------------------------------ *
+ * Fused decode append: for every sequence b < batch_count, prep the new
+ * token's q heads into d_q_prepared and prep + store its K and V rows in the
+ * paged cache at position d_token_position[b].
+ * Replaces phase_decode_q_paged_kv_norm_rope,
+ * src/gemma4_flash_attention_decode.cu:305-375 (argument names follow it).
+ * q is [batch, q_heads, head_dim]; k, v are [batch, kv_heads, head_dim];
+ * d_v == NULL derives V from raw K.
+ * ------------------------------------------------------------------ */
+int b200kv_decode_append_bf16(b200kv_bf16 *d_q_prepared,
+                              b200kv_bf16 *d_cache_k, b200kv_bf16 *d_cache_v,
+                              Gemma4KvCacheConfig cache_config,
+                              const int32_t *d_page_table,
+                              const int32_t *d_token_position,
+                              int32_t cache_layer, const b200kv_bf16 *d_q,
+                              const b200kv_bf16 *d_k, const b200kv_bf16 *d_v,
+                              const b200kv_bf16 *d_q_norm_weight,
+                              const b200kv_bf16 *d_k_norm_weight,
+                              const float *d_cos, const float *d_sin,
+                              int32_t batch_count, int32_t q_heads,
+                              int32_t rotary_dim, int32_t norm_mode,
+                              b200kv_stream stream);
+
+/* ------------------------------------------------------------------ *
+ * Split-KV flash-decode over the paged cache, then the combine.
+ * Replaces phase_decode_paged_grouped_split + phase_decode_paged_reduce
+ * (+ the single-split direct path), src/gemma4_flash_attention_decode.cu:613-977,
+ * with the meaning of split_size / num_splits kept: split s of sequence b
+ * covers keys [first_key + s*split_size, min(seq_len, ... + split_size)),
+ * first_key = max(0, seq_len - window); splits beyond the live count do
+ * nothing; num_splits == 1 writes the output directly and needs no scratch.
+ *
+ * d_out [batch, q_heads, head_dim] bf16; d_lse [batch, q_heads] fp32 natural
+ * log-sum-exp of the scaled scores (may be NULL; -inf when no key is live);
+ * scratch as in src/gemma4_prompt.cu:231-248:
+ *   d_partial_m, d_partial_l  [batch * q_heads * num_splits] fp32
+ *   d_partial_acc             [batch * q_heads * num_splits * head_dim] fp32
+ * d_status: optional int32[4] device word block; a kernel that gives up a
+ * bounded wait writes a non-zero code to d_status[0] (see B200KV_STATUS_*).
+ * ------------------------------------------------------------------ */
+int b200kv_decode_attention_bf16(b200kv_bf16 *d_out, float *d_lse,
+                                 const b200kv_bf16 *d_q_prepared,
+                                 const b200kv_bf16 *d_cache_k,
+                                 const b200kv_bf16 *d_cache_v,
+                                 Gemma4KvCacheConfig cache_config,
+                                 const int32_t *d_page_table,
+                                 const int32_t *d_seq_lengths,
+                                 int32_t cache_layer, float softmax_scale,
+                                 int32_t split_size, int32_t num_splits,
+                                 int32_t batch_count, int32_t q_heads,
+                                 float *d_partial_m, float *d_partial_l,
+                                 float *d_partial_acc, int32_t *d_status,
+                                 b200kv_stream stream);
+
+enum {
+  B200KV_STATUS_OK = 0,
+  B200KV_STATUS_WAIT_TIMEOUT = 1 /* a bounded mbarrier wait ran out */
+};
+
+/* Bytes of scratch for the three partial buffers, in the order m, l, acc. */
+void b200kv_decode_workspace_bytes(int32_t batch_count, int32_t q_heads,
+                                   int32_t head_dim, int32_t num_splits,
+                                   size_t *partial_m_bytes,
+                                   size_t *partial_l_bytes,
+                                   size_t *partial_acc_bytes);
+
+/* Picks a split size (a multiple of the kernel's key tile) and the matching
+ * split count so that batch_count * num_splits fills the GPU's SMs a few
+ * times over; max_live_keys is the largest min(seq_len, window) in the batch.
+ * The reference hard-codes 20 keys per split (src/gemma4.h:24), tuned for an
+ * 84-SM GPU. */
+void b200kv_plan_splits(int32_t batch_count, int32_t max_live_keys,
+                        int32_t kv_heads, int32_t sm_count,
+                        int32_t *split_size, int32_t *num_splits);
+
+/* ------------------------------------------------------------------ *
+ * One layer-step = fused append + split-KV decode + combine, enqueued back to
+ * back on one stream. The fields carry the attention_* members of
+ * Gemma4DecodeMegakernelLayerArgs, src/gemma4_megakernel.cuh:42-66, with the
+ * same names minus the prefix; it stands where the three bracketed phases of
+ * decode_megakernel_fused_layer_kernel run
+ * (src/gemma4_flash_attention_decode.cu:514-523,1004-1031).
+ * ------------------------------------------------------------------ */
+typedef struct B200KvLayerStepArgs {
+  b200kv_bf16 *q;                 /* out: prepared q [batch, q_heads, head_dim] */
+  b200kv_bf16 *out;               /* out: attention [batch, q_heads, head_dim] */
+  float *lse;                     /* out, optional */
+  float *partial_m, *partial_l, *partial_acc;
+  b200kv_bf16 *cache_k, *cache_v;
+  Gemma4KvCacheConfig cache_config;
+  const int32_t *page_table;
+  const int32_t *token_position;
+  const int32_t *seq_lengths;
+  int32_t cache_layer;
+  int32_t split_size;
+  int32_t num_splits;
+  float softmax_scale;
+  const b200kv_bf16 *raw_q, *raw_k, *raw_v; /* this step's projections */
+  const b200kv_bf16 *q_norm_weight, *k_norm_weight;
+  const float *cos, *sin;
+  int32_t batch_count;
+  int32_t q_heads;
+  int32_t rotary_dim;
+  int32_t norm_mode;
+  int32_t *status;                /* optional int32[4] */
+  /* Optional profiling hooks: cudaEvent_t handles recorded on `stream` right
+   * before and right after the attention (split + combine) launches. */
+  void *event_before_attention;
+  void *event_after_attention;
+} B200KvLayerStepArgs;
+
+int b200kv_decode_layer_step_bf16(const B200KvLayerStepArgs *args,
+                                  b200kv_stream stream);
+
+/* One decode step over `layer_count` layers, enqueued in order on `stream`:
+ * the layer loop of gemma4_decode_megakernel, src/gemma4_decode_megakernel.cu:172-183,
+ * restricted to the KV path (the caller supplies each layer's projections). */
+int b200kv_decode_step_bf16(const B200KvLayerStepArgs *layers,
+                            int32_t layer_count, b200kv_stream stream);
+
+/* Timing events for the hooks above (cudaEventCreate / Destroy / ElapsedTime).
+ * No counterpart in the reference library; its benches time with the same
+ * CUDA events, src/benches/gemma4_bench_utils.cuh:336-370. */
+int b200kv_timer_create(void **event);
+int b200kv_timer_destroy(void *event);
+int b200kv_timer_record(void *event, b200kv_stream stream);
+int b200kv_timer_elapsed_ms(void *begin, void *end, float *ms);
+
+/* Library/version probe: returns the compiled SM architecture (1000 for
+ * sm_100a) so a loader can check it got the CUDA build. */
+int32_t b200kv_compiled_arch(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* GEMMA4_B200KV_H_ */

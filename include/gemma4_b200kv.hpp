@@ -1,0 +1,128 @@
+// C++ host interface of libgemma4_b200kv.so, source-compatible with the
+// declarations a gemma.c translation unit gets from
+//   src/gemma4_kv_cache.cuh:9-66   (config, offset, page helpers, cache write)
+//   src/gemma4_runtime.cuh:12-64   (Gemma4RuntimeState and its four functions)
+// so that code written against those headers builds against this one and
+// links to the B200 library instead of gemma4_kv_cache.cu / gemma4_runtime.cu.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <stdint.h>
+#include <vector>
+
+#define GEMMA4_KV_CACHE_CONFIG_DEFINED
+struct Gemma4KvCacheConfig {
+  int32_t num_layers;
+  int32_t num_pages;
+  int32_t page_size;
+  int32_t max_pages_per_seq;
+  int32_t batch_size;
+  int32_t num_heads;
+  int32_t head_dim;
+  int32_t window_size;
+};
+
+#define GEMMA4_B200KV_TYPED_CACHE_WRITE
+#include "gemma4_b200kv.h"
+
+// src/gemma4_kv_cache.cuh:55-66, same symbol as the C declaration.
+extern "C" cudaError_t gemma4_kv_cache_write_bf16(
+    __nv_bfloat16 *__restrict__ d_cache_k,
+    __nv_bfloat16 *__restrict__ d_cache_v, Gemma4KvCacheConfig config,
+    const int32_t *__restrict__ d_page_table,
+    const int32_t *__restrict__ d_token_batch,
+    const int32_t *__restrict__ d_token_position, int32_t token_count,
+    int32_t layer, const __nv_bfloat16 *__restrict__ d_k,
+    const __nv_bfloat16 *__restrict__ d_v, cudaStream_t stream);
+
+// src/gemma4_kv_cache.cu:76-91
+Gemma4KvCacheConfig gemma4_kv_cache_make_config(bool global, int32_t num_pages,
+                                                int32_t page_size,
+                                                int32_t max_pages_per_seq);
+
+// src/gemma4_kv_cache.cu:94-105
+int32_t gemma4_kv_cache_layer_index(int32_t model_layer, bool global_cache);
+
+// src/gemma4_kv_cache.cuh:28-38: flat offset into
+// [layer, page, page_offset, head, dim].
+__host__ __device__ constexpr inline int64_t gemma4_kv_cache_offset(
+    const Gemma4KvCacheConfig &config, int32_t layer, int32_t page,
+    int32_t page_offset, int32_t head, int32_t dim) {
+  return (((int64_t(layer) * config.num_pages + page) * config.page_size +
+           page_offset) *
+              config.num_heads +
+          head) *
+             config.head_dim +
+         dim;
+}
+
+// src/gemma4_kv_cache.cu:108-123
+int32_t gemma4_kv_cache_ensure_page(std::vector<int32_t> &page_table,
+                                    std::vector<int32_t> &slot_logical_pages,
+                                    const Gemma4KvCacheConfig &config,
+                                    int32_t batch, int32_t position);
+
+// src/gemma4_kv_cache.cu:126-146
+int32_t gemma4_kv_cache_ensure_range(std::vector<int32_t> &page_table,
+                                     std::vector<int32_t> &slot_logical_pages,
+                                     const Gemma4KvCacheConfig &config,
+                                     int32_t batch, int32_t first_position,
+                                     int32_t token_count);
+
+// src/gemma4_runtime.cuh:12-42. Member names, types and order are the
+// reference's; `geometry` is appended so one owner can also hold caches of a
+// non-default shape.
+struct Gemma4RuntimeState {
+  int32_t batch_size = 0;
+  int32_t max_seq_len = 0;
+  int32_t page_size = 0;
+  int32_t token_count = 0;
+
+  Gemma4KvCacheConfig sliding_cache_config = {};
+  Gemma4KvCacheConfig global_cache_config = {};
+  __nv_bfloat16 *sliding_cache_k = nullptr;
+  __nv_bfloat16 *sliding_cache_v = nullptr;
+  __nv_bfloat16 *global_cache_k = nullptr;
+  __nv_bfloat16 *global_cache_v = nullptr;
+
+  int32_t *sliding_page_table = nullptr;
+  int32_t *global_page_table = nullptr;
+  int32_t *seq_lengths = nullptr;
+  int32_t *token_batch = nullptr;
+  int32_t *token_position = nullptr;
+  float *sliding_cos = nullptr;
+  float *sliding_sin = nullptr;
+  float *global_cos = nullptr;
+  float *global_sin = nullptr;
+
+  std::vector<int32_t> h_sliding_page_table;
+  std::vector<int32_t> h_global_page_table;
+  std::vector<int32_t> h_sliding_slot_logical_pages;
+  std::vector<int32_t> h_global_slot_logical_pages;
+  std::vector<int32_t> h_seq_lengths;
+  std::vector<int32_t> h_token_batch;
+  std::vector<int32_t> h_token_position;
+
+  B200KvRuntimeGeometry geometry = {};
+};
+
+// src/gemma4_runtime.cu:95-234. `state` must be zero-initialised or freed.
+cudaError_t gemma4_runtime_state_init(Gemma4RuntimeState *state,
+                                      int32_t batch_size, int32_t max_seq_len,
+                                      int32_t page_size, cudaStream_t stream);
+// Same, for caches of another geometry.
+cudaError_t gemma4_runtime_state_init_geometry(
+    Gemma4RuntimeState *state, int32_t batch_size, int32_t max_seq_len,
+    int32_t page_size, const B200KvRuntimeGeometry &geometry,
+    cudaStream_t stream);
+// src/gemma4_runtime.cu:77-92
+void gemma4_runtime_state_free(Gemma4RuntimeState *state);
+// src/gemma4_runtime.cu:237-273
+cudaError_t gemma4_runtime_prepare_prefill(Gemma4RuntimeState *state,
+                                           int32_t seq_len,
+                                           cudaStream_t stream);
+// src/gemma4_runtime.cu:276-341
+cudaError_t gemma4_runtime_prepare_decode_step(Gemma4RuntimeState *state,
+                                               cudaStream_t stream);

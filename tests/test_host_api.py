@@ -1,0 +1,149 @@
+"""CPU-only checks of the product library: it loads, exports every symbol the header declares,
+and its host-side logic (geometry, page bookkeeping, RoPE tables, split planning) agrees with
+the oracle. No device call is made here."""
+from __future__ import annotations
+
+import re
+import subprocess
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+REPO = Path(__file__).resolve().parent.parent
+HEADER = REPO / "include" / "gemma4_b200kv.h"
+
+
+def _declared_in_header() -> set[str]:
+    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    names = set(re.findall(r"\b((?:b200kv|gemma4)_[a-z0-9_]+)\s*\(", text))
+    return names
+
+
+def test_library_exports_every_declared_symbol(kv):
+    lib = kv.load_library()
+    declared = _declared_in_header()
+    assert declared, "no declarations parsed from the header"
+    assert declared == set(kv.declared_symbols())
+    nm = subprocess.run(["nm", "-D", "--defined-only", str(kv.library_path())], capture_output=True, text=True)
+    exported = {line.split()[-1] for line in nm.stdout.splitlines() if line.strip()}
+    for name in declared:
+        assert name in exported, name
+        assert getattr(lib, name) is not None
+    assert lib.b200kv_compiled_arch() == 1000
+
+
+def test_make_config_and_layer_index_match_oracle(kv, orc):
+    for is_global in (False, True):
+        a = kv.make_config(is_global, 130, 16, 65)
+        b = orc.make_config(is_global, 130, 16, 65)
+        assert a.astuple() == tuple(getattr(b, n) for n, _ in b._fields_)
+    # five sliding layers then one global, and the last layer is global (src/gemma4.h:105-108)
+    pattern = [kv.is_global_layer(i) for i in range(48)]
+    assert pattern == [((i + 1) % 6 == 0) or i == 47 for i in range(48)]
+    assert sum(pattern) == 8
+    for layer in range(-1, 49):
+        for g in (False, True):
+            assert kv.layer_index(layer, g) == orc.lib().orc_layer_index(layer, int(g))
+    assert kv.layer_index(5, True) == 0 and kv.layer_index(11, True) == 1 and kv.layer_index(6, False) == 5
+    assert kv.layer_index(5, False) == -1
+
+
+def test_cache_offset_matches_oracle(kv, orc):
+    rng = np.random.default_rng(0)
+    for _ in range(200):
+        cfg = kv.make_kv_config(*(int(x) for x in rng.integers(1, 40, size=8)))
+        idx = [int(rng.integers(0, 30)) for _ in range(5)]
+        assert kv.cache_offset(cfg, *idx) == orc.cache_offset(cfg, *idx)
+    big = kv.make_kv_config(8, 70000, 16, 2049, 64, 8, 256, 0)
+    assert kv.cache_offset(big, 7, 69999, 15, 7, 255) == 8 * 70000 * 16 * 8 * 256 - 1   # needs int64
+
+
+def test_ensure_page_and_range_match_oracle(kv, orc):
+    rng = np.random.default_rng(1)
+    for trial in range(30):
+        page_size = int(rng.choice([1, 2, 4, 16, 64]))
+        mpps = int(rng.integers(1, 9))
+        batch = int(rng.integers(1, 4))
+        window = int(rng.choice([0, page_size * mpps]))
+        cfg = kv.make_kv_config(1, batch * mpps, page_size, mpps, batch, 2, 16, window)
+        ta = np.full(batch * mpps, -1, dtype=np.int32); sa = ta.copy()
+        tb = ta.copy(); sb = ta.copy()
+        for _ in range(60):
+            b = int(rng.integers(0, batch))
+            pos = int(rng.integers(0, page_size * mpps * 3))
+            if rng.random() < 0.5:
+                ra = kv.ensure_page(ta, sa, cfg, b, pos)
+                rb = orc.ensure_page(tb, sb, cfg, b, pos)
+            else:
+                n = int(rng.integers(0, 2 * page_size + 2))
+                ra = kv.ensure_range(ta, sa, cfg, b, pos, n)
+                rb = orc.ensure_range(tb, sb, cfg, b, pos, n)
+            assert ra == rb
+            assert np.array_equal(ta, tb) and np.array_equal(sa, sb)
+
+
+def test_stale_slot_is_refused(kv):
+    """src/gemma4_kv_cache.cu:117: a slot that already holds a later logical page rejects an
+    earlier one; the tables stay as they were."""
+    cfg = kv.make_kv_config(1, 2, 4, 2, 1, 1, 16, 8)
+    table = np.full(2, -1, dtype=np.int32); slots = table.copy()
+    assert kv.ensure_page(table, slots, cfg, 0, 9) == 0      # logical page 2 -> slot 0
+    before = (table.copy(), slots.copy())
+    assert kv.ensure_page(table, slots, cfg, 0, 1) == -1     # logical page 0 -> slot 0, stale
+    assert np.array_equal(table, before[0]) and np.array_equal(slots, before[1])
+    assert kv.ensure_range(table, slots, cfg, 0, 0, 0) == 0  # empty range is fine
+    assert kv.ensure_range(table, slots, cfg, 0, 0, 6) == -1
+
+
+def test_sliding_pages_per_sequence(kv, orc):
+    for max_seq in (1, 4, 66, 1024, 1025, 5000):
+        for page in (1, 2, 16, 64):
+            assert kv.sliding_pages_per_sequence(max_seq, page) == orc.lib().orc_sliding_pages_per_sequence(max_seq, page)
+    assert kv.sliding_pages_per_sequence(66, 64) == 2
+    assert kv.sliding_pages_per_sequence(4096, 16) == 65 and kv.sliding_pages_per_sequence(4096, 64) == 17
+
+
+@pytest.mark.parametrize("half,theta,exp_dim", [(128, 10000.0, 256), (64, 1000000.0, 512), (128, 1000000.0, 256)])
+def test_rope_tables_bit_exact_with_oracle(kv, orc, half, theta, exp_dim):
+    a = kv.fill_rope_tables(300, half, theta, exp_dim)
+    b = orc.fill_rope_tables(300, half, theta, exp_dim)
+    assert np.array_equal(a[0].view(np.uint32), b[0].view(np.uint32))
+    assert np.array_equal(a[1].view(np.uint32), b[1].view(np.uint32))
+
+
+def test_plan_splits_and_workspace(kv):
+    for batch, keys, heads in ((1, 1024, 8), (1, 4096, 8), (64, 32768, 8), (1, 131072, 8), (1, 131072, 1), (32, 8192, 8)):
+        size, count = kv.plan_splits(batch, keys, heads, 148)
+        tile = (16 // heads) * 4
+        assert size % tile == 0 and size >= tile
+        assert (count - 1) * size < keys <= count * size
+    assert kv.plan_splits(1, 0, 8, 148)[1] == 1
+    m, l, acc = kv.decode_workspace_bytes(64, 16, 256, 128)
+    assert (m, l, acc) == (64 * 16 * 128 * 4,) * 2 + (64 * 16 * 128 * 256 * 4,)
+    assert kv.decode_workspace_bytes(64, 16, 256, 1) == (0, 0, 0)
+
+
+def test_host_argument_rejection_needs_no_device(kv):
+    """Bad host arguments return cudaErrorInvalidValue before any launch
+    (src/gemma4_kv_cache.cu:162-173); an empty write is a success (:161)."""
+    cfg = kv.make_kv_config(1, 2, 4, 2, 1, 2, 16, 0)
+    assert kv.kv_cache_write(None, None, cfg, None, None, None, 0, 0, None, None, stream=0, check=False) == 0
+    assert kv.kv_cache_write(None, None, cfg, None, None, None, 1, 0, None, None, stream=0, check=False) == 1
+    bad = kv.make_kv_config(1, 2, 4, 2, 1, 2, 12, 0)     # head_dim not a multiple of 8
+    assert kv.kv_cache_write(16, 16, bad, 16, 16, 16, 1, 0, 16, 16, stream=0, check=False) == 1
+    assert kv.kv_cache_write(16, 16, cfg, 16, 16, 16, 1, 1, 16, 16, stream=0, check=False) == 1   # layer out of range
+    assert kv.kv_cache_write(16, 16, cfg, 16, 16, 16, -1, 0, 16, 16, stream=0, check=False) == 1
+    good = kv.make_kv_config(1, 64, 16, 64, 1, 8, 256, 1024)
+    args = dict(cache_layer=0, softmax_scale=1 / 16, split_size=64, num_splits=16, batch_count=1, q_heads=16,
+                stream=0, check=False)
+    assert kv.decode_attention(None, None, 16, 16, 16, good, 16, 16, **args) == 1          # null output
+    assert kv.decode_attention(16, None, 16, 16, 16, good, 16, 16, **args) == 1            # splits without scratch
+    tight = kv.make_kv_config(1, 32, 16, 32, 1, 8, 256, 1024)                               # ring < window
+    assert kv.decode_attention(16, None, 16, 16, 16, tight, 16, 16, **{**args, "num_splits": 1}) == 1
+    odd = kv.make_kv_config(1, 64, 16, 64, 1, 3, 256, 0)                                    # unknown geometry
+    assert kv.decode_attention(16, None, 16, 16, 16, odd, 16, 16, **{**args, "num_splits": 1, "q_heads": 6}) == 1
+    assert kv.decode_attention(16, None, 16, 16, 16, good, 16, 16, **{**args, "num_splits": 1, "softmax_scale": 0.0}) == 1
+    assert kv.decode_append(None, 16, 16, good, 16, 16, 0, 16, 16, 16, 16, 16, 16, 16, 1, 16, 256, stream=0, check=False) == 1
+    assert kv.decode_append(16, 16, 16, good, 16, 16, 0, 16, 16, 16, 16, 16, 16, 16, 1, 16, 100, stream=0, check=False) == 1
+    assert kv.decode_append(16, 16, 16, good, 16, 16, 0, 16, 16, 16, 16, 16, 16, 16, 0, 16, 256, stream=0, check=False) == 0
