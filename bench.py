@@ -1,0 +1,561 @@
+#!/usr/bin/env python
+"""Benchmark of the KV append + split-KV decode attention path on B200.
+
+Workload (BASELINE.json configs[2], the batched paged decode the metric's roofline target is quoted
+on): 64 sequences, context lengths uniform in [512, 32768] from a seed, 16-token pages in one pool
+with a randomly permuted block table, 16 Q / 8 KV heads, head_dim 256, bf16. One step = one decode
+step through one period of the 5:1 layer pattern: five sliding-window layers (ring of 1024 live
+keys) and one global layer (linear cache), each layer-step being fused append + split-KV decode +
+combine. Sequences are sharded over ranks (greedy longest-first on context length); no collective is
+on the data path.
+
+    python bench.py --gpus N --steps K --warmup W            # this library (CUDA, through the C-ABI)
+    python bench.py --impl reference --gpus N ...            # CPU restatement of the reference, all cores
+
+Prints one JSON line (rank 0).
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+import numpy as np
+
+REPO = Path(__file__).resolve().parent
+sys.path.insert(0, str(REPO))
+
+HQ, HKV, D, PAGE, WINDOW = 16, 8, 256, 16, 1024
+LOCAL_LAYERS, GLOBAL_LAYERS = 5, 1
+E_KV = 2  # bytes per cached element (bf16)
+METRIC = "KV append + decode attention: achieved HBM GB/s (us per layer-step alongside)"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--seqs", type=int, default=64)
+    ap.add_argument("--min-ctx", type=int, default=512)
+    ap.add_argument("--max-ctx", type=int, default=32768)
+    ap.add_argument("--seed", type=int, default=20260)
+    ap.add_argument("--e2e-steps", type=int, default=10)
+    ap.add_argument("--cpu-seconds", type=float, default=10.0, help="target CPU time of the cpu_baseline sample")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--split-global", type=int, default=0, help="override the planned global split size")
+    ap.add_argument("--split-local", type=int, default=0)
+    return ap.parse_args()
+
+
+# --------------------------------------------------------------------------- workload description
+def context_lengths(args) -> np.ndarray:
+    rng = np.random.default_rng(args.seed)
+    return rng.integers(args.min_ctx, args.max_ctx + 1, size=args.seqs).astype(np.int64)
+
+
+def shard_sequences(ctx: np.ndarray, world: int) -> list[list[int]]:
+    """Greedy longest-first partition of sequences over ranks by context length."""
+    order = np.argsort(-ctx, kind="stable")
+    load = [0] * world
+    shards: list[list[int]] = [[] for _ in range(world)]
+    for i in order:
+        r = int(np.argmin(load))
+        shards[r].append(int(i))
+        load[r] += int(ctx[i])
+    return shards
+
+
+def layer_step_bytes(seq_len_after_append: np.ndarray, window: int) -> int:
+    """Algorithmic HBM bytes of one layer-step (append + decode attention) for the given sequences."""
+    s = np.asarray(seq_len_after_append, dtype=np.int64)
+    live = np.minimum(s, window) if window > 0 else s
+    first = s - live
+    pages_touched = (s - 1) // PAGE - first // PAGE + 1
+    attn = live * HKV * D * 2 * E_KV + HQ * D * 2 + HQ * D * 2 + 4 * pages_touched
+    append = (HQ + 2 * HKV) * D * 2 + HQ * D * 2 + 2 * HKV * D * E_KV + 4
+    return int((attn + append).sum())
+
+
+def attention_kernel_bytes(seq_len_after_append: np.ndarray, window: int) -> int:
+    """Algorithmic bytes of the split-KV attention launch alone (K/V stream, q, output, page table)."""
+    s = np.asarray(seq_len_after_append, dtype=np.int64)
+    live = np.minimum(s, window) if window > 0 else s
+    first = s - live
+    pages_touched = (s - 1) // PAGE - first // PAGE + 1
+    return int((live * HKV * D * 2 * E_KV + HQ * D * 2 + HQ * D * 2 + 4 * pages_touched).sum())
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.path = tempfile.NamedTemporaryFile(prefix="clocks_", suffix=".csv", delete=False).name
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu=timestamp,{self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "20", "-i", str(gpu_index)],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+        self.marks: dict[str, float] = {}
+
+    def mark(self, name: str):
+        self.marks[name] = time.time()
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        import datetime as dt
+
+        rows = []
+        for line in open(self.path):
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                ts = dt.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                rows.append((ts, float(parts[1]), float(parts[2]), float(parts[3]), parts[4:]))
+            except ValueError:
+                continue
+        os.unlink(self.path)
+        t0, t1 = self.marks.get("timed_begin", 0.0), self.marks.get("timed_end", float("inf"))
+        inside = [r for r in rows if t0 <= r[0] <= t1]
+        window = "timed region"
+        if len(inside) < 3:   # region shorter than the sampling period: use everything sampled under load
+            lo, hi = self.marks.get("load_begin", 0.0), self.marks.get("load_end", float("inf"))
+            inside = [r for r in rows if lo <= r[0] <= hi]
+            window = "warm-up + timed + e2e (timed region shorter than the sampling period)"
+        if not inside:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"], "samples": 0}
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[4][1 + i].lower().startswith("active") for r in inside)]
+        return {"sm_mhz": statistics.median(r[1] for r in inside), "sm_max_mhz": inside[0][2],
+                "power_w_max": max(r[3] for r in inside), "reasons": reasons, "samples": len(inside),
+                "window": window}
+
+
+# --------------------------------------------------------------------------- device workload
+class RankWorkload:
+    """Everything one rank holds in HBM for its shard of sequences."""
+
+    def __init__(self, kv, torch, ctx: np.ndarray, total_steps: int, seed: int, args):
+        self.kv, self.torch = kv, torch
+        dev = "cuda"
+        self.B = B = int(ctx.size)
+        self.ctx = ctx
+        self.total_steps = total_steps
+        sm = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(seed)
+        rng = np.random.default_rng(seed)
+
+        def normal_bf16(n):
+            t = torch.empty(n, dtype=torch.bfloat16, device=dev)
+            t.normal_(generator=gen)
+            return t
+
+        # global layer: linear cache, one pool, permuted block table
+        pages_b = (ctx + total_steps + PAGE) // PAGE
+        self.g_pages = int(pages_b.sum())
+        self.g_mpps = int(pages_b.max())
+        table = np.full((B, self.g_mpps), -1, dtype=np.int32)
+        pool = rng.permutation(self.g_pages).astype(np.int32)
+        cur = 0
+        for b in range(B):
+            table[b, :pages_b[b]] = pool[cur:cur + pages_b[b]]
+            cur += int(pages_b[b])
+        self.g_cfg = kv.make_kv_config(GLOBAL_LAYERS, self.g_pages, PAGE, self.g_mpps, B, HKV, D, 0)
+        self.g_table = torch.from_numpy(table).to(dev)
+        self.g_k = normal_bf16(self.g_cfg.cache_elements())
+        self.g_v = normal_bf16(self.g_cfg.cache_elements())
+        # local layers: ring of window + one page of slack per sequence
+        self.l_mpps = (WINDOW + PAGE - 1 + PAGE - 1) // PAGE
+        self.l_pages = B * self.l_mpps
+        ltable = rng.permutation(self.l_pages).astype(np.int32).reshape(B, self.l_mpps)
+        self.l_cfg = kv.make_kv_config(LOCAL_LAYERS, self.l_pages, PAGE, self.l_mpps, B, HKV, D, WINDOW)
+        self.l_table = torch.from_numpy(ltable).to(dev)
+        self.l_k = normal_bf16(self.l_cfg.cache_elements())
+        self.l_v = normal_bf16(self.l_cfg.cache_elements())
+
+        # RoPE tables from the library's own host builder
+        max_pos = int(ctx.max()) + total_steps + 1
+        lc, ls = kv.fill_rope_tables(max_pos, D // 2, 10000.0, D)
+        gc, gs = kv.fill_rope_tables(max_pos, D // 2, 1000000.0, D)
+        self.l_cos, self.l_sin = torch.from_numpy(lc).to(dev), torch.from_numpy(ls).to(dev)
+        self.g_cos, self.g_sin = torch.from_numpy(gc).to(dev), torch.from_numpy(gs).to(dev)
+        w = torch.empty(2, D, dtype=torch.float32, device=dev).normal_(1.0, 0.05, generator=gen)
+        self.q_w, self.k_w = w[0].to(torch.bfloat16).contiguous(), w[1].to(torch.bfloat16).contiguous()
+
+        # this step's projections for every layer: [layers, B, (HQ + 2 HKV) * D]
+        L = LOCAL_LAYERS + GLOBAL_LAYERS
+        self.L = L
+        self.row = (HQ + 2 * HKV) * D
+        self.raw = normal_bf16(L * B * self.row).view(L, B, self.row)
+        self.raw_host = torch.empty((L, B, self.row), dtype=torch.bfloat16).pin_memory()
+        self.raw_host.copy_(self.raw)
+        self.raw_q = torch.empty((L, B, HQ * D), dtype=torch.bfloat16, device=dev)
+        self.raw_k = torch.empty((L, B, HKV * D), dtype=torch.bfloat16, device=dev)
+        self.raw_v = torch.empty((L, B, HKV * D), dtype=torch.bfloat16, device=dev)
+        self._unpack_raw()
+        self.q_prepared = torch.empty((L, B, HQ, D), dtype=torch.bfloat16, device=dev)
+        self.out = torch.empty((L, B, HQ, D), dtype=torch.bfloat16, device=dev)
+        self.out_host = torch.empty((L, B, HQ, D), dtype=torch.bfloat16).pin_memory()
+        self.lse = torch.empty((L, B, HQ), dtype=torch.float32, device=dev)
+        self.status = torch.zeros(4, dtype=torch.int32, device=dev)
+
+        # per-step metadata, resident: position of the appended token and length after the append
+        steps = np.arange(total_steps, dtype=np.int64)[:, None]
+        self.pos_all = torch.from_numpy((ctx[None, :] + steps).astype(np.int32)).to(dev)
+        self.len_all = torch.from_numpy((ctx[None, :] + steps + 1).astype(np.int32)).to(dev)
+
+        self.g_split, self.g_nsplit = kv.plan_splits(B, int(ctx.max()) + total_steps, HKV, sm)
+        self.l_split, self.l_nsplit = kv.plan_splits(B, WINDOW, HKV, sm)
+        if args.split_global:
+            self.g_split = args.split_global
+            self.g_nsplit = -(-(int(ctx.max()) + total_steps) // self.g_split)
+        if args.split_local:
+            self.l_split = args.split_local
+            self.l_nsplit = -(-WINDOW // self.l_split)
+        nmax = max(self.g_nsplit, self.l_nsplit)
+        rows = B * HQ * nmax
+        self.pm = torch.empty(rows, dtype=torch.float32, device=dev)
+        self.pl = torch.empty(rows, dtype=torch.float32, device=dev)
+        self.pacc = torch.empty(rows * D, dtype=torch.float32, device=dev)
+
+        self.layers = (kv.LayerStepArgs * L)()
+        self.ev_begin = [kv.Timer() for _ in range(total_steps)]
+        self.ev_end = [kv.Timer() for _ in range(total_steps)]
+        for i in range(L):
+            a = self.layers[i]
+            is_global = i == L - 1
+            a.q, a.out, a.lse = self.q_prepared[i].data_ptr(), self.out[i].data_ptr(), self.lse[i].data_ptr()
+            a.partial_m, a.partial_l, a.partial_acc = self.pm.data_ptr(), self.pl.data_ptr(), self.pacc.data_ptr()
+            a.cache_k = (self.g_k if is_global else self.l_k).data_ptr()
+            a.cache_v = (self.g_v if is_global else self.l_v).data_ptr()
+            a.cache_config = self.g_cfg if is_global else self.l_cfg
+            a.page_table = (self.g_table if is_global else self.l_table).data_ptr()
+            a.cache_layer = 0 if is_global else i
+            a.split_size = self.g_split if is_global else self.l_split
+            a.num_splits = self.g_nsplit if is_global else self.l_nsplit
+            a.softmax_scale = 1.0 / math.sqrt(D)
+            a.raw_q, a.raw_k, a.raw_v = self.raw_q[i].data_ptr(), self.raw_k[i].data_ptr(), self.raw_v[i].data_ptr()
+            a.q_norm_weight, a.k_norm_weight = self.q_w.data_ptr(), self.k_w.data_ptr()
+            a.cos = (self.g_cos if is_global else self.l_cos).data_ptr()
+            a.sin = (self.g_sin if is_global else self.l_sin).data_ptr()
+            a.batch_count, a.q_heads, a.rotary_dim, a.norm_mode = B, HQ, D, kv.NORM_RSQRT_APPROX
+            a.status = self.status.data_ptr()
+        self.stream = torch.cuda.current_stream().cuda_stream
+        self.launches_per_step = L * 3   # append, split, combine per layer (combine only when num_splits > 1)
+        if self.g_nsplit == 1:
+            self.launches_per_step -= 1
+        if self.l_nsplit == 1:
+            self.launches_per_step -= LOCAL_LAYERS
+
+    def _unpack_raw(self):
+        q, k, v = self.raw.split([HQ * D, HKV * D, HKV * D], dim=2)
+        self.raw_q.copy_(q)
+        self.raw_k.copy_(k)
+        self.raw_v.copy_(v)
+
+    def step(self, s: int):
+        """One decode step, inputs resident in HBM."""
+        pos = self.pos_all[s].data_ptr()
+        length = self.len_all[s].data_ptr()
+        g = self.layers[self.L - 1]
+        for i in range(self.L):
+            self.layers[i].token_position = pos
+            self.layers[i].seq_lengths = length
+        g.event_before_attention = self.ev_begin[s].handle
+        g.event_after_attention = self.ev_end[s].handle
+        self.kv.decode_step(self.layers, self.L, stream=self.stream)
+
+    def step_e2e(self, s: int):
+        """The same step called with host buffers: projections come from pinned host memory and the
+        attention outputs go back to the host, every step."""
+        torch = self.torch
+        self.raw.copy_(self.raw_host, non_blocking=True)
+        self._unpack_raw()
+        self.step(s)
+        self.out_host.copy_(self.out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    def bytes_for_step(self, s: int) -> tuple[int, int]:
+        after = self.ctx + s + 1
+        return (LOCAL_LAYERS * layer_step_bytes(after, WINDOW) + GLOBAL_LAYERS * layer_step_bytes(after, 0),
+                attention_kernel_bytes(after, 0))
+
+
+# --------------------------------------------------------------------------- CPU baseline
+def cpu_layer_step_sample(ctx: np.ndarray, threads: int, target_seconds: float, max_keys: int = 131072):
+    """Times the CPU restatement (oracle) on a bounded sample of the same workload: the global layer-step
+    for the first sequences of the batch (about `max_keys` keys, 1 GiB of K+V), repeated until roughly
+    `target_seconds` of host time have passed."""
+    from oracle import binding as orc
+
+    orc.build()
+    rng = np.random.default_rng(1)
+    chosen, total = [], 0
+    for c in ctx:
+        if chosen and total + int(c) > max_keys:
+            break
+        chosen.append(int(c))
+        total += int(c)
+    sample_ctx = np.array(chosen, dtype=np.int64)
+    B = sample_ctx.size
+    pages_b = (sample_ctx + 1 + PAGE - 1) // PAGE
+    num_pages, mpps = int(pages_b.sum()), int(pages_b.max())
+    table = np.full((B, mpps), -1, dtype=np.int32)
+    pool = rng.permutation(num_pages).astype(np.int32)
+    cur = 0
+    for b in range(B):
+        table[b, :pages_b[b]] = pool[cur:cur + pages_b[b]]
+        cur += int(pages_b[b])
+    cfg = (1, num_pages, PAGE, mpps, B, HKV, D, 0)
+    elems = num_pages * PAGE * HKV * D
+    block = orc.f32_to_bf16(rng.standard_normal(1 << 22, dtype=np.float32))
+    reps = -(-elems // block.size)
+    ck = np.tile(block, reps)[:elems].copy()
+    cv = np.tile(block[::-1], reps)[:elems].copy()
+    q = orc.f32_to_bf16(rng.standard_normal((B, HQ, D), dtype=np.float32))
+    k = orc.f32_to_bf16(rng.standard_normal((B, HKV, D), dtype=np.float32))
+    v = orc.f32_to_bf16(rng.standard_normal((B, HKV, D), dtype=np.float32))
+    w = orc.f32_to_bf16(np.ones(D, dtype=np.float32))
+    cos, sin = orc.fill_rope_tables(int(sample_ctx.max()) + 1, D // 2, 1000000.0, D)
+    pos = sample_ctx.astype(np.int32)
+    lens = (sample_ctx + 1).astype(np.int32)
+    out = np.zeros((B, HQ, D), dtype=np.uint16)
+    qp = np.zeros((B, HQ, D), dtype=np.uint16)
+    nbytes = layer_step_bytes(sample_ctx + 1, 0)
+    secs, runs = 0.0, 0
+    while runs < 1 or (secs < target_seconds and runs < 1000):
+        secs += orc.layer_step_timed(threads, out, qp, ck, cv, cfg, table, pos, lens, 0, q, k, v, w, w, cos, sin,
+                                     B, HQ, 1.0 / math.sqrt(D), 256)
+        runs += 1
+    return {"seconds": secs, "bytes": nbytes * runs, "gbps": nbytes * runs / secs / 1e9, "sequences": int(B),
+            "keys": int(sample_ctx.sum()) + int(B), "runs": runs, "us_per_layer_step": secs / runs * 1e6}
+
+
+def run_reference_arm(args):
+    """CPU restatement of the reference's path on all host cores; each step is one global layer-step over
+    a bounded sample of the workload's sequences."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import binding as orc
+
+    orc.build()
+    threads = orc.hardware_threads()
+    ctx = context_lengths(args)
+    per_step = max(0.5, min(args.cpu_seconds, 120.0 / max(1, args.steps + args.warmup)))
+    times, sample = [], None
+    for i in range(args.warmup + args.steps):
+        sample = cpu_layer_step_sample(ctx, threads, per_step)
+        if i >= args.warmup:
+            times.append(sample)
+    secs = sum(t["seconds"] for t in times)
+    nbytes = sum(t["bytes"] for t in times)
+    value = nbytes / secs / 1e9
+    desc = (f"global layer-step (append + split attention + reduce) over the first {sample['sequences']} "
+            f"sequences ({sample['keys']} keys) of the 64-sequence batch, {sample['runs']} passes per step")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs / len(times) * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": workload_config(args, 1, "cpu"),
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port", "sample": desc},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+        "note": "the reference has no CPU implementation of this path; this is the oracle port of its CUDA "
+                "phases (oracle/kv_oracle.cpp) on all host threads",
+    }
+    print(json.dumps(line))
+
+
+def workload_config(args, world, where):
+    return {
+        "workload": "configs[2]: batched paged decode, 64 sequences ctx~U[512,32768], 16-token pages, "
+                    "permuted block table, 16Q/8KV/D256 bf16; step = 5 sliding (window 1024) + 1 global layer-step",
+        "sequences": args.seqs, "ctx_range": [args.min_ctx, args.max_ctx], "seed": args.seed,
+        "page_size": PAGE, "layers_per_step": LOCAL_LAYERS + GLOBAL_LAYERS,
+        "parallelism": f"sequence-sharded x{world}, no collective",
+        "l2": "inputs larger than L2: every step streams more than 1 GB per rank before any byte is revisited",
+        "where": where,
+    }
+
+
+# --------------------------------------------------------------------------- main arm
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    from __graft_entry__ import load_package
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    kv = load_package()
+    kv.load_library(build_if_missing=False)
+    sampler = ClockSampler(local_rank) if rank == 0 else None   # started early: nvidia-smi takes a second to come up
+
+    ctx_all = context_lengths(args)
+    shards = shard_sequences(ctx_all, world)
+    ctx = ctx_all[shards[rank]]
+    e2e_warm = 3
+    total_steps = args.warmup + args.steps + e2e_warm + args.e2e_steps
+    wl = RankWorkload(kv, torch, ctx, total_steps, args.seed + 1000 * rank, args)
+    torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    if sampler:
+        sampler.mark("load_begin")
+    s = 0
+    for _ in range(args.warmup):
+        wl.step(s)
+        s += 1
+    barrier()
+    if sampler:
+        sampler.mark("timed_begin")
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    first_timed = s
+    t0.record()
+    for _ in range(args.steps):
+        wl.step(s)
+        s += 1
+    t1.record()
+    barrier()
+    if sampler:
+        sampler.mark("timed_end")
+    elapsed_ms = t0.elapsed_time(t1)
+    attn_ms = [wl.ev_begin[i].elapsed_ms(wl.ev_end[i]) for i in range(first_timed, first_timed + args.steps)]
+    step_bytes = sum(wl.bytes_for_step(i)[0] for i in range(first_timed, first_timed + args.steps))
+    attn_bytes = statistics.mean(wl.bytes_for_step(i)[1] for i in range(first_timed, first_timed + args.steps))
+    status = int(wl.status[0].item())
+
+    # end to end through host buffers
+    for _ in range(e2e_warm):
+        wl.step_e2e(s)
+        s += 1
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    first_e2e = s
+    e0.record()
+    for _ in range(args.e2e_steps):
+        wl.step_e2e(s)
+        s += 1
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+    e2e_bytes = sum(wl.bytes_for_step(i)[0] for i in range(first_e2e, first_e2e + args.e2e_steps))
+    if sampler:
+        sampler.mark("load_end")
+        clocks = sampler.stop()
+
+    stats = torch.tensor([elapsed_ms, e2e_ms, -float(step_bytes), -float(e2e_bytes), float(status),
+                          statistics.mean(attn_ms)], dtype=torch.float64, device="cuda")
+    if world > 1:
+        mx = stats.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        sm_ = stats.clone()
+        dist.all_reduce(sm_, op=dist.ReduceOp.SUM)
+        elapsed_ms, e2e_ms, status = mx[0].item(), mx[1].item(), int(mx[4].item())
+        step_bytes, e2e_bytes = -sm_[2].item(), -sm_[3].item()
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks_path = REPO / "MEASURED_PEAKS.json"
+    if peaks_path.exists():
+        peak, peak_src = float(json.loads(peaks_path.read_text())["hbm_gbs"]), "MEASURED_PEAKS.json hbm_gbs"
+    else:
+        peak, peak_src = 6650.0, "fallback 6.65 TB/s (MEASURED_PEAKS.json absent)"
+
+    value = step_bytes / (elapsed_ms * 1e-3) / 1e9
+    layer_steps = args.steps * wl.L
+    attn_achieved = attn_bytes / (statistics.mean(attn_ms) * 1e-3) / 1e9
+    line = {
+        "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": workload_config(args, world, "B200"),
+        "us_per_layer_step": elapsed_ms * 1e3 / layer_steps,
+        "us_global_layer_attention": statistics.mean(attn_ms) * 1e3,
+        "frac_of_hbm_peak": value / (peak * world),
+        "roofline": {
+            "bound": "hbm", "kernel": "decode_split_kernel + combine, global layer (rank 0)",
+            "achieved": attn_achieved, "peak": peak, "unit": "GB/s", "frac": attn_achieved / peak,
+            "traffic": None, "peak_source": peak_src,
+            "algorithmic_bytes_per_launch": attn_bytes, "avg_launch_ms": statistics.mean(attn_ms),
+        },
+        "e2e": {
+            "value": e2e_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
+            "h2d_bytes_per_step": int(wl.raw_host.numel() * 2), "d2h_bytes_per_step": int(wl.out_host.numel() * 2),
+            "steps": args.e2e_steps, "ms_per_step": e2e_ms / args.e2e_steps,
+            "note": "per rank, rank 0's copy sizes; host buffers are pinned, copies and a stream sync are inside "
+                    "the timed region every step",
+        },
+        "gpu_launches": wl.launches_per_step * args.steps,
+        "splits": {"global": [wl.g_split, wl.g_nsplit], "local": [wl.l_split, wl.l_nsplit]},
+        "device_status": status,
+        "clocks": clocks,
+    }
+    traffic_path = REPO / "profiles" / "decode_split_traffic.json"
+    if traffic_path.exists():
+        try:
+            t = json.loads(traffic_path.read_text())
+            line["roofline"]["traffic"] = t["dram_bytes_per_algorithmic_byte"] * attn_bytes
+            line["roofline"]["traffic_source"] = t.get("source")
+        except (ValueError, KeyError):
+            pass
+    if not args.no_cpu_baseline and world == 1:
+        threads = os.cpu_count() or 1
+        base = cpu_layer_step_sample(ctx_all, threads, args.cpu_seconds)
+        line["cpu_baseline"] = {
+            "value": base["gbps"], "unit": "GB/s", "cores": threads, "kind": "port",
+            "sample": f"global layer-step over the first {base['sequences']} sequences ({base['keys']} keys) of the "
+                      f"batch, repeated {base['runs']}x, {base['seconds']:.2f} s of host time, oracle port on all "
+                      f"host threads",
+        }
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -98,7 +98,7 @@ def test_fused_append_bit_exact_ieee(kv, orc, kw):
                       case.rotary_dim)
     assert np.array_equal(got_k, ck)
     assert np.array_equal(got_v, cv)
-    assert np.array_equal(got_q, qp)
+    assert np.array_equal(got_q, qp.reshape(-1))
 
 
 @pytest.mark.parametrize("kw", APPEND_CASES[:3])
@@ -110,7 +110,7 @@ def test_fused_append_rsqrt_mode_within_one_ulp(kv, orc, kw):
     orc.decode_append(qp, ck, cv, case.cfg, case.page_table, case.token_position, case.layer, case.q, case.k,
                       case.v, case.q_w, case.k_w, case.cos, case.sin, case.token_position.size, case.q_heads,
                       case.rotary_dim)
-    for got, want in ((got_k, ck), (got_v, cv), (got_q, qp)):
+    for got, want in ((got_k, ck), (got_v, cv), (got_q, qp.reshape(-1))):
         a = orc.bf16_to_f32(got).astype(np.float64)
         b = orc.bf16_to_f32(want).astype(np.float64)
         step = np.maximum(np.abs(b), 2.0 ** -100) * 2.0 ** -7
@@ -165,9 +165,9 @@ def test_prefill_prep_bit_exact_ieee(kv, orc, geometry):
     kv.prefill_prep(dq, dk, dv, dev(q), dev(k), dev(v) if has_v else None, dev(qw), dev(kw_), dev(cos), dev(sin),
                     dev(pos), rows, q_heads, kv_heads, D, rot, kv.NORM_IEEE)
     wq, wk, wv = orc.prefill_prep(q, k, v, qw, kw_, cos, sin, pos, q_heads, kv_heads, D, rot)
-    assert np.array_equal(host_u16(dq), wq)
-    assert np.array_equal(host_u16(dk), wk)
-    assert np.array_equal(host_u16(dv), wv)
+    assert np.array_equal(host_u16(dq), wq.reshape(-1))
+    assert np.array_equal(host_u16(dk), wk.reshape(-1))
+    assert np.array_equal(host_u16(dv), wv.reshape(-1))
 
 
 def test_global_prep_pins_of_the_reference_test(kv, orc):
