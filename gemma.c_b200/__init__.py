@@ -136,6 +136,7 @@ _SIGNATURES = {
     "b200kv_prefill_prep_bf16": (c_int, [_P] * 11 + [c_int64, c_int32, c_int32, c_int32, c_int32, c_int32, _P]),
     "b200kv_decode_append_bf16": (c_int, [_P, _P, _P, KvConfig, _P, _P, c_int32] + [_P] * 7 + [c_int32, c_int32, c_int32, c_int32, _P]),
     "b200kv_decode_attention_bf16": (c_int, [_P, _P, _P, _P, _P, KvConfig, _P, _P, c_int32, c_float, c_int32, c_int32, c_int32, c_int32, _P, _P, _P, _P, _P]),
+    "b200kv_decode_attention_static_scratch_bf16": (c_int, [_P, _P, _P, _P, _P, KvConfig, _P, _P, c_int32, c_float, c_int32, c_int32, c_int32, c_int32, _P, _P]),
     "b200kv_decode_workspace_bytes": (None, [c_int32, c_int32, c_int32, c_int32, POINTER(c_size_t), POINTER(c_size_t), POINTER(c_size_t)]),
     "b200kv_plan_splits": (None, [c_int32, c_int32, c_int32, c_int32, POINTER(c_int32), POINTER(c_int32)]),
     "b200kv_decode_layer_step_bf16": (c_int, [POINTER(LayerStepArgs), _P]),
@@ -362,6 +363,23 @@ def decode_attention(out, lse, q_prepared, cache_k, cache_v, cfg: KvConfig, page
         _ptr(seq_lengths), cache_layer, softmax_scale, split_size, num_splits, batch_count, q_heads,
         _ptr(partial_m), _ptr(partial_l), _ptr(partial_acc), _ptr(status), _stream(stream))
     return _check(code, "b200kv_decode_attention_bf16", check)
+
+
+STATIC_SCRATCH_BYTES = 16 << 20
+
+
+def decode_attention_static_scratch(out, lse, q_prepared, cache_k, cache_v, cfg: KvConfig, page_table, seq_lengths,
+                                    cache_layer: int, softmax_scale: float, split_size: int, num_splits: int,
+                                    batch_count: int, q_heads: int, status=None, stream=None,
+                                    check: bool = True) -> int:
+    """Decode attention whose split partials live in the library's built-in 16 MiB array: for callers
+    that cannot allocate scratch (no allocator of their own, all device memory already committed, or a
+    path that must not synchronise the device). Calls on one device share the array; keep them on one stream."""
+    code = load_library().b200kv_decode_attention_static_scratch_bf16(
+        _ptr(out), _ptr(lse), _ptr(q_prepared), _ptr(cache_k), _ptr(cache_v), cfg, _ptr(page_table),
+        _ptr(seq_lengths), cache_layer, softmax_scale, split_size, num_splits, batch_count, q_heads,
+        _ptr(status), _stream(stream))
+    return _check(code, "b200kv_decode_attention_static_scratch_bf16", check)
 
 
 def decode_layer_step(args: LayerStepArgs, stream=None, check: bool = True) -> int:

@@ -246,6 +246,36 @@ enum {
   B200KV_STATUS_WAIT_TIMEOUT = 1 /* a bounded mbarrier wait ran out */
 };
 
+/* The same attention for callers that cannot hand over scratch buffers: a
+ * serving engine that gave all device memory to its page pool at start-up, a
+ * plug-in that owns no allocator, or a latency path that must not pay the
+ * device-wide synchronisation of cudaMalloc / cudaFree. This entry point has
+ * no counterpart in the reference (whose callers always pass the partial
+ * buffers, src/gemma4_prompt.cu:231-248). The split partials live in an array
+ * of B200KV_STATIC_SCRATCH_BYTES that is part of the library image, held on
+ * every GPU the library is loaded on until the process exits; the call makes
+ * no cudaMalloc, cudaFree or other allocating call.
+ *   - Refused with cudaErrorInvalidValue (and a line on stderr) when
+ *     2 * round_up(batch*q_heads*num_splits, 64) * 4
+ *       + batch*q_heads*num_splits*head_dim*4 bytes exceed that size;
+ *     num_splits == 1 needs no scratch and is always accepted.
+ *   - The first call on each device looks the array's device address up
+ *     (cudaGetSymbolAddress, with that device current); make that first call
+ *     before any stream capture begins.
+ *   - All calls on a device share the array and it keeps the last call's
+ *     contents. Nothing needs clearing between calls, but calls whose kernels
+ *     may overlap on the GPU race on it: keep them on one stream.
+ * Arguments and results are those of b200kv_decode_attention_bf16 minus the
+ * three partial pointers. */
+#define B200KV_STATIC_SCRATCH_BYTES (16u << 20)
+int b200kv_decode_attention_static_scratch_bf16(
+    b200kv_bf16 *d_out, float *d_lse, const b200kv_bf16 *d_q_prepared,
+    const b200kv_bf16 *d_cache_k, const b200kv_bf16 *d_cache_v,
+    Gemma4KvCacheConfig cache_config, const int32_t *d_page_table,
+    const int32_t *d_seq_lengths, int32_t cache_layer, float softmax_scale,
+    int32_t split_size, int32_t num_splits, int32_t batch_count,
+    int32_t q_heads, int32_t *d_status, b200kv_stream stream);
+
 /* Bytes of scratch for the three partial buffers, in the order m, l, acc. */
 void b200kv_decode_workspace_bytes(int32_t batch_count, int32_t q_heads,
                                    int32_t head_dim, int32_t num_splits,
