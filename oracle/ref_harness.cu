@@ -1,0 +1,84 @@
+// Harness around the reference's OWN CUDA code for the KV hot path. TEST INFRASTRUCTURE ONLY.
+//
+// This translation unit #includes the reference's decode source where it lies (the build recipe puts
+// the reference's src/ directory on the include path; nothing of it is copied into this repository)
+// and adds stand-alone __global__ wrappers around its three hot phases with the CTA mapping the phases
+// were written for ("x = batch row, y = KV head, z = split", src/gemma4_flash_attention_decode.cu:715-716):
+//   phase_decode_q_paged_kv_norm_rope   (:305-375)  fused append
+//   phase_decode_paged_grouped_split    (:692-878)  split-KV attention
+//   phase_decode_paged_reduce           (:881-977)  combine
+// The fused layer kernel in that file also references the FFN device function, whose own source needs a
+// CUTLASS example that is not available; it is never launched here, so a stub satisfies the linker.
+// The result, oracle/_ref/libgemma4_ref.so, is a second checker beside the host oracle and the source
+// of the golden fixtures in tests/golden (recorded on a B200).
+#include "gemma4_flash_attention_decode.cu"
+
+extern "C" __device__ void gemma4_ffn_decode_fused_bf16_device(
+    __nv_bfloat16 *__restrict__, __nv_bfloat16 *__restrict__, const __nv_bfloat16 *__restrict__,
+    const __nv_bfloat16 *__restrict__, const __nv_bfloat16 *__restrict__, const __nv_bfloat16 *__restrict__,
+    const __nv_bfloat16 *__restrict__, Gemma4FfnDecodeScratch *__restrict__, const __nv_bfloat16 *__restrict__,
+    float) {}
+
+namespace {
+
+namespace ref = gemma4_flash_attention;
+using Sliding = ref::Gemma4AttentionTraits<false>;   // 8 KV heads x 256, rotary 256, own V projection
+constexpr int kThreads = ref::kDecodeMegaThreads;    // 512, the block size the phases run with in the product
+
+__global__ __launch_bounds__(kThreads) void ref_append_kernel(
+    __nv_bfloat16 *q_prepared, __nv_bfloat16 *cache_k, __nv_bfloat16 *cache_v, Gemma4KvCacheConfig cfg,
+    const int32_t *page_table, const int32_t *token_position, int cache_layer, const __nv_bfloat16 *q,
+    const __nv_bfloat16 *k, const __nv_bfloat16 *v, const __nv_bfloat16 *q_w, const __nv_bfloat16 *k_w,
+    const float *cos, const float *sin) {
+  ref::phase_decode_q_paged_kv_norm_rope<Sliding>(q_prepared, cache_k, cache_v, cfg, page_table, token_position,
+                                                  cache_layer, q, k, v, q_w, k_w, cos, sin, int(blockIdx.x),
+                                                  int(blockIdx.y), int(threadIdx.x));
+}
+
+__global__ __launch_bounds__(kThreads) void ref_split_kernel(
+    __nv_bfloat16 *out, float *pm, float *pl, float *pacc, const __nv_bfloat16 *q, const __nv_bfloat16 *cache_k,
+    const __nv_bfloat16 *cache_v, const int32_t *page_table, const int32_t *seq_lengths, Gemma4KvCacheConfig cfg,
+    int32_t layer, float scale, int32_t split_size, int32_t num_splits, int32_t batch_count) {
+  ref::phase_decode_paged_grouped_split<Sliding, kThreads>(out, pm, pl, pacc, q, cache_k, cache_v, page_table,
+                                                           seq_lengths, cfg, layer, scale, split_size, num_splits,
+                                                           int(blockIdx.x), int(blockIdx.y), int(blockIdx.z),
+                                                           int(threadIdx.x), batch_count);
+}
+
+__global__ __launch_bounds__(kThreads) void ref_reduce_kernel(
+    __nv_bfloat16 *out, const float *pm, const float *pl, const float *pacc, const int32_t *seq_lengths,
+    Gemma4KvCacheConfig cfg, int32_t split_size, int32_t num_splits) {
+  ref::phase_decode_paged_reduce<Sliding, kThreads>(out, pm, pl, pacc, seq_lengths, cfg, split_size, num_splits,
+                                                    int(blockIdx.x), int(blockIdx.y), int(threadIdx.x),
+                                                    int(blockDim.x));
+}
+
+}  // namespace
+
+extern "C" int ref_decode_append(__nv_bfloat16 *q_prepared, __nv_bfloat16 *cache_k, __nv_bfloat16 *cache_v,
+                                 Gemma4KvCacheConfig cfg, const int32_t *page_table, const int32_t *token_position,
+                                 int cache_layer, const __nv_bfloat16 *q, const __nv_bfloat16 *k,
+                                 const __nv_bfloat16 *v, const __nv_bfloat16 *q_w, const __nv_bfloat16 *k_w,
+                                 const float *cos, const float *sin, int batch_count, cudaStream_t stream) {
+  if (cfg.num_heads != Sliding::kKvHeads || cfg.head_dim != Sliding::kHeadDim) return cudaErrorInvalidValue;
+  ref_append_kernel<<<dim3(batch_count, Sliding::kKvHeads), kThreads, 0, stream>>>(
+      q_prepared, cache_k, cache_v, cfg, page_table, token_position, cache_layer, q, k, v, q_w, k_w, cos, sin);
+  return cudaGetLastError();
+}
+
+extern "C" int ref_decode_attention(__nv_bfloat16 *out, float *pm, float *pl, float *pacc, const __nv_bfloat16 *q,
+                                    const __nv_bfloat16 *cache_k, const __nv_bfloat16 *cache_v,
+                                    const int32_t *page_table, const int32_t *seq_lengths, Gemma4KvCacheConfig cfg,
+                                    int32_t layer, float scale, int32_t split_size, int32_t num_splits,
+                                    int32_t batch_count, cudaStream_t stream) {
+  if (cfg.num_heads != Sliding::kKvHeads || cfg.head_dim != Sliding::kHeadDim) return cudaErrorInvalidValue;
+  if (num_splits > 65535) return cudaErrorInvalidValue;
+  ref_split_kernel<<<dim3(batch_count, Sliding::kKvHeads, num_splits), kThreads, 0, stream>>>(
+      out, pm, pl, pacc, q, cache_k, cache_v, page_table, seq_lengths, cfg, layer, scale, split_size, num_splits,
+      batch_count);
+  cudaError_t st = cudaGetLastError();
+  if (st != cudaSuccess || num_splits == 1) return st;
+  ref_reduce_kernel<<<dim3(batch_count, GEMMA4_NUM_QUERY_HEADS), kThreads, 0, stream>>>(
+      out, pm, pl, pacc, seq_lengths, cfg, split_size, num_splits);
+  return cudaGetLastError();
+}

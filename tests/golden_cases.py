@@ -1,0 +1,59 @@
+"""Seeded cases whose expected outputs were recorded from the reference's own CUDA kernels on a B200
+(tests/golden/make_golden.py). Inputs are rebuilt from the seeds; a digest stored with each fixture
+guards against the generator drifting."""
+from __future__ import annotations
+
+import hashlib
+
+import numpy as np
+
+from tests.helpers import make_append_case, make_attn_case
+
+GEOM = dict(kv_heads=8, q_heads=16, head_dim=256)    # the geometry the reference's sliding traits are built for
+
+APPEND = {
+    "append_cfg1_tight_ring_wrap": dict(seed=9001, positions=[1024], window=1024, ring_pages=64, max_pos=1025),
+    "append_slack_ring_wrap": dict(seed=9002, positions=[1040], window=1024, max_pos=1041),
+    "append_linear_theta1e6_batch": dict(seed=9003, positions=[0, 15, 16, 4095], window=0, theta=1e6),
+    "append_page64": dict(seed=9004, positions=[63, 64, 200], window=0, page_size=64),
+}
+
+ATTENTION = {
+    # name: (case kwargs, split_size, num_splits)
+    "attn_cfg1_tight_ring_wrapped_split20": (dict(seed=9101, seq_lens=[1025], window=1024, ring_pages=64), 20, 52),
+    "attn_cfg1_single_split": (dict(seed=9101, seq_lens=[1025], window=1024, ring_pages=64), 1024, 1),
+    "attn_linear_4096_split64": (dict(seed=9102, seq_lens=[4096], window=0), 64, 64),
+    "attn_mixed_batch_overprovisioned": (dict(seed=9103, seq_lens=[300, 17, 1, 129, 700], window=0), 37, 25),
+    "attn_ring_mixed_batch": (dict(seed=9104, seq_lens=[5000, 90, 1024, 1025], window=1024), 20, 52),
+    "attn_page64_straddle": (dict(seed=9105, seq_lens=[1000, 65], window=0, page_size=64), 20, 50),
+    "attn_outliers": (dict(seed=9106, seq_lens=[3000], window=0, outlier_frac=0.01), 128, 24),
+}
+
+
+def build_append(name):
+    kw = dict(APPEND[name])
+    seed = kw.pop("seed")
+    return make_append_case(seed, **kw, **GEOM)
+
+
+def build_attention(name):
+    kw, split_size, num_splits = ATTENTION[name]
+    kw = dict(kw)
+    seed = kw.pop("seed")
+    return make_attn_case(seed, **kw, **GEOM), split_size, num_splits
+
+
+def digest(*arrays) -> str:
+    h = hashlib.sha256()
+    for a in arrays:
+        if a is not None:
+            h.update(np.ascontiguousarray(a).tobytes())
+    return h.hexdigest()
+
+
+def append_digest(case) -> str:
+    return digest(case.page_table, case.token_position, case.q, case.k, case.v, case.q_w, case.k_w, case.cos, case.sin)
+
+
+def attention_digest(case) -> str:
+    return digest(case.page_table, case.seq_lengths, case.q, case.cache_k, case.cache_v)
