@@ -54,6 +54,12 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--split-global", type=int, default=0, help="override the planned global split size")
     ap.add_argument("--split-local", type=int, default=0)
+    ap.add_argument("--partition", default="balanced", choices=["balanced", "splits"],
+                    help="balanced: keys of the batch divided evenly over a fixed grid (split_size 0); "
+                         "splits: fixed-size splits as the reference defines them")
+    ap.add_argument("--emulate-world", type=int, default=0,
+                    help="tuning aid: on one GPU, run the shard that rank --emulate-rank of this many ranks would own")
+    ap.add_argument("--emulate-rank", type=int, default=0)
     return ap.parse_args()
 
 
@@ -227,8 +233,12 @@ class RankWorkload:
         self.pos_all = torch.from_numpy((ctx[None, :] + steps).astype(np.int32)).to(dev)
         self.len_all = torch.from_numpy((ctx[None, :] + steps + 1).astype(np.int32)).to(dev)
 
-        self.g_split, self.g_nsplit = kv.plan_splits(B, int(ctx.max()) + total_steps, HKV, sm)
-        self.l_split, self.l_nsplit = kv.plan_splits(B, WINDOW, HKV, sm)
+        self.g_split, self.g_nsplit = kv.plan_splits_total(B, int(ctx.max()) + total_steps,
+                                                           int(ctx.sum()) + B * total_steps, HKV, sm)
+        self.l_split, self.l_nsplit = kv.plan_splits_total(B, WINDOW, B * WINDOW, HKV, sm)
+        if args.partition == "balanced":
+            self.g_split = self.l_split = 0
+            self.g_nsplit = self.l_nsplit = kv.plan_balanced(B, sm)
         if args.split_global:
             self.g_split = args.split_global
             self.g_nsplit = -(-(int(ctx.max()) + total_steps) // self.g_split)
@@ -265,9 +275,9 @@ class RankWorkload:
             a.status = self.status.data_ptr()
         self.stream = torch.cuda.current_stream().cuda_stream
         self.launches_per_step = L * 3   # append, split, combine per layer (combine only when num_splits > 1)
-        if self.g_nsplit == 1:
+        if self.g_nsplit == 1 and self.g_split > 0:
             self.launches_per_step -= 1
-        if self.l_nsplit == 1:
+        if self.l_nsplit == 1 and self.l_split > 0:
             self.launches_per_step -= LOCAL_LAYERS
 
     def _unpack_raw(self):
@@ -397,6 +407,7 @@ def workload_config(args, world, where):
         "sequences": args.seqs, "ctx_range": [args.min_ctx, args.max_ctx], "seed": args.seed,
         "page_size": PAGE, "layers_per_step": LOCAL_LAYERS + GLOBAL_LAYERS,
         "parallelism": f"sequence-sharded x{world}, no collective",
+        "partition": args.partition,
         "l2": "inputs larger than L2: every step streams more than 1 GB per rank before any byte is revisited",
         "where": where,
     }
@@ -432,6 +443,8 @@ def main():
     ctx_all = context_lengths(args)
     shards = shard_sequences(ctx_all, world)
     ctx = ctx_all[shards[rank]]
+    if args.emulate_world > 1 and world == 1:
+        ctx = ctx_all[shard_sequences(ctx_all, args.emulate_world)[args.emulate_rank]]
     e2e_warm = 3
     total_steps = args.warmup + args.steps + e2e_warm + args.e2e_steps
     wl = RankWorkload(kv, torch, ctx, total_steps, args.seed + 1000 * rank, args)

@@ -139,6 +139,8 @@ _SIGNATURES = {
     "b200kv_decode_attention_static_scratch_bf16": (c_int, [_P, _P, _P, _P, _P, KvConfig, _P, _P, c_int32, c_float, c_int32, c_int32, c_int32, c_int32, _P, _P]),
     "b200kv_decode_workspace_bytes": (None, [c_int32, c_int32, c_int32, c_int32, POINTER(c_size_t), POINTER(c_size_t), POINTER(c_size_t)]),
     "b200kv_plan_splits": (None, [c_int32, c_int32, c_int32, c_int32, POINTER(c_int32), POINTER(c_int32)]),
+    "b200kv_plan_balanced": (None, [c_int32, c_int32, POINTER(c_int32)]),
+    "b200kv_plan_splits_total": (None, [c_int32, c_int32, c_int64, c_int32, c_int32, POINTER(c_int32), POINTER(c_int32)]),
     "b200kv_decode_layer_step_bf16": (c_int, [POINTER(LayerStepArgs), _P]),
     "b200kv_decode_step_bf16": (c_int, [POINTER(LayerStepArgs), c_int32, _P]),
     "b200kv_timer_create": (c_int, [POINTER(_P)]),
@@ -256,6 +258,20 @@ def fill_rope_tables(max_seq_len: int, rotary_half: int, theta: float, exponent_
 def plan_splits(batch_count: int, max_live_keys: int, kv_heads: int, sm_count: int):
     size, count = c_int32(), c_int32()
     load_library().b200kv_plan_splits(batch_count, max_live_keys, kv_heads, sm_count, ctypes.byref(size), ctypes.byref(count))
+    return size.value, count.value
+
+
+def plan_balanced(batch_count: int, sm_count: int) -> int:
+    """num_splits to pass with split_size == 0 (balanced partition)."""
+    n = c_int32()
+    load_library().b200kv_plan_balanced(batch_count, sm_count, ctypes.byref(n))
+    return n.value
+
+
+def plan_splits_total(batch_count: int, max_live_keys: int, total_live_keys: int, kv_heads: int, sm_count: int):
+    size, count = c_int32(), c_int32()
+    load_library().b200kv_plan_splits_total(batch_count, max_live_keys, total_live_keys, kv_heads, sm_count,
+                                            ctypes.byref(size), ctypes.byref(count))
     return size.value, count.value
 
 

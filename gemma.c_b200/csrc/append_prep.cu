@@ -120,6 +120,20 @@ __global__ void decode_append_kernel(AppendArgs a) {
   const int G = a.q_heads / c.num_heads;
   const bool has_v = a.v != nullptr;
 
+  // The launch before this one may still be reading the q buffer or the
+  // cache this kernel is about to overwrite.
+  pdl_wait_for_predecessor();
+  pdl_release_successor();
+
+  // The row this warp preps does not depend on the position: fetch it first
+  // so its latency overlaps the position and page-table lookups.
+  const int64_t src = (int64_t(batch) * c.num_heads + kv_head) * D;
+  const __nv_bfloat16 *row_in =
+      warp < G ? a.q + (int64_t(batch) * a.q_heads + kv_head * G + warp) * D
+               : (warp == G || !has_v ? a.k + src : a.v + src);
+  float x[D / 32];
+  load_head<D>(row_in, lane, x);
+
   const int position = __ldg(a.token_position + batch);
   if (position < 0) return;
   const float *cos_row = a.cos + int64_t(position) * (ROT / 2);
@@ -127,8 +141,6 @@ __global__ void decode_append_kernel(AppendArgs a) {
 
   if (warp < G) {
     const int64_t off = (int64_t(batch) * a.q_heads + kv_head * G + warp) * D;
-    float x[D / 32];
-    load_head<D>(a.q + off, lane, x);
     prep_weighted_rope<D, ROT, kIeee>(a.q_prepared + off, x, a.q_norm_weight,
                                       cos_row, sin_row, lane);
     return;
@@ -144,17 +156,11 @@ __global__ void decode_append_kernel(AppendArgs a) {
   const int64_t dst = cache_offset(c, a.cache_layer, physical,
                                    position - logical_page * c.page_size,
                                    kv_head, 0);
-  const int64_t src = (int64_t(batch) * c.num_heads + kv_head) * D;
-
   if (warp == G) {
-    float x[D / 32];
-    load_head<D>(a.k + src, lane, x);
     prep_weighted_rope<D, ROT, kIeee>(a.cache_k + dst, x, a.k_norm_weight,
                                       cos_row, sin_row, lane);
     if (!has_v) prep_scale_free<D, kIeee>(a.cache_v + dst, x, lane);
   } else if (has_v) {
-    float x[D / 32];
-    load_head<D>(a.v + src, lane, x);
     prep_scale_free<D, kIeee>(a.cache_v + dst, x, lane);
   }
 }
@@ -277,10 +283,10 @@ cudaError_t decode_append_bf16(const AppendArgs &a, cudaStream_t stream) {
   const dim3 grid(a.batch_count, c.num_heads);
   return dispatch_geometry(
       c.head_dim, a.rotary_dim, a.norm_mode, [&](auto d, auto rot, auto ieee) {
-        decode_append_kernel<decltype(d)::value, decltype(rot)::value,
-                             decltype(ieee)::value>
-            <<<grid, warps * 32, 0, stream>>>(a);
-        return cudaGetLastError();
+        return launch_pdl(
+            decode_append_kernel<decltype(d)::value, decltype(rot)::value,
+                                 decltype(ieee)::value>,
+            grid, dim3(warps * 32), 0, stream, a);
       });
 }
 

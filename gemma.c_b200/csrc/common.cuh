@@ -5,6 +5,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <utility>
+
 #include "../../include/gemma4_b200kv.hpp"
 
 namespace b200kv {
@@ -148,8 +150,36 @@ __device__ __forceinline__ float bf16_hi(uint32_t w) {
   return __uint_as_float(w & 0xffff0000u);
 }
 
+// Programmatic dependent launch: a kernel launched with launch_pdl() may start
+// while its predecessor in the stream is still draining; it must not touch
+// anything the predecessor writes before pdl_wait_for_predecessor() returns
+// (which is when the predecessor has completed and its writes are visible).
+__device__ __forceinline__ void pdl_wait_for_predecessor() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_release_successor() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 __device__ __forceinline__ void set_status(int32_t *status, int32_t code) {
   if (status != nullptr) atomicCAS(status, 0, code);
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block,
+                              size_t smem_bytes, cudaStream_t stream,
+                              Args &&...args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem_bytes;
+  config.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attr;
+  config.numAttrs = 1;
+  return cudaLaunchKernelEx(&config, kernel, std::forward<Args>(args)...);
 }
 
 }  // namespace b200kv

@@ -1,0 +1,370 @@
+// Split-KV flash-decode with evenly balanced key ranges.
+//
+// The reference (and decode_attention.cu) cut every sequence into splits of a
+// fixed size and give each split a CTA; with ragged batches the CTA count is
+// whatever the lengths make it, so the last wave is partly empty and every CTA
+// pays its own pipeline fill and drain. Here the live keys of the whole batch
+// are laid end to end and divided into one contiguous range per CTA, the same
+// number of keys each. The grid is a fixed number of CTAs (two per SM), every
+// CTA streams the same amount of HBM, the producer's ring never drains at a
+// split boundary, and a sequence produces at most one partial per CTA that
+// touches it (a sequence that falls entirely inside one range is finished by
+// that CTA and never goes through scratch). The CTA walks the sequences of
+// its range in order; a query head's (m, l, acc) is flushed when the walk
+// leaves the sequence.
+//
+// Same math per stage as the fixed-split kernel (decode_common.cuh); same
+// results within fp32 summation order. Partials live in the caller's scratch:
+// the partial of CTA c for sequence b sits in slot c + b, which is unique
+// because ranges and sequences advance together.
+#include "decode_common.cuh"
+#include "kernels.cuh"
+
+namespace b200kv {
+
+namespace {
+
+constexpr int kMaxBalancedBatch = 1024;  // live-key prefix sums live in smem
+constexpr int kMinKeysPerCta = 16;       // below this a CTA is all latency
+
+struct BalancedParams {
+  __nv_bfloat16 *out;
+  float *lse;
+  const __nv_bfloat16 *q;
+  const __nv_bfloat16 *cache_k;
+  const __nv_bfloat16 *cache_v;
+  Gemma4KvCacheConfig cfg;
+  const int32_t *page_table;
+  const int32_t *seq_lengths;
+  int32_t layer;
+  float scale_log2;
+  int32_t batch_count;
+  int32_t q_heads;
+  float *partial_m;
+  float *partial_l;
+  float *partial_acc;
+  int32_t num_ctas;  // CTAs of the split kernel (the combine recomputes ranges)
+  int32_t *status;
+};
+
+__device__ __forceinline__ int range_width(int total, int num_ctas, int tile) {
+  const int even = div_up(div_up(total, num_ctas), tile) * tile;
+  return max(kMinKeysPerCta, even);
+}
+
+// Exclusive prefix sums of the live key counts into s_prefix[0..batch] and the
+// first live position of each sequence into s_first[0..batch). All threads of
+// the CTA call it; returns after a barrier.
+__device__ void scan_live_keys(const BalancedParams &p, int *s_prefix,
+                               int *s_first, int *s_warp_sums) {
+  const int tid = int(threadIdx.x);
+  const int nthreads = int(blockDim.x);
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+  const int per_thread = div_up(p.batch_count, nthreads);
+  const int b0 = tid * per_thread;
+  int counts[kMaxBalancedBatch / 256 + 1];
+  int sum = 0;
+  for (int i = 0; i < per_thread && i < int(sizeof(counts) / sizeof(int)); ++i) {
+    const int b = b0 + i;
+    int n = 0;
+    if (b < p.batch_count) {
+      const int len = __ldg(p.seq_lengths + b);
+      const int first = p.cfg.window_size > 0 ? max(0, len - p.cfg.window_size) : 0;
+      n = max(0, len - first);
+      s_first[b] = first;
+    }
+    counts[i] = n;
+    sum += n;
+  }
+  int incl = sum;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int t = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += t;
+  }
+  if (lane == 31) s_warp_sums[warp] = incl;
+  __syncthreads();
+  int offset = incl - sum;
+  for (int w = 0; w < warp; ++w) offset += s_warp_sums[w];
+  for (int i = 0; i < per_thread && i < int(sizeof(counts) / sizeof(int)); ++i) {
+    const int b = b0 + i;
+    if (b < p.batch_count) s_prefix[b] = offset;
+    offset += counts[i];
+  }
+  if (tid == nthreads - 1) s_prefix[p.batch_count] = offset;
+  __syncthreads();
+}
+
+struct Segment {
+  int b;      // sequence
+  int pos0;   // first key position of the piece
+  int pos1;   // one past the last
+  bool whole; // the piece is the sequence's entire live range
+};
+
+// Next piece of the flattened range [flat, r1): the part of one sequence.
+__device__ __forceinline__ bool next_segment(int &b, int &flat, int r1,
+                                             const int *s_prefix,
+                                             const int *s_first, Segment &seg) {
+  if (flat >= r1) return false;
+  while (s_prefix[b + 1] <= flat) ++b;  // sequences already done or empty
+  const int end = min(r1, s_prefix[b + 1]);
+  seg.b = b;
+  seg.pos0 = s_first[b] + (flat - s_prefix[b]);
+  seg.pos1 = s_first[b] + (end - s_prefix[b]);
+  seg.whole = flat == s_prefix[b] && end == s_prefix[b + 1];
+  flat = end;
+  return true;
+}
+
+template <class T>
+__global__ __launch_bounds__(T::kThreads, T::kCtasPerSm) void decode_balanced_kernel(
+    BalancedParams p) {
+  constexpr int G = T::G;
+  constexpr int ST = T::kStageTokens;
+  static_assert(T::kWarpsPerHead == 1, "one warp per KV head: no merge step");
+  extern __shared__ __align__(128) uint8_t smem[];
+  int *s_prefix = reinterpret_cast<int *>(smem + T::kRingBytes);
+  int *s_first = s_prefix + kMaxBalancedBatch + 1;
+  __shared__ int s_warp_sums[32];
+
+  const int warp = int(threadIdx.x) >> 5;
+  const int lane = int(threadIdx.x) & 31;
+  const Gemma4KvCacheConfig &cfg = p.cfg;
+
+  pdl_wait_for_predecessor();
+  pdl_release_successor();
+
+  scan_live_keys(p, s_prefix, s_first, s_warp_sums);
+  const int total = s_prefix[p.batch_count];
+  if (total == 0) return;  // the combine writes the zero rows
+  const int width = range_width(total, p.num_ctas, ST);
+  const int r0 = int(blockIdx.x) * width;
+  if (r0 >= total) return;
+  const int r1 = min(total, r0 + width);
+  int b_start = 0;
+  {
+    int lo = 0, hi = p.batch_count - 1;  // last b with prefix[b] <= r0
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (s_prefix[mid] <= r0) lo = mid; else hi = mid - 1;
+    }
+    b_start = lo;
+  }
+
+  const Ring<T> ring(smem);
+  if (threadIdx.x == 0) ring.init_barriers();
+  __syncthreads();
+
+  if (warp == T::kConsumerWarps) {
+    // ------------------------------ producer ------------------------------
+    const uint64_t policy = l2_policy_evict_first();
+    const KvSource src = {p.cache_k, p.cache_v, p.page_table, p.layer};
+    bool ok = true;
+    int it = 0;  // stages armed so far, across all pieces of the range
+    int b = b_start, flat = r0;
+    Segment seg;
+    while (ok && next_segment(b, flat, r1, s_prefix, s_first, seg)) {
+      const int a0 = (seg.pos0 / ST) * ST;
+      const int nchunks = div_up(seg.pos1 - a0, ST);
+      for (int c = 0; c < nchunks; ++c, ++it) {
+        const int stage = it % kStages;
+        const int fill = it / kStages;
+        if (fill > 0 &&
+            !mbar_wait_bounded(ring.empty_bar(stage), uint32_t(fill - 1) & 1u)) {
+          ok = false;
+          break;
+        }
+        const int base = a0 + c * ST;
+        producer_fill_stage<T>(ring, src, cfg, seg.b, base, max(seg.pos0, base),
+                               min(seg.pos1, base + ST), stage, policy, lane);
+      }
+    }
+    for (int s = 0; s < kStages && s < it; ++s) {
+      const int fill = (it - 1 - s) / kStages;
+      if (!mbar_wait_bounded(ring.full_bar(s), uint32_t(fill) & 1u)) ok = false;
+    }
+    if (!ok && lane == 0) set_status(p.status, B200KV_STATUS_WAIT_TIMEOUT);
+    return;
+  }
+
+  // -------------------------------- consumers --------------------------------
+  const int head = warp;  // kWarpsPerHead == 1
+  WarpState<T> st;
+  int b = b_start, flat = r0;
+  Segment seg, next;
+  bool have = next_segment(b, flat, r1, s_prefix, s_first, seg);
+  uint4 raw[G];
+  load_q_raw<T>(raw, p.q, int64_t(seg.b) * p.q_heads + head * G, lane);
+  int it = 0;
+  while (have) {
+    st.set_q(raw, p.scale_log2);
+    st.reset();
+    // Fetch the next sequence's query rows while this one streams.
+    const bool have_next = next_segment(b, flat, r1, s_prefix, s_first, next);
+    if (have_next) {
+      load_q_raw<T>(raw, p.q, int64_t(next.b) * p.q_heads + head * G, lane);
+    }
+    const int a0 = (seg.pos0 / ST) * ST;
+    const int nchunks = div_up(seg.pos1 - a0, ST);
+    for (int c = 0; c < nchunks; ++c, ++it) {
+      const int stage = it % kStages;
+      const int fill = it / kStages;
+      if (!mbar_wait_bounded(ring.full_bar(stage), uint32_t(fill) & 1u)) {
+        if (lane == 0) set_status(p.status, B200KV_STATUS_WAIT_TIMEOUT);
+        return;  // every other wait in this CTA is bounded as well
+      }
+      consume_stage<T>(st, ring, stage, head, 0, lane);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(ring.empty_bar(stage));
+    }
+    float l[G];
+    st.denominators(l, lane);
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const int q_head = head * G + g;
+      if (seg.whole) {
+        write_output_row<T>(p.out, p.lse, int64_t(seg.b) * p.q_heads + q_head,
+                            st.acc[g], st.m[g], l[g], lane);
+      } else {
+        const int64_t slot = int64_t(int(blockIdx.x) + seg.b) * p.q_heads + q_head;
+        write_partial_row<T>(p.partial_m, p.partial_l, p.partial_acc, slot,
+                             st.acc[g], st.m[g], l[g], lane);
+      }
+    }
+    seg = next;
+    have = have_next;
+  }
+}
+
+// One CTA per (sequence, q_head) row. Recomputes which CTAs touched the
+// sequence from the same prefix sums and combines their partials; rows that
+// one CTA finished alone are left as they are; empty rows are zeroed.
+template <int D>
+__global__ __launch_bounds__(kCombineThreads) void balanced_combine_kernel(
+    BalancedParams p, int tile) {
+  __shared__ float s_w[kCombineChunk];
+  __shared__ float s_red[kCombineThreads / 32];
+  __shared__ float4 s_val[kCombineGroups][D / 4];
+  __shared__ int s_sum[3][kCombineThreads / 32];
+  const int row = int(blockIdx.x);
+  const int b = row / p.q_heads;
+  const int q_head = row - b * p.q_heads;
+  const int tid = int(threadIdx.x);
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+
+  pdl_wait_for_predecessor();
+  pdl_release_successor();
+
+  int before = 0, all = 0, mine = 0;
+  for (int i = tid; i < p.batch_count; i += kCombineThreads) {
+    const int len = __ldg(p.seq_lengths + i);
+    const int first = p.cfg.window_size > 0 ? max(0, len - p.cfg.window_size) : 0;
+    const int n = max(0, len - first);
+    all += n;
+    if (i < b) before += n;
+    if (i == b) mine = n;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    before += __shfl_xor_sync(0xffffffffu, before, o);
+    all += __shfl_xor_sync(0xffffffffu, all, o);
+    mine += __shfl_xor_sync(0xffffffffu, mine, o);
+  }
+  if (lane == 0) {
+    s_sum[0][warp] = before;
+    s_sum[1][warp] = all;
+    s_sum[2][warp] = mine;
+  }
+  __syncthreads();
+  before = all = mine = 0;
+#pragma unroll
+  for (int w = 0; w < kCombineThreads / 32; ++w) {
+    before += s_sum[0][w];
+    all += s_sum[1][w];
+    mine += s_sum[2][w];
+  }
+
+  __nv_bfloat16 *out_row = p.out + int64_t(row) * D;
+  float *lse_row = p.lse != nullptr ? p.lse + row : nullptr;
+  if (mine == 0) {
+    combine_empty_row<D>(out_row, lse_row);
+    return;
+  }
+  const int width = range_width(all, p.num_ctas, tile);
+  const int c_first = before / width;
+  const int c_last = (before + mine - 1) / width;
+  if (c_first == c_last) return;  // finished by that CTA
+  combine_row<D>(out_row, lse_row, p.partial_m, p.partial_l, p.partial_acc,
+                 int64_t(c_first + b) * p.q_heads + q_head, p.q_heads,
+                 c_last - c_first + 1, s_w, s_red, s_val);
+}
+
+}  // namespace
+
+bool decode_balanced_supported(const Gemma4KvCacheConfig &c, int q_heads,
+                               int batch_count) {
+  return c.head_dim == 256 && c.num_heads == 8 && q_heads == 16 &&
+         batch_count <= kMaxBalancedBatch;
+}
+
+cudaError_t decode_attention_balanced_bf16(const DecodeArgs &a,
+                                           cudaStream_t stream) {
+  using T = DecodeTraits<256, 8, 2, 8>;
+  constexpr int kSmem = T::kRingBytes + (2 * kMaxBalancedBatch + 1) * 4;
+  static_assert(2 * kSmem <= 226 * 1024, "two CTAs per SM");
+  const Gemma4KvCacheConfig &c = a.cfg;
+  if (!decode_balanced_supported(c, a.q_heads, a.batch_count)) {
+    return cudaErrorInvalidValue;
+  }
+  int device = 0, sm_count = 0;
+  cudaError_t st = cudaGetDevice(&device);
+  if (st != cudaSuccess) return st;
+  st = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
+  if (st != cudaSuccess) return st;
+  // Scratch holds batch * num_splits slots per head; slot c + b needs
+  // num_ctas + batch - 1 of them.
+  const int64_t capacity = int64_t(a.batch_count) * a.num_splits;
+  const int64_t num_ctas =
+      std::min<int64_t>(int64_t(sm_count) * T::kCtasPerSm, capacity - a.batch_count);
+  if (num_ctas < 1 || a.partial_m == nullptr || a.partial_l == nullptr ||
+      a.partial_acc == nullptr) {
+    return cudaErrorInvalidValue;
+  }
+  BalancedParams p;
+  p.out = a.out;
+  p.lse = a.lse;
+  p.q = a.q;
+  p.cache_k = a.cache_k;
+  p.cache_v = a.cache_v;
+  p.cfg = c;
+  p.page_table = a.page_table;
+  p.seq_lengths = a.seq_lengths;
+  p.layer = a.layer;
+  p.scale_log2 = a.softmax_scale * 1.4426950408889634f;
+  p.batch_count = a.batch_count;
+  p.q_heads = a.q_heads;
+  p.partial_m = a.partial_m;
+  p.partial_l = a.partial_l;
+  p.partial_acc = a.partial_acc;
+  p.num_ctas = int32_t(num_ctas);
+  p.status = a.status;
+  st = cudaFuncSetAttribute(decode_balanced_kernel<T>,
+                            cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+  if (st != cudaSuccess) return st;
+  st = launch_pdl(decode_balanced_kernel<T>, dim3(unsigned(num_ctas)),
+                  dim3(T::kThreads), kSmem, stream, p);
+  if (st != cudaSuccess) return st;
+  return launch_pdl(balanced_combine_kernel<256>,
+                    dim3(a.batch_count * a.q_heads), dim3(kCombineThreads), 0,
+                    stream, p, int(T::kStageTokens));
+}
+
+int decode_balanced_num_splits(int batch_count, int sm_count) {
+  const int ctas = std::max(sm_count, 1) * 2;
+  return div_up(ctas, std::max(batch_count, 1)) + 1;
+}
+
+}  // namespace b200kv

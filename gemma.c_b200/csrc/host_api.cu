@@ -620,19 +620,53 @@ void b200kv_decode_workspace_bytes(int32_t batch_count, int32_t q_heads,
   if (partial_acc_bytes) *partial_acc_bytes = rows * head_dim * sizeof(float);
 }
 
+void b200kv_plan_balanced(int32_t batch_count, int32_t sm_count,
+                          int32_t *num_splits) {
+  *num_splits = b200kv::decode_balanced_num_splits(batch_count, sm_count);
+}
+
+void b200kv_plan_splits_total(int32_t batch_count, int32_t max_live_keys,
+                              int64_t total_live_keys, int32_t kv_heads,
+                              int32_t sm_count, int32_t *split_size,
+                              int32_t *num_splits) {
+  const int tile = b200kv::decode_stage_tokens(kv_heads);
+  const int64_t batch = std::max(batch_count, 1);
+  const int64_t longest = std::max(max_live_keys, 1);
+  const int64_t total = std::max<int64_t>(total_live_keys, 1);
+  // Resident CTAs: two per SM for the 8-KV-head kernel, one otherwise.
+  const int64_t slots = int64_t(std::max(sm_count, 1)) * (kv_heads == 8 ? 2 : 1);
+  // Cost in "keys of streaming time per slot": a CTA pays its keys plus a
+  // fixed fill/drain of about 6 keys' worth, and its partials (written once,
+  // read once) cost about 4 keys' worth of bandwidth shared by all slots.
+  int64_t best_size = tile;
+  double best_cost = 1e300;
+  for (int64_t size = tile; size <= 64 * tile; size += tile) {
+    // Upper bound of live CTAs: every sequence may end in a partial split.
+    const int64_t ctas = std::min(total / size + batch,
+                                  batch * b200kv::div_up(longest, size));
+    const int64_t waves = (ctas + slots - 1) / slots;
+    const bool single = size >= longest;  // one split per row: no partials
+    const double cost = double(waves) * double(size + 6) +
+                        (single ? 0.0 : 4.0 * double(ctas) / double(slots));
+    if (cost < best_cost - 1e-9 || (cost < best_cost + 1e-9 && size > best_size)) {
+      best_cost = cost;
+      best_size = size;
+    }
+    if (size >= longest) break;
+  }
+  *split_size = int32_t(best_size);
+  *num_splits = int32_t(std::max<int64_t>(1, b200kv::div_up(longest, best_size)));
+}
+
 void b200kv_plan_splits(int32_t batch_count, int32_t max_live_keys,
                         int32_t kv_heads, int32_t sm_count,
                         int32_t *split_size, int32_t *num_splits) {
-  const int tile = b200kv::decode_stage_tokens(kv_heads);
+  // Without the true sum, assume sequences average half the longest one.
   const int64_t total = int64_t(std::max(batch_count, 1)) *
-                        std::max(max_live_keys, 1);
-  const int64_t target_ctas = int64_t(std::max(sm_count, 1)) * 4;
-  int64_t size = b200kv::div_up(total, target_ctas);
-  size = b200kv::div_up(size, int64_t(tile)) * tile;
-  size = std::min<int64_t>(std::max<int64_t>(size, tile), 32 * tile);
-  *split_size = int32_t(size);
-  *num_splits =
-      int32_t(std::max<int64_t>(1, b200kv::div_up(int64_t(max_live_keys), size)));
+                        ((int64_t(std::max(max_live_keys, 1)) + 1) / 2);
+  b200kv_plan_splits_total(batch_count, max_live_keys,
+                           batch_count <= 1 ? max_live_keys : total, kv_heads,
+                           sm_count, split_size, num_splits);
 }
 
 int b200kv_decode_layer_step_bf16(const B200KvLayerStepArgs *s,

@@ -32,6 +32,15 @@ struct DecodeArgs {
 
 cudaError_t decode_attention_bf16(const DecodeArgs &args, cudaStream_t stream);
 
+// split_size == 0 in DecodeArgs selects this path (see decode_balanced.cu):
+// the batch's live keys are divided evenly over a fixed grid; num_splits then
+// only sizes the scratch (batch * num_splits slots per head).
+cudaError_t decode_attention_balanced_bf16(const DecodeArgs &args,
+                                           cudaStream_t stream);
+bool decode_balanced_supported(const Gemma4KvCacheConfig &cfg, int q_heads,
+                               int batch_count);
+int decode_balanced_num_splits(int batch_count, int sm_count);
+
 // Key tile of the split kernel for a given KV-head count: split sizes that
 // are multiples of it keep every shared-memory stage full.
 int decode_stage_tokens(int kv_heads);

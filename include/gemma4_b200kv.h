@@ -226,6 +226,14 @@ int b200kv_decode_append_bf16(b200kv_bf16 *d_q_prepared,
  *   d_partial_acc             [batch * q_heads * num_splits * head_dim] fp32
  * d_status: optional int32[4] device word block; a kernel that gives up a
  * bounded wait writes a non-zero code to d_status[0] (see B200KV_STATUS_*).
+ *
+ * split_size == 0 (not a value the reference accepts) asks for the balanced
+ * partition instead: the live keys of the whole batch are divided evenly over
+ * a fixed grid of two CTAs per SM, whatever the individual lengths, so ragged
+ * batches leave no SM idle. num_splits then only states how large the scratch
+ * is (still batch * q_heads * num_splits rows; use b200kv_plan_balanced).
+ * Available for 8 KV heads x 256 with 16 query heads and batch <= 1024;
+ * cudaErrorInvalidValue otherwise.
  * ------------------------------------------------------------------ */
 int b200kv_decode_attention_bf16(b200kv_bf16 *d_out, float *d_lse,
                                  const b200kv_bf16 *d_q_prepared,
@@ -291,6 +299,18 @@ void b200kv_decode_workspace_bytes(int32_t batch_count, int32_t q_heads,
 void b200kv_plan_splits(int32_t batch_count, int32_t max_live_keys,
                         int32_t kv_heads, int32_t sm_count,
                         int32_t *split_size, int32_t *num_splits);
+/* num_splits to pass with split_size == 0 so that the scratch can hold one
+ * partial per CTA and sequence boundary: ceil(2 * sm_count / batch) + 1. */
+void b200kv_plan_balanced(int32_t batch_count, int32_t sm_count,
+                          int32_t *num_splits);
+/* Same, when the host also knows the sum of live keys over the batch (it does:
+ * the runtime state mirrors seq_lengths on the host, src/gemma4_runtime.cuh:38):
+ * picks the split size that minimises waves x per-CTA time plus the traffic of
+ * the partials for that many CTAs. */
+void b200kv_plan_splits_total(int32_t batch_count, int32_t max_live_keys,
+                              int64_t total_live_keys, int32_t kv_heads,
+                              int32_t sm_count, int32_t *split_size,
+                              int32_t *num_splits);
 
 /* ------------------------------------------------------------------ *
  * One layer-step = fused append + split-KV decode + combine, enqueued back to

@@ -85,11 +85,16 @@ CASES = {
 
 
 @pytest.mark.parametrize("name", list(CASES))
-@pytest.mark.parametrize("split", ["one", "tile", "ref20", "ragged_overprovisioned"])
+@pytest.mark.parametrize("split", ["one", "tile", "ref20", "ragged_overprovisioned", "balanced"])
 def test_decode_attention_matches_oracle(kv, orc, name, split):
     case = make_attn_case(2024, **CASES[name])
     longest = max(live_keys(case))
-    if split == "one":
+    if split == "balanced":
+        if case.kv_heads != 8:
+            pytest.skip("balanced partition is built for 8 KV heads")
+        sms = torch.cuda.get_device_properties(0).multi_processor_count
+        split_size, num_splits = 0, kv.plan_balanced(case.batch, sms)
+    elif split == "one":
         split_size, num_splits = max(longest, 1), 1
     elif split == "tile":
         split_size = 64
@@ -103,7 +108,7 @@ def test_decode_attention_matches_oracle(kv, orc, name, split):
     d = DeviceCase(kv, case)
     out, lse, pm = d.run(split_size, num_splits, poison=float("nan"))
     check(orc, case, out, lse)
-    if pm is not None:
+    if pm is not None and split_size > 0:
         for b, n in enumerate(live_keys(case)):
             actual = -(-n // split_size)
             assert not np.isnan(pm[b, :, :actual]).any()
@@ -123,10 +128,45 @@ def test_unmapped_pages_and_empty_rows(kv, orc):
         assert np.isneginf(lse[1]).all() and np.isneginf(lse[3]).all()
 
 
+def test_balanced_partition_edge_cases(kv, orc):
+    """split_size == 0: ranges cut sequences anywhere, skip empty and unmapped ones, and a scratch that
+    only allows a few CTAs still gives the same answer."""
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    case = make_attn_case(77, [100, 0, 40, 64, 3000, 1, 0, 517], window=0)
+    case.page_table[0, 2] = -1
+    case.page_table[3, :] = -1
+    d = DeviceCase(kv, case)
+    for num_splits in (kv.plan_balanced(case.batch, sms), 2, 3, 9):
+        out, lse, _ = d.run(0, num_splits, poison=float("nan"))
+        check(orc, case, out, lse)
+        assert not out[1].any() and not out[3].any() and not out[6].any()
+    ring = make_attn_case(78, [5000, 90, 1024, 1023, 1025, 0, 2000], window=1024)
+    d = DeviceCase(kv, ring)
+    for num_splits in (kv.plan_balanced(ring.batch, sms), 2):
+        out, lse, _ = d.run(0, num_splits, poison=float("nan"))
+        check(orc, ring, out, lse)
+    many = make_attn_case(79, list(np.random.default_rng(3).integers(0, 40, size=300)), window=0)
+    out, lse, _ = DeviceCase(kv, many).run(0, kv.plan_balanced(many.batch, sms), poison=float("nan"))
+    check(orc, many, out, lse)
+    # rejected: scratch too small for even one CTA, or a geometry the balanced kernel is not built for
+    small = make_attn_case(80, [64, 64], window=0)
+    d = DeviceCase(kv, small)
+    B, H, D = 2, 16, 256
+    buf = torch.zeros(B * H * D, dtype=torch.float32, device="cuda")
+    args = (torch.zeros((B, H, D), dtype=torch.int16, device="cuda"), None, d.q, d.ck, d.cv, d.cfg, d.table, d.seq,
+            0, small.scale, 0, 1, B, H, buf, buf, buf)
+    assert kv.decode_attention(*args, check=False) == kv.CUDA_ERROR_INVALID_VALUE
+    kv4 = make_attn_case(81, [64], window=0, kv_heads=4, q_heads=8)
+    d4 = DeviceCase(kv, kv4)
+    assert kv.decode_attention(torch.zeros((1, 8, 256), dtype=torch.int16, device="cuda"), None, d4.q, d4.ck, d4.cv,
+                               d4.cfg, d4.table, d4.seq, 0, kv4.scale, 0, 8, 1, 8, buf, buf, buf,
+                               check=False) == kv.CUDA_ERROR_INVALID_VALUE
+
+
 def test_all_sequences_empty(kv, orc):
     case = make_attn_case(14, [0, 0], window=0)
     d = DeviceCase(kv, case)
-    for split_size, num_splits in ((16, 1), (16, 3)):
+    for split_size, num_splits in ((16, 1), (16, 3), (0, 200)):
         out, lse, _ = d.run(split_size, num_splits)
         assert not out.any() and np.isneginf(lse).all()
 
@@ -146,7 +186,7 @@ def test_uniform_scores_give_the_mean_and_log_count(kv, orc):
     case = make_attn_case(16, [777, 1500], window=1024)
     case.cache_k[:] = 0
     d = DeviceCase(kv, case)
-    for split_size, num_splits in ((1024, 1), (64, 16), (24, 50)):
+    for split_size, num_splits in ((1024, 1), (64, 16), (24, 50), (0, 160)):
         out, lse, _ = d.run(split_size, num_splits)
         for b, n in enumerate(live_keys(case)):
             assert np.abs(lse[b] - math.log(n)).max() <= 1e-4
