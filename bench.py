@@ -34,7 +34,6 @@ REPO = Path(__file__).resolve().parent
 sys.path.insert(0, str(REPO))
 
 HQ, HKV, D, PAGE, WINDOW = 16, 8, 256, 16, 1024
-LOCAL_LAYERS, GLOBAL_LAYERS = 5, 1
 E_KV = 2  # bytes per cached element (bf16)
 METRIC = "KV append + decode attention: achieved HBM GB/s (us per layer-step alongside)"
 
@@ -54,6 +53,9 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--split-global", type=int, default=0, help="override the planned global split size")
     ap.add_argument("--split-local", type=int, default=0)
+    ap.add_argument("--workload", default="cfg3", choices=["cfg1", "cfg2", "cfg3", "cfg4", "cfg5"],
+                    help="BASELINE.json configs (1-based): cfg3 (default) is the batched paged decode the "
+                         "metric is quoted on; the others are reported as extra lines on request")
     ap.add_argument("--partition", default="balanced", choices=["balanced", "splits"],
                     help="balanced: keys of the batch divided evenly over a fixed grid (split_size 0); "
                          "splits: fixed-size splits as the reference defines them")
@@ -81,24 +83,28 @@ def shard_sequences(ctx: np.ndarray, world: int) -> list[list[int]]:
     return shards
 
 
-def layer_step_bytes(seq_len_after_append: np.ndarray, window: int) -> int:
+def layer_step_bytes(seq_len_after_append: np.ndarray, window: int, hkv: int = HKV, e_kv: int = E_KV) -> int:
     """Algorithmic HBM bytes of one layer-step (append + decode attention) for the given sequences."""
     s = np.asarray(seq_len_after_append, dtype=np.int64)
+    hq = 2 * hkv
     live = np.minimum(s, window) if window > 0 else s
     first = s - live
     pages_touched = (s - 1) // PAGE - first // PAGE + 1
-    attn = live * HKV * D * 2 * E_KV + HQ * D * 2 + HQ * D * 2 + 4 * pages_touched
-    append = (HQ + 2 * HKV) * D * 2 + HQ * D * 2 + 2 * HKV * D * E_KV + 4
+    scales = 4 * pages_touched * hkv * 2 if e_kv == 1 else 0
+    attn = live * hkv * D * 2 * e_kv + hq * D * 2 + hq * D * 2 + 4 * pages_touched + scales
+    append = (hq + 2 * hkv) * D * 2 + hq * D * 2 + 2 * hkv * D * e_kv + 4
     return int((attn + append).sum())
 
 
-def attention_kernel_bytes(seq_len_after_append: np.ndarray, window: int) -> int:
+def attention_kernel_bytes(seq_len_after_append: np.ndarray, window: int, hkv: int = HKV, e_kv: int = E_KV) -> int:
     """Algorithmic bytes of the split-KV attention launch alone (K/V stream, q, output, page table)."""
     s = np.asarray(seq_len_after_append, dtype=np.int64)
+    hq = 2 * hkv
     live = np.minimum(s, window) if window > 0 else s
     first = s - live
     pages_touched = (s - 1) // PAGE - first // PAGE + 1
-    return int((live * HKV * D * 2 * E_KV + HQ * D * 2 + HQ * D * 2 + 4 * pages_touched).sum())
+    scales = 4 * pages_touched * hkv * 2 if e_kv == 1 else 0
+    return int((live * hkv * D * 2 * e_kv + hq * D * 2 + hq * D * 2 + 4 * pages_touched + scales).sum())
 
 
 # --------------------------------------------------------------------------- clocks
@@ -160,15 +166,29 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------- device workload
-class RankWorkload:
-    """Everything one rank holds in HBM for its shard of sequences."""
+class Spec:
+    """Which layers one step runs and on what geometry."""
 
-    def __init__(self, kv, torch, ctx: np.ndarray, total_steps: int, seed: int, args):
-        self.kv, self.torch = kv, torch
+    def __init__(self, name, text, n_local, n_global, hkv=8, fp8=False, tight_ring=False, outliers=False,
+                 gather=False):
+        self.name, self.text = name, text
+        self.n_local, self.n_global = n_local, n_global
+        self.hkv, self.hq = hkv, 2 * hkv           # KV / query heads held by this rank
+        self.fp8, self.tight_ring, self.outliers, self.gather = fp8, tight_ring, outliers, gather
+        self.e_kv = 1 if fp8 else 2
+
+
+class RankWorkload:
+    """Everything one rank holds in HBM for its share of the workload."""
+
+    def __init__(self, kv, torch, ctx: np.ndarray, total_steps: int, seed: int, args, spec: Spec):
+        self.kv, self.torch, self.spec = kv, torch, spec
         dev = "cuda"
         self.B = B = int(ctx.size)
         self.ctx = ctx
         self.total_steps = total_steps
+        HKV, HQ = spec.hkv, spec.hq
+        nl, ng = spec.n_local, spec.n_global
         sm = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
         gen = torch.Generator(device=dev)
         gen.manual_seed(seed)
@@ -179,40 +199,53 @@ class RankWorkload:
             t.normal_(generator=gen)
             return t
 
-        # global layer: linear cache, one pool, permuted block table
-        pages_b = (ctx + total_steps + PAGE) // PAGE
-        self.g_pages = int(pages_b.sum())
-        self.g_mpps = int(pages_b.max())
-        table = np.full((B, self.g_mpps), -1, dtype=np.int32)
-        pool = rng.permutation(self.g_pages).astype(np.int32)
-        cur = 0
-        for b in range(B):
-            table[b, :pages_b[b]] = pool[cur:cur + pages_b[b]]
-            cur += int(pages_b[b])
-        self.g_cfg = kv.make_kv_config(GLOBAL_LAYERS, self.g_pages, PAGE, self.g_mpps, B, HKV, D, 0)
-        self.g_table = torch.from_numpy(table).to(dev)
-        self.g_k = normal_bf16(self.g_cfg.cache_elements())
-        self.g_v = normal_bf16(self.g_cfg.cache_elements())
-        # local layers: ring of window + one page of slack per sequence
-        self.l_mpps = (WINDOW + PAGE - 1 + PAGE - 1) // PAGE
-        self.l_pages = B * self.l_mpps
-        ltable = rng.permutation(self.l_pages).astype(np.int32).reshape(B, self.l_mpps)
-        self.l_cfg = kv.make_kv_config(LOCAL_LAYERS, self.l_pages, PAGE, self.l_mpps, B, HKV, D, WINDOW)
-        self.l_table = torch.from_numpy(ltable).to(dev)
-        self.l_k = normal_bf16(self.l_cfg.cache_elements())
-        self.l_v = normal_bf16(self.l_cfg.cache_elements())
-
-        # RoPE tables from the library's own host builder
         max_pos = int(ctx.max()) + total_steps + 1
-        lc, ls = kv.fill_rope_tables(max_pos, D // 2, 10000.0, D)
-        gc, gs = kv.fill_rope_tables(max_pos, D // 2, 1000000.0, D)
-        self.l_cos, self.l_sin = torch.from_numpy(lc).to(dev), torch.from_numpy(ls).to(dev)
-        self.g_cos, self.g_sin = torch.from_numpy(gc).to(dev), torch.from_numpy(gs).to(dev)
+        self.g_cfg = self.l_cfg = None
+        if ng:
+            # global layers: linear cache, one pool, permuted block table
+            pages_b = (ctx + total_steps + PAGE) // PAGE
+            self.g_pages = int(pages_b.sum())
+            self.g_mpps = int(pages_b.max())
+            table = np.full((B, self.g_mpps), -1, dtype=np.int32)
+            pool = rng.permutation(self.g_pages).astype(np.int32)
+            cur = 0
+            for b in range(B):
+                table[b, :pages_b[b]] = pool[cur:cur + pages_b[b]]
+                cur += int(pages_b[b])
+            self.g_cfg = kv.make_kv_config(ng, self.g_pages, PAGE, self.g_mpps, B, HKV, D, 0)
+            self.g_table = torch.from_numpy(table).to(dev)
+            gc, gs = kv.fill_rope_tables(max_pos, D // 2, 1000000.0, D)
+            self.g_cos, self.g_sin = torch.from_numpy(gc).to(dev), torch.from_numpy(gs).to(dev)
+            if spec.fp8:
+                n = self.g_cfg.cache_elements()
+                self.g_k = torch.empty(n, dtype=torch.uint8, device=dev)
+                self.g_v = torch.empty(n, dtype=torch.uint8, device=dev)
+                self.g_sk = torch.zeros(ng * self.g_pages * HKV, dtype=torch.float32, device=dev)
+                self.g_sv = torch.zeros_like(self.g_sk)
+                self._fill_fp8(normal_bf16)
+            else:
+                self.g_k = normal_bf16(self.g_cfg.cache_elements())
+                self.g_v = normal_bf16(self.g_cfg.cache_elements())
+                if spec.outliers:      # 1 % of the keys scaled x8 (attention-sink-like rows)
+                    rows = self.g_k.view(-1, D)
+                    pick = torch.rand(rows.shape[0], device=dev, generator=gen) < 0.01
+                    rows[pick] *= 8.0
+        if nl:
+            # local layers: ring of the window plus one page of slack (or exactly the window)
+            self.l_mpps = WINDOW // PAGE if spec.tight_ring else (WINDOW + PAGE - 1 + PAGE - 1) // PAGE
+            self.l_pages = B * self.l_mpps
+            ltable = rng.permutation(self.l_pages).astype(np.int32).reshape(B, self.l_mpps)
+            self.l_cfg = kv.make_kv_config(nl, self.l_pages, PAGE, self.l_mpps, B, HKV, D, WINDOW)
+            self.l_table = torch.from_numpy(ltable).to(dev)
+            self.l_k = normal_bf16(self.l_cfg.cache_elements())
+            self.l_v = normal_bf16(self.l_cfg.cache_elements())
+            lc, ls = kv.fill_rope_tables(max_pos, D // 2, 10000.0, D)
+            self.l_cos, self.l_sin = torch.from_numpy(lc).to(dev), torch.from_numpy(ls).to(dev)
         w = torch.empty(2, D, dtype=torch.float32, device=dev).normal_(1.0, 0.05, generator=gen)
         self.q_w, self.k_w = w[0].to(torch.bfloat16).contiguous(), w[1].to(torch.bfloat16).contiguous()
 
         # this step's projections for every layer: [layers, B, (HQ + 2 HKV) * D]
-        L = LOCAL_LAYERS + GLOBAL_LAYERS
+        L = nl + ng
         self.L = L
         self.row = (HQ + 2 * HKV) * D
         self.raw = normal_bf16(L * B * self.row).view(L, B, self.row)
@@ -227,16 +260,20 @@ class RankWorkload:
         self.out_host = torch.empty((L, B, HQ, D), dtype=torch.bfloat16).pin_memory()
         self.lse = torch.empty((L, B, HQ), dtype=torch.float32, device=dev)
         self.status = torch.zeros(4, dtype=torch.int32, device=dev)
+        self.world = int(os.environ.get("WORLD_SIZE", "1")) if spec.gather else 1
+        if spec.gather and self.world > 1:
+            self.out_all = torch.empty((self.world, L, B, HQ, D), dtype=torch.bfloat16, device=dev)
 
         # per-step metadata, resident: position of the appended token and length after the append
         steps = np.arange(total_steps, dtype=np.int64)[:, None]
         self.pos_all = torch.from_numpy((ctx[None, :] + steps).astype(np.int32)).to(dev)
         self.len_all = torch.from_numpy((ctx[None, :] + steps + 1).astype(np.int32)).to(dev)
 
+        balanced_ok = HKV == 8 and B <= 1024
         self.g_split, self.g_nsplit = kv.plan_splits_total(B, int(ctx.max()) + total_steps,
                                                            int(ctx.sum()) + B * total_steps, HKV, sm)
         self.l_split, self.l_nsplit = kv.plan_splits_total(B, WINDOW, B * WINDOW, HKV, sm)
-        if args.partition == "balanced":
+        if (args.partition == "balanced" and balanced_ok) or spec.fp8:
             self.g_split = self.l_split = 0
             self.g_nsplit = self.l_nsplit = kv.plan_balanced(B, sm)
         if args.split_global:
@@ -245,7 +282,7 @@ class RankWorkload:
         if args.split_local:
             self.l_split = args.split_local
             self.l_nsplit = -(-WINDOW // self.l_split)
-        nmax = max(self.g_nsplit, self.l_nsplit)
+        nmax = max(self.g_nsplit if ng else 1, self.l_nsplit if nl else 1)
         rows = B * HQ * nmax
         self.pm = torch.empty(rows, dtype=torch.float32, device=dev)
         self.pl = torch.empty(rows, dtype=torch.float32, device=dev)
@@ -256,14 +293,16 @@ class RankWorkload:
         self.ev_end = [kv.Timer() for _ in range(total_steps)]
         for i in range(L):
             a = self.layers[i]
-            is_global = i == L - 1
+            # the reference's cadence: five sliding layers, then one global (src/gemma4.h:105-108)
+            is_global = self.layer_is_global(i)
+            li = self.cache_layer_of(i)
             a.q, a.out, a.lse = self.q_prepared[i].data_ptr(), self.out[i].data_ptr(), self.lse[i].data_ptr()
             a.partial_m, a.partial_l, a.partial_acc = self.pm.data_ptr(), self.pl.data_ptr(), self.pacc.data_ptr()
             a.cache_k = (self.g_k if is_global else self.l_k).data_ptr()
             a.cache_v = (self.g_v if is_global else self.l_v).data_ptr()
             a.cache_config = self.g_cfg if is_global else self.l_cfg
             a.page_table = (self.g_table if is_global else self.l_table).data_ptr()
-            a.cache_layer = 0 if is_global else i
+            a.cache_layer = li
             a.split_size = self.g_split if is_global else self.l_split
             a.num_splits = self.g_nsplit if is_global else self.l_nsplit
             a.softmax_scale = 1.0 / math.sqrt(D)
@@ -273,30 +312,82 @@ class RankWorkload:
             a.sin = (self.g_sin if is_global else self.l_sin).data_ptr()
             a.batch_count, a.q_heads, a.rotary_dim, a.norm_mode = B, HQ, D, kv.NORM_RSQRT_APPROX
             a.status = self.status.data_ptr()
+        self.timed_layer = max((i for i in range(L) if self.layer_is_global(i)), default=L - 1)
         self.stream = torch.cuda.current_stream().cuda_stream
-        self.launches_per_step = L * 3   # append, split, combine per layer (combine only when num_splits > 1)
-        if self.g_nsplit == 1 and self.g_split > 0:
-            self.launches_per_step -= 1
-        if self.l_nsplit == 1 and self.l_split > 0:
-            self.launches_per_step -= LOCAL_LAYERS
+        self.launches_per_step = 0
+        for i in range(L):
+            g = self.layer_is_global(i)
+            split, nsplit = (self.g_split, self.g_nsplit) if g else (self.l_split, self.l_nsplit)
+            self.launches_per_step += 2 if (nsplit == 1 and split > 0) else 3   # append, split[, combine]
+
+    def layer_is_global(self, i: int) -> bool:
+        nl, ng = self.spec.n_local, self.spec.n_global
+        if ng == 0:
+            return False
+        if nl == 0:
+            return True
+        period = (nl + ng) // ng
+        return (i + 1) % period == 0
+
+    def cache_layer_of(self, i: int) -> int:
+        g = self.layer_is_global(i)
+        return sum(1 for j in range(i) if self.layer_is_global(j) == g)
+
+    def _fill_fp8(self, normal_bf16):
+        """Fill the fp8 global cache the way a prompt would: bf16 N(0,1) rows through the bulk
+        quantise-on-append entry point, sequence by sequence."""
+        kv, torch, spec = self.kv, self.torch, self.spec
+        HKV = spec.hkv
+        for layer in range(spec.n_global):
+            for b in range(self.B):
+                n = int(self.ctx[b])
+                rows_k, rows_v = normal_bf16(n * HKV * D), normal_bf16(n * HKV * D)
+                one = lambda x: torch.tensor([x], dtype=torch.int32, device="cuda")
+                kv.fp8_append_rows(self.g_k, self.g_v, self.g_sk, self.g_sv, self.g_cfg, self.g_table, one(b), one(0),
+                                   one(n), one(0), 1, n, layer, rows_k, rows_v)
+        torch.cuda.synchronize()
 
     def _unpack_raw(self):
-        q, k, v = self.raw.split([HQ * D, HKV * D, HKV * D], dim=2)
+        hq, hkv = self.spec.hq, self.spec.hkv
+        q, k, v = self.raw.split([hq * D, hkv * D, hkv * D], dim=2)
         self.raw_q.copy_(q)
         self.raw_k.copy_(k)
         self.raw_v.copy_(v)
 
     def step(self, s: int):
         """One decode step, inputs resident in HBM."""
+        kv = self.kv
         pos = self.pos_all[s].data_ptr()
         length = self.len_all[s].data_ptr()
-        g = self.layers[self.L - 1]
-        for i in range(self.L):
-            self.layers[i].token_position = pos
-            self.layers[i].seq_lengths = length
-        g.event_before_attention = self.ev_begin[s].handle
-        g.event_after_attention = self.ev_end[s].handle
-        self.kv.decode_step(self.layers, self.L, stream=self.stream)
+        if self.spec.fp8:
+            # the fp8 cache has its own two entry points; the layer loop is here instead of in the library
+            for i in range(self.L):
+                li = self.cache_layer_of(i)
+                kv.decode_append_fp8(self.q_prepared[i], self.g_k, self.g_v, self.g_sk, self.g_sv, self.g_cfg,
+                                     self.g_table, pos, li, self.raw_q[i], self.raw_k[i], self.raw_v[i], self.q_w,
+                                     self.k_w, self.g_cos, self.g_sin, self.B, self.spec.hq, D,
+                                     kv.NORM_RSQRT_APPROX, stream=self.stream)
+                if i == self.timed_layer:
+                    self.ev_begin[s].record(self.stream)
+                kv.decode_attention_fp8(self.out[i], self.lse[i], self.q_prepared[i], self.g_k, self.g_v, self.g_sk,
+                                        self.g_sv, self.g_cfg, self.g_table, length, li, 1.0 / math.sqrt(D),
+                                        self.g_nsplit, self.B, self.spec.hq, self.pm, self.pl, self.pacc,
+                                        self.status, stream=self.stream)
+                if i == self.timed_layer:
+                    self.ev_end[s].record(self.stream)
+        else:
+            for i in range(self.L):
+                self.layers[i].token_position = pos
+                self.layers[i].seq_lengths = length
+            g = self.layers[self.timed_layer]
+            g.event_before_attention = self.ev_begin[s].handle
+            g.event_after_attention = self.ev_end[s].handle
+            kv.decode_step(self.layers, self.L, stream=self.stream)
+        if self.spec.gather and self.world > 1:
+            # KV-head sharding: every rank holds all heads' outputs after the step
+            import torch.distributed as dist
+
+            dist.all_gather_into_tensor(self.out_all, self.out)
 
     def step_e2e(self, s: int):
         """The same step called with host buffers: projections come from pinned host memory and the
@@ -309,9 +400,12 @@ class RankWorkload:
         torch.cuda.current_stream().synchronize()
 
     def bytes_for_step(self, s: int) -> tuple[int, int]:
+        sp = self.spec
         after = self.ctx + s + 1
-        return (LOCAL_LAYERS * layer_step_bytes(after, WINDOW) + GLOBAL_LAYERS * layer_step_bytes(after, 0),
-                attention_kernel_bytes(after, 0))
+        total = (sp.n_local * layer_step_bytes(after, WINDOW, sp.hkv, sp.e_kv)
+                 + sp.n_global * layer_step_bytes(after, 0, sp.hkv, sp.e_kv))
+        timed_window = 0 if sp.n_global else WINDOW
+        return total, attention_kernel_bytes(after, timed_window, sp.hkv, sp.e_kv)
 
 
 # --------------------------------------------------------------------------- CPU baseline
@@ -374,7 +468,7 @@ def run_reference_arm(args):
 
     orc.build()
     threads = orc.hardware_threads()
-    ctx = context_lengths(args)
+    _, ctx, _, _, _ = plan_workload(args, 1, 0)
     per_step = max(0.5, min(args.cpu_seconds, 120.0 / max(1, args.steps + args.warmup)))
     times, sample = [], None
     for i in range(args.warmup + args.steps):
@@ -385,7 +479,7 @@ def run_reference_arm(args):
     nbytes = sum(t["bytes"] for t in times)
     value = nbytes / secs / 1e9
     desc = (f"global layer-step (append + split attention + reduce) over the first {sample['sequences']} "
-            f"sequences ({sample['keys']} keys) of the 64-sequence batch, {sample['runs']} passes per step")
+            f"sequences ({sample['keys']} keys) of the workload, {sample['runs']} passes per step")
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs / len(times) * 1e3,
@@ -400,17 +494,68 @@ def run_reference_arm(args):
     print(json.dumps(line))
 
 
-def workload_config(args, world, where):
-    return {
-        "workload": "configs[2]: batched paged decode, 64 sequences ctx~U[512,32768], 16-token pages, "
-                    "permuted block table, 16Q/8KV/D256 bf16; step = 5 sliding (window 1024) + 1 global layer-step",
-        "sequences": args.seqs, "ctx_range": [args.min_ctx, args.max_ctx], "seed": args.seed,
-        "page_size": PAGE, "layers_per_step": LOCAL_LAYERS + GLOBAL_LAYERS,
-        "parallelism": f"sequence-sharded x{world}, no collective",
+WORKLOADS = {
+    "cfg1": "configs[0]: single sliding layer, batch 1, tight 1024-token ring pre-filled, one token appended "
+            "per step (wraps), 16Q/8KV/D256 bf16",
+    "cfg2": "configs[1]: 48-layer stack (40 sliding window-1024 + 8 global at context 4096), batch 1, "
+            "16Q/8KV/D256 bf16, one token appended per layer per step",
+    "cfg3": "configs[2]: batched paged decode, 64 sequences ctx~U[512,32768], 16-token pages, permuted block "
+            "table, 16Q/8KV/D256 bf16; step = 5 sliding (window 1024) + 1 global layer-step",
+    "cfg4": "configs[3]: one sequence of 131072 keys (1 % of keys x8), global layer, split-KV decode; KV heads "
+            "sharded over the ranks, all-gather of the head outputs",
+    "cfg5": "configs[4]: FP8 e4m3 cache (fp32 scale per 16-token page and KV head), batch 32, context 8192, "
+            "global layer, quantise-on-append + fused dequant",
+}
+
+
+def plan_workload(args, world: int, rank: int):
+    """Returns (spec, all context lengths, this rank's context lengths, parallelism text, scaling)."""
+    name = args.workload
+    if name == "cfg3":
+        ctx_all = context_lengths(args)
+        mine = ctx_all[shard_sequences(ctx_all, world)[rank]]
+        return Spec(name, WORKLOADS[name], 5, 1), ctx_all, mine, f"sequence-sharded x{world}, no collective", "strong"
+    if name == "cfg5":
+        ctx_all = np.full(32, 8192, dtype=np.int64)
+        mine = ctx_all[shard_sequences(ctx_all, world)[rank]]
+        return (Spec(name, WORKLOADS[name], 0, 1, fp8=True), ctx_all, mine,
+                f"sequence-sharded x{world}, no collective", "strong")
+    if name == "cfg4":
+        if 8 % world:
+            raise SystemExit("cfg4 shards 8 KV heads: --gpus must divide 8")
+        ctx_all = np.array([131072], dtype=np.int64)
+        return (Spec(name, WORKLOADS[name], 0, 1, hkv=8 // world, outliers=True, gather=True), ctx_all, ctx_all,
+                f"KV-head-sharded x{world} ({8 // world} KV heads per rank), NCCL all-gather of head outputs",
+                "strong")
+    if world > 1:
+        raise SystemExit(f"{name} is a batch-1 latency case: run it on one GPU")
+    if name == "cfg1":
+        ctx_all = np.array([1024], dtype=np.int64)
+        return Spec(name, WORKLOADS[name], 1, 0, tight_ring=True), ctx_all, ctx_all, "single GPU", "strong"
+    ctx_all = np.array([4096], dtype=np.int64)
+    return Spec(name, WORKLOADS[name], 40, 8), ctx_all, ctx_all, "single GPU", "strong"
+
+
+def workload_config(args, world, where, parallelism=None, layers=None):
+    cfg = {
+        "workload": WORKLOADS[args.workload],
+        "seed": args.seed, "page_size": PAGE,
+        "parallelism": parallelism or f"x{world}",
         "partition": args.partition,
-        "l2": "inputs larger than L2: every step streams more than 1 GB per rank before any byte is revisited",
         "where": where,
     }
+    if args.workload == "cfg3":
+        cfg.update({"sequences": args.seqs, "ctx_range": [args.min_ctx, args.max_ctx], "layers_per_step": 6,
+                    "l2": "inputs larger than L2: every step streams more than 1 GB per rank before any byte "
+                          "is revisited"})
+    elif layers is not None:
+        cfg["layers_per_step"] = layers
+    if args.workload in ("cfg1", "cfg2"):
+        cfg["l2"] = ("working set of a step (8 MB / 600 MB) against a 126 MB L2: cfg1 is L2-resident by "
+                     "construction and is a latency case, not a bandwidth claim")
+    elif args.workload in ("cfg4", "cfg5"):
+        cfg["l2"] = "inputs larger than L2: a step streams more than 130 MB per rank" 
+    return cfg
 
 
 # --------------------------------------------------------------------------- main arm
@@ -440,14 +585,12 @@ def main():
     kv.load_library(build_if_missing=False)
     sampler = ClockSampler(local_rank) if rank == 0 else None   # started early: nvidia-smi takes a second to come up
 
-    ctx_all = context_lengths(args)
-    shards = shard_sequences(ctx_all, world)
-    ctx = ctx_all[shards[rank]]
-    if args.emulate_world > 1 and world == 1:
+    spec, ctx_all, ctx, parallelism, scaling = plan_workload(args, world, rank)
+    if args.emulate_world > 1 and world == 1 and args.workload in ("cfg3", "cfg5"):
         ctx = ctx_all[shard_sequences(ctx_all, args.emulate_world)[args.emulate_rank]]
     e2e_warm = 3
     total_steps = args.warmup + args.steps + e2e_warm + args.e2e_steps
-    wl = RankWorkload(kv, torch, ctx, total_steps, args.seed + 1000 * rank, args)
+    wl = RankWorkload(kv, torch, ctx, total_steps, args.seed + 1000 * rank, args, spec)
     torch.cuda.synchronize()
 
     def barrier():
@@ -525,13 +668,17 @@ def main():
     line = {
         "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": workload_config(args, world, "B200"),
+        "scaling": scaling, "vs_baseline": None, "dtype": "fp8 e4m3 cache, fp32 math" if spec.fp8 else "bf16",
+        "data": "synthetic",
+        "config": workload_config(args, world, "B200", parallelism, wl.L),
         "us_per_layer_step": elapsed_ms * 1e3 / layer_steps,
         "us_global_layer_attention": statistics.mean(attn_ms) * 1e3,
         "frac_of_hbm_peak": value / (peak * world),
         "roofline": {
-            "bound": "hbm", "kernel": "decode_split_kernel + combine, global layer (rank 0)",
+            "bound": "hbm",
+            "kernel": ("decode_balanced_kernel" if wl.layers[wl.timed_layer].split_size == 0 or spec.fp8
+                       else "decode_split_kernel") + " + combine, "
+                      + ("global" if spec.n_global else "sliding") + " layer (rank 0)",
             "achieved": attn_achieved, "peak": peak, "unit": "GB/s", "frac": attn_achieved / peak,
             "traffic": None, "peak_source": peak_src,
             "algorithmic_bytes_per_launch": attn_bytes, "avg_launch_ms": statistics.mean(attn_ms),

@@ -137,6 +137,9 @@ _SIGNATURES = {
     "b200kv_decode_append_bf16": (c_int, [_P, _P, _P, KvConfig, _P, _P, c_int32] + [_P] * 7 + [c_int32, c_int32, c_int32, c_int32, _P]),
     "b200kv_decode_attention_bf16": (c_int, [_P, _P, _P, _P, _P, KvConfig, _P, _P, c_int32, c_float, c_int32, c_int32, c_int32, c_int32, _P, _P, _P, _P, _P]),
     "b200kv_decode_attention_static_scratch_bf16": (c_int, [_P, _P, _P, _P, _P, KvConfig, _P, _P, c_int32, c_float, c_int32, c_int32, c_int32, c_int32, _P, _P]),
+    "b200kv_decode_append_fp8": (c_int, [_P, _P, _P, _P, _P, KvConfig, _P, _P, c_int32] + [_P] * 7 + [c_int32, c_int32, c_int32, c_int32, _P]),
+    "b200kv_fp8_append_rows": (c_int, [_P, _P, _P, _P, KvConfig, _P, _P, _P, _P, _P, c_int32, c_int32, c_int32, _P, _P, _P]),
+    "b200kv_decode_attention_fp8": (c_int, [_P] * 7 + [KvConfig, _P, _P, c_int32, c_float, c_int32, c_int32, c_int32, _P, _P, _P, _P, _P]),
     "b200kv_decode_workspace_bytes": (None, [c_int32, c_int32, c_int32, c_int32, POINTER(c_size_t), POINTER(c_size_t), POINTER(c_size_t)]),
     "b200kv_plan_splits": (None, [c_int32, c_int32, c_int32, c_int32, POINTER(c_int32), POINTER(c_int32)]),
     "b200kv_plan_balanced": (None, [c_int32, c_int32, POINTER(c_int32)]),
@@ -429,3 +432,36 @@ class Timer:
         if self.handle:
             load_library().b200kv_timer_destroy(self.handle)
             self.handle = c_void_p()
+
+
+# ------------------------------------------------------------------ fp8 e4m3 cache
+def decode_append_fp8(q_prepared, cache_k, cache_v, scale_k, scale_v, cfg: KvConfig, page_table, token_position,
+                      cache_layer: int, q, k, v, q_norm_weight, k_norm_weight, cos, sin, batch_count: int,
+                      q_heads: int, rotary_dim: int, norm_mode: int = NORM_RSQRT_APPROX, stream=None,
+                      check: bool = True) -> int:
+    code = load_library().b200kv_decode_append_fp8(
+        _ptr(q_prepared), _ptr(cache_k), _ptr(cache_v), _ptr(scale_k), _ptr(scale_v), cfg, _ptr(page_table),
+        _ptr(token_position), cache_layer, _ptr(q), _ptr(k), _ptr(v), _ptr(q_norm_weight), _ptr(k_norm_weight),
+        _ptr(cos), _ptr(sin), batch_count, q_heads, rotary_dim, norm_mode, _stream(stream))
+    return _check(code, "b200kv_decode_append_fp8", check)
+
+
+def fp8_append_rows(cache_k, cache_v, scale_k, scale_v, cfg: KvConfig, page_table, seq_batch, first_position,
+                    row_count, row_start, run_count: int, max_row_count: int, cache_layer: int, k_prepared,
+                    v_prepared, stream=None, check: bool = True) -> int:
+    code = load_library().b200kv_fp8_append_rows(
+        _ptr(cache_k), _ptr(cache_v), _ptr(scale_k), _ptr(scale_v), cfg, _ptr(page_table), _ptr(seq_batch),
+        _ptr(first_position), _ptr(row_count), _ptr(row_start), run_count, max_row_count, cache_layer,
+        _ptr(k_prepared), _ptr(v_prepared), _stream(stream))
+    return _check(code, "b200kv_fp8_append_rows", check)
+
+
+def decode_attention_fp8(out, lse, q_prepared, cache_k, cache_v, scale_k, scale_v, cfg: KvConfig, page_table,
+                         seq_lengths, cache_layer: int, softmax_scale: float, num_splits: int, batch_count: int,
+                         q_heads: int, partial_m, partial_l, partial_acc, status=None, stream=None,
+                         check: bool = True) -> int:
+    code = load_library().b200kv_decode_attention_fp8(
+        _ptr(out), _ptr(lse), _ptr(q_prepared), _ptr(cache_k), _ptr(cache_v), _ptr(scale_k), _ptr(scale_v), cfg,
+        _ptr(page_table), _ptr(seq_lengths), cache_layer, softmax_scale, num_splits, batch_count, q_heads,
+        _ptr(partial_m), _ptr(partial_l), _ptr(partial_acc), _ptr(status), _stream(stream))
+    return _check(code, "b200kv_decode_attention_fp8", check)

@@ -12,100 +12,14 @@
 // One warp owns one head; lane l holds elements l + 32*i (the reference's
 // ownership), the sum of squares is an fma chain per lane followed by the xor
 // butterfly 16,8,4,2,1 -- that order defines the bit pattern of the scale.
-#include "common.cuh"
 #include "kernels.cuh"
+#include "prep_common.cuh"
 
 #include <type_traits>
 
 namespace b200kv {
 
 namespace {
-
-constexpr float kRmsEps = 1.0e-6f;  // GEMMA4_RMS_NORM_EPS, src/gemma4.h:29
-
-// The reference compiles its prep call sites with flush-to-zero multiplies
-// and the shared norm/rope helpers without; the approx mode reproduces that
-// split, the IEEE mode uses plain round-to-nearest everywhere.
-template <bool kIeee>
-__device__ __forceinline__ float mul_prep(float a, float b) {
-  if constexpr (kIeee) {
-    return __fmul_rn(a, b);
-  } else {
-    float r;
-    asm("mul.ftz.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
-    return r;
-  }
-}
-
-template <int D, bool kIeee>
-__device__ __forceinline__ float warp_rms_scale(const float (&x)[D / 32]) {
-  float ss = 0.0f;
-#pragma unroll
-  for (int i = 0; i < D / 32; ++i) ss = __fmaf_rn(x[i], x[i], ss);
-#pragma unroll
-  for (int offset = 16; offset > 0; offset /= 2) {
-    ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, offset));
-  }
-  const float t = __fadd_rn(__fdiv_rn(ss, float(D)), kRmsEps);
-  if constexpr (kIeee) {
-    return __fdiv_rn(1.0f, __fsqrt_rn(t));
-  } else {
-    return rsqrtf(t);
-  }
-}
-
-template <int D>
-__device__ __forceinline__ void load_head(const __nv_bfloat16 *in, int lane,
-                                          float (&x)[D / 32]) {
-#pragma unroll
-  for (int i = 0; i < D / 32; ++i) {
-    x[i] = __bfloat162float(in[lane + i * 32]);
-  }
-}
-
-// Learned-weight RMSNorm, then split-half RoPE on the first ROT dims.
-template <int D, int ROT, bool kIeee>
-__device__ __forceinline__ void prep_weighted_rope(
-    __nv_bfloat16 *out, const float (&x)[D / 32], const __nv_bfloat16 *weight,
-    const float *cos_row, const float *sin_row, int lane) {
-  constexpr int kHalf = ROT / 2;
-  constexpr int kPairs = kHalf / 32;
-  const float scale = warp_rms_scale<D, kIeee>(x);
-#pragma unroll
-  for (int i = 0; i < kPairs; ++i) {
-    const int dim = lane + i * 32;
-    const float lo = mul_prep<kIeee>(mul_prep<kIeee>(x[i], scale),
-                                     __bfloat162float(__ldg(weight + dim)));
-    const float hi =
-        mul_prep<kIeee>(mul_prep<kIeee>(x[i + kPairs], scale),
-                        __bfloat162float(__ldg(weight + kHalf + dim)));
-    const float c = __ldg(cos_row + dim);
-    const float s = __ldg(sin_row + dim);
-    out[dim] = __float2bfloat16_rn(__fmaf_rn(-hi, s, __fmul_rn(lo, c)));
-    out[kHalf + dim] = __float2bfloat16_rn(__fmaf_rn(lo, s, __fmul_rn(hi, c)));
-  }
-#pragma unroll
-  for (int i = 0; i < D / 32; ++i) {
-    const int dim = lane + i * 32;
-    if (dim >= ROT) {
-      const float value = mul_prep<kIeee>(mul_prep<kIeee>(x[i], scale),
-                                          __bfloat162float(__ldg(weight + dim)));
-      out[dim] = __float2bfloat16_rn(value);
-    }
-  }
-}
-
-// Scale-free RMSNorm (V rows): no weight, no rotation.
-template <int D, bool kIeee>
-__device__ __forceinline__ void prep_scale_free(__nv_bfloat16 *out,
-                                                const float (&x)[D / 32],
-                                                int lane) {
-  const float scale = warp_rms_scale<D, kIeee>(x);
-#pragma unroll
-  for (int i = 0; i < D / 32; ++i) {
-    out[lane + i * 32] = __float2bfloat16_rn(mul_prep<kIeee>(x[i], scale));
-  }
-}
 
 // grid (batch, kv_head); warps 0..G-1 prep the G query heads of the group,
 // warp G preps and stores K, warp G+1 (only when V has its own projection)

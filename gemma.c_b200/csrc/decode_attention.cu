@@ -99,7 +99,9 @@ __global__ __launch_bounds__(T::kThreads, T::kCtasPerSm) void decode_split_kerne
   if (warp == kConsumerWarps) {
     // ------------------------------ producer ------------------------------
     const uint64_t policy = l2_policy_evict_first();
-    const KvSource src = {p.cache_k, p.cache_v, p.page_table, p.layer};
+    const KvSource src = {reinterpret_cast<const uint8_t *>(p.cache_k),
+                          reinterpret_cast<const uint8_t *>(p.cache_v),
+                          p.page_table, p.layer};
     bool ok = true;
     int issued = 0;  // chunks whose full barrier has been armed
     for (int c = 0; c < nchunks; ++c) {

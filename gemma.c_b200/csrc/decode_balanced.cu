@@ -18,6 +18,7 @@
 // the partial of CTA c for sequence b sits in slot c + b, which is unique
 // because ranges and sequences advance together.
 #include "decode_common.cuh"
+#include "decode_fp8.cuh"
 #include "kernels.cuh"
 
 namespace b200kv {
@@ -31,8 +32,10 @@ struct BalancedParams {
   __nv_bfloat16 *out;
   float *lse;
   const __nv_bfloat16 *q;
-  const __nv_bfloat16 *cache_k;
-  const __nv_bfloat16 *cache_v;
+  const void *cache_k;     // bf16 or e4m3 rows, Layout-A
+  const void *cache_v;
+  const float *scale_k;    // fp8 only: [layer, page, head]
+  const float *scale_v;
   Gemma4KvCacheConfig cfg;
   const int32_t *page_table;
   const int32_t *seq_lengths;
@@ -160,7 +163,9 @@ __global__ __launch_bounds__(T::kThreads, T::kCtasPerSm) void decode_balanced_ke
   if (warp == T::kConsumerWarps) {
     // ------------------------------ producer ------------------------------
     const uint64_t policy = l2_policy_evict_first();
-    const KvSource src = {p.cache_k, p.cache_v, p.page_table, p.layer};
+    const KvSource src = {static_cast<const uint8_t *>(p.cache_k),
+                          static_cast<const uint8_t *>(p.cache_v),
+                          p.page_table, p.layer};
     bool ok = true;
     int it = 0;  // stages armed so far, across all pieces of the range
     int b = b_start, flat = r0;
@@ -177,8 +182,15 @@ __global__ __launch_bounds__(T::kThreads, T::kCtasPerSm) void decode_balanced_ke
           break;
         }
         const int base = a0 + c * ST;
-        producer_fill_stage<T>(ring, src, cfg, seg.b, base, max(seg.pos0, base),
-                               min(seg.pos1, base + ST), stage, policy, lane);
+        if constexpr (T::kFp8) {
+          const Fp8Scales scales = {p.scale_k, p.scale_v};
+          producer_fill_stage_fp8(ring, src, scales, cfg, seg.b, base,
+                                  max(seg.pos0, base), min(seg.pos1, base + ST),
+                                  stage, policy, lane);
+        } else {
+          producer_fill_stage<T>(ring, src, cfg, seg.b, base, max(seg.pos0, base),
+                                 min(seg.pos1, base + ST), stage, policy, lane);
+        }
       }
     }
     for (int s = 0; s < kStages && s < it; ++s) {
@@ -215,7 +227,13 @@ __global__ __launch_bounds__(T::kThreads, T::kCtasPerSm) void decode_balanced_ke
         if (lane == 0) set_status(p.status, B200KV_STATUS_WAIT_TIMEOUT);
         return;  // every other wait in this CTA is bounded as well
       }
-      consume_stage<T>(st, ring, stage, head, 0, lane);
+      if constexpr (T::kFp8) {
+        const int base = a0 + c * ST;
+        consume_stage_fp8(st, ring, stage, head, lane, base, max(seg.pos0, base),
+                          cfg.page_size);
+      } else {
+        consume_stage<T>(st, ring, stage, head, 0, lane);
+      }
       __syncwarp();
       if (lane == 0) mbar_arrive(ring.empty_bar(stage));
     }
@@ -310,36 +328,45 @@ bool decode_balanced_supported(const Gemma4KvCacheConfig &c, int q_heads,
          batch_count <= kMaxBalancedBatch;
 }
 
-cudaError_t decode_attention_balanced_bf16(const DecodeArgs &a,
-                                           cudaStream_t stream) {
-  using T = DecodeTraits<256, 8, 2, 8>;
+namespace {
+
+template <class T>
+cudaError_t launch_balanced(BalancedParams p, int64_t scratch_slots,
+                            cudaStream_t stream) {
   constexpr int kSmem = T::kRingBytes + (2 * kMaxBalancedBatch + 1) * 4;
   static_assert(2 * kSmem <= 226 * 1024, "two CTAs per SM");
-  const Gemma4KvCacheConfig &c = a.cfg;
-  if (!decode_balanced_supported(c, a.q_heads, a.batch_count)) {
-    return cudaErrorInvalidValue;
-  }
   int device = 0, sm_count = 0;
   cudaError_t st = cudaGetDevice(&device);
   if (st != cudaSuccess) return st;
   st = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
   if (st != cudaSuccess) return st;
-  // Scratch holds batch * num_splits slots per head; slot c + b needs
-  // num_ctas + batch - 1 of them.
-  const int64_t capacity = int64_t(a.batch_count) * a.num_splits;
-  const int64_t num_ctas =
-      std::min<int64_t>(int64_t(sm_count) * T::kCtasPerSm, capacity - a.batch_count);
-  if (num_ctas < 1 || a.partial_m == nullptr || a.partial_l == nullptr ||
-      a.partial_acc == nullptr) {
+  // Slot c + b needs num_ctas + batch - 1 slots per head.
+  const int64_t num_ctas = std::min<int64_t>(int64_t(sm_count) * T::kCtasPerSm,
+                                             scratch_slots - p.batch_count);
+  if (num_ctas < 1 || p.partial_m == nullptr || p.partial_l == nullptr ||
+      p.partial_acc == nullptr) {
     return cudaErrorInvalidValue;
   }
-  BalancedParams p;
+  p.num_ctas = int32_t(num_ctas);
+  st = cudaFuncSetAttribute(decode_balanced_kernel<T>,
+                            cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+  if (st != cudaSuccess) return st;
+  st = launch_pdl(decode_balanced_kernel<T>, dim3(unsigned(num_ctas)),
+                  dim3(T::kThreads), kSmem, stream, p);
+  if (st != cudaSuccess) return st;
+  return launch_pdl(balanced_combine_kernel<256>,
+                    dim3(p.batch_count * p.q_heads), dim3(kCombineThreads), 0,
+                    stream, p, int(T::kStageTokens));
+}
+
+BalancedParams balanced_params(const DecodeArgs &a) {
+  BalancedParams p = {};
   p.out = a.out;
   p.lse = a.lse;
   p.q = a.q;
   p.cache_k = a.cache_k;
   p.cache_v = a.cache_v;
-  p.cfg = c;
+  p.cfg = a.cfg;
   p.page_table = a.page_table;
   p.seq_lengths = a.seq_lengths;
   p.layer = a.layer;
@@ -349,17 +376,51 @@ cudaError_t decode_attention_balanced_bf16(const DecodeArgs &a,
   p.partial_m = a.partial_m;
   p.partial_l = a.partial_l;
   p.partial_acc = a.partial_acc;
-  p.num_ctas = int32_t(num_ctas);
   p.status = a.status;
-  st = cudaFuncSetAttribute(decode_balanced_kernel<T>,
-                            cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
-  if (st != cudaSuccess) return st;
-  st = launch_pdl(decode_balanced_kernel<T>, dim3(unsigned(num_ctas)),
-                  dim3(T::kThreads), kSmem, stream, p);
-  if (st != cudaSuccess) return st;
-  return launch_pdl(balanced_combine_kernel<256>,
-                    dim3(a.batch_count * a.q_heads), dim3(kCombineThreads), 0,
-                    stream, p, int(T::kStageTokens));
+  return p;
+}
+
+}  // namespace
+
+cudaError_t decode_attention_balanced_bf16(const DecodeArgs &a,
+                                           cudaStream_t stream) {
+  if (!decode_balanced_supported(a.cfg, a.q_heads, a.batch_count)) {
+    return cudaErrorInvalidValue;
+  }
+  return launch_balanced<DecodeTraits<256, 8, 2, 8>>(
+      balanced_params(a), int64_t(a.batch_count) * a.num_splits, stream);
+}
+
+cudaError_t decode_attention_fp8(const DecodeArgs &a, const void *cache_k,
+                                 const void *cache_v, const float *scale_k,
+                                 const float *scale_v, cudaStream_t stream) {
+  const Gemma4KvCacheConfig &c = a.cfg;
+  if (a.out == nullptr || a.q == nullptr || cache_k == nullptr ||
+      cache_v == nullptr || scale_k == nullptr || scale_v == nullptr ||
+      a.page_table == nullptr || a.seq_lengths == nullptr ||
+      a.batch_count <= 0 || a.layer < 0 || a.layer >= c.num_layers ||
+      c.num_pages <= 0 || c.page_size <= 0 || c.max_pages_per_seq <= 0 ||
+      c.window_size < 0 || a.num_splits <= 0 || !(a.softmax_scale > 0.0f) ||
+      !decode_balanced_supported(c, a.q_heads, a.batch_count)) {
+    return cudaErrorInvalidValue;
+  }
+  if (c.window_size > 0 &&
+      int64_t(c.max_pages_per_seq) * c.page_size < c.window_size) {
+    return cudaErrorInvalidValue;
+  }
+  const uintptr_t align = reinterpret_cast<uintptr_t>(cache_k) |
+                          reinterpret_cast<uintptr_t>(cache_v) |
+                          reinterpret_cast<uintptr_t>(a.q) |
+                          reinterpret_cast<uintptr_t>(a.out) |
+                          reinterpret_cast<uintptr_t>(a.partial_acc);
+  if ((align & 15u) != 0) return cudaErrorInvalidValue;
+  BalancedParams p = balanced_params(a);
+  p.cache_k = cache_k;
+  p.cache_v = cache_v;
+  p.scale_k = scale_k;
+  p.scale_v = scale_v;
+  return launch_balanced<Fp8DecodeTraits>(
+      p, int64_t(a.batch_count) * a.num_splits, stream);
 }
 
 int decode_balanced_num_splits(int batch_count, int sm_count) {

@@ -23,6 +23,8 @@ struct DecodeTraits {
   static constexpr int kCtasPerSm = CW_ <= 8 ? 2 : 1;
   static constexpr int kWarpsPerHead = kConsumerWarps / HKV;
   static constexpr int kStageTokens = kWarpsPerHead * kTokPerWarp;
+  static constexpr bool kFp8 = false;
+  static constexpr int kElemBytes = 2;
   static constexpr int kRowBytes = HKV * D * 2;  // one token, all heads
   static constexpr int kStageTensorBytes = kStageTokens * kRowBytes;
   static constexpr int kStageBytes = 2 * kStageTensorBytes;  // K then V
@@ -111,8 +113,8 @@ struct Ring {
 };
 
 struct KvSource {
-  const __nv_bfloat16 *cache_k;
-  const __nv_bfloat16 *cache_v;
+  const uint8_t *cache_k;  // byte pointers: elements are bf16 or e4m3
+  const uint8_t *cache_v;
   const int32_t *page_table;
   int32_t layer;
 };
@@ -176,10 +178,10 @@ __device__ __forceinline__ void producer_fill_stage(
             cache_offset(cfg, src.layer, phys, s0 - lp * ps, 0, 0);
         const uint32_t dst_off = uint32_t(s0 - base) * T::kRowBytes;
         const uint32_t nbytes = uint32_t(s1 - s0) * T::kRowBytes;
-        bulk_load_hint(k_dst + dst_off, src.cache_k + off, nbytes,
-                       ring.full_bar(stage), policy);
-        bulk_load_hint(v_dst + dst_off, src.cache_v + off, nbytes,
-                       ring.full_bar(stage), policy);
+        bulk_load_hint(k_dst + dst_off, src.cache_k + off * T::kElemBytes,
+                       nbytes, ring.full_bar(stage), policy);
+        bulk_load_hint(v_dst + dst_off, src.cache_v + off * T::kElemBytes,
+                       nbytes, ring.full_bar(stage), policy);
       }
     }
   }

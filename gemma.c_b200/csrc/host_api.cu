@@ -607,6 +607,98 @@ int b200kv_decode_attention_bf16(b200kv_bf16 *d_out, float *d_lse,
   return b200kv::decode_attention_bf16(a, static_cast<cudaStream_t>(stream));
 }
 
+int b200kv_decode_append_fp8(b200kv_bf16 *d_q_prepared, uint8_t *d_cache_k,
+                             uint8_t *d_cache_v, float *d_scale_k,
+                             float *d_scale_v, Gemma4KvCacheConfig cache_config,
+                             const int32_t *d_page_table,
+                             const int32_t *d_token_position,
+                             int32_t cache_layer, const b200kv_bf16 *d_q,
+                             const b200kv_bf16 *d_k, const b200kv_bf16 *d_v,
+                             const b200kv_bf16 *d_q_norm_weight,
+                             const b200kv_bf16 *d_k_norm_weight,
+                             const float *d_cos, const float *d_sin,
+                             int32_t batch_count, int32_t q_heads,
+                             int32_t rotary_dim, int32_t norm_mode,
+                             b200kv_stream stream) {
+  using bf = __nv_bfloat16;
+  b200kv::AppendArgs a;
+  a.q_prepared = reinterpret_cast<bf *>(d_q_prepared);
+  a.cfg = cache_config;
+  a.page_table = d_page_table;
+  a.token_position = d_token_position;
+  a.cache_layer = cache_layer;
+  a.q = reinterpret_cast<const bf *>(d_q);
+  a.k = reinterpret_cast<const bf *>(d_k);
+  a.v = reinterpret_cast<const bf *>(d_v);
+  a.q_norm_weight = reinterpret_cast<const bf *>(d_q_norm_weight);
+  a.k_norm_weight = reinterpret_cast<const bf *>(d_k_norm_weight);
+  a.cos = d_cos;
+  a.sin = d_sin;
+  a.batch_count = batch_count;
+  a.q_heads = q_heads;
+  a.rotary_dim = rotary_dim;
+  a.norm_mode = norm_mode;
+  return b200kv::decode_append_fp8(a, d_cache_k, d_cache_v, d_scale_k,
+                                   d_scale_v, static_cast<cudaStream_t>(stream));
+}
+
+int b200kv_fp8_append_rows(uint8_t *d_cache_k, uint8_t *d_cache_v,
+                           float *d_scale_k, float *d_scale_v,
+                           Gemma4KvCacheConfig cache_config,
+                           const int32_t *d_page_table,
+                           const int32_t *d_seq_batch,
+                           const int32_t *d_first_position,
+                           const int32_t *d_row_count,
+                           const int32_t *d_row_start, int32_t run_count,
+                           int32_t max_row_count, int32_t cache_layer,
+                           const b200kv_bf16 *d_k_prepared,
+                           const b200kv_bf16 *d_v_prepared,
+                           b200kv_stream stream) {
+  using bf = __nv_bfloat16;
+  return b200kv::fp8_append_rows(
+      d_cache_k, d_cache_v, d_scale_k, d_scale_v, cache_config, d_page_table,
+      d_seq_batch, d_first_position, d_row_count, d_row_start, run_count,
+      max_row_count, cache_layer, reinterpret_cast<const bf *>(d_k_prepared),
+      reinterpret_cast<const bf *>(d_v_prepared),
+      static_cast<cudaStream_t>(stream));
+}
+
+int b200kv_decode_attention_fp8(b200kv_bf16 *d_out, float *d_lse,
+                                const b200kv_bf16 *d_q_prepared,
+                                const uint8_t *d_cache_k,
+                                const uint8_t *d_cache_v,
+                                const float *d_scale_k, const float *d_scale_v,
+                                Gemma4KvCacheConfig cache_config,
+                                const int32_t *d_page_table,
+                                const int32_t *d_seq_lengths,
+                                int32_t cache_layer, float softmax_scale,
+                                int32_t num_splits, int32_t batch_count,
+                                int32_t q_heads, float *d_partial_m,
+                                float *d_partial_l, float *d_partial_acc,
+                                int32_t *d_status, b200kv_stream stream) {
+  using bf = __nv_bfloat16;
+  b200kv::DecodeArgs a;
+  a.out = reinterpret_cast<bf *>(d_out);
+  a.lse = d_lse;
+  a.q = reinterpret_cast<const bf *>(d_q_prepared);
+  a.cfg = cache_config;
+  a.page_table = d_page_table;
+  a.seq_lengths = d_seq_lengths;
+  a.layer = cache_layer;
+  a.softmax_scale = softmax_scale;
+  a.split_size = 0;
+  a.num_splits = num_splits;
+  a.batch_count = batch_count;
+  a.q_heads = q_heads;
+  a.partial_m = d_partial_m;
+  a.partial_l = d_partial_l;
+  a.partial_acc = d_partial_acc;
+  a.status = d_status;
+  return b200kv::decode_attention_fp8(a, d_cache_k, d_cache_v, d_scale_k,
+                                      d_scale_v,
+                                      static_cast<cudaStream_t>(stream));
+}
+
 void b200kv_decode_workspace_bytes(int32_t batch_count, int32_t q_heads,
                                    int32_t head_dim, int32_t num_splits,
                                    size_t *partial_m_bytes,

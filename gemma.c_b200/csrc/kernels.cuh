@@ -37,6 +37,11 @@ cudaError_t decode_attention_bf16(const DecodeArgs &args, cudaStream_t stream);
 // only sizes the scratch (batch * num_splits slots per head).
 cudaError_t decode_attention_balanced_bf16(const DecodeArgs &args,
                                            cudaStream_t stream);
+// FP8 e4m3 cache (one fp32 scale per page and KV head): balanced partition
+// only; args.cache_k / cache_v are ignored in favour of the byte pointers.
+cudaError_t decode_attention_fp8(const DecodeArgs &args, const void *cache_k,
+                                 const void *cache_v, const float *scale_k,
+                                 const float *scale_v, cudaStream_t stream);
 bool decode_balanced_supported(const Gemma4KvCacheConfig &cfg, int q_heads,
                                int batch_count);
 int decode_balanced_num_splits(int batch_count, int sm_count);
@@ -90,6 +95,19 @@ struct PrefillPrepArgs {
 
 cudaError_t prefill_prep_bf16(const PrefillPrepArgs &args,
                               cudaStream_t stream);
+
+// FP8 e4m3 cache (fp8_cache.cu). args.cache_k / cache_v are unused.
+cudaError_t decode_append_fp8(const AppendArgs &args, uint8_t *cache_k,
+                              uint8_t *cache_v, float *scale_k, float *scale_v,
+                              cudaStream_t stream);
+cudaError_t fp8_append_rows(uint8_t *cache_k, uint8_t *cache_v, float *scale_k,
+                            float *scale_v, Gemma4KvCacheConfig config,
+                            const int32_t *page_table, const int32_t *seq_batch,
+                            const int32_t *first_position,
+                            const int32_t *row_count, const int32_t *row_start,
+                            int32_t seq_count, int32_t max_row_count,
+                            int32_t layer, const __nv_bfloat16 *k,
+                            const __nv_bfloat16 *v, cudaStream_t stream);
 
 cudaError_t kv_cache_write_bf16(__nv_bfloat16 *cache_k, __nv_bfloat16 *cache_v,
                                 Gemma4KvCacheConfig config,

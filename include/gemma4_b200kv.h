@@ -249,6 +249,69 @@ int b200kv_decode_attention_bf16(b200kv_bf16 *d_out, float *d_lse,
                                  float *d_partial_acc, int32_t *d_status,
                                  b200kv_stream stream);
 
+/* ------------------------------------------------------------------ *
+ * FP8 e4m3 KV cache with one fp32 scale per (16-token page, KV head) and
+ * tensor. No counterpart in the reference, whose caches are bf16 only. Cache
+ * tensors keep the [layer, page, offset, head, dim] layout with one byte per
+ * element; d_scale_k / d_scale_v are fp32 [layer, page, head] and must be
+ * zero before a cache is first used. Quantisation rule, per tensor, page and
+ * head, per call: with R the rows of the call landing in the page and o0 the
+ * offset of the first, s_old = (o0 == 0 ? 0 : scale), s_new = max(s_old,
+ * max(amax(R)/448, FLT_MIN)); if s_new > s_old the rows already stored below
+ * o0 are re-encoded as enc(dec(byte)*s_old/s_new); R is stored as enc(x/s_new)
+ * (round to nearest even, saturating at +-448) and the scale becomes s_new.
+ * Built for 8 KV heads x 256 (16 query heads, rotary 256).
+ * ------------------------------------------------------------------ */
+/* Fused decode append (prep as b200kv_decode_append_bf16, then the rule above
+ * for the one new row of every sequence). */
+int b200kv_decode_append_fp8(b200kv_bf16 *d_q_prepared, uint8_t *d_cache_k,
+                             uint8_t *d_cache_v, float *d_scale_k,
+                             float *d_scale_v, Gemma4KvCacheConfig cache_config,
+                             const int32_t *d_page_table,
+                             const int32_t *d_token_position,
+                             int32_t cache_layer, const b200kv_bf16 *d_q,
+                             const b200kv_bf16 *d_k, const b200kv_bf16 *d_v,
+                             const b200kv_bf16 *d_q_norm_weight,
+                             const b200kv_bf16 *d_k_norm_weight,
+                             const float *d_cos, const float *d_sin,
+                             int32_t batch_count, int32_t q_heads,
+                             int32_t rotary_dim, int32_t norm_mode,
+                             b200kv_stream stream);
+/* Bulk append of already prepared rows (a prompt): run i covers positions
+ * [d_first_position[i], + d_row_count[i]) of sequence d_seq_batch[i]; its rows
+ * start at row d_row_start[i] of d_k_prepared / d_v_prepared
+ * ([rows, kv_heads, head_dim] bf16). max_row_count >= every d_row_count[i]
+ * (sizes the grid). All rows of a run that share a page are quantised as one
+ * group. The rows of one call must map to distinct cache rows. */
+int b200kv_fp8_append_rows(uint8_t *d_cache_k, uint8_t *d_cache_v,
+                           float *d_scale_k, float *d_scale_v,
+                           Gemma4KvCacheConfig cache_config,
+                           const int32_t *d_page_table,
+                           const int32_t *d_seq_batch,
+                           const int32_t *d_first_position,
+                           const int32_t *d_row_count,
+                           const int32_t *d_row_start, int32_t run_count,
+                           int32_t max_row_count, int32_t cache_layer,
+                           const b200kv_bf16 *d_k_prepared,
+                           const b200kv_bf16 *d_v_prepared,
+                           b200kv_stream stream);
+/* Decode attention over the fp8 cache, dequantisation fused (K scale on the
+ * score, V scale on the softmax weight). Always the balanced partition; the
+ * scratch holds batch * q_heads * num_splits rows (b200kv_plan_balanced). */
+int b200kv_decode_attention_fp8(b200kv_bf16 *d_out, float *d_lse,
+                                const b200kv_bf16 *d_q_prepared,
+                                const uint8_t *d_cache_k,
+                                const uint8_t *d_cache_v,
+                                const float *d_scale_k, const float *d_scale_v,
+                                Gemma4KvCacheConfig cache_config,
+                                const int32_t *d_page_table,
+                                const int32_t *d_seq_lengths,
+                                int32_t cache_layer, float softmax_scale,
+                                int32_t num_splits, int32_t batch_count,
+                                int32_t q_heads, float *d_partial_m,
+                                float *d_partial_l, float *d_partial_acc,
+                                int32_t *d_status, b200kv_stream stream);
+
 enum {
   B200KV_STATUS_OK = 0,
   B200KV_STATUS_WAIT_TIMEOUT = 1 /* a bounded mbarrier wait ran out */
