@@ -44,13 +44,15 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--seqs", type=int, default=64)
+    ap.add_argument("--seqs", type=int, default=0, help="sequences in the batch (cfg3: 64, cfg5: 32)")
     ap.add_argument("--min-ctx", type=int, default=512)
     ap.add_argument("--max-ctx", type=int, default=32768)
     ap.add_argument("--seed", type=int, default=20260)
     ap.add_argument("--e2e-steps", type=int, default=10)
     ap.add_argument("--cpu-seconds", type=float, default=10.0, help="target CPU time of the cpu_baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-reference-cuda", action="store_true",
+                    help="skip timing the reference's own CUDA kernels (oracle/_ref) beside the library")
     ap.add_argument("--split-global", type=int, default=0, help="override the planned global split size")
     ap.add_argument("--split-local", type=int, default=0)
     ap.add_argument("--workload", default="cfg3", choices=["cfg1", "cfg2", "cfg3", "cfg4", "cfg5"],
@@ -68,7 +70,7 @@ def parse_args():
 # --------------------------------------------------------------------------- workload description
 def context_lengths(args) -> np.ndarray:
     rng = np.random.default_rng(args.seed)
-    return rng.integers(args.min_ctx, args.max_ctx + 1, size=args.seqs).astype(np.int64)
+    return rng.integers(args.min_ctx, args.max_ctx + 1, size=args.seqs or 64).astype(np.int64)
 
 
 def shard_sequences(ctx: np.ndarray, world: int) -> list[list[int]]:
@@ -458,6 +460,63 @@ def cpu_layer_step_sample(ctx: np.ndarray, threads: int, target_seconds: float, 
             "keys": int(sample_ctx.sum()) + int(B), "runs": runs, "us_per_layer_step": secs / runs * 1e6}
 
 
+def reference_cuda_numbers(wl, torch, step_index: int):
+    """The reference's own CUDA kernels (compiled from the gemma.c sources for sm_100a into oracle/_ref, when
+    that library is present) on the timed layer of this rank's workload, same cache, same inputs, same GPU:
+    fused append phase, split phase + reduce phase at the reference's default split size of 20 keys
+    (src/gemma4.h:24) and at larger splits. Reported beside the library's number; never part of it."""
+    from oracle import ref_binding as ref
+
+    sp = wl.spec
+    if not ref.available() or sp.fp8 or sp.hkv != 8:
+        return None
+    i = wl.timed_layer
+    is_global = wl.layer_is_global(i)
+    cfg = (wl.g_cfg if is_global else wl.l_cfg).astuple()
+    ck, cv = (wl.g_k, wl.g_v) if is_global else (wl.l_k, wl.l_v)
+    table = wl.g_table if is_global else wl.l_table
+    cos, sin = (wl.g_cos, wl.g_sin) if is_global else (wl.l_cos, wl.l_sin)
+    layer = wl.cache_layer_of(i)
+    pos, length = wl.pos_all[step_index], wl.len_all[step_index]
+    window = 0 if is_global else WINDOW
+    longest = int(wl.ctx.max()) + step_index + 1
+    live = min(longest, window) if window else longest
+    nbytes = attention_kernel_bytes(wl.ctx + step_index + 1, window, sp.hkv, sp.e_kv)
+    qp = torch.empty_like(wl.q_prepared[i])
+    out = torch.empty_like(wl.out[i])
+
+    def timed(fn, reps):
+        fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / reps * 1e3
+
+    result = {"kernels": "phase_decode_q_paged_kv_norm_rope / phase_decode_paged_grouped_split / "
+                         "phase_decode_paged_reduce of src/gemma4_flash_attention_decode.cu, sm_100a build",
+              "layer": "global" if is_global else "sliding", "attention": []}
+    result["append_us"] = timed(lambda: ref.decode_append(qp, ck, cv, cfg, table, pos, layer, wl.raw_q[i], wl.raw_k[i],
+                                                          wl.raw_v[i], wl.q_w, wl.k_w, cos, sin, wl.B), 5)
+    for split in (20, 64, 256):
+        nsplit = max(1, -(-live // split))
+        rows = wl.B * sp.hq * nsplit
+        if rows * (D + 2) * 4 > 8e9 or nsplit > 65535:
+            continue
+        pm = torch.empty(rows, dtype=torch.float32, device="cuda")
+        pl = torch.empty(rows, dtype=torch.float32, device="cuda")
+        pacc = torch.empty(rows * D, dtype=torch.float32, device="cuda")
+        us = timed(lambda: ref.decode_attention(out, pm, pl, pacc, qp, ck, cv, table, length, cfg, layer,
+                                                1.0 / math.sqrt(D), split, nsplit, wl.B), 2)
+        result["attention"].append({"split_size": split, "num_splits": nsplit, "us": us,
+                                    "GBps": nbytes / (us * 1e-6) / 1e9})
+        del pm, pl, pacc
+    return result
+
+
 def run_reference_arm(args):
     """CPU restatement of the reference's path on all host cores; each step is one global layer-step over
     a bounded sample of the workload's sequences."""
@@ -516,7 +575,7 @@ def plan_workload(args, world: int, rank: int):
         mine = ctx_all[shard_sequences(ctx_all, world)[rank]]
         return Spec(name, WORKLOADS[name], 5, 1), ctx_all, mine, f"sequence-sharded x{world}, no collective", "strong"
     if name == "cfg5":
-        ctx_all = np.full(32, 8192, dtype=np.int64)
+        ctx_all = np.full(args.seqs or 32, 8192, dtype=np.int64)
         mine = ctx_all[shard_sequences(ctx_all, world)[rank]]
         return (Spec(name, WORKLOADS[name], 0, 1, fp8=True), ctx_all, mine,
                 f"sequence-sharded x{world}, no collective", "strong")
@@ -545,7 +604,7 @@ def workload_config(args, world, where, parallelism=None, layers=None):
         "where": where,
     }
     if args.workload == "cfg3":
-        cfg.update({"sequences": args.seqs, "ctx_range": [args.min_ctx, args.max_ctx], "layers_per_step": 6,
+        cfg.update({"sequences": args.seqs or 64, "ctx_range": [args.min_ctx, args.max_ctx], "layers_per_step": 6,
                     "l2": "inputs larger than L2: every step streams more than 1 GB per rank before any byte "
                           "is revisited"})
     elif layers is not None:
@@ -703,6 +762,13 @@ def main():
             line["roofline"]["traffic_source"] = t.get("source")
         except (ValueError, KeyError):
             pass
+    if not args.no_reference_cuda and world == 1:
+        try:
+            ref_cuda = reference_cuda_numbers(wl, torch, first_timed)
+        except Exception as exc:  # the second checker must never cost the bench line
+            ref_cuda = {"error": repr(exc)}
+        if ref_cuda is not None:
+            line["reference_cuda"] = ref_cuda
     if not args.no_cpu_baseline and world == 1:
         threads = os.cpu_count() or 1
         base = cpu_layer_step_sample(ctx_all, threads, args.cpu_seconds)
