@@ -136,15 +136,24 @@ __global__ __launch_bounds__(T::kThreads, T::kCtasPerSm) void decode_balanced_ke
   const int lane = int(threadIdx.x) & 31;
   const Gemma4KvCacheConfig &cfg = p.cfg;
 
-  pdl_wait_for_predecessor();
+  // Launched programmatically after the append of this layer-step: lengths,
+  // page table and every cache row except the ones that append is writing were
+  // complete before that append started, so the partition and the first
+  // stages of old keys do not wait for it. What the append produces -- the
+  // prepared q and the rows of the page that holds each sequence's newest key
+  // (the fp8 append may re-encode that whole page) -- is touched only after
+  // pdl_wait_for_predecessor(). Every CTA waits before it exits, so "this grid
+  // is complete" still implies "everything before it is complete".
   pdl_release_successor();
 
   scan_live_keys(p, s_prefix, s_first, s_warp_sums);
   const int total = s_prefix[p.batch_count];
-  if (total == 0) return;  // the combine writes the zero rows
-  const int width = range_width(total, p.num_ctas, ST);
+  const int width = range_width(max(total, 1), p.num_ctas, ST);
   const int r0 = int(blockIdx.x) * width;
-  if (r0 >= total) return;
+  if (total == 0 || r0 >= total) {  // nothing to do; the combine zeroes empty rows
+    pdl_wait_for_predecessor();
+    return;
+  }
   const int r1 = min(total, r0 + width);
   int b_start = 0;
   {
@@ -167,13 +176,21 @@ __global__ __launch_bounds__(T::kThreads, T::kCtasPerSm) void decode_balanced_ke
                           static_cast<const uint8_t *>(p.cache_v),
                           p.page_table, p.layer};
     bool ok = true;
+    bool waited = false;
     int it = 0;  // stages armed so far, across all pieces of the range
     int b = b_start, flat = r0;
     Segment seg;
     while (ok && next_segment(b, flat, r1, s_prefix, s_first, seg)) {
       const int a0 = (seg.pos0 / ST) * ST;
       const int nchunks = div_up(seg.pos1 - a0, ST);
+      // first position of the page that holds this sequence's newest key
+      const int seq_len = s_first[seg.b] + s_prefix[seg.b + 1] - s_prefix[seg.b];
+      const int fresh = ((seq_len - 1) / cfg.page_size) * cfg.page_size;
       for (int c = 0; c < nchunks; ++c, ++it) {
+        if (!waited && min(seg.pos1, a0 + (c + 1) * ST) > fresh) {
+          pdl_wait_for_predecessor();
+          waited = true;
+        }
         const int stage = it % kStages;
         const int fill = it / kStages;
         if (fill > 0 &&
@@ -197,11 +214,13 @@ __global__ __launch_bounds__(T::kThreads, T::kCtasPerSm) void decode_balanced_ke
       const int fill = (it - 1 - s) / kStages;
       if (!mbar_wait_bounded(ring.full_bar(s), uint32_t(fill) & 1u)) ok = false;
     }
+    if (!waited) pdl_wait_for_predecessor();
     if (!ok && lane == 0) set_status(p.status, B200KV_STATUS_WAIT_TIMEOUT);
     return;
   }
 
   // -------------------------------- consumers --------------------------------
+  pdl_wait_for_predecessor();  // the prepared q comes from the append
   const int head = warp;  // kWarpsPerHead == 1
   WarpState<T> st;
   int b = b_start, flat = r0;
@@ -273,7 +292,6 @@ __global__ __launch_bounds__(kCombineThreads) void balanced_combine_kernel(
   const int lane = tid & 31;
   const int warp = tid >> 5;
 
-  pdl_wait_for_predecessor();
   pdl_release_successor();
 
   int before = 0, all = 0, mine = 0;
@@ -305,6 +323,9 @@ __global__ __launch_bounds__(kCombineThreads) void balanced_combine_kernel(
     mine += s_sum[2][w];
   }
 
+  // The lengths were final before the split kernel started; its partials and
+  // directly written rows are not.
+  pdl_wait_for_predecessor();
   __nv_bfloat16 *out_row = p.out + int64_t(row) * D;
   float *lse_row = p.lse != nullptr ? p.lse + row : nullptr;
   if (mine == 0) {

@@ -234,6 +234,15 @@ int b200kv_decode_append_bf16(b200kv_bf16 *d_q_prepared,
  * is (still batch * q_heads * num_splits rows; use b200kv_plan_balanced).
  * Available for 8 KV heads x 256 with 16 query heads and batch <= 1024;
  * cudaErrorInvalidValue otherwise.
+ *
+ * Ordering: the call may follow b200kv_decode_append_* on the same stream
+ * with nothing in between (as b200kv_decode_layer_step_bf16 does). The
+ * kernels are launched programmatically dependent: the attention starts
+ * streaming keys while that append is still running and only waits for it
+ * before it touches the prepared q or the page that holds each sequence's
+ * newest key. The append must therefore be the one of this decode step, i.e.
+ * write position seq_length - 1; rows of older pages must have been written
+ * by earlier work on the stream. Any other predecessor is waited for in full.
  * ------------------------------------------------------------------ */
 int b200kv_decode_attention_bf16(b200kv_bf16 *d_out, float *d_lse,
                                  const b200kv_bf16 *d_q_prepared,
