@@ -61,6 +61,9 @@ def parse_args():
     ap.add_argument("--partition", default="balanced", choices=["balanced", "splits"],
                     help="balanced: keys of the batch divided evenly over a fixed grid (split_size 0); "
                          "splits: fixed-size splits as the reference defines them")
+    ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"],
+                    help="replay each step from a CUDA graph captured once (auto: on for the batch-1 latency "
+                         "workloads cfg1/cfg2, where the host cannot issue 3 launches per layer fast enough)")
     ap.add_argument("--emulate-world", type=int, default=0,
                     help="tuning aid: on one GPU, run the shard that rank --emulate-rank of this many ranks would own")
     ap.add_argument("--emulate-rank", type=int, default=0)
@@ -356,11 +359,48 @@ class RankWorkload:
         self.raw_k.copy_(k)
         self.raw_v.copy_(v)
 
+    def enable_graph(self, first_step: int):
+        """Capture one step into a CUDA graph. The captured launches read the step's positions and lengths
+        from two fixed buffers that the graph itself advances by one at its end, so replaying it walks
+        through consecutive decode steps. The per-layer timing hooks are not captured."""
+        torch = self.torch
+        self.pos_cur = self.pos_all[first_step].clone()
+        self.len_cur = self.len_all[first_step].clone()
+        self.graph_next = first_step
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):      # warm-up outside capture (first-use attribute calls)
+            self._launch_step(self.pos_cur.data_ptr(), self.len_cur.data_ptr(), None, side.cuda_stream)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self._launch_step(self.pos_cur.data_ptr(), self.len_cur.data_ptr(), None,
+                              torch.cuda.current_stream().cuda_stream)
+            self.pos_cur.add_(1)
+            self.len_cur.add_(1)
+        torch.cuda.synchronize()
+
     def step(self, s: int):
         """One decode step, inputs resident in HBM."""
+        if getattr(self, "graph", None) is not None:
+            assert s == self.graph_next, "graph replay walks consecutive steps"
+            self.graph.replay()
+            self.graph_next += 1
+            if self.spec.gather and self.world > 1:
+                import torch.distributed as dist
+
+                dist.all_gather_into_tensor(self.out_all, self.out)
+            return
+        self._launch_step(self.pos_all[s].data_ptr(), self.len_all[s].data_ptr(), s, self.stream)
+        if self.spec.gather and self.world > 1:
+            # KV-head sharding: every rank holds all heads' outputs after the step
+            import torch.distributed as dist
+
+            dist.all_gather_into_tensor(self.out_all, self.out)
+
+    def _launch_step(self, pos: int, length: int, s, stream: int):
         kv = self.kv
-        pos = self.pos_all[s].data_ptr()
-        length = self.len_all[s].data_ptr()
         if self.spec.fp8:
             # the fp8 cache has its own two entry points; the layer loop is here instead of in the library
             for i in range(self.L):
@@ -368,28 +408,23 @@ class RankWorkload:
                 kv.decode_append_fp8(self.q_prepared[i], self.g_k, self.g_v, self.g_sk, self.g_sv, self.g_cfg,
                                      self.g_table, pos, li, self.raw_q[i], self.raw_k[i], self.raw_v[i], self.q_w,
                                      self.k_w, self.g_cos, self.g_sin, self.B, self.spec.hq, D,
-                                     kv.NORM_RSQRT_APPROX, stream=self.stream)
-                if i == self.timed_layer:
-                    self.ev_begin[s].record(self.stream)
+                                     kv.NORM_RSQRT_APPROX, stream=stream)
+                if i == self.timed_layer and s is not None:
+                    self.ev_begin[s].record(stream)
                 kv.decode_attention_fp8(self.out[i], self.lse[i], self.q_prepared[i], self.g_k, self.g_v, self.g_sk,
                                         self.g_sv, self.g_cfg, self.g_table, length, li, 1.0 / math.sqrt(D),
                                         self.g_nsplit, self.B, self.spec.hq, self.pm, self.pl, self.pacc,
-                                        self.status, stream=self.stream)
-                if i == self.timed_layer:
-                    self.ev_end[s].record(self.stream)
+                                        self.status, stream=stream)
+                if i == self.timed_layer and s is not None:
+                    self.ev_end[s].record(stream)
         else:
             for i in range(self.L):
                 self.layers[i].token_position = pos
                 self.layers[i].seq_lengths = length
             g = self.layers[self.timed_layer]
-            g.event_before_attention = self.ev_begin[s].handle
-            g.event_after_attention = self.ev_end[s].handle
-            kv.decode_step(self.layers, self.L, stream=self.stream)
-        if self.spec.gather and self.world > 1:
-            # KV-head sharding: every rank holds all heads' outputs after the step
-            import torch.distributed as dist
-
-            dist.all_gather_into_tensor(self.out_all, self.out)
+            g.event_before_attention = self.ev_begin[s].handle if s is not None else None
+            g.event_after_attention = self.ev_end[s].handle if s is not None else None
+            kv.decode_step(self.layers, self.L, stream=stream)
 
     def step_e2e(self, s: int):
         """The same step called with host buffers: projections come from pinned host memory and the
@@ -602,6 +637,8 @@ def workload_config(args, world, where, parallelism=None, layers=None):
         "parallelism": parallelism or f"x{world}",
         "partition": args.partition,
         "where": where,
+        "launch": "one CUDA graph replay per step" if (args.graph == "on" or (args.graph == "auto" and args.workload
+                  in ("cfg1", "cfg2"))) else "stream launches (programmatic dependent launch between kernels)",
     }
     if args.workload == "cfg3":
         cfg.update({"sequences": args.seqs or 64, "ctx_range": [args.min_ctx, args.max_ctx], "layers_per_step": 6,
@@ -648,7 +685,9 @@ def main():
     if args.emulate_world > 1 and world == 1 and args.workload in ("cfg3", "cfg5"):
         ctx = ctx_all[shard_sequences(ctx_all, args.emulate_world)[args.emulate_rank]]
     e2e_warm = 3
-    total_steps = args.warmup + args.steps + e2e_warm + args.e2e_steps
+    use_graph = args.graph == "on" or (args.graph == "auto" and args.workload in ("cfg1", "cfg2"))
+    probe_steps = 8 if use_graph else 0     # ungraphed steps after the timed region, for the per-kernel events
+    total_steps = args.warmup + args.steps + e2e_warm + args.e2e_steps + probe_steps
     wl = RankWorkload(kv, torch, ctx, total_steps, args.seed + 1000 * rank, args, spec)
     torch.cuda.synchronize()
 
@@ -660,6 +699,8 @@ def main():
     if sampler:
         sampler.mark("load_begin")
     s = 0
+    if use_graph:
+        wl.enable_graph(0)
     for _ in range(args.warmup):
         wl.step(s)
         s += 1
@@ -677,7 +718,8 @@ def main():
     if sampler:
         sampler.mark("timed_end")
     elapsed_ms = t0.elapsed_time(t1)
-    attn_ms = [wl.ev_begin[i].elapsed_ms(wl.ev_end[i]) for i in range(first_timed, first_timed + args.steps)]
+    if not use_graph:
+        attn_ms = [wl.ev_begin[i].elapsed_ms(wl.ev_end[i]) for i in range(first_timed, first_timed + args.steps)]
     step_bytes = sum(wl.bytes_for_step(i)[0] for i in range(first_timed, first_timed + args.steps))
     attn_bytes = statistics.mean(wl.bytes_for_step(i)[1] for i in range(first_timed, first_timed + args.steps))
     status = int(wl.status[0].item())
@@ -697,6 +739,16 @@ def main():
     barrier()
     e2e_ms = e0.elapsed_time(e1)
     e2e_bytes = sum(wl.bytes_for_step(i)[0] for i in range(first_e2e, first_e2e + args.e2e_steps))
+    if use_graph:
+        # per-kernel events cannot be read out of a replayed graph: time the attention launch of the same
+        # workload in a few ungraphed steps right after
+        wl.graph = None
+        probe0 = s
+        for _ in range(probe_steps):
+            wl.step(s)
+            s += 1
+        torch.cuda.synchronize()
+        attn_ms = [wl.ev_begin[i].elapsed_ms(wl.ev_end[i]) for i in range(probe0 + 3, probe0 + probe_steps)]
     if sampler:
         sampler.mark("load_end")
         clocks = sampler.stop()
