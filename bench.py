@@ -806,7 +806,7 @@ def main():
         "device_status": status,
         "clocks": clocks,
     }
-    traffic_path = REPO / "profiles" / "decode_split_traffic.json"
+    traffic_path = REPO / "profiles" / "decode_balanced_traffic.json"
     if traffic_path.exists():
         try:
             t = json.loads(traffic_path.read_text())
