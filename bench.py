@@ -77,15 +77,13 @@ def context_lengths(args) -> np.ndarray:
 
 
 def shard_sequences(ctx: np.ndarray, world: int) -> list[list[int]]:
-    """Greedy longest-first partition of sequences over ranks by context length."""
-    order = np.argsort(-ctx, kind="stable")
-    load = [0] * world
-    shards: list[list[int]] = [[] for _ in range(world)]
-    for i in order:
-        r = int(np.argmin(load))
-        shards[r].append(int(i))
-        load[r] += int(ctx[i])
-    return shards
+    """Greedy longest-first partition of sequences over ranks (gemma.c_b200/sharding.py)."""
+    from __graft_entry__ import load_package
+
+    load_package()
+    from gemma_c_b200 import sharding
+
+    return sharding.shard_sequences(ctx, world)
 
 
 def layer_step_bytes(seq_len_after_append: np.ndarray, window: int, hkv: int = HKV, e_kv: int = E_KV) -> int:
