@@ -17,6 +17,8 @@
 // results within fp32 summation order. Partials live in the caller's scratch:
 // the partial of CTA c for sequence b sits in slot c + b, which is unique
 // because ranges and sequences advance together.
+#include <type_traits>
+
 #include "decode_common.cuh"
 #include "decode_fp8.cuh"
 #include "kernels.cuh"
@@ -200,7 +202,7 @@ __global__ __launch_bounds__(T::kThreads, T::kCtasPerSm) void decode_balanced_ke
         }
         const int base = a0 + c * ST;
         if constexpr (T::kFp8) {
-          const Fp8Scales scales = {p.scale_k, p.scale_v};
+          const Fp8Scales scales = {p.scale_k, p.scale_v, p.scale_log2};
           producer_fill_stage_fp8(ring, src, scales, cfg, seg.b, base,
                                   max(seg.pos0, base), min(seg.pos1, base + ST),
                                   stage, policy, lane);
@@ -222,20 +224,28 @@ __global__ __launch_bounds__(T::kThreads, T::kCtasPerSm) void decode_balanced_ke
   // -------------------------------- consumers --------------------------------
   pdl_wait_for_predecessor();  // the prepared q comes from the append
   const int head = warp;  // kWarpsPerHead == 1
-  WarpState<T> st;
+  std::conditional_t<T::kFp8, Fp8WarpState, WarpState<T>> st;
   int b = b_start, flat = r0;
   Segment seg, next;
   bool have = next_segment(b, flat, r1, s_prefix, s_first, seg);
-  uint4 raw[G];
-  load_q_raw<T>(raw, p.q, int64_t(seg.b) * p.q_heads + head * G, lane);
+  [[maybe_unused]] uint4 raw[G];
+  if constexpr (!T::kFp8) {
+    load_q_raw<T>(raw, p.q, int64_t(seg.b) * p.q_heads + head * G, lane);
+  }
   int it = 0;
   while (have) {
-    st.set_q(raw, p.scale_log2);
+    if constexpr (T::kFp8) {
+      st.load_q(p.q + (int64_t(seg.b) * p.q_heads + head * G) * T::D, lane);
+    } else {
+      st.set_q(raw, p.scale_log2);
+    }
     st.reset();
     // Fetch the next sequence's query rows while this one streams.
     const bool have_next = next_segment(b, flat, r1, s_prefix, s_first, next);
-    if (have_next) {
-      load_q_raw<T>(raw, p.q, int64_t(next.b) * p.q_heads + head * G, lane);
+    if constexpr (!T::kFp8) {
+      if (have_next) {
+        load_q_raw<T>(raw, p.q, int64_t(next.b) * p.q_heads + head * G, lane);
+      }
     }
     const int a0 = (seg.pos0 / ST) * ST;
     const int nchunks = div_up(seg.pos1 - a0, ST);
@@ -247,9 +257,7 @@ __global__ __launch_bounds__(T::kThreads, T::kCtasPerSm) void decode_balanced_ke
         return;  // every other wait in this CTA is bounded as well
       }
       if constexpr (T::kFp8) {
-        const int base = a0 + c * ST;
-        consume_stage_fp8(st, ring, stage, head, lane, base, max(seg.pos0, base),
-                          cfg.page_size);
+        consume_stage_fp8(st, ring, stage, head, lane);
       } else {
         consume_stage<T>(st, ring, stage, head, 0, lane);
       }
@@ -422,6 +430,7 @@ cudaError_t decode_attention_fp8(const DecodeArgs &a, const void *cache_k,
       a.batch_count <= 0 || a.layer < 0 || a.layer >= c.num_layers ||
       c.num_pages <= 0 || c.page_size <= 0 || c.max_pages_per_seq <= 0 ||
       c.window_size < 0 || a.num_splits <= 0 || !(a.softmax_scale > 0.0f) ||
+      c.page_size % Fp8DecodeTraits::kStageTokens != 0 ||
       !decode_balanced_supported(c, a.q_heads, a.batch_count)) {
     return cudaErrorInvalidValue;
   }

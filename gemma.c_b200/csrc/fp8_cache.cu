@@ -14,8 +14,16 @@
 // enc = round-to-nearest-even e4m3 with saturation to +-448; x are the
 // prepared bf16 values (the same ones the bf16 cache would hold).
 //
-// Cache tensors are [layer, page, offset, head, dim] with one byte per element
-// (the bf16 layout with the element size halved); scales [layer, page, head].
+// V is [layer, page, offset, head, dim] with one byte per element (the bf16
+// layout with the element size halved); scales are [layer, page, head].
+// K has its own order inside a page, chosen for the tensor-core score step of
+// the decode kernel (decode_fp8.cuh): blocks of 8 tokens, inside a block
+// head-major, then token, then the 256-byte row with its 16-byte granules
+// permuted: granule' = granule ^ 4 * (token & 1). A block of 8 tokens is still
+// one contiguous 8 * heads * 256 bytes, so the decode producer copies it whole;
+// one head's 8 rows are contiguous, so the MMA fragment loads are 128-bit and,
+// with the permutation, free of bank conflicts. page_size must be a multiple
+// of 8.
 #include <cuda_fp8.h>
 
 #include <cfloat>
@@ -43,11 +51,28 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// Byte index of element `dim` of row `r` (page offset) of `head`.
+template <bool kIsK>
+__device__ __forceinline__ int64_t fp8_byte_index(const Gemma4KvCacheConfig &c,
+                                                  int layer, int physical, int r,
+                                                  int head, int dim) {
+  if constexpr (!kIsK) {
+    return cache_offset(c, layer, physical, r, head, dim);
+  } else {
+    const int64_t page_bytes = int64_t(c.page_size) * c.num_heads * c.head_dim;
+    const int64_t base = (int64_t(layer) * c.num_pages + physical) * page_bytes;
+    const int tk = r & 7;
+    const int granule = (dim >> 4) ^ ((tk & 1) << 2);
+    return base + (int64_t(r >> 3) * c.num_heads + head) * 8 * c.head_dim +
+           tk * c.head_dim + granule * 16 + (dim & 15);
+  }
+}
+
 // One warp stores `nrows` prepared rows of one (page, head, tensor) starting
 // at page offset o0; value(r, j) is element lane + 32*j of row r as fp32.
 // Applies the rule above, including the requantisation of the rows already in
 // the page.
-template <int D, class RowValue>
+template <int D, bool kIsK, class RowValue>
 __device__ __forceinline__ void fp8_store_rows(uint8_t *cache, float *scale_slot,
                                                const Gemma4KvCacheConfig &c,
                                                int layer, int physical, int head,
@@ -67,19 +92,21 @@ __device__ __forceinline__ void fp8_store_rows(uint8_t *cache, float *scale_slot
   const float s_new = fmaxf(s_old, fmaxf(__fdiv_rn(amax, 448.0f), FLT_MIN));
   if (s_new > s_old) {
     for (int r = 0; r < o0; ++r) {
-      uint8_t *row = cache + cache_offset(c, layer, physical, r, head, 0);
 #pragma unroll
       for (int j = 0; j < D / 32; ++j) {
-        const float v = __fmul_rn(dec_e4m3(row[lane + 32 * j]), s_old);
-        row[lane + 32 * j] = enc_e4m3(__fdiv_rn(v, s_new));
+        uint8_t *at = cache + fp8_byte_index<kIsK>(c, layer, physical, r, head,
+                                                   lane + 32 * j);
+        const float v = __fmul_rn(dec_e4m3(*at), s_old);
+        *at = enc_e4m3(__fdiv_rn(v, s_new));
       }
     }
   }
   for (int r = 0; r < nrows; ++r) {
-    uint8_t *row = cache + cache_offset(c, layer, physical, o0 + r, head, 0);
 #pragma unroll
     for (int j = 0; j < D / 32; ++j) {
-      row[lane + 32 * j] = enc_e4m3(__fdiv_rn(value(r, j), s_new));
+      cache[fp8_byte_index<kIsK>(c, layer, physical, o0 + r, head,
+                                 lane + 32 * j)] =
+          enc_e4m3(__fdiv_rn(value(r, j), s_new));
     }
   }
   if (lane == 0) *scale_slot = s_new;
@@ -140,18 +167,20 @@ __global__ void decode_append_fp8_kernel(Fp8AppendArgs args) {
   if (warp == G) {
     prep_weighted_rope_values<D, ROT, kIeee>(y, x, a.k_norm_weight, cos_row,
                                              sin_row, lane);
-    fp8_store_rows<D>(args.cache_k, args.scale_k + scale_index, c, a.cache_layer,
-                      physical, kv_head, o0, 1, lane, from_registers);
+    fp8_store_rows<D, true>(args.cache_k, args.scale_k + scale_index, c,
+                            a.cache_layer, physical, kv_head, o0, 1, lane,
+                            from_registers);
     if (!has_v) {
       prep_scale_free_values<D, kIeee>(y, x);
-      fp8_store_rows<D>(args.cache_v, args.scale_v + scale_index, c,
-                        a.cache_layer, physical, kv_head, o0, 1, lane,
-                        from_registers);
+      fp8_store_rows<D, false>(args.cache_v, args.scale_v + scale_index, c,
+                               a.cache_layer, physical, kv_head, o0, 1, lane,
+                               from_registers);
     }
   } else if (has_v) {
     prep_scale_free_values<D, kIeee>(y, x);
-    fp8_store_rows<D>(args.cache_v, args.scale_v + scale_index, c, a.cache_layer,
-                      physical, kv_head, o0, 1, lane, from_registers);
+    fp8_store_rows<D, false>(args.cache_v, args.scale_v + scale_index, c,
+                             a.cache_layer, physical, kv_head, o0, 1, lane,
+                             from_registers);
   }
 }
 
@@ -205,10 +234,15 @@ __global__ __launch_bounds__(64) void fp8_append_rows_kernel(Fp8RowsArgs a) {
   auto from_global = [=](int r, int j) {
     return __bfloat162float(src[r * row_stride + lane + 32 * j]);
   };
-  fp8_store_rows<D>(tensor == 0 ? a.cache_k : a.cache_v,
-                    (tensor == 0 ? a.scale_k : a.scale_v) + scale_index, c,
-                    a.layer, physical, head, p0 - logical_page * ps, p1 - p0,
-                    lane, from_global);
+  if (tensor == 0) {
+    fp8_store_rows<D, true>(a.cache_k, a.scale_k + scale_index, c, a.layer,
+                            physical, head, p0 - logical_page * ps, p1 - p0, lane,
+                            from_global);
+  } else {
+    fp8_store_rows<D, false>(a.cache_v, a.scale_v + scale_index, c, a.layer,
+                             physical, head, p0 - logical_page * ps, p1 - p0, lane,
+                             from_global);
+  }
 }
 
 }  // namespace
@@ -234,7 +268,9 @@ cudaError_t decode_append_fp8(const AppendArgs &a, uint8_t *cache_k,
   const int G = a.q_heads / c.num_heads;
   const int warps = G + (a.v != nullptr ? 2 : 1);
   if (warps > 32 || c.num_heads > 65535) return cudaErrorInvalidValue;
-  if (c.head_dim != 256 || a.rotary_dim != 256) return cudaErrorInvalidValue;
+  if (c.head_dim != 256 || a.rotary_dim != 256 || c.page_size % 8 != 0) {
+    return cudaErrorInvalidValue;
+  }
   Fp8AppendArgs args = {a, cache_k, cache_v, scale_k, scale_v};
   const dim3 grid(a.batch_count, c.num_heads);
   if (a.norm_mode == B200KV_NORM_IEEE) {
@@ -261,7 +297,8 @@ cudaError_t fp8_append_rows(uint8_t *cache_k, uint8_t *cache_v, float *scale_k,
       seq_count > 65535 || max_row_count < 0 || layer < 0 ||
       layer >= c.num_layers || c.num_pages <= 0 || c.page_size <= 0 ||
       c.max_pages_per_seq <= 0 || c.batch_size <= 0 || c.window_size < 0 ||
-      c.num_heads <= 0 || c.num_heads > 65535 || c.head_dim != 256) {
+      c.num_heads <= 0 || c.num_heads > 65535 || c.head_dim != 256 ||
+      c.page_size % 8 != 0) {
     return cudaErrorInvalidValue;
   }
   Fp8RowsArgs a = {cache_k, cache_v, scale_k, scale_v, c, page_table, seq_batch,

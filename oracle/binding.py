@@ -87,6 +87,7 @@ def lib() -> ctypes.CDLL:
         "orc_decode_append": (None, [_P, _P, _P, C, _P, _P, c_int32] + [_P] * 7 + [c_int32] * 4),
         "orc_decode_attention_ref": (None, [_P] * 9 + [C, c_int32, c_float] + [c_int32] * 4),
         "orc_decode_attention_f64": (None, [_P] * 7 + [C, c_int32, c_float, c_int32, c_int32]),
+        "orc_fp8_k_index": (c_int64, [C] + [c_int32] * 5),
         "orc_fp8_append": (None, [_P, _P, _P, _P, C, _P, _P, _P, _P, c_int32, c_int32, _P, _P]),
         "orc_fp8_decode_attention_f64": (None, [_P] * 9 + [C, c_int32, c_float, c_int32, c_int32]),
         "orc_layer_step_timed": (c_double, [c_int32, _P, _P, _P, _P, C, _P, _P, _P, c_int32] + [_P] * 7 + [c_int32, c_int32, c_float, c_int32]),
@@ -247,6 +248,21 @@ def decode_attention_f64(q, cache_k, cache_v, page_table, seq_lengths, cfg, laye
     lib().orc_decode_attention_f64(_p(out), _p(lse), _p(q), _p(cache_k), _p(cache_v), _p(page_table),
                                    _p(seq_lengths), ctypes.byref(c), layer, scale, batch_count, q_heads)
     return out, lse
+
+
+def fp8_k_rows(cache_k, cfg) -> np.ndarray:
+    """The fp8 K cache re-ordered to [layer, page, token, head, dim] (undoes the block / swizzle layout)."""
+    c = OrcKvConfig.of(cfg)
+    tok = np.arange(c.page_size)
+    dim = np.arange(c.head_dim)
+    head = np.arange(c.num_heads)
+    block, tk = tok >> 3, tok & 7
+    granule = (dim[None, :] >> 4) ^ ((tk[:, None] & 1) << 2)                        # [token, dim]
+    inner = granule * 16 + (dim[None, :] & 15)
+    idx = (block[:, None, None] * 8 * c.num_heads * c.head_dim + head[None, :, None] * 8 * c.head_dim
+           + tk[:, None, None] * c.head_dim + inner[:, None, :])                      # [token, head, dim]
+    pages = np.asarray(cache_k).reshape(c.num_layers, c.num_pages, -1)
+    return pages[:, :, idx]
 
 
 def fp8_append(cache_k, cache_v, scale_k, scale_v, cfg, page_table, seq_batch, first_position, row_count,

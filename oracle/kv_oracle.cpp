@@ -46,6 +46,25 @@ inline int64_t cache_offset(const OrcKvConfig &c, int32_t layer, int32_t page,
   return (token * c.num_heads + head) * c.head_dim + dim;
 }
 
+// Byte index of one K element in the FP8 cache (no counterpart in the
+// reference). V keeps the [page, offset, head, dim] order; K pages are stored
+// as half-page blocks of 8 tokens, head-major inside a block, and inside each
+// 256-byte row the 16-byte granules are XOR-swizzled with the token's parity:
+//   [layer][page][token / 8][head][token % 8][granule ^ 4*(token & 1)][16]
+// (a block is the unit the decode kernel copies into shared memory, where the
+// tensor-core fragment loads of 8 tokens then hit 32 distinct banks).
+// Needs page_size % 8 == 0 and head_dim == 256.
+inline int64_t fp8_k_index(const OrcKvConfig &c, int32_t layer, int32_t page,
+                           int32_t token, int32_t head, int32_t dim) {
+  const int64_t page_elems = int64_t(c.page_size) * c.num_heads * c.head_dim;
+  const int64_t base = (int64_t(layer) * c.num_pages + page) * page_elems;
+  const int block = token >> 3, tk = token & 7;
+  const int granule = (dim >> 4) ^ ((tk & 1) << 2);
+  return base + int64_t(block) * 8 * c.num_heads * c.head_dim +
+         int64_t(head) * 8 * c.head_dim + int64_t(tk) * c.head_dim +
+         granule * 16 + (dim & 15);
+}
+
 // rmsnorm.cu:90-101 with the lane ownership of decode.cu:216-227 and the xor
 // butterfly of cuda_utils.cuh:165-170. The reference's rsqrtf is replaced by
 // IEEE 1/sqrt: the one deliberate deviation (the GPU approximation cannot be
@@ -790,6 +809,11 @@ void orc_decode_attention_f64(float *out_f32, float *lse, const uint16_t *q,
   }
 }
 
+int64_t orc_fp8_k_index(const OrcKvConfig *cfg, int32_t layer, int32_t page,
+                        int32_t token, int32_t head, int32_t dim) {
+  return fp8_k_index(*cfg, layer, page, token, head, dim);
+}
+
 void orc_fp8_append(uint8_t *cache_k, uint8_t *cache_v, float *scale_k,
                     float *scale_v, const OrcKvConfig *cfg,
                     const int32_t *page_table, const int32_t *seq_batch,
@@ -843,20 +867,22 @@ void orc_fp8_append(uint8_t *cache_k, uint8_t *cache_v, float *scale_k,
           const float s_row =
               std::max(amax / 448.0f, std::numeric_limits<float>::min());
           const float s_new = std::max(s_old, s_row);
+          auto at = [&](int token, int d) -> uint8_t & {
+            return cache[tensor == 0
+                             ? fp8_k_index(c, layer, physical, token, h, d)
+                             : cache_offset(c, layer, physical, token, h, d)];
+          };
           if (s_new > s_old) {
             for (int r = 0; r < o0; ++r) {
-              uint8_t *dst = cache + cache_offset(c, layer, physical, r, h, 0);
               for (int d = 0; d < D; ++d) {
-                dst[d] = enc_e4m3((dec_e4m3(dst[d]) * s_old) / s_new);
+                at(r, d) = enc_e4m3((dec_e4m3(at(r, d)) * s_old) / s_new);
               }
             }
           }
           for (int r = 0; r < span; ++r) {
             const int64_t row = seq_src_row + (page_pos - first) + r;
             const uint16_t *x = src + (row * c.num_heads + h) * D;
-            uint8_t *dst =
-                cache + cache_offset(c, layer, physical, o0 + r, h, 0);
-            for (int d = 0; d < D; ++d) dst[d] = enc_e4m3(bf(x[d]) / s_new);
+            for (int d = 0; d < D; ++d) at(o0 + r, d) = enc_e4m3(bf(x[d]) / s_new);
           }
           *sp = s_new;
         }
@@ -896,8 +922,11 @@ void orc_fp8_decode_attention_f64(float *out_f32, float *lse,
         const int64_t sidx =
             (int64_t(layer) * c.num_pages + physical) * c.num_heads + kvh;
         double s = 0.0;
+        const int token = pos - logical_page * c.page_size;
         for (int d = 0; d < D; ++d) {
-          s += double(bf(q[row * D + d])) * double(dec_e4m3(cache_k[base + d]));
+          s += double(bf(q[row * D + d])) *
+               double(dec_e4m3(
+                   cache_k[fp8_k_index(c, layer, physical, token, kvh, d)]));
         }
         scores.push_back(s * double(scale_k[sidx]) * double(softmax_scale));
         vscale.push_back(double(scale_v[sidx]));

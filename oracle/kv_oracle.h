@@ -145,6 +145,10 @@ void orc_decode_attention_f64(float *out_f32, float *lse,
 // ---- FP8 e4m3 cache with one fp32 scale per (page, kv head) ---------------
 // No counterpart in the reference; this file defines the rule.
 // scale_* are [num_layers, num_pages, num_heads] fp32, zero before first use.
+// Byte index of a K element in the fp8 cache (half-page blocks, head-major,
+// swizzled rows); V uses orc_cache_offset.
+int64_t orc_fp8_k_index(const OrcKvConfig *cfg, int32_t layer, int32_t page,
+                        int32_t token, int32_t head, int32_t dim);
 void orc_fp8_append(uint8_t *cache_k, uint8_t *cache_v, float *scale_k,
                     float *scale_v, const OrcKvConfig *cfg,
                     const int32_t *page_table, const int32_t *seq_batch,

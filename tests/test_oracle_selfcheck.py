@@ -232,7 +232,9 @@ def test_fp8_append_rule(orc):
             assert np.all(sk[page * 2:(page + 1) * 2] >= prev)
         prev = sk[page * 2:(page + 1) * 2].copy()
     # dequantised rows stay close to the source: |x - dec * s| <= s * 2^-3 * |code| quantum bound ~ 1/16 rel
-    kd = orc.e4m3_to_f32(ck).reshape(3, 16, 2, 256)
+    kd = orc.e4m3_to_f32(orc.fp8_k_rows(ck, cfg)[0])          # [page, token, head, dim]
+    assert orc.lib().orc_fp8_k_index(__import__("ctypes").byref(orc.OrcKvConfig.of(cfg)), 0, 1, 9, 1, 37) == \
+        1 * 16 * 2 * 256 + 1 * 8 * 2 * 256 + 1 * 8 * 256 + 1 * 256 + ((2 ^ 4) * 16 + 5)
     for t in range(n):
         page = int(table[0, t // 16])
         for h in range(2):
