@@ -379,8 +379,10 @@ class RankWorkload:
             self.len_cur.add_(1)
         torch.cuda.synchronize()
 
-    def step(self, s: int):
-        """One decode step, inputs resident in HBM."""
+    def step(self, s: int, events: bool = False):
+        """One decode step, inputs resident in HBM. `events` brackets the timed layer's attention with
+        device timers; an event between the append and the attention keeps the attention from starting
+        under the append's tail, so the timed steps run without them."""
         if getattr(self, "graph", None) is not None:
             assert s == self.graph_next, "graph replay walks consecutive steps"
             self.graph.replay()
@@ -390,7 +392,7 @@ class RankWorkload:
 
                 dist.all_gather_into_tensor(self.out_all, self.out)
             return
-        self._launch_step(self.pos_all[s].data_ptr(), self.len_all[s].data_ptr(), s, self.stream)
+        self._launch_step(self.pos_all[s].data_ptr(), self.len_all[s].data_ptr(), s if events else None, self.stream)
         if self.spec.gather and self.world > 1:
             # KV-head sharding: every rank holds all heads' outputs after the step
             import torch.distributed as dist
@@ -684,7 +686,7 @@ def main():
         ctx = ctx_all[shard_sequences(ctx_all, args.emulate_world)[args.emulate_rank]]
     e2e_warm = 3
     use_graph = args.graph == "on" or (args.graph == "auto" and args.workload in ("cfg1", "cfg2"))
-    probe_steps = 8 if use_graph else 0     # ungraphed steps after the timed region, for the per-kernel events
+    probe_steps = 11                        # steps after the timed regions that carry the per-kernel events
     total_steps = args.warmup + args.steps + e2e_warm + args.e2e_steps + probe_steps
     wl = RankWorkload(kv, torch, ctx, total_steps, args.seed + 1000 * rank, args, spec)
     torch.cuda.synchronize()
@@ -716,8 +718,6 @@ def main():
     if sampler:
         sampler.mark("timed_end")
     elapsed_ms = t0.elapsed_time(t1)
-    if not use_graph:
-        attn_ms = [wl.ev_begin[i].elapsed_ms(wl.ev_end[i]) for i in range(first_timed, first_timed + args.steps)]
     step_bytes = sum(wl.bytes_for_step(i)[0] for i in range(first_timed, first_timed + args.steps))
     attn_bytes = statistics.mean(wl.bytes_for_step(i)[1] for i in range(first_timed, first_timed + args.steps))
     status = int(wl.status[0].item())
@@ -737,16 +737,16 @@ def main():
     barrier()
     e2e_ms = e0.elapsed_time(e1)
     e2e_bytes = sum(wl.bytes_for_step(i)[0] for i in range(first_e2e, first_e2e + args.e2e_steps))
-    if use_graph:
-        # per-kernel events cannot be read out of a replayed graph: time the attention launch of the same
-        # workload in a few ungraphed steps right after
-        wl.graph = None
-        probe0 = s
-        for _ in range(probe_steps):
-            wl.step(s)
-            s += 1
-        torch.cuda.synchronize()
-        attn_ms = [wl.ev_begin[i].elapsed_ms(wl.ev_end[i]) for i in range(probe0 + 3, probe0 + probe_steps)]
+    # per-kernel events cannot be read out of a replayed graph, and on stream launches they would stand
+    # between the append and the attention: time the attention launch of the same workload in a few
+    # plainly launched steps right after
+    wl.graph = None
+    probe0 = s
+    for _ in range(probe_steps):
+        wl.step(s, events=True)
+        s += 1
+    torch.cuda.synchronize()
+    attn_ms = [wl.ev_begin[i].elapsed_ms(wl.ev_end[i]) for i in range(probe0 + 3, probe0 + probe_steps)]
     if sampler:
         sampler.mark("load_end")
         clocks = sampler.stop()
@@ -777,7 +777,8 @@ def main():
     line = {
         "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
-        "scaling": scaling, "vs_baseline": None, "dtype": "fp8 e4m3 cache, fp32 math" if spec.fp8 else "bf16",
+        "scaling": scaling, "vs_baseline": None, "dtype": ("fp8 e4m3 cache; scores e4m3 tensor-core MMA (query hi+lo) with fp32 accumulate, P*V fp16 per 8 keys into fp32"
+                                                            if spec.fp8 else "bf16"),
         "data": "synthetic",
         "config": workload_config(args, world, "B200", parallelism, wl.L),
         "us_per_layer_step": elapsed_ms * 1e3 / layer_steps,
@@ -808,6 +809,7 @@ def main():
     if traffic_path.exists():
         try:
             t = json.loads(traffic_path.read_text())
+            t = t.get("fp8", t) if spec.fp8 else t
             line["roofline"]["traffic"] = t["dram_bytes_per_algorithmic_byte"] * attn_bytes
             line["roofline"]["traffic_source"] = t.get("source")
         except (ValueError, KeyError):

@@ -47,7 +47,11 @@ struct Fp8DecodeTraits {
   // per stage: K multipliers of the 8 heads, then V scales of the 8 heads
   static constexpr int kScaleFloatsPerStage = 2 * HKV;
   static constexpr int kScaleBytes = kStages * kScaleFloatsPerStage * 4;
-  static constexpr int kRingBytes = kStages * kStageBytes + kMetaBytes + kScaleBytes;
+  // per consumer warp: the stage's 8 x 2 softmax weights as (p, p) half2 pairs
+  static constexpr int kWeightBytesPerWarp = kStageTokens * G * 4;
+  static constexpr int kWeightBytes = kConsumerWarps * kWeightBytesPerWarp;
+  static constexpr int kRingBytes =
+      kStages * kStageBytes + kMetaBytes + kScaleBytes + kWeightBytes;
 };
 
 struct Fp8Scales {
@@ -172,16 +176,13 @@ struct Fp8WarpState {
     const int t = lane & 3;
     const uint4 *row =
         reinterpret_cast<const uint4 *>(q_rows + ((n >> 1) & 1) * Fp8DecodeTraits::D);
-    uint4 raw[8];
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      raw[2 * c] = __ldg(row + 2 * (t + 4 * c));
-      raw[2 * c + 1] = __ldg(row + 2 * (t + 4 * c) + 1);
-    }
+    // two passes over the same 8 loads (the second hits L1): holding them
+    // across the reduction costs registers the streaming loop needs
     float amax = 0.0f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+      const uint4 raw = __ldg(row + 2 * (t + 4 * (i >> 1)) + (i & 1));
+      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         amax = fmaxf(amax, fmaxf(fabsf(bf16_lo(w[k])), fabsf(bf16_hi(w[k]))));
@@ -196,7 +197,8 @@ struct Fp8WarpState {
     const bool lo_term = (n & 1) != 0;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+      const uint4 raw = __ldg(row + 2 * (t + 4 * (i >> 1)) + (i & 1));
+      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
       uint32_t packed[2];
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
@@ -213,7 +215,7 @@ struct Fp8WarpState {
           packed[k >> 1] |= code << 16;
         }
       }
-      // raw[2c + u] covers dims 16 (t + 4c) + 8u + {0..7}: MMA j = 2c + u = i
+      // load i = 2c + u covers dims 16 (t + 4c) + 8u + {0..7}: MMA j = 2c + u = i
       qb[2 * i] = n < 4 ? packed[0] : 0u;
       qb[2 * i + 1] = n < 4 ? packed[1] : 0u;
     }
@@ -284,10 +286,18 @@ __device__ __forceinline__ void consume_stage_fp8(Fp8WarpState &st,
   }
   const float pr = ex2_approx(my_s - ((t & 1) == 0 ? st.m[0] : st.m[1]));
   st.l_lane += pr;
-  // lane 4g holds (p of head 0, p of head 1) of key g as one half2
-  const float pr_other = __shfl_xor_sync(0xffffffffu, pr, 1);
-  const __half2 p_pair = __floats2half2_rn(pr, pr_other);
-  const uint32_t p_bits = *reinterpret_cast<const uint32_t *>(&p_pair);
+  // Every lane needs every key's two weights, duplicated into both halves of a
+  // half2: exchanged through 64 bytes of shared memory per warp (the previous
+  // stage's reads are behind the __syncwarp that ends a stage).
+  constexpr uint32_t kWeightOffset =
+      kStages * T::kStageBytes + T::kMetaBytes + T::kScaleBytes;
+  const uint32_t w_off = kWeightOffset + uint32_t(head) * T::kWeightBytesPerWarp;
+  if (t < 2) {
+    const __half2 pp = __float2half2_rn(pr);
+    reinterpret_cast<uint32_t *>(ring.smem + w_off)[g * 2 + t] =
+        *reinterpret_cast<const uint32_t *>(&pp);
+  }
+  __syncwarp();
 
   // ---- P*V on the codes, fp16 over the stage, then one scaled fp32 update
   const uint32_t v_base = ring.k_stage(stage) + T::kStageTensorBytes +
@@ -298,21 +308,33 @@ __device__ __forceinline__ void consume_stage_fp8(Fp8WarpState &st,
 #pragma unroll
     for (int i = 0; i < 4; ++i) part[h][i] = __float2half2_rn(0.0f);
   }
+  auto add_key = [&](int tk, uint32_t p0_bits, uint32_t p1_bits) {
+    const __half2 p0 = *reinterpret_cast<const __half2 *>(&p0_bits);
+    const __half2 p1 = *reinterpret_cast<const __half2 *>(&p1_bits);
+    const uint2 vv = lds64(v_base + uint32_t(tk) * T::kRowBytes);
+    const __half2 v[4] = {e4m3x2_to_half2(vv.x), e4m3x2_to_half2(vv.x >> 16),
+                          e4m3x2_to_half2(vv.y), e4m3x2_to_half2(vv.y >> 16)};
 #pragma unroll
-  for (int tk = 0; tk < T::kStageTokens; ++tk) {
-    if ((mask >> tk) & 1u) {  // uniform: rows outside the range may hold anything
-      const uint32_t pb = __shfl_sync(0xffffffffu, p_bits, tk << 2);
-      const __half2 pp = *reinterpret_cast<const __half2 *>(&pb);
-      const __half2 p0 = __low2half2(pp);
-      const __half2 p1 = __high2half2(pp);
-      const uint2 vv = lds64(v_base + uint32_t(tk) * T::kRowBytes);
-      const __half2 v[4] = {e4m3x2_to_half2(vv.x), e4m3x2_to_half2(vv.x >> 16),
-                            e4m3x2_to_half2(vv.y), e4m3x2_to_half2(vv.y >> 16)};
+    for (int i = 0; i < 4; ++i) {
+      part[0][i] = __hfma2(p0, v[i], part[0][i]);
+      part[1][i] = __hfma2(p1, v[i], part[1][i]);
+    }
+  };
+  if (mask == 0xffu) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        part[0][i] = __hfma2(p0, v[i], part[0][i]);
-        part[1][i] = __hfma2(p1, v[i], part[1][i]);
-      }
+    for (int pair = 0; pair < T::kStageTokens / 2; ++pair) {
+      const uint4 w = lds128(ring.base + w_off + uint32_t(pair) * 16u);
+      add_key(2 * pair, w.x, w.y);
+      add_key(2 * pair + 1, w.z, w.w);
+    }
+  } else {
+    // rows outside the range may hold anything (a NaN code times a zero weight
+    // is still a NaN): they are skipped, not weighted by zero
+#pragma unroll
+    for (int pair = 0; pair < T::kStageTokens / 2; ++pair) {
+      const uint4 w = lds128(ring.base + w_off + uint32_t(pair) * 16u);
+      if ((mask >> (2 * pair)) & 1u) add_key(2 * pair, w.x, w.y);
+      if ((mask >> (2 * pair + 1)) & 1u) add_key(2 * pair + 1, w.z, w.w);
     }
   }
 #pragma unroll

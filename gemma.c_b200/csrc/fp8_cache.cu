@@ -68,6 +68,21 @@ __device__ __forceinline__ int64_t fp8_byte_index(const Gemma4KvCacheConfig &c,
   }
 }
 
+// First byte of the 256-byte row `r` of `head` (granule permutation aside).
+template <bool kIsK>
+__device__ __forceinline__ int64_t fp8_row_base(const Gemma4KvCacheConfig &c,
+                                                int layer, int physical, int r,
+                                                int head) {
+  if constexpr (!kIsK) {
+    return cache_offset(c, layer, physical, r, head, 0);
+  } else {
+    const int64_t page_bytes = int64_t(c.page_size) * c.num_heads * c.head_dim;
+    return (int64_t(layer) * c.num_pages + physical) * page_bytes +
+           (int64_t(r >> 3) * c.num_heads + head) * 8 * c.head_dim +
+           (r & 7) * c.head_dim;
+  }
+}
+
 // One warp stores `nrows` prepared rows of one (page, head, tensor) starting
 // at page offset o0; value(r, j) is element lane + 32*j of row r as fp32.
 // Applies the rule above, including the requantisation of the rows already in
@@ -91,13 +106,35 @@ __device__ __forceinline__ void fp8_store_rows(uint8_t *cache, float *scale_slot
   }
   const float s_new = fmaxf(s_old, fmaxf(__fdiv_rn(amax, 448.0f), FLT_MIN));
   if (s_new > s_old) {
-    for (int r = 0; r < o0; ++r) {
+    // A stored row is 256 contiguous bytes in either layout (K only permutes
+    // the granules inside it) and the re-encoding is elementwise, so a lane
+    // takes 8 bytes of each row; 8 rows are in flight at a time.
+    static_assert(D == 256, "a lane re-encodes 8 of a row's 256 bytes");
+    constexpr int kBatch = 8;
+    for (int r0 = 0; r0 < o0; r0 += kBatch) {
+      uint2 w[kBatch];
 #pragma unroll
-      for (int j = 0; j < D / 32; ++j) {
-        uint8_t *at = cache + fp8_byte_index<kIsK>(c, layer, physical, r, head,
-                                                   lane + 32 * j);
-        const float v = __fmul_rn(dec_e4m3(*at), s_old);
-        *at = enc_e4m3(__fdiv_rn(v, s_new));
+      for (int i = 0; i < kBatch; ++i) {
+        if (r0 + i < o0) {
+          w[i] = *reinterpret_cast<const uint2 *>(
+              cache + fp8_row_base<kIsK>(c, layer, physical, r0 + i, head) +
+              lane * 8);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < kBatch; ++i) {
+        if (r0 + i < o0) {
+          uint32_t in[2] = {w[i].x, w[i].y}, out[2] = {0u, 0u};
+#pragma unroll
+          for (int b = 0; b < 8; ++b) {
+            const float v =
+                __fmul_rn(dec_e4m3(uint8_t(in[b >> 2] >> (8 * (b & 3)))), s_old);
+            out[b >> 2] |= uint32_t(enc_e4m3(__fdiv_rn(v, s_new))) << (8 * (b & 3));
+          }
+          *reinterpret_cast<uint2 *>(
+              cache + fp8_row_base<kIsK>(c, layer, physical, r0 + i, head) +
+              lane * 8) = make_uint2(out[0], out[1]);
+        }
       }
     }
   }
@@ -262,7 +299,9 @@ cudaError_t decode_append_fp8(const AppendArgs &a, uint8_t *cache_k,
       c.window_size < 0 || c.num_heads <= 0 || a.q_heads <= 0 ||
       a.q_heads % c.num_heads != 0 ||
       (a.norm_mode != B200KV_NORM_IEEE &&
-       a.norm_mode != B200KV_NORM_RSQRT_APPROX)) {
+       a.norm_mode != B200KV_NORM_RSQRT_APPROX) ||
+      ((reinterpret_cast<uintptr_t>(cache_k) |
+        reinterpret_cast<uintptr_t>(cache_v)) & 15u) != 0) {
     return cudaErrorInvalidValue;
   }
   const int G = a.q_heads / c.num_heads;
@@ -298,7 +337,9 @@ cudaError_t fp8_append_rows(uint8_t *cache_k, uint8_t *cache_v, float *scale_k,
       layer >= c.num_layers || c.num_pages <= 0 || c.page_size <= 0 ||
       c.max_pages_per_seq <= 0 || c.batch_size <= 0 || c.window_size < 0 ||
       c.num_heads <= 0 || c.num_heads > 65535 || c.head_dim != 256 ||
-      c.page_size % 8 != 0) {
+      c.page_size % 8 != 0 ||
+      ((reinterpret_cast<uintptr_t>(cache_k) |
+        reinterpret_cast<uintptr_t>(cache_v)) & 15u) != 0) {
     return cudaErrorInvalidValue;
   }
   Fp8RowsArgs a = {cache_k, cache_v, scale_k, scale_v, c, page_table, seq_batch,
