@@ -321,7 +321,12 @@ class RankWorkload:
         for i in range(L):
             g = self.layer_is_global(i)
             split, nsplit = (self.g_split, self.g_nsplit) if g else (self.l_split, self.l_nsplit)
-            self.launches_per_step += 2 if (nsplit == 1 and split > 0) else 3   # append, split[, combine]
+            fused = (split == 0 and not spec.fp8 and spec.hkv == 8 and B <= 1024
+                     and os.environ.get("B200KV_FUSED_LAYER_STEP", "1") != "0")
+            if fused:
+                self.launches_per_step += 2          # balanced kernel with the append inside, combine
+            else:
+                self.launches_per_step += 2 if (nsplit == 1 and split > 0) else 3   # append, split[, combine]
 
     def layer_is_global(self, i: int) -> bool:
         nl, ng = self.spec.n_local, self.spec.n_global
@@ -362,8 +367,9 @@ class RankWorkload:
         from two fixed buffers that the graph itself advances by one at its end, so replaying it walks
         through consecutive decode steps. The per-layer timing hooks are not captured."""
         torch = self.torch
-        self.pos_cur = self.pos_all[first_step].clone()
-        self.len_cur = self.len_all[first_step].clone()
+        # positions and lengths of the replayed step live in one buffer so that one small kernel advances both
+        self.step_state = torch.stack([self.pos_all[first_step], self.len_all[first_step]]).contiguous()
+        self.pos_cur, self.len_cur = self.step_state[0], self.step_state[1]
         self.graph_next = first_step
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
@@ -375,8 +381,7 @@ class RankWorkload:
         with torch.cuda.graph(self.graph):
             self._launch_step(self.pos_cur.data_ptr(), self.len_cur.data_ptr(), None,
                               torch.cuda.current_stream().cuda_stream)
-            self.pos_cur.add_(1)
-            self.len_cur.add_(1)
+            self.step_state.add_(1)
         torch.cuda.synchronize()
 
     def step(self, s: int, events: bool = False):

@@ -175,9 +175,8 @@ cudaError_t dispatch_geometry(int head_dim, int rotary_dim, int norm_mode,
 
 }  // namespace
 
-cudaError_t decode_append_bf16(const AppendArgs &a, cudaStream_t stream) {
+cudaError_t validate_append_args(const AppendArgs &a) {
   const Gemma4KvCacheConfig &c = a.cfg;
-  if (a.batch_count == 0) return cudaSuccess;
   if (a.q_prepared == nullptr || a.cache_k == nullptr ||
       a.cache_v == nullptr || a.page_table == nullptr ||
       a.token_position == nullptr || a.q == nullptr || a.k == nullptr ||
@@ -194,6 +193,16 @@ cudaError_t decode_append_bf16(const AppendArgs &a, cudaStream_t stream) {
   const int G = a.q_heads / c.num_heads;
   const int warps = G + (a.v != nullptr ? 2 : 1);
   if (warps > 32 || c.num_heads > 65535) return cudaErrorInvalidValue;
+  return cudaSuccess;
+}
+
+cudaError_t decode_append_bf16(const AppendArgs &a, cudaStream_t stream) {
+  const Gemma4KvCacheConfig &c = a.cfg;
+  if (a.batch_count == 0) return cudaSuccess;
+  const cudaError_t valid = validate_append_args(a);
+  if (valid != cudaSuccess) return valid;
+  const int G = a.q_heads / c.num_heads;
+  const int warps = G + (a.v != nullptr ? 2 : 1);
   const dim3 grid(a.batch_count, c.num_heads);
   return dispatch_geometry(
       c.head_dim, a.rotary_dim, a.norm_mode, [&](auto d, auto rot, auto ieee) {

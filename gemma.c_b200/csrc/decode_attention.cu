@@ -213,14 +213,16 @@ __global__ __launch_bounds__(T::kThreads, T::kCtasPerSm) void decode_split_kerne
   }
 }
 
-// One CTA per (batch, q_head) row: combine of that row's live splits.
-template <int D>
+// One CTA per (batch, q_head) row and dim slice: combine of that row's live
+// splits.
+template <int D, int kSlices>
 __global__ __launch_bounds__(kCombineThreads) void decode_combine_kernel(
     DecodeParams p) {
   __shared__ float s_w[kCombineChunk];
   __shared__ float s_red[kCombineThreads / 32];
-  __shared__ float4 s_val[kCombineGroups][D / 4];
+  __shared__ float4 s_val[kCombineThreads];
   const int row = int(blockIdx.x);
+  const int slice = int(blockIdx.y);
   const int batch = row / p.q_heads;
 
   pdl_wait_for_predecessor();
@@ -234,11 +236,12 @@ __global__ __launch_bounds__(kCombineThreads) void decode_combine_kernel(
   __nv_bfloat16 *out_row = p.out + int64_t(row) * D;
   float *lse_row = p.lse != nullptr ? p.lse + row : nullptr;
   if (n == 0) {
-    combine_empty_row<D>(out_row, lse_row);
+    combine_empty_row<D, kSlices>(out_row, lse_row, slice);
     return;
   }
-  combine_row<D>(out_row, lse_row, p.partial_m, p.partial_l, p.partial_acc,
-                 int64_t(row) * p.num_splits, 1, n, s_w, s_red, s_val);
+  combine_row<D, kSlices>(out_row, lse_row, p.partial_m, p.partial_l,
+                          p.partial_acc, int64_t(row) * p.num_splits, 1, n, slice,
+                          s_w, s_red, s_val);
 }
 
 template <class T>
@@ -271,7 +274,7 @@ int forced_consumer_warps() {
 }
 }  // namespace
 
-cudaError_t decode_attention_bf16(const DecodeArgs &a, cudaStream_t stream) {
+cudaError_t validate_decode_args(const DecodeArgs &a) {
   const Gemma4KvCacheConfig &c = a.cfg;
   // Validation mirrors gemma4_fa_valid_cache_config and the launcher checks
   // (src/gemma4_flash_attention_decode.cu:377-392,1129-1134).
@@ -301,6 +304,14 @@ cudaError_t decode_attention_bf16(const DecodeArgs &a, cudaStream_t stream) {
                           reinterpret_cast<uintptr_t>(a.out) |
                           reinterpret_cast<uintptr_t>(a.partial_acc);
   if ((align & 15u) != 0) return cudaErrorInvalidValue;
+  return cudaSuccess;
+}
+
+cudaError_t decode_attention_bf16(const DecodeArgs &a, cudaStream_t stream) {
+  const Gemma4KvCacheConfig &c = a.cfg;
+  const cudaError_t valid = validate_decode_args(a);
+  if (valid != cudaSuccess) return valid;
+  const bool balanced = a.split_size == 0;
   if (balanced) return decode_attention_balanced_bf16(a, stream);
 
   DecodeParams p;
@@ -342,9 +353,14 @@ cudaError_t decode_attention_bf16(const DecodeArgs &a, cudaStream_t stream) {
   }
   if (st != cudaSuccess) return st;
   if (a.num_splits > 1) {
-    st = launch_pdl(decode_combine_kernel<256>,
-                    dim3(a.batch_count * a.q_heads), dim3(kCombineThreads), 0,
-                    stream, p);
+    const unsigned rows = unsigned(a.batch_count * a.q_heads);
+    if (combine_slices(rows) == 4) {
+      st = launch_pdl(decode_combine_kernel<256, 4>, dim3(rows, 4),
+                      dim3(kCombineThreads), 0, stream, p);
+    } else {
+      st = launch_pdl(decode_combine_kernel<256, 1>, dim3(rows),
+                      dim3(kCombineThreads), 0, stream, p);
+    }
   }
   return st;
 }

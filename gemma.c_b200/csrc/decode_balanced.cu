@@ -17,11 +17,13 @@
 // results within fp32 summation order. Partials live in the caller's scratch:
 // the partial of CTA c for sequence b sits in slot c + b, which is unique
 // because ranges and sequences advance together.
+#include <cstring>
 #include <type_traits>
 
 #include "decode_common.cuh"
 #include "decode_fp8.cuh"
 #include "kernels.cuh"
+#include "prep_common.cuh"
 
 namespace b200kv {
 
@@ -50,7 +52,21 @@ struct BalancedParams {
   float *partial_acc;
   int32_t num_ctas;  // CTAs of the split kernel (the combine recomputes ranges)
   int32_t *status;
+  // Fused kernels only: this step's projections and what the append needs to
+  // prepare them; the kernel writes the new cache rows and the prepared q.
+  const __nv_bfloat16 *raw_q;
+  const __nv_bfloat16 *raw_k;
+  const __nv_bfloat16 *raw_v;  // nullptr: V is derived from raw K
+  const __nv_bfloat16 *q_norm_weight;
+  const __nv_bfloat16 *k_norm_weight;
+  const float *cos;
+  const float *sin;
+  const int32_t *token_position;
+  __nv_bfloat16 *q_prepared;
 };
+
+enum : int { kAttentionOnly = 0, kFusedApprox = 1, kFusedIeee = 2 };
+constexpr int kAppendBufferBytesPerWarp = 1024;
 
 __device__ __forceinline__ int range_width(int total, int num_ctas, int tile) {
   const int even = div_up(div_up(total, num_ctas), tile) * tile;
@@ -123,37 +139,194 @@ __device__ __forceinline__ bool next_segment(int &b, int &flat, int r1,
   return true;
 }
 
-template <class T>
+// ---- in-kernel append (fused kernels) ---------------------------------------
+// One consumer warp = one KV head. The arithmetic and the lane ownership are
+// the append kernel's (prep_common.cuh), so the rows are the same bits; the
+// per-warp 1 KiB buffer turns "lane l holds elements l + 32 i" into rows in
+// memory order.
+
+// Prepared query rows of heads 2 * head, 2 * head + 1 of sequence b, returned
+// as the 16 bytes per lane the attention wants (dims 8 * lane .. + 7). When
+// `with_kv`, also leaves the prepared K row at wbuf[0, 512) and the V row at
+// wbuf[512, 1024).
+template <bool kIeee>
+__device__ __forceinline__ void prepare_rows(uint4 (&qpack)[2],
+                                             const BalancedParams &p, int b,
+                                             int head, int pos, bool with_kv,
+                                             uint8_t *wbuf, int lane) {
+  constexpr int D = 256;
+  const float *cos_row = p.cos + int64_t(pos) * (D / 2);
+  const float *sin_row = p.sin + int64_t(pos) * (D / 2);
+  const int64_t kv_src = (int64_t(b) * p.cfg.num_heads + head) * D;
+  float xq[2][D / 32], xk[D / 32], xv[D / 32];
+#pragma unroll
+  for (int g = 0; g < 2; ++g) {
+    load_head<D>(p.raw_q + (int64_t(b) * p.q_heads + head * 2 + g) * D, lane,
+                 xq[g]);
+  }
+  const bool has_v = p.raw_v != nullptr;
+  if (with_kv) {
+    load_head<D>(p.raw_k + kv_src, lane, xk);
+    if (has_v) load_head<D>(p.raw_v + kv_src, lane, xv);
+  }
+  __nv_bfloat16 *rows = reinterpret_cast<__nv_bfloat16 *>(wbuf);
+  __nv_bfloat16 y[D / 32];
+#pragma unroll
+  for (int g = 0; g < 2; ++g) {
+    prep_weighted_rope_values<D, D, kIeee>(y, xq[g], p.q_norm_weight, cos_row,
+                                           sin_row, lane);
+    store_head<D>(rows + g * D, y, lane);
+  }
+  __syncwarp();
+#pragma unroll
+  for (int g = 0; g < 2; ++g) {
+    qpack[g] = reinterpret_cast<const uint4 *>(wbuf)[g * 32 + lane];
+  }
+  __syncwarp();
+  if (with_kv) {
+    prep_weighted_rope_values<D, D, kIeee>(y, xk, p.k_norm_weight, cos_row,
+                                           sin_row, lane);
+    store_head<D>(rows, y, lane);
+    if (has_v) {
+      prep_scale_free_values<D, kIeee>(y, xv);
+    } else {
+      prep_scale_free_values<D, kIeee>(y, xk);
+    }
+    store_head<D>(rows + D, y, lane);
+    __syncwarp();
+  }
+}
+
+// Physical page of position pos of sequence b, or -1 (unmapped: nothing is
+// appended, src/gemma4_flash_attention_decode.cu:333-338).
+__device__ __forceinline__ int append_page(const BalancedParams &p, int b,
+                                           int pos) {
+  const Gemma4KvCacheConfig &c = p.cfg;
+  const int slot = (pos / c.page_size) % c.max_pages_per_seq;
+  const int e = __ldg(p.page_table + int64_t(b) * c.max_pages_per_seq + slot);
+  return (e >= 0 && e < c.num_pages) ? e : -1;
+}
+
+// What the append leaves in global memory for one (sequence, KV head): the two
+// prepared query rows and, if the page is mapped, the new K and V rows (from
+// wbuf). Call only after pdl_wait_for_predecessor().
+__device__ __forceinline__ void store_appended_rows(const BalancedParams &p,
+                                                    const uint4 (&qpack)[2],
+                                                    int b, int head, int pos,
+                                                    int physical,
+                                                    const uint8_t *wbuf,
+                                                    int lane) {
+  constexpr int D = 256;
+#pragma unroll
+  for (int g = 0; g < 2; ++g) {
+    reinterpret_cast<uint4 *>(p.q_prepared +
+                              (int64_t(b) * p.q_heads + head * 2 + g) * D)[lane] =
+        qpack[g];
+  }
+  if (physical >= 0) {
+    const Gemma4KvCacheConfig &c = p.cfg;
+    const int64_t off = cache_offset(
+        c, p.layer, physical, pos - (pos / c.page_size) * c.page_size, head, 0);
+    const uint4 *rows = reinterpret_cast<const uint4 *>(wbuf);
+    // the fused kernels are handed the caches they may write
+    uint4 *dst_k = reinterpret_cast<uint4 *>(
+        static_cast<__nv_bfloat16 *>(const_cast<void *>(p.cache_k)) + off);
+    uint4 *dst_v = reinterpret_cast<uint4 *>(
+        static_cast<__nv_bfloat16 *>(const_cast<void *>(p.cache_v)) + off);
+    dst_k[lane] = rows[lane];
+    dst_v[lane] = rows[32 + lane];
+  }
+}
+
+// Appends of sequences whose new position is not a live key of the attention
+// (lengths and positions that do not belong together): no CTA meets the row
+// while streaming, so CTA (b mod grid) does it here. All lanes of a consumer
+// warp call it, after the warp's last use of wbuf.
+template <bool kIeee>
+__device__ __forceinline__ void append_unstreamed_rows(const BalancedParams &p,
+                                                       const int *s_prefix,
+                                                       const int *s_first,
+                                                       int head, uint8_t *wbuf,
+                                                       int lane) {
+  for (int b = int(blockIdx.x); b < p.batch_count; b += int(gridDim.x)) {
+    const int pos = __ldg(p.token_position + b);
+    if (pos < 0) continue;
+    const int first = s_first[b];
+    const int count = s_prefix[b + 1] - s_prefix[b];
+    if (pos >= first && pos < first + count) continue;  // its streamer does it
+    uint4 qpack[2];
+    prepare_rows<kIeee>(qpack, p, b, head, pos, true, wbuf, lane);
+    pdl_wait_for_predecessor();
+    store_appended_rows(p, qpack, b, head, pos, append_page(p, b, pos), wbuf,
+                        lane);
+    __syncwarp();
+  }
+}
+
+// kMode: kAttentionOnly reads the prepared q and expects the step's rows in
+// the cache (a preceding append launch); the fused modes take the step's raw
+// projections, prepare q in the consumer warps, and the CTA whose range holds a
+// sequence's new key prepares that row, uses it from shared memory and writes
+// it to the cache: one launch per layer-step instead of two, and nothing the
+// attention streams early depends on a preceding kernel.
+template <class T, int kMode>
 __global__ __launch_bounds__(T::kThreads, T::kCtasPerSm) void decode_balanced_kernel(
     BalancedParams p) {
   constexpr int G = T::G;
   constexpr int ST = T::kStageTokens;
+  constexpr bool kFused = kMode != kAttentionOnly;
+  constexpr bool kIeee = kMode == kFusedIeee;
   static_assert(T::kWarpsPerHead == 1, "one warp per KV head: no merge step");
+  static_assert(!kFused || !T::kFp8, "the fused append is bf16 only");
   extern __shared__ __align__(128) uint8_t smem[];
-  int *s_prefix = reinterpret_cast<int *>(smem + T::kRingBytes);
+  constexpr int kAppendBytes =
+      kFused ? T::kConsumerWarps * kAppendBufferBytesPerWarp : 0;
+  int *s_prefix = reinterpret_cast<int *>(smem + T::kRingBytes + kAppendBytes);
   int *s_first = s_prefix + kMaxBalancedBatch + 1;
   __shared__ int s_warp_sums[32];
 
   const int warp = int(threadIdx.x) >> 5;
   const int lane = int(threadIdx.x) & 31;
   const Gemma4KvCacheConfig &cfg = p.cfg;
+  [[maybe_unused]] uint8_t *wbuf =
+      smem + T::kRingBytes + (warp & 7) * kAppendBufferBytesPerWarp;
 
-  // Launched programmatically after the append of this layer-step: lengths,
-  // page table and every cache row except the ones that append is writing were
-  // complete before that append started, so the partition and the first
-  // stages of old keys do not wait for it. What the append produces -- the
-  // prepared q and the rows of the page that holds each sequence's newest key
-  // (the fp8 append may re-encode that whole page) -- is touched only after
-  // pdl_wait_for_predecessor(). Every CTA waits before it exits, so "this grid
-  // is complete" still implies "everything before it is complete".
-  pdl_release_successor();
+  // Programmatic dependent launch. What this kernel reads before its
+  // pdl_wait_for_predecessor() must have been complete before the preceding
+  // kernel started:
+  //  * attention only: the preceding kernel is this layer-step's append;
+  //    lengths, page table and every cache row except those of the page that
+  //    holds each sequence's newest key (the fp8 append may re-encode that
+  //    whole page) qualify; the prepared q does not.
+  //  * fused: the preceding kernel is the previous layer-step's combine, which
+  //    started only after every CTA of that step's fused kernel had passed its
+  //    own wait (the release below comes after the wait), so two kernels back
+  //    everything is complete; one kernel back a cache row may still be in
+  //    flight -- the previous step's newest key -- and the scratch may still be
+  //    read. Pages from that key's page on are loaded after the wait; scratch,
+  //    outputs and cache rows are written after the wait.
+  // Every CTA waits before it exits, so "this grid is complete" still implies
+  // "everything before it is complete".
+  if constexpr (!kFused) pdl_release_successor();
 
   scan_live_keys(p, s_prefix, s_first, s_warp_sums);
   const int total = s_prefix[p.batch_count];
   const int width = range_width(max(total, 1), p.num_ctas, ST);
   const int r0 = int(blockIdx.x) * width;
-  if (total == 0 || r0 >= total) {  // nothing to do; the combine zeroes empty rows
+  if (total == 0 || r0 >= total) {  // nothing to stream; the combine zeroes empty rows
+    if constexpr (kFused) {
+      if (warp < T::kConsumerWarps) {
+        append_unstreamed_rows<kIeee>(p, s_prefix, s_first, warp, wbuf, lane);
+      }
+      // An idle CTA has touched nothing a predecessor owns (or has waited in
+      // the append above) and leaves at once: small batches keep most of the
+      // grid idle, and the next layer-step's CTAs need the room to start under
+      // this one. CTA 0 keeps the "complete implies predecessors complete"
+      // chain when no CTA has keys (a CTA with keys always waits).
+      if (blockIdx.x != 0) return;
+    }
     pdl_wait_for_predecessor();
+    if constexpr (kFused) pdl_release_successor();
     return;
   }
   const int r1 = min(total, r0 + width);
@@ -185,9 +358,10 @@ __global__ __launch_bounds__(T::kThreads, T::kCtasPerSm) void decode_balanced_ke
     while (ok && next_segment(b, flat, r1, s_prefix, s_first, seg)) {
       const int a0 = (seg.pos0 / ST) * ST;
       const int nchunks = div_up(seg.pos1 - a0, ST);
-      // first position of the page that holds this sequence's newest key
+      // first position of the first page the preceding kernels may have touched
       const int seq_len = s_first[seg.b] + s_prefix[seg.b + 1] - s_prefix[seg.b];
-      const int fresh = ((seq_len - 1) / cfg.page_size) * cfg.page_size;
+      const int newest = max(seq_len - (kFused ? 2 : 1), 0);
+      const int fresh = (newest / cfg.page_size) * cfg.page_size;
       for (int c = 0; c < nchunks; ++c, ++it) {
         if (!waited && min(seg.pos1, a0 + (c + 1) * ST) > fresh) {
           pdl_wait_for_predecessor();
@@ -217,32 +391,47 @@ __global__ __launch_bounds__(T::kThreads, T::kCtasPerSm) void decode_balanced_ke
       if (!mbar_wait_bounded(ring.full_bar(s), uint32_t(fill) & 1u)) ok = false;
     }
     if (!waited) pdl_wait_for_predecessor();
+    if constexpr (kFused) pdl_release_successor();
     if (!ok && lane == 0) set_status(p.status, B200KV_STATUS_WAIT_TIMEOUT);
     return;
   }
 
   // -------------------------------- consumers --------------------------------
-  pdl_wait_for_predecessor();  // the prepared q comes from the append
+  if constexpr (!kFused) pdl_wait_for_predecessor();  // q comes from the append
   const int head = warp;  // kWarpsPerHead == 1
   std::conditional_t<T::kFp8, Fp8WarpState, WarpState<T>> st;
   int b = b_start, flat = r0;
   Segment seg, next;
   bool have = next_segment(b, flat, r1, s_prefix, s_first, seg);
   [[maybe_unused]] uint4 raw[G];
-  if constexpr (!T::kFp8) {
+  if constexpr (!T::kFp8 && !kFused) {
     load_q_raw<T>(raw, p.q, int64_t(seg.b) * p.q_heads + head * G, lane);
   }
   int it = 0;
   while (have) {
+    // fused: position of the sequence's new row, and whether this piece of the
+    // sequence contains it (then this warp prepares, uses and stores the row)
+    [[maybe_unused]] int new_pos = -1;
+    [[maybe_unused]] bool owns_new = false;
     if constexpr (T::kFp8) {
       st.load_q(p.q + (int64_t(seg.b) * p.q_heads + head * G) * T::D, lane);
+    } else if constexpr (kFused) {
+      new_pos = __ldg(p.token_position + seg.b);
+      owns_new = new_pos >= seg.pos0 && new_pos < seg.pos1;
+      if (new_pos >= 0) {
+        prepare_rows<kIeee>(raw, p, seg.b, head, new_pos, owns_new, wbuf, lane);
+      } else {  // no append for this sequence: q is what the caller left there
+        load_q_raw<T>(raw, p.q_prepared, int64_t(seg.b) * p.q_heads + head * G,
+                      lane);
+      }
+      st.set_q(raw, p.scale_log2);
     } else {
       st.set_q(raw, p.scale_log2);
     }
     st.reset();
     // Fetch the next sequence's query rows while this one streams.
     const bool have_next = next_segment(b, flat, r1, s_prefix, s_first, next);
-    if constexpr (!T::kFp8) {
+    if constexpr (!T::kFp8 && !kFused) {
       if (have_next) {
         load_q_raw<T>(raw, p.q, int64_t(next.b) * p.q_heads + head * G, lane);
       }
@@ -259,6 +448,24 @@ __global__ __launch_bounds__(T::kThreads, T::kCtasPerSm) void decode_balanced_ke
       if constexpr (T::kFp8) {
         consume_stage_fp8(st, ring, stage, head, lane);
       } else {
+        if constexpr (kFused) {
+          // The stage that holds the new key: the copy brought whatever the
+          // cache had there; this head's slice of the row is replaced by the
+          // prepared one (only this warp reads the slice). The slot's mask bit
+          // is set exactly when its page is mapped.
+          const int slot = new_pos - (a0 + c * ST);
+          if (owns_new && slot >= 0 && slot < ST &&
+              ((ring.masks()[stage] >> slot) & 1ull) != 0ull) {
+            uint8_t *k_row = smem + stage * T::kStageBytes +
+                             slot * T::kRowBytes + head * T::D * 2;
+            const uint4 *rows = reinterpret_cast<const uint4 *>(wbuf);
+            reinterpret_cast<uint4 *>(k_row)[lane] = rows[lane];
+            reinterpret_cast<uint4 *>(k_row + T::kStageTensorBytes)[lane] =
+                rows[32 + lane];
+            fence_proxy_async_shared();  // the next fill of the stage is a bulk copy
+            __syncwarp();
+          }
+        }
         consume_stage<T>(st, ring, stage, head, 0, lane);
       }
       __syncwarp();
@@ -266,6 +473,15 @@ __global__ __launch_bounds__(T::kThreads, T::kCtasPerSm) void decode_balanced_ke
     }
     float l[G];
     st.denominators(l, lane);
+    if constexpr (kFused) {
+      pdl_wait_for_predecessor();
+      pdl_release_successor();
+      if (owns_new) {
+        store_appended_rows(p, raw, seg.b, head, new_pos,
+                            append_page(p, seg.b, new_pos), wbuf, lane);
+        __syncwarp();
+      }
+    }
 #pragma unroll
     for (int g = 0; g < G; ++g) {
       const int q_head = head * G + g;
@@ -281,19 +497,23 @@ __global__ __launch_bounds__(T::kThreads, T::kCtasPerSm) void decode_balanced_ke
     seg = next;
     have = have_next;
   }
+  if constexpr (kFused) {
+    append_unstreamed_rows<kIeee>(p, s_prefix, s_first, head, wbuf, lane);
+  }
 }
 
 // One CTA per (sequence, q_head) row. Recomputes which CTAs touched the
 // sequence from the same prefix sums and combines their partials; rows that
 // one CTA finished alone are left as they are; empty rows are zeroed.
-template <int D>
+template <int D, int kSlices>
 __global__ __launch_bounds__(kCombineThreads) void balanced_combine_kernel(
     BalancedParams p, int tile) {
   __shared__ float s_w[kCombineChunk];
   __shared__ float s_red[kCombineThreads / 32];
-  __shared__ float4 s_val[kCombineGroups][D / 4];
+  __shared__ float4 s_val[kCombineThreads];
   __shared__ int s_sum[3][kCombineThreads / 32];
   const int row = int(blockIdx.x);
+  const int slice = int(blockIdx.y);
   const int b = row / p.q_heads;
   const int q_head = row - b * p.q_heads;
   const int tid = int(threadIdx.x);
@@ -337,16 +557,17 @@ __global__ __launch_bounds__(kCombineThreads) void balanced_combine_kernel(
   __nv_bfloat16 *out_row = p.out + int64_t(row) * D;
   float *lse_row = p.lse != nullptr ? p.lse + row : nullptr;
   if (mine == 0) {
-    combine_empty_row<D>(out_row, lse_row);
+    combine_empty_row<D, kSlices>(out_row, lse_row, slice);
     return;
   }
   const int width = range_width(all, p.num_ctas, tile);
   const int c_first = before / width;
   const int c_last = (before + mine - 1) / width;
   if (c_first == c_last) return;  // finished by that CTA
-  combine_row<D>(out_row, lse_row, p.partial_m, p.partial_l, p.partial_acc,
-                 int64_t(c_first + b) * p.q_heads + q_head, p.q_heads,
-                 c_last - c_first + 1, s_w, s_red, s_val);
+  combine_row<D, kSlices>(out_row, lse_row, p.partial_m, p.partial_l,
+                          p.partial_acc, int64_t(c_first + b) * p.q_heads + q_head,
+                          p.q_heads, c_last - c_first + 1, slice, s_w, s_red,
+                          s_val);
 }
 
 }  // namespace
@@ -359,11 +580,15 @@ bool decode_balanced_supported(const Gemma4KvCacheConfig &c, int q_heads,
 
 namespace {
 
-template <class T>
+template <class T, int kMode = kAttentionOnly>
 cudaError_t launch_balanced(BalancedParams p, int64_t scratch_slots,
                             cudaStream_t stream) {
-  constexpr int kSmem = T::kRingBytes + (2 * kMaxBalancedBatch + 1) * 4;
-  static_assert(2 * kSmem <= 226 * 1024, "two CTAs per SM");
+  constexpr int kSmem =
+      T::kRingBytes + (2 * kMaxBalancedBatch + 1) * 4 +
+      (kMode != kAttentionOnly ? T::kConsumerWarps * kAppendBufferBytesPerWarp : 0);
+  static_assert(T::kRingBytes % 16 == 0, "the append buffers hold 16-byte rows");
+  // per SM: two CTAs, each with 1 KiB the system reserves and the static arrays
+  static_assert(2 * (kSmem + 1024 + 256) <= 228 * 1024, "two CTAs per SM");
   int device = 0, sm_count = 0;
   cudaError_t st = cudaGetDevice(&device);
   if (st != cudaSuccess) return st;
@@ -377,15 +602,19 @@ cudaError_t launch_balanced(BalancedParams p, int64_t scratch_slots,
     return cudaErrorInvalidValue;
   }
   p.num_ctas = int32_t(num_ctas);
-  st = cudaFuncSetAttribute(decode_balanced_kernel<T>,
+  st = cudaFuncSetAttribute(decode_balanced_kernel<T, kMode>,
                             cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
   if (st != cudaSuccess) return st;
-  st = launch_pdl(decode_balanced_kernel<T>, dim3(unsigned(num_ctas)),
+  st = launch_pdl(decode_balanced_kernel<T, kMode>, dim3(unsigned(num_ctas)),
                   dim3(T::kThreads), kSmem, stream, p);
   if (st != cudaSuccess) return st;
-  return launch_pdl(balanced_combine_kernel<256>,
-                    dim3(p.batch_count * p.q_heads), dim3(kCombineThreads), 0,
-                    stream, p, int(T::kStageTokens));
+  const unsigned rows = unsigned(p.batch_count * p.q_heads);
+  if (combine_slices(rows) == 4) {
+    return launch_pdl(balanced_combine_kernel<256, 4>, dim3(rows, 4),
+                      dim3(kCombineThreads), 0, stream, p, int(T::kStageTokens));
+  }
+  return launch_pdl(balanced_combine_kernel<256, 1>, dim3(rows),
+                    dim3(kCombineThreads), 0, stream, p, int(T::kStageTokens));
 }
 
 BalancedParams balanced_params(const DecodeArgs &a) {
@@ -451,6 +680,46 @@ cudaError_t decode_attention_fp8(const DecodeArgs &a, const void *cache_k,
   p.scale_v = scale_v;
   return launch_balanced<Fp8DecodeTraits>(
       p, int64_t(a.batch_count) * a.num_splits, stream);
+}
+
+bool decode_fused_supported(const AppendArgs &ap, const DecodeArgs &a) {
+  const Gemma4KvCacheConfig &c = a.cfg;
+  return a.split_size == 0 &&
+         decode_balanced_supported(c, a.q_heads, a.batch_count) &&
+         ap.rotary_dim == 256 && ap.q_heads == a.q_heads &&
+         ap.batch_count == a.batch_count && ap.cache_layer == a.layer &&
+         ap.page_table == a.page_table && ap.q_prepared == a.q &&
+         ap.cache_k == a.cache_k && ap.cache_v == a.cache_v &&
+         memcmp(&ap.cfg, &c, sizeof(c)) == 0;
+}
+
+cudaError_t decode_layer_step_fused_bf16(const AppendArgs &ap,
+                                         const DecodeArgs &a,
+                                         cudaStream_t stream) {
+  cudaError_t st = validate_append_args(ap);
+  if (st != cudaSuccess) return st;
+  st = validate_decode_args(a);
+  if (st != cudaSuccess) return st;
+  if (!decode_fused_supported(ap, a)) return cudaErrorInvalidValue;
+  if ((reinterpret_cast<uintptr_t>(ap.q_prepared) & 15u) != 0) {
+    return cudaErrorInvalidValue;
+  }
+  BalancedParams p = balanced_params(a);
+  p.raw_q = ap.q;
+  p.raw_k = ap.k;
+  p.raw_v = ap.v;
+  p.q_norm_weight = ap.q_norm_weight;
+  p.k_norm_weight = ap.k_norm_weight;
+  p.cos = ap.cos;
+  p.sin = ap.sin;
+  p.token_position = ap.token_position;
+  p.q_prepared = ap.q_prepared;
+  using T = DecodeTraits<256, 8, 2, 8>;
+  const int64_t slots = int64_t(a.batch_count) * a.num_splits;
+  if (ap.norm_mode == B200KV_NORM_IEEE) {
+    return launch_balanced<T, kFusedIeee>(p, slots, stream);
+  }
+  return launch_balanced<T, kFusedApprox>(p, slots, stream);
 }
 
 int decode_balanced_num_splits(int batch_count, int sm_count) {

@@ -364,33 +364,57 @@ __device__ __forceinline__ void write_partial_row(float *partial_m,
 }
 
 // LSE-style combine of n partials of one (sequence, query head) row; partial i
-// lives at scratch index first + i * stride. 256 threads = 4 groups of 64: a
-// group owns every 4th partial and a thread 4 of the 256 dims, so loads of
-// different partials are independent and in flight together
+// lives at scratch index first + i * stride
 // (src/gemma4_flash_attention_decode.cu:881-977 does the same sums serially).
+// A CTA of 256 threads handles slice `slice` of kSlices equal slices of the
+// row's D dims: the threads form kGroups groups of kCols (one float4 column
+// each); a group owns every kGroups-th partial and keeps four loads in flight,
+// so 4 * kGroups partials are read per round trip. kSlices = 1 suits many rows
+// with few partials each; with few rows and many partials (small batches) the
+// combine is a chain of load round trips on a handful of SMs, and kSlices = 4
+// puts four times the SMs on it with four times the partials per round.
 constexpr int kCombineThreads = 256;
-constexpr int kCombineGroups = 4;
 constexpr int kCombineChunk = 1024;  // partials whose weights fit the table
 
-template <int D>
+template <int D, int kSlices>
+struct CombineShape {
+  static constexpr int kCols = D / 4 / kSlices;
+  static constexpr int kGroups = kCombineThreads / kCols;
+  static_assert(kCols * kSlices * 4 == D && kCols * kGroups == kCombineThreads,
+                "thread mapping");
+};
+
+template <int D, int kSlices>
 __device__ __forceinline__ void combine_row(__nv_bfloat16 *out_row, float *lse_row,
                                             const float *partial_m,
                                             const float *partial_l,
                                             const float *partial_acc,
                                             int64_t first, int64_t stride, int n,
-                                            float *s_w, float *s_red,
-                                            float4 (*s_val)[D / 4]) {
-  static_assert(D / 4 * kCombineGroups == kCombineThreads, "thread mapping");
+                                            int slice, float *s_w, float *s_red,
+                                            float4 *s_val) {
+  using Shape = CombineShape<D, kSlices>;
+  constexpr int kCols = Shape::kCols;
+  constexpr int kGroups = Shape::kGroups;
   const int tid = int(threadIdx.x);
   const int lane = tid & 31;
   const int warp = tid >> 5;
-  const int group = tid / (D / 4);
-  const int col = tid % (D / 4);
+  const int group = tid / kCols;
+  const int col = slice * kCols + tid % kCols;
   const float *pm = partial_m + first;
   const float *pl = partial_l + first;
   const float4 *acc =
       reinterpret_cast<const float4 *>(partial_acc + first * D) + col;
   const size_t acc_stride = size_t(stride) * (D / 4);
+
+  // The first round of accumulator loads does not depend on the weights: it
+  // is issued before the maxima are known and lands while they are reduced.
+  float4 pre[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int s = group + j * kGroups;
+    pre[j] = s < n ? __ldg(acc + size_t(s) * acc_stride)
+                   : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
 
   // Pass 1: the row maximum over the partials.
   float M = -INFINITY;
@@ -407,9 +431,18 @@ __device__ __forceinline__ void combine_row(__nv_bfloat16 *out_row, float *lse_r
   __syncthreads();
 
   // Pass 2: weights 2^(m_i - M) (0 for partials without mass, :953-956), the
-  // denominator, and the weighted sum of the accumulators.
+  // denominator, and the weighted sum of the accumulators. A weight of 0 must
+  // drop its partial whatever the scratch holds.
   float L = 0.0f;
   float4 value = make_float4(0.f, 0.f, 0.f, 0.f);
+  auto add = [&value](const float4 &a, float w) {
+    if (w > 0.0f) {
+      value.x = fmaf(a.x, w, value.x);
+      value.y = fmaf(a.y, w, value.y);
+      value.z = fmaf(a.z, w, value.z);
+      value.w = fmaf(a.w, w, value.w);
+    }
+  };
   for (int base = 0; base < n; base += kCombineChunk) {
     const int cnt = min(kCombineChunk, n - base);
     for (int s = tid; s < cnt; s += kCombineThreads) {
@@ -421,47 +454,41 @@ __device__ __forceinline__ void combine_row(__nv_bfloat16 *out_row, float *lse_r
     }
     __syncthreads();
     int s = group;
-    for (; s + 3 * kCombineGroups < cnt; s += 4 * kCombineGroups) {
-      const float4 a0 = __ldg(acc + size_t(base + s) * acc_stride);
-      const float4 a1 = __ldg(acc + size_t(base + s + kCombineGroups) * acc_stride);
-      const float4 a2 = __ldg(acc + size_t(base + s + 2 * kCombineGroups) * acc_stride);
-      const float4 a3 = __ldg(acc + size_t(base + s + 3 * kCombineGroups) * acc_stride);
-      const float w0 = s_w[s], w1 = s_w[s + kCombineGroups];
-      const float w2 = s_w[s + 2 * kCombineGroups], w3 = s_w[s + 3 * kCombineGroups];
-      // A weight of 0 must drop its partial whatever the scratch holds.
-      value.x += (w0 > 0.f ? a0.x * w0 : 0.f) + (w1 > 0.f ? a1.x * w1 : 0.f) +
-                 (w2 > 0.f ? a2.x * w2 : 0.f) + (w3 > 0.f ? a3.x * w3 : 0.f);
-      value.y += (w0 > 0.f ? a0.y * w0 : 0.f) + (w1 > 0.f ? a1.y * w1 : 0.f) +
-                 (w2 > 0.f ? a2.y * w2 : 0.f) + (w3 > 0.f ? a3.y * w3 : 0.f);
-      value.z += (w0 > 0.f ? a0.z * w0 : 0.f) + (w1 > 0.f ? a1.z * w1 : 0.f) +
-                 (w2 > 0.f ? a2.z * w2 : 0.f) + (w3 > 0.f ? a3.z * w3 : 0.f);
-      value.w += (w0 > 0.f ? a0.w * w0 : 0.f) + (w1 > 0.f ? a1.w * w1 : 0.f) +
-                 (w2 > 0.f ? a2.w * w2 : 0.f) + (w3 > 0.f ? a3.w * w3 : 0.f);
-    }
-    for (; s < cnt; s += kCombineGroups) {
-      const float w = s_w[s];
-      if (w > 0.0f) {
-        const float4 a = __ldg(acc + size_t(base + s) * acc_stride);
-        value.x = fmaf(a.x, w, value.x);
-        value.y = fmaf(a.y, w, value.y);
-        value.z = fmaf(a.z, w, value.z);
-        value.w = fmaf(a.w, w, value.w);
+    if (base == 0) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (s + j * kGroups < cnt) add(pre[j], s_w[s + j * kGroups]);
       }
+      s += 4 * kGroups;
+    }
+    for (; s + 3 * kGroups < cnt; s += 4 * kGroups) {
+      const float4 a0 = __ldg(acc + size_t(base + s) * acc_stride);
+      const float4 a1 = __ldg(acc + size_t(base + s + kGroups) * acc_stride);
+      const float4 a2 = __ldg(acc + size_t(base + s + 2 * kGroups) * acc_stride);
+      const float4 a3 = __ldg(acc + size_t(base + s + 3 * kGroups) * acc_stride);
+      add(a0, s_w[s]);
+      add(a1, s_w[s + kGroups]);
+      add(a2, s_w[s + 2 * kGroups]);
+      add(a3, s_w[s + 3 * kGroups]);
+    }
+    for (; s < cnt; s += kGroups) {
+      const float w = s_w[s];
+      if (w > 0.0f) add(__ldg(acc + size_t(base + s) * acc_stride), w);
     }
     __syncthreads();
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
   if (lane == 0) s_red[warp] = L;
-  s_val[group][col] = value;
+  s_val[tid] = value;  // [group][column of the slice]
   __syncthreads();
   if (group != 0) return;
   L = 0.0f;
 #pragma unroll
   for (int w = 0; w < kCombineThreads / 32; ++w) L += s_red[w];
-#pragma unroll
-  for (int g = 1; g < kCombineGroups; ++g) {
-    const float4 o = s_val[g][col];
+#pragma unroll 4
+  for (int g = 1; g < kGroups; ++g) {
+    const float4 o = s_val[g * kCols + tid];
     value.x += o.x;
     value.y += o.y;
     value.z += o.z;
@@ -473,19 +500,25 @@ __device__ __forceinline__ void combine_row(__nv_bfloat16 *out_row, float *lse_r
   reinterpret_cast<uint2 *>(out_row)[col] =
       make_uint2(*reinterpret_cast<const uint32_t *>(&lo),
                  *reinterpret_cast<const uint32_t *>(&hi));
-  if (lse_row != nullptr && tid == 0) {
+  if (lse_row != nullptr && tid == 0 && slice == 0) {
     *lse_row = L > 0.0f ? (M + lg2_approx(L)) * 0.6931471805599453f : -INFINITY;
   }
 }
 
+// How many dim slices the combine of `rows` output rows is cut into.
+inline int combine_slices(int64_t rows) { return rows <= 256 ? 4 : 1; }
+
 // Row of zeros and LSE = -inf for a (sequence, head) without live keys
 // (src/gemma4_flash_attention_decode.cu:920-926).
-template <int D>
+template <int D, int kSlices>
 __device__ __forceinline__ void combine_empty_row(__nv_bfloat16 *out_row,
-                                                  float *lse_row) {
+                                                  float *lse_row, int slice) {
+  constexpr int kCols = CombineShape<D, kSlices>::kCols;
   const int tid = int(threadIdx.x);
-  if (tid < D / 4) reinterpret_cast<uint2 *>(out_row)[tid] = make_uint2(0, 0);
-  if (lse_row != nullptr && tid == 0) *lse_row = -INFINITY;
+  if (tid < kCols) {
+    reinterpret_cast<uint2 *>(out_row)[slice * kCols + tid] = make_uint2(0, 0);
+  }
+  if (lse_row != nullptr && tid == 0 && slice == 0) *lse_row = -INFINITY;
 }
 
 }  // namespace b200kv

@@ -8,6 +8,8 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
+#include <cstring>
 #include <new>
 #include <vector>
 
@@ -332,6 +334,18 @@ cudaError_t gemma4_runtime_prepare_decode_step(Gemma4RuntimeState *state,
 struct B200KvRuntimeState {
   Gemma4RuntimeState state;
 };
+
+namespace {
+// B200KV_FUSED_LAYER_STEP=0 keeps the layer-step on separate append and
+// attention launches (for A/B timing); read once.
+bool fused_layer_step_enabled() {
+  static const bool enabled = [] {
+    const char *v = std::getenv("B200KV_FUSED_LAYER_STEP");
+    return v == nullptr || std::strcmp(v, "0") != 0;
+  }();
+  return enabled;
+}
+}  // namespace
 
 extern "C" {
 
@@ -806,9 +820,23 @@ int b200kv_decode_layer_step_bf16(const B200KvLayerStepArgs *s,
   d.partial_acc = s->partial_acc;
   d.status = s->status;
 
-  // Stream order makes the appended row visible to the attention kernel, the
-  // job the grid-wide barrier does inside the reference's fused layer kernel
-  // (src/gemma4_flash_attention_decode.cu:524).
+  // One launch for append + attention where the balanced kernel can do both
+  // (the reference's decode_megakernel_fused_layer_kernel is one launch too,
+  // src/gemma4_flash_attention_decode.cu:1004-1031). The profiling hooks ask
+  // for a boundary between the two, which only the two-launch form has.
+  if (s->event_before_attention == nullptr && s->batch_count > 0 &&
+      fused_layer_step_enabled() && b200kv::decode_fused_supported(a, d)) {
+    const cudaError_t st_fused = b200kv::decode_layer_step_fused_bf16(a, d, st);
+    if (st_fused != cudaSuccess) return st_fused;
+    if (s->event_after_attention != nullptr) {
+      B200KV_TRY(cudaEventRecord(
+          static_cast<cudaEvent_t>(s->event_after_attention), st));
+    }
+    return cudaSuccess;
+  }
+  // Two launches: stream order makes the appended row visible to the attention
+  // kernel, the job the grid-wide barrier does inside the reference's fused
+  // layer kernel (src/gemma4_flash_attention_decode.cu:524).
   const cudaError_t st_append = b200kv::decode_append_bf16(a, st);
   if (st_append != cudaSuccess) return st_append;
   if (s->event_before_attention != nullptr) {

@@ -73,6 +73,20 @@ struct AppendArgs {
 
 cudaError_t decode_append_bf16(const AppendArgs &args, cudaStream_t stream);
 
+// Argument checks of the two launches above without the launch
+// (cudaSuccess or cudaErrorInvalidValue).
+cudaError_t validate_append_args(const AppendArgs &args);
+cudaError_t validate_decode_args(const DecodeArgs &args);
+
+// One layer-step in one attention launch (plus the combine): the balanced
+// kernel prepares and appends the step's rows itself. Only for the geometry
+// decode_fused_supported() accepts; the results are those of
+// decode_append_bf16 followed by decode_attention_bf16 with split_size == 0.
+bool decode_fused_supported(const AppendArgs &append, const DecodeArgs &decode);
+cudaError_t decode_layer_step_fused_bf16(const AppendArgs &append,
+                                         const DecodeArgs &decode,
+                                         cudaStream_t stream);
+
 struct PrefillPrepArgs {
   __nv_bfloat16 *q_prepared = nullptr;
   __nv_bfloat16 *k_prepared = nullptr;
