@@ -215,12 +215,12 @@ __global__ __launch_bounds__(T::kThreads, T::kCtasPerSm) void decode_split_kerne
 
 // One CTA per (batch, q_head) row and dim slice: combine of that row's live
 // splits.
-template <int D, int kSlices>
-__global__ __launch_bounds__(kCombineThreads) void decode_combine_kernel(
+template <int D, int kSlices, int kThreads>
+__global__ __launch_bounds__(kThreads) void decode_combine_kernel(
     DecodeParams p) {
   __shared__ float s_w[kCombineChunk];
-  __shared__ float s_red[kCombineThreads / 32];
-  __shared__ float4 s_val[kCombineThreads];
+  __shared__ float s_red[kThreads / 32];
+  __shared__ float4 s_val[kThreads];
   const int row = int(blockIdx.x);
   const int slice = int(blockIdx.y);
   const int batch = row / p.q_heads;
@@ -239,7 +239,7 @@ __global__ __launch_bounds__(kCombineThreads) void decode_combine_kernel(
     combine_empty_row<D, kSlices>(out_row, lse_row, slice);
     return;
   }
-  combine_row<D, kSlices>(out_row, lse_row, p.partial_m, p.partial_l,
+  combine_row<D, kSlices, kThreads>(out_row, lse_row, p.partial_m, p.partial_l,
                           p.partial_acc, int64_t(row) * p.num_splits, 1, n, slice,
                           s_w, s_red, s_val);
 }
@@ -353,14 +353,8 @@ cudaError_t decode_attention_bf16(const DecodeArgs &a, cudaStream_t stream) {
   }
   if (st != cudaSuccess) return st;
   if (a.num_splits > 1) {
-    const unsigned rows = unsigned(a.batch_count * a.q_heads);
-    if (combine_slices(rows) == 4) {
-      st = launch_pdl(decode_combine_kernel<256, 4>, dim3(rows, 4),
-                      dim3(kCombineThreads), 0, stream, p);
-    } else {
-      st = launch_pdl(decode_combine_kernel<256, 1>, dim3(rows),
-                      dim3(kCombineThreads), 0, stream, p);
-    }
+    const int64_t rows = int64_t(a.batch_count) * a.q_heads;
+    st = B200KV_LAUNCH_COMBINE(decode_combine_kernel, rows, stream, p);
   }
   return st;
 }

@@ -30,6 +30,10 @@ namespace b200kv {
 namespace {
 
 constexpr int kMaxBalancedBatch = 1024;  // live-key prefix sums live in smem
+// Second instantiation of the fused kernel for small batches: 8 KiB less
+// shared memory, which is what lets a CTA of the next layer-step's kernel (and
+// a waiting combine CTA) share an SM with a CTA of this one.
+constexpr int kSmallBalancedBatch = 64;
 constexpr int kMinKeysPerCta = 16;       // below this a CTA is all latency
 
 struct BalancedParams {
@@ -76,6 +80,7 @@ __device__ __forceinline__ int range_width(int total, int num_ctas, int tile) {
 // Exclusive prefix sums of the live key counts into s_prefix[0..batch] and the
 // first live position of each sequence into s_first[0..batch). All threads of
 // the CTA call it; returns after a barrier.
+template <int kMaxBatch>
 __device__ void scan_live_keys(const BalancedParams &p, int *s_prefix,
                                int *s_first, int *s_warp_sums) {
   const int tid = int(threadIdx.x);
@@ -84,7 +89,7 @@ __device__ void scan_live_keys(const BalancedParams &p, int *s_prefix,
   const int warp = tid >> 5;
   const int per_thread = div_up(p.batch_count, nthreads);
   const int b0 = tid * per_thread;
-  int counts[kMaxBalancedBatch / 256 + 1];
+  int counts[kMaxBatch / 256 + 1];
   int sum = 0;
   for (int i = 0; i < per_thread && i < int(sizeof(counts) / sizeof(int)); ++i) {
     const int b = b0 + i;
@@ -269,7 +274,7 @@ __device__ __forceinline__ void append_unstreamed_rows(const BalancedParams &p,
 // sequence's new key prepares that row, uses it from shared memory and writes
 // it to the cache: one launch per layer-step instead of two, and nothing the
 // attention streams early depends on a preceding kernel.
-template <class T, int kMode>
+template <class T, int kMode, int kMaxBatch>
 __global__ __launch_bounds__(T::kThreads, T::kCtasPerSm) void decode_balanced_kernel(
     BalancedParams p) {
   constexpr int G = T::G;
@@ -282,7 +287,7 @@ __global__ __launch_bounds__(T::kThreads, T::kCtasPerSm) void decode_balanced_ke
   constexpr int kAppendBytes =
       kFused ? T::kConsumerWarps * kAppendBufferBytesPerWarp : 0;
   int *s_prefix = reinterpret_cast<int *>(smem + T::kRingBytes + kAppendBytes);
-  int *s_first = s_prefix + kMaxBalancedBatch + 1;
+  int *s_first = s_prefix + kMaxBatch + 1;
   __shared__ int s_warp_sums[32];
 
   const int warp = int(threadIdx.x) >> 5;
@@ -309,7 +314,7 @@ __global__ __launch_bounds__(T::kThreads, T::kCtasPerSm) void decode_balanced_ke
   // "everything before it is complete".
   if constexpr (!kFused) pdl_release_successor();
 
-  scan_live_keys(p, s_prefix, s_first, s_warp_sums);
+  scan_live_keys<kMaxBatch>(p, s_prefix, s_first, s_warp_sums);
   const int total = s_prefix[p.batch_count];
   const int width = range_width(max(total, 1), p.num_ctas, ST);
   const int r0 = int(blockIdx.x) * width;
@@ -412,12 +417,14 @@ __global__ __launch_bounds__(T::kThreads, T::kCtasPerSm) void decode_balanced_ke
     // fused: position of the sequence's new row, and whether this piece of the
     // sequence contains it (then this warp prepares, uses and stores the row)
     [[maybe_unused]] int new_pos = -1;
+    [[maybe_unused]] int new_page = -1;
     [[maybe_unused]] bool owns_new = false;
     if constexpr (T::kFp8) {
       st.load_q(p.q + (int64_t(seg.b) * p.q_heads + head * G) * T::D, lane);
     } else if constexpr (kFused) {
       new_pos = __ldg(p.token_position + seg.b);
       owns_new = new_pos >= seg.pos0 && new_pos < seg.pos1;
+      if (owns_new) new_page = append_page(p, seg.b, new_pos);  // in flight early
       if (new_pos >= 0) {
         prepare_rows<kIeee>(raw, p, seg.b, head, new_pos, owns_new, wbuf, lane);
       } else {  // no append for this sequence: q is what the caller left there
@@ -477,8 +484,7 @@ __global__ __launch_bounds__(T::kThreads, T::kCtasPerSm) void decode_balanced_ke
       pdl_wait_for_predecessor();
       pdl_release_successor();
       if (owns_new) {
-        store_appended_rows(p, raw, seg.b, head, new_pos,
-                            append_page(p, seg.b, new_pos), wbuf, lane);
+        store_appended_rows(p, raw, seg.b, head, new_pos, new_page, wbuf, lane);
         __syncwarp();
       }
     }
@@ -505,69 +511,78 @@ __global__ __launch_bounds__(T::kThreads, T::kCtasPerSm) void decode_balanced_ke
 // One CTA per (sequence, q_head) row. Recomputes which CTAs touched the
 // sequence from the same prefix sums and combines their partials; rows that
 // one CTA finished alone are left as they are; empty rows are zeroed.
-template <int D, int kSlices>
-__global__ __launch_bounds__(kCombineThreads) void balanced_combine_kernel(
+// Combine of the balanced kernels: a CTA takes (row, slice) items -- one when
+// the grid has a CTA per item, several in turn when it does not -- recomputes
+// which CTAs touched the row's sequence from the same prefix sums and combines
+// their partials; rows that one CTA finished alone are left as they are; empty
+// rows are zeroed.
+template <int D, int kSlices, int kThreads>
+__global__ __launch_bounds__(kThreads) void balanced_combine_kernel(
     BalancedParams p, int tile) {
   __shared__ float s_w[kCombineChunk];
-  __shared__ float s_red[kCombineThreads / 32];
-  __shared__ float4 s_val[kCombineThreads];
-  __shared__ int s_sum[3][kCombineThreads / 32];
-  const int row = int(blockIdx.x);
-  const int slice = int(blockIdx.y);
-  const int b = row / p.q_heads;
-  const int q_head = row - b * p.q_heads;
+  __shared__ float s_red[kThreads / 32];
+  __shared__ float4 s_val[kThreads];
+  __shared__ int s_sum[3][kThreads / 32];
   const int tid = int(threadIdx.x);
   const int lane = tid & 31;
   const int warp = tid >> 5;
+  const int items = p.batch_count * p.q_heads * kSlices;
 
   pdl_release_successor();
 
-  int before = 0, all = 0, mine = 0;
-  for (int i = tid; i < p.batch_count; i += kCombineThreads) {
-    const int len = __ldg(p.seq_lengths + i);
-    const int first = p.cfg.window_size > 0 ? max(0, len - p.cfg.window_size) : 0;
-    const int n = max(0, len - first);
-    all += n;
-    if (i < b) before += n;
-    if (i == b) mine = n;
-  }
+  for (int item = int(blockIdx.x); item < items; item += int(gridDim.x)) {
+    const int row = item / kSlices;
+    const int slice = item - row * kSlices;
+    const int b = row / p.q_heads;
+    const int q_head = row - b * p.q_heads;
+    int before = 0, all = 0, mine = 0;
+    for (int i = tid; i < p.batch_count; i += kThreads) {
+      const int len = __ldg(p.seq_lengths + i);
+      const int first = p.cfg.window_size > 0 ? max(0, len - p.cfg.window_size) : 0;
+      const int n = max(0, len - first);
+      all += n;
+      if (i < b) before += n;
+      if (i == b) mine = n;
+    }
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    before += __shfl_xor_sync(0xffffffffu, before, o);
-    all += __shfl_xor_sync(0xffffffffu, all, o);
-    mine += __shfl_xor_sync(0xffffffffu, mine, o);
-  }
-  if (lane == 0) {
-    s_sum[0][warp] = before;
-    s_sum[1][warp] = all;
-    s_sum[2][warp] = mine;
-  }
-  __syncthreads();
-  before = all = mine = 0;
+    for (int o = 16; o > 0; o >>= 1) {
+      before += __shfl_xor_sync(0xffffffffu, before, o);
+      all += __shfl_xor_sync(0xffffffffu, all, o);
+      mine += __shfl_xor_sync(0xffffffffu, mine, o);
+    }
+    if (lane == 0) {
+      s_sum[0][warp] = before;
+      s_sum[1][warp] = all;
+      s_sum[2][warp] = mine;
+    }
+    __syncthreads();
+    before = all = mine = 0;
 #pragma unroll
-  for (int w = 0; w < kCombineThreads / 32; ++w) {
-    before += s_sum[0][w];
-    all += s_sum[1][w];
-    mine += s_sum[2][w];
-  }
+    for (int w = 0; w < kThreads / 32; ++w) {
+      before += s_sum[0][w];
+      all += s_sum[1][w];
+      mine += s_sum[2][w];
+    }
+    __syncthreads();  // s_sum is rewritten by the next item
 
-  // The lengths were final before the split kernel started; its partials and
-  // directly written rows are not.
-  pdl_wait_for_predecessor();
-  __nv_bfloat16 *out_row = p.out + int64_t(row) * D;
-  float *lse_row = p.lse != nullptr ? p.lse + row : nullptr;
-  if (mine == 0) {
-    combine_empty_row<D, kSlices>(out_row, lse_row, slice);
-    return;
+    // The lengths were final before the attention kernel started; its
+    // partials and directly written rows are not.
+    pdl_wait_for_predecessor();
+    __nv_bfloat16 *out_row = p.out + int64_t(row) * D;
+    float *lse_row = p.lse != nullptr ? p.lse + row : nullptr;
+    if (mine == 0) {
+      combine_empty_row<D, kSlices>(out_row, lse_row, slice);
+      continue;
+    }
+    const int width = range_width(all, p.num_ctas, tile);
+    const int c_first = before / width;
+    const int c_last = (before + mine - 1) / width;
+    if (c_first == c_last) continue;  // finished by that CTA
+    combine_row<D, kSlices, kThreads>(
+        out_row, lse_row, p.partial_m, p.partial_l, p.partial_acc,
+        int64_t(c_first + b) * p.q_heads + q_head, p.q_heads,
+        c_last - c_first + 1, slice, s_w, s_red, s_val);
   }
-  const int width = range_width(all, p.num_ctas, tile);
-  const int c_first = before / width;
-  const int c_last = (before + mine - 1) / width;
-  if (c_first == c_last) return;  // finished by that CTA
-  combine_row<D, kSlices>(out_row, lse_row, p.partial_m, p.partial_l,
-                          p.partial_acc, int64_t(c_first + b) * p.q_heads + q_head,
-                          p.q_heads, c_last - c_first + 1, slice, s_w, s_red,
-                          s_val);
 }
 
 }  // namespace
@@ -580,11 +595,11 @@ bool decode_balanced_supported(const Gemma4KvCacheConfig &c, int q_heads,
 
 namespace {
 
-template <class T, int kMode = kAttentionOnly>
+template <class T, int kMode = kAttentionOnly, int kMaxBatch = kMaxBalancedBatch>
 cudaError_t launch_balanced(BalancedParams p, int64_t scratch_slots,
                             cudaStream_t stream) {
   constexpr int kSmem =
-      T::kRingBytes + (2 * kMaxBalancedBatch + 1) * 4 +
+      T::kRingBytes + (2 * kMaxBatch + 1) * 4 +
       (kMode != kAttentionOnly ? T::kConsumerWarps * kAppendBufferBytesPerWarp : 0);
   static_assert(T::kRingBytes % 16 == 0, "the append buffers hold 16-byte rows");
   // per SM: two CTAs, each with 1 KiB the system reserves and the static arrays
@@ -602,19 +617,26 @@ cudaError_t launch_balanced(BalancedParams p, int64_t scratch_slots,
     return cudaErrorInvalidValue;
   }
   p.num_ctas = int32_t(num_ctas);
-  st = cudaFuncSetAttribute(decode_balanced_kernel<T, kMode>,
+  if (p.batch_count > kMaxBatch) return cudaErrorInvalidValue;
+  st = cudaFuncSetAttribute(decode_balanced_kernel<T, kMode, kMaxBatch>,
                             cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
   if (st != cudaSuccess) return st;
-  st = launch_pdl(decode_balanced_kernel<T, kMode>, dim3(unsigned(num_ctas)),
-                  dim3(T::kThreads), kSmem, stream, p);
+  st = launch_pdl(decode_balanced_kernel<T, kMode, kMaxBatch>,
+                  dim3(unsigned(num_ctas)), dim3(T::kThreads), kSmem, stream, p);
   if (st != cudaSuccess) return st;
-  const unsigned rows = unsigned(p.batch_count * p.q_heads);
-  if (combine_slices(rows) == 4) {
-    return launch_pdl(balanced_combine_kernel<256, 4>, dim3(rows, 4),
-                      dim3(kCombineThreads), 0, stream, p, int(T::kStageTokens));
+  const int64_t rows = int64_t(p.batch_count) * p.q_heads;
+  const int tile = int(T::kStageTokens);
+  switch (combine_shape(rows)) {
+    case 0:
+      return launch_pdl(balanced_combine_kernel<256, 4, 256>,
+                        dim3(unsigned(rows * 4)), dim3(256), 0, stream, p, tile);
+    case 1:
+      return launch_pdl(balanced_combine_kernel<256, 4, 128>,
+                        dim3(unsigned(rows * 4)), dim3(128), 0, stream, p, tile);
+    default:
+      return launch_pdl(balanced_combine_kernel<256, 1, 256>,
+                        dim3(unsigned(rows)), dim3(256), 0, stream, p, tile);
   }
-  return launch_pdl(balanced_combine_kernel<256, 1>, dim3(rows),
-                    dim3(kCombineThreads), 0, stream, p, int(T::kStageTokens));
 }
 
 BalancedParams balanced_params(const DecodeArgs &a) {
@@ -716,10 +738,13 @@ cudaError_t decode_layer_step_fused_bf16(const AppendArgs &ap,
   p.q_prepared = ap.q_prepared;
   using T = DecodeTraits<256, 8, 2, 8>;
   const int64_t slots = int64_t(a.batch_count) * a.num_splits;
+  const bool small = a.batch_count <= kSmallBalancedBatch;
   if (ap.norm_mode == B200KV_NORM_IEEE) {
-    return launch_balanced<T, kFusedIeee>(p, slots, stream);
+    return small ? launch_balanced<T, kFusedIeee, kSmallBalancedBatch>(p, slots, stream)
+                 : launch_balanced<T, kFusedIeee>(p, slots, stream);
   }
-  return launch_balanced<T, kFusedApprox>(p, slots, stream);
+  return small ? launch_balanced<T, kFusedApprox, kSmallBalancedBatch>(p, slots, stream)
+               : launch_balanced<T, kFusedApprox>(p, slots, stream);
 }
 
 int decode_balanced_num_splits(int batch_count, int sm_count) {

@@ -366,25 +366,31 @@ __device__ __forceinline__ void write_partial_row(float *partial_m,
 // LSE-style combine of n partials of one (sequence, query head) row; partial i
 // lives at scratch index first + i * stride
 // (src/gemma4_flash_attention_decode.cu:881-977 does the same sums serially).
-// A CTA of 256 threads handles slice `slice` of kSlices equal slices of the
-// row's D dims: the threads form kGroups groups of kCols (one float4 column
-// each); a group owns every kGroups-th partial and keeps four loads in flight,
-// so 4 * kGroups partials are read per round trip. kSlices = 1 suits many rows
-// with few partials each; with few rows and many partials (small batches) the
-// combine is a chain of load round trips on a handful of SMs, and kSlices = 4
-// puts four times the SMs on it with four times the partials per round.
-constexpr int kCombineThreads = 256;
-constexpr int kCombineChunk = 1024;  // partials whose weights fit the table
+// A CTA of kThreads threads handles slice `slice` of kSlices equal slices of
+// the row's D dims: the threads form kGroups groups of kCols (one float4
+// column each); a group owns every kGroups-th partial and keeps four loads in
+// flight, so 4 * kGroups partials are read per round trip. Three shapes are
+// used (combine_shape): one slice of 256 threads for many rows with few
+// partials each; with few rows and many partials (small batches) the combine
+// is a chain of load round trips on a handful of SMs, and four slices put four
+// times the SMs on it; in between, four slices of 128 threads: the combine's
+// CTAs are resident, waiting for the attention kernel to finish, while the next
+// layer-step's attention CTAs look for room to start, and half the threads
+// leave room for one of those per SM. (A second one does not fit beside a
+// combine CTA: two attention CTAs put five 96-register warps on two of the
+// SM's four register-file partitions, 15 360 of 16 384 registers.)
+constexpr int kCombineChunk = 512;  // partials whose weights fit the table
 
-template <int D, int kSlices>
+template <int D, int kSlices, int kThreads>
 struct CombineShape {
   static constexpr int kCols = D / 4 / kSlices;
-  static constexpr int kGroups = kCombineThreads / kCols;
-  static_assert(kCols * kSlices * 4 == D && kCols * kGroups == kCombineThreads,
+  static constexpr int kGroups = kThreads / kCols;
+  static constexpr int kWarps = kThreads / 32;
+  static_assert(kCols * kSlices * 4 == D && kCols * kGroups == kThreads,
                 "thread mapping");
 };
 
-template <int D, int kSlices>
+template <int D, int kSlices, int kThreads>
 __device__ __forceinline__ void combine_row(__nv_bfloat16 *out_row, float *lse_row,
                                             const float *partial_m,
                                             const float *partial_l,
@@ -392,7 +398,8 @@ __device__ __forceinline__ void combine_row(__nv_bfloat16 *out_row, float *lse_r
                                             int64_t first, int64_t stride, int n,
                                             int slice, float *s_w, float *s_red,
                                             float4 *s_val) {
-  using Shape = CombineShape<D, kSlices>;
+  using Shape = CombineShape<D, kSlices, kThreads>;
+  constexpr int kWarps = Shape::kWarps;
   constexpr int kCols = Shape::kCols;
   constexpr int kGroups = Shape::kGroups;
   const int tid = int(threadIdx.x);
@@ -418,7 +425,7 @@ __device__ __forceinline__ void combine_row(__nv_bfloat16 *out_row, float *lse_r
 
   // Pass 1: the row maximum over the partials.
   float M = -INFINITY;
-  for (int s = tid; s < n; s += kCombineThreads) {
+  for (int s = tid; s < n; s += kThreads) {
     M = fmaxf(M, __ldg(pm + s * stride));
   }
 #pragma unroll
@@ -427,7 +434,7 @@ __device__ __forceinline__ void combine_row(__nv_bfloat16 *out_row, float *lse_r
   __syncthreads();
   M = s_red[0];
 #pragma unroll
-  for (int w = 1; w < kCombineThreads / 32; ++w) M = fmaxf(M, s_red[w]);
+  for (int w = 1; w < kWarps; ++w) M = fmaxf(M, s_red[w]);
   __syncthreads();
 
   // Pass 2: weights 2^(m_i - M) (0 for partials without mass, :953-956), the
@@ -445,7 +452,7 @@ __device__ __forceinline__ void combine_row(__nv_bfloat16 *out_row, float *lse_r
   };
   for (int base = 0; base < n; base += kCombineChunk) {
     const int cnt = min(kCombineChunk, n - base);
-    for (int s = tid; s < cnt; s += kCombineThreads) {
+    for (int s = tid; s < cnt; s += kThreads) {
       const float sl = __ldg(pl + (base + s) * stride);
       const float w =
           sl > 0.0f ? ex2_approx(__ldg(pm + (base + s) * stride) - M) : 0.0f;
@@ -482,38 +489,54 @@ __device__ __forceinline__ void combine_row(__nv_bfloat16 *out_row, float *lse_r
   if (lane == 0) s_red[warp] = L;
   s_val[tid] = value;  // [group][column of the slice]
   __syncthreads();
-  if (group != 0) return;
-  L = 0.0f;
+  if (group == 0) {
+    L = 0.0f;
 #pragma unroll
-  for (int w = 0; w < kCombineThreads / 32; ++w) L += s_red[w];
+    for (int w = 0; w < kWarps; ++w) L += s_red[w];
 #pragma unroll 4
-  for (int g = 1; g < kGroups; ++g) {
-    const float4 o = s_val[g * kCols + tid];
-    value.x += o.x;
-    value.y += o.y;
-    value.z += o.z;
-    value.w += o.w;
+    for (int g = 1; g < kGroups; ++g) {
+      const float4 o = s_val[g * kCols + tid];
+      value.x += o.x;
+      value.y += o.y;
+      value.z += o.z;
+      value.w += o.w;
+    }
+    const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(value.x * inv, value.y * inv);
+    const __nv_bfloat162 hi = __floats2bfloat162_rn(value.z * inv, value.w * inv);
+    reinterpret_cast<uint2 *>(out_row)[col] =
+        make_uint2(*reinterpret_cast<const uint32_t *>(&lo),
+                   *reinterpret_cast<const uint32_t *>(&hi));
+    if (lse_row != nullptr && tid == 0 && slice == 0) {
+      *lse_row = L > 0.0f ? (M + lg2_approx(L)) * 0.6931471805599453f : -INFINITY;
+    }
   }
-  const float inv = L > 0.0f ? 1.0f / L : 0.0f;
-  const __nv_bfloat162 lo = __floats2bfloat162_rn(value.x * inv, value.y * inv);
-  const __nv_bfloat162 hi = __floats2bfloat162_rn(value.z * inv, value.w * inv);
-  reinterpret_cast<uint2 *>(out_row)[col] =
-      make_uint2(*reinterpret_cast<const uint32_t *>(&lo),
-                 *reinterpret_cast<const uint32_t *>(&hi));
-  if (lse_row != nullptr && tid == 0 && slice == 0) {
-    *lse_row = L > 0.0f ? (M + lg2_approx(L)) * 0.6931471805599453f : -INFINITY;
-  }
+  __syncthreads();  // the shared arrays are free for the caller's next row
 }
 
-// How many dim slices the combine of `rows` output rows is cut into.
-inline int combine_slices(int64_t rows) { return rows <= 256 ? 4 : 1; }
+// Shape of the combine launch for `rows` output rows: 0 = four slices of 256
+// threads, 1 = four slices of 128 threads, 2 = one slice of 256 threads.
+inline int combine_shape(int64_t rows) {
+  return rows <= 32 ? 0 : (rows <= 512 ? 1 : 2);
+}
+
+// Launches kernel<D, slices, threads> for the shape of `rows`.
+#define B200KV_LAUNCH_COMBINE(kernel, rows, stream, ...)                       \
+  (combine_shape(rows) == 0                                                    \
+       ? launch_pdl(kernel<256, 4, 256>, dim3(unsigned(rows), 4), dim3(256), 0,  \
+                    stream, __VA_ARGS__)                                       \
+       : combine_shape(rows) == 1                                              \
+             ? launch_pdl(kernel<256, 4, 128>, dim3(unsigned(rows), 4),          \
+                          dim3(128), 0, stream, __VA_ARGS__)                   \
+             : launch_pdl(kernel<256, 1, 256>, dim3(unsigned(rows)), dim3(256),  \
+                          0, stream, __VA_ARGS__))
 
 // Row of zeros and LSE = -inf for a (sequence, head) without live keys
 // (src/gemma4_flash_attention_decode.cu:920-926).
 template <int D, int kSlices>
 __device__ __forceinline__ void combine_empty_row(__nv_bfloat16 *out_row,
                                                   float *lse_row, int slice) {
-  constexpr int kCols = CombineShape<D, kSlices>::kCols;
+  constexpr int kCols = D / 4 / kSlices;  // <= 64: every shape has the threads
   const int tid = int(threadIdx.x);
   if (tid < kCols) {
     reinterpret_cast<uint2 *>(out_row)[slice * kCols + tid] = make_uint2(0, 0);
