@@ -119,6 +119,7 @@ class CudaError(RuntimeError):
 _P = c_void_p
 _SIGNATURES = {
     "gemma4_kv_cache_write_bf16": (c_int, [_P, _P, KvConfig, _P, _P, _P, c_int32, c_int32, _P, _P, _P]),
+    "b200kv_prefill_cache_fill_bf16": (c_int, [_P, _P, KvConfig, _P, _P, _P, c_int32, c_int32, c_int32, _P, _P, _P]),
     "b200kv_cache_offset": (c_int64, [POINTER(KvConfig), c_int32, c_int32, c_int32, c_int32, c_int32]),
     "b200kv_make_config": (None, [POINTER(KvConfig), c_int32, c_int32, c_int32, c_int32]),
     "b200kv_is_global_layer": (c_int32, [c_int32]),
@@ -351,6 +352,16 @@ def kv_cache_write(cache_k, cache_v, cfg: KvConfig, page_table, token_batch, tok
         _ptr(cache_k), _ptr(cache_v), cfg, _ptr(page_table), _ptr(token_batch), _ptr(token_position),
         token_count, layer, _ptr(k), _ptr(v), _stream(stream))
     return _check(code, "gemma4_kv_cache_write_bf16", check)
+
+
+def prefill_cache_fill(cache_k, cache_v, cfg: KvConfig, page_table, token_batch, token_position,
+                       batch_size: int, seq_len: int, layer: int, k_prepared, v_prepared, stream=None,
+                       check: bool = True) -> int:
+    """Prompt rows into the cache in one launch; a sliding cache keeps only each sequence's last window."""
+    code = load_library().b200kv_prefill_cache_fill_bf16(
+        _ptr(cache_k), _ptr(cache_v), cfg, _ptr(page_table), _ptr(token_batch), _ptr(token_position),
+        batch_size, seq_len, layer, _ptr(k_prepared), _ptr(v_prepared), _stream(stream))
+    return _check(code, "b200kv_prefill_cache_fill_bf16", check)
 
 
 def prefill_prep(q_prepared, k_prepared, v_prepared, q, k, v, q_norm_weight, k_norm_weight, cos, sin,

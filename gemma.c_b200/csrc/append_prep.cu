@@ -114,13 +114,19 @@ __global__ void prefill_prep_kernel(PrefillPrepArgs a) {
 }
 
 // One CTA per token: all heads of the token are one contiguous row in the
-// source and in the cache page, moved as 128-bit packs.
+// source and in the cache page, moved as 128-bit packs. With live_rows > 0 the
+// grid covers only the last live_rows rows of every run of seq_len source rows
+// (a prompt longer than the sliding window: only its tail stays in the ring).
 __global__ __launch_bounds__(256) void kv_cache_write_kernel(
     __nv_bfloat16 *cache_k, __nv_bfloat16 *cache_v, Gemma4KvCacheConfig c,
     const int32_t *token_batch, const int32_t *token_position,
     const int32_t *page_table, int32_t layer, const __nv_bfloat16 *k,
-    const __nv_bfloat16 *v) {
-  const int token = int(blockIdx.x);
+    const __nv_bfloat16 *v, int32_t seq_len, int32_t live_rows) {
+  int token = int(blockIdx.x);
+  if (live_rows > 0) {
+    const int run = token / live_rows;
+    token = run * seq_len + (seq_len - live_rows) + (token - run * live_rows);
+  }
   const int batch = __ldg(token_batch + token);
   const int position = __ldg(token_position + token);
   // Guards of src/gemma4_kv_cache.cu:27-34.
@@ -235,6 +241,26 @@ cudaError_t prefill_prep_bf16(const PrefillPrepArgs &a, cudaStream_t stream) {
       });
 }
 
+namespace {
+// Argument contract of src/gemma4_kv_cache.cu:149-180.
+bool valid_cache_write_args(const __nv_bfloat16 *cache_k,
+                            const __nv_bfloat16 *cache_v,
+                            const Gemma4KvCacheConfig &config,
+                            const int32_t *page_table,
+                            const int32_t *token_batch,
+                            const int32_t *token_position, int32_t layer,
+                            const __nv_bfloat16 *k, const __nv_bfloat16 *v) {
+  return !(layer < 0 || layer >= config.num_layers || config.num_pages <= 0 ||
+           config.page_size <= 0 || config.max_pages_per_seq <= 0 ||
+           config.batch_size <= 0 || config.window_size < 0 ||
+           config.num_heads <= 0 || config.head_dim <= 0 ||
+           config.head_dim % 8 != 0 || cache_k == nullptr ||
+           cache_v == nullptr || page_table == nullptr ||
+           token_batch == nullptr || token_position == nullptr ||
+           k == nullptr || v == nullptr);
+}
+}  // namespace
+
 cudaError_t kv_cache_write_bf16(__nv_bfloat16 *cache_k, __nv_bfloat16 *cache_v,
                                 Gemma4KvCacheConfig config,
                                 const int32_t *page_table,
@@ -243,23 +269,53 @@ cudaError_t kv_cache_write_bf16(__nv_bfloat16 *cache_k, __nv_bfloat16 *cache_v,
                                 int32_t token_count, int32_t layer,
                                 const __nv_bfloat16 *k, const __nv_bfloat16 *v,
                                 cudaStream_t stream) {
-  // Argument contract of src/gemma4_kv_cache.cu:149-180.
   if (token_count == 0) return cudaSuccess;
-  if (token_count < 0 || layer < 0 || layer >= config.num_layers ||
-      config.num_pages <= 0 || config.page_size <= 0 ||
-      config.max_pages_per_seq <= 0 || config.batch_size <= 0 ||
-      config.window_size < 0 || config.num_heads <= 0 ||
-      config.head_dim <= 0 || config.head_dim % 8 != 0 ||
-      cache_k == nullptr || cache_v == nullptr || page_table == nullptr ||
-      token_batch == nullptr || token_position == nullptr || k == nullptr ||
-      v == nullptr) {
+  if (token_count < 0 ||
+      !valid_cache_write_args(cache_k, cache_v, config, page_table, token_batch,
+                              token_position, layer, k, v)) {
     return cudaErrorInvalidValue;
   }
   const int vecs = config.num_heads * config.head_dim / 8;
   const int threads = vecs >= 256 ? 256 : ((vecs + 31) / 32) * 32;
   kv_cache_write_kernel<<<token_count, threads, 0, stream>>>(
       cache_k, cache_v, config, token_batch, token_position, page_table, layer,
-      k, v);
+      k, v, 0, 0);
+  return cudaGetLastError();
+}
+
+cudaError_t prefill_cache_fill_bf16(__nv_bfloat16 *cache_k,
+                                    __nv_bfloat16 *cache_v,
+                                    Gemma4KvCacheConfig config,
+                                    const int32_t *page_table,
+                                    const int32_t *token_batch,
+                                    const int32_t *token_position,
+                                    int32_t batch_size, int32_t seq_len,
+                                    int32_t layer, const __nv_bfloat16 *k,
+                                    const __nv_bfloat16 *v,
+                                    cudaStream_t stream) {
+  if (batch_size < 0 || seq_len < 0) return cudaErrorInvalidValue;
+  const int64_t rows = int64_t(batch_size) * seq_len;
+  if (rows > 2147483647ll) return cudaErrorInvalidValue;
+  // src/gemma4_prefill_megakernel.cu:189-207: everything for a linear cache or
+  // a prompt that fits the window, else the last window_size rows of every
+  // sequence (the reference issues one write per sequence for those).
+  if (config.window_size == 0 || seq_len <= config.window_size) {
+    return kv_cache_write_bf16(cache_k, cache_v, config, page_table, token_batch,
+                               token_position, int32_t(rows), layer, k, v,
+                               stream);
+  }
+  if (batch_size == 0) return cudaSuccess;
+  if (!valid_cache_write_args(cache_k, cache_v, config, page_table, token_batch,
+                              token_position, layer, k, v)) {
+    return cudaErrorInvalidValue;
+  }
+  const int64_t live = int64_t(batch_size) * config.window_size;
+  if (live > 2147483647ll) return cudaErrorInvalidValue;
+  const int vecs = config.num_heads * config.head_dim / 8;
+  const int threads = vecs >= 256 ? 256 : ((vecs + 31) / 32) * 32;
+  kv_cache_write_kernel<<<unsigned(live), threads, 0, stream>>>(
+      cache_k, cache_v, config, token_batch, token_position, page_table, layer,
+      k, v, seq_len, config.window_size);
   return cudaGetLastError();
 }
 

@@ -363,6 +363,25 @@ cudaError_t gemma4_kv_cache_write_bf16(
                                      d_v, stream);
 }
 
+int b200kv_prefill_cache_fill_bf16(b200kv_bf16 *d_cache_k,
+                                   b200kv_bf16 *d_cache_v,
+                                   Gemma4KvCacheConfig config,
+                                   const int32_t *d_page_table,
+                                   const int32_t *d_token_batch,
+                                   const int32_t *d_token_position,
+                                   int32_t batch_size, int32_t seq_len,
+                                   int32_t layer, const b200kv_bf16 *d_k_prepared,
+                                   const b200kv_bf16 *d_v_prepared,
+                                   b200kv_stream stream) {
+  using bf = __nv_bfloat16;
+  return b200kv::prefill_cache_fill_bf16(
+      reinterpret_cast<bf *>(d_cache_k), reinterpret_cast<bf *>(d_cache_v),
+      config, d_page_table, d_token_batch, d_token_position, batch_size, seq_len,
+      layer, reinterpret_cast<const bf *>(d_k_prepared),
+      reinterpret_cast<const bf *>(d_v_prepared),
+      static_cast<cudaStream_t>(stream));
+}
+
 int64_t b200kv_cache_offset(const Gemma4KvCacheConfig *config, int32_t layer,
                             int32_t page, int32_t page_offset, int32_t head,
                             int32_t dim) {

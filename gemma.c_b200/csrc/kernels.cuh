@@ -132,4 +132,18 @@ cudaError_t kv_cache_write_bf16(__nv_bfloat16 *cache_k, __nv_bfloat16 *cache_v,
                                 const __nv_bfloat16 *k, const __nv_bfloat16 *v,
                                 cudaStream_t stream);
 
+// Cache fill after a prompt of batch_size x seq_len prepared rows (row
+// b * seq_len + t is token t of sequence b): one launch that writes every row,
+// or for a sliding cache and a prompt longer than its window only the last
+// window_size rows of each sequence.
+cudaError_t prefill_cache_fill_bf16(__nv_bfloat16 *cache_k,
+                                    __nv_bfloat16 *cache_v,
+                                    Gemma4KvCacheConfig config,
+                                    const int32_t *page_table,
+                                    const int32_t *token_batch,
+                                    const int32_t *token_position,
+                                    int32_t batch_size, int32_t seq_len,
+                                    int32_t layer, const __nv_bfloat16 *k,
+                                    const __nv_bfloat16 *v, cudaStream_t stream);
+
 }  // namespace b200kv

@@ -188,6 +188,27 @@ int b200kv_prefill_prep_bf16(b200kv_bf16 *d_q_prepared,
                              int32_t norm_mode, b200kv_stream stream);
 
 /* ------------------------------------------------------------------ *
+ * Cache fill after a prompt: the prepared K/V rows of batch_size sequences of
+ * seq_len tokens each (row b * seq_len + t, with d_token_batch / d_token_position
+ * as gemma4_runtime_prepare_prefill leaves them) go into the cache in one
+ * launch. A linear cache, or a prompt no longer than the window, takes every
+ * row; a sliding cache with a longer prompt takes only the last window_size
+ * rows of each sequence. Replaces the write step of gemma4_prefill_megakernel,
+ * src/gemma4_prefill_megakernel.cu:189-207 (which loops over sequences with
+ * one gemma4_kv_cache_write_bf16 call each for the second case).
+ * ------------------------------------------------------------------ */
+int b200kv_prefill_cache_fill_bf16(b200kv_bf16 *d_cache_k,
+                                   b200kv_bf16 *d_cache_v,
+                                   Gemma4KvCacheConfig config,
+                                   const int32_t *d_page_table,
+                                   const int32_t *d_token_batch,
+                                   const int32_t *d_token_position,
+                                   int32_t batch_size, int32_t seq_len,
+                                   int32_t layer, const b200kv_bf16 *d_k_prepared,
+                                   const b200kv_bf16 *d_v_prepared,
+                                   b200kv_stream stream);
+
+/* ------------------------------------------------------------------ *
  * Fused decode append: for every sequence b < batch_count, prep the new
  * token's q heads into d_q_prepared and prep + store its K and V rows in the
  * paged cache at position d_token_position[b].

@@ -249,3 +249,39 @@ def test_runtime_state_metadata_on_device(kv):
     assert v.global_cache_config.astuple() == (8, 1, 4, 1, 1, 1, 512, 0)
     rt.close()
     assert kv.RuntimeState(0, 4, 4, check=False).status == kv.CUDA_ERROR_INVALID_VALUE
+
+
+@pytest.mark.parametrize("window,seq_len", [(64, 200), (64, 64), (64, 17), (0, 200)])
+def test_prompt_cache_fill_keeps_the_live_tail(kv, orc, window, seq_len):
+    """b200kv_prefill_cache_fill_bf16 against the reference's write step
+    (src/gemma4_prefill_megakernel.cu:189-207) restated with the oracle's cache write: every row for a
+    linear cache or a prompt within the window, else one write of the last `window` rows per sequence."""
+    rng = np.random.default_rng(77)
+    batch, page_size, heads, dim = 3, 16, 8, 256
+    mpps = -(-seq_len // page_size) if window == 0 else -(-(window + page_size - 1) // page_size)
+    table, num_pages = helpers.build_page_table(rng, batch, mpps, [mpps] * batch)
+    cfg = kv.make_kv_config(2, num_pages, page_size, mpps, batch, heads, dim, window)
+    rows = batch * seq_len
+    tb = np.repeat(np.arange(batch, dtype=np.int32), seq_len)           # gemma4_runtime_prepare_prefill's layout
+    tp = np.tile(np.arange(seq_len, dtype=np.int32), batch)
+    k = helpers.bf16_normal(rng, (rows, heads, dim))
+    v = helpers.bf16_normal(rng, (rows, heads, dim))
+    ck = rng.integers(0, 65536, size=cfg.cache_elements()).astype(np.uint16)
+    cv = rng.integers(0, 65536, size=cfg.cache_elements()).astype(np.uint16)
+    dck, dcv = dev(ck), dev(cv)
+    kv.prefill_cache_fill(dck, dcv, cfg, dev(table), dev(tb), dev(tp), batch, seq_len, 1, dev(k), dev(v))
+    if window == 0 or seq_len <= window:
+        assert orc.kv_cache_write(ck, cv, cfg.astuple(), table, tb, tp, 1, k, v) == 0
+    else:
+        for b in range(batch):
+            lo = b * seq_len + seq_len - window
+            sl = slice(lo, lo + window)
+            assert orc.kv_cache_write(ck, cv, cfg.astuple(), table, np.ascontiguousarray(tb[sl]),
+                                      np.ascontiguousarray(tp[sl]), 1, np.ascontiguousarray(k[sl]),
+                                      np.ascontiguousarray(v[sl])) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(host_u16(dck), ck) and np.array_equal(host_u16(dcv), cv)
+    assert kv.prefill_cache_fill(dck, dcv, cfg, dev(table), dev(tb), dev(tp), -1, seq_len, 1, dev(k), dev(v),
+                                 check=False) == kv.CUDA_ERROR_INVALID_VALUE
+    assert kv.prefill_cache_fill(dck, dcv, cfg, dev(table), dev(tb), dev(tp), batch, seq_len, 2, dev(k), dev(v),
+                                 check=False) == kv.CUDA_ERROR_INVALID_VALUE
