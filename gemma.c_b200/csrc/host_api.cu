@@ -841,10 +841,14 @@ int b200kv_decode_layer_step_bf16(const B200KvLayerStepArgs *s,
 
   // One launch for append + attention where the balanced kernel can do both
   // (the reference's decode_megakernel_fused_layer_kernel is one launch too,
-  // src/gemma4_flash_attention_decode.cu:1004-1031). The profiling hooks ask
-  // for a boundary between the two, which only the two-launch form has.
-  if (s->event_before_attention == nullptr && s->batch_count > 0 &&
-      fused_layer_step_enabled() && b200kv::decode_fused_supported(a, d)) {
+  // src/gemma4_flash_attention_decode.cu:1004-1031). The profiling hooks then
+  // bracket that launch and its combine.
+  if (s->batch_count > 0 && fused_layer_step_enabled() &&
+      b200kv::decode_fused_supported(a, d)) {
+    if (s->event_before_attention != nullptr) {
+      B200KV_TRY(cudaEventRecord(
+          static_cast<cudaEvent_t>(s->event_before_attention), st));
+    }
     const cudaError_t st_fused = b200kv::decode_layer_step_fused_bf16(a, d, st);
     if (st_fused != cudaSuccess) return st_fused;
     if (s->event_after_attention != nullptr) {

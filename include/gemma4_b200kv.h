@@ -412,6 +412,16 @@ void b200kv_plan_splits_total(int32_t batch_count, int32_t max_live_keys,
  * same names minus the prefix; it stands where the three bracketed phases of
  * decode_megakernel_fused_layer_kernel run
  * (src/gemma4_flash_attention_decode.cu:514-523,1004-1031).
+ *
+ * With split_size == 0, 8 KV heads x 256, 16 query heads, rotary_dim 256 and
+ * batch <= 1024 the append runs inside the attention kernel (one launch plus
+ * the combine): the CTA that streams a sequence's newest key prepares that
+ * row, uses it from shared memory and writes it to the cache; q is prepared
+ * by the warps that use it and written to `q` as the separate append would.
+ * Cache bytes, `q`, `out` and `lse` are the same bits as those of
+ * b200kv_decode_append_bf16 followed by b200kv_decode_attention_bf16.
+ * The environment variable B200KV_FUSED_LAYER_STEP=0 (read once) keeps the two
+ * launches apart, for comparison.
  * ------------------------------------------------------------------ */
 typedef struct B200KvLayerStepArgs {
   b200kv_bf16 *q;                 /* out: prepared q [batch, q_heads, head_dim] */
@@ -436,7 +446,9 @@ typedef struct B200KvLayerStepArgs {
   int32_t norm_mode;
   int32_t *status;                /* optional int32[4] */
   /* Optional profiling hooks: cudaEvent_t handles recorded on `stream` right
-   * before and right after the attention (split + combine) launches. */
+   * before and right after the attention (split + combine) launches; when the
+   * layer-step runs as one fused launch (append inside the attention kernel),
+   * right before and after that launch and its combine. */
   void *event_before_attention;
   void *event_after_attention;
 } B200KvLayerStepArgs;
