@@ -44,6 +44,12 @@ cudaError_t decode_attention_fp8(const DecodeArgs &args, const void *cache_k,
                                  const float *scale_v, cudaStream_t stream);
 bool decode_balanced_supported(const Gemma4KvCacheConfig &cfg, int q_heads,
                                int batch_count);
+// The reference's native global-layer geometry, 16 query heads on one KV head
+// of 512 dims (decode_gqa16.cu): balanced partition only (split_size == 0).
+bool decode_gqa16_supported(const Gemma4KvCacheConfig &cfg, int q_heads,
+                            int batch_count);
+cudaError_t decode_attention_gqa16_bf16(const DecodeArgs &args,
+                                        cudaStream_t stream);
 int decode_balanced_num_splits(int batch_count, int sm_count);
 
 // Key tile of the split kernel for a given KV-head count: split sizes that
