@@ -55,7 +55,7 @@ def parse_args():
                     help="skip timing the reference's own CUDA kernels (oracle/_ref) beside the library")
     ap.add_argument("--split-global", type=int, default=0, help="override the planned global split size")
     ap.add_argument("--split-local", type=int, default=0)
-    ap.add_argument("--workload", default="cfg3", choices=["cfg1", "cfg2", "cfg3", "cfg4", "cfg5"],
+    ap.add_argument("--workload", default="cfg3", choices=["cfg1", "cfg2", "cfg3", "cfg4", "cfg5", "native_global"],
                     help="BASELINE.json configs (1-based): cfg3 (default) is the batched paged decode the "
                          "metric is quoted on; the others are reported as extra lines on request")
     ap.add_argument("--partition", default="balanced", choices=["balanced", "splits"],
@@ -659,6 +659,142 @@ def workload_config(args, world, where, parallelism=None, layers=None):
     return cfg
 
 
+# --------------------------------------------------------------------------- next row: native global geometry
+def run_native_global(args, kv, torch, sampler):
+    """Extra line (not a BASELINE config): the reference's native global-layer geometry, 16 query heads on
+    one KV head of 512 dims, rotary 128, V derived from raw K (src/gemma4.h:19-21,28) -- append + tensor-core
+    decode attention through b200kv_decode_layer_step_bf16 on a ragged batch (--seqs, default 64; context
+    lengths as cfg3) in a permuted page pool. One GPU."""
+    H, HKVG, DG, ROT = 16, 1, 512, 128
+    rng = np.random.default_rng(args.seed)
+    B = args.seqs or 64
+    ctx = rng.integers(args.min_ctx, args.max_ctx + 1, size=B).astype(np.int64)
+    e2e_warm, probe = 3, 11
+    total = args.warmup + args.steps + e2e_warm + args.e2e_steps + probe
+    pages = (ctx + total + PAGE - 1) // PAGE
+    mpps, num_pages = int(pages.max()), int(pages.sum())
+    pool = rng.permutation(num_pages).astype(np.int32)
+    table = np.full((B, mpps), -1, np.int32)
+    cur = 0
+    for b in range(B):
+        table[b, :pages[b]] = pool[cur:cur + pages[b]]
+        cur += int(pages[b])
+    dev = torch.device("cuda")
+    cfg = kv.make_kv_config(1, num_pages, PAGE, mpps, B, HKVG, DG, 0)
+    elems = num_pages * PAGE * HKVG * DG
+    ck = torch.randn(elems, dtype=torch.bfloat16, device=dev)
+    cv = torch.randn(elems, dtype=torch.bfloat16, device=dev)
+    raw_host = torch.randn((B, H + HKVG, DG), dtype=torch.bfloat16).pin_memory()
+    raw = raw_host.to(dev)
+    raw_q, raw_k = raw[:, :H].contiguous(), raw[:, H:].contiguous()
+    ones = torch.ones(DG, dtype=torch.bfloat16, device=dev)
+    cos_h, sin_h = kv.fill_rope_tables(int(ctx.max()) + total + 1, ROT // 2, 1.0e6, DG)
+    cos, sin = torch.from_numpy(cos_h).to(dev), torch.from_numpy(sin_h).to(dev)
+    dtable = torch.from_numpy(table).to(dev)
+    pos_all = torch.from_numpy((ctx[None, :] + np.arange(total)[:, None]).astype(np.int32)).to(dev)
+    len_all = pos_all + 1
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    nsplit = kv.plan_balanced(B, sms)
+    qp = torch.empty((B, H, DG), dtype=torch.bfloat16, device=dev)
+    out = torch.empty_like(qp)
+    out_host = torch.empty((B, H, DG), dtype=torch.bfloat16).pin_memory()
+    lse = torch.empty((B, H), dtype=torch.float32, device=dev)
+    pm = torch.empty(B * H * nsplit, dtype=torch.float32, device=dev)
+    pl = torch.empty_like(pm)
+    pacc = torch.empty(B * H * nsplit * DG, dtype=torch.float32, device=dev)
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    ev0 = [kv.Timer() for _ in range(total)]
+    ev1 = [kv.Timer() for _ in range(total)]
+    stream = torch.cuda.current_stream().cuda_stream
+    a = kv.LayerStepArgs()
+    a.q, a.out, a.lse = qp.data_ptr(), out.data_ptr(), lse.data_ptr()
+    a.partial_m, a.partial_l, a.partial_acc = pm.data_ptr(), pl.data_ptr(), pacc.data_ptr()
+    a.cache_k, a.cache_v, a.cache_config = ck.data_ptr(), cv.data_ptr(), cfg
+    a.page_table = dtable.data_ptr()
+    a.cache_layer, a.split_size, a.num_splits, a.softmax_scale = 0, 0, nsplit, 1.0 / math.sqrt(DG)
+    a.raw_q, a.raw_k, a.raw_v = raw_q.data_ptr(), raw_k.data_ptr(), None
+    a.q_norm_weight, a.k_norm_weight, a.cos, a.sin = ones.data_ptr(), ones.data_ptr(), cos.data_ptr(), sin.data_ptr()
+    a.batch_count, a.q_heads, a.rotary_dim, a.norm_mode = B, H, ROT, kv.NORM_RSQRT_APPROX
+    a.status = status.data_ptr()
+
+    def step(s, events=False):
+        a.token_position, a.seq_lengths = pos_all[s].data_ptr(), len_all[s].data_ptr()
+        a.event_before_attention = ev0[s].handle if events else None
+        a.event_after_attention = ev1[s].handle if events else None
+        kv.decode_layer_step(a, stream=stream)
+
+    def bytes_of(s):
+        n = ctx + s + 1
+        pg = (n - 1) // PAGE + 1
+        attn = int((n * HKVG * DG * 2 * 2 + 2 * H * DG * 2 + 4 * pg).sum())
+        append = B * ((H + HKVG) * DG * 2 + H * DG * 2 + 2 * HKVG * DG * 2 + 4)
+        return attn + append, attn
+
+    s = 0
+    for _ in range(args.warmup):
+        step(s); s += 1
+    torch.cuda.synchronize()
+    if sampler:
+        sampler.mark("timed_begin")
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    first = s
+    t0.record()
+    for _ in range(args.steps):
+        step(s); s += 1
+    t1.record()
+    torch.cuda.synchronize()
+    if sampler:
+        sampler.mark("timed_end")
+    ms = t0.elapsed_time(t1)
+    step_bytes = sum(bytes_of(i)[0] for i in range(first, first + args.steps))
+    for _ in range(e2e_warm):
+        step(s); s += 1
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    first_e = s
+    e0.record()
+    for _ in range(args.e2e_steps):
+        raw.copy_(raw_host, non_blocking=True)
+        raw_q.copy_(raw[:, :H]); raw_k.copy_(raw[:, H:])
+        step(s); s += 1
+        out_host.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    e1.record()
+    torch.cuda.synchronize()
+    e2e_ms = e0.elapsed_time(e1)
+    e2e_bytes = sum(bytes_of(i)[0] for i in range(first_e, first_e + args.e2e_steps))
+    p0 = s
+    for _ in range(probe):
+        step(s, events=True); s += 1
+    torch.cuda.synchronize()
+    attn_ms = statistics.mean(ev0[i].elapsed_ms(ev1[i]) for i in range(p0 + 3, p0 + probe))
+    attn_bytes = statistics.mean(bytes_of(i)[1] for i in range(p0 + 3, p0 + probe))
+    clocks = None
+    if sampler:
+        sampler.mark("load_end")
+        clocks = sampler.stop()
+    peaks_path = REPO / "MEASURED_PEAKS.json"
+    peak = float(json.loads(peaks_path.read_text())["hbm_gbs"]) if peaks_path.exists() else 6650.0
+    value = step_bytes / (ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16 (tensor-core QK^T and P*V, fp32 accumulate and softmax)", "data": "synthetic",
+        "config": {"workload": "next row, not a BASELINE config: reference-native global geometry, 16 Q / 1 KV / "
+                               "head_dim 512, rotary 128, V from raw K; ragged batch, permuted 16-token pages",
+                   "sequences": B, "ctx_range": [args.min_ctx, args.max_ctx], "seed": args.seed,
+                   "l2": "inputs larger than L2" if step_bytes / args.steps > 2.6e8 else "step smaller than 2x L2",
+                   "launch": "append + attention + combine, programmatic dependent launch"},
+        "us_per_layer_step": ms * 1e3 / args.steps, "frac_of_hbm_peak": value / peak,
+        "roofline": {"bound": "hbm", "kernel": "decode_gqa16_kernel + combine", "achieved": attn_bytes / (attn_ms * 1e-3) / 1e9,
+                     "peak": peak, "unit": "GB/s", "frac": attn_bytes / (attn_ms * 1e-3) / 1e9 / peak, "traffic": None,
+                     "algorithmic_bytes_per_launch": attn_bytes, "avg_launch_ms": attn_ms},
+        "e2e": {"value": e2e_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
+                "h2d_bytes_per_step": int(raw_host.numel() * 2), "d2h_bytes_per_step": int(out_host.numel() * 2)},
+        "gpu_launches": 3 * args.steps, "device_status": int(status[0].item()), "clocks": clocks,
+    }))
+
+
 # --------------------------------------------------------------------------- main arm
 def main():
     args = parse_args()
@@ -686,6 +822,11 @@ def main():
     kv.load_library(build_if_missing=False)
     sampler = ClockSampler(local_rank) if rank == 0 else None   # started early: nvidia-smi takes a second to come up
 
+    if args.workload == "native_global":
+        if world > 1:
+            raise SystemExit("--workload native_global is a one-GPU line")
+        run_native_global(args, kv, torch, sampler)
+        return
     spec, ctx_all, ctx, parallelism, scaling = plan_workload(args, world, rank)
     if args.emulate_world > 1 and world == 1 and args.workload in ("cfg3", "cfg5"):
         ctx = ctx_all[shard_sequences(ctx_all, args.emulate_world)[args.emulate_rank]]

@@ -10,8 +10,8 @@
 // Same partition, scratch layout, combine and programmatic-launch rules as
 // decode_balanced.cu (balanced_partition.cuh). Per CTA: one producer warp and
 // four consumer warps; a stage is 16 keys (K rows then V rows, 1 KiB each,
-// copied row by row into rows padded to 1040 bytes so that the 8 rows of an
-// ldmatrix tile fall into different banks).
+// copied in pairs of rows with 16 bytes of padding after each pair, see
+// Gqa16Traits).
 //   scores: warp w contracts dims [128 w, 128 w + 128) for all 16 keys (16
 //           MMAs), the four partial 16 x 16 tiles are summed through shared
 //           memory (one named barrier per stage, double-buffered);
@@ -36,18 +36,29 @@ struct Gqa16Traits {
   static constexpr int kCtasPerSm = 2;
   static constexpr int kStageTokens = 16;
   static constexpr int kRowBytes = D * 2;             // one key, the one head
-  static constexpr int kRowStride = kRowBytes + 16;   // padded row in the stage
-  static constexpr int kStageTensorBytes = kStageTokens * kRowStride;
+  // Rows sit in the stage in pairs: 2 KiB contiguous (one bulk copy when both
+  // rows are wanted), then 16 bytes of padding. The 8 rows of an ldmatrix tile
+  // then fall into 4 bank groups (2-way conflict) instead of 1 (8-way); single
+  // padded rows would be conflict-free but need twice the bulk copies, and the
+  // copy engine's rate per copy, not the banks, is what limits this kernel.
+  static constexpr int kPairStride = 2 * kRowBytes + 16;
+  static constexpr int kStageTensorBytes = (kStageTokens / 2) * kPairStride;
   static constexpr int kStageBytes = 2 * kStageTensorBytes;  // K then V
   static constexpr int kMetaBytes = 256;
   static constexpr int kRingBytes = kStages * kStageBytes + kMetaBytes;
-  // partial score tiles: [buffer][warp][lane][8 floats]
+  // partial score tiles: [buffer][warp][key half][lane][4 floats]
   static constexpr int kExchangeBytes = 2 * kConsumerWarps * 32 * 8 * 4;
   static constexpr int kMaxBatch = 256;
   static constexpr int kSmem =
       kRingBytes + kExchangeBytes + (2 * kMaxBatch + 1) * 4 + 16;
   static constexpr int kDimsPerWarp = D / kConsumerWarps;  // 128
 };
+
+// Byte offset of key row `key` inside a stage's K (or V) rows.
+__device__ __forceinline__ uint32_t gqa16_row_offset(int key) {
+  return uint32_t(key >> 1) * Gqa16Traits::kPairStride +
+         uint32_t(key & 1) * Gqa16Traits::kRowBytes;
+}
 
 __device__ __forceinline__ void mma_bf16_m16n8k16(float (&d)[4], uint32_t a0,
                                                   uint32_t a1, uint32_t a2,
@@ -117,8 +128,10 @@ struct Gqa16Ring {
   }
 };
 
-// Producer warp: lane i < 16 owns key base + i of the stage: resolves its page
-// and copies its K row and its V row (1 KiB each) into the padded stage.
+// Producer warp: lane i < 16 resolves the page of key base + i of the stage;
+// an even lane whose neighbour's row is wanted too and follows it in memory
+// copies both rows (K and V, 2 KiB each) at once, otherwise every wanted row
+// is copied by its own lane (1 KiB each).
 __device__ __forceinline__ void gqa16_fill_stage(const Gqa16Ring &ring,
                                                  const BalancedParams &p,
                                                  int batch, int base, int c0,
@@ -127,7 +140,7 @@ __device__ __forceinline__ void gqa16_fill_stage(const Gqa16Ring &ring,
   using T = Gqa16Traits;
   const Gemma4KvCacheConfig &cfg = p.cfg;
   const int pos = base + lane;
-  int64_t off = -1;
+  long long off = -1;
   if (lane < T::kStageTokens && pos >= c0 && pos < c1) {
     const int lp = pos / cfg.page_size;
     const int slot = lp % cfg.max_pages_per_seq;
@@ -138,6 +151,11 @@ __device__ __forceinline__ void gqa16_fill_stage(const Gqa16Ring &ring,
     }
   }
   const uint32_t mask = __ballot_sync(0xffffffffu, off >= 0);
+  const long long next_off = __shfl_down_sync(0xffffffffu, off, 1);
+  const long long prev_off = __shfl_up_sync(0xffffffffu, off, 1);
+  const bool pair_head =
+      (lane & 1) == 0 && off >= 0 && next_off == off + T::D;
+  const bool pair_tail = (lane & 1) == 1 && off >= 0 && prev_off == off - T::D;
   if (lane == 0) {
     ring.masks()[stage] = mask;
     if (mask != 0u) {
@@ -148,14 +166,14 @@ __device__ __forceinline__ void gqa16_fill_stage(const Gqa16Ring &ring,
     }
   }
   __syncwarp();
-  if (off >= 0) {
-    const uint32_t dst = ring.k_stage(stage) + uint32_t(lane) * T::kRowStride;
-    bulk_load_hint(dst,
-                   static_cast<const __nv_bfloat16 *>(p.cache_k) + off,
-                   T::kRowBytes, ring.full_bar(stage), policy);
+  if (off >= 0 && !pair_tail) {
+    const uint32_t bytes = pair_head ? 2u * T::kRowBytes : uint32_t(T::kRowBytes);
+    const uint32_t dst = ring.k_stage(stage) + gqa16_row_offset(lane);
+    bulk_load_hint(dst, static_cast<const __nv_bfloat16 *>(p.cache_k) + off,
+                   bytes, ring.full_bar(stage), policy);
     bulk_load_hint(dst + T::kStageTensorBytes,
-                   static_cast<const __nv_bfloat16 *>(p.cache_v) + off,
-                   T::kRowBytes, ring.full_bar(stage), policy);
+                   static_cast<const __nv_bfloat16 *>(p.cache_v) + off, bytes,
+                   ring.full_bar(stage), policy);
   }
 }
 
@@ -250,9 +268,9 @@ decode_gqa16_kernel(BalancedParams p) {
   const int dim0 = warp * T::kDimsPerWarp;
   // ldmatrix row addresses of this lane, relative to a stage's K (V) rows
   const uint32_t k_lane_off =
-      uint32_t(lane & 7) * T::kRowStride + uint32_t(dim0 + 8 * (lane >> 3)) * 2u;
+      gqa16_row_offset(lane & 7) + uint32_t(dim0 + 8 * (lane >> 3)) * 2u;
   const uint32_t v_lane_off =
-      uint32_t((lane & 7) + 8 * ((lane >> 3) & 1)) * T::kRowStride +
+      gqa16_row_offset((lane & 7) + 8 * ((lane >> 3) & 1)) +
       uint32_t(dim0 + 8 * (lane >> 4)) * 2u;
 
   int b = b_start, flat = r0;
@@ -302,8 +320,8 @@ decode_gqa16_kernel(BalancedParams p) {
 #pragma unroll
           for (int s2 = 0; s2 < 4; ++s2) {
             uint32_t kb[4];
-            ldmatrix_x4(kb, k_base + uint32_t(8 * j) * T::kRowStride +
-                                k_lane_off + uint32_t(32 * s2) * 2u);
+            ldmatrix_x4(kb, k_base + gqa16_row_offset(8 * j) + k_lane_off +
+                                uint32_t(32 * s2) * 2u);
             mma_bf16_m16n8k16(sc[j], qa[2 * s2][0], qa[2 * s2][1],
                               qa[2 * s2][2], qa[2 * s2][3], kb[0], kb[1]);
             mma_bf16_m16n8k16(sc[j], qa[2 * s2 + 1][0], qa[2 * s2 + 1][1],
@@ -317,9 +335,9 @@ decode_gqa16_kernel(BalancedParams p) {
         // previous contents)
         float *xw = exchange + ((exchanges & 1) * T::kConsumerWarps) * 256;
         ++exchanges;
-        reinterpret_cast<float4 *>(xw + warp * 256)[lane * 2] =
+        reinterpret_cast<float4 *>(xw + warp * 256)[lane] =
             make_float4(sc[0][0], sc[0][1], sc[0][2], sc[0][3]);
-        reinterpret_cast<float4 *>(xw + warp * 256)[lane * 2 + 1] =
+        reinterpret_cast<float4 *>(xw + warp * 256)[32 + lane] =
             make_float4(sc[1][0], sc[1][1], sc[1][2], sc[1][3]);
         consumer_barrier();
         if (*ring.abort_flag() != 0) {
@@ -335,9 +353,9 @@ decode_gqa16_kernel(BalancedParams p) {
         }
 #pragma unroll
         for (int w = 0; w < T::kConsumerWarps; ++w) {
-          const float4 u0 = reinterpret_cast<const float4 *>(xw + w * 256)[lane * 2];
+          const float4 u0 = reinterpret_cast<const float4 *>(xw + w * 256)[lane];
           const float4 u1 =
-              reinterpret_cast<const float4 *>(xw + w * 256)[lane * 2 + 1];
+              reinterpret_cast<const float4 *>(xw + w * 256)[32 + lane];
           sc[0][0] += u0.x; sc[0][1] += u0.y; sc[0][2] += u0.z; sc[0][3] += u0.w;
           sc[1][0] += u1.x; sc[1][1] += u1.y; sc[1][2] += u1.z; sc[1][3] += u1.w;
         }
@@ -400,7 +418,7 @@ decode_gqa16_kernel(BalancedParams p) {
             if (((mask >> key) & 1u) == 0u && lane < 16) {
               reinterpret_cast<uint4 *>(smem + stage * T::kStageBytes +
                                         T::kStageTensorBytes +
-                                        key * T::kRowStride + dim0 * 2)[lane] =
+                                        gqa16_row_offset(key) + dim0 * 2)[lane] =
                   make_uint4(0u, 0u, 0u, 0u);
             }
           }
@@ -476,7 +494,7 @@ cudaError_t decode_attention_gqa16_bf16(const DecodeArgs &a,
     return cudaErrorInvalidValue;
   }
   static_assert(2 * (T::kSmem + 1024 + 256) <= 228 * 1024, "two CTAs per SM");
-  static_assert(T::kRingBytes % 16 == 0 && T::kRowStride % 16 == 0, "alignment");
+  static_assert(T::kRingBytes % 16 == 0 && T::kPairStride % 16 == 0, "alignment");
   BalancedParams p = {};
   p.out = a.out;
   p.lse = a.lse;
