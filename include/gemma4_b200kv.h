@@ -253,8 +253,10 @@ int b200kv_decode_append_bf16(b200kv_bf16 *d_q_prepared,
  * a fixed grid of two CTAs per SM, whatever the individual lengths, so ragged
  * batches leave no SM idle. num_splits then only states how large the scratch
  * is (still batch * q_heads * num_splits rows; use b200kv_plan_balanced).
- * Available for 8 KV heads x 256 with 16 query heads and batch <= 1024;
- * cudaErrorInvalidValue otherwise.
+ * Available for 8 KV heads x 256 with 16 query heads and batch <= 1024, and
+ * for the reference's native global-layer geometry, 1 KV head x 512 with 16
+ * query heads and batch <= 256 (src/gemma4_flash_attention_decode.cu:150-157;
+ * this geometry has no fixed-split form here); cudaErrorInvalidValue otherwise.
  *
  * Ordering: the call may follow b200kv_decode_append_* on the same stream
  * with nothing in between (as b200kv_decode_layer_step_bf16 does). The
