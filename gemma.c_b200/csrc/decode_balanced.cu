@@ -200,6 +200,10 @@ __global__ __launch_bounds__(T::kThreads, T::kCtasPerSm) void decode_balanced_ke
   // "everything before it is complete".
   if constexpr (!kFused) pdl_release_successor();
 
+  // The barriers are initialised under the scan's first load; its barriers
+  // make them visible to the CTA.
+  const Ring<T> ring(smem);
+  if (threadIdx.x == 0) ring.init_barriers();
   scan_live_keys<kMaxBatch>(p, s_prefix, s_first, s_warp_sums);
   const int total = s_prefix[p.batch_count];
   const int width = range_width(max(total, 1), p.num_ctas, ST);
@@ -230,10 +234,6 @@ __global__ __launch_bounds__(T::kThreads, T::kCtasPerSm) void decode_balanced_ke
     }
     b_start = lo;
   }
-
-  const Ring<T> ring(smem);
-  if (threadIdx.x == 0) ring.init_barriers();
-  __syncthreads();
 
   if (warp == T::kConsumerWarps) {
     // ------------------------------ producer ------------------------------

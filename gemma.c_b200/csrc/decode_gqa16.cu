@@ -199,6 +199,9 @@ decode_gqa16_kernel(BalancedParams p) {
   // CTA waits before it exits.
   pdl_release_successor();
 
+  // initialised under the scan's first load; its barriers publish them
+  const Gqa16Ring ring(smem);
+  if (threadIdx.x == 0) ring.init();
   scan_live_keys<T::kMaxBatch>(p, s_prefix, s_first, s_warp_sums);
   const int total = s_prefix[p.batch_count];
   const int width = range_width(max(total, 1), p.num_ctas, ST);
@@ -217,10 +220,6 @@ decode_gqa16_kernel(BalancedParams p) {
     }
     b_start = lo;
   }
-
-  const Gqa16Ring ring(smem);
-  if (threadIdx.x == 0) ring.init();
-  __syncthreads();
 
   if (warp == T::kConsumerWarps) {
     // ------------------------------ producer ------------------------------

@@ -199,7 +199,7 @@ __global__ void decode_append_fp8_kernel(Fp8AppendArgs args) {
   const int64_t scale_index =
       (int64_t(a.cache_layer) * c.num_pages + physical) * c.num_heads + kv_head;
 
-  __nv_bfloat16 y[D / 32];
+  __nv_bfloat16 y[D / 32] = {};
   auto from_registers = [&y](int, int j) { return __bfloat162float(y[j]); };
   if (warp == G) {
     prep_weighted_rope_values<D, ROT, kIeee>(y, x, a.k_norm_weight, cos_row,
