@@ -23,47 +23,90 @@ namespace {
 
 namespace ref = gemma4_flash_attention;
 using Sliding = ref::Gemma4AttentionTraits<false>;   // 8 KV heads x 256, rotary 256, own V projection
+using Global = ref::Gemma4AttentionTraits<true>;     // 1 KV head x 512, rotary 128, V derived from raw K
 constexpr int kThreads = ref::kDecodeMegaThreads;    // 512, the block size the phases run with in the product
 
+template <class Traits>
 __global__ __launch_bounds__(kThreads) void ref_append_kernel(
     __nv_bfloat16 *q_prepared, __nv_bfloat16 *cache_k, __nv_bfloat16 *cache_v, Gemma4KvCacheConfig cfg,
     const int32_t *page_table, const int32_t *token_position, int cache_layer, const __nv_bfloat16 *q,
     const __nv_bfloat16 *k, const __nv_bfloat16 *v, const __nv_bfloat16 *q_w, const __nv_bfloat16 *k_w,
     const float *cos, const float *sin) {
-  ref::phase_decode_q_paged_kv_norm_rope<Sliding>(q_prepared, cache_k, cache_v, cfg, page_table, token_position,
-                                                  cache_layer, q, k, v, q_w, k_w, cos, sin, int(blockIdx.x),
-                                                  int(blockIdx.y), int(threadIdx.x));
+  ref::phase_decode_q_paged_kv_norm_rope<Traits>(q_prepared, cache_k, cache_v, cfg, page_table, token_position,
+                                                 cache_layer, q, k, v, q_w, k_w, cos, sin, int(blockIdx.x),
+                                                 int(blockIdx.y), int(threadIdx.x));
 }
 
+template <class Traits>
 __global__ __launch_bounds__(kThreads) void ref_split_kernel(
     __nv_bfloat16 *out, float *pm, float *pl, float *pacc, const __nv_bfloat16 *q, const __nv_bfloat16 *cache_k,
     const __nv_bfloat16 *cache_v, const int32_t *page_table, const int32_t *seq_lengths, Gemma4KvCacheConfig cfg,
     int32_t layer, float scale, int32_t split_size, int32_t num_splits, int32_t batch_count) {
-  ref::phase_decode_paged_grouped_split<Sliding, kThreads>(out, pm, pl, pacc, q, cache_k, cache_v, page_table,
-                                                           seq_lengths, cfg, layer, scale, split_size, num_splits,
-                                                           int(blockIdx.x), int(blockIdx.y), int(blockIdx.z),
-                                                           int(threadIdx.x), batch_count);
+  ref::phase_decode_paged_grouped_split<Traits, kThreads>(out, pm, pl, pacc, q, cache_k, cache_v, page_table,
+                                                          seq_lengths, cfg, layer, scale, split_size, num_splits,
+                                                          int(blockIdx.x), int(blockIdx.y), int(blockIdx.z),
+                                                          int(threadIdx.x), batch_count);
 }
 
+template <class Traits>
 __global__ __launch_bounds__(kThreads) void ref_reduce_kernel(
     __nv_bfloat16 *out, const float *pm, const float *pl, const float *pacc, const int32_t *seq_lengths,
     Gemma4KvCacheConfig cfg, int32_t split_size, int32_t num_splits) {
-  ref::phase_decode_paged_reduce<Sliding, kThreads>(out, pm, pl, pacc, seq_lengths, cfg, split_size, num_splits,
-                                                    int(blockIdx.x), int(blockIdx.y), int(threadIdx.x),
-                                                    int(blockDim.x));
+  ref::phase_decode_paged_reduce<Traits, kThreads>(out, pm, pl, pacc, seq_lengths, cfg, split_size, num_splits,
+                                                   int(blockIdx.x), int(blockIdx.y), int(threadIdx.x),
+                                                   int(blockDim.x));
+}
+
+template <class Traits>
+bool geometry_is(const Gemma4KvCacheConfig &cfg) {
+  return cfg.num_heads == Traits::kKvHeads && cfg.head_dim == Traits::kHeadDim;
+}
+
+template <class Traits>
+int run_append(__nv_bfloat16 *q_prepared, __nv_bfloat16 *cache_k, __nv_bfloat16 *cache_v,
+               Gemma4KvCacheConfig cfg, const int32_t *page_table, const int32_t *token_position,
+               int cache_layer, const __nv_bfloat16 *q, const __nv_bfloat16 *k, const __nv_bfloat16 *v,
+               const __nv_bfloat16 *q_w, const __nv_bfloat16 *k_w, const float *cos, const float *sin,
+               int batch_count, cudaStream_t stream) {
+  ref_append_kernel<Traits><<<dim3(batch_count, Traits::kKvHeads), kThreads, 0, stream>>>(
+      q_prepared, cache_k, cache_v, cfg, page_table, token_position, cache_layer, q, k, v, q_w, k_w, cos, sin);
+  return cudaGetLastError();
+}
+
+template <class Traits>
+int run_attention(__nv_bfloat16 *out, float *pm, float *pl, float *pacc, const __nv_bfloat16 *q,
+                  const __nv_bfloat16 *cache_k, const __nv_bfloat16 *cache_v, const int32_t *page_table,
+                  const int32_t *seq_lengths, Gemma4KvCacheConfig cfg, int32_t layer, float scale,
+                  int32_t split_size, int32_t num_splits, int32_t batch_count, cudaStream_t stream) {
+  if (num_splits > 65535) return cudaErrorInvalidValue;
+  ref_split_kernel<Traits><<<dim3(batch_count, Traits::kKvHeads, num_splits), kThreads, 0, stream>>>(
+      out, pm, pl, pacc, q, cache_k, cache_v, page_table, seq_lengths, cfg, layer, scale, split_size, num_splits,
+      batch_count);
+  cudaError_t st = cudaGetLastError();
+  if (st != cudaSuccess || num_splits == 1) return st;
+  ref_reduce_kernel<Traits><<<dim3(batch_count, GEMMA4_NUM_QUERY_HEADS), kThreads, 0, stream>>>(
+      out, pm, pl, pacc, seq_lengths, cfg, split_size, num_splits);
+  return cudaGetLastError();
 }
 
 }  // namespace
 
+// Both entry points pick the reference's traits from the cache geometry: 8 KV heads x 256 (sliding) or
+// 1 KV head x 512 (global; `v` is ignored there, the phase derives V from raw K).
 extern "C" int ref_decode_append(__nv_bfloat16 *q_prepared, __nv_bfloat16 *cache_k, __nv_bfloat16 *cache_v,
                                  Gemma4KvCacheConfig cfg, const int32_t *page_table, const int32_t *token_position,
                                  int cache_layer, const __nv_bfloat16 *q, const __nv_bfloat16 *k,
                                  const __nv_bfloat16 *v, const __nv_bfloat16 *q_w, const __nv_bfloat16 *k_w,
                                  const float *cos, const float *sin, int batch_count, cudaStream_t stream) {
-  if (cfg.num_heads != Sliding::kKvHeads || cfg.head_dim != Sliding::kHeadDim) return cudaErrorInvalidValue;
-  ref_append_kernel<<<dim3(batch_count, Sliding::kKvHeads), kThreads, 0, stream>>>(
-      q_prepared, cache_k, cache_v, cfg, page_table, token_position, cache_layer, q, k, v, q_w, k_w, cos, sin);
-  return cudaGetLastError();
+  if (geometry_is<Sliding>(cfg)) {
+    return run_append<Sliding>(q_prepared, cache_k, cache_v, cfg, page_table, token_position, cache_layer, q, k, v,
+                               q_w, k_w, cos, sin, batch_count, stream);
+  }
+  if (geometry_is<Global>(cfg)) {
+    return run_append<Global>(q_prepared, cache_k, cache_v, cfg, page_table, token_position, cache_layer, q, k, v,
+                              q_w, k_w, cos, sin, batch_count, stream);
+  }
+  return cudaErrorInvalidValue;
 }
 
 extern "C" int ref_decode_attention(__nv_bfloat16 *out, float *pm, float *pl, float *pacc, const __nv_bfloat16 *q,
@@ -71,14 +114,13 @@ extern "C" int ref_decode_attention(__nv_bfloat16 *out, float *pm, float *pl, fl
                                     const int32_t *page_table, const int32_t *seq_lengths, Gemma4KvCacheConfig cfg,
                                     int32_t layer, float scale, int32_t split_size, int32_t num_splits,
                                     int32_t batch_count, cudaStream_t stream) {
-  if (cfg.num_heads != Sliding::kKvHeads || cfg.head_dim != Sliding::kHeadDim) return cudaErrorInvalidValue;
-  if (num_splits > 65535) return cudaErrorInvalidValue;
-  ref_split_kernel<<<dim3(batch_count, Sliding::kKvHeads, num_splits), kThreads, 0, stream>>>(
-      out, pm, pl, pacc, q, cache_k, cache_v, page_table, seq_lengths, cfg, layer, scale, split_size, num_splits,
-      batch_count);
-  cudaError_t st = cudaGetLastError();
-  if (st != cudaSuccess || num_splits == 1) return st;
-  ref_reduce_kernel<<<dim3(batch_count, GEMMA4_NUM_QUERY_HEADS), kThreads, 0, stream>>>(
-      out, pm, pl, pacc, seq_lengths, cfg, split_size, num_splits);
-  return cudaGetLastError();
+  if (geometry_is<Sliding>(cfg)) {
+    return run_attention<Sliding>(out, pm, pl, pacc, q, cache_k, cache_v, page_table, seq_lengths, cfg, layer, scale,
+                                  split_size, num_splits, batch_count, stream);
+  }
+  if (geometry_is<Global>(cfg)) {
+    return run_attention<Global>(out, pm, pl, pacc, q, cache_k, cache_v, page_table, seq_lengths, cfg, layer, scale,
+                                 split_size, num_splits, batch_count, stream);
+  }
+  return cudaErrorInvalidValue;
 }

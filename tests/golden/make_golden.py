@@ -32,7 +32,7 @@ def record_append(name, out_dir):
     cv = torch.zeros(elems, dtype=torch.int16, device="cuda")
     qp = torch.zeros(case.q.shape, dtype=torch.int16, device="cuda")
     rc = ref.decode_append(qp, ck, cv, cfg, dev(case.page_table), dev(case.token_position), case.layer, dev(case.q),
-                           dev(case.k), dev(case.v), dev(case.q_w), dev(case.k_w), dev(case.cos), dev(case.sin),
+                           dev(case.k), None if case.v is None else dev(case.v), dev(case.q_w), dev(case.k_w), dev(case.cos), dev(case.sin),
                            case.token_position.size)
     torch.cuda.synchronize()
     assert rc == 0, rc
@@ -73,9 +73,9 @@ def main():
     out_dir = Path(sys.argv[1]) if len(sys.argv) > 1 else REPO / "gpurun_out" / "golden"
     out_dir.mkdir(parents=True, exist_ok=True)
     assert ref.available(), "oracle/_ref/libgemma4_ref.so is missing: run oracle/build_ref.sh where the sources are"
-    for name in gc.APPEND:
+    for name in gc.APPEND_ALL:
         record_append(name, out_dir)
-    for name in gc.ATTENTION:
+    for name in gc.ATTENTION_ALL:
         record_attention(name, out_dir)
 
 

@@ -30,17 +30,41 @@ ATTENTION = {
 }
 
 
+# The reference's native global-layer geometry (src/gemma4.h:19-21,28): 16 query heads on one KV head of
+# 512 dims, rotary on the first 128 dims, V = scale-free norm of raw K (no V projection).
+GEOM_GLOBAL = dict(kv_heads=1, q_heads=16, head_dim=512)
+
+APPEND_GLOBAL = {
+    "append_global_linear_batch": dict(seed=9201, positions=[0, 15, 16, 4095], window=0, theta=1e6),
+    "append_global_page64": dict(seed=9202, positions=[63, 64, 200], window=0, page_size=64, theta=1e6),
+}
+
+ATTENTION_GLOBAL = {
+    "attn_global_4096_page64_split64": (dict(seed=9301, seq_lens=[4096], window=0, page_size=64), 64, 64),
+    "attn_global_mixed_batch": (dict(seed=9302, seq_lens=[300, 17, 1, 129, 700], window=0), 37, 25),
+    "attn_global_outliers": (dict(seed=9303, seq_lens=[3000], window=0, outlier_frac=0.01), 128, 24),
+}
+
+APPEND_ALL = list(APPEND) + list(APPEND_GLOBAL)
+ATTENTION_ALL = list(ATTENTION) + list(ATTENTION_GLOBAL)
+
+
 def build_append(name):
+    if name in APPEND_GLOBAL:
+        kw = dict(APPEND_GLOBAL[name])
+        seed = kw.pop("seed")
+        return make_append_case(seed, **kw, **GEOM_GLOBAL, rotary_dim=128, has_v=False)
     kw = dict(APPEND[name])
     seed = kw.pop("seed")
     return make_append_case(seed, **kw, **GEOM)
 
 
 def build_attention(name):
-    kw, split_size, num_splits = ATTENTION[name]
+    table, geom = (ATTENTION_GLOBAL, GEOM_GLOBAL) if name in ATTENTION_GLOBAL else (ATTENTION, GEOM)
+    kw, split_size, num_splits = table[name]
     kw = dict(kw)
     seed = kw.pop("seed")
-    return make_attn_case(seed, **kw, **GEOM), split_size, num_splits
+    return make_attn_case(seed, **kw, **geom), split_size, num_splits
 
 
 def digest(*arrays) -> str:

@@ -17,7 +17,7 @@ from tests import golden_cases as gc
 from tests.helpers import ATTN_MAX_ABS, ATTN_MAX_REL, attention_error
 
 GOLDEN = Path(__file__).resolve().parent / "golden"
-have_golden = all((GOLDEN / f"{n}.npz").exists() for n in list(gc.APPEND) + list(gc.ATTENTION))
+have_golden = all((GOLDEN / f"{n}.npz").exists() for n in gc.APPEND_ALL + gc.ATTENTION_ALL)
 need_golden = pytest.mark.skipif(not have_golden, reason="golden fixtures not recorded yet")
 
 # The reference's attention accumulates in fp32 with __expf and block-wide tree sums; the oracle restates
@@ -34,7 +34,7 @@ def _ulp_close(orc, got_u16, want_u16, max_fraction):
 
 
 @need_golden
-@pytest.mark.parametrize("name", list(gc.APPEND))
+@pytest.mark.parametrize("name", gc.APPEND_ALL)
 def test_oracle_append_against_reference_kernel_output(orc, name):
     """IEEE 1/sqrt on the host vs rsqrt.approx on the GPU: identical except for rare one-step differences."""
     g = np.load(GOLDEN / f"{name}.npz")
@@ -58,7 +58,7 @@ def test_oracle_append_against_reference_kernel_output(orc, name):
 
 
 @need_golden
-@pytest.mark.parametrize("name", list(gc.ATTENTION))
+@pytest.mark.parametrize("name", gc.ATTENTION_ALL)
 def test_oracle_attention_against_reference_kernel_output(orc, name):
     g = np.load(GOLDEN / f"{name}.npz")
     case, split_size, num_splits = gc.build_attention(name)
@@ -84,14 +84,14 @@ def _device_append(kv, case, mode):
     cv = torch.zeros_like(ck)
     qp = torch.zeros(case.q.shape, dtype=torch.int16, device="cuda")
     kv.decode_append(qp, ck, cv, cfg, dev(case.page_table), dev(case.token_position), case.layer, dev(case.q),
-                     dev(case.k), dev(case.v), dev(case.q_w), dev(case.k_w), dev(case.cos), dev(case.sin),
-                     case.token_position.size, case.q_heads, case.rotary_dim, mode)
+                     dev(case.k), None if case.v is None else dev(case.v), dev(case.q_w), dev(case.k_w),
+                     dev(case.cos), dev(case.sin), case.token_position.size, case.q_heads, case.rotary_dim, mode)
     torch.cuda.synchronize()
     return host_u16(qp), host_u16(ck), host_u16(cv), (qp, ck, cv)
 
 
 @need_golden
-@pytest.mark.parametrize("name", list(gc.APPEND))
+@pytest.mark.parametrize("name", gc.APPEND_ALL)
 @pytest.mark.gpu
 @pytest.mark.skipif(not torch.cuda.is_available(), reason="needs a CUDA device")
 def test_product_append_bit_exact_with_reference_kernel_output(kv, orc, name):
@@ -112,7 +112,7 @@ def test_product_append_bit_exact_with_reference_kernel_output(kv, orc, name):
 
 
 @need_golden
-@pytest.mark.parametrize("name", list(gc.ATTENTION))
+@pytest.mark.parametrize("name", gc.ATTENTION_ALL)
 @pytest.mark.gpu
 @pytest.mark.skipif(not torch.cuda.is_available(), reason="needs a CUDA device")
 def test_product_attention_against_reference_kernel_output(kv, orc, name):
@@ -122,6 +122,9 @@ def test_product_attention_against_reference_kernel_output(kv, orc, name):
     assert gc.attention_digest(case) == str(g["digest"])
     cfg = kv.make_kv_config(*case.cfg)
     B, H, D = case.batch, case.q_heads, case.head_dim
+    if name in gc.ATTENTION_GLOBAL:      # this geometry runs on the balanced partition only
+        split_size = 0
+        num_splits = kv.plan_balanced(B, torch.cuda.get_device_properties(0).multi_processor_count)
     out = torch.zeros((B, H, D), dtype=torch.int16, device="cuda")
     rows = B * H * num_splits
     pm = torch.zeros(rows, dtype=torch.float32, device="cuda"); pl = torch.zeros_like(pm)
