@@ -2,7 +2,7 @@
 """Records golden vectors from the reference's own CUDA kernels (oracle/_ref/libgemma4_ref.so, built
 from the gemma.c sources by oracle/build_ref.sh) on a CUDA device.
 
-    python tests/golden/make_golden.py [output_dir]      # default: gpurun_out/golden
+    python tests/golden/make_golden.py [output_dir]      # default: tests/golden/_recorded
 
 Writes one small .npz per case of tests/golden_cases.py: the outputs only (prepared q, the appended
 cache rows, attention rows), plus a digest of the seeded inputs. Copy the files into tests/golden/.
@@ -70,7 +70,7 @@ def record_attention(name, out_dir):
 
 
 def main():
-    out_dir = Path(sys.argv[1]) if len(sys.argv) > 1 else REPO / "gpurun_out" / "golden"
+    out_dir = Path(sys.argv[1]) if len(sys.argv) > 1 else REPO / "tests" / "golden" / "_recorded"
     out_dir.mkdir(parents=True, exist_ok=True)
     assert ref.available(), "oracle/_ref/libgemma4_ref.so is missing: run oracle/build_ref.sh where the sources are"
     for name in gc.APPEND_ALL:
