@@ -659,6 +659,14 @@ def workload_config(args, world, where, parallelism=None, layers=None):
     return cfg
 
 
+def step_stats(marks) -> dict:
+    """Distribution of the per-step device times between consecutive events of the timed region."""
+    ms = np.array([marks[i].elapsed_time(marks[i + 1]) for i in range(len(marks) - 1)], dtype=np.float64)
+    q = lambda p: float(np.percentile(ms, p))
+    return {"median": q(50), "min": float(ms.min()), "max": float(ms.max()), "p95": q(95), "p99": q(99),
+            "iqr": q(75) - q(25), "samples": int(ms.size)}
+
+
 # --------------------------------------------------------------------------- next row: native global geometry
 def run_native_global(args, kv, torch, sampler):
     """Extra line (not a BASELINE config): the reference's native global-layer geometry, 16 query heads on
@@ -736,16 +744,16 @@ def run_native_global(args, kv, torch, sampler):
     torch.cuda.synchronize()
     if sampler:
         sampler.mark("timed_begin")
-    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
     first = s
-    t0.record()
-    for _ in range(args.steps):
+    marks[0].record()
+    for i in range(args.steps):
         step(s); s += 1
-    t1.record()
+        marks[i + 1].record()
     torch.cuda.synchronize()
     if sampler:
         sampler.mark("timed_end")
-    ms = t0.elapsed_time(t1)
+    ms = marks[0].elapsed_time(marks[-1])
     step_bytes = sum(bytes_of(i)[0] for i in range(first, first + args.steps))
     for _ in range(e2e_warm):
         step(s); s += 1
@@ -786,6 +794,7 @@ def run_native_global(args, kv, torch, sampler):
                    "l2": "inputs larger than L2" if step_bytes / args.steps > 2.6e8 else "step smaller than 2x L2",
                    "launch": "append + attention + combine, programmatic dependent launch"},
         "us_per_layer_step": ms * 1e3 / args.steps, "frac_of_hbm_peak": value / peak,
+        "step_ms_stats": step_stats(marks),
         "roofline": {"bound": "hbm", "kernel": "decode_gqa16_kernel + combine", "achieved": attn_bytes / (attn_ms * 1e-3) / 1e9,
                      "peak": peak, "unit": "GB/s", "frac": attn_bytes / (attn_ms * 1e-3) / 1e9 / peak, "traffic": None,
                      "algorithmic_bytes_per_launch": attn_bytes, "avg_launch_ms": attn_ms},
@@ -853,17 +862,17 @@ def main():
     barrier()
     if sampler:
         sampler.mark("timed_begin")
-    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
     first_timed = s
-    t0.record()
-    for _ in range(args.steps):
+    marks[0].record()
+    for i in range(args.steps):
         wl.step(s)
         s += 1
-    t1.record()
+        marks[i + 1].record()
     barrier()
     if sampler:
         sampler.mark("timed_end")
-    elapsed_ms = t0.elapsed_time(t1)
+    elapsed_ms = marks[0].elapsed_time(marks[-1])
     step_bytes = sum(wl.bytes_for_step(i)[0] for i in range(first_timed, first_timed + args.steps))
     attn_bytes = statistics.mean(wl.bytes_for_step(i)[1] for i in range(first_timed, first_timed + args.steps))
     status = int(wl.status[0].item())
@@ -929,6 +938,7 @@ def main():
         "config": workload_config(args, world, "B200", parallelism, wl.L),
         "us_per_layer_step": elapsed_ms * 1e3 / layer_steps,
         "us_global_layer_attention": statistics.mean(attn_ms) * 1e3,
+        "step_ms_stats": step_stats(marks),
         "frac_of_hbm_peak": value / (peak * world),
         "roofline": {
             "bound": "hbm",
