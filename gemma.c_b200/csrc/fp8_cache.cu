@@ -83,29 +83,13 @@ __device__ __forceinline__ int64_t fp8_row_base(const Gemma4KvCacheConfig &c,
   }
 }
 
-// One warp stores `nrows` prepared rows of one (page, head, tensor) starting
-// at page offset o0; value(r, j) is element lane + 32*j of row r as fp32.
-// Applies the rule above, including the requantisation of the rows already in
-// the page.
-template <int D, bool kIsK, class RowValue>
-__device__ __forceinline__ void fp8_store_rows(uint8_t *cache, float *scale_slot,
-                                               const Gemma4KvCacheConfig &c,
-                                               int layer, int physical, int head,
-                                               int o0, int nrows, int lane,
-                                               RowValue value) {
-  float amax = 0.0f;
-  for (int r = 0; r < nrows; ++r) {
-#pragma unroll
-    for (int j = 0; j < D / 32; ++j) amax = fmaxf(amax, fabsf(value(r, j)));
-  }
-  amax = warp_max(amax);
-  float s_old = 0.0f;
-  if (o0 != 0) {
-    if (lane == 0) s_old = *scale_slot;
-    s_old = __shfl_sync(0xffffffffu, s_old, 0);
-  }
-  const float s_new = fmaxf(s_old, fmaxf(__fdiv_rn(amax, 448.0f), FLT_MIN));
-  if (s_new > s_old) {
+// Re-encodes the rows < o0 already stored in a page for a grown scale.
+template <int D, bool kIsK>
+__device__ __forceinline__ void fp8_requantise_rows(uint8_t *cache,
+                                                    const Gemma4KvCacheConfig &c,
+                                                    int layer, int physical,
+                                                    int head, int o0, float s_old,
+                                                    float s_new, int lane) {
     // A stored row is 256 contiguous bytes in either layout (K only permutes
     // the granules inside it) and the re-encoding is elementwise, so a lane
     // takes 8 bytes of each row; 8 rows are in flight at a time.
@@ -137,6 +121,33 @@ __device__ __forceinline__ void fp8_store_rows(uint8_t *cache, float *scale_slot
         }
       }
     }
+}
+
+// One warp stores `nrows` prepared rows of one (page, head, tensor) starting
+// at page offset o0; value(r, j) is element lane + 32*j of row r as fp32.
+// Applies the rule above, including the requantisation of the rows already in
+// the page.
+template <int D, bool kIsK, class RowValue>
+__device__ __forceinline__ void fp8_store_rows(uint8_t *cache, float *scale_slot,
+                                               const Gemma4KvCacheConfig &c,
+                                               int layer, int physical, int head,
+                                               int o0, int nrows, int lane,
+                                               RowValue value) {
+  float amax = 0.0f;
+  for (int r = 0; r < nrows; ++r) {
+#pragma unroll
+    for (int j = 0; j < D / 32; ++j) amax = fmaxf(amax, fabsf(value(r, j)));
+  }
+  amax = warp_max(amax);
+  float s_old = 0.0f;
+  if (o0 != 0) {
+    if (lane == 0) s_old = *scale_slot;
+    s_old = __shfl_sync(0xffffffffu, s_old, 0);
+  }
+  const float s_new = fmaxf(s_old, fmaxf(__fdiv_rn(amax, 448.0f), FLT_MIN));
+  if (s_new > s_old) {
+    fp8_requantise_rows<D, kIsK>(cache, c, layer, physical, head, o0, s_old, s_new,
+                                 lane);
   }
   for (int r = 0; r < nrows; ++r) {
 #pragma unroll
@@ -144,6 +155,78 @@ __device__ __forceinline__ void fp8_store_rows(uint8_t *cache, float *scale_slot
       cache[fp8_byte_index<kIsK>(c, layer, physical, o0 + r, head,
                                  lane + 32 * j)] =
           enc_e4m3(__fdiv_rn(value(r, j), s_new));
+    }
+  }
+  if (lane == 0) *scale_slot = s_new;
+}
+
+// The same rule for rows that come from memory (a prompt): row r of the call is
+// 256 bf16 at src + r * row_stride. A lane takes 8 contiguous elements of every
+// row (one 128-bit load, one 64-bit store); the rule is elementwise apart from
+// the maximum, so the bytes are those of fp8_store_rows.
+template <int D, bool kIsK>
+__device__ __forceinline__ void fp8_store_rows_from_memory(
+    uint8_t *cache, float *scale_slot, const Gemma4KvCacheConfig &c, int layer,
+    int physical, int head, int o0, int nrows, int lane,
+    const __nv_bfloat16 *src, int64_t row_stride) {
+  static_assert(D == 256, "a lane owns 8 of a row's 256 elements");
+  constexpr int kBatch = 8;
+  const uint4 *rows = reinterpret_cast<const uint4 *>(src) + lane;
+  const int64_t stride16 = row_stride / 8;
+  float amax = 0.0f;
+  for (int r0 = 0; r0 < nrows; r0 += kBatch) {
+    uint4 w[kBatch];
+#pragma unroll
+    for (int i = 0; i < kBatch; ++i) {
+      w[i] = r0 + i < nrows ? __ldg(rows + (r0 + i) * stride16)
+                            : make_uint4(0u, 0u, 0u, 0u);
+    }
+#pragma unroll
+    for (int i = 0; i < kBatch; ++i) {
+      const uint32_t u[4] = {w[i].x, w[i].y, w[i].z, w[i].w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        amax = fmaxf(amax, fmaxf(fabsf(bf16_lo(u[k])), fabsf(bf16_hi(u[k]))));
+      }
+    }
+  }
+  amax = warp_max(amax);
+  float s_old = 0.0f;
+  if (o0 != 0) {
+    if (lane == 0) s_old = *scale_slot;
+    s_old = __shfl_sync(0xffffffffu, s_old, 0);
+  }
+  const float s_new = fmaxf(s_old, fmaxf(__fdiv_rn(amax, 448.0f), FLT_MIN));
+  if (s_new > s_old) {
+    fp8_requantise_rows<D, kIsK>(cache, c, layer, physical, head, o0, s_old, s_new,
+                                 lane);
+  }
+  for (int r0 = 0; r0 < nrows; r0 += kBatch) {
+    uint4 w[kBatch];
+#pragma unroll
+    for (int i = 0; i < kBatch; ++i) {
+      w[i] = r0 + i < nrows ? __ldg(rows + (r0 + i) * stride16)
+                            : make_uint4(0u, 0u, 0u, 0u);
+    }
+#pragma unroll
+    for (int i = 0; i < kBatch; ++i) {
+      if (r0 + i < nrows) {
+        const int r = o0 + r0 + i;
+        const uint32_t u[4] = {w[i].x, w[i].y, w[i].z, w[i].w};
+        uint32_t out[2] = {0u, 0u};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const uint32_t lo = enc_e4m3(__fdiv_rn(bf16_lo(u[k]), s_new));
+          const uint32_t hi = enc_e4m3(__fdiv_rn(bf16_hi(u[k]), s_new));
+          out[k >> 1] |= (lo | (hi << 8)) << (16 * (k & 1));
+        }
+        // byte offset of elements 8 * lane .. + 7 inside the 256-byte row
+        const int granule = kIsK ? ((lane >> 1) ^ ((r & 1) << 2)) : (lane >> 1);
+        *reinterpret_cast<uint2 *>(cache +
+                                   fp8_row_base<kIsK>(c, layer, physical, r, head) +
+                                   granule * 16 + (lane & 1) * 8) =
+            make_uint2(out[0], out[1]);
+      }
     }
   }
   if (lane == 0) *scale_slot = s_new;
@@ -268,17 +351,16 @@ __global__ __launch_bounds__(64) void fp8_append_rows_kernel(Fp8RowsArgs a) {
   const int64_t row_stride = int64_t(c.num_heads) * D;
   const int64_t scale_index =
       (int64_t(a.layer) * c.num_pages + physical) * c.num_heads + head;
-  auto from_global = [=](int r, int j) {
-    return __bfloat162float(src[r * row_stride + lane + 32 * j]);
-  };
   if (tensor == 0) {
-    fp8_store_rows<D, true>(a.cache_k, a.scale_k + scale_index, c, a.layer,
-                            physical, head, p0 - logical_page * ps, p1 - p0, lane,
-                            from_global);
+    fp8_store_rows_from_memory<D, true>(a.cache_k, a.scale_k + scale_index, c,
+                                        a.layer, physical, head,
+                                        p0 - logical_page * ps, p1 - p0, lane, src,
+                                        row_stride);
   } else {
-    fp8_store_rows<D, false>(a.cache_v, a.scale_v + scale_index, c, a.layer,
-                             physical, head, p0 - logical_page * ps, p1 - p0, lane,
-                             from_global);
+    fp8_store_rows_from_memory<D, false>(a.cache_v, a.scale_v + scale_index, c,
+                                         a.layer, physical, head,
+                                         p0 - logical_page * ps, p1 - p0, lane, src,
+                                         row_stride);
   }
 }
 
@@ -339,7 +421,8 @@ cudaError_t fp8_append_rows(uint8_t *cache_k, uint8_t *cache_v, float *scale_k,
       c.num_heads <= 0 || c.num_heads > 65535 || c.head_dim != 256 ||
       c.page_size % 8 != 0 ||
       ((reinterpret_cast<uintptr_t>(cache_k) |
-        reinterpret_cast<uintptr_t>(cache_v)) & 15u) != 0) {
+        reinterpret_cast<uintptr_t>(cache_v) | reinterpret_cast<uintptr_t>(k) |
+        reinterpret_cast<uintptr_t>(v)) & 15u) != 0) {
     return cudaErrorInvalidValue;
   }
   Fp8RowsArgs a = {cache_k, cache_v, scale_k, scale_v, c, page_table, seq_batch,

@@ -52,38 +52,62 @@ __device__ __forceinline__ void load_head(const __nv_bfloat16 *in, int lane,
   }
 }
 
+// This lane's norm weights (elements lane + 32 i) and RoPE factors (dims
+// lane + 32 i of the first ROT / 2) in registers.
+template <int D, int ROT>
+struct PrepTables {
+  float w[D / 32];
+  float c[ROT / 64];
+  float s[ROT / 64];
+
+  __device__ __forceinline__ void load_weight(const __nv_bfloat16 *weight,
+                                              int lane) {
+#pragma unroll
+    for (int i = 0; i < D / 32; ++i) {
+      w[i] = __bfloat162float(__ldg(weight + lane + i * 32));
+    }
+  }
+  __device__ __forceinline__ void load_rope(const float *cos_row,
+                                            const float *sin_row, int lane) {
+#pragma unroll
+    for (int i = 0; i < ROT / 64; ++i) {
+      c[i] = __ldg(cos_row + lane + i * 32);
+      s[i] = __ldg(sin_row + lane + i * 32);
+    }
+  }
+};
+
 // Learned-weight RMSNorm, then split-half RoPE on the first ROT dims; the
 // bf16 results stay in registers, y[j] being element lane + 32*j.
+template <int D, int ROT, bool kIeee>
+__device__ __forceinline__ void prep_weighted_rope_tables(
+    __nv_bfloat16 (&y)[D / 32], const float (&x)[D / 32],
+    const PrepTables<D, ROT> &t) {
+  constexpr int kPairs = ROT / 64;
+  const float scale = warp_rms_scale<D, kIeee>(x);
+#pragma unroll
+  for (int i = 0; i < kPairs; ++i) {
+    const float lo = mul_prep<kIeee>(mul_prep<kIeee>(x[i], scale), t.w[i]);
+    const float hi =
+        mul_prep<kIeee>(mul_prep<kIeee>(x[i + kPairs], scale), t.w[i + kPairs]);
+    y[i] = __float2bfloat16_rn(__fmaf_rn(-hi, t.s[i], __fmul_rn(lo, t.c[i])));
+    y[i + kPairs] = __float2bfloat16_rn(__fmaf_rn(lo, t.s[i], __fmul_rn(hi, t.c[i])));
+  }
+#pragma unroll
+  for (int i = 2 * kPairs; i < D / 32; ++i) {  // dims >= ROT: no rotation
+    y[i] = __float2bfloat16_rn(mul_prep<kIeee>(mul_prep<kIeee>(x[i], scale), t.w[i]));
+  }
+}
+
 template <int D, int ROT, bool kIeee>
 __device__ __forceinline__ void prep_weighted_rope_values(
     __nv_bfloat16 (&y)[D / 32], const float (&x)[D / 32],
     const __nv_bfloat16 *weight, const float *cos_row, const float *sin_row,
     int lane) {
-  constexpr int kHalf = ROT / 2;
-  constexpr int kPairs = kHalf / 32;
-  const float scale = warp_rms_scale<D, kIeee>(x);
-#pragma unroll
-  for (int i = 0; i < kPairs; ++i) {
-    const int dim = lane + i * 32;
-    const float lo = mul_prep<kIeee>(mul_prep<kIeee>(x[i], scale),
-                                     __bfloat162float(__ldg(weight + dim)));
-    const float hi =
-        mul_prep<kIeee>(mul_prep<kIeee>(x[i + kPairs], scale),
-                        __bfloat162float(__ldg(weight + kHalf + dim)));
-    const float c = __ldg(cos_row + dim);
-    const float s = __ldg(sin_row + dim);
-    y[i] = __float2bfloat16_rn(__fmaf_rn(-hi, s, __fmul_rn(lo, c)));
-    y[i + kPairs] = __float2bfloat16_rn(__fmaf_rn(lo, s, __fmul_rn(hi, c)));
-  }
-#pragma unroll
-  for (int i = 0; i < D / 32; ++i) {
-    const int dim = lane + i * 32;
-    if (dim >= ROT) {
-      const float value = mul_prep<kIeee>(mul_prep<kIeee>(x[i], scale),
-                                          __bfloat162float(__ldg(weight + dim)));
-      y[i] = __float2bfloat16_rn(value);
-    }
-  }
+  PrepTables<D, ROT> t;
+  t.load_weight(weight, lane);
+  t.load_rope(cos_row, sin_row, lane);
+  prep_weighted_rope_tables<D, ROT, kIeee>(y, x, t);
 }
 
 template <int D>
