@@ -40,7 +40,7 @@ class _State:
 
 
 def _run_steps(kv, orc, *, window, ring_pages, start, steps, norm_mode, has_v=True, unmapped=None,
-               length_of=None, seed=7):
+               length_of=None, seed=7, page_size=16):
     """start: first position per sequence (-1: never appended). length_of(b, pos) -> seq_length given to
     the attention (default pos + 1)."""
     rng = np.random.default_rng(seed)
@@ -48,7 +48,7 @@ def _run_steps(kv, orc, *, window, ring_pages, start, steps, norm_mode, has_v=Tr
     B = start.size
     max_pos = int(start.max()) + steps + 1
     acase = helpers.make_append_case(seed, np.maximum(start, 0), window=window, ring_pages=ring_pages,
-                                     max_pos=max_pos, has_v=has_v)
+                                     max_pos=max_pos, has_v=has_v, page_size=page_size)
     if unmapped is not None:
         acase.page_table[unmapped] = -1
     cfg_t = acase.cfg
@@ -152,3 +152,29 @@ def test_fused_step_v_from_raw_k(kv, orc):
 def test_fused_step_batch_one_long_context(kv, orc):
     """Batch 1, 3000 keys: the new key sits in the last of ~190 ranges; everything else streams before it."""
     _run_steps(kv, orc, window=0, ring_pages=None, start=[3000], steps=6, norm_mode=kv.NORM_RSQRT_APPROX, seed=19)
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_fused_step_random_shapes(kv, orc, seed):
+    """Seeded random batches (1..100 sequences, so both with and without idle CTAs), page sizes 4 / 16 / 64,
+    sliding and linear caches, a few unmapped pages and skipped sequences: fused and two-launch forms must
+    agree bit for bit, and both with the oracle."""
+    rng = np.random.default_rng(1000 + seed)
+    batch = int(rng.choice([1, 2, 7, 33, 80, 100]))
+    page = int(rng.choice([4, 16, 64]))
+    window = int(rng.choice([0, 0, 48, 256]))
+    hi = 700 if batch <= 33 else 120
+    start = rng.integers(0, hi, size=batch).astype(np.int32)
+    start[rng.random(batch) < 0.1] = -1
+    if (start < 0).all():
+        start[0] = 5
+    steps = 6
+    ring_pages = None if window == 0 else -(-window // page) + int(rng.integers(0, 2))
+    acase = helpers.make_append_case(2000 + seed, np.maximum(start, 0), page_size=page, window=window,
+                                     ring_pages=ring_pages, max_pos=int(start.max()) + steps + 1)
+    unmapped = None
+    if rng.random() < 0.5:
+        b = int(rng.integers(0, batch))
+        unmapped = (b, int(rng.integers(0, acase.page_table.shape[1])))
+    _run_steps(kv, orc, window=window, ring_pages=ring_pages, start=start, steps=steps, norm_mode=kv.NORM_IEEE,
+               unmapped=unmapped, seed=2000 + seed, page_size=page)
