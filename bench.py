@@ -55,7 +55,7 @@ def parse_args():
                     help="skip timing the reference's own CUDA kernels (oracle/_ref) beside the library")
     ap.add_argument("--split-global", type=int, default=0, help="override the planned global split size")
     ap.add_argument("--split-local", type=int, default=0)
-    ap.add_argument("--workload", default="cfg3", choices=["cfg1", "cfg2", "cfg3", "cfg4", "cfg5", "native_global"],
+    ap.add_argument("--workload", default="cfg3", choices=["cfg1", "cfg2", "cfg3", "cfg4", "cfg5", "native_global", "prefill"],
                     help="BASELINE.json configs (1-based): cfg3 (default) is the batched paged decode the "
                          "metric is quoted on; the others are reported as extra lines on request")
     ap.add_argument("--partition", default="balanced", choices=["balanced", "splits"],
@@ -804,6 +804,90 @@ def run_native_global(args, kv, torch, sampler):
     }))
 
 
+# --------------------------------------------------------------------------- next row: prompt attention
+def run_prefill(args, kv, torch, sampler):
+    """Extra lines (not a BASELINE config): the two prompt-attention entry points of
+    src/gemma4_flash_attention.cuh -- prep + causal attention -- on seeded N(0,1) prompts, sliding
+    (8 KV x 256, window 1024) and global (1 KV x 512) geometry, with the reference's own kernels
+    (oracle/_ref) timed beside them when present. Tensor-bound: reported in TFLOP/s of the attention
+    (4 * D * visible (query, key) pairs * 16 heads)."""
+    from oracle import ref_binding as ref
+    dev = torch.device("cuda")
+    B = args.seqs or 4
+    S = min(args.max_ctx, 4096)
+    H = 16
+    results = []
+    for kind, HKVp, Dp, ROT, theta, window in (("sliding", 8, 256, 256, 1.0e4, 1024), ("global", 1, 512, 128, 1.0e6, 0)):
+        rows = B * S
+        q = torch.randn(rows, H, Dp, dtype=torch.bfloat16, device=dev)
+        k = torch.randn(rows, HKVp, Dp, dtype=torch.bfloat16, device=dev)
+        v = torch.randn(rows, HKVp, Dp, dtype=torch.bfloat16, device=dev)
+        out, qp = torch.empty_like(q), torch.empty_like(q)
+        kp, vp = torch.empty_like(k), torch.empty_like(k)
+        w = torch.ones(Dp, dtype=torch.bfloat16, device=dev)
+        cos_h, sin_h = kv.fill_rope_tables(S, ROT // 2, theta, Dp)
+        cos, sin = torch.from_numpy(cos_h).to(dev), torch.from_numpy(sin_h).to(dev)
+        pos = torch.arange(S, dtype=torch.int32, device=dev).repeat(B)
+        scale = 1.0 / math.sqrt(Dp)
+        r = np.arange(S, dtype=np.int64)
+        pairs = int((r + 1).sum()) if window == 0 else int(np.minimum(r + 1, window).sum())
+        flops = 4.0 * Dp * pairs * H * B
+
+        def mine():
+            if kind == "sliding":
+                kv.flash_attention_sliding_fwd(out, qp, kp, vp, q, k, v, w, w, cos, sin, pos, B, S, S, window, scale)
+            else:
+                kv.flash_attention_global_fwd(out, qp, kp, vp, q, k, w, w, cos, sin, pos, B, S, S, scale)
+
+        def attn_only():
+            kv.prefill_attention(out, qp, kp, vp, B, S, H, HKVp, Dp, window, scale)
+
+        def theirs():
+            if kind == "sliding":
+                ref.prefill_sliding(out, qp, kp, vp, q, k, v, w, w, cos, sin, pos, B, S, S, window, scale)
+            else:
+                ref.prefill_global(out, qp, kp, vp, q, k, w, w, cos, sin, pos, B, S, S, scale)
+
+        def timed(fn, n):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(n):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / n
+
+        n = max(3, min(args.steps, 50))
+        entry = {"kind": kind, "batch": B, "seq_len": S, "window": window, "ms_call": timed(mine, n),
+                 "ms_attention": timed(attn_only, n)}
+        entry["tflops_attention"] = flops / (entry["ms_attention"] * 1e-3) / 1e12
+        if ref.has_prefill() and not args.no_reference_cuda:
+            entry["reference_cuda_ms_call"] = timed(theirs, max(3, n // 5))
+        results.append(entry)
+    clocks = None
+    if sampler:
+        sampler.mark("timed_begin"); sampler.mark("timed_end"); sampler.mark("load_end")
+        clocks = sampler.stop()
+    peaks_path = REPO / "MEASURED_PEAKS.json"
+    peak = float(json.loads(peaks_path.read_text()).get("bf16_tflops", 1590.0)) if peaks_path.exists() else 1590.0
+    best = results[0]
+    print(json.dumps({
+        "metric": "prompt attention (causal, sliding window 1024): TFLOP/s of the attention stage", "unit": "TFLOP/s",
+        "value": best["tflops_attention"], "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": best["ms_call"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16 (mma.sync m16n8k16, fp32 accumulate and softmax)", "data": "synthetic",
+        "config": {"workload": "next row, not a BASELINE config: gemma4_flash_attention_{sliding,global}_fwd_bf16_norm_rope, "
+                               "prompts of %d x %d tokens" % (B, S)},
+        "roofline": {"bound": "tensor", "achieved": best["tflops_attention"], "peak": peak, "unit": "TFLOP/s",
+                     "frac": best["tflops_attention"] / peak, "traffic": None,
+                     "note": "peak = measured cuBLAS bf16 (tcgen05); this kernel uses the legacy mma.sync path"},
+        "results": results, "gpu_launches": 2 * args.steps, "clocks": clocks,
+    }))
+
+
 # --------------------------------------------------------------------------- main arm
 def main():
     args = parse_args()
@@ -831,6 +915,11 @@ def main():
     kv.load_library(build_if_missing=False)
     sampler = ClockSampler(local_rank) if rank == 0 else None   # started early: nvidia-smi takes a second to come up
 
+    if args.workload == "prefill":
+        if world > 1:
+            raise SystemExit("--workload prefill is a one-GPU line")
+        run_prefill(args, kv, torch, sampler)
+        return
     if args.workload == "native_global":
         if world > 1:
             raise SystemExit("--workload native_global is a one-GPU line")

@@ -119,6 +119,9 @@ class CudaError(RuntimeError):
 _P = c_void_p
 _SIGNATURES = {
     "gemma4_kv_cache_write_bf16": (c_int, [_P, _P, KvConfig, _P, _P, _P, c_int32, c_int32, _P, _P, _P]),
+    "b200kv_flash_attention_sliding_fwd_bf16_norm_rope": (c_int, [_P] * 12 + [c_int32] * 4 + [c_float, _P]),
+    "b200kv_flash_attention_global_fwd_bf16_norm_rope": (c_int, [_P] * 11 + [c_int32] * 3 + [c_float, _P]),
+    "b200kv_prefill_attention_bf16": (c_int, [_P] * 4 + [c_int32] * 6 + [c_float, _P]),
     "b200kv_prefill_cache_fill_bf16": (c_int, [_P, _P, KvConfig, _P, _P, _P, c_int32, c_int32, c_int32, _P, _P, _P]),
     "b200kv_cache_offset": (c_int64, [POINTER(KvConfig), c_int32, c_int32, c_int32, c_int32, c_int32]),
     "b200kv_make_config": (None, [POINTER(KvConfig), c_int32, c_int32, c_int32, c_int32]),
@@ -352,6 +355,38 @@ def kv_cache_write(cache_k, cache_v, cfg: KvConfig, page_table, token_batch, tok
         _ptr(cache_k), _ptr(cache_v), cfg, _ptr(page_table), _ptr(token_batch), _ptr(token_position),
         token_count, layer, _ptr(k), _ptr(v), _stream(stream))
     return _check(code, "gemma4_kv_cache_write_bf16", check)
+
+
+def flash_attention_sliding_fwd(out, q_prepared, k_prepared, v_prepared, q, k, v, q_norm_weight, k_norm_weight,
+                                cos, sin, token_position, batch_size: int, seqlen_q: int, seqlen_k: int,
+                                window_size: int, softmax_scale: float, stream=None, check: bool = True) -> int:
+    """gemma4_flash_attention_sliding_fwd_bf16_norm_rope: prompt prep + causal sliding-window attention."""
+    code = load_library().b200kv_flash_attention_sliding_fwd_bf16_norm_rope(
+        _ptr(out), _ptr(q_prepared), _ptr(k_prepared), _ptr(v_prepared), _ptr(q), _ptr(k), _ptr(v),
+        _ptr(q_norm_weight), _ptr(k_norm_weight), _ptr(cos), _ptr(sin), _ptr(token_position), batch_size,
+        seqlen_q, seqlen_k, window_size, softmax_scale, _stream(stream))
+    return _check(code, "b200kv_flash_attention_sliding_fwd_bf16_norm_rope", check)
+
+
+def flash_attention_global_fwd(out, q_prepared, k_prepared, v_prepared, q, k, q_norm_weight, k_norm_weight,
+                               cos, sin, token_position, batch_size: int, seqlen_q: int, seqlen_k: int,
+                               softmax_scale: float, stream=None, check: bool = True) -> int:
+    """gemma4_flash_attention_global_fwd_bf16_norm_rope: 16 Q / 1 KV x 512, rotary 128, V from raw K."""
+    code = load_library().b200kv_flash_attention_global_fwd_bf16_norm_rope(
+        _ptr(out), _ptr(q_prepared), _ptr(k_prepared), _ptr(v_prepared), _ptr(q), _ptr(k), _ptr(q_norm_weight),
+        _ptr(k_norm_weight), _ptr(cos), _ptr(sin), _ptr(token_position), batch_size, seqlen_q, seqlen_k,
+        softmax_scale, _stream(stream))
+    return _check(code, "b200kv_flash_attention_global_fwd_bf16_norm_rope", check)
+
+
+def prefill_attention(out, q_prepared, k_prepared, v_prepared, batch_size: int, seq_len: int, q_heads: int,
+                      kv_heads: int, head_dim: int, window_size: int, softmax_scale: float, stream=None,
+                      check: bool = True) -> int:
+    """Causal (+ window) attention of each sequence over its own prepared rows."""
+    code = load_library().b200kv_prefill_attention_bf16(
+        _ptr(out), _ptr(q_prepared), _ptr(k_prepared), _ptr(v_prepared), batch_size, seq_len, q_heads, kv_heads,
+        head_dim, window_size, softmax_scale, _stream(stream))
+    return _check(code, "b200kv_prefill_attention_bf16", check)
 
 
 def prefill_cache_fill(cache_k, cache_v, cfg: KvConfig, page_table, token_batch, token_position,

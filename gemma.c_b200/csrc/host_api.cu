@@ -335,6 +335,91 @@ struct B200KvRuntimeState {
   Gemma4RuntimeState state;
 };
 
+// ===========================================================================
+// Prompt attention entry points of src/gemma4_flash_attention.cuh
+// ===========================================================================
+namespace {
+// Geometry constants of src/gemma4.h:13-28 for the two layer kinds.
+constexpr int kQueryHeads = 16;
+constexpr int kSlidingKvHeads = 8, kSlidingHeadDim = 256;
+constexpr int kGlobalKvHeads = 1, kGlobalHeadDim = 512, kGlobalRotaryDim = 128;
+
+cudaError_t prompt_forward(__nv_bfloat16 *out, __nv_bfloat16 *q_prepared,
+                           __nv_bfloat16 *k_prepared, __nv_bfloat16 *v_prepared,
+                           const __nv_bfloat16 *q, const __nv_bfloat16 *k,
+                           const __nv_bfloat16 *v, const __nv_bfloat16 *q_w,
+                           const __nv_bfloat16 *k_w, const float *cos,
+                           const float *sin, const int32_t *token_position,
+                           int batch_size, int seqlen_q, int seqlen_k,
+                           int kv_heads, int head_dim, int rotary_dim, int window,
+                           float softmax_scale, cudaStream_t stream) {
+  // src/gemma4_flash_attention_prefill.cu:1131-1139
+  if (batch_size <= 0 || seqlen_q <= 0 || seqlen_q != seqlen_k ||
+      out == nullptr || q_prepared == nullptr || k_prepared == nullptr ||
+      v_prepared == nullptr || token_position == nullptr) {
+    return cudaErrorInvalidValue;
+  }
+  b200kv::PrefillPrepArgs prep;
+  prep.q_prepared = q_prepared;
+  prep.k_prepared = k_prepared;
+  prep.v_prepared = v_prepared;
+  prep.q = q;
+  prep.k = k;
+  prep.v = v;
+  prep.q_norm_weight = q_w;
+  prep.k_norm_weight = k_w;
+  prep.cos = cos;
+  prep.sin = sin;
+  prep.token_position = token_position;
+  prep.rows = int64_t(batch_size) * seqlen_q;
+  prep.q_heads = kQueryHeads;
+  prep.kv_heads = kv_heads;
+  prep.head_dim = head_dim;
+  prep.rotary_dim = rotary_dim;
+  prep.norm_mode = B200KV_NORM_RSQRT_APPROX;
+  const cudaError_t st = b200kv::prefill_prep_bf16(prep, stream);
+  if (st != cudaSuccess) return st;
+  return b200kv::prefill_attention_bf16(out, q_prepared, k_prepared, v_prepared,
+                                        batch_size, seqlen_q, kQueryHeads, kv_heads,
+                                        head_dim, window, softmax_scale, stream);
+}
+}  // namespace
+
+cudaError_t gemma4_flash_attention_sliding_fwd_bf16_norm_rope(
+    __nv_bfloat16 *__restrict__ d_out, __nv_bfloat16 *__restrict__ d_q_prepared,
+    __nv_bfloat16 *__restrict__ d_k_prepared,
+    __nv_bfloat16 *__restrict__ d_v_prepared, const __nv_bfloat16 *__restrict__ d_q,
+    const __nv_bfloat16 *__restrict__ d_k, const __nv_bfloat16 *__restrict__ d_v,
+    const __nv_bfloat16 *__restrict__ d_q_norm_weight,
+    const __nv_bfloat16 *__restrict__ d_k_norm_weight,
+    const float *__restrict__ d_cos, const float *__restrict__ d_sin,
+    const int32_t *__restrict__ d_token_position, int batch_size, int seqlen_q,
+    int seqlen_k, int window_size, float softmax_scale, cudaStream_t stream) {
+  if (window_size <= 0 || d_v == nullptr) return cudaErrorInvalidValue;
+  return prompt_forward(d_out, d_q_prepared, d_k_prepared, d_v_prepared, d_q, d_k,
+                        d_v, d_q_norm_weight, d_k_norm_weight, d_cos, d_sin,
+                        d_token_position, batch_size, seqlen_q, seqlen_k,
+                        kSlidingKvHeads, kSlidingHeadDim, kSlidingHeadDim,
+                        window_size, softmax_scale, stream);
+}
+
+cudaError_t gemma4_flash_attention_global_fwd_bf16_norm_rope(
+    __nv_bfloat16 *__restrict__ d_out, __nv_bfloat16 *__restrict__ d_q_prepared,
+    __nv_bfloat16 *__restrict__ d_k_prepared,
+    __nv_bfloat16 *__restrict__ d_v_prepared, const __nv_bfloat16 *__restrict__ d_q,
+    const __nv_bfloat16 *__restrict__ d_k,
+    const __nv_bfloat16 *__restrict__ d_q_norm_weight,
+    const __nv_bfloat16 *__restrict__ d_k_norm_weight,
+    const float *__restrict__ d_cos, const float *__restrict__ d_sin,
+    const int32_t *__restrict__ d_token_position, int batch_size, int seqlen_q,
+    int seqlen_k, float softmax_scale, cudaStream_t stream) {
+  return prompt_forward(d_out, d_q_prepared, d_k_prepared, d_v_prepared, d_q, d_k,
+                        nullptr, d_q_norm_weight, d_k_norm_weight, d_cos, d_sin,
+                        d_token_position, batch_size, seqlen_q, seqlen_k,
+                        kGlobalKvHeads, kGlobalHeadDim, kGlobalRotaryDim, 0,
+                        softmax_scale, stream);
+}
+
 namespace {
 // B200KV_FUSED_LAYER_STEP=0 keeps the layer-step on separate append and
 // attention launches (for A/B timing); read once.
@@ -361,6 +446,61 @@ cudaError_t gemma4_kv_cache_write_bf16(
                                      d_page_table, d_token_batch,
                                      d_token_position, token_count, layer, d_k,
                                      d_v, stream);
+}
+
+int b200kv_flash_attention_sliding_fwd_bf16_norm_rope(
+    b200kv_bf16 *d_out, b200kv_bf16 *d_q_prepared, b200kv_bf16 *d_k_prepared,
+    b200kv_bf16 *d_v_prepared, const b200kv_bf16 *d_q, const b200kv_bf16 *d_k,
+    const b200kv_bf16 *d_v, const b200kv_bf16 *d_q_norm_weight,
+    const b200kv_bf16 *d_k_norm_weight, const float *d_cos, const float *d_sin,
+    const int32_t *d_token_position, int32_t batch_size, int32_t seqlen_q,
+    int32_t seqlen_k, int32_t window_size, float softmax_scale,
+    b200kv_stream stream) {
+  using bf = __nv_bfloat16;
+  return gemma4_flash_attention_sliding_fwd_bf16_norm_rope(
+      reinterpret_cast<bf *>(d_out), reinterpret_cast<bf *>(d_q_prepared),
+      reinterpret_cast<bf *>(d_k_prepared), reinterpret_cast<bf *>(d_v_prepared),
+      reinterpret_cast<const bf *>(d_q), reinterpret_cast<const bf *>(d_k),
+      reinterpret_cast<const bf *>(d_v),
+      reinterpret_cast<const bf *>(d_q_norm_weight),
+      reinterpret_cast<const bf *>(d_k_norm_weight), d_cos, d_sin,
+      d_token_position, batch_size, seqlen_q, seqlen_k, window_size,
+      softmax_scale, static_cast<cudaStream_t>(stream));
+}
+
+int b200kv_flash_attention_global_fwd_bf16_norm_rope(
+    b200kv_bf16 *d_out, b200kv_bf16 *d_q_prepared, b200kv_bf16 *d_k_prepared,
+    b200kv_bf16 *d_v_prepared, const b200kv_bf16 *d_q, const b200kv_bf16 *d_k,
+    const b200kv_bf16 *d_q_norm_weight, const b200kv_bf16 *d_k_norm_weight,
+    const float *d_cos, const float *d_sin, const int32_t *d_token_position,
+    int32_t batch_size, int32_t seqlen_q, int32_t seqlen_k, float softmax_scale,
+    b200kv_stream stream) {
+  using bf = __nv_bfloat16;
+  return gemma4_flash_attention_global_fwd_bf16_norm_rope(
+      reinterpret_cast<bf *>(d_out), reinterpret_cast<bf *>(d_q_prepared),
+      reinterpret_cast<bf *>(d_k_prepared), reinterpret_cast<bf *>(d_v_prepared),
+      reinterpret_cast<const bf *>(d_q), reinterpret_cast<const bf *>(d_k),
+      reinterpret_cast<const bf *>(d_q_norm_weight),
+      reinterpret_cast<const bf *>(d_k_norm_weight), d_cos, d_sin,
+      d_token_position, batch_size, seqlen_q, seqlen_k, softmax_scale,
+      static_cast<cudaStream_t>(stream));
+}
+
+int b200kv_prefill_attention_bf16(b200kv_bf16 *d_out,
+                                  const b200kv_bf16 *d_q_prepared,
+                                  const b200kv_bf16 *d_k_prepared,
+                                  const b200kv_bf16 *d_v_prepared,
+                                  int32_t batch_size, int32_t seq_len,
+                                  int32_t q_heads, int32_t kv_heads,
+                                  int32_t head_dim, int32_t window_size,
+                                  float softmax_scale, b200kv_stream stream) {
+  using bf = __nv_bfloat16;
+  return b200kv::prefill_attention_bf16(
+      reinterpret_cast<bf *>(d_out), reinterpret_cast<const bf *>(d_q_prepared),
+      reinterpret_cast<const bf *>(d_k_prepared),
+      reinterpret_cast<const bf *>(d_v_prepared), batch_size, seq_len, q_heads,
+      kv_heads, head_dim, window_size, softmax_scale,
+      static_cast<cudaStream_t>(stream));
 }
 
 int b200kv_prefill_cache_fill_bf16(b200kv_bf16 *d_cache_k,

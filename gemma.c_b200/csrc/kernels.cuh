@@ -116,6 +116,14 @@ struct PrefillPrepArgs {
 cudaError_t prefill_prep_bf16(const PrefillPrepArgs &args,
                               cudaStream_t stream);
 
+// Causal (+ sliding window) attention of every sequence over its own prepared
+// rows (prefill_attention.cu); window 0 = causal only; head_dim 256 or 512.
+cudaError_t prefill_attention_bf16(__nv_bfloat16 *out, const __nv_bfloat16 *q,
+                                   const __nv_bfloat16 *k, const __nv_bfloat16 *v,
+                                   int batch, int seq_len, int q_heads,
+                                   int kv_heads, int head_dim, int window,
+                                   float softmax_scale, cudaStream_t stream);
+
 // FP8 e4m3 cache (fp8_cache.cu). args.cache_k / cache_v are unused.
 cudaError_t decode_append_fp8(const AppendArgs &args, uint8_t *cache_k,
                               uint8_t *cache_v, float *scale_k, float *scale_v,

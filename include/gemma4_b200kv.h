@@ -188,6 +188,42 @@ int b200kv_prefill_prep_bf16(b200kv_bf16 *d_q_prepared,
                              int32_t norm_mode, b200kv_stream stream);
 
 /* ------------------------------------------------------------------ *
+ * Prompt attention, C bindings of gemma4_flash_attention_sliding_fwd_bf16_norm_rope
+ * and gemma4_flash_attention_global_fwd_bf16_norm_rope
+ * (src/gemma4_flash_attention.cuh:9-45): prep of every row (as
+ * b200kv_prefill_prep_bf16, norm mode rsqrt.approx like the reference's GPU
+ * code) into d_*_prepared, then causal attention of each sequence over its own
+ * prepared rows -- query row r sees keys c <= r and, for the sliding variant,
+ * c >= max(0, r - window_size + 1) -- into d_out [row, 16, D]. seqlen_q must
+ * equal seqlen_k (cudaErrorInvalidValue otherwise, as the reference).
+ * b200kv_prefill_attention_bf16 is the attention stage alone on rows that are
+ * already prepared (window_size 0: causal only; head_dim 256 or 512).
+ * ------------------------------------------------------------------ */
+int b200kv_flash_attention_sliding_fwd_bf16_norm_rope(
+    b200kv_bf16 *d_out, b200kv_bf16 *d_q_prepared, b200kv_bf16 *d_k_prepared,
+    b200kv_bf16 *d_v_prepared, const b200kv_bf16 *d_q, const b200kv_bf16 *d_k,
+    const b200kv_bf16 *d_v, const b200kv_bf16 *d_q_norm_weight,
+    const b200kv_bf16 *d_k_norm_weight, const float *d_cos, const float *d_sin,
+    const int32_t *d_token_position, int32_t batch_size, int32_t seqlen_q,
+    int32_t seqlen_k, int32_t window_size, float softmax_scale,
+    b200kv_stream stream);
+int b200kv_flash_attention_global_fwd_bf16_norm_rope(
+    b200kv_bf16 *d_out, b200kv_bf16 *d_q_prepared, b200kv_bf16 *d_k_prepared,
+    b200kv_bf16 *d_v_prepared, const b200kv_bf16 *d_q, const b200kv_bf16 *d_k,
+    const b200kv_bf16 *d_q_norm_weight, const b200kv_bf16 *d_k_norm_weight,
+    const float *d_cos, const float *d_sin, const int32_t *d_token_position,
+    int32_t batch_size, int32_t seqlen_q, int32_t seqlen_k, float softmax_scale,
+    b200kv_stream stream);
+int b200kv_prefill_attention_bf16(b200kv_bf16 *d_out,
+                                  const b200kv_bf16 *d_q_prepared,
+                                  const b200kv_bf16 *d_k_prepared,
+                                  const b200kv_bf16 *d_v_prepared,
+                                  int32_t batch_size, int32_t seq_len,
+                                  int32_t q_heads, int32_t kv_heads,
+                                  int32_t head_dim, int32_t window_size,
+                                  float softmax_scale, b200kv_stream stream);
+
+/* ------------------------------------------------------------------ *
  * Cache fill after a prompt: the prepared K/V rows of batch_size sequences of
  * seq_len tokens each (row b * seq_len + t, with d_token_batch / d_token_position
  * as gemma4_runtime_prepare_prefill leaves them) go into the cache in one

@@ -37,6 +37,32 @@ extern "C" cudaError_t gemma4_kv_cache_write_bf16(
     int32_t layer, const __nv_bfloat16 *__restrict__ d_k,
     const __nv_bfloat16 *__restrict__ d_v, cudaStream_t stream);
 
+// src/gemma4_flash_attention.cuh:9-45: prompt attention with the norm + RoPE
+// prep fused in front. Same names, argument order and error behaviour; rows are
+// batch * seq_len + t, q / out [row, 16, D], k / v [row, kv_heads, D] with
+// 8 KV heads x 256 (sliding) or 1 KV head x 512, rotary 128, V from K (global).
+cudaError_t gemma4_flash_attention_sliding_fwd_bf16_norm_rope(
+    __nv_bfloat16 *__restrict__ d_out, __nv_bfloat16 *__restrict__ d_q_prepared,
+    __nv_bfloat16 *__restrict__ d_k_prepared,
+    __nv_bfloat16 *__restrict__ d_v_prepared, const __nv_bfloat16 *__restrict__ d_q,
+    const __nv_bfloat16 *__restrict__ d_k, const __nv_bfloat16 *__restrict__ d_v,
+    const __nv_bfloat16 *__restrict__ d_q_norm_weight,
+    const __nv_bfloat16 *__restrict__ d_k_norm_weight,
+    const float *__restrict__ d_cos, const float *__restrict__ d_sin,
+    const int32_t *__restrict__ d_token_position, int batch_size, int seqlen_q,
+    int seqlen_k, int window_size, float softmax_scale, cudaStream_t stream);
+
+cudaError_t gemma4_flash_attention_global_fwd_bf16_norm_rope(
+    __nv_bfloat16 *__restrict__ d_out, __nv_bfloat16 *__restrict__ d_q_prepared,
+    __nv_bfloat16 *__restrict__ d_k_prepared,
+    __nv_bfloat16 *__restrict__ d_v_prepared, const __nv_bfloat16 *__restrict__ d_q,
+    const __nv_bfloat16 *__restrict__ d_k,
+    const __nv_bfloat16 *__restrict__ d_q_norm_weight,
+    const __nv_bfloat16 *__restrict__ d_k_norm_weight,
+    const float *__restrict__ d_cos, const float *__restrict__ d_sin,
+    const int32_t *__restrict__ d_token_position, int batch_size, int seqlen_q,
+    int seqlen_k, float softmax_scale, cudaStream_t stream);
+
 // src/gemma4_kv_cache.cu:76-91
 Gemma4KvCacheConfig gemma4_kv_cache_make_config(bool global, int32_t num_pages,
                                                 int32_t page_size,

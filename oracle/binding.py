@@ -90,6 +90,7 @@ def lib() -> ctypes.CDLL:
         "orc_fp8_k_index": (c_int64, [C] + [c_int32] * 5),
         "orc_fp8_append": (None, [_P, _P, _P, _P, C, _P, _P, _P, _P, c_int32, c_int32, _P, _P]),
         "orc_fp8_decode_attention_f64": (None, [_P] * 9 + [C, c_int32, c_float, c_int32, c_int32]),
+        "orc_prefill_attention_f64": (None, [_P] * 5 + [c_int32] * 6 + [c_float, c_int32]),
         "orc_layer_step_timed": (c_double, [c_int32, _P, _P, _P, _P, C, _P, _P, _P, c_int32] + [_P] * 7 + [c_int32, c_int32, c_float, c_int32]),
         "orc_hardware_threads": (c_int32, []),
     }
@@ -247,6 +248,16 @@ def decode_attention_f64(q, cache_k, cache_v, page_table, seq_lengths, cfg, laye
     lse = np.zeros((batch_count, q_heads), dtype=np.float32)
     lib().orc_decode_attention_f64(_p(out), _p(lse), _p(q), _p(cache_k), _p(cache_v), _p(page_table),
                                    _p(seq_lengths), ctypes.byref(c), layer, scale, batch_count, q_heads)
+    return out, lse
+
+
+def prefill_attention_f64(q, k, v, batch, seq_len, q_heads, kv_heads, head_dim, window, scale):
+    """Causal (+ sliding window) prompt attention in double precision over contiguous prepared rows.
+    Returns (out fp32 [batch*seq, q_heads, D], lse fp32 [batch*seq, q_heads])."""
+    out = np.empty((batch * seq_len, q_heads, head_dim), dtype=np.float32)
+    lse = np.empty((batch * seq_len, q_heads), dtype=np.float32)
+    lib().orc_prefill_attention_f64(_p(out), _p(lse), _p(q), _p(k), _p(v), batch, seq_len, q_heads, kv_heads,
+                                    head_dim, window, scale, lib().orc_hardware_threads())
     return out, lse
 
 

@@ -1007,6 +1007,63 @@ double orc_layer_step_timed(int32_t threads, uint16_t *out,
   return std::chrono::duration<double>(t1 - t0).count();
 }
 
+// Prompt attention over contiguous prepared rows, the second stage of
+// gemma4_flash_attention_{sliding,global}_fwd_bf16_norm_rope
+// (src/gemma4_flash_attention_prefill.cu:502-540 for the mask, :1110-1257 for
+// the entry points): query row r of a sequence sees keys c <= r and, with a
+// window, c >= max(0, r - window + 1). Double precision, direct softmax;
+// fp32 output (not rounded) and natural-log LSE.
+void orc_prefill_attention_f64(float *out_f32, float *lse, const uint16_t *q,
+                               const uint16_t *k, const uint16_t *v,
+                               int32_t batch, int32_t seq_len, int32_t q_heads,
+                               int32_t kv_heads, int32_t head_dim,
+                               int32_t window, float softmax_scale,
+                               int32_t threads) {
+  const int D = head_dim;
+  const int G = q_heads / kv_heads;
+  const int units = batch * q_heads;
+  auto work = [&](int u0, int u1) {
+    std::vector<double> scores, acc(D);
+    for (int u = u0; u < u1; ++u) {
+      const int b = u / q_heads, h = u % q_heads, kvh = h / G;
+      for (int r = 0; r < seq_len; ++r) {
+        const int64_t row = int64_t(b) * seq_len + r;
+        const uint16_t *qr = q + (row * q_heads + h) * D;
+        const int left = window > 0 ? std::max(0, r - window + 1) : 0;
+        scores.assign(size_t(r - left + 1), 0.0);
+        double M = -std::numeric_limits<double>::infinity();
+        for (int c = left; c <= r; ++c) {
+          const uint16_t *kr =
+              k + ((int64_t(b) * seq_len + c) * kv_heads + kvh) * D;
+          double s = 0.0;
+          for (int d = 0; d < D; ++d) s += double(bf(qr[d])) * double(bf(kr[d]));
+          s *= double(softmax_scale);
+          scores[size_t(c - left)] = s;
+          M = std::max(M, s);
+        }
+        double L = 0.0;
+        std::fill(acc.begin(), acc.end(), 0.0);
+        for (int c = left; c <= r; ++c) {
+          const double p = std::exp(scores[size_t(c - left)] - M);
+          L += p;
+          const uint16_t *vr =
+              v + ((int64_t(b) * seq_len + c) * kv_heads + kvh) * D;
+          for (int d = 0; d < D; ++d) acc[size_t(d)] += p * double(bf(vr[d]));
+        }
+        float *o = out_f32 + (row * q_heads + h) * D;
+        for (int d = 0; d < D; ++d) o[d] = float(acc[size_t(d)] / L);
+        if (lse != nullptr) lse[row * q_heads + h] = float(M + std::log(L));
+      }
+    }
+  };
+  const int nt = std::max(1, std::min(threads, units));
+  std::vector<std::thread> pool;
+  for (int t = 0; t < nt; ++t) {
+    pool.emplace_back(work, units * t / nt, units * (t + 1) / nt);
+  }
+  for (auto &th : pool) th.join();
+}
+
 int32_t orc_hardware_threads(void) {
   const unsigned n = std::thread::hardware_concurrency();
   return n == 0 ? 1 : int32_t(n);

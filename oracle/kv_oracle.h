@@ -165,6 +165,16 @@ void orc_fp8_decode_attention_f64(float *out_f32, float *lse,
                                   float softmax_scale, int32_t batch_count,
                                   int32_t q_heads);
 
+// ---- prompt attention (prefill.cu:502-540,1110-1257): causal (+ window) over
+// contiguous prepared rows q [batch*seq, q_heads, D], k/v [batch*seq, kv_heads, D];
+// double precision; fp32 output, natural-log LSE (may be NULL).
+void orc_prefill_attention_f64(float *out_f32, float *lse, const uint16_t *q,
+                               const uint16_t *k, const uint16_t *v,
+                               int32_t batch, int32_t seq_len, int32_t q_heads,
+                               int32_t kv_heads, int32_t head_dim,
+                               int32_t window, float softmax_scale,
+                               int32_t threads);
+
 // ---- timed CPU baseline: one layer-step (append + attention + reduce) -----
 // Runs orc_decode_append then the reference-order attention with `threads`
 // host threads over (sequence, kv head) units. Returns seconds of wall time.

@@ -28,6 +28,11 @@ def lib() -> ctypes.CDLL:
         L.ref_decode_append.argtypes = [_P, _P, _P, OrcKvConfig, _P, _P, c_int] + [_P] * 7 + [c_int, _P]
         L.ref_decode_attention.restype = c_int
         L.ref_decode_attention.argtypes = [_P] * 9 + [OrcKvConfig, c_int32, c_float, c_int32, c_int32, c_int32, _P]
+        if hasattr(L, "ref_prefill_sliding"):
+            L.ref_prefill_sliding.restype = c_int
+            L.ref_prefill_sliding.argtypes = [_P] * 12 + [c_int] * 4 + [c_float, _P]
+            L.ref_prefill_global.restype = c_int
+            L.ref_prefill_global.argtypes = [_P] * 11 + [c_int] * 3 + [c_float, _P]
         _lib = L
     return _lib
 
@@ -60,3 +65,24 @@ def decode_attention(out, pm, pl, pacc, q, cache_k, cache_v, page_table, seq_len
     return lib().ref_decode_attention(_ptr(out), _ptr(pm), _ptr(pl), _ptr(pacc), _ptr(q), _ptr(cache_k),
                                       _ptr(cache_v), _ptr(page_table), _ptr(seq_lengths), OrcKvConfig.of(cfg), layer,
                                       scale, split_size, num_splits, batch_count, _stream())
+
+
+def has_prefill() -> bool:
+    return available() and hasattr(lib(), "ref_prefill_sliding")
+
+
+def prefill_sliding(out, q_prepared, k_prepared, v_prepared, q, k, v, q_w, k_w, cos, sin, token_position,
+                    batch_size, seqlen_q, seqlen_k, window_size, scale) -> int:
+    """The reference's gemma4_flash_attention_sliding_fwd_bf16_norm_rope."""
+    return lib().ref_prefill_sliding(_ptr(out), _ptr(q_prepared), _ptr(k_prepared), _ptr(v_prepared), _ptr(q),
+                                     _ptr(k), _ptr(v), _ptr(q_w), _ptr(k_w), _ptr(cos), _ptr(sin),
+                                     _ptr(token_position), batch_size, seqlen_q, seqlen_k, window_size, scale,
+                                     _stream())
+
+
+def prefill_global(out, q_prepared, k_prepared, v_prepared, q, k, q_w, k_w, cos, sin, token_position, batch_size,
+                   seqlen_q, seqlen_k, scale) -> int:
+    """The reference's gemma4_flash_attention_global_fwd_bf16_norm_rope."""
+    return lib().ref_prefill_global(_ptr(out), _ptr(q_prepared), _ptr(k_prepared), _ptr(v_prepared), _ptr(q),
+                                    _ptr(k), _ptr(q_w), _ptr(k_w), _ptr(cos), _ptr(sin), _ptr(token_position),
+                                    batch_size, seqlen_q, seqlen_k, scale, _stream())

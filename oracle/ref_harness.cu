@@ -12,6 +12,7 @@
 // The result, oracle/_ref/libgemma4_ref.so, is a second checker beside the host oracle and the source
 // of the golden fixtures in tests/golden (recorded on a B200).
 #include "gemma4_flash_attention_decode.cu"
+#include "gemma4_flash_attention.cuh"
 
 extern "C" __device__ void gemma4_ffn_decode_fused_bf16_device(
     __nv_bfloat16 *__restrict__, __nv_bfloat16 *__restrict__, const __nv_bfloat16 *__restrict__,
@@ -123,4 +124,27 @@ extern "C" int ref_decode_attention(__nv_bfloat16 *out, float *pm, float *pl, fl
                                  split_size, num_splits, batch_count, stream);
   }
   return cudaErrorInvalidValue;
+}
+
+// C names for the reference's two prompt-attention entry points
+// (src/gemma4_flash_attention.cuh:9-45; defined in gemma4_flash_attention_prefill.cu, linked in as it is).
+extern "C" int ref_prefill_sliding(__nv_bfloat16 *out, __nv_bfloat16 *q_prepared, __nv_bfloat16 *k_prepared,
+                                   __nv_bfloat16 *v_prepared, const __nv_bfloat16 *q, const __nv_bfloat16 *k,
+                                   const __nv_bfloat16 *v, const __nv_bfloat16 *q_w, const __nv_bfloat16 *k_w,
+                                   const float *cos, const float *sin, const int32_t *token_position,
+                                   int batch_size, int seqlen_q, int seqlen_k, int window_size, float scale,
+                                   cudaStream_t stream) {
+  return gemma4_flash_attention_sliding_fwd_bf16_norm_rope(out, q_prepared, k_prepared, v_prepared, q, k, v, q_w,
+                                                           k_w, cos, sin, token_position, batch_size, seqlen_q,
+                                                           seqlen_k, window_size, scale, stream);
+}
+
+extern "C" int ref_prefill_global(__nv_bfloat16 *out, __nv_bfloat16 *q_prepared, __nv_bfloat16 *k_prepared,
+                                  __nv_bfloat16 *v_prepared, const __nv_bfloat16 *q, const __nv_bfloat16 *k,
+                                  const __nv_bfloat16 *q_w, const __nv_bfloat16 *k_w, const float *cos,
+                                  const float *sin, const int32_t *token_position, int batch_size, int seqlen_q,
+                                  int seqlen_k, float scale, cudaStream_t stream) {
+  return gemma4_flash_attention_global_fwd_bf16_norm_rope(out, q_prepared, k_prepared, v_prepared, q, k, q_w, k_w,
+                                                          cos, sin, token_position, batch_size, seqlen_q, seqlen_k,
+                                                          scale, stream);
 }
