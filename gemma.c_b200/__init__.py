@@ -122,6 +122,7 @@ _SIGNATURES = {
     "b200kv_flash_attention_sliding_fwd_bf16_norm_rope": (c_int, [_P] * 12 + [c_int32] * 4 + [c_float, _P]),
     "b200kv_flash_attention_global_fwd_bf16_norm_rope": (c_int, [_P] * 11 + [c_int32] * 3 + [c_float, _P]),
     "b200kv_prefill_attention_bf16": (c_int, [_P] * 4 + [c_int32] * 6 + [c_float, _P]),
+    "b200kv_prefill_attention_fault": (c_int, []),
     "b200kv_prefill_cache_fill_bf16": (c_int, [_P, _P, KvConfig, _P, _P, _P, c_int32, c_int32, c_int32, _P, _P, _P]),
     "b200kv_cache_offset": (c_int64, [POINTER(KvConfig), c_int32, c_int32, c_int32, c_int32, c_int32]),
     "b200kv_make_config": (None, [POINTER(KvConfig), c_int32, c_int32, c_int32, c_int32]),
@@ -387,6 +388,11 @@ def prefill_attention(out, q_prepared, k_prepared, v_prepared, batch_size: int, 
         _ptr(out), _ptr(q_prepared), _ptr(k_prepared), _ptr(v_prepared), batch_size, seq_len, q_heads, kv_heads,
         head_dim, window_size, softmax_scale, _stream(stream))
     return _check(code, "b200kv_prefill_attention_bf16", check)
+
+
+def prefill_attention_fault() -> int:
+    """Synchronises; 0, or which bounded wait of the head_dim-256 tensor-core kernel ran out last launch."""
+    return int(load_library().b200kv_prefill_attention_fault())
 
 
 def prefill_cache_fill(cache_k, cache_v, cfg: KvConfig, page_table, token_batch, token_position,

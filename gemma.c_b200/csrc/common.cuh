@@ -77,14 +77,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // without a limit.
 constexpr long long kWaitClockLimit = 1ll << 31;
 
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar,
-                                                  uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait_bounded(
+    uint32_t bar, uint32_t parity, long long clock_limit = kWaitClockLimit) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long start = clock64();
   for (uint32_t poll = 0;; ++poll) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((poll & 63u) == 63u) {
-      if (clock64() - start > kWaitClockLimit) return false;
+      if (clock64() - start > clock_limit) return false;
       __nanosleep(64);
     }
   }

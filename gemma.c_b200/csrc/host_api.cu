@@ -486,6 +486,10 @@ int b200kv_flash_attention_global_fwd_bf16_norm_rope(
       static_cast<cudaStream_t>(stream));
 }
 
+int b200kv_prefill_attention_fault(void) {
+  return b200kv::prefill_attention_sm100_fault();
+}
+
 int b200kv_prefill_attention_bf16(b200kv_bf16 *d_out,
                                   const b200kv_bf16 *d_q_prepared,
                                   const b200kv_bf16 *d_k_prepared,

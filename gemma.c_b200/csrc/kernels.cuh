@@ -123,6 +123,17 @@ cudaError_t prefill_attention_bf16(__nv_bfloat16 *out, const __nv_bfloat16 *q,
                                    int batch, int seq_len, int q_heads,
                                    int kv_heads, int head_dim, int window,
                                    float softmax_scale, cudaStream_t stream);
+// head_dim 256 on tcgen05 tensor cores with accumulators in tensor memory
+// (prefill_attention_sm100.cu); arguments already validated by the caller.
+cudaError_t prefill_attention_sm100_bf16(__nv_bfloat16 *out,
+                                         const __nv_bfloat16 *q,
+                                         const __nv_bfloat16 *k,
+                                         const __nv_bfloat16 *v, int batch,
+                                         int seq_len, int q_heads, int kv_heads,
+                                         int window, float softmax_scale,
+                                         cudaStream_t stream);
+// Synchronises; 0, or which wait of the last launch of that kernel ran out.
+int prefill_attention_sm100_fault();
 
 // FP8 e4m3 cache (fp8_cache.cu). args.cache_k / cache_v are unused.
 cudaError_t decode_append_fp8(const AppendArgs &args, uint8_t *cache_k,

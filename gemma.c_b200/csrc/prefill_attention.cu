@@ -19,6 +19,8 @@
 // domain, the score accumulators are reused as the A operand of P*V. With
 // D = 512 the two warps of a row group both compute the full score tile (no
 // exchange) and split the output dims.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "kernels.cuh"
 
@@ -360,6 +362,15 @@ cudaError_t prefill_attention_bf16(__nv_bfloat16 *out, const __nv_bfloat16 *q,
                      seq_len,  q_heads,  kv_heads, window,
                      softmax_scale * 1.4426950408889634f};
   if (head_dim == 256) {
+    // tcgen05 kernel unless B200KV_PREFILL_MMA_SYNC=1 asks for the mma.sync arm
+    static const bool legacy = [] {
+      const char *e = std::getenv("B200KV_PREFILL_MMA_SYNC");
+      return e != nullptr && e[0] == '1';
+    }();
+    if (!legacy) {
+      return prefill_attention_sm100_bf16(out, q, k, v, batch, seq_len, q_heads,
+                                          kv_heads, window, softmax_scale, stream);
+    }
     return launch_prefill_attention<PrefillTraits<256, 1>>(p, batch, stream);
   }
   if (head_dim == 512) {

@@ -198,6 +198,10 @@ int b200kv_prefill_prep_bf16(b200kv_bf16 *d_q_prepared,
  * equal seqlen_k (cudaErrorInvalidValue otherwise, as the reference).
  * b200kv_prefill_attention_bf16 is the attention stage alone on rows that are
  * already prepared (window_size 0: causal only; head_dim 256 or 512).
+ * b200kv_prefill_attention_fault synchronises the device and returns 0, or
+ * which bounded wait of the head_dim-256 tensor-core kernel ran out in the
+ * last launch (1..3; its output is then undefined), or -1 if the word could
+ * not be read. The reference has no counterpart: its kernels do not wait.
  * ------------------------------------------------------------------ */
 int b200kv_flash_attention_sliding_fwd_bf16_norm_rope(
     b200kv_bf16 *d_out, b200kv_bf16 *d_q_prepared, b200kv_bf16 *d_k_prepared,
@@ -222,6 +226,7 @@ int b200kv_prefill_attention_bf16(b200kv_bf16 *d_out,
                                   int32_t q_heads, int32_t kv_heads,
                                   int32_t head_dim, int32_t window_size,
                                   float softmax_scale, b200kv_stream stream);
+int b200kv_prefill_attention_fault(void);
 
 /* ------------------------------------------------------------------ *
  * Cache fill after a prompt: the prepared K/V rows of batch_size sequences of

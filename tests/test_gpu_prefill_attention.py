@@ -43,6 +43,7 @@ def test_prefill_attention_against_double_precision(kv, orc, name, geom, batch, 
     out = torch.full((batch * seq, H, D), 0x7FC0, dtype=torch.int16, device="cuda")
     kv.prefill_attention(out, dev(q), dev(k), dev(v), batch, seq, H, HKV, D, window, scale)
     torch.cuda.synchronize()
+    assert kv.prefill_attention_fault() == 0
     ref, _ = orc.prefill_attention_f64(q, k, v, batch, seq, H, HKV, D, window, scale)
     got = host_u16(out)
     assert not np.isnan(orc.bf16_to_f32(got)).any()
