@@ -1,33 +1,39 @@
 // Prompt attention for head_dim 256 on the fifth-generation tensor cores:
 // tcgen05.mma with both operands in shared memory and the accumulators in
-// tensor memory. Same contract as prefill_attention.cu (which keeps the
-// mma.sync path for head_dim 512 and as the comparison arm): each sequence's
-// query row r sees its own keys c <= r and, with a window, c >= r - window + 1
-// (src/gemma4_flash_attention_prefill.cu:502-540).
+// tensor memory, tiles brought in by TMA. Same contract as prefill_attention.cu
+// (which keeps the mma.sync path for head_dim 512 and as the comparison arm):
+// each sequence's query row r sees its own keys c <= r and, with a window,
+// c >= r - window + 1 (src/gemma4_flash_attention_prefill.cu:502-540).
 //
-// One CTA = 128 query rows of one query head, 128 threads, thread = row.
-//   shared memory: Q (128 x 256), two stages of K and of V (64 keys x 256
-//     each), P (128 x 64), all bf16, all stored as column blocks of 64 elements
-//     (128 bytes per row) whose 16-byte chunks are XOR-permuted by the row index
-//     -- the canonical 128-byte-swizzled layout that tcgen05 smem descriptors
-//     name, K-major for Q, K and P, MN-major for V. The tiles are filled with
-//     cp.async (16 bytes per thread), so no tensor maps are needed.
-//   tensor memory: S[2] (128 lanes x 64 columns fp32, double-buffered) and O
-//     (128 x 256 fp32); lane = query row.
-//   per 64-key tile: 16 MMAs (M 128, N 64, K 16) give S = Q K^T; every thread
-//     reads its row of S with tcgen05.ld, does the online softmax on it without
-//     any shuffle, writes the bf16 weights as its row of P; 4 MMAs (M 128,
-//     N 256, K 16) add P V to O. One elected thread issues the MMAs and commits
-//     them to mbarriers; the scores of the next tile are computed while the
-//     threads work on the softmax of this one.
-//   The running maximum a row scales by is only raised when the tile's maximum
-//     exceeds it by more than 2^8 (the weights then stay below 256, exact enough
-//     in bf16 and fp32), so the rescaling of O in tensor memory is rare.
-// Every wait is bounded (tens of milliseconds: a tile takes microseconds); a wait
-// that runs out records which one in a device-side fault word, makes the CTA
-// skip to the exit, which always frees the tensor memory, and makes the CTAs
-// that start later return at once. The host clears the word before each launch
-// and reads it through prefill_attention_sm100_fault().
+// One CTA = 128 query rows of one query head, key tiles of 128. Ten warps:
+//   warps 0-7  softmax: two threads per query row, 64 key columns each
+//   warp 8     one thread issues the TMA loads (Q once, then K and V tiles)
+//   warp 9     one thread issues the MMAs and commits them to mbarriers
+// shared memory: Q (128 x 256), K and V (128 keys x 256, one stage each) and
+//   P (128 x 128), all bf16, all as column blocks of 64 elements (128 bytes per
+//   row) in the 128-byte swizzle that both the tensor maps and the tcgen05 smem
+//   descriptors name; K-major for Q, K and P, MN-major for V.
+// tensor memory (512 columns): S[2] (128 lanes x 128 columns fp32, double-
+//   buffered) and O (128 x 256 fp32); lane = query row.
+// per key tile: 16 MMAs (M 128, N 128, K 16) give S = Q K^T; the softmax threads
+//   read their row of S with tcgen05.ld, do the online softmax without a shuffle
+//   (the two threads of a row exchange their maxima through shared memory),
+//   write the bf16 weights as their row of P; 8 MMAs (M 128, N 256, K 16) add
+//   P V to O. K of the next tile is loaded as soon as Q K^T of this one is
+//   done, and its scores are computed while the threads do this tile's softmax;
+//   V of the next tile is loaded as soon as P V of this one is done.
+// The running maximum a row scales by is only raised when the tile's maximum
+// exceeds it by more than 2^8 (the weights then stay below 256, exact enough in
+// bf16 and fp32), so the rescaling of O in tensor memory is rare.
+//
+// Every wait is bounded (tens of milliseconds: a tile takes microseconds). A
+// wait that runs out records which one in a device-side fault word and raises
+// the CTA's abort flag, which every other wait polls; all roles then fall
+// through to the common exit, which waits (bounded) for the loads in flight and
+// frees the tensor memory. CTAs that start later return at once. The host clears
+// the word before each launch and reads it through prefill_attention_sm100_fault().
+#include <cuda.h>
+
 #include "common.cuh"
 #include "kernels.cuh"
 
@@ -37,25 +43,27 @@ namespace {
 
 constexpr int kD = 256;
 constexpr int kBlockM = 128;
-constexpr int kBlockN = 64;
-constexpr int kThreads = 128;
-constexpr int kQBytes = kBlockM * kD * 2;         // 64 KiB: 4 column blocks of 16 KiB
-constexpr int kKvTileBytes = kBlockN * kD * 2;    // 32 KiB: 4 column blocks of 8 KiB
-constexpr int kPBytes = kBlockM * kBlockN * 2;    // 16 KiB: one column block
-constexpr int kSmemBytes = kQBytes + 4 * kKvTileBytes + kPBytes + 1024;  // + alignment slack
-constexpr uint32_t kTmemColumns = 512;            // S[2] at 0 and 64, O at 128
-constexpr uint32_t kTmemO = 128;
-constexpr float kRescaleSlack = 8.0f;             // log2 units
-constexpr long long kTileWaitClocks = 1ll << 26;  // ~35 ms
+constexpr int kBlockN = 128;
+constexpr int kHalfN = kBlockN / 2;
+constexpr int kSoftmaxThreads = 256;
+constexpr int kSoftmaxWarps = kSoftmaxThreads / 32;
+constexpr int kThreads = kSoftmaxThreads + 64;
+constexpr int kBlockBytes = 128 * 128;                  // 128 rows x 64 elements
+constexpr int kQBytes = kBlockM * kD * 2;               // 4 column blocks
+constexpr int kKvTileBytes = kBlockN * kD * 2;          // 4 column blocks
+constexpr int kPBytes = kBlockM * kBlockN * 2;          // 2 column blocks
+constexpr int kTileBytes = kQBytes + 2 * kKvTileBytes + kPBytes;
+constexpr uint32_t kTmemColumns = 512;                  // S[2] at 0 and 128, O at 256
+constexpr uint32_t kTmemO = 2 * kBlockN;
+constexpr float kRescaleSlack = 8.0f;                   // log2 units
+constexpr long long kTileWaitClocks = 1ll << 26;        // ~35 ms
 
-// 0, or which wait ran out: 1 P V of the previous tile, 2 scores, 3 last P V
+// 0, or which wait ran out: 1 softmax on scores, 2 softmax on P V, 3 loader,
+// 4 MMA issuer, 5 last P V; 6: the shared-memory window was not 1024-byte aligned
 __device__ int g_prefill_sm100_fault;
 
 struct Sm100PrefillParams {
   __nv_bfloat16 *out;
-  const __nv_bfloat16 *q;
-  const __nv_bfloat16 *k;
-  const __nv_bfloat16 *v;
   int32_t seq_len;
   int32_t q_heads;
   int32_t kv_heads;
@@ -99,7 +107,7 @@ __device__ __forceinline__ void tc_fence_before() {
 __device__ __forceinline__ void tc_fence_after() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&r)[32]) {
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float *r) {
   uint32_t u[32];
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -117,7 +125,7 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&r)[32]) {
 #pragma unroll
   for (int i = 0; i < 32; ++i) r[i] = __uint_as_float(u[i]);
 }
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&r)[32]) {
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float *r) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
       "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,"
@@ -142,48 +150,56 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&r)[32]) 
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
-__device__ __forceinline__ void cp16(uint32_t dst, const void *src, bool valid) {
-  const int bytes = valid ? 16 : 0;  // 0: zero-filled
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src),
-               "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ void cp_commit() {
-  asm volatile("cp.async.commit_group;" ::: "memory");
-}
-__device__ __forceinline__ void cp_wait_all() {
-  asm volatile("cp.async.wait_group 0;" ::: "memory");
+// One box of 128 rows x 64 elements of a [batch][token][elements] tensor into a
+// swizzled column block; bytes counted on the mbarrier (rows past the sequence
+// arrive as zeros and count all the same).
+__device__ __forceinline__ void tma_load_block(uint32_t dst, const CUtensorMap *map,
+                                               int x, int y, int z, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(bar)
+      : "memory");
 }
 
-// All threads: `rows` rows of 256 elements (row r at src + r * stride elements,
-// zero beyond valid_rows) into a tile of four column blocks of `rows` rows.
-__device__ __forceinline__ void load_rows(uint32_t dst, const __nv_bfloat16 *src,
-                                          int64_t stride, int rows,
-                                          int valid_rows) {
-  const int chunks = rows * 32;
-  for (int i = int(threadIdx.x); i < chunks; i += kThreads) {
-    const int r = i >> 5;
-    const int c = i & 31;
-    const bool valid = r < valid_rows;
-    const __nv_bfloat16 *from = src + (valid ? int64_t(r) * stride : 0) + c * 8;
-    cp16(dst + uint32_t(c >> 3) * uint32_t(rows) * 128u + uint32_t(r) * 128u +
-             (uint32_t((c & 7) ^ (r & 7)) << 4),
-         from, valid);
-  }
-}
+struct Barriers {
+  uint64_t q_full;
+  uint64_t k_full;
+  uint64_t v_full;
+  uint64_t s_full[2];   // Q K^T into S[b] done (also: the K stage is free)
+  uint64_t s_empty[2];  // the softmax warps have read S[b]
+  uint64_t p_full;      // the softmax warps have written P
+  uint64_t pv_done;     // P V done: P and the V stage are free, O is stable
+};
+
+struct SmallState {
+  Barriers bars;
+  uint32_t tmem_base;
+  int abort;
+  float row_max[2][2][kBlockM];  // [tile parity][column half][row]
+};
+constexpr int kSmemBytes = kTileBytes + int(sizeof(SmallState));
 
 __global__ __launch_bounds__(kThreads, 1) void prefill_attention_sm100_kernel(
-    Sm100PrefillParams p) {
-  extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t s_bars[3];  // S[0], S[1] ready; P V done
-  __shared__ uint32_t s_tmem_base;
-  // 128-byte-swizzled tiles want 1024-byte alignment
-  const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t s_q = smem0;
+    Sm100PrefillParams p, const __grid_constant__ CUtensorMap map_q,
+    const __grid_constant__ CUtensorMap map_k,
+    const __grid_constant__ CUtensorMap map_v) {
+  // All shared memory is dynamic: the four tiles, 1024-byte aligned as their
+  // 128-byte swizzle wants (the window of a kernel without static shared memory
+  // starts on such a boundary; checked below), then the small state.
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  SmallState &small = *reinterpret_cast<SmallState *>(smem_raw + kTileBytes);
+  Barriers &s_bars = small.bars;
+  float(&s_max)[2][2][kBlockM] = small.row_max;
+  const uint32_t s_q = smem_u32(smem_raw);
   const uint32_t s_k = s_q + kQBytes;
-  const uint32_t s_v = s_k + 2 * kKvTileBytes;
-  const uint32_t s_p = s_v + 2 * kKvTileBytes;
-  uint8_t *p_generic = smem_raw + (s_p - smem_u32(smem_raw));
+  const uint32_t s_v = s_k + kKvTileBytes;
+  const uint32_t s_p = s_v + kKvTileBytes;
+  uint8_t *p_generic = smem_raw + (kQBytes + 2 * kKvTileBytes);
+  if ((s_q & 1023u) != 0) {
+    if (threadIdx.x == 0) atomicCAS(&g_prefill_sm100_fault, 0, 6);
+    return;
+  }
 
   // an earlier CTA gave up: the whole CTA returns, on one common reading
   if (__syncthreads_or(*reinterpret_cast<volatile int *>(&g_prefill_sm100_fault) != 0)) {
@@ -191,230 +207,291 @@ __global__ __launch_bounds__(kThreads, 1) void prefill_attention_sm100_kernel(
   }
   const int tid = int(threadIdx.x);
   const int warp = tid >> 5;
+  const int lane = tid & 31;
   const int S = p.seq_len;
   const int m_block = int(gridDim.x) - 1 - int(blockIdx.x);  // longest first
   const int batch = int(blockIdx.y);
   const int head = int(blockIdx.z);
   const int kv_head = head / (p.q_heads / p.kv_heads);
   const int m0 = m_block * kBlockM;
-  const int row = m0 + tid;
-  const int64_t seq_row0 = int64_t(batch) * S;
-  const int64_t q_stride = int64_t(p.q_heads) * kD;
-  const int64_t kv_stride = int64_t(p.kv_heads) * kD;
-  const __nv_bfloat16 *q_src = p.q + ((seq_row0 + m0) * p.q_heads + head) * kD;
-  const __nv_bfloat16 *k_base = p.k + (seq_row0 * p.kv_heads + kv_head) * kD;
-  const __nv_bfloat16 *v_base = p.v + (seq_row0 * p.kv_heads + kv_head) * kD;
   const int last_row = min(m0 + kBlockM, S) - 1;
   const int tile_hi = last_row / kBlockN;
   const int tile_lo = p.window > 0 ? max(0, m0 - p.window + 1) / kBlockN : 0;
+  const int tiles = tile_hi - tile_lo + 1;
 
-  const uint32_t bar_s0 = smem_u32(&s_bars[0]);  // S[b] ready at bar_s0 + 8 b
-  const uint32_t bar_o = smem_u32(&s_bars[2]);
+  const uint32_t bar_q_full = smem_u32(&s_bars.q_full);
+  const uint32_t bar_k_full = smem_u32(&s_bars.k_full);
+  const uint32_t bar_v_full = smem_u32(&s_bars.v_full);
+  const uint32_t bar_s_full = smem_u32(&s_bars.s_full[0]);    // + 8 b
+  const uint32_t bar_s_empty = smem_u32(&s_bars.s_empty[0]);  // + 8 b
+  const uint32_t bar_p_full = smem_u32(&s_bars.p_full);
+  const uint32_t bar_pv_done = smem_u32(&s_bars.pv_done);
   if (tid == 0) {
-    mbar_init(bar_s0, 1);
-    mbar_init(bar_s0 + 8, 1);
-    mbar_init(bar_o, 1);
+    mbar_init(bar_q_full, 1);
+    mbar_init(bar_k_full, 1);
+    mbar_init(bar_v_full, 1);
+    mbar_init(bar_s_full, 1);
+    mbar_init(bar_s_full + 8, 1);
+    mbar_init(bar_s_empty, kSoftmaxWarps);
+    mbar_init(bar_s_empty + 8, kSoftmaxWarps);
+    mbar_init(bar_p_full, kSoftmaxWarps);
+    mbar_init(bar_pv_done, 1);
+    small.abort = 0;
     mbar_fence_init();
   }
   if (warp == 0) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                     smem_u32(&s_tmem_base)),
+                     smem_u32(&small.tmem_base)),
                  "r"(kTmemColumns)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::
                      : "memory");
   }
-  load_rows(s_q, q_src, q_stride, kBlockM, S - m0);
-  load_rows(s_k, k_base + int64_t(tile_lo) * kBlockN * kv_stride, kv_stride, kBlockN,
-            S - tile_lo * kBlockN);
-  load_rows(s_v, v_base + int64_t(tile_lo) * kBlockN * kv_stride, kv_stride, kBlockN,
-            S - tile_lo * kBlockN);
-  cp_commit();
-  cp_wait_all();
-  fence_proxy_async_shared();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem = s_tmem_base;
-  const uint32_t lane_base = uint32_t(32 * warp) << 16;
+  const uint32_t tmem = small.tmem_base;
+  volatile int *abort_flag = &small.abort;
 
-  constexpr uint32_t kIdescQK = umma_idesc(kBlockN, false);
-  constexpr uint32_t kIdescPV = umma_idesc(kD, true);
-  // S[buf] = Q K(stage)^T: 16 steps of 16 dims; a step moves 32 bytes inside a
-  // column block, four steps move to the next block
-  auto issue_qk = [&](int stage, int buf) {
-    const uint32_t k_tile = s_k + uint32_t(stage) * kKvTileBytes;
-#pragma unroll
-    for (int ks = 0; ks < kD / 16; ++ks) {
-      const uint32_t blk = uint32_t(ks >> 2), in = uint32_t(ks & 3) * 32u;
-      umma_bf16(tmem + uint32_t(buf) * kBlockN,
-                umma_desc(s_q + blk * (kBlockM * 128u) + in, 1, 64),
-                umma_desc(k_tile + blk * (kBlockN * 128u) + in, 1, 64), kIdescQK,
-                ks > 0);
-    }
-    umma_commit(bar_s0 + 8u * uint32_t(buf));
-  };
-  // O (+)= P V(stage): 4 steps of 16 keys; V is MN-major: 8-key groups 1024
-  // bytes apart, 64-dim blocks kBlockN * 128 bytes apart
-  auto issue_pv = [&](int stage, bool accumulate) {
-    const uint32_t v_tile = s_v + uint32_t(stage) * kKvTileBytes;
-#pragma unroll
-    for (int j = 0; j < kBlockN / 16; ++j) {
-      umma_bf16(tmem + kTmemO, umma_desc(s_p + uint32_t(j) * 32u, 1, 64),
-                umma_desc(v_tile + uint32_t(j) * 2048u, (kBlockN * 128u) >> 4, 64),
-                kIdescPV, accumulate || j > 0);
-    }
-    umma_commit(bar_o);
-  };
-
-  if (tid == 0) issue_qk(0, 0);
-
-  float m_ref = -INFINITY;  // the maximum this row's weights are scaled by
-  float l_run = 0.0f;
-  int fault = 0;          // which wait of this thread ran out
-  bool ok = true;
-  uint32_t s_phase = 0;   // bit b: parity of the next completion of S[b]
-  uint32_t o_phase = 0;
-  for (int tile = tile_lo; tile <= tile_hi; ++tile) {
-    const int it = tile - tile_lo;
-    const int stage = it & 1;
-    const int buf = it & 1;
-    const int k0 = tile * kBlockN;
-    // P V of the previous tile done: its V stage and P are free, O is stable
-    if (it > 0) {
-      if (!mbar_wait_bounded(bar_o, o_phase, kTileWaitClocks)) fault = 1;
-      o_phase ^= 1;
-    }
-    if (tile < tile_hi) {  // the next K / V tile goes into the other stage
-      const int nxt = tile + 1;
-      load_rows(s_k + uint32_t(stage ^ 1) * kKvTileBytes,
-                k_base + int64_t(nxt) * kBlockN * kv_stride, kv_stride, kBlockN,
-                S - nxt * kBlockN);
-      load_rows(s_v + uint32_t(stage ^ 1) * kKvTileBytes,
-                v_base + int64_t(nxt) * kBlockN * kv_stride, kv_stride, kBlockN,
-                S - nxt * kBlockN);
-      cp_commit();
-    }
-    // this tile's scores
-    if (!mbar_wait_bounded(bar_s0 + 8u * uint32_t(buf), (s_phase >> buf) & 1u,
-                           kTileWaitClocks)) {
-      fault = 2;
-    }
-    s_phase ^= 1u << buf;
-    tc_fence_after();
-    float s[kBlockN];
-    {
-      float lo[32], hi[32];
-      tmem_ld32(tmem + lane_base + uint32_t(buf) * kBlockN, lo);
-      tmem_ld32(tmem + lane_base + uint32_t(buf) * kBlockN + 32, hi);
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        s[i] = lo[i];
-        s[32 + i] = hi[i];
+  // Bounded wait that also gives up when another role has; false = give up.
+  auto wait = [&](uint32_t bar, uint32_t parity, int code) -> bool {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long start = clock64();
+    for (uint32_t poll = 0;; ++poll) {
+      if (mbar_try_wait(bar, parity)) return true;
+      if ((poll & 31u) == 31u) {
+        if (*abort_flag != 0) return false;
+        if (clock64() - start > kTileWaitClocks) {
+          atomicCAS(&g_prefill_sm100_fault, 0, code);
+          *abort_flag = 1;
+          return false;
+        }
       }
     }
-    // the next tile's keys have landed: its scores run under this softmax
-    if (tile < tile_hi) {
-      cp_wait_all();
-      fence_proxy_async_shared();
+  };
+
+  if (warp == kSoftmaxWarps) {
+    // ------------------------------------------------------------ loader
+    if (lane == 0) {
+      mbar_arrive_expect_tx(bar_q_full, kQBytes);
+#pragma unroll
+      for (int blk = 0; blk < kD / 64; ++blk) {
+        tma_load_block(s_q + blk * kBlockBytes, &map_q, head * kD + blk * 64, m0, batch,
+                       bar_q_full);
+      }
+      int k_issued = 0, v_issued = 0;
+      for (int it = 0; it < tiles; ++it) {
+        const int y = (tile_lo + it) * kBlockN;
+        // K stage free: Q K^T of the previous tile done
+        if (it > 0 && !wait(bar_s_full + 8u * uint32_t((it - 1) & 1),
+                            uint32_t((it - 1) >> 1) & 1u, 3)) {
+          break;
+        }
+        mbar_arrive_expect_tx(bar_k_full, kKvTileBytes);
+#pragma unroll
+        for (int blk = 0; blk < kD / 64; ++blk) {
+          tma_load_block(s_k + blk * kBlockBytes, &map_k, kv_head * kD + blk * 64, y,
+                         batch, bar_k_full);
+        }
+        ++k_issued;
+        // V stage free: P V of the previous tile done
+        if (it > 0 && !wait(bar_pv_done, uint32_t(it - 1) & 1u, 3)) break;
+        mbar_arrive_expect_tx(bar_v_full, kKvTileBytes);
+#pragma unroll
+        for (int blk = 0; blk < kD / 64; ++blk) {
+          tma_load_block(s_v + blk * kBlockBytes, &map_v, kv_head * kD + blk * 64, y,
+                         batch, bar_v_full);
+        }
+        ++v_issued;
+      }
+      if (*abort_flag != 0) {
+        // nobody may be waiting for the last loads any more: see them land
+        // before the CTA gives its shared memory back
+        mbar_wait_bounded(bar_q_full, 0, kTileWaitClocks);
+        mbar_wait_bounded(bar_k_full, uint32_t(k_issued - 1) & 1u, kTileWaitClocks);
+        if (v_issued > 0) {
+          mbar_wait_bounded(bar_v_full, uint32_t(v_issued - 1) & 1u, kTileWaitClocks);
+        }
+      }
     }
-    tc_fence_before();
-    // every thread has read S[buf]; the next K / V are visible to all; and the
-    // CTA agrees on whether any wait ran out
-    if (__syncthreads_or(fault != 0)) {
-      ok = false;
-      break;
+  } else if (warp == kSoftmaxWarps + 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t kIdescQK = umma_idesc(kBlockN, false);
+      constexpr uint32_t kIdescPV = umma_idesc(kD, true);
+      // S[buf] = Q K^T: 16 steps of 16 dims; a step moves 32 bytes inside a
+      // column block, four steps move to the next block
+      auto issue_qk = [&](int buf) {
+#pragma unroll
+        for (int ks = 0; ks < kD / 16; ++ks) {
+          const uint32_t off = uint32_t(ks >> 2) * kBlockBytes + uint32_t(ks & 3) * 32u;
+          umma_bf16(tmem + uint32_t(buf) * kBlockN, umma_desc(s_q + off, 1, 64),
+                    umma_desc(s_k + off, 1, 64), kIdescQK, ks > 0);
+        }
+        umma_commit(bar_s_full + 8u * uint32_t(buf));
+      };
+      // O (+)= P V: 8 steps of 16 keys. P is K-major like Q; V is MN-major:
+      // 8-key groups 1024 bytes apart, 64-dim blocks one column block apart
+      auto issue_pv = [&](bool accumulate) {
+#pragma unroll
+        for (int j = 0; j < kBlockN / 16; ++j) {
+          const uint32_t p_off = uint32_t(j >> 2) * kBlockBytes + uint32_t(j & 3) * 32u;
+          umma_bf16(tmem + kTmemO, umma_desc(s_p + p_off, 1, 64),
+                    umma_desc(s_v + uint32_t(j) * 2048u, kBlockBytes >> 4, 64), kIdescPV,
+                    accumulate || j > 0);
+        }
+        umma_commit(bar_pv_done);
+      };
+      bool ok = wait(bar_q_full, 0, 4) && wait(bar_k_full, 0, 4);
+      if (ok) {
+        tc_fence_after();
+        issue_qk(0);
+      }
+      for (int it = 0; it < tiles && ok; ++it) {
+        if (it + 1 < tiles) {
+          // next tile's scores: its K has landed and S[(it + 1) & 1] has been read
+          const int n = it + 1;
+          ok = wait(bar_k_full, uint32_t(n) & 1u, 4);
+          if (ok && n >= 2) {
+            ok = wait(bar_s_empty + 8u * uint32_t(n & 1), uint32_t((n >> 1) - 1) & 1u, 4);
+          }
+          if (!ok) break;
+          tc_fence_after();
+          issue_qk(n & 1);
+        }
+        ok = wait(bar_v_full, uint32_t(it) & 1u, 4) && wait(bar_p_full, uint32_t(it) & 1u, 4);
+        if (!ok) break;
+        tc_fence_after();
+        issue_pv(it > 0);
+      }
     }
-    if (tile < tile_hi && tid == 0) {
+  } else {
+    // ------------------------------------------------------------ softmax
+    const int half = warp >> 2;  // which 64 of a tile's 128 key columns
+    const int row_in = tid & (kBlockM - 1);
+    const int row = m0 + row_in;
+    const uint32_t lane_base = uint32_t(32 * (warp & 3)) << 16;
+    const int pair_barrier = 1 + (warp & 3);  // the two warps that share 32 rows
+    float m_ref = -INFINITY;  // the maximum this row's weights are scaled by
+    float l_run = 0.0f;       // this thread's half of the row's denominator
+    bool ok = true;
+    for (int it = 0; it < tiles; ++it) {
+      const int tile = tile_lo + it;
+      const int buf = it & 1;
+      const int k0 = tile * kBlockN + half * kHalfN;
+      ok = wait(bar_s_full + 8u * uint32_t(buf), uint32_t(it >> 1) & 1u, 1);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
       tc_fence_after();
-      issue_qk(stage ^ 1, buf ^ 1);
-    }
+      float s[kHalfN];
+      const uint32_t s_at = tmem + lane_base + uint32_t(buf) * kBlockN + uint32_t(half) * kHalfN;
+      tmem_ld32(s_at, s);
+      tmem_ld32(s_at + 32, s + 32);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_s_empty + 8u * uint32_t(buf));
 
-    // ---- online softmax on this row
-    const bool edge = k0 + kBlockN - 1 > m0 ||
-                      (p.window > 0 && k0 < last_row - p.window + 1);
-    float m_tile = -INFINITY;
+      const bool edge = tile * kBlockN + kBlockN - 1 > m0 ||
+                        (p.window > 0 && tile * kBlockN < last_row - p.window + 1);
+      float m_half = -INFINITY;
 #pragma unroll
-    for (int c = 0; c < kBlockN; ++c) {
-      float x = s[c] * p.scale_log2;
-      if (edge) {
-        const int col = k0 + c;
-        if (col > row || (p.window > 0 && col < row - p.window + 1)) x = -INFINITY;
+      for (int c = 0; c < kHalfN; ++c) {
+        float x = s[c] * p.scale_log2;
+        if (edge) {
+          const int col = k0 + c;
+          if (col > row || (p.window > 0 && col < row - p.window + 1)) x = -INFINITY;
+        }
+        s[c] = x;
+        m_half = fmaxf(m_half, x);
       }
-      s[c] = x;
-      m_tile = fmaxf(m_tile, x);
-    }
-    float factor = 1.0f;
-    if (m_tile > m_ref + kRescaleSlack || m_ref == -INFINITY) {
-      if (m_tile > -INFINITY) {
-        factor = m_ref == -INFINITY ? 1.0f : ex2_approx(m_ref - m_tile);
-        m_ref = m_tile;
+      s_max[buf][half][row_in] = m_half;
+      named_barrier_sync(pair_barrier, 64);
+      // both threads of a row take the same decisions
+      const float m_tile = fmaxf(m_half, s_max[buf][half ^ 1][row_in]);
+      float factor = 1.0f;
+      if (m_tile > m_ref + kRescaleSlack || m_ref == -INFINITY) {
+        if (m_tile > -INFINITY) {
+          factor = m_ref == -INFINITY ? 1.0f : ex2_approx(m_ref - m_tile);
+          m_ref = m_tile;
+        }
       }
-    }
-    // tensor-memory accesses are warp-wide: the warp rescales if any row must
-    if (it > 0 && __any_sync(0xffffffffu, factor != 1.0f)) {
-#pragma unroll 1
-      for (int c = 0; c < kD; c += 32) {
-        float o[32];
-        tmem_ld32(tmem + lane_base + kTmemO + uint32_t(c), o);
+      const float m_use = m_ref == -INFINITY ? 0.0f : m_ref;
+      float l_tile = 0.0f;
+      uint32_t packed[kHalfN / 2];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) o[i] *= factor;
-        tmem_st32(tmem + lane_base + kTmemO + uint32_t(c), o);
-      }
-    }
-    l_run *= factor;
-    const float m_use = m_ref == -INFINITY ? 0.0f : m_ref;
-    float l_tile = 0.0f;
-    uint8_t *p_row = p_generic + tid * 128;
-#pragma unroll
-    for (int c8 = 0; c8 < kBlockN / 8; ++c8) {
-      uint32_t packed[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float e0 = ex2_approx(s[8 * c8 + 2 * i] - m_use);
-        const float e1 = ex2_approx(s[8 * c8 + 2 * i + 1] - m_use);
+      for (int i = 0; i < kHalfN / 2; ++i) {
+        const float e0 = ex2_approx(s[2 * i] - m_use);
+        const float e1 = ex2_approx(s[2 * i + 1] - m_use);
         l_tile += e0 + e1;
         const __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
         packed[i] = *reinterpret_cast<const uint32_t *>(&h);
       }
-      *reinterpret_cast<uint4 *>(p_row + ((c8 ^ (tid & 7)) << 4)) =
-          make_uint4(packed[0], packed[1], packed[2], packed[3]);
-    }
-    l_run += l_tile;
-    fence_proxy_async_shared();  // P is read by the tensor core
-    tc_fence_before();
-    __syncthreads();
-    if (tid == 0) {
-      tc_fence_after();
-      issue_pv(stage, it > 0);
-    }
-  }
-
-  // ---- the last P V, then O / l as bf16
-  if (ok && !mbar_wait_bounded(bar_o, o_phase, kTileWaitClocks)) fault = 3;
-  if (fault != 0) atomicCAS(&g_prefill_sm100_fault, 0, fault);
-  ok = !__syncthreads_or(!ok || fault != 0);
-  tc_fence_after();
-  if (ok) {
-    // tensor-memory loads are warp-wide: rows past the sequence take part in
-    // them and only skip the stores
-    const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
-    __nv_bfloat16 *dst = p.out + ((seq_row0 + row) * p.q_heads + head) * kD;
+      l_run = l_run * factor + l_tile;
+      // P V of the previous tile done: P is free, O is stable
+      if (it > 0) {
+        ok = wait(bar_pv_done, uint32_t(it - 1) & 1u, 2);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        // tensor-memory accesses are warp-wide: the warp rescales its half of the
+        // columns of O if any of its rows must
+        if (__any_sync(0xffffffffu, factor != 1.0f)) {
 #pragma unroll 1
-    for (int c = 0; c < kD; c += 32) {
-      float o[32];
-      tmem_ld32(tmem + lane_base + kTmemO + uint32_t(c), o);
-      if (row < S) {
+          for (int c = 0; c < kD / 2; c += 32) {
+            float o[32];
+            const uint32_t at = tmem + lane_base + kTmemO + uint32_t(half * (kD / 2) + c);
+            tmem_ld32(at, o);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          uint32_t w[4];
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const __nv_bfloat162 h = __floats2bfloat162_rn(
-                o[8 * i + 2 * j] * inv, o[8 * i + 2 * j + 1] * inv);
-            w[j] = *reinterpret_cast<const uint32_t *>(&h);
+            for (int i = 0; i < 32; ++i) o[i] *= factor;
+            tmem_st32(at, o);
           }
-          reinterpret_cast<uint4 *>(dst + c)[i] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      }
+      // this thread's 64 weights: 8 chunks of one 128-byte row of column block `half`
+      uint8_t *p_row = p_generic + half * kBlockBytes + row_in * 128;
+#pragma unroll
+      for (int c8 = 0; c8 < kHalfN / 8; ++c8) {
+        *reinterpret_cast<uint4 *>(p_row + ((c8 ^ (row_in & 7)) << 4)) =
+            make_uint4(packed[4 * c8], packed[4 * c8 + 1], packed[4 * c8 + 2],
+                       packed[4 * c8 + 3]);
+      }
+      fence_proxy_async_shared();  // P is read by the tensor core
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_p_full);
+    }
+
+    // ---- the last P V, then O / l as bf16
+    if (ok) {
+      ok = wait(bar_pv_done, uint32_t(tiles - 1) & 1u, 5);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      tc_fence_after();
+      s_max[0][half][row_in] = l_run;
+      named_barrier_sync(pair_barrier, 64);
+      const float l_row = l_run + s_max[0][half ^ 1][row_in];
+      const float inv = l_row > 0.0f ? 1.0f / l_row : 0.0f;
+      __nv_bfloat16 *dst =
+          p.out + ((int64_t(batch) * S + row) * p.q_heads + head) * kD + half * (kD / 2);
+      // tensor-memory loads are warp-wide: rows past the sequence take part in
+      // them and only skip the stores
+#pragma unroll 1
+      for (int c = 0; c < kD / 2; c += 32) {
+        float o[32];
+        tmem_ld32(tmem + lane_base + kTmemO + uint32_t(half * (kD / 2) + c), o);
+        if (row < S) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const __nv_bfloat162 h = __floats2bfloat162_rn(o[8 * i + 2 * j] * inv,
+                                                             o[8 * i + 2 * j + 1] * inv);
+              w[j] = *reinterpret_cast<const uint32_t *>(&h);
+            }
+            reinterpret_cast<uint4 *>(dst + c)[i] = make_uint4(w[0], w[1], w[2], w[3]);
+          }
         }
       }
     }
@@ -428,6 +505,45 @@ __global__ __launch_bounds__(kThreads, 1) void prefill_attention_sm100_kernel(
   }
 }
 
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                   const cuuint64_t *, const cuuint64_t *,
+                                   const cuuint32_t *, const cuuint32_t *,
+                                   CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void *ptr = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault,
+                                &result) != cudaSuccess ||
+        result != cudaDriverEntryPointSuccess) {
+      return EncodeTiledFn(nullptr);
+    }
+    return reinterpret_cast<EncodeTiledFn>(ptr);
+  }();
+  return fn;
+}
+
+// [batch][token][heads * 256] bf16, boxes of 128 tokens x 64 elements, 128-byte
+// swizzle; tokens past the sequence read as zeros.
+bool make_rows_map(CUtensorMap *map, const __nv_bfloat16 *base, int batch, int seq_len,
+                   int heads) {
+  EncodeTiledFn encode = encode_tiled_fn();
+  if (encode == nullptr) return false;
+  const cuuint64_t dims[3] = {cuuint64_t(heads) * kD, cuuint64_t(seq_len),
+                              cuuint64_t(batch)};
+  const cuuint64_t strides[2] = {cuuint64_t(heads) * kD * 2,
+                                 cuuint64_t(seq_len) * heads * kD * 2};
+  const cuuint32_t box[3] = {64, 128, 1};
+  const cuuint32_t elem_strides[3] = {1, 1, 1};
+  return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
+                const_cast<__nv_bfloat16 *>(base), dims, strides, box, elem_strides,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 }  // namespace
 
 cudaError_t prefill_attention_sm100_bf16(__nv_bfloat16 *out,
@@ -438,9 +554,15 @@ cudaError_t prefill_attention_sm100_bf16(__nv_bfloat16 *out,
                                          int window, float softmax_scale,
                                          cudaStream_t stream) {
   static_assert(kSmemBytes <= 227 * 1024, "tiles must fit one SM");
-  Sm100PrefillParams p = {out,     q,        k,      v,
-                          seq_len, q_heads,  kv_heads, window,
-                          softmax_scale * 1.4426950408889634f};
+  static_assert(kBlockM == 128 && kBlockN == 128, "boxes are 128 rows");
+  CUtensorMap map_q, map_k, map_v;
+  if (!make_rows_map(&map_q, q, batch, seq_len, q_heads) ||
+      !make_rows_map(&map_k, k, batch, seq_len, kv_heads) ||
+      !make_rows_map(&map_v, v, batch, seq_len, kv_heads)) {
+    return cudaErrorInvalidValue;
+  }
+  Sm100PrefillParams p = {out,    seq_len, q_heads, kv_heads,
+                          window, softmax_scale * 1.4426950408889634f};
   cudaError_t st = cudaFuncSetAttribute(
       prefill_attention_sm100_kernel,
       cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
@@ -452,7 +574,8 @@ cudaError_t prefill_attention_sm100_bf16(__nv_bfloat16 *out,
   if (st != cudaSuccess) return st;
   const dim3 grid(unsigned(div_up(seq_len, kBlockM)), unsigned(batch),
                   unsigned(q_heads));
-  prefill_attention_sm100_kernel<<<grid, kThreads, kSmemBytes, stream>>>(p);
+  prefill_attention_sm100_kernel<<<grid, kThreads, kSmemBytes, stream>>>(p, map_q, map_k,
+                                                                         map_v);
   return cudaGetLastError();
 }
 
