@@ -878,12 +878,12 @@ def run_prefill(args, kv, torch, sampler):
         "metric": "prompt attention (causal, sliding window 1024): TFLOP/s of the attention stage", "unit": "TFLOP/s",
         "value": best["tflops_attention"], "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": best["ms_call"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16 (mma.sync m16n8k16, fp32 accumulate and softmax)", "data": "synthetic",
+        "dtype": "bf16 (sliding: tcgen05.mma, accumulators in tensor memory; global: mma.sync m16n8k16; fp32 accumulate and softmax)", "data": "synthetic",
         "config": {"workload": "next row, not a BASELINE config: gemma4_flash_attention_{sliding,global}_fwd_bf16_norm_rope, "
                                "prompts of %d x %d tokens" % (B, S)},
         "roofline": {"bound": "tensor", "achieved": best["tflops_attention"], "peak": peak, "unit": "TFLOP/s",
                      "frac": best["tflops_attention"] / peak, "traffic": None,
-                     "note": "peak = measured cuBLAS bf16 (tcgen05); this kernel uses the legacy mma.sync path"},
+                     "note": "peak = measured cuBLAS bf16; flops = 4 * head_dim per visible (query, key) pair"},
         "results": results, "gpu_launches": 2 * args.steps, "clocks": clocks,
     }))
 

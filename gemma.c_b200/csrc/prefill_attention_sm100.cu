@@ -5,10 +5,12 @@
 // each sequence's query row r sees its own keys c <= r and, with a window,
 // c >= r - window + 1 (src/gemma4_flash_attention_prefill.cu:502-540).
 //
-// One CTA = 128 query rows of one query head, key tiles of 128. Ten warps:
-//   warps 0-7  softmax: two threads per query row, 64 key columns each
-//   warp 8     one thread issues the TMA loads (Q once, then K and V tiles)
-//   warp 9     one thread issues the MMAs and commits them to mbarriers
+// One CTA = 128 query rows of one query head, key tiles of 128. Nineteen warps:
+//   warps 0-15 softmax: four threads per query row, 32 key columns each (the
+//              softmax is latency-bound per warp; 16 warps hide it)
+//   warp 16    one thread issues the TMA loads of Q (once) and of the K tiles
+//   warp 17    one thread issues the MMAs and commits them to mbarriers
+//   warp 18    one thread issues the TMA loads of the V tiles
 // shared memory: Q (128 x 256), K and V (128 keys x 256, one stage each) and
 //   P (128 x 128), all bf16, all as column blocks of 64 elements (128 bytes per
 //   row) in the 128-byte swizzle that both the tensor maps and the tcgen05 smem
@@ -17,7 +19,7 @@
 //   buffered) and O (128 x 256 fp32); lane = query row.
 // per key tile: 16 MMAs (M 128, N 128, K 16) give S = Q K^T; the softmax threads
 //   read their row of S with tcgen05.ld, do the online softmax without a shuffle
-//   (the two threads of a row exchange their maxima through shared memory),
+//   (the four threads of a row exchange their maxima through shared memory),
 //   write the bf16 weights as their row of P; 8 MMAs (M 128, N 256, K 16) add
 //   P V to O. K of the next tile is loaded as soon as Q K^T of this one is
 //   done, and its scores are computed while the threads do this tile's softmax;
@@ -44,10 +46,10 @@ namespace {
 constexpr int kD = 256;
 constexpr int kBlockM = 128;
 constexpr int kBlockN = 128;
-constexpr int kHalfN = kBlockN / 2;
-constexpr int kSoftmaxThreads = 256;
+constexpr int kQuarterN = kBlockN / 4;
+constexpr int kSoftmaxThreads = 512;
 constexpr int kSoftmaxWarps = kSoftmaxThreads / 32;
-constexpr int kThreads = kSoftmaxThreads + 64;
+constexpr int kThreads = kSoftmaxThreads + 96;
 constexpr int kBlockBytes = 128 * 128;                  // 128 rows x 64 elements
 constexpr int kQBytes = kBlockM * kD * 2;               // 4 column blocks
 constexpr int kKvTileBytes = kBlockN * kD * 2;          // 4 column blocks
@@ -176,7 +178,7 @@ struct SmallState {
   Barriers bars;
   uint32_t tmem_base;
   int abort;
-  float row_max[2][2][kBlockM];  // [tile parity][column half][row]
+  __nv_bfloat16 row_max[2][4][kBlockM];  // [tile parity][column quarter][row]
 };
 constexpr int kSmemBytes = kTileBytes + int(sizeof(SmallState));
 
@@ -190,7 +192,7 @@ __global__ __launch_bounds__(kThreads, 1) void prefill_attention_sm100_kernel(
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   SmallState &small = *reinterpret_cast<SmallState *>(smem_raw + kTileBytes);
   Barriers &s_bars = small.bars;
-  float(&s_max)[2][2][kBlockM] = small.row_max;
+  __nv_bfloat16(&s_max)[2][4][kBlockM] = small.row_max;
   const uint32_t s_q = smem_u32(smem_raw);
   const uint32_t s_k = s_q + kQBytes;
   const uint32_t s_v = s_k + kKvTileBytes;
@@ -271,7 +273,7 @@ __global__ __launch_bounds__(kThreads, 1) void prefill_attention_sm100_kernel(
   };
 
   if (warp == kSoftmaxWarps) {
-    // ------------------------------------------------------------ loader
+    // ------------------------------------------------------------ Q and K loader
     if (lane == 0) {
       mbar_arrive_expect_tx(bar_q_full, kQBytes);
 #pragma unroll
@@ -279,9 +281,8 @@ __global__ __launch_bounds__(kThreads, 1) void prefill_attention_sm100_kernel(
         tma_load_block(s_q + blk * kBlockBytes, &map_q, head * kD + blk * 64, m0, batch,
                        bar_q_full);
       }
-      int k_issued = 0, v_issued = 0;
+      int issued = 0;
       for (int it = 0; it < tiles; ++it) {
-        const int y = (tile_lo + it) * kBlockN;
         // K stage free: Q K^T of the previous tile done
         if (it > 0 && !wait(bar_s_full + 8u * uint32_t((it - 1) & 1),
                             uint32_t((it - 1) >> 1) & 1u, 3)) {
@@ -290,28 +291,38 @@ __global__ __launch_bounds__(kThreads, 1) void prefill_attention_sm100_kernel(
         mbar_arrive_expect_tx(bar_k_full, kKvTileBytes);
 #pragma unroll
         for (int blk = 0; blk < kD / 64; ++blk) {
-          tma_load_block(s_k + blk * kBlockBytes, &map_k, kv_head * kD + blk * 64, y,
-                         batch, bar_k_full);
+          tma_load_block(s_k + blk * kBlockBytes, &map_k, kv_head * kD + blk * 64,
+                         (tile_lo + it) * kBlockN, batch, bar_k_full);
         }
-        ++k_issued;
-        // V stage free: P V of the previous tile done
-        if (it > 0 && !wait(bar_pv_done, uint32_t(it - 1) & 1u, 3)) break;
-        mbar_arrive_expect_tx(bar_v_full, kKvTileBytes);
-#pragma unroll
-        for (int blk = 0; blk < kD / 64; ++blk) {
-          tma_load_block(s_v + blk * kBlockBytes, &map_v, kv_head * kD + blk * 64, y,
-                         batch, bar_v_full);
-        }
-        ++v_issued;
+        ++issued;
       }
       if (*abort_flag != 0) {
         // nobody may be waiting for the last loads any more: see them land
         // before the CTA gives its shared memory back
         mbar_wait_bounded(bar_q_full, 0, kTileWaitClocks);
-        mbar_wait_bounded(bar_k_full, uint32_t(k_issued - 1) & 1u, kTileWaitClocks);
-        if (v_issued > 0) {
-          mbar_wait_bounded(bar_v_full, uint32_t(v_issued - 1) & 1u, kTileWaitClocks);
+        if (issued > 0) {
+          mbar_wait_bounded(bar_k_full, uint32_t(issued - 1) & 1u, kTileWaitClocks);
         }
+      }
+    }
+  } else if (warp == kSoftmaxWarps + 2) {
+    // ------------------------------------------------------------ V loader
+    // (its own thread: a V tile waits for P V of the previous tile, a K tile for
+    // Q K^T of the previous tile, and neither should queue behind the other)
+    if (lane == 0) {
+      int issued = 0;
+      for (int it = 0; it < tiles; ++it) {
+        if (it > 0 && !wait(bar_pv_done, uint32_t(it - 1) & 1u, 3)) break;
+        mbar_arrive_expect_tx(bar_v_full, kKvTileBytes);
+#pragma unroll
+        for (int blk = 0; blk < kD / 64; ++blk) {
+          tma_load_block(s_v + blk * kBlockBytes, &map_v, kv_head * kD + blk * 64,
+                         (tile_lo + it) * kBlockN, batch, bar_v_full);
+        }
+        ++issued;
+      }
+      if (*abort_flag != 0 && issued > 0) {
+        mbar_wait_bounded(bar_v_full, uint32_t(issued - 1) & 1u, kTileWaitClocks);
       }
     }
   } else if (warp == kSoftmaxWarps + 1) {
@@ -367,47 +378,56 @@ __global__ __launch_bounds__(kThreads, 1) void prefill_attention_sm100_kernel(
     }
   } else {
     // ------------------------------------------------------------ softmax
-    const int half = warp >> 2;  // which 64 of a tile's 128 key columns
+    const int quarter = warp >> 2;  // which 32 of a tile's 128 key columns
     const int row_in = tid & (kBlockM - 1);
     const int row = m0 + row_in;
     const uint32_t lane_base = uint32_t(32 * (warp & 3)) << 16;
-    const int pair_barrier = 1 + (warp & 3);  // the two warps that share 32 rows
+    const int row_barrier = 1 + (warp & 3);  // the four warps that share 32 rows
+    const float scale = p.scale_log2;
     float m_ref = -INFINITY;  // the maximum this row's weights are scaled by
-    float l_run = 0.0f;       // this thread's half of the row's denominator
+    float l_run = 0.0f;       // this thread's quarter of the row's denominator
     bool ok = true;
     for (int it = 0; it < tiles; ++it) {
       const int tile = tile_lo + it;
       const int buf = it & 1;
-      const int k0 = tile * kBlockN + half * kHalfN;
+      const int k0 = tile * kBlockN + quarter * kQuarterN;
       ok = wait(bar_s_full + 8u * uint32_t(buf), uint32_t(it >> 1) & 1u, 1);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      float s[kHalfN];
-      const uint32_t s_at = tmem + lane_base + uint32_t(buf) * kBlockN + uint32_t(half) * kHalfN;
-      tmem_ld32(s_at, s);
-      tmem_ld32(s_at + 32, s + 32);
+      float s[kQuarterN];
+      tmem_ld32(tmem + lane_base + uint32_t(buf) * kBlockN + uint32_t(quarter) * kQuarterN, s);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_s_empty + 8u * uint32_t(buf));
 
       const bool edge = tile * kBlockN + kBlockN - 1 > m0 ||
                         (p.window > 0 && tile * kBlockN < last_row - p.window + 1);
-      float m_half = -INFINITY;
+      if (edge) {
 #pragma unroll
-      for (int c = 0; c < kHalfN; ++c) {
-        float x = s[c] * p.scale_log2;
-        if (edge) {
+        for (int c = 0; c < kQuarterN; ++c) {
           const int col = k0 + c;
-          if (col > row || (p.window > 0 && col < row - p.window + 1)) x = -INFINITY;
+          if (col > row || (p.window > 0 && col < row - p.window + 1)) s[c] = -INFINITY;
         }
-        s[c] = x;
-        m_half = fmaxf(m_half, x);
       }
-      s_max[buf][half][row_in] = m_half;
-      named_barrier_sync(pair_barrier, 64);
-      // both threads of a row take the same decisions
-      const float m_tile = fmaxf(m_half, s_max[buf][half ^ 1][row_in]);
+      // maximum of the raw scores in four independent chains (the scale is positive)
+      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int c = 0; c < kQuarterN; c += 4) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) mx[u] = fmaxf(mx[u], s[c + u]);
+      }
+      // The four threads of a row publish their maxima rounded to bf16 and all
+      // use the largest published value: the same number in every thread, and
+      // close enough to the true maximum for a scaling reference.
+      const __nv_bfloat16 m_mine =
+          __float2bfloat16_rn(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale);
+      s_max[buf][quarter][row_in] = m_mine;
+      named_barrier_sync(row_barrier, 128);
+      const float m_tile = fmaxf(fmaxf(__bfloat162float(s_max[buf][0][row_in]),
+                                       __bfloat162float(s_max[buf][1][row_in])),
+                                 fmaxf(__bfloat162float(s_max[buf][2][row_in]),
+                                       __bfloat162float(s_max[buf][3][row_in])));
       float factor = 1.0f;
       if (m_tile > m_ref + kRescaleSlack || m_ref == -INFINITY) {
         if (m_tile > -INFINITY) {
@@ -415,31 +435,33 @@ __global__ __launch_bounds__(kThreads, 1) void prefill_attention_sm100_kernel(
           m_ref = m_tile;
         }
       }
-      const float m_use = m_ref == -INFINITY ? 0.0f : m_ref;
-      float l_tile = 0.0f;
-      uint32_t packed[kHalfN / 2];
+      const float neg_m = m_ref == -INFINITY ? 0.0f : -m_ref;
+      float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      uint32_t packed[kQuarterN / 2];
 #pragma unroll
-      for (int i = 0; i < kHalfN / 2; ++i) {
-        const float e0 = ex2_approx(s[2 * i] - m_use);
-        const float e1 = ex2_approx(s[2 * i + 1] - m_use);
-        l_tile += e0 + e1;
+      for (int i = 0; i < kQuarterN / 2; ++i) {
+        const float e0 = ex2_approx(fmaf(s[2 * i], scale, neg_m));
+        const float e1 = ex2_approx(fmaf(s[2 * i + 1], scale, neg_m));
         const __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
-        packed[i] = *reinterpret_cast<const uint32_t *>(&h);
+        const uint32_t u = *reinterpret_cast<const uint32_t *>(&h);
+        packed[i] = u;
+        // the denominator sums the weights as rounded, the ones P V uses
+        sum[i & 3] += __uint_as_float(u << 16) + __uint_as_float(u & 0xffff0000u);
       }
-      l_run = l_run * factor + l_tile;
+      l_run = l_run * factor + ((sum[0] + sum[1]) + (sum[2] + sum[3]));
       // P V of the previous tile done: P is free, O is stable
       if (it > 0) {
         ok = wait(bar_pv_done, uint32_t(it - 1) & 1u, 2);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
-        // tensor-memory accesses are warp-wide: the warp rescales its half of the
-        // columns of O if any of its rows must
+        // tensor-memory accesses are warp-wide: the warp rescales its quarter of
+        // the columns of O if any of its rows must
         if (__any_sync(0xffffffffu, factor != 1.0f)) {
 #pragma unroll 1
-          for (int c = 0; c < kD / 2; c += 32) {
+          for (int c = 0; c < kD / 4; c += 32) {
             float o[32];
-            const uint32_t at = tmem + lane_base + kTmemO + uint32_t(half * (kD / 2) + c);
+            const uint32_t at = tmem + lane_base + kTmemO + uint32_t(quarter * (kD / 4) + c);
             tmem_ld32(at, o);
 #pragma unroll
             for (int i = 0; i < 32; ++i) o[i] *= factor;
@@ -447,11 +469,11 @@ __global__ __launch_bounds__(kThreads, 1) void prefill_attention_sm100_kernel(
           }
         }
       }
-      // this thread's 64 weights: 8 chunks of one 128-byte row of column block `half`
-      uint8_t *p_row = p_generic + half * kBlockBytes + row_in * 128;
+      // this thread's 32 weights: 4 chunks of one 128-byte row of a column block
+      uint8_t *p_row = p_generic + (quarter >> 1) * kBlockBytes + row_in * 128;
 #pragma unroll
-      for (int c8 = 0; c8 < kHalfN / 8; ++c8) {
-        *reinterpret_cast<uint4 *>(p_row + ((c8 ^ (row_in & 7)) << 4)) =
+      for (int c8 = 0; c8 < kQuarterN / 8; ++c8) {
+        *reinterpret_cast<uint4 *>(p_row + ((((quarter & 1) * 4 + c8) ^ (row_in & 7)) << 4)) =
             make_uint4(packed[4 * c8], packed[4 * c8 + 1], packed[4 * c8 + 2],
                        packed[4 * c8 + 3]);
       }
@@ -468,18 +490,21 @@ __global__ __launch_bounds__(kThreads, 1) void prefill_attention_sm100_kernel(
     }
     if (ok) {
       tc_fence_after();
-      s_max[0][half][row_in] = l_run;
-      named_barrier_sync(pair_barrier, 64);
-      const float l_row = l_run + s_max[0][half ^ 1][row_in];
+      // P is no longer read: its first bytes carry the four partial denominators
+      float *l_part = reinterpret_cast<float *>(p_generic);
+      l_part[quarter * kBlockM + row_in] = l_run;
+      named_barrier_sync(row_barrier, 128);
+      const float l_row = (l_part[row_in] + l_part[kBlockM + row_in]) +
+                          (l_part[2 * kBlockM + row_in] + l_part[3 * kBlockM + row_in]);
       const float inv = l_row > 0.0f ? 1.0f / l_row : 0.0f;
       __nv_bfloat16 *dst =
-          p.out + ((int64_t(batch) * S + row) * p.q_heads + head) * kD + half * (kD / 2);
+          p.out + ((int64_t(batch) * S + row) * p.q_heads + head) * kD + quarter * (kD / 4);
       // tensor-memory loads are warp-wide: rows past the sequence take part in
       // them and only skip the stores
 #pragma unroll 1
-      for (int c = 0; c < kD / 2; c += 32) {
+      for (int c = 0; c < kD / 4; c += 32) {
         float o[32];
-        tmem_ld32(tmem + lane_base + kTmemO + uint32_t(half * (kD / 2) + c), o);
+        tmem_ld32(tmem + lane_base + kTmemO + uint32_t(quarter * (kD / 4) + c), o);
         if (row < S) {
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
