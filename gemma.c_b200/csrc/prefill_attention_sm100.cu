@@ -98,6 +98,17 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc,
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(uint32_t(accumulate))
       : "memory");
 }
+// The same with the A operand in tensor memory: lane = row, each 32-bit column
+// two consecutive bf16 of the contraction dimension (8 columns per K = 16).
+__device__ __forceinline__ void umma_bf16_a_tmem(uint32_t d_tmem, uint32_t a_tmem,
+                                                 uint64_t b_desc, uint32_t idesc,
+                                                 bool accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(uint32_t(accumulate))
+      : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile(
       "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
@@ -152,6 +163,17 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float *r) {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t *r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+      "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]),
+      "r"(r[14]), "r"(r[15])
+      : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
 // One box of 128 rows x 64 elements of a [batch][token][elements] tensor into a
 // swizzled column block; bytes counted on the mbarrier (rows past the sequence
 // arrive as zeros and count all the same).
@@ -169,9 +191,8 @@ struct Barriers {
   uint64_t k_full;
   uint64_t v_full;
   uint64_t s_full[2];   // Q K^T into S[b] done (also: the K stage is free)
-  uint64_t s_empty[2];  // the softmax warps have read S[b]
-  uint64_t p_full;      // the softmax warps have written P
-  uint64_t pv_done;     // P V done: P and the V stage are free, O is stable
+  uint64_t p_full;      // the softmax warps have written P over their scores
+  uint64_t pv_done;     // P V done: S[b] (the weights) and the V stage are free, O is stable
 };
 
 struct SmallState {
@@ -225,7 +246,6 @@ __global__ __launch_bounds__(kThreads, 1) void prefill_attention_sm100_kernel(
   const uint32_t bar_k_full = smem_u32(&s_bars.k_full);
   const uint32_t bar_v_full = smem_u32(&s_bars.v_full);
   const uint32_t bar_s_full = smem_u32(&s_bars.s_full[0]);    // + 8 b
-  const uint32_t bar_s_empty = smem_u32(&s_bars.s_empty[0]);  // + 8 b
   const uint32_t bar_p_full = smem_u32(&s_bars.p_full);
   const uint32_t bar_pv_done = smem_u32(&s_bars.pv_done);
   if (tid == 0) {
@@ -234,8 +254,6 @@ __global__ __launch_bounds__(kThreads, 1) void prefill_attention_sm100_kernel(
     mbar_init(bar_v_full, 1);
     mbar_init(bar_s_full, 1);
     mbar_init(bar_s_full + 8, 1);
-    mbar_init(bar_s_empty, kSoftmaxWarps);
-    mbar_init(bar_s_empty + 8, kSoftmaxWarps);
     mbar_init(bar_p_full, kSoftmaxWarps);
     mbar_init(bar_pv_done, 1);
     small.abort = 0;
@@ -341,15 +359,18 @@ __global__ __launch_bounds__(kThreads, 1) void prefill_attention_sm100_kernel(
         }
         umma_commit(bar_s_full + 8u * uint32_t(buf));
       };
-      // O (+)= P V: 8 steps of 16 keys. P is K-major like Q; V is MN-major:
-      // 8-key groups 1024 bytes apart, 64-dim blocks one column block apart
-      auto issue_pv = [&](bool accumulate) {
+      // O (+)= P V: 8 steps of 16 keys. P sits in tensor memory where the scores
+      // were: the thread that read columns [32 q, 32 q + 32) of S[buf] left its 32
+      // weights in the first 16 of them. V is MN-major: 8-key groups 1024 bytes
+      // apart, 64-dim blocks one column block apart
+      auto issue_pv = [&](int buf, bool accumulate) {
 #pragma unroll
         for (int j = 0; j < kBlockN / 16; ++j) {
-          const uint32_t p_off = uint32_t(j >> 2) * kBlockBytes + uint32_t(j & 3) * 32u;
-          umma_bf16(tmem + kTmemO, umma_desc(s_p + p_off, 1, 64),
-                    umma_desc(s_v + uint32_t(j) * 2048u, kBlockBytes >> 4, 64), kIdescPV,
-                    accumulate || j > 0);
+          const uint32_t p_at =
+              tmem + uint32_t(buf) * kBlockN + uint32_t(j >> 1) * kQuarterN + uint32_t(j & 1) * 8u;
+          umma_bf16_a_tmem(tmem + kTmemO, p_at,
+                           umma_desc(s_v + uint32_t(j) * 2048u, kBlockBytes >> 4, 64),
+                           kIdescPV, accumulate || j > 0);
         }
         umma_commit(bar_pv_done);
       };
@@ -360,12 +381,11 @@ __global__ __launch_bounds__(kThreads, 1) void prefill_attention_sm100_kernel(
       }
       for (int it = 0; it < tiles && ok; ++it) {
         if (it + 1 < tiles) {
-          // next tile's scores: its K has landed and S[(it + 1) & 1] has been read
+          // next tile's scores: its K has landed and S[(it + 1) & 1], which held
+          // the weights of tile it - 1, is no longer read
           const int n = it + 1;
           ok = wait(bar_k_full, uint32_t(n) & 1u, 4);
-          if (ok && n >= 2) {
-            ok = wait(bar_s_empty + 8u * uint32_t(n & 1), uint32_t((n >> 1) - 1) & 1u, 4);
-          }
+          if (ok && n >= 2) ok = wait(bar_pv_done, uint32_t(n - 2) & 1u, 4);
           if (!ok) break;
           tc_fence_after();
           issue_qk(n & 1);
@@ -373,7 +393,7 @@ __global__ __launch_bounds__(kThreads, 1) void prefill_attention_sm100_kernel(
         ok = wait(bar_v_full, uint32_t(it) & 1u, 4) && wait(bar_p_full, uint32_t(it) & 1u, 4);
         if (!ok) break;
         tc_fence_after();
-        issue_pv(it > 0);
+        issue_pv(it & 1, it > 0);
       }
     }
   } else {
@@ -396,10 +416,9 @@ __global__ __launch_bounds__(kThreads, 1) void prefill_attention_sm100_kernel(
       if (!ok) break;
       tc_fence_after();
       float s[kQuarterN];
-      tmem_ld32(tmem + lane_base + uint32_t(buf) * kBlockN + uint32_t(quarter) * kQuarterN, s);
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_s_empty + 8u * uint32_t(buf));
+      const uint32_t s_at =
+          tmem + lane_base + uint32_t(buf) * kBlockN + uint32_t(quarter) * kQuarterN;
+      tmem_ld32(s_at, s);
 
       const bool edge = tile * kBlockN + kBlockN - 1 > m0 ||
                         (p.window > 0 && tile * kBlockN < last_row - p.window + 1);
@@ -449,35 +468,26 @@ __global__ __launch_bounds__(kThreads, 1) void prefill_attention_sm100_kernel(
         sum[i & 3] += __uint_as_float(u << 16) + __uint_as_float(u & 0xffff0000u);
       }
       l_run = l_run * factor + ((sum[0] + sum[1]) + (sum[2] + sum[3]));
-      // P V of the previous tile done: P is free, O is stable
-      if (it > 0) {
+      // tensor-memory accesses are warp-wide: the warp rescales its quarter of
+      // the columns of O if any of its rows must, once P V of the previous tile
+      // no longer adds to them
+      if (it > 0 && __any_sync(0xffffffffu, factor != 1.0f)) {
         ok = wait(bar_pv_done, uint32_t(it - 1) & 1u, 2);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
-        // tensor-memory accesses are warp-wide: the warp rescales its quarter of
-        // the columns of O if any of its rows must
-        if (__any_sync(0xffffffffu, factor != 1.0f)) {
 #pragma unroll 1
-          for (int c = 0; c < kD / 4; c += 32) {
-            float o[32];
-            const uint32_t at = tmem + lane_base + kTmemO + uint32_t(quarter * (kD / 4) + c);
-            tmem_ld32(at, o);
+        for (int c = 0; c < kD / 4; c += 32) {
+          float o[32];
+          const uint32_t at = tmem + lane_base + kTmemO + uint32_t(quarter * (kD / 4) + c);
+          tmem_ld32(at, o);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] *= factor;
-            tmem_st32(at, o);
-          }
+          for (int i = 0; i < 32; ++i) o[i] *= factor;
+          tmem_st32(at, o);
         }
       }
-      // this thread's 32 weights: 4 chunks of one 128-byte row of a column block
-      uint8_t *p_row = p_generic + (quarter >> 1) * kBlockBytes + row_in * 128;
-#pragma unroll
-      for (int c8 = 0; c8 < kQuarterN / 8; ++c8) {
-        *reinterpret_cast<uint4 *>(p_row + ((((quarter & 1) * 4 + c8) ^ (row_in & 7)) << 4)) =
-            make_uint4(packed[4 * c8], packed[4 * c8 + 1], packed[4 * c8 + 2],
-                       packed[4 * c8 + 3]);
-      }
-      fence_proxy_async_shared();  // P is read by the tensor core
+      // this thread's 32 weights go where it read its scores from
+      tmem_st16(s_at, packed);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_p_full);
