@@ -123,15 +123,16 @@ cudaError_t prefill_attention_bf16(__nv_bfloat16 *out, const __nv_bfloat16 *q,
                                    int batch, int seq_len, int q_heads,
                                    int kv_heads, int head_dim, int window,
                                    float softmax_scale, cudaStream_t stream);
-// head_dim 256 on tcgen05 tensor cores with accumulators in tensor memory
-// (prefill_attention_sm100.cu); arguments already validated by the caller.
+// The same on tcgen05 tensor cores with accumulators in tensor memory
+// (prefill_attention_sm100.cu), head_dim 256 or 512; arguments already validated
+// by the caller.
 cudaError_t prefill_attention_sm100_bf16(__nv_bfloat16 *out,
                                          const __nv_bfloat16 *q,
                                          const __nv_bfloat16 *k,
                                          const __nv_bfloat16 *v, int batch,
                                          int seq_len, int q_heads, int kv_heads,
-                                         int window, float softmax_scale,
-                                         cudaStream_t stream);
+                                         int head_dim, int window,
+                                         float softmax_scale, cudaStream_t stream);
 // Synchronises; 0, or which wait of the last launch of that kernel ran out.
 int prefill_attention_sm100_fault();
 

@@ -361,16 +361,17 @@ cudaError_t prefill_attention_bf16(__nv_bfloat16 *out, const __nv_bfloat16 *q,
   PrefillParams p = {out,      q,        k,      v,
                      seq_len,  q_heads,  kv_heads, window,
                      softmax_scale * 1.4426950408889634f};
+  if (head_dim != 256 && head_dim != 512) return cudaErrorInvalidValue;
+  // tcgen05 kernel unless B200KV_PREFILL_MMA_SYNC=1 asks for the mma.sync arm
+  static const bool legacy = [] {
+    const char *e = std::getenv("B200KV_PREFILL_MMA_SYNC");
+    return e != nullptr && e[0] == '1';
+  }();
+  if (!legacy) {
+    return prefill_attention_sm100_bf16(out, q, k, v, batch, seq_len, q_heads, kv_heads,
+                                        head_dim, window, softmax_scale, stream);
+  }
   if (head_dim == 256) {
-    // tcgen05 kernel unless B200KV_PREFILL_MMA_SYNC=1 asks for the mma.sync arm
-    static const bool legacy = [] {
-      const char *e = std::getenv("B200KV_PREFILL_MMA_SYNC");
-      return e != nullptr && e[0] == '1';
-    }();
-    if (!legacy) {
-      return prefill_attention_sm100_bf16(out, q, k, v, batch, seq_len, q_heads,
-                                          kv_heads, window, softmax_scale, stream);
-    }
     return launch_prefill_attention<PrefillTraits<256, 1>>(p, batch, stream);
   }
   if (head_dim == 512) {

@@ -1,32 +1,43 @@
-// Prompt attention for head_dim 256 on the fifth-generation tensor cores:
-// tcgen05.mma with both operands in shared memory and the accumulators in
-// tensor memory, tiles brought in by TMA. Same contract as prefill_attention.cu
-// (which keeps the mma.sync path for head_dim 512 and as the comparison arm):
-// each sequence's query row r sees its own keys c <= r and, with a window,
-// c >= r - window + 1 (src/gemma4_flash_attention_prefill.cu:502-540).
+// Prompt attention on the fifth-generation tensor cores: tcgen05.mma with the
+// accumulators (and the softmax weights) in tensor memory, tiles brought in by
+// TMA. Same contract as prefill_attention.cu (which keeps the mma.sync path as
+// the comparison arm): each sequence's query row r sees its own keys c <= r and,
+// with a window, c >= r - window + 1 (src/gemma4_flash_attention_prefill.cu:502-540).
 //
-// One CTA = 128 query rows of one query head, key tiles of 128. Nineteen warps:
-//   warps 0-15 softmax: four threads per query row, 32 key columns each (the
-//              softmax is latency-bound per warp; 16 warps hide it)
+// Two geometries share one kernel template:
+//   head_dim 256 (sliding layers): one CTA = 128 query rows of one query head,
+//     key tiles of 128.
+//   head_dim 512 (global layers): the 512 output dims do not fit tensor memory
+//     beside the scores, so one CTA = 128 query rows of one query head and ONE
+//     HALF of the output dims (256 of V's 512); the two CTAs of a head each
+//     compute the full scores (Q K^T over 512 dims) and the same softmax, and
+//     multiply by their own half of V. Key tiles of 64.
+// Nineteen warps:
+//   warps 0-15 softmax: four threads per query row, a quarter of the tile's key
+//              columns each (the softmax is latency-bound per warp; 16 warps
+//              hide it)
 //   warp 16    one thread issues the TMA loads of Q (once) and of the K tiles
 //   warp 17    one thread issues the MMAs and commits them to mbarriers
 //   warp 18    one thread issues the TMA loads of the V tiles
-// shared memory: Q (128 x 256), K and V (128 keys x 256, one stage each) and
-//   P (128 x 128), all bf16, all as column blocks of 64 elements (128 bytes per
+// shared memory: Q (128 x head_dim), one K tile (keys x head_dim) and one V tile
+//   (keys x 256), all bf16, all as column blocks of 64 elements (128 bytes per
 //   row) in the 128-byte swizzle that both the tensor maps and the tcgen05 smem
-//   descriptors name; K-major for Q, K and P, MN-major for V.
-// tensor memory (512 columns): S[2] (128 lanes x 128 columns fp32, double-
-//   buffered) and O (128 x 256 fp32); lane = query row.
-// per key tile: 16 MMAs (M 128, N 128, K 16) give S = Q K^T; the softmax threads
-//   read their row of S with tcgen05.ld, do the online softmax without a shuffle
-//   (the four threads of a row exchange their maxima through shared memory),
-//   write the bf16 weights as their row of P; 8 MMAs (M 128, N 256, K 16) add
-//   P V to O. K of the next tile is loaded as soon as Q K^T of this one is
-//   done, and its scores are computed while the threads do this tile's softmax;
-//   V of the next tile is loaded as soon as P V of this one is done.
+//   descriptors name; K-major for Q and K, MN-major for V.
+// tensor memory (512 columns): S[2] (128 lanes x tile keys fp32, double-buffered)
+//   and O (128 x 256 fp32); lane = query row.
+// per key tile: head_dim / 16 MMAs (M 128, N = tile keys, K 16) give S = Q K^T;
+//   the softmax threads read their part of their row of S with tcgen05.ld, do the
+//   online softmax without a shuffle (the four threads of a row exchange their
+//   maxima through shared memory) and write the bf16 weights back over the
+//   scores they read (two per 32-bit column); tile keys / 16 MMAs (M 128, N 256,
+//   K 16) with P as the tensor-memory A operand add P V to O. K of the next tile
+//   is loaded as soon as Q K^T of this one is done, and its scores are computed
+//   while the threads do this tile's softmax; V of the next tile is loaded as
+//   soon as P V of this one is done.
 // The running maximum a row scales by is only raised when the tile's maximum
 // exceeds it by more than 2^8 (the weights then stay below 256, exact enough in
-// bf16 and fp32), so the rescaling of O in tensor memory is rare.
+// bf16 and fp32), so the rescaling of O in tensor memory is rare. The denominator
+// sums the weights as rounded to bf16, the numbers P V uses.
 //
 // Every wait is bounded (tens of milliseconds: a tile takes microseconds). A
 // wait that runs out records which one in a device-side fault word and raises
@@ -43,22 +54,31 @@ namespace b200kv {
 
 namespace {
 
-constexpr int kD = 256;
 constexpr int kBlockM = 128;
-constexpr int kBlockN = 128;
-constexpr int kQuarterN = kBlockN / 4;
+constexpr int kDv = 256;                                // output dims per CTA
 constexpr int kSoftmaxThreads = 512;
 constexpr int kSoftmaxWarps = kSoftmaxThreads / 32;
 constexpr int kThreads = kSoftmaxThreads + 96;
-constexpr int kBlockBytes = 128 * 128;                  // 128 rows x 64 elements
-constexpr int kQBytes = kBlockM * kD * 2;               // 4 column blocks
-constexpr int kKvTileBytes = kBlockN * kD * 2;          // 4 column blocks
-constexpr int kPBytes = kBlockM * kBlockN * 2;          // 2 column blocks
-constexpr int kTileBytes = kQBytes + 2 * kKvTileBytes + kPBytes;
-constexpr uint32_t kTmemColumns = 512;                  // S[2] at 0 and 128, O at 256
-constexpr uint32_t kTmemO = 2 * kBlockN;
+constexpr uint32_t kTmemColumns = 512;
 constexpr float kRescaleSlack = 8.0f;                   // log2 units
 constexpr long long kTileWaitClocks = 1ll << 26;        // ~35 ms
+
+template <int kHeadDim_, int kBlockN_>
+struct Sm100Traits {
+  static constexpr int kHeadDim = kHeadDim_;            // contraction dims of Q K^T
+  static constexpr int kBlockN = kBlockN_;              // keys per tile
+  static constexpr int kQuarterN = kBlockN / 4;         // score columns per softmax thread
+  static constexpr int kVSplits = kHeadDim / kDv;       // CTAs that share a head's scores
+  static constexpr int kQBlockBytes = kBlockM * 128;    // 128 rows x 64 elements
+  static constexpr int kKBlockBytes = kBlockN * 128;    // keys x 64 elements
+  static constexpr int kQBytes = kBlockM * kHeadDim * 2;
+  static constexpr int kKBytes = kBlockN * kHeadDim * 2;
+  static constexpr int kVBytes = kBlockN * kDv * 2;
+  static constexpr int kTileBytes = kQBytes + kKBytes + kVBytes;
+  static constexpr uint32_t kTmemO = 2 * kBlockN;       // S[2] at 0 and kBlockN, O behind
+  static_assert(kQuarterN == 32 || kQuarterN == 16, "tensor-memory access shapes");
+  static_assert(kTmemO + kDv <= kTmemColumns, "tensor memory");
+};
 
 // 0, or which wait ran out: 1 softmax on scores, 2 softmax on P V, 3 loader,
 // 4 MMA issuer, 5 last P V; 6: the shared-memory window was not 1024-byte aligned
@@ -186,13 +206,52 @@ __device__ __forceinline__ void tma_load_block(uint32_t dst, const CUtensorMap *
       : "memory");
 }
 
+// kCount fp32 columns of this thread's lane (kCount = 32 or 16)
+template <int kCount>
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, float *r) {
+  if constexpr (kCount == 32) {
+    tmem_ld32(taddr, r);
+  } else {
+    uint32_t u[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]),
+          "=r"(u[6]), "=r"(u[7]), "=r"(u[8]), "=r"(u[9]), "=r"(u[10]), "=r"(u[11]),
+          "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) r[i] = __uint_as_float(u[i]);
+  }
+}
+// kCount packed bf16 pairs into this thread's lane (kCount = 16 or 8)
+template <int kCount>
+__device__ __forceinline__ void tmem_st_packed(uint32_t taddr, const uint32_t *r) {
+  if constexpr (kCount == 16) {
+    tmem_st16(taddr, r);
+  } else {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+        "r"(r[7])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+  }
+}
+
 struct Barriers {
   uint64_t q_full;
   uint64_t k_full;
   uint64_t v_full;
-  uint64_t s_full[2];   // Q K^T into S[b] done (also: the K stage is free)
-  uint64_t p_full;      // the softmax warps have written P over their scores
-  uint64_t pv_done;     // P V done: S[b] (the weights) and the V stage are free, O is stable
+  uint64_t s_full[2];   // Q K^T into S[b] done (also: the K tile is free)
+  // The softmax warps have written P over their scores in S[b]. One barrier per
+  // buffer: the softmax may finish tile it + 1 before the MMA thread has looked
+  // at tile it (it waits for V as well), and a single barrier would then be two
+  // phases ahead of its reader.
+  uint64_t p_full[2];
+  uint64_t pv_done;     // P V done: S[b] (the weights) and the V tile are free, O is stable
 };
 
 struct SmallState {
@@ -201,24 +260,25 @@ struct SmallState {
   int abort;
   __nv_bfloat16 row_max[2][4][kBlockM];  // [tile parity][column quarter][row]
 };
-constexpr int kSmemBytes = kTileBytes + int(sizeof(SmallState));
 
+template <class T>
 __global__ __launch_bounds__(kThreads, 1) void prefill_attention_sm100_kernel(
     Sm100PrefillParams p, const __grid_constant__ CUtensorMap map_q,
     const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v) {
-  // All shared memory is dynamic: the four tiles, 1024-byte aligned as their
+  constexpr int kHeadDim = T::kHeadDim;
+  constexpr int kBlockN = T::kBlockN;
+  constexpr int kQuarterN = T::kQuarterN;
+  // All shared memory is dynamic: the three tiles, 1024-byte aligned as their
   // 128-byte swizzle wants (the window of a kernel without static shared memory
   // starts on such a boundary; checked below), then the small state.
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  SmallState &small = *reinterpret_cast<SmallState *>(smem_raw + kTileBytes);
+  SmallState &small = *reinterpret_cast<SmallState *>(smem_raw + T::kTileBytes);
   Barriers &s_bars = small.bars;
   __nv_bfloat16(&s_max)[2][4][kBlockM] = small.row_max;
   const uint32_t s_q = smem_u32(smem_raw);
-  const uint32_t s_k = s_q + kQBytes;
-  const uint32_t s_v = s_k + kKvTileBytes;
-  const uint32_t s_p = s_v + kKvTileBytes;
-  uint8_t *p_generic = smem_raw + (kQBytes + 2 * kKvTileBytes);
+  const uint32_t s_k = s_q + T::kQBytes;
+  const uint32_t s_v = s_k + T::kKBytes;
   if ((s_q & 1023u) != 0) {
     if (threadIdx.x == 0) atomicCAS(&g_prefill_sm100_fault, 0, 6);
     return;
@@ -234,7 +294,8 @@ __global__ __launch_bounds__(kThreads, 1) void prefill_attention_sm100_kernel(
   const int S = p.seq_len;
   const int m_block = int(gridDim.x) - 1 - int(blockIdx.x);  // longest first
   const int batch = int(blockIdx.y);
-  const int head = int(blockIdx.z);
+  const int head = int(blockIdx.z) / T::kVSplits;
+  const int v_part = int(blockIdx.z) % T::kVSplits;  // which 256 of V's dims
   const int kv_head = head / (p.q_heads / p.kv_heads);
   const int m0 = m_block * kBlockM;
   const int last_row = min(m0 + kBlockM, S) - 1;
@@ -246,7 +307,7 @@ __global__ __launch_bounds__(kThreads, 1) void prefill_attention_sm100_kernel(
   const uint32_t bar_k_full = smem_u32(&s_bars.k_full);
   const uint32_t bar_v_full = smem_u32(&s_bars.v_full);
   const uint32_t bar_s_full = smem_u32(&s_bars.s_full[0]);    // + 8 b
-  const uint32_t bar_p_full = smem_u32(&s_bars.p_full);
+  const uint32_t bar_p_full = smem_u32(&s_bars.p_full[0]);    // + 8 b
   const uint32_t bar_pv_done = smem_u32(&s_bars.pv_done);
   if (tid == 0) {
     mbar_init(bar_q_full, 1);
@@ -255,6 +316,7 @@ __global__ __launch_bounds__(kThreads, 1) void prefill_attention_sm100_kernel(
     mbar_init(bar_s_full, 1);
     mbar_init(bar_s_full + 8, 1);
     mbar_init(bar_p_full, kSoftmaxWarps);
+    mbar_init(bar_p_full + 8, kSoftmaxWarps);
     mbar_init(bar_pv_done, 1);
     small.abort = 0;
     mbar_fence_init();
@@ -293,23 +355,23 @@ __global__ __launch_bounds__(kThreads, 1) void prefill_attention_sm100_kernel(
   if (warp == kSoftmaxWarps) {
     // ------------------------------------------------------------ Q and K loader
     if (lane == 0) {
-      mbar_arrive_expect_tx(bar_q_full, kQBytes);
+      mbar_arrive_expect_tx(bar_q_full, T::kQBytes);
 #pragma unroll
-      for (int blk = 0; blk < kD / 64; ++blk) {
-        tma_load_block(s_q + blk * kBlockBytes, &map_q, head * kD + blk * 64, m0, batch,
-                       bar_q_full);
+      for (int blk = 0; blk < kHeadDim / 64; ++blk) {
+        tma_load_block(s_q + blk * T::kQBlockBytes, &map_q, head * kHeadDim + blk * 64, m0,
+                       batch, bar_q_full);
       }
       int issued = 0;
       for (int it = 0; it < tiles; ++it) {
-        // K stage free: Q K^T of the previous tile done
+        // K tile free: Q K^T of the previous tile done
         if (it > 0 && !wait(bar_s_full + 8u * uint32_t((it - 1) & 1),
                             uint32_t((it - 1) >> 1) & 1u, 3)) {
           break;
         }
-        mbar_arrive_expect_tx(bar_k_full, kKvTileBytes);
+        mbar_arrive_expect_tx(bar_k_full, T::kKBytes);
 #pragma unroll
-        for (int blk = 0; blk < kD / 64; ++blk) {
-          tma_load_block(s_k + blk * kBlockBytes, &map_k, kv_head * kD + blk * 64,
+        for (int blk = 0; blk < kHeadDim / 64; ++blk) {
+          tma_load_block(s_k + blk * T::kKBlockBytes, &map_k, kv_head * kHeadDim + blk * 64,
                          (tile_lo + it) * kBlockN, batch, bar_k_full);
         }
         ++issued;
@@ -331,10 +393,11 @@ __global__ __launch_bounds__(kThreads, 1) void prefill_attention_sm100_kernel(
       int issued = 0;
       for (int it = 0; it < tiles; ++it) {
         if (it > 0 && !wait(bar_pv_done, uint32_t(it - 1) & 1u, 3)) break;
-        mbar_arrive_expect_tx(bar_v_full, kKvTileBytes);
+        mbar_arrive_expect_tx(bar_v_full, T::kVBytes);
 #pragma unroll
-        for (int blk = 0; blk < kD / 64; ++blk) {
-          tma_load_block(s_v + blk * kBlockBytes, &map_v, kv_head * kD + blk * 64,
+        for (int blk = 0; blk < kDv / 64; ++blk) {
+          tma_load_block(s_v + blk * T::kKBlockBytes, &map_v,
+                         kv_head * kHeadDim + v_part * kDv + blk * 64,
                          (tile_lo + it) * kBlockN, batch, bar_v_full);
         }
         ++issued;
@@ -347,29 +410,32 @@ __global__ __launch_bounds__(kThreads, 1) void prefill_attention_sm100_kernel(
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t kIdescQK = umma_idesc(kBlockN, false);
-      constexpr uint32_t kIdescPV = umma_idesc(kD, true);
-      // S[buf] = Q K^T: 16 steps of 16 dims; a step moves 32 bytes inside a
-      // column block, four steps move to the next block
+      constexpr uint32_t kIdescPV = umma_idesc(kDv, true);
+      // S[buf] = Q K^T: steps of 16 dims; a step moves 32 bytes inside a column
+      // block, four steps move to the next block
       auto issue_qk = [&](int buf) {
 #pragma unroll
-        for (int ks = 0; ks < kD / 16; ++ks) {
-          const uint32_t off = uint32_t(ks >> 2) * kBlockBytes + uint32_t(ks & 3) * 32u;
-          umma_bf16(tmem + uint32_t(buf) * kBlockN, umma_desc(s_q + off, 1, 64),
-                    umma_desc(s_k + off, 1, 64), kIdescQK, ks > 0);
+        for (int ks = 0; ks < kHeadDim / 16; ++ks) {
+          const uint32_t in = uint32_t(ks & 3) * 32u;
+          umma_bf16(tmem + uint32_t(buf) * kBlockN,
+                    umma_desc(s_q + uint32_t(ks >> 2) * T::kQBlockBytes + in, 1, 64),
+                    umma_desc(s_k + uint32_t(ks >> 2) * T::kKBlockBytes + in, 1, 64),
+                    kIdescQK, ks > 0);
         }
         umma_commit(bar_s_full + 8u * uint32_t(buf));
       };
-      // O (+)= P V: 8 steps of 16 keys. P sits in tensor memory where the scores
-      // were: the thread that read columns [32 q, 32 q + 32) of S[buf] left its 32
-      // weights in the first 16 of them. V is MN-major: 8-key groups 1024 bytes
-      // apart, 64-dim blocks one column block apart
+      // O (+)= P V: steps of 16 keys. P sits in tensor memory where the scores
+      // were: the thread that read a quarter of the columns of S[buf] left its
+      // weights, two per column, in the first half of them. V is MN-major:
+      // 8-key groups 1024 bytes apart, 64-dim blocks one column block apart
       auto issue_pv = [&](int buf, bool accumulate) {
 #pragma unroll
         for (int j = 0; j < kBlockN / 16; ++j) {
-          const uint32_t p_at =
-              tmem + uint32_t(buf) * kBlockN + uint32_t(j >> 1) * kQuarterN + uint32_t(j & 1) * 8u;
-          umma_bf16_a_tmem(tmem + kTmemO, p_at,
-                           umma_desc(s_v + uint32_t(j) * 2048u, kBlockBytes >> 4, 64),
+          const uint32_t key = 16u * uint32_t(j);
+          const uint32_t p_at = tmem + uint32_t(buf) * kBlockN + (key / kQuarterN) * kQuarterN +
+                                (key % kQuarterN) / 2u;
+          umma_bf16_a_tmem(tmem + T::kTmemO, p_at,
+                           umma_desc(s_v + uint32_t(j) * 2048u, T::kKBlockBytes >> 4, 64),
                            kIdescPV, accumulate || j > 0);
         }
         umma_commit(bar_pv_done);
@@ -390,7 +456,8 @@ __global__ __launch_bounds__(kThreads, 1) void prefill_attention_sm100_kernel(
           tc_fence_after();
           issue_qk(n & 1);
         }
-        ok = wait(bar_v_full, uint32_t(it) & 1u, 4) && wait(bar_p_full, uint32_t(it) & 1u, 4);
+        ok = wait(bar_v_full, uint32_t(it) & 1u, 4) &&
+             wait(bar_p_full + 8u * uint32_t(it & 1), uint32_t(it >> 1) & 1u, 4);
         if (!ok) break;
         tc_fence_after();
         issue_pv(it & 1, it > 0);
@@ -398,7 +465,7 @@ __global__ __launch_bounds__(kThreads, 1) void prefill_attention_sm100_kernel(
     }
   } else {
     // ------------------------------------------------------------ softmax
-    const int quarter = warp >> 2;  // which 32 of a tile's 128 key columns
+    const int quarter = warp >> 2;  // which quarter of a tile's key columns
     const int row_in = tid & (kBlockM - 1);
     const int row = m0 + row_in;
     const uint32_t lane_base = uint32_t(32 * (warp & 3)) << 16;
@@ -418,7 +485,7 @@ __global__ __launch_bounds__(kThreads, 1) void prefill_attention_sm100_kernel(
       float s[kQuarterN];
       const uint32_t s_at =
           tmem + lane_base + uint32_t(buf) * kBlockN + uint32_t(quarter) * kQuarterN;
-      tmem_ld32(s_at, s);
+      tmem_ld<kQuarterN>(s_at, s);
 
       const bool edge = tile * kBlockN + kBlockN - 1 > m0 ||
                         (p.window > 0 && tile * kBlockN < last_row - p.window + 1);
@@ -477,20 +544,20 @@ __global__ __launch_bounds__(kThreads, 1) void prefill_attention_sm100_kernel(
         if (!ok) break;
         tc_fence_after();
 #pragma unroll 1
-        for (int c = 0; c < kD / 4; c += 32) {
+        for (int c = 0; c < kDv / 4; c += 32) {
           float o[32];
-          const uint32_t at = tmem + lane_base + kTmemO + uint32_t(quarter * (kD / 4) + c);
+          const uint32_t at = tmem + lane_base + T::kTmemO + uint32_t(quarter * (kDv / 4) + c);
           tmem_ld32(at, o);
 #pragma unroll
           for (int i = 0; i < 32; ++i) o[i] *= factor;
           tmem_st32(at, o);
         }
       }
-      // this thread's 32 weights go where it read its scores from
-      tmem_st16(s_at, packed);
+      // this thread's weights go where it read its scores from
+      tmem_st_packed<kQuarterN / 2>(s_at, packed);
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_p_full);
+      if (lane == 0) mbar_arrive(bar_p_full + 8u * uint32_t(buf));
     }
 
     // ---- the last P V, then O / l as bf16
@@ -500,21 +567,22 @@ __global__ __launch_bounds__(kThreads, 1) void prefill_attention_sm100_kernel(
     }
     if (ok) {
       tc_fence_after();
-      // P is no longer read: its first bytes carry the four partial denominators
-      float *l_part = reinterpret_cast<float *>(p_generic);
-      l_part[quarter * kBlockM + row_in] = l_run;
+      // the V tile is no longer read: its first bytes carry the four partial
+      // denominators of every row
+      float *row_sum = reinterpret_cast<float *>(smem_raw + T::kQBytes + T::kKBytes);
+      row_sum[quarter * kBlockM + row_in] = l_run;
       named_barrier_sync(row_barrier, 128);
-      const float l_row = (l_part[row_in] + l_part[kBlockM + row_in]) +
-                          (l_part[2 * kBlockM + row_in] + l_part[3 * kBlockM + row_in]);
+      const float l_row = (row_sum[row_in] + row_sum[kBlockM + row_in]) +
+                          (row_sum[2 * kBlockM + row_in] + row_sum[3 * kBlockM + row_in]);
       const float inv = l_row > 0.0f ? 1.0f / l_row : 0.0f;
-      __nv_bfloat16 *dst =
-          p.out + ((int64_t(batch) * S + row) * p.q_heads + head) * kD + quarter * (kD / 4);
+      __nv_bfloat16 *dst = p.out + ((int64_t(batch) * S + row) * p.q_heads + head) * kHeadDim +
+                           v_part * kDv + quarter * (kDv / 4);
       // tensor-memory loads are warp-wide: rows past the sequence take part in
       // them and only skip the stores
 #pragma unroll 1
-      for (int c = 0; c < kD / 4; c += 32) {
+      for (int c = 0; c < kDv / 4; c += 32) {
         float o[32];
-        tmem_ld32(tmem + lane_base + kTmemO + uint32_t(quarter * (kD / 4) + c), o);
+        tmem_ld32(tmem + lane_base + T::kTmemO + uint32_t(quarter * (kDv / 4) + c), o);
         if (row < S) {
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
@@ -560,23 +628,53 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
-// [batch][token][heads * 256] bf16, boxes of 128 tokens x 64 elements, 128-byte
-// swizzle; tokens past the sequence read as zeros.
+// [batch][token][heads * head_dim] bf16, boxes of box_rows tokens x 64 elements,
+// 128-byte swizzle; tokens past the sequence read as zeros.
 bool make_rows_map(CUtensorMap *map, const __nv_bfloat16 *base, int batch, int seq_len,
-                   int heads) {
+                   int row_elems, int box_rows) {
   EncodeTiledFn encode = encode_tiled_fn();
   if (encode == nullptr) return false;
-  const cuuint64_t dims[3] = {cuuint64_t(heads) * kD, cuuint64_t(seq_len),
-                              cuuint64_t(batch)};
-  const cuuint64_t strides[2] = {cuuint64_t(heads) * kD * 2,
-                                 cuuint64_t(seq_len) * heads * kD * 2};
-  const cuuint32_t box[3] = {64, 128, 1};
+  const cuuint64_t dims[3] = {cuuint64_t(row_elems), cuuint64_t(seq_len), cuuint64_t(batch)};
+  const cuuint64_t strides[2] = {cuuint64_t(row_elems) * 2,
+                                 cuuint64_t(seq_len) * row_elems * 2};
+  const cuuint32_t box[3] = {64, cuuint32_t(box_rows), 1};
   const cuuint32_t elem_strides[3] = {1, 1, 1};
   return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
                 const_cast<__nv_bfloat16 *>(base), dims, strides, box, elem_strides,
                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <class T>
+cudaError_t launch_sm100(__nv_bfloat16 *out, const __nv_bfloat16 *q, const __nv_bfloat16 *k,
+                         const __nv_bfloat16 *v, int batch, int seq_len, int q_heads,
+                         int kv_heads, int window, float softmax_scale,
+                         cudaStream_t stream) {
+  constexpr int kSmemBytes = T::kTileBytes + int(sizeof(SmallState));
+  static_assert(kSmemBytes <= 227 * 1024, "tiles must fit one SM");
+  CUtensorMap map_q, map_k, map_v;
+  if (!make_rows_map(&map_q, q, batch, seq_len, q_heads * T::kHeadDim, kBlockM) ||
+      !make_rows_map(&map_k, k, batch, seq_len, kv_heads * T::kHeadDim, T::kBlockN) ||
+      !make_rows_map(&map_v, v, batch, seq_len, kv_heads * T::kHeadDim, T::kBlockN)) {
+    return cudaErrorInvalidValue;
+  }
+  Sm100PrefillParams p = {out,    seq_len, q_heads, kv_heads,
+                          window, softmax_scale * 1.4426950408889634f};
+  cudaError_t st = cudaFuncSetAttribute(prefill_attention_sm100_kernel<T>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        kSmemBytes);
+  if (st != cudaSuccess) return st;
+  void *fault_word = nullptr;
+  st = cudaGetSymbolAddress(&fault_word, g_prefill_sm100_fault);
+  if (st != cudaSuccess) return st;
+  st = cudaMemsetAsync(fault_word, 0, sizeof(int), stream);
+  if (st != cudaSuccess) return st;
+  const dim3 grid(unsigned(div_up(seq_len, kBlockM)), unsigned(batch),
+                  unsigned(q_heads * T::kVSplits));
+  prefill_attention_sm100_kernel<T><<<grid, kThreads, kSmemBytes, stream>>>(p, map_q, map_k,
+                                                                            map_v);
+  return cudaGetLastError();
 }
 
 }  // namespace
@@ -586,32 +684,18 @@ cudaError_t prefill_attention_sm100_bf16(__nv_bfloat16 *out,
                                          const __nv_bfloat16 *k,
                                          const __nv_bfloat16 *v, int batch,
                                          int seq_len, int q_heads, int kv_heads,
-                                         int window, float softmax_scale,
+                                         int head_dim, int window, float softmax_scale,
                                          cudaStream_t stream) {
-  static_assert(kSmemBytes <= 227 * 1024, "tiles must fit one SM");
-  static_assert(kBlockM == 128 && kBlockN == 128, "boxes are 128 rows");
-  CUtensorMap map_q, map_k, map_v;
-  if (!make_rows_map(&map_q, q, batch, seq_len, q_heads) ||
-      !make_rows_map(&map_k, k, batch, seq_len, kv_heads) ||
-      !make_rows_map(&map_v, v, batch, seq_len, kv_heads)) {
-    return cudaErrorInvalidValue;
+  if (q_heads * (head_dim / kDv) > 65535) return cudaErrorInvalidValue;
+  if (head_dim == 256) {
+    return launch_sm100<Sm100Traits<256, 128>>(out, q, k, v, batch, seq_len, q_heads,
+                                               kv_heads, window, softmax_scale, stream);
   }
-  Sm100PrefillParams p = {out,    seq_len, q_heads, kv_heads,
-                          window, softmax_scale * 1.4426950408889634f};
-  cudaError_t st = cudaFuncSetAttribute(
-      prefill_attention_sm100_kernel,
-      cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-  if (st != cudaSuccess) return st;
-  void *fault_word = nullptr;
-  st = cudaGetSymbolAddress(&fault_word, g_prefill_sm100_fault);
-  if (st != cudaSuccess) return st;
-  st = cudaMemsetAsync(fault_word, 0, sizeof(int), stream);
-  if (st != cudaSuccess) return st;
-  const dim3 grid(unsigned(div_up(seq_len, kBlockM)), unsigned(batch),
-                  unsigned(q_heads));
-  prefill_attention_sm100_kernel<<<grid, kThreads, kSmemBytes, stream>>>(p, map_q, map_k,
-                                                                         map_v);
-  return cudaGetLastError();
+  if (head_dim == 512) {
+    return launch_sm100<Sm100Traits<512, 64>>(out, q, k, v, batch, seq_len, q_heads,
+                                              kv_heads, window, softmax_scale, stream);
+  }
+  return cudaErrorInvalidValue;
 }
 
 int prefill_attention_sm100_fault() {

@@ -155,3 +155,54 @@ def test_entry_points_against_live_reference_kernels(kv, orc, kind, batch, seq, 
         assert torch.equal(res["ref"][i], res["mine"][i]), ("prepared", i)
     max_abs, max_rel = attention_error(host_u16(res["mine"][0]), orc.bf16_to_f32(host_u16(res["ref"][0])))
     assert max_abs <= ATTN_MAX_ABS and max_rel <= ATTN_MAX_REL, (max_abs, max_rel)
+
+
+@pytest.mark.parametrize("geom,batch,seq,window", [(SLIDING, 2, 2048, 1024), (SLIDING, 3, 700, 0),
+                                                   (GLOBAL, 1, 2048, 0), (GLOBAL, 2, 900, 256)])
+def test_prefill_attention_repeats_without_a_wait_running_out(kv, geom, batch, seq, window):
+    """Many key tiles per CTA and many calls: every bounded wait of the tensor-core kernel is met (the fault
+    word stays 0 -- a role running a barrier phase ahead of its reader would show here) and the result is
+    the same bits every time."""
+    rng = np.random.default_rng(seq)
+    q, k, v = _rows(rng, batch, seq, **geom)
+    H, HKV, D = geom["q_heads"], geom["kv_heads"], geom["head_dim"]
+    dq, dk, dv = dev(q), dev(k), dev(v)
+    first = None
+    for _ in range(40):
+        out = torch.full((batch * seq, H, D), 0x7FC0, dtype=torch.int16, device="cuda")
+        kv.prefill_attention(out, dq, dk, dv, batch, seq, H, HKV, D, window, D ** -0.5)
+        torch.cuda.synchronize()
+        assert kv.prefill_attention_fault() == 0
+        if first is None:
+            first = out
+        else:
+            assert torch.equal(out, first)
+
+
+@pytest.mark.parametrize("geom,batch,seq,window", [(SLIDING, 2, 1500, 1024), (GLOBAL, 1, 1300, 0)])
+def test_prefill_attention_long_prompt_against_torch_fp32(kv, orc, geom, batch, seq, window):
+    """Prompts too long for the double-precision host oracle in a test: plain fp32 torch attention on the same
+    bf16 rows as the reference, same tolerance."""
+    rng = np.random.default_rng(seq + 1)
+    q, k, v = _rows(rng, batch, seq, **geom)
+    H, HKV, D = geom["q_heads"], geom["kv_heads"], geom["head_dim"]
+    scale = D ** -0.5
+    dq, dk, dv = dev(q), dev(k), dev(v)
+    out = torch.full((batch * seq, H, D), 0x7FC0, dtype=torch.int16, device="cuda")
+    kv.prefill_attention(out, dq, dk, dv, batch, seq, H, HKV, D, window, scale)
+    torch.cuda.synchronize()
+    assert kv.prefill_attention_fault() == 0
+
+    def f32(t, heads):
+        return t.view(torch.bfloat16).float().view(batch, seq, heads, D).transpose(1, 2)
+    qf, kf, vf = f32(dq, H), f32(dk, HKV).repeat_interleave(H // HKV, 1), f32(dv, HKV).repeat_interleave(H // HKV, 1)
+    s = qf @ kf.transpose(-1, -2) * scale
+    r = torch.arange(seq, device="cuda")[:, None]
+    c = torch.arange(seq, device="cuda")[None, :]
+    mask = c > r
+    if window > 0:
+        mask |= c < r - window + 1
+    s.masked_fill_(mask, float("-inf"))
+    ref = (torch.softmax(s, -1) @ vf).transpose(1, 2).reshape(batch * seq, H, D).cpu().numpy().astype(np.float64)
+    max_abs, max_rel = attention_error(host_u16(out), ref)
+    assert max_abs <= ATTN_MAX_ABS and max_rel <= ATTN_MAX_REL, (max_abs, max_rel)
