@@ -109,6 +109,49 @@ class LayerStepArgs(ctypes.Structure):
     ]
 
 
+class IngressArgs(ctypes.Structure):
+    """B200KvIngressArgs: input RMSNorm + [Q|K|V] projection
+    (src/gemma4_flash_attention_decode.cu:447-496)."""
+
+    _fields_ = [
+        ("raw_qkv", c_void_p), ("x", c_void_p), ("input_norm_weight", c_void_p),
+        ("qkv_proj_col_major", c_void_p),
+        ("batch_count", c_int32), ("hidden_size", c_int32),
+        ("cols", c_int32), ("q_width", c_int32), ("k_width", c_int32),
+        ("norm_mode", c_int32), ("status", c_void_p),
+    ]
+
+
+class EgressArgs(ctypes.Structure):
+    """B200KvEgressArgs: O projection + post-attention norm + residual
+    (src/gemma4_flash_attention_decode.cu:35-129)."""
+
+    _fields_ = [
+        ("residual_out", c_void_p), ("normed_out", c_void_p), ("ffn_residual", c_void_p),
+        ("ffn_x", c_void_p), ("attention_out", c_void_p), ("o_proj_col_major", c_void_p),
+        ("post_norm_weight", c_void_p), ("pre_ffn_norm_weight", c_void_p),
+        ("x", c_void_p), ("ticket", c_void_p),
+        ("batch_count", c_int32), ("hidden_size", c_int32),
+        ("attention_width", c_int32), ("norm_mode", c_int32), ("status", c_void_p),
+    ]
+
+
+class AttentionLayerArgs(ctypes.Structure):
+    """B200KvAttentionLayerArgs: ingress + layer-step + egress, the attention
+    half of Gemma4DecodeMegakernelLayerArgs (src/gemma4_megakernel.cuh:32-66)."""
+
+    _fields_ = [
+        ("kv", LayerStepArgs),
+        ("attention_x", c_void_p), ("attention_input_norm_weight", c_void_p),
+        ("attention_qkv_proj_col_major", c_void_p), ("attention_o_proj_col_major", c_void_p),
+        ("attention_post_norm_weight", c_void_p), ("attention_pre_ffn_norm_weight", c_void_p),
+        ("raw_qkv", c_void_p),
+        ("residual_out", c_void_p), ("normed_out", c_void_p), ("ffn_residual", c_void_p),
+        ("ffn_x", c_void_p), ("ticket", c_void_p),
+        ("hidden_size", c_int32), ("has_v_projection", c_int32),
+    ]
+
+
 class CudaError(RuntimeError):
     def __init__(self, code: int, where: str):
         super().__init__(f"{where} returned cudaError {code}")
@@ -151,6 +194,9 @@ _SIGNATURES = {
     "b200kv_plan_splits_total": (None, [c_int32, c_int32, c_int64, c_int32, c_int32, POINTER(c_int32), POINTER(c_int32)]),
     "b200kv_decode_layer_step_bf16": (c_int, [POINTER(LayerStepArgs), _P]),
     "b200kv_decode_step_bf16": (c_int, [POINTER(LayerStepArgs), c_int32, _P]),
+    "b200kv_decode_ingress_bf16": (c_int, [POINTER(IngressArgs), _P]),
+    "b200kv_decode_egress_bf16": (c_int, [POINTER(EgressArgs), _P]),
+    "b200kv_decode_attention_layer_bf16": (c_int, [POINTER(AttentionLayerArgs), _P]),
     "b200kv_timer_create": (c_int, [POINTER(_P)]),
     "b200kv_timer_destroy": (c_int, [_P]),
     "b200kv_timer_record": (c_int, [_P, _P]),
@@ -462,6 +508,21 @@ def decode_step(layers, layer_count: int, stream=None, check: bool = True) -> in
     """`layers` is a ctypes array (LayerStepArgs * n)."""
     code = load_library().b200kv_decode_step_bf16(layers, layer_count, _stream(stream))
     return _check(code, "b200kv_decode_step_bf16", check)
+
+
+def decode_ingress(args: IngressArgs, stream=None, check: bool = True) -> int:
+    code = load_library().b200kv_decode_ingress_bf16(ctypes.byref(args), _stream(stream))
+    return _check(code, "b200kv_decode_ingress_bf16", check)
+
+
+def decode_egress(args: EgressArgs, stream=None, check: bool = True) -> int:
+    code = load_library().b200kv_decode_egress_bf16(ctypes.byref(args), _stream(stream))
+    return _check(code, "b200kv_decode_egress_bf16", check)
+
+
+def decode_attention_layer(args: AttentionLayerArgs, stream=None, check: bool = True) -> int:
+    code = load_library().b200kv_decode_attention_layer_bf16(ctypes.byref(args), _stream(stream))
+    return _check(code, "b200kv_decode_attention_layer_bf16", check)
 
 
 class Timer:

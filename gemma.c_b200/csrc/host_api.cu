@@ -1029,6 +1029,104 @@ int b200kv_decode_step_bf16(const B200KvLayerStepArgs *layers,
   return cudaSuccess;
 }
 
+int b200kv_decode_ingress_bf16(const B200KvIngressArgs *s,
+                               b200kv_stream stream) {
+  if (s == nullptr) return cudaErrorInvalidValue;
+  using bf = __nv_bfloat16;
+  b200kv::IngressArgs a;
+  a.raw_qkv = reinterpret_cast<bf *>(s->raw_qkv);
+  a.x = reinterpret_cast<const bf *>(s->x);
+  a.input_norm_weight = reinterpret_cast<const bf *>(s->input_norm_weight);
+  a.qkv_proj_col_major = reinterpret_cast<const bf *>(s->qkv_proj_col_major);
+  a.rows = s->batch_count;
+  a.hidden = s->hidden_size;
+  a.cols = s->cols;
+  a.q_width = s->q_width;
+  a.k_width = s->k_width;
+  a.norm_mode = s->norm_mode;
+  a.status = s->status;
+  return b200kv::decode_ingress_bf16(a, static_cast<cudaStream_t>(stream));
+}
+
+int b200kv_decode_egress_bf16(const B200KvEgressArgs *s, b200kv_stream stream) {
+  if (s == nullptr) return cudaErrorInvalidValue;
+  using bf = __nv_bfloat16;
+  b200kv::EgressArgs a;
+  a.residual_out = reinterpret_cast<bf *>(s->residual_out);
+  a.normed_out = reinterpret_cast<bf *>(s->normed_out);
+  a.ffn_residual = reinterpret_cast<bf *>(s->ffn_residual);
+  a.ffn_x = reinterpret_cast<bf *>(s->ffn_x);
+  a.attention_out = reinterpret_cast<const bf *>(s->attention_out);
+  a.o_proj_col_major = reinterpret_cast<const bf *>(s->o_proj_col_major);
+  a.post_norm_weight = reinterpret_cast<const bf *>(s->post_norm_weight);
+  a.pre_ffn_norm_weight = reinterpret_cast<const bf *>(s->pre_ffn_norm_weight);
+  a.x = reinterpret_cast<const bf *>(s->x);
+  a.ticket = s->ticket;
+  a.rows = s->batch_count;
+  a.hidden = s->hidden_size;
+  a.attention_width = s->attention_width;
+  a.norm_mode = s->norm_mode;
+  a.status = s->status;
+  return b200kv::decode_egress_bf16(a, static_cast<cudaStream_t>(stream));
+}
+
+int b200kv_decode_attention_layer_bf16(const B200KvAttentionLayerArgs *s,
+                                       b200kv_stream stream) {
+  if (s == nullptr) return cudaErrorInvalidValue;
+  const B200KvLayerStepArgs &kv = s->kv;
+  const Gemma4KvCacheConfig &cfg = kv.cache_config;
+  if (kv.batch_count < 0 || kv.q_heads <= 0 || cfg.head_dim <= 0 ||
+      cfg.num_heads <= 0 || s->raw_qkv == nullptr) {
+    return cudaErrorInvalidValue;
+  }
+  if (kv.batch_count == 0) return cudaSuccess;
+  const int32_t q_width = kv.q_heads * cfg.head_dim;
+  const int32_t k_width = cfg.num_heads * cfg.head_dim;
+  const int32_t cols = q_width + k_width * (s->has_v_projection ? 2 : 1);
+  const int64_t rows = kv.batch_count;
+
+  B200KvIngressArgs in = {};
+  in.raw_qkv = s->raw_qkv;
+  in.x = s->attention_x;
+  in.input_norm_weight = s->attention_input_norm_weight;
+  in.qkv_proj_col_major = s->attention_qkv_proj_col_major;
+  in.batch_count = kv.batch_count;
+  in.hidden_size = s->hidden_size;
+  in.cols = cols;
+  in.q_width = q_width;
+  in.k_width = k_width;
+  in.norm_mode = kv.norm_mode;
+  in.status = kv.status;
+  int st = b200kv_decode_ingress_bf16(&in, stream);
+  if (st != cudaSuccess) return st;
+
+  B200KvLayerStepArgs step = kv;
+  step.raw_q = s->raw_qkv;
+  step.raw_k = s->raw_qkv + rows * q_width;
+  step.raw_v = s->has_v_projection ? s->raw_qkv + rows * (q_width + k_width)
+                                   : nullptr;
+  st = b200kv_decode_layer_step_bf16(&step, stream);
+  if (st != cudaSuccess) return st;
+
+  B200KvEgressArgs out = {};
+  out.residual_out = s->residual_out;
+  out.normed_out = s->normed_out;
+  out.ffn_residual = s->ffn_residual;
+  out.ffn_x = s->ffn_x;
+  out.attention_out = kv.out;
+  out.o_proj_col_major = s->attention_o_proj_col_major;
+  out.post_norm_weight = s->attention_post_norm_weight;
+  out.pre_ffn_norm_weight = s->attention_pre_ffn_norm_weight;
+  out.x = s->attention_x;
+  out.ticket = s->ticket;
+  out.batch_count = kv.batch_count;
+  out.hidden_size = s->hidden_size;
+  out.attention_width = q_width;
+  out.norm_mode = kv.norm_mode;
+  out.status = kv.status;
+  return b200kv_decode_egress_bf16(&out, stream);
+}
+
 int b200kv_timer_create(void **event) {
   if (event == nullptr) return cudaErrorInvalidValue;
   cudaEvent_t ev = nullptr;

@@ -93,6 +93,45 @@ cudaError_t decode_layer_step_fused_bf16(const AppendArgs &append,
                                          const DecodeArgs &decode,
                                          cudaStream_t stream);
 
+// Decode projections either side of the KV path (decode_projection.cu), rows of
+// one token each; hidden size 3840. Weights are column-major: output column c
+// is `width` contiguous bf16 (the reference's *_proj_col_major layout).
+struct IngressArgs {
+  // out: raw q [rows][q_width], then raw k [rows][k_width], then raw v
+  // [rows][cols - q_width - k_width] (one row: the reference's [q|k|v] scratch)
+  __nv_bfloat16 *raw_qkv = nullptr;
+  const __nv_bfloat16 *x = nullptr;  // [rows][hidden]
+  const __nv_bfloat16 *input_norm_weight = nullptr;
+  const __nv_bfloat16 *qkv_proj_col_major = nullptr;  // [cols][hidden]
+  int32_t rows = 0;
+  int32_t hidden = 0;
+  int32_t cols = 0;
+  int32_t q_width = 0;
+  int32_t k_width = 0;
+  int32_t norm_mode = B200KV_NORM_RSQRT_APPROX;
+  int32_t *status = nullptr;
+};
+cudaError_t decode_ingress_bf16(const IngressArgs &args, cudaStream_t stream);
+
+struct EgressArgs {
+  __nv_bfloat16 *residual_out = nullptr;  // out [rows][hidden]: O projection
+  __nv_bfloat16 *normed_out = nullptr;    // out [rows][hidden]
+  __nv_bfloat16 *ffn_residual = nullptr;  // out [rows][hidden]
+  __nv_bfloat16 *ffn_x = nullptr;         // out, optional
+  const __nv_bfloat16 *attention_out = nullptr;  // [rows][attention_width]
+  const __nv_bfloat16 *o_proj_col_major = nullptr;  // [hidden][attention_width]
+  const __nv_bfloat16 *post_norm_weight = nullptr;
+  const __nv_bfloat16 *pre_ffn_norm_weight = nullptr;
+  const __nv_bfloat16 *x = nullptr;       // [rows][hidden]: the layer's input
+  unsigned int *ticket = nullptr;         // [rows], zero before the first call
+  int32_t rows = 0;
+  int32_t hidden = 0;
+  int32_t attention_width = 0;
+  int32_t norm_mode = B200KV_NORM_RSQRT_APPROX;
+  int32_t *status = nullptr;
+};
+cudaError_t decode_egress_bf16(const EgressArgs &args, cudaStream_t stream);
+
 struct PrefillPrepArgs {
   __nv_bfloat16 *q_prepared = nullptr;
   __nv_bfloat16 *k_prepared = nullptr;

@@ -505,6 +505,94 @@ int b200kv_decode_layer_step_bf16(const B200KvLayerStepArgs *args,
 int b200kv_decode_step_bf16(const B200KvLayerStepArgs *layers,
                             int32_t layer_count, b200kv_stream stream);
 
+/* ------------------------------------------------------------------ *
+ * The steps either side of the KV path inside the reference's fused decode
+ * layer, for `batch_count` rows of one token each and hidden size 3840
+ * (GEMMA4_HIDDEN_SIZE, src/gemma4.h:6). Matrices are column-major as the
+ * reference packs them (`*_proj_col_major`): output column c is `width`
+ * contiguous bf16. The sums are added in the order of the reference's
+ * 512-thread block, so the bf16 results are the bits its kernels write
+ * (norm_mode B200KV_NORM_RSQRT_APPROX) or the host oracle's (B200KV_NORM_IEEE).
+ *
+ * b200kv_decode_ingress_bf16 replaces phase_decode_rmsnorm_project_bf16,
+ * src/gemma4_flash_attention_decode.cu:447-496: RMSNorm of the layer input with
+ * `input_norm_weight`, then the [Q|K|V] projection. `raw_qkv` receives raw q
+ * [batch, q_width], then raw k [batch, k_width], then raw v [batch, cols -
+ * q_width - k_width] (for one row the reference's raw scratch; v is absent for
+ * the global geometry, whose V comes from raw K).
+ *
+ * b200kv_decode_egress_bf16 replaces project_attention_out_post_attention,
+ * src/gemma4_flash_attention_decode.cu:35-129, and the pre-FFN norm that
+ * follows it (:1049-1058): residual_out = attention_out x O; normed_out =
+ * RMSNorm(residual_out, post_norm_weight); ffn_residual = x + normed_out;
+ * ffn_x = RMSNorm(ffn_residual, pre_ffn_norm_weight) when ffn_x is given.
+ * attention_width is 4096 or 8192. `ticket` is uint32[batch_count], zero before
+ * the first call (the kernel leaves it zero): the CTA that finishes a row last
+ * runs the norms, where the reference uses two grid-wide barriers.
+ *
+ * Both return cudaErrorInvalidValue for null or misaligned (16 B) pointers and
+ * sizes other than the above; batch_count 0 is a no-op.
+ * ------------------------------------------------------------------ */
+typedef struct B200KvIngressArgs {
+  b200kv_bf16 *raw_qkv;
+  const b200kv_bf16 *x;                    /* [batch, 3840] */
+  const b200kv_bf16 *input_norm_weight;    /* [3840] */
+  const b200kv_bf16 *qkv_proj_col_major;   /* [cols, 3840] */
+  int32_t batch_count;
+  int32_t hidden_size;                     /* 3840 */
+  int32_t cols, q_width, k_width;
+  int32_t norm_mode;
+  int32_t *status;                         /* optional, as for the decode kernels */
+} B200KvIngressArgs;
+
+int b200kv_decode_ingress_bf16(const B200KvIngressArgs *args,
+                               b200kv_stream stream);
+
+typedef struct B200KvEgressArgs {
+  b200kv_bf16 *residual_out, *normed_out, *ffn_residual;  /* [batch, 3840] */
+  b200kv_bf16 *ffn_x;                      /* optional [batch, 3840] */
+  const b200kv_bf16 *attention_out;        /* [batch, attention_width] */
+  const b200kv_bf16 *o_proj_col_major;     /* [3840, attention_width] */
+  const b200kv_bf16 *post_norm_weight, *pre_ffn_norm_weight;
+  const b200kv_bf16 *x;                    /* [batch, 3840]: the layer input */
+  uint32_t *ticket;
+  int32_t batch_count;
+  int32_t hidden_size;
+  int32_t attention_width;
+  int32_t norm_mode;
+  int32_t *status;
+} B200KvEgressArgs;
+
+int b200kv_decode_egress_bf16(const B200KvEgressArgs *args,
+                              b200kv_stream stream);
+
+/* One decode layer from the layer input to the FFN input: ingress, the
+ * layer-step above (append + attention + combine) and egress, enqueued in order
+ * on `stream` -- the work of gemma4_decode_megakernel_flash_attention_layer_bf16,
+ * src/gemma4_flash_attention_decode.cu:1033-1058,1122-1157, up to the call of the
+ * FFN (which is not part of this library). Field names follow
+ * Gemma4DecodeMegakernelLayerArgs, src/gemma4_megakernel.cuh:32-66. `kv.raw_q /
+ * raw_k / raw_v` are ignored and set from `raw_qkv`; the geometry (q_heads,
+ * head_dim, KV heads) is `kv`'s; has_v_projection 0 = the global geometry
+ * (no V columns; V from raw K). */
+typedef struct B200KvAttentionLayerArgs {
+  B200KvLayerStepArgs kv;
+  const b200kv_bf16 *attention_x;
+  const b200kv_bf16 *attention_input_norm_weight;
+  const b200kv_bf16 *attention_qkv_proj_col_major;
+  const b200kv_bf16 *attention_o_proj_col_major;
+  const b200kv_bf16 *attention_post_norm_weight;
+  const b200kv_bf16 *attention_pre_ffn_norm_weight;
+  b200kv_bf16 *raw_qkv;                    /* scratch, see the ingress */
+  b200kv_bf16 *residual_out, *normed_out, *ffn_residual, *ffn_x;
+  uint32_t *ticket;
+  int32_t hidden_size;
+  int32_t has_v_projection;
+} B200KvAttentionLayerArgs;
+
+int b200kv_decode_attention_layer_bf16(const B200KvAttentionLayerArgs *args,
+                                       b200kv_stream stream);
+
 /* Timing events for the hooks above (cudaEventCreate / Destroy / ElapsedTime).
  * No counterpart in the reference library; its benches time with the same
  * CUDA events, src/benches/gemma4_bench_utils.cuh:336-370. */

@@ -93,6 +93,10 @@ def lib() -> ctypes.CDLL:
         "orc_prefill_attention_f64": (None, [_P] * 5 + [c_int32] * 6 + [c_float, c_int32]),
         "orc_layer_step_timed": (c_double, [c_int32, _P, _P, _P, _P, C, _P, _P, _P, c_int32] + [_P] * 7 + [c_int32, c_int32, c_float, c_int32]),
         "orc_hardware_threads": (c_int32, []),
+        "orc_hidden_rmsnorm": (None, [_P, _P, _P, c_int32]),
+        "orc_project_cols": (None, [_P, _P, _P, c_int32, c_int32, c_int32, c_int32]),
+        "orc_decode_ingress": (None, [_P] * 5 + [c_int32] * 3),
+        "orc_decode_egress": (None, [_P] * 9 + [c_int32] * 3),
     }
     for name, (res, args) in sigs.items():
         fn = getattr(L, name)
@@ -306,3 +310,31 @@ def layer_step_timed(threads, out, q_prepared, cache_k, cache_v, cfg, page_table
 
 def hardware_threads() -> int:
     return lib().orc_hardware_threads()
+
+
+# ------------------------------------------------------------------ decode projections
+def hidden_rmsnorm(x, weight):
+    x = np.ascontiguousarray(x, dtype=np.uint16)
+    out = np.empty_like(x)
+    lib().orc_hidden_rmsnorm(_p(out), _p(x), _p(weight), x.size)
+    return out
+
+
+def decode_ingress(x, input_norm_weight, qkv_proj_col_major, threads=0):
+    """x [hidden] bf16 bits, weights [cols, hidden]; returns (raw_qkv [cols], normed [hidden])."""
+    cols, hidden = qkv_proj_col_major.shape
+    raw = np.empty(cols, dtype=np.uint16)
+    normed = np.empty(hidden, dtype=np.uint16)
+    lib().orc_decode_ingress(_p(raw), _p(normed), _p(x), _p(input_norm_weight), _p(qkv_proj_col_major),
+                             hidden, cols, threads or hardware_threads())
+    return raw, normed
+
+
+def decode_egress(attention_out, o_proj_col_major, post_norm_weight, pre_ffn_norm_weight, x, threads=0):
+    """attention_out [width], weights [hidden, width]; returns residual_out, normed_out, ffn_residual, ffn_x."""
+    hidden, width = o_proj_col_major.shape
+    outs = [np.empty(hidden, dtype=np.uint16) for _ in range(4)]
+    lib().orc_decode_egress(_p(outs[0]), _p(outs[1]), _p(outs[2]), _p(outs[3]), _p(attention_out),
+                            _p(o_proj_col_major), _p(post_norm_weight), _p(pre_ffn_norm_weight), _p(x),
+                            width, hidden, threads or hardware_threads())
+    return tuple(outs)

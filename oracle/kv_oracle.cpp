@@ -1064,6 +1064,156 @@ void orc_prefill_attention_f64(float *out_f32, float *lse, const uint16_t *q,
   for (auto &th : pool) th.join();
 }
 
+}  // extern "C"
+
+// ---------------------------------------------------------------------------
+// Decode projections either side of the KV path: input RMSNorm + [Q|K|V]
+// projection into the raw scratch (decode.cu:395-496) and the O projection
+// with the post-attention norm and residual (decode.cu:35-129). The summation
+// order is the 512-thread block's: thread t chains fmaf over packs t, t+512, ..
+// (8 elements each, cuda_utils.cuh:88-103); every warp folds with
+// __shfl_down 16..1 (cuda_utils.cuh:174-182); warp 0 folds the 16 warp sums
+// the same way with zeros in lanes 16..31 (decode.cu:396-419).
+// ---------------------------------------------------------------------------
+namespace {
+
+constexpr int kBlockThreads = 512;  // kDecodeMegaThreads, decode.cu:30
+
+inline float shfl_down_tree(float (&v)[kWarp]) {
+  for (int offset = kWarp / 2; offset > 0; offset >>= 1) {
+    float next[kWarp];
+    for (int i = 0; i < kWarp; ++i) {
+      next[i] = v[i] + (i + offset < kWarp ? v[i + offset] : v[i]);
+    }
+    std::memcpy(v, next, sizeof(next));
+  }
+  return v[0];
+}
+
+inline float shfl_xor_tree(float (&v)[kWarp]) {
+  // warp_reduce_sum, cuda_utils.cuh:165-170
+  for (int offset = kWarp / 2; offset > 0; offset /= 2) {
+    float next[kWarp];
+    for (int i = 0; i < kWarp; ++i) next[i] = v[i] + v[i ^ offset];
+    std::memcpy(v, next, sizeof(next));
+  }
+  return v[0];
+}
+
+// One output column: dot of x with one weight column, both bf16 [width].
+// active_threads: threads that take part (480 for the 3840-wide input of the
+// QKV projection, decode.cu:430-433; all 512 for the O projection).
+inline float block_dot(const uint16_t *x, const uint16_t *w, int width,
+                       int active_threads) {
+  const int packs = width / 8;
+  float warp_sums[kBlockThreads / kWarp];
+  for (int warp = 0; warp < kBlockThreads / kWarp; ++warp) {
+    float lanes[kWarp];
+    for (int lane = 0; lane < kWarp; ++lane) {
+      const int t = warp * kWarp + lane;
+      float sum = 0.0f;
+      if (t < active_threads) {
+        for (int pack = t; pack < packs; pack += kBlockThreads) {
+          for (int e = 0; e < 8; ++e) {
+            sum = std::fmaf(bf(x[pack * 8 + e]), bf(w[pack * 8 + e]), sum);
+          }
+        }
+      }
+      lanes[lane] = sum;
+    }
+    warp_sums[warp] = shfl_down_tree(lanes);
+  }
+  float lanes[kWarp];
+  for (int lane = 0; lane < kWarp; ++lane) {
+    lanes[lane] = lane < kBlockThreads / kWarp ? warp_sums[lane] : 0.0f;
+  }
+  return shfl_down_tree(lanes);
+}
+
+// gemma4_rmsnorm_row_bf16 with 512 threads (rmsnorm.cu:27-87), IEEE 1/sqrt in
+// place of rsqrtf (the oracle's one documented deviation).
+void hidden_rmsnorm(uint16_t *out, const uint16_t *in, const uint16_t *weight,
+                    int width) {
+  const int packs = width / 8;
+  float warp_sums[kBlockThreads / kWarp];
+  for (int warp = 0; warp < kBlockThreads / kWarp; ++warp) {
+    float lanes[kWarp];
+    for (int lane = 0; lane < kWarp; ++lane) {
+      const int t = warp * kWarp + lane;
+      float ss = 0.0f;
+      for (int pack = t; pack < packs; pack += kBlockThreads) {
+        for (int e = 0; e < 8; ++e) {
+          const float v = bf(in[pack * 8 + e]);
+          ss = std::fmaf(v, v, ss);
+        }
+      }
+      lanes[lane] = ss;
+    }
+    warp_sums[warp] = shfl_xor_tree(lanes);
+  }
+  float lanes[kWarp];
+  for (int lane = 0; lane < kWarp; ++lane) {
+    lanes[lane] = lane < kBlockThreads / kWarp ? warp_sums[lane] : 0.0f;
+  }
+  const float sum_sq = shfl_xor_tree(lanes);
+  const float scale = 1.0f / std::sqrt(sum_sq / float(width) + kEps);
+  for (int i = 0; i < width; ++i) {
+    const float scaled = bf(in[i]) * scale;
+    out[i] = to_bf(scaled * bf(weight[i]));
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+void orc_hidden_rmsnorm(uint16_t *out, const uint16_t *in,
+                        const uint16_t *weight, int32_t width) {
+  hidden_rmsnorm(out, in, weight, width);
+}
+
+void orc_project_cols(uint16_t *out, const uint16_t *x,
+                      const uint16_t *w_col_major, int32_t width, int32_t cols,
+                      int32_t active_threads, int32_t threads) {
+  parallel_for(threads, cols, [&](int col) {
+    out[col] = to_bf(
+        block_dot(x, w_col_major + int64_t(col) * width, width, active_threads));
+  });
+}
+
+void orc_decode_ingress(uint16_t *raw_qkv, uint16_t *normed, const uint16_t *x,
+                        const uint16_t *input_norm_weight,
+                        const uint16_t *qkv_proj_col_major, int32_t hidden,
+                        int32_t cols, int32_t threads) {
+  // decode.cu:447-496: CTA 0 norms the row, every CTA projects column tiles.
+  std::vector<uint16_t> local(size_t(hidden), uint16_t(0));
+  uint16_t *n = normed != nullptr ? normed : local.data();
+  hidden_rmsnorm(n, x, input_norm_weight, hidden);
+  orc_project_cols(raw_qkv, n, qkv_proj_col_major, hidden, cols, hidden / 8,
+                   threads);
+}
+
+void orc_decode_egress(uint16_t *residual_out, uint16_t *normed_out,
+                       uint16_t *ffn_residual, uint16_t *ffn_x,
+                       const uint16_t *attention_out,
+                       const uint16_t *o_proj_col_major,
+                       const uint16_t *post_norm_weight,
+                       const uint16_t *pre_ffn_norm_weight, const uint16_t *x,
+                       int32_t attention_width, int32_t hidden,
+                       int32_t threads) {
+  // decode.cu:35-129: O projection, post-attention norm, residual add;
+  // decode.cu:1049-1058: the pre-FFN norm of that sum (ffn_x, optional here).
+  orc_project_cols(residual_out, attention_out, o_proj_col_major,
+                   attention_width, hidden, kBlockThreads, threads);
+  hidden_rmsnorm(normed_out, residual_out, post_norm_weight, hidden);
+  for (int i = 0; i < hidden; ++i) {
+    ffn_residual[i] = to_bf(bf(x[i]) + bf(normed_out[i]));  // cuda_utils.cuh:105-122
+  }
+  if (ffn_x != nullptr) {
+    hidden_rmsnorm(ffn_x, ffn_residual, pre_ffn_norm_weight, hidden);
+  }
+}
+
 int32_t orc_hardware_threads(void) {
   const unsigned n = std::thread::hardware_concurrency();
   return n == 0 ? 1 : int32_t(n);

@@ -175,6 +175,31 @@ void orc_prefill_attention_f64(float *out_f32, float *lse, const uint16_t *q,
                                int32_t window, float softmax_scale,
                                int32_t threads);
 
+// ---- decode projections either side of the KV path -------------------------
+// (decode.cu:35-129 O projection + post-attention norm + residual;
+//  decode.cu:395-496 input RMSNorm + [Q|K|V] projection; rmsnorm.cu:27-87).
+// Weights are column-major: column c is `width` contiguous bf16. Sums follow
+// the 512-thread block's order; `threads` are host threads over columns.
+void orc_hidden_rmsnorm(uint16_t *out, const uint16_t *in,
+                        const uint16_t *weight, int32_t width);
+void orc_project_cols(uint16_t *out, const uint16_t *x,
+                      const uint16_t *w_col_major, int32_t width, int32_t cols,
+                      int32_t active_threads, int32_t threads);
+// normed (the bf16 normed row, [hidden]) may be NULL.
+void orc_decode_ingress(uint16_t *raw_qkv, uint16_t *normed, const uint16_t *x,
+                        const uint16_t *input_norm_weight,
+                        const uint16_t *qkv_proj_col_major, int32_t hidden,
+                        int32_t cols, int32_t threads);
+// ffn_x may be NULL (then pre_ffn_norm_weight is unused).
+void orc_decode_egress(uint16_t *residual_out, uint16_t *normed_out,
+                       uint16_t *ffn_residual, uint16_t *ffn_x,
+                       const uint16_t *attention_out,
+                       const uint16_t *o_proj_col_major,
+                       const uint16_t *post_norm_weight,
+                       const uint16_t *pre_ffn_norm_weight, const uint16_t *x,
+                       int32_t attention_width, int32_t hidden,
+                       int32_t threads);
+
 // ---- timed CPU baseline: one layer-step (append + attention + reduce) -----
 // Runs orc_decode_append then the reference-order attention with `threads`
 // host threads over (sequence, kv head) units. Returns seconds of wall time.

@@ -33,6 +33,11 @@ def lib() -> ctypes.CDLL:
             L.ref_prefill_sliding.argtypes = [_P] * 12 + [c_int] * 4 + [c_float, _P]
             L.ref_prefill_global.restype = c_int
             L.ref_prefill_global.argtypes = [_P] * 11 + [c_int] * 3 + [c_float, _P]
+        if hasattr(L, "ref_decode_ingress"):
+            L.ref_decode_ingress.restype = c_int
+            L.ref_decode_ingress.argtypes = [_P] * 5 + [c_int, _P]
+            L.ref_decode_egress.restype = c_int
+            L.ref_decode_egress.argtypes = [_P] * 9 + [c_int, _P]
         _lib = L
     return _lib
 
@@ -86,3 +91,21 @@ def prefill_global(out, q_prepared, k_prepared, v_prepared, q, k, q_w, k_w, cos,
     return lib().ref_prefill_global(_ptr(out), _ptr(q_prepared), _ptr(k_prepared), _ptr(v_prepared), _ptr(q),
                                     _ptr(k), _ptr(q_w), _ptr(k_w), _ptr(cos), _ptr(sin), _ptr(token_position),
                                     batch_size, seqlen_q, seqlen_k, scale, _stream())
+
+
+def has_projections() -> bool:
+    return available() and hasattr(lib(), "ref_decode_ingress")
+
+
+def decode_ingress(raw_qkv, normed_out, x, input_norm_weight, qkv_proj_col_major, global_geometry: bool) -> int:
+    """The reference's phase_decode_rmsnorm_project_bf16 (one row), launched cooperatively."""
+    return lib().ref_decode_ingress(_ptr(raw_qkv), _ptr(normed_out), _ptr(x), _ptr(input_norm_weight),
+                                    _ptr(qkv_proj_col_major), int(global_geometry), _stream())
+
+
+def decode_egress(residual_out, normed_out, ffn_residual, ffn_x, attention_out, o_proj_col_major, post_norm_weight,
+                  pre_ffn_norm_weight, x, global_geometry: bool) -> int:
+    """The reference's project_attention_out_post_attention followed by its pre-FFN norm (one row)."""
+    return lib().ref_decode_egress(_ptr(residual_out), _ptr(normed_out), _ptr(ffn_residual), _ptr(ffn_x),
+                                   _ptr(attention_out), _ptr(o_proj_col_major), _ptr(post_norm_weight),
+                                   _ptr(pre_ffn_norm_weight), _ptr(x), int(global_geometry), _stream())

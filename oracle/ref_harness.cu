@@ -148,3 +148,81 @@ extern "C" int ref_prefill_global(__nv_bfloat16 *out, __nv_bfloat16 *q_prepared,
                                                           cos, sin, token_position, batch_size, seqlen_q, seqlen_k,
                                                           scale, stream);
 }
+
+// ---- the steps either side of the KV path inside the reference's fused layer kernel ----------------
+//   phase_decode_rmsnorm_project_bf16      (:447-496)  input RMSNorm + [Q|K|V] projection
+//   project_attention_out_post_attention   (:35-129)   O projection + post-attention norm + residual
+// and the pre-FFN norm the fused kernel runs next (:1049-1058, a call of the reference's own
+// gemma4_rmsnorm_hidden_row_512_bf16_device). Both phases hold grid-wide barriers, so the wrappers are
+// launched cooperatively with the grid the reference's launcher would use (:1076-1111).
+namespace {
+
+template <int Width>
+__global__ __launch_bounds__(kThreads, 1) void ref_ingress_kernel(Gemma4DecodeMegakernelLayerArgs args,
+                                                                  __nv_bfloat16 *raw) {
+  ref::phase_decode_rmsnorm_project_bf16<Width>(args, raw, ref::cg::this_grid());
+}
+
+template <class Traits>
+__global__ __launch_bounds__(kThreads, 1) void ref_egress_kernel(Gemma4DecodeMegakernelLayerArgs args) {
+  ref::project_attention_out_post_attention<Traits>(args, ref::cg::this_grid());
+  if (blockIdx.x == 0 && args.ffn_x != nullptr) {
+    __shared__ Bf16Packed128 cached_input[ref::kFfnHiddenPacks];
+    __shared__ float warp_sums[ref::kDecodeMegaWarps];
+    __shared__ float scale;
+    gemma4_rmsnorm_hidden_row_512_bf16_device(args.ffn_x, args.ffn_residual, args.attention_pre_ffn_norm_weight,
+                                              GEMMA4_RMS_NORM_EPS, cached_input, warp_sums, &scale,
+                                              int(threadIdx.x));
+  }
+}
+
+template <class Kernel, class... Args>
+int launch_cooperative(Kernel kernel, cudaStream_t stream, Args... args) {
+  int device = 0, sms = 0, per_sm = 0;
+  cudaError_t st = cudaGetDevice(&device);
+  if (st != cudaSuccess) return st;
+  st = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  if (st != cudaSuccess) return st;
+  st = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, 0);
+  if (st != cudaSuccess) return st;
+  if (per_sm <= 0) return cudaErrorInvalidValue;
+  void *params[] = {(void *)&args...};
+  st = cudaLaunchCooperativeKernel((void *)kernel, dim3(per_sm * sms), dim3(kThreads), params, 0, stream);
+  return st != cudaSuccess ? st : cudaGetLastError();
+}
+
+}  // namespace
+
+// global_geometry 0: 16 Q + 8 K + 8 V heads of 256 (8192 columns); 1: 16 Q + 1 K head of 512 (8704 columns).
+extern "C" int ref_decode_ingress(__nv_bfloat16 *raw_qkv, __nv_bfloat16 *normed_out, const __nv_bfloat16 *x,
+                                  const __nv_bfloat16 *input_norm_weight, const __nv_bfloat16 *qkv_proj_col_major,
+                                  int global_geometry, cudaStream_t stream) {
+  Gemma4DecodeMegakernelLayerArgs args;
+  args.normed_out = normed_out;
+  args.attention_x = x;
+  args.attention_input_norm_weight = input_norm_weight;
+  args.attention_qkv_proj_col_major = qkv_proj_col_major;
+  if (global_geometry) {
+    return launch_cooperative(ref_ingress_kernel<GEMMA4_GLOBAL_QK_PROJ_SIZE>, stream, args, raw_qkv);
+  }
+  return launch_cooperative(ref_ingress_kernel<GEMMA4_SLIDING_QKV_SIZE>, stream, args, raw_qkv);
+}
+
+extern "C" int ref_decode_egress(__nv_bfloat16 *residual_out, __nv_bfloat16 *normed_out,
+                                 __nv_bfloat16 *ffn_residual, __nv_bfloat16 *ffn_x,
+                                 const __nv_bfloat16 *attention_out, const __nv_bfloat16 *o_proj_col_major,
+                                 const __nv_bfloat16 *post_norm_weight, const __nv_bfloat16 *pre_ffn_norm_weight,
+                                 const __nv_bfloat16 *x, int global_geometry, cudaStream_t stream) {
+  Gemma4DecodeMegakernelLayerArgs args;
+  args.residual_out = residual_out;
+  args.normed_out = normed_out;
+  args.ffn_residual = ffn_residual;
+  args.ffn_x = ffn_x;
+  args.attention_out = const_cast<__nv_bfloat16 *>(attention_out);
+  args.attention_o_proj_col_major = o_proj_col_major;
+  args.attention_post_norm_weight = post_norm_weight;
+  args.attention_pre_ffn_norm_weight = pre_ffn_norm_weight;
+  args.attention_x = x;
+  if (global_geometry) return launch_cooperative(ref_egress_kernel<Global>, stream, args);
+  return launch_cooperative(ref_egress_kernel<Sliding>, stream, args);
+}

@@ -5,7 +5,7 @@ from the gemma.c sources by oracle/build_ref.sh) on a CUDA device.
     python tests/golden/make_golden.py [output_dir]      # default: tests/golden/_recorded
 
 Writes one small .npz per case of tests/golden_cases.py: the outputs only (prepared q, the appended
-cache rows, attention rows), plus a digest of the seeded inputs. Copy the files into tests/golden/.
+cache rows, attention rows, projection rows), plus a digest of the seeded inputs. Copy the files into tests/golden/.
 """
 from __future__ import annotations
 
@@ -69,6 +69,21 @@ def record_attention(name, out_dir):
     print(name, "ok")
 
 
+def record_projection(name, out_dir):
+    case = gc.build_projection(name)
+    d = {n: dev(case[n]) for n in gc.PROJECTION_INPUTS}
+    raw = torch.zeros(case["cols"], dtype=torch.int16, device="cuda")
+    scratch = torch.zeros(gc.HIDDEN, dtype=torch.int16, device="cuda")
+    rc = ref.decode_ingress(raw, scratch, d["x"], d["w_in"], d["w_qkv"], case["global_geometry"])
+    outs = [torch.zeros(gc.HIDDEN, dtype=torch.int16, device="cuda") for _ in range(4)]
+    rc2 = ref.decode_egress(*outs, d["attn"], d["w_o"], d["w_post"], d["w_pre"], d["x"], case["global_geometry"])
+    torch.cuda.synchronize()
+    assert rc == 0 and rc2 == 0, (rc, rc2)
+    values = dict(zip(gc.PROJECTION_OUTPUTS, [host_u16(raw)] + [host_u16(t) for t in outs]))
+    np.savez_compressed(out_dir / f"{name}.npz", digest=np.array(gc.projection_digest(case)), **values)
+    print(name, "ok")
+
+
 def main():
     out_dir = Path(sys.argv[1]) if len(sys.argv) > 1 else REPO / "tests" / "golden" / "_recorded"
     out_dir.mkdir(parents=True, exist_ok=True)
@@ -77,6 +92,9 @@ def main():
         record_append(name, out_dir)
     for name in gc.ATTENTION_ALL:
         record_attention(name, out_dir)
+    if ref.has_projections():
+        for name in gc.PROJECTION_ALL:
+            record_projection(name, out_dir)
 
 
 if __name__ == "__main__":

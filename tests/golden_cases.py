@@ -7,7 +7,7 @@ import hashlib
 
 import numpy as np
 
-from tests.helpers import make_append_case, make_attn_case
+from tests.helpers import bf16_normal, make_append_case, make_attn_case
 
 GEOM = dict(kv_heads=8, q_heads=16, head_dim=256)    # the geometry the reference's sliding traits are built for
 
@@ -81,3 +81,34 @@ def append_digest(case) -> str:
 
 def attention_digest(case) -> str:
     return digest(case.page_table, case.seq_lengths, case.q, case.cache_k, case.cache_v)
+
+
+# The decode projections either side of the KV path (src/gemma4_flash_attention_decode.cu:35-129,447-496),
+# one row, hidden size 3840, for the reference's two geometries.
+HIDDEN = 3840
+PROJECTION = {
+    "proj_sliding": dict(seed=9401, cols=8192, q_width=4096, k_width=2048, global_geometry=False),
+    "proj_global": dict(seed=9402, cols=8704, q_width=8192, k_width=512, global_geometry=True),
+}
+PROJECTION_ALL = list(PROJECTION)
+PROJECTION_INPUTS = ("x", "w_in", "w_qkv", "attn", "w_o", "w_post", "w_pre")
+PROJECTION_OUTPUTS = ("raw_qkv", "residual_out", "normed_out", "ffn_residual", "ffn_x")
+
+
+def build_projection(name) -> dict:
+    kw = PROJECTION[name]
+    rng = np.random.default_rng(kw["seed"])
+    width = kw["q_width"]
+    return dict(
+        x=bf16_normal(rng, (HIDDEN,), std=1.7),
+        w_in=bf16_normal(rng, (HIDDEN,), std=0.05, mean=1.0),
+        w_qkv=bf16_normal(rng, (kw["cols"], HIDDEN), std=1.0 / np.sqrt(HIDDEN)),
+        attn=bf16_normal(rng, (width,)),
+        w_o=bf16_normal(rng, (HIDDEN, width), std=1.0 / np.sqrt(width)),
+        w_post=bf16_normal(rng, (HIDDEN,), std=0.05, mean=1.0),
+        w_pre=bf16_normal(rng, (HIDDEN,), std=0.05, mean=1.0),
+        **{k: kw[k] for k in ("cols", "q_width", "k_width", "global_geometry")})
+
+
+def projection_digest(case) -> str:
+    return digest(*(case[n] for n in PROJECTION_INPUTS))

@@ -196,3 +196,59 @@ def test_product_against_live_reference_kernels(kv, orc):
     kv.kv_cache_write(bufs["mine"][1], bufs["mine"][2], cfg, table, tb, tp, 4, 0, k, v)
     torch.cuda.synchronize()
     assert torch.equal(bufs["ref"][1], bufs["mine"][1]) and torch.equal(bufs["ref"][2], bufs["mine"][2])
+
+
+have_projection_golden = all((GOLDEN / f"{n}.npz").exists() for n in gc.PROJECTION_ALL)
+need_projection_golden = pytest.mark.skipif(not have_projection_golden,
+                                            reason="projection fixtures not recorded yet")
+
+
+@need_projection_golden
+@pytest.mark.parametrize("name", gc.PROJECTION_ALL)
+def test_oracle_projections_against_reference_kernel_output(orc, name):
+    """The host restatement of the block's summation order against what the reference's phases wrote on a
+    B200. The O projection has no norm before it: bit for bit. Everything behind a norm may differ by rare
+    one-step roundings (IEEE 1/sqrt on the host, rsqrt.approx on the GPU)."""
+    g = np.load(GOLDEN / f"{name}.npz")
+    case = gc.build_projection(name)
+    assert gc.projection_digest(case) == str(g["digest"]), "seeded inputs differ from the recorded ones"
+    raw, _ = orc.decode_ingress(case["x"], case["w_in"], case["w_qkv"])
+    _ulp_close(orc, raw, g["raw_qkv"], 0.02)
+    residual_out, normed_out, ffn_residual, ffn_x = orc.decode_egress(case["attn"], case["w_o"], case["w_post"],
+                                                                     case["w_pre"], case["x"])
+    assert np.array_equal(residual_out, g["residual_out"])
+    _ulp_close(orc, normed_out, g["normed_out"], 0.02)
+    _ulp_close(orc, ffn_residual, g["ffn_residual"], 0.02)
+    _ulp_close(orc, ffn_x, g["ffn_x"], 0.02)
+
+
+@need_projection_golden
+@pytest.mark.parametrize("name", gc.PROJECTION_ALL)
+@pytest.mark.gpu
+@pytest.mark.skipif(not torch.cuda.is_available(), reason="needs a CUDA device")
+def test_product_projections_bit_exact_with_reference_kernel_output(kv, name):
+    """Default norm mode: the recorded bits of the reference's kernels, all five rows."""
+    from tests.gpu_util import dev, host_u16
+
+    g = np.load(GOLDEN / f"{name}.npz")
+    case = gc.build_projection(name)
+    d = {n: dev(case[n]) for n in gc.PROJECTION_INPUTS}
+    raw = torch.zeros(case["cols"], dtype=torch.int16, device="cuda")
+    a = kv.IngressArgs()
+    a.raw_qkv, a.x, a.input_norm_weight, a.qkv_proj_col_major = (raw.data_ptr(), d["x"].data_ptr(),
+                                                                 d["w_in"].data_ptr(), d["w_qkv"].data_ptr())
+    a.batch_count, a.hidden_size, a.cols, a.q_width, a.k_width = 1, gc.HIDDEN, case["cols"], case["q_width"], case["k_width"]
+    a.norm_mode = kv.NORM_RSQRT_APPROX
+    kv.decode_ingress(a)
+    outs = [torch.zeros(gc.HIDDEN, dtype=torch.int16, device="cuda") for _ in range(4)]
+    ticket = torch.zeros(1, dtype=torch.int32, device="cuda")
+    e = kv.EgressArgs()
+    e.residual_out, e.normed_out, e.ffn_residual, e.ffn_x = (t.data_ptr() for t in outs)
+    e.attention_out, e.o_proj_col_major, e.post_norm_weight, e.pre_ffn_norm_weight, e.x = (
+        d[n].data_ptr() for n in ("attn", "w_o", "w_post", "w_pre", "x"))
+    e.ticket, e.batch_count, e.hidden_size, e.attention_width = ticket.data_ptr(), 1, gc.HIDDEN, case["q_width"]
+    e.norm_mode = kv.NORM_RSQRT_APPROX
+    kv.decode_egress(e)
+    torch.cuda.synchronize()
+    for n, t in zip(gc.PROJECTION_OUTPUTS, [raw] + outs):
+        assert np.array_equal(host_u16(t), g[n]), (n, int((host_u16(t) != g[n]).sum()))

@@ -1,0 +1,241 @@
+"""The decode projections either side of the KV path through the C-ABI:
+b200kv_decode_ingress_bf16 (input RMSNorm + [Q|K|V] projection), b200kv_decode_egress_bf16 (O projection +
+post-attention norm + residual + pre-FFN norm) and b200kv_decode_attention_layer_bf16 (ingress + layer-step +
+egress). The results are bf16 roundings of fp32 sums whose order is the reference block's, so the comparison
+is bit for bit: in B200KV_NORM_IEEE mode against the CPU oracle, in the default mode against the
+reference's own phases compiled for this GPU (oracle/_ref), when that library is present."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from tests import helpers
+from tests.gpu_util import dev, host_u16, need_gpu
+from tests.helpers import ATTN_MAX_ABS, ATTN_MAX_REL, attention_error
+
+pytestmark = [pytest.mark.gpu, need_gpu]
+
+HIDDEN = 3840
+POISON = 0x7FC0  # bf16 NaN
+
+
+def _weights(rng, cols, width):
+    """Column-major projection matrix with entries ~ N(0, 1/width): outputs of unit scale."""
+    return helpers.bf16_normal(rng, (cols, width), std=1.0 / np.sqrt(width))
+
+
+def _poison(*shape):
+    return torch.full(shape, POISON, dtype=torch.int16, device="cuda")
+
+
+def _ingress_case(seed, rows, cols):
+    rng = np.random.default_rng(seed)
+    return dict(x=helpers.bf16_normal(rng, (rows, HIDDEN), std=1.7),
+                w_in=helpers.bf16_normal(rng, (HIDDEN,), std=0.05, mean=1.0), w=_weights(rng, cols, HIDDEN))
+
+
+def _run_ingress(kv, case, rows, cols, q_width, k_width, norm_mode):
+    raw = _poison(rows * cols)
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    keep = [dev(case["x"]), dev(case["w_in"]), dev(case["w"])]
+    a = kv.IngressArgs()
+    a.raw_qkv, a.x, a.input_norm_weight, a.qkv_proj_col_major = (raw.data_ptr(), keep[0].data_ptr(),
+                                                                 keep[1].data_ptr(), keep[2].data_ptr())
+    a.batch_count, a.hidden_size, a.cols, a.q_width, a.k_width = rows, HIDDEN, cols, q_width, k_width
+    a.norm_mode, a.status = norm_mode, status.data_ptr()
+    kv.decode_ingress(a)
+    torch.cuda.synchronize()
+    assert status[0].item() == 0
+    return host_u16(raw), keep
+
+
+def _segments(raw, rows, cols, q_width, k_width):
+    """Row r of the [q | k | v] tensors the ingress lays out one after the other -> [rows, cols]."""
+    v_width = cols - q_width - k_width
+    q = raw[: rows * q_width].reshape(rows, q_width)
+    k = raw[rows * q_width: rows * (q_width + k_width)].reshape(rows, k_width)
+    v = raw[rows * (q_width + k_width):].reshape(rows, v_width)
+    return np.concatenate([q, k, v], axis=1)
+
+
+@pytest.mark.parametrize("rows,cols,q_width,k_width", [(1, 8192, 4096, 2048), (3, 8192, 4096, 2048),
+                                                        (1, 8704, 8192, 512), (2, 8704, 8192, 512)])
+def test_ingress_matches_the_oracle_bit_for_bit(kv, orc, rows, cols, q_width, k_width):
+    case = _ingress_case(100 + rows + cols, rows, cols)
+    raw, _ = _run_ingress(kv, case, rows, cols, q_width, k_width, kv.NORM_IEEE)
+    got = _segments(raw, rows, cols, q_width, k_width)
+    for r in range(rows):
+        want, _ = orc.decode_ingress(case["x"][r], case["w_in"], case["w"])
+        assert np.array_equal(got[r], want), (r, int((got[r] != want).sum()))
+
+
+def test_ingress_small_and_odd_column_counts(kv, orc):
+    """Fewer columns than CTAs x stage, and a count that leaves the last stage of a CTA ragged."""
+    for cols in (8, 40, 1096):
+        case = _ingress_case(7 + cols, 1, cols)
+        raw, _ = _run_ingress(kv, case, 1, cols, cols, 0, kv.NORM_IEEE)
+        want, _ = orc.decode_ingress(case["x"][0], case["w_in"], case["w"])
+        assert np.array_equal(raw, want), cols
+
+
+def _egress_case(seed, rows, width):
+    rng = np.random.default_rng(seed)
+    return dict(attn=helpers.bf16_normal(rng, (rows, width)), w_o=_weights(rng, HIDDEN, width),
+                w_post=helpers.bf16_normal(rng, (HIDDEN,), std=0.05, mean=1.0),
+                w_pre=helpers.bf16_normal(rng, (HIDDEN,), std=0.05, mean=1.0),
+                x=helpers.bf16_normal(rng, (rows, HIDDEN), std=1.7))
+
+
+def _run_egress(kv, case, rows, width, norm_mode, with_ffn_x=True, ticket=None, calls=1):
+    outs = [_poison(rows, HIDDEN) for _ in range(4)]
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    ticket = torch.zeros(rows, dtype=torch.int32, device="cuda") if ticket is None else ticket
+    keep = [dev(case[n]) for n in ("attn", "w_o", "w_post", "w_pre", "x")]
+    a = kv.EgressArgs()
+    a.residual_out, a.normed_out, a.ffn_residual = (t.data_ptr() for t in outs[:3])
+    a.ffn_x = outs[3].data_ptr() if with_ffn_x else None
+    a.attention_out, a.o_proj_col_major, a.post_norm_weight, a.pre_ffn_norm_weight, a.x = (
+        t.data_ptr() for t in keep)
+    a.ticket, a.batch_count, a.hidden_size, a.attention_width = ticket.data_ptr(), rows, HIDDEN, width
+    a.norm_mode, a.status = norm_mode, status.data_ptr()
+    for _ in range(calls):
+        kv.decode_egress(a)
+    torch.cuda.synchronize()
+    assert status[0].item() == 0
+    assert int(ticket.abs().sum().item()) == 0, "the ticket must be left at zero"
+    return [host_u16(t).reshape(rows, HIDDEN) for t in outs]
+
+
+@pytest.mark.parametrize("rows,width", [(1, 4096), (2, 4096), (1, 8192), (3, 8192)])
+def test_egress_matches_the_oracle_bit_for_bit(kv, orc, rows, width):
+    case = _egress_case(200 + rows + width, rows, width)
+    got = _run_egress(kv, case, rows, width, kv.NORM_IEEE, calls=3)   # repeated: the ticket is reused
+    for r in range(rows):
+        want = orc.decode_egress(case["attn"][r], case["w_o"], case["w_post"], case["w_pre"], case["x"][r])
+        for name, g, w in zip(("residual_out", "normed_out", "ffn_residual", "ffn_x"), got, want):
+            assert np.array_equal(g[r], w), (name, r, int((g[r] != w).sum()))
+
+
+def test_egress_without_ffn_x_leaves_it_alone(kv, orc):
+    case = _egress_case(31, 1, 4096)
+    got = _run_egress(kv, case, 1, 4096, kv.NORM_IEEE, with_ffn_x=False)
+    want = orc.decode_egress(case["attn"][0], case["w_o"], case["w_post"], case["w_pre"], case["x"][0])
+    assert np.array_equal(got[2][0], want[2])
+    assert (got[3] == POISON).all()
+
+
+def test_projection_argument_checks(kv):
+    a = kv.IngressArgs()
+    assert kv.decode_ingress(a, check=False) == kv.CUDA_SUCCESS          # zero rows: nothing to do
+    a.batch_count, a.hidden_size, a.cols, a.q_width = 1, HIDDEN, 8192, 4096
+    assert kv.decode_ingress(a, check=False) == kv.CUDA_ERROR_INVALID_VALUE  # null pointers
+    e = kv.EgressArgs()
+    e.batch_count, e.hidden_size, e.attention_width = 1, HIDDEN, 1000
+    assert kv.decode_egress(e, check=False) == kv.CUDA_ERROR_INVALID_VALUE
+
+
+def _ref():
+    from oracle import ref_binding
+
+    if not ref_binding.has_projections():
+        pytest.skip("oracle/_ref (the reference's own kernels) is not built here")
+    return ref_binding
+
+
+@pytest.mark.parametrize("global_geometry", [False, True])
+def test_default_mode_equals_the_reference_kernels(kv, global_geometry):
+    """Default norm mode (rsqrt.approx as in the reference's GPU code) against the reference's own phases on
+    the same GPU: raw q/k/v, O projection, both norms and the residual, all bit for bit."""
+    ref = _ref()
+    cols, q_width, k_width = (8704, 8192, 512) if global_geometry else (8192, 4096, 2048)
+    case = _ingress_case(300 + cols, 1, cols)
+    raw, keep = _run_ingress(kv, case, 1, cols, q_width, k_width, kv.NORM_RSQRT_APPROX)
+    ref_raw, ref_normed = _poison(cols), _poison(HIDDEN)
+    assert ref.decode_ingress(ref_raw, ref_normed, keep[0], keep[1], keep[2], global_geometry) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(raw, host_u16(ref_raw)), int((raw != host_u16(ref_raw)).sum())
+
+    width = q_width
+    ecase = _egress_case(400 + cols, 1, width)
+    got = _run_egress(kv, ecase, 1, width, kv.NORM_RSQRT_APPROX)
+    outs = [_poison(HIDDEN) for _ in range(4)]
+    keep = [dev(ecase[n]) for n in ("attn", "w_o", "w_post", "w_pre", "x")]
+    assert ref.decode_egress(*outs, *keep, global_geometry) == 0
+    torch.cuda.synchronize()
+    for name, g, w in zip(("residual_out", "normed_out", "ffn_residual", "ffn_x"), got, outs):
+        assert np.array_equal(g[0], host_u16(w)), (name, int((g[0] != host_u16(w)).sum()))
+
+
+@pytest.mark.parametrize("rows,window", [(1, 1024), (3, 0)])
+def test_attention_layer_chain(kv, orc, rows, window):
+    """Layer input -> FFN input in one call. Oracle: ingress, append, double-precision attention (tolerance),
+    then egress from the attention rows the GPU produced (so the last stage is again compared bit for bit)."""
+    HQ, H, D = 16, 8, 256
+    cols, q_width, k_width = 8192, 4096, 2048
+    rng = np.random.default_rng(500 + rows)
+    start = np.array([700, 33, 1500][:rows], np.int32) if window == 0 else np.array([1500][:rows], np.int32)
+    acase = helpers.make_append_case(41 + rows, start, window=window, ring_pages=None if window == 0 else 65,
+                                     max_pos=int(start.max()) + 2)
+    cfg_t = acase.cfg
+    cfg = kv.make_kv_config(*cfg_t)
+    elems = cfg_t[0] * cfg_t[1] * cfg_t[2] * cfg_t[5] * cfg_t[6]
+    ck = orc.f32_to_bf16(rng.standard_normal(elems, dtype=np.float32))
+    cv = orc.f32_to_bf16(rng.standard_normal(elems, dtype=np.float32))
+    icase = _ingress_case(600 + rows, rows, cols)
+    ecase = _egress_case(700 + rows, rows, q_width)
+    length = (start + 1).astype(np.int32)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    num_splits = kv.plan_balanced(rows, sms)
+
+    d = {n: dev(v) for n, v in dict(ck=ck, cv=cv, table=acase.page_table, pos=start, length=length, qw=acase.q_w,
+                                    kw=acase.k_w, cos=acase.cos, sin=acase.sin, x=icase["x"], w_in=icase["w_in"],
+                                    w=icase["w"], w_o=ecase["w_o"], w_post=ecase["w_post"],
+                                    w_pre=ecase["w_pre"]).items()}
+    q, out = _poison(rows, HQ, D), _poison(rows, HQ, D)
+    n_part = rows * HQ * num_splits
+    pm = torch.zeros(n_part, dtype=torch.float32, device="cuda")
+    pl, pacc = pm.clone(), torch.zeros(n_part * D, dtype=torch.float32, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    raw = _poison(rows * cols)
+    outs = [_poison(rows, HIDDEN) for _ in range(4)]
+    ticket = torch.zeros(rows, dtype=torch.int32, device="cuda")
+
+    a = kv.AttentionLayerArgs()
+    s = a.kv
+    s.q, s.out, s.lse = q.data_ptr(), out.data_ptr(), None
+    s.partial_m, s.partial_l, s.partial_acc = pm.data_ptr(), pl.data_ptr(), pacc.data_ptr()
+    s.cache_k, s.cache_v, s.cache_config = d["ck"].data_ptr(), d["cv"].data_ptr(), cfg
+    s.page_table, s.token_position, s.seq_lengths = d["table"].data_ptr(), d["pos"].data_ptr(), d["length"].data_ptr()
+    s.cache_layer, s.split_size, s.num_splits, s.softmax_scale = 0, 0, num_splits, 1.0 / 16.0
+    s.q_norm_weight, s.k_norm_weight, s.cos, s.sin = (d["qw"].data_ptr(), d["kw"].data_ptr(), d["cos"].data_ptr(),
+                                                     d["sin"].data_ptr())
+    s.batch_count, s.q_heads, s.rotary_dim, s.norm_mode, s.status = rows, HQ, D, kv.NORM_IEEE, status.data_ptr()
+    a.attention_x, a.attention_input_norm_weight = d["x"].data_ptr(), d["w_in"].data_ptr()
+    a.attention_qkv_proj_col_major, a.attention_o_proj_col_major = d["w"].data_ptr(), d["w_o"].data_ptr()
+    a.attention_post_norm_weight, a.attention_pre_ffn_norm_weight = d["w_post"].data_ptr(), d["w_pre"].data_ptr()
+    a.raw_qkv = raw.data_ptr()
+    a.residual_out, a.normed_out, a.ffn_residual, a.ffn_x = (t.data_ptr() for t in outs)
+    a.ticket, a.hidden_size, a.has_v_projection = ticket.data_ptr(), HIDDEN, 1
+    kv.decode_attention_layer(a)
+    torch.cuda.synchronize()
+    assert status[0].item() == 0
+
+    raw_rows = np.stack([orc.decode_ingress(icase["x"][r], icase["w_in"], icase["w"])[0] for r in range(rows)])
+    rq = np.ascontiguousarray(raw_rows[:, :q_width]).reshape(rows, HQ, D)
+    rk = np.ascontiguousarray(raw_rows[:, q_width:q_width + k_width]).reshape(rows, H, D)
+    rv = np.ascontiguousarray(raw_rows[:, q_width + k_width:]).reshape(rows, H, D)
+    qp = np.zeros((rows, HQ, D), np.uint16)
+    orc.decode_append(qp, ck, cv, cfg_t, acase.page_table, start, 0, rq, rk, rv, acase.q_w, acase.k_w, acase.cos,
+                      acase.sin, rows, HQ, D)
+    assert np.array_equal(host_u16(q), qp.reshape(-1))
+    assert np.array_equal(host_u16(d["ck"]), ck) and np.array_equal(host_u16(d["cv"]), cv)
+    ref, _ = orc.decode_attention_f64(qp, ck, cv, acase.page_table, length, cfg_t, 0, 1.0 / 16.0, rows, HQ)
+    max_abs, max_rel = attention_error(host_u16(out), ref)
+    assert max_abs <= ATTN_MAX_ABS and max_rel <= ATTN_MAX_REL, (max_abs, max_rel)
+    attn = host_u16(out).reshape(rows, q_width)
+    got = [host_u16(t).reshape(rows, HIDDEN) for t in outs]
+    for r in range(rows):
+        want = orc.decode_egress(attn[r], ecase["w_o"], ecase["w_post"], ecase["w_pre"], icase["x"][r])
+        for name, g, w in zip(("residual_out", "normed_out", "ffn_residual", "ffn_x"), got, want):
+            assert np.array_equal(g[r], w), (name, r, int((g[r] != w).sum()))
