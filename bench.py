@@ -55,7 +55,7 @@ def parse_args():
                     help="skip timing the reference's own CUDA kernels (oracle/_ref) beside the library")
     ap.add_argument("--split-global", type=int, default=0, help="override the planned global split size")
     ap.add_argument("--split-local", type=int, default=0)
-    ap.add_argument("--workload", default="cfg3", choices=["cfg1", "cfg2", "cfg3", "cfg4", "cfg5", "native_global", "prefill"],
+    ap.add_argument("--workload", default="cfg3", choices=["cfg1", "cfg2", "cfg3", "cfg4", "cfg5", "native_global", "prefill", "layer"],
                     help="BASELINE.json configs (1-based): cfg3 (default) is the batched paged decode the "
                          "metric is quoted on; the others are reported as extra lines on request")
     ap.add_argument("--partition", default="balanced", choices=["balanced", "splits"],
@@ -64,6 +64,7 @@ def parse_args():
     ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"],
                     help="replay each step from a CUDA graph captured once (auto: on for the batch-1 latency "
                          "workloads cfg1/cfg2, where the host cannot issue 3 launches per layer fast enough)")
+    ap.add_argument("--layers", type=int, default=48, help="--workload layer: layers in the stack")
     ap.add_argument("--emulate-world", type=int, default=0,
                     help="tuning aid: on one GPU, run the shard that rank --emulate-rank of this many ranks would own")
     ap.add_argument("--emulate-rank", type=int, default=0)
@@ -108,6 +109,14 @@ def attention_kernel_bytes(seq_len_after_append: np.ndarray, window: int, hkv: i
     pages_touched = (s - 1) // PAGE - first // PAGE + 1
     scales = 4 * pages_touched * hkv * 2 if e_kv == 1 else 0
     return int((live * hkv * D * 2 * e_kv + hq * D * 2 + hq * D * 2 + 4 * pages_touched + scales).sum())
+
+
+def hbm_peak():
+    """The measured copy bandwidth of this pool's B200s (driver-written), else the stated fallback."""
+    peaks_path = REPO / "MEASURED_PEAKS.json"
+    if peaks_path.exists():
+        return float(json.loads(peaks_path.read_text())["hbm_gbs"]), "MEASURED_PEAKS.json hbm_gbs"
+    return 6650.0, "fallback 6.65 TB/s (MEASURED_PEAKS.json absent)"
 
 
 # --------------------------------------------------------------------------- clocks
@@ -804,6 +813,205 @@ def run_native_global(args, kv, torch, sampler):
     }))
 
 
+# --------------------------------------------------------------------------- next row: the decode layer around the KV path
+def run_layer(args, kv, torch, sampler):
+    """Extra line (not a BASELINE config): the attention half of the reference's fused decode layer for batch 1,
+    b200kv_decode_attention_layer_bf16 = input RMSNorm + [Q|K|V] projection (ingress), append + decode attention
+    + combine (the KV path), O projection + post-attention norm + residual + pre-FFN norm (egress), on the stack
+    of BASELINE config 2: --layers layers (48) in the 5:1 pattern, sliding layers on a 1024-token ring, global
+    layers on a linear cache of 4096 keys, 16 Q / 8 KV heads of 256, hidden 3840, every layer with its own
+    seeded weights (94 MB per layer, so nothing is served from L2 twice) and the layer input chained from the
+    previous layer's ffn_residual. One step = one token through all layers; the position is the same every step
+    (the row is rewritten in place), so that a step can be replayed from a CUDA graph. One GPU."""
+    dev = torch.device("cuda")
+    HID, H, QW, KW = 3840, 16, 16 * D, HKV * D
+    COLS = QW + 2 * KW
+    L = args.layers
+    is_global = [(l + 1) % 6 == 0 for l in range(L)]            # gemma4_is_global_layer, src/gemma4.h:105-108
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(args.seed)
+    rng = np.random.default_rng(args.seed)
+
+    def cache(window, ctx, layers):
+        mpps = (window + PAGE - 1) // PAGE + 1 if window else (ctx + PAGE) // PAGE + 1
+        table = rng.permutation(mpps).astype(np.int32)[None, :]
+        cfg = kv.make_kv_config(layers, mpps, PAGE, mpps, 1, HKV, D, window)
+        elems = layers * mpps * PAGE * HKV * D
+        return dict(cfg=cfg, table=torch.from_numpy(table).to(dev),
+                    k=torch.randn(elems, dtype=torch.bfloat16, device=dev, generator=gen),
+                    v=torch.randn(elems, dtype=torch.bfloat16, device=dev, generator=gen),
+                    pos=torch.tensor([ctx], dtype=torch.int32, device=dev),
+                    length=torch.tensor([ctx + 1], dtype=torch.int32, device=dev), keys=min(ctx + 1, window) if window else ctx + 1)
+
+    n_global = sum(is_global)
+    caches = {False: cache(1024, 1500, max(L - n_global, 1)), True: cache(0, 4096, max(n_global, 1))}
+    w_qkv = (torch.randn(L, COLS, HID, dtype=torch.float32, device=dev, generator=gen) * HID ** -0.5).bfloat16() if L <= 8 else None
+    if w_qkv is None:                       # generated layer by layer: the fp32 staging copy of 48 layers is 12 GB
+        w_qkv = torch.empty(L, COLS, HID, dtype=torch.bfloat16, device=dev)
+        for l in range(L):
+            w_qkv[l] = (torch.randn(COLS, HID, dtype=torch.float32, device=dev, generator=gen) * HID ** -0.5).bfloat16()
+    w_o = torch.empty(L, HID, QW, dtype=torch.bfloat16, device=dev)
+    for l in range(L):
+        w_o[l] = (torch.randn(HID, QW, dtype=torch.float32, device=dev, generator=gen) * QW ** -0.5).bfloat16()
+    norm_w = (1.0 + 0.05 * torch.randn(4, L, HID, dtype=torch.float32, device=dev, generator=gen)).bfloat16()
+    head_w = (1.0 + 0.05 * torch.randn(2, D, dtype=torch.float32, device=dev, generator=gen)).bfloat16()
+    x_host = torch.randn(HID, dtype=torch.bfloat16).pin_memory()
+    x = torch.zeros(L + 1, HID, dtype=torch.bfloat16, device=dev)
+    out_host = torch.empty(HID, dtype=torch.bfloat16).pin_memory()
+    cos_s, sin_s = (torch.from_numpy(t).to(dev) for t in kv.fill_rope_tables(4200, D // 2, 1.0e4, D))
+    cos_g, sin_g = (torch.from_numpy(t).to(dev) for t in kv.fill_rope_tables(4200, D // 2, 1.0e6, D))
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    nsplit = kv.plan_balanced(1, sms)
+    q, out = (torch.empty(H * D, dtype=torch.bfloat16, device=dev) for _ in range(2))
+    pm, pl = (torch.empty(H * nsplit, dtype=torch.float32, device=dev) for _ in range(2))
+    pacc = torch.empty(H * nsplit * D, dtype=torch.float32, device=dev)
+    raw = torch.empty(COLS, dtype=torch.bfloat16, device=dev)
+    o_proj, normed, ffn_x = (torch.empty(HID, dtype=torch.bfloat16, device=dev) for _ in range(3))
+    ticket = torch.zeros(1, dtype=torch.int32, device=dev)
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+
+    layers = []
+    seen = {False: 0, True: 0}
+    for l in range(L):
+        c = caches[is_global[l]]
+        a = kv.AttentionLayerArgs()
+        s = a.kv
+        s.q, s.out, s.lse = q.data_ptr(), out.data_ptr(), None
+        s.partial_m, s.partial_l, s.partial_acc = pm.data_ptr(), pl.data_ptr(), pacc.data_ptr()
+        s.cache_k, s.cache_v, s.cache_config = c["k"].data_ptr(), c["v"].data_ptr(), c["cfg"]
+        s.page_table, s.token_position, s.seq_lengths = c["table"].data_ptr(), c["pos"].data_ptr(), c["length"].data_ptr()
+        s.cache_layer, s.split_size, s.num_splits, s.softmax_scale = seen[is_global[l]], 0, nsplit, 1.0 / math.sqrt(D)
+        seen[is_global[l]] += 1
+        s.q_norm_weight, s.k_norm_weight = head_w[0].data_ptr(), head_w[1].data_ptr()
+        s.cos, s.sin = (cos_g.data_ptr(), sin_g.data_ptr()) if is_global[l] else (cos_s.data_ptr(), sin_s.data_ptr())
+        s.batch_count, s.q_heads, s.rotary_dim, s.norm_mode, s.status = 1, H, D, kv.NORM_RSQRT_APPROX, status.data_ptr()
+        a.attention_x, a.attention_input_norm_weight = x[l].data_ptr(), norm_w[0, l].data_ptr()
+        a.attention_qkv_proj_col_major, a.attention_o_proj_col_major = w_qkv[l].data_ptr(), w_o[l].data_ptr()
+        a.attention_post_norm_weight, a.attention_pre_ffn_norm_weight = norm_w[1, l].data_ptr(), norm_w[2, l].data_ptr()
+        a.raw_qkv, a.residual_out, a.normed_out = raw.data_ptr(), o_proj.data_ptr(), normed.data_ptr()
+        a.ffn_residual, a.ffn_x, a.ticket = x[l + 1].data_ptr(), ffn_x.data_ptr(), ticket.data_ptr()
+        a.hidden_size, a.has_v_projection = HID, 1
+        layers.append(a)
+
+    def step():
+        for a in layers:
+            kv.decode_attention_layer(a)
+
+    def step_e2e():
+        x[0].copy_(x_host, non_blocking=True)
+        run()
+        out_host.copy_(x[L], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    def timed(fn, n):
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    x[0].copy_(x_host)
+    use_graph = args.graph != "off"
+    run = step
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    if use_graph:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step()
+        run = graph.replay
+        for _ in range(3):
+            run()
+    steps = max(3, min(args.steps, 50))
+    if sampler:
+        sampler.mark("timed_begin")
+    ms = timed(run, steps)
+    if sampler:
+        sampler.mark("timed_end")
+    e2e_ms = timed(step_e2e, max(3, min(args.e2e_steps, 20)))
+
+    # the two projection kernels alone, every call on another layer's matrix (cold in L2)
+    def only(kind):
+        calls = []
+        for l, a in enumerate(layers):
+            if kind == "ingress":
+                i = kv.IngressArgs()
+                i.raw_qkv, i.x, i.input_norm_weight = raw.data_ptr(), x[l].data_ptr(), norm_w[0, l].data_ptr()
+                i.qkv_proj_col_major, i.batch_count, i.hidden_size = w_qkv[l].data_ptr(), 1, HID
+                i.cols, i.q_width, i.k_width, i.norm_mode, i.status = COLS, QW, KW, kv.NORM_RSQRT_APPROX, status.data_ptr()
+                calls.append((kv.decode_ingress, i))
+            else:
+                e = kv.EgressArgs()
+                e.residual_out, e.normed_out, e.ffn_residual, e.ffn_x = (o_proj.data_ptr(), normed.data_ptr(),
+                                                                         x[l + 1].data_ptr(), ffn_x.data_ptr())
+                e.attention_out, e.o_proj_col_major = out.data_ptr(), w_o[l].data_ptr()
+                e.post_norm_weight, e.pre_ffn_norm_weight = norm_w[1, l].data_ptr(), norm_w[2, l].data_ptr()
+                e.x, e.ticket, e.batch_count, e.hidden_size = x[l].data_ptr(), ticket.data_ptr(), 1, HID
+                e.attention_width, e.norm_mode, e.status = QW, kv.NORM_RSQRT_APPROX, status.data_ptr()
+                calls.append((kv.decode_egress, e))
+
+        def go():
+            for fn, a in calls:
+                fn(a)
+        go()
+        return timed(go, max(3, steps // 4)) * 1e3 / L
+
+    us_ingress, us_egress = only("ingress"), only("egress")
+    reference = None
+    try:
+        from oracle import ref_binding as ref
+        if ref.has_projections() and not args.no_reference_cuda:
+            scratch = torch.empty(HID, dtype=torch.bfloat16, device=dev)
+
+            def ref_in():
+                for l in range(L):
+                    ref.decode_ingress(raw, scratch, x[l], norm_w[0, l], w_qkv[l], False)
+
+            def ref_out():
+                for l in range(L):
+                    ref.decode_egress(o_proj, normed, scratch, ffn_x, out, w_o[l], norm_w[1, l], norm_w[2, l], x[l], False)
+            ref_in(); ref_out()
+            reference = {"kernels": "phase_decode_rmsnorm_project_bf16 / project_attention_out_post_attention of "
+                                    "src/gemma4_flash_attention_decode.cu (sm_100a build, cooperative launch)",
+                         "ingress_us": timed(ref_in, 3) * 1e3 / L, "egress_us": timed(ref_out, 3) * 1e3 / L}
+    except OSError:
+        reference = None
+    clocks = None
+    if sampler:
+        sampler.mark("load_end")
+        clocks = sampler.stop()
+
+    w_bytes = (COLS * HID + HID * QW) * 2
+    small = (HID * 2 * 2 + COLS * 2 + QW * 2 + HID * 2 * 5)        # rows read and written around the matrices
+    per_layer = [w_bytes + small + layer_step_bytes(np.array([caches[g]["keys"]]), 1024 if not g else 0) for g in is_global]
+    step_bytes = int(sum(per_layer))
+    peak, peak_source = hbm_peak()
+    gbs = step_bytes / (ms * 1e-3) / 1e9
+    ingress_gbs = COLS * HID * 2 / (us_ingress * 1e-6) / 1e9
+    print(json.dumps({
+        "metric": "decode attention layer (QKV projection + KV append + decode attention + O projection), batch 1: "
+                  "achieved HBM GB/s (us per layer alongside)", "unit": "GB/s", "value": gbs, "n_gpus": 1,
+        "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16 (fp32 accumulate)", "data": "synthetic",
+        "config": {"workload": "next row, not a BASELINE config: b200kv_decode_attention_layer_bf16 over %d layers "
+                               "(5 sliding : 1 global, ring 1024 / linear 4096), batch 1, hidden 3840" % L,
+                   "launch": "one CUDA graph replay per step" if use_graph else "stream launches",
+                   "l2": "every layer has its own 94 MB of weights: %d MB per step, nothing revisited within L2's reach" % (step_bytes >> 20)},
+        "us_per_layer": ms * 1e3 / L, "frac_of_hbm_peak": gbs / peak,
+        "kernels_alone_us": {"ingress": us_ingress, "egress": us_egress},
+        "roofline": {"bound": "hbm", "kernel": "decode_projection_kernel (QKV projection, 8192 x 3840)", "achieved": ingress_gbs,
+                     "peak": peak, "unit": "GB/s", "frac": ingress_gbs / peak, "traffic": None, "peak_source": peak_source,
+                     "algorithmic_bytes_per_launch": COLS * HID * 2, "avg_launch_ms": us_ingress * 1e-3},
+        "e2e": {"value": step_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": HID * 2,
+                "d2h_bytes_per_step": HID * 2, "ms_per_step": e2e_ms},
+        "gpu_launches": 4 * L * steps, "device_status": int(status[0].item()), "reference_cuda": reference, "clocks": clocks,
+    }))
+
+
 # --------------------------------------------------------------------------- next row: prompt attention
 def run_prefill(args, kv, torch, sampler):
     """Extra lines (not a BASELINE config): the two prompt-attention entry points of
@@ -919,6 +1127,11 @@ def main():
         if world > 1:
             raise SystemExit("--workload prefill is a one-GPU line")
         run_prefill(args, kv, torch, sampler)
+        return
+    if args.workload == "layer":
+        if world > 1:
+            raise SystemExit("--workload layer is a one-GPU line")
+        run_layer(args, kv, torch, sampler)
         return
     if args.workload == "native_global":
         if world > 1:

@@ -51,6 +51,10 @@ struct BalancedParams {
   const float *sin;
   const int32_t *token_position;
   __nv_bfloat16 *q_prepared;
+  // Non-zero: raw_q / raw_k / raw_v are written by the kernel launched just
+  // before this one (the QKV projection), so the consumer warps wait for it
+  // before they read a raw row; the key stream of the producer warp is not held.
+  int32_t raw_from_predecessor;
 };
 
 enum : int { kAttentionOnly = 0, kFusedApprox = 1, kFusedIeee = 2 };

@@ -146,6 +146,7 @@ __device__ __forceinline__ void append_unstreamed_rows(const BalancedParams &p,
     const int count = s_prefix[b + 1] - s_prefix[b];
     if (pos >= first && pos < first + count) continue;  // its streamer does it
     uint4 qpack[2];
+    if (p.raw_from_predecessor) pdl_wait_for_predecessor();
     prepare_rows<kIeee>(qpack, p, b, head, pos, true, wbuf, lane);
     pdl_wait_for_predecessor();
     store_appended_rows(p, qpack, b, head, pos, append_page(p, b, pos), wbuf,
@@ -288,7 +289,11 @@ __global__ __launch_bounds__(T::kThreads, T::kCtasPerSm) void decode_balanced_ke
   }
 
   // -------------------------------- consumers --------------------------------
-  if constexpr (!kFused) pdl_wait_for_predecessor();  // q comes from the append
+  if constexpr (!kFused) {
+    pdl_wait_for_predecessor();  // q comes from the append
+  } else {
+    if (p.raw_from_predecessor) pdl_wait_for_predecessor();
+  }
   const int head = warp;  // kWarpsPerHead == 1
   std::conditional_t<T::kFp8, Fp8WarpState, WarpState<T>> st;
   int b = b_start, flat = r0;
@@ -539,6 +544,7 @@ cudaError_t decode_layer_step_fused_bf16(const AppendArgs &ap,
   p.sin = ap.sin;
   p.token_position = ap.token_position;
   p.q_prepared = ap.q_prepared;
+  p.raw_from_predecessor = ap.raw_from_predecessor ? 1 : 0;
   using T = DecodeTraits<256, 8, 2, 8>;
   const int64_t slots = int64_t(a.batch_count) * a.num_splits;
   const bool small = a.batch_count <= kSmallBalancedBatch;

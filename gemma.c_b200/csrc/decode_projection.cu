@@ -123,9 +123,11 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 // by 512 threads (src/gemma4_rmsnorm.cu:27-87): fma chain per pack, xor fold
 // per warp, xor fold of the 16 warp sums with zeros in lanes 16..31.
 // `red` is 16 floats of shared memory not used by anything else until the
-// barrier inside has been passed by all 512 threads.
+// barrier inside has been passed by all 512 threads. `g` is this thread's pack
+// of the weight (loaded by the caller ahead of the values: it never depends on
+// a preceding kernel).
 __device__ __forceinline__ uint4 hidden_rmsnorm_pack(
-    const uint4 &values, const __nv_bfloat16 *weight, float *red, int thread,
+    const uint4 &values, const uint4 &g, float *red, int thread,
     int norm_mode) {
   const int lane = thread & 31, warp = thread >> 5;
   float ss = 0.0f;
@@ -141,7 +143,6 @@ __device__ __forceinline__ uint4 hidden_rmsnorm_pack(
                           : rsqrtf(t);
   uint4 result = make_uint4(0, 0, 0, 0);
   if (thread < kProjHiddenPacks) {
-    const uint4 g = __ldg(reinterpret_cast<const uint4 *>(weight) + thread);
     const uint32_t v[4] = {values.x, values.y, values.z, values.w};
     const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
     uint32_t r[4];
@@ -154,6 +155,13 @@ __device__ __forceinline__ uint4 hidden_rmsnorm_pack(
     result = make_uint4(r[0], r[1], r[2], r[3]);
   }
   return result;
+}
+
+__device__ __forceinline__ uint4 load_hidden_pack(const __nv_bfloat16 *row,
+                                                  int thread) {
+  return thread < kProjHiddenPacks
+             ? __ldg(reinterpret_cast<const uint4 *>(row) + thread)
+             : make_uint4(0, 0, 0, 0);
 }
 
 // One column: this lane's 16 chain sums, folded in the block's order.
@@ -281,7 +289,17 @@ decode_projection_kernel(const ProjParams p) {
     return;
   }
 
-  // Consumers: the input row is the preceding kernel's output.
+  // Consumers: the input row is the preceding kernel's output; the norm
+  // weights and the layer input (the residual) are older than that.
+  uint4 gamma0 = make_uint4(0, 0, 0, 0), gamma1 = gamma0, gamma2 = gamma0,
+        resid = gamma0;
+  if constexpr (!kEgress) {
+    gamma0 = load_hidden_pack(p.input_norm_weight, thread);
+  } else {
+    gamma1 = load_hidden_pack(p.post_norm_weight, thread);
+    if (p.ffn_x != nullptr) gamma2 = load_hidden_pack(p.pre_ffn_norm_weight, thread);
+    resid = load_hidden_pack(p.residual_in + int64_t(row) * kProjHidden, thread);
+  }
   pdl_wait_for_predecessor();
   pdl_release_successor();
   {
@@ -292,8 +310,8 @@ decode_projection_kernel(const ProjParams p) {
       if (thread < kProjHiddenPacks) {
         values = *(reinterpret_cast<const uint4 *>(x_row) + thread);
       }
-      const uint4 normed = hidden_rmsnorm_pack(values, p.input_norm_weight,
-                                               red[0], thread, p.norm_mode);
+      const uint4 normed =
+          hidden_rmsnorm_pack(values, gamma0, red[0], thread, p.norm_mode);
       if (thread < kProjHiddenPacks) x_rows[thread] = normed;
     } else {
       for (int pack = thread; pack < T::kWidth / 8; pack += kProjConsumerThreads) {
@@ -346,14 +364,13 @@ decode_projection_kernel(const ProjParams p) {
     named_barrier_sync(1, kProjConsumerThreads);
     if (last_flag == 0u) return;
     __threadfence();
-    uint4 o = make_uint4(0, 0, 0, 0), resid = make_uint4(0, 0, 0, 0);
+    uint4 o = make_uint4(0, 0, 0, 0);
     const int64_t base = int64_t(row) * kProjHidden;
     if (thread < kProjHiddenPacks) {
       o = __ldcg(reinterpret_cast<const uint4 *>(p.out + base) + thread);
-      resid = __ldg(reinterpret_cast<const uint4 *>(p.residual_in + base) + thread);
     }
     const uint4 normed =
-        hidden_rmsnorm_pack(o, p.post_norm_weight, red[1], thread, p.norm_mode);
+        hidden_rmsnorm_pack(o, gamma1, red[1], thread, p.norm_mode);
     uint4 sum = make_uint4(0, 0, 0, 0);
     if (thread < kProjHiddenPacks) {
       const uint32_t a[4] = {resid.x, resid.y, resid.z, resid.w};
@@ -369,8 +386,8 @@ decode_projection_kernel(const ProjParams p) {
       *(reinterpret_cast<uint4 *>(p.ffn_residual + base) + thread) = sum;
     }
     if (p.ffn_x != nullptr) {
-      const uint4 fx = hidden_rmsnorm_pack(sum, p.pre_ffn_norm_weight, red[2],
-                                           thread, p.norm_mode);
+      const uint4 fx =
+          hidden_rmsnorm_pack(sum, gamma2, red[2], thread, p.norm_mode);
       if (thread < kProjHiddenPacks) {
         *(reinterpret_cast<uint4 *>(p.ffn_x + base) + thread) = fx;
       }

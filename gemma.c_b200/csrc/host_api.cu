@@ -938,8 +938,14 @@ void b200kv_plan_splits(int32_t batch_count, int32_t max_live_keys,
                            sm_count, split_size, num_splits);
 }
 
-int b200kv_decode_layer_step_bf16(const B200KvLayerStepArgs *s,
-                                  b200kv_stream stream) {
+}  // extern "C"
+
+namespace {
+
+// raw_from_predecessor: the raw rows come from the kernel enqueued just before
+// (the attention-layer call's QKV projection), not from an earlier step.
+int layer_step(const B200KvLayerStepArgs *s, bool raw_from_predecessor,
+               b200kv_stream stream) {
   if (s == nullptr) return cudaErrorInvalidValue;
   using bf = __nv_bfloat16;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -962,6 +968,7 @@ int b200kv_decode_layer_step_bf16(const B200KvLayerStepArgs *s,
   a.q_heads = s->q_heads;
   a.rotary_dim = s->rotary_dim;
   a.norm_mode = s->norm_mode;
+  a.raw_from_predecessor = raw_from_predecessor;
 
   b200kv::DecodeArgs d;
   d.out = reinterpret_cast<bf *>(s->out);
@@ -1017,6 +1024,15 @@ int b200kv_decode_layer_step_bf16(const B200KvLayerStepArgs *s,
         static_cast<cudaEvent_t>(s->event_after_attention), st));
   }
   return cudaSuccess;
+}
+
+}  // namespace
+
+extern "C" {
+
+int b200kv_decode_layer_step_bf16(const B200KvLayerStepArgs *s,
+                                  b200kv_stream stream) {
+  return layer_step(s, false, stream);
 }
 
 int b200kv_decode_step_bf16(const B200KvLayerStepArgs *layers,
@@ -1105,7 +1121,7 @@ int b200kv_decode_attention_layer_bf16(const B200KvAttentionLayerArgs *s,
   step.raw_k = s->raw_qkv + rows * q_width;
   step.raw_v = s->has_v_projection ? s->raw_qkv + rows * (q_width + k_width)
                                    : nullptr;
-  st = b200kv_decode_layer_step_bf16(&step, stream);
+  st = layer_step(&step, true, stream);
   if (st != cudaSuccess) return st;
 
   B200KvEgressArgs out = {};

@@ -75,6 +75,11 @@ struct AppendArgs {
   int32_t q_heads = 0;
   int32_t rotary_dim = 0;
   int32_t norm_mode = B200KV_NORM_RSQRT_APPROX;
+  // The raw rows are written by the kernel enqueued just before this call (the
+  // QKV projection). Only the fused layer-step needs to be told: it reads raw
+  // rows before it waits for its predecessor unless this is set. The append
+  // kernels wait before anything else.
+  bool raw_from_predecessor = false;
 };
 
 cudaError_t decode_append_bf16(const AppendArgs &args, cudaStream_t stream);
