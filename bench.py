@@ -986,6 +986,24 @@ def run_layer(args, kv, torch, sampler):
         clocks = sampler.stop()
 
     w_bytes = (COLS * HID + HID * QW) * 2
+    cpu = None
+    if not args.no_cpu_baseline:          # the oracle's two projections of layer 0 on all host threads
+        from oracle import binding as orc
+
+        def bits(t):
+            return t.detach().cpu().contiguous().view(torch.int16).numpy().view(np.uint16)
+        h = dict(x=bits(x[0]), w_in=bits(norm_w[0, 0]), w=bits(w_qkv[0]), attn=bits(out), w_o=bits(w_o[0]),
+                 w_post=bits(norm_w[1, 0]), w_pre=bits(norm_w[2, 0]))
+        threads = orc.hardware_threads()
+        reps, t0 = 0, time.time()
+        while time.time() - t0 < max(args.cpu_seconds, 1.0):
+            orc.decode_ingress(h["x"], h["w_in"], h["w"], threads=threads)
+            orc.decode_egress(h["attn"], h["w_o"], h["w_post"], h["w_pre"], h["x"], threads=threads)
+            reps += 1
+        cpu_s = (time.time() - t0) / reps
+        cpu = {"value": w_bytes / cpu_s / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+               "sample": "the two projections of one layer (94 MB of weights), %d repetitions, %.1f s of host time, "
+                         "oracle port on all host threads; the KV path's CPU figure is the default workload's" % (reps, cpu_s * reps)}
     small = (HID * 2 * 2 + COLS * 2 + QW * 2 + HID * 2 * 5)        # rows read and written around the matrices
     per_layer = [w_bytes + small + layer_step_bytes(np.array([caches[g]["keys"]]), 1024 if not g else 0) for g in is_global]
     step_bytes = int(sum(per_layer))
@@ -1008,7 +1026,7 @@ def run_layer(args, kv, torch, sampler):
                      "algorithmic_bytes_per_launch": COLS * HID * 2, "avg_launch_ms": us_ingress * 1e-3},
         "e2e": {"value": step_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": HID * 2,
                 "d2h_bytes_per_step": HID * 2, "ms_per_step": e2e_ms},
-        "gpu_launches": 4 * L * steps, "device_status": int(status[0].item()), "reference_cuda": reference, "clocks": clocks,
+        "gpu_launches": 4 * L * steps, "device_status": int(status[0].item()), "reference_cuda": reference, "cpu_baseline": cpu, "clocks": clocks,
     }))
 
 
