@@ -65,6 +65,9 @@ def parse_args():
                     help="replay each step from a CUDA graph captured once (auto: on for the batch-1 latency "
                          "workloads cfg1/cfg2, where the host cannot issue 3 launches per layer fast enough)")
     ap.add_argument("--layers", type=int, default=48, help="--workload layer: layers in the stack")
+    ap.add_argument("--gather", default="peer", choices=["peer", "nccl"],
+                    help="cfg4 on more than one GPU: all-gather of the head outputs by the library's peer-memory "
+                         "kernel (b200kv_peer_allgather) or by ncclAllGather")
     ap.add_argument("--emulate-world", type=int, default=0,
                     help="tuning aid: on one GPU, run the shard that rank --emulate-rank of this many ranks would own")
     ap.add_argument("--emulate-rank", type=int, default=0)
@@ -273,8 +276,20 @@ class RankWorkload:
         self.lse = torch.empty((L, B, HQ), dtype=torch.float32, device=dev)
         self.status = torch.zeros(4, dtype=torch.int32, device=dev)
         self.world = int(os.environ.get("WORLD_SIZE", "1")) if spec.gather else 1
+        self.peer = None
         if spec.gather and self.world > 1:
+            import torch.distributed as dist
+
             self.out_all = torch.empty((self.world, L, B, HQ, D), dtype=torch.bfloat16, device=dev)
+            if args.gather == "peer":
+                self.out_bytes = self.out.numel() * 2
+                self.peer = kv.PeerBuffer(self.out_bytes, self.world, int(os.environ.get("RANK", "0")))
+                mine = torch.tensor(list(self.peer.export), dtype=torch.uint8, device=dev)
+                everyone = torch.empty(self.world * 64, dtype=torch.uint8, device=dev)
+                dist.all_gather_into_tensor(everyone, mine)
+                self.peer.connect(bytes(everyone.cpu().tolist()))
+                dist.barrier()
+                self.gather_checked = False
 
         # per-step metadata, resident: position of the appended token and length after the append
         steps = np.arange(total_steps, dtype=np.int64)[:, None]
@@ -336,6 +351,8 @@ class RankWorkload:
                 self.launches_per_step += 2          # balanced kernel with the append inside, combine
             else:
                 self.launches_per_step += 2 if (nsplit == 1 and split > 0) else 3   # append, split[, combine]
+        if self.peer is not None:
+            self.launches_per_step += 1              # the peer-memory all-gather kernel
 
     def layer_is_global(self, i: int) -> bool:
         nl, ng = self.spec.n_local, self.spec.n_global
@@ -404,14 +421,31 @@ class RankWorkload:
             if self.spec.gather and self.world > 1:
                 import torch.distributed as dist
 
-                dist.all_gather_into_tensor(self.out_all, self.out)
+                if self.peer is not None:
+                    self.gathered_ptr = self.peer.allgather(self.out, self.out_bytes, status=self.status,
+                                                            stream=self.stream)
+                else:
+                    dist.all_gather_into_tensor(self.out_all, self.out)
             return
         self._launch_step(self.pos_all[s].data_ptr(), self.len_all[s].data_ptr(), s if events else None, self.stream)
         if self.spec.gather and self.world > 1:
             # KV-head sharding: every rank holds all heads' outputs after the step
             import torch.distributed as dist
 
-            dist.all_gather_into_tensor(self.out_all, self.out)
+            if self.peer is None:
+                dist.all_gather_into_tensor(self.out_all, self.out)
+                return
+            self.gathered_ptr = self.peer.allgather(self.out, self.out_bytes, status=self.status, stream=self.stream)
+            if not self.gather_checked:          # once, in the warm-up: the same rows as NCCL's all-gather
+                self.gather_checked = True
+                dist.all_gather_into_tensor(self.out_all, self.out)
+                got = self.torch.empty_like(self.out_all)
+                cudart = ctypes.CDLL("libcudart.so.12")
+                cudart.cudaMemcpy.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int]
+                self.torch.cuda.synchronize()
+                rc = cudart.cudaMemcpy(got.data_ptr(), self.gathered_ptr, got.numel() * 2, 3)
+                assert rc == 0 and self.torch.equal(got.view(self.torch.int16), self.out_all.view(self.torch.int16)), \
+                    "peer all-gather differs from ncclAllGather"
 
     def _launch_step(self, pos: int, length: int, s, stream: int):
         kv = self.kv
@@ -633,7 +667,9 @@ def plan_workload(args, world: int, rank: int):
             raise SystemExit("cfg4 shards 8 KV heads: --gpus must divide 8")
         ctx_all = np.array([131072], dtype=np.int64)
         return (Spec(name, WORKLOADS[name], 0, 1, hkv=8 // world, outliers=True, gather=True), ctx_all, ctx_all,
-                f"KV-head-sharded x{world} ({8 // world} KV heads per rank), NCCL all-gather of head outputs",
+                f"KV-head-sharded x{world} ({8 // world} KV heads per rank), all-gather of head outputs: "
+                + ("one peer-store kernel per rank over NVLink (b200kv_peer_allgather)" if args.gather == "peer"
+                   else "ncclAllGather"),
                 "strong")
     if world > 1:
         raise SystemExit(f"{name} is a batch-1 latency case: run it on one GPU")

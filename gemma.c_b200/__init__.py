@@ -197,6 +197,10 @@ _SIGNATURES = {
     "b200kv_decode_ingress_bf16": (c_int, [POINTER(IngressArgs), _P]),
     "b200kv_decode_egress_bf16": (c_int, [POINTER(EgressArgs), _P]),
     "b200kv_decode_attention_layer_bf16": (c_int, [POINTER(AttentionLayerArgs), _P]),
+    "b200kv_peer_buffer_create": (c_int, [c_int64, c_int32, c_int32, POINTER(_P), _P]),
+    "b200kv_peer_buffer_connect": (c_int, [_P, _P]),
+    "b200kv_peer_allgather": (c_int, [_P, _P, c_int64, _P, _P, POINTER(_P)]),
+    "b200kv_peer_buffer_destroy": (c_int, [_P]),
     "b200kv_timer_create": (c_int, [POINTER(_P)]),
     "b200kv_timer_destroy": (c_int, [_P]),
     "b200kv_timer_record": (c_int, [_P, _P]),
@@ -523,6 +527,36 @@ def decode_egress(args: EgressArgs, stream=None, check: bool = True) -> int:
 def decode_attention_layer(args: AttentionLayerArgs, stream=None, check: bool = True) -> int:
     code = load_library().b200kv_decode_attention_layer_bf16(ctypes.byref(args), _stream(stream))
     return _check(code, "b200kv_decode_attention_layer_bf16", check)
+
+
+class PeerBuffer:
+    """This rank's side of the peer-memory all-gather (b200kv_peer_*): `export` is the 64 bytes the other
+    ranks need; connect() takes all ranks' exports in rank order (bytes of length 64 * world)."""
+
+    def __init__(self, slot_bytes: int, world: int, rank: int):
+        self.world, self.rank, self.slot_bytes = world, rank, slot_bytes
+        self._handle = c_void_p()
+        buf = ctypes.create_string_buffer(64)
+        _check(load_library().b200kv_peer_buffer_create(slot_bytes, world, rank, ctypes.byref(self._handle), buf),
+               "b200kv_peer_buffer_create", True)
+        self.export = bytes(buf.raw)
+
+    def connect(self, exports: bytes):
+        assert len(exports) == 64 * self.world
+        _check(load_library().b200kv_peer_buffer_connect(self._handle, exports), "b200kv_peer_buffer_connect", True)
+
+    def allgather(self, src, nbytes: int, status=None, stream=None, check: bool = True) -> int:
+        """Enqueue the gather; returns the device address of the [world][slot_bytes] result."""
+        out = c_void_p()
+        code = load_library().b200kv_peer_allgather(self._handle, _ptr(src), nbytes, _ptr(status), _stream(stream),
+                                                    ctypes.byref(out))
+        _check(code, "b200kv_peer_allgather", check)
+        return out.value or 0
+
+    def close(self):
+        if self._handle:
+            load_library().b200kv_peer_buffer_destroy(self._handle)
+            self._handle = c_void_p()
 
 
 class Timer:

@@ -1143,6 +1143,27 @@ int b200kv_decode_attention_layer_bf16(const B200KvAttentionLayerArgs *s,
   return b200kv_decode_egress_bf16(&out, stream);
 }
 
+int b200kv_peer_buffer_create(int64_t slot_bytes, int32_t world, int32_t rank,
+                              void **handle, void *export_64_bytes) {
+  return b200kv::peer_buffer_create(slot_bytes, world, rank, handle,
+                                    export_64_bytes);
+}
+
+int b200kv_peer_buffer_connect(void *handle, const void *exports) {
+  return b200kv::peer_buffer_connect(handle, exports);
+}
+
+int b200kv_peer_allgather(void *handle, const void *src, int64_t bytes,
+                          int32_t *status, b200kv_stream stream,
+                          void **gathered) {
+  return b200kv::peer_allgather(handle, src, bytes, status,
+                                static_cast<cudaStream_t>(stream), gathered);
+}
+
+int b200kv_peer_buffer_destroy(void *handle) {
+  return b200kv::peer_buffer_destroy(handle);
+}
+
 int b200kv_timer_create(void **event) {
   if (event == nullptr) return cudaErrorInvalidValue;
   cudaEvent_t ev = nullptr;

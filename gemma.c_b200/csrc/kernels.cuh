@@ -137,6 +137,20 @@ struct EgressArgs {
 };
 cudaError_t decode_egress_bf16(const EgressArgs &args, cudaStream_t stream);
 
+// All-gather of per-rank rows over peer memory (peer_gather.cu), one process
+// per GPU. create: allocates this rank's buffer ([2][world][slot_bytes] + flags)
+// and fills a 64-byte export for the other ranks; connect: maps the other
+// ranks' buffers from their exports ([world][64] bytes, own entry ignored);
+// allgather: one kernel on `stream`, *gathered = this rank's [world][slot_bytes]
+// view that holds the result once the kernel has run.
+cudaError_t peer_buffer_create(int64_t slot_bytes, int world, int rank,
+                               void **handle, void *export_64_bytes);
+cudaError_t peer_buffer_connect(void *handle, const void *exports);
+cudaError_t peer_allgather(void *handle, const void *src, int64_t bytes,
+                           int32_t *status, cudaStream_t stream,
+                           void **gathered);
+cudaError_t peer_buffer_destroy(void *handle);
+
 struct PrefillPrepArgs {
   __nv_bfloat16 *q_prepared = nullptr;
   __nv_bfloat16 *k_prepared = nullptr;

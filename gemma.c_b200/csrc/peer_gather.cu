@@ -1,0 +1,202 @@
+// All-gather of the per-rank attention rows over NVLink peer memory, for the
+// KV-head-sharded mode (one process per GPU, each rank attends its own KV
+// heads, every rank needs all heads' rows for the O projection). The payload
+// is a few KiB, so the cost of a library collective is its launch and protocol
+// latency; here one small kernel per rank does the whole exchange:
+//
+//   1. stores this rank's rows into slot `rank` of every peer's gathered
+//      buffer (plain peer stores through the NVLink mapping; no multicast),
+//   2. fence.sys, then writes the call's epoch into flag `rank` on every peer,
+//   3. waits (bounded) until its own flags show the epoch from every rank.
+//
+// When the kernel ends, the gathered buffer on this GPU holds every rank's
+// rows and later work on the stream may read it. Buffers are double-buffered
+// by epoch parity: a rank can be at most one call ahead of a peer (it needs the
+// peer's flag of call e + 1 to get past call e + 1), so half (e & 1) is never
+// overwritten while a peer still reads call e.
+//
+// No counterpart in the reference (single GPU). Every wait is bounded; a rank
+// whose peers do not show up within about a second records
+// B200KV_STATUS_WAIT_TIMEOUT and returns.
+#include <cstring>
+#include <new>
+#include <vector>
+
+#include "common.cuh"
+#include "kernels.cuh"
+
+namespace b200kv {
+namespace {
+
+constexpr int kMaxPeers = 8;
+constexpr int kGatherThreads = 256;
+
+struct PeerGatherParams {
+  const uint4 *src;
+  int64_t packs;               // 16-byte packs this rank contributes
+  int64_t slot_packs;          // capacity of one slot, in packs
+  uint4 *data[kMaxPeers];      // peer r's gathered buffer [2][world][slot_packs]
+  uint32_t *flags[kMaxPeers];  // peer r's flags [2][world]
+  uint32_t *epoch;             // this rank's call counter (device)
+  int32_t rank;
+  int32_t world;
+  int32_t *status;
+};
+
+__device__ __forceinline__ void store_release_sys(uint32_t *addr, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ uint32_t load_acquire_sys(const uint32_t *addr) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+
+__global__ void __launch_bounds__(kGatherThreads) peer_allgather_kernel(
+    const PeerGatherParams p) {
+  __shared__ uint32_t s_epoch;
+  pdl_wait_for_predecessor();  // the rows come from the preceding kernel
+  pdl_release_successor();
+  if (threadIdx.x == 0) s_epoch = *p.epoch + 1u;
+  __syncthreads();
+  const uint32_t e = s_epoch;
+  const int64_t half = int64_t(e & 1u) * p.world;
+  // 1. this rank's rows into its slot on every rank (its own included)
+  for (int r = 0; r < p.world; ++r) {
+    uint4 *dst = p.data[r] + (half + p.rank) * p.slot_packs;
+    for (int64_t i = threadIdx.x; i < p.packs; i += kGatherThreads) {
+      dst[i] = p.src[i];
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  // 2. + 3. one thread per peer: announce, then wait for that peer
+  if (threadIdx.x < p.world) {
+    const int r = int(threadIdx.x);
+    store_release_sys(p.flags[r] + half + p.rank, e);
+    const uint32_t *mine = p.flags[p.rank] + half + r;
+    const long long start = clock64();
+    while (int32_t(load_acquire_sys(mine) - e) < 0) {
+      if (clock64() - start > kWaitClockLimit) {
+        set_status(p.status, B200KV_STATUS_WAIT_TIMEOUT);
+        break;
+      }
+      __nanosleep(100);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) *p.epoch = e;
+}
+
+struct PeerBuffer {
+  int world = 0;
+  int rank = 0;
+  int64_t slot_bytes = 0;
+  unsigned char *base = nullptr;          // own allocation
+  unsigned char *peer[kMaxPeers] = {};    // mapped bases (peer[rank] == base)
+  bool connected = false;
+  uint32_t calls = 0;                     // host mirror of the device epoch
+};
+
+int64_t data_bytes(const PeerBuffer &b) { return 2 * int64_t(b.world) * b.slot_bytes; }
+int64_t flag_offset(const PeerBuffer &b) { return (data_bytes(b) + 255) / 256 * 256; }
+int64_t total_bytes(const PeerBuffer &b) { return flag_offset(b) + 256; }
+
+}  // namespace
+
+cudaError_t peer_buffer_create(int64_t slot_bytes, int world, int rank,
+                               void **handle, void *export_64_bytes) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "export size");
+  if (handle == nullptr || export_64_bytes == nullptr || world < 1 ||
+      world > kMaxPeers || rank < 0 || rank >= world || slot_bytes <= 0 ||
+      slot_bytes % 16 != 0) {
+    return cudaErrorInvalidValue;
+  }
+  PeerBuffer *b = new (std::nothrow) PeerBuffer;
+  if (b == nullptr) return cudaErrorMemoryAllocation;
+  b->world = world;
+  b->rank = rank;
+  b->slot_bytes = slot_bytes;
+  cudaError_t st = cudaMalloc(&b->base, size_t(total_bytes(*b)));
+  if (st == cudaSuccess) st = cudaMemset(b->base, 0, size_t(total_bytes(*b)));
+  if (st == cudaSuccess) st = cudaDeviceSynchronize();
+  cudaIpcMemHandle_t h;
+  if (st == cudaSuccess) st = cudaIpcGetMemHandle(&h, b->base);
+  if (st != cudaSuccess) {
+    if (b->base != nullptr) cudaFree(b->base);
+    delete b;
+    return st;
+  }
+  std::memcpy(export_64_bytes, &h, sizeof(h));
+  b->peer[rank] = b->base;
+  if (world == 1) b->connected = true;
+  *handle = b;
+  return cudaSuccess;
+}
+
+cudaError_t peer_buffer_connect(void *handle, const void *exports) {
+  PeerBuffer *b = static_cast<PeerBuffer *>(handle);
+  if (b == nullptr || exports == nullptr) return cudaErrorInvalidValue;
+  for (int r = 0; r < b->world; ++r) {
+    if (r == b->rank || b->peer[r] != nullptr) continue;
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, static_cast<const unsigned char *>(exports) + 64 * r, sizeof(h));
+    void *mapped = nullptr;
+    const cudaError_t st =
+        cudaIpcOpenMemHandle(&mapped, h, cudaIpcMemLazyEnablePeerAccess);
+    if (st != cudaSuccess) return st;
+    b->peer[r] = static_cast<unsigned char *>(mapped);
+  }
+  b->connected = true;
+  return cudaSuccess;
+}
+
+cudaError_t peer_allgather(void *handle, const void *src, int64_t bytes,
+                           int32_t *status, cudaStream_t stream,
+                           void **gathered) {
+  PeerBuffer *b = static_cast<PeerBuffer *>(handle);
+  if (b == nullptr || !b->connected || src == nullptr || bytes <= 0 ||
+      bytes % 16 != 0 || bytes > b->slot_bytes ||
+      (reinterpret_cast<uintptr_t>(src) & 15u) != 0) {
+    return cudaErrorInvalidValue;
+  }
+  PeerGatherParams p = {};
+  p.src = static_cast<const uint4 *>(src);
+  p.packs = bytes / 16;
+  p.slot_packs = b->slot_bytes / 16;
+  for (int r = 0; r < b->world; ++r) {
+    p.data[r] = reinterpret_cast<uint4 *>(b->peer[r]);
+    p.flags[r] = reinterpret_cast<uint32_t *>(b->peer[r] + flag_offset(*b));
+  }
+  p.epoch = reinterpret_cast<uint32_t *>(b->base + flag_offset(*b)) + 2 * kMaxPeers;
+  p.rank = b->rank;
+  p.world = b->world;
+  p.status = status;
+  const cudaError_t st = launch_pdl(peer_allgather_kernel, dim3(1),
+                                    dim3(kGatherThreads), 0, stream, p);
+  if (st != cudaSuccess) return st;
+  b->calls += 1;
+  if (gathered != nullptr) {
+    *gathered = b->base + int64_t(b->calls & 1u) * b->world * b->slot_bytes;
+  }
+  return cudaSuccess;
+}
+
+cudaError_t peer_buffer_destroy(void *handle) {
+  PeerBuffer *b = static_cast<PeerBuffer *>(handle);
+  if (b == nullptr) return cudaSuccess;
+  cudaError_t first = cudaSuccess;
+  for (int r = 0; r < b->world; ++r) {
+    if (r != b->rank && b->peer[r] != nullptr) {
+      const cudaError_t st = cudaIpcCloseMemHandle(b->peer[r]);
+      if (first == cudaSuccess) first = st;
+    }
+  }
+  const cudaError_t st = cudaFree(b->base);
+  if (first == cudaSuccess) first = st;
+  delete b;
+  return first;
+}
+
+}  // namespace b200kv

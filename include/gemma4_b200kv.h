@@ -593,6 +593,37 @@ typedef struct B200KvAttentionLayerArgs {
 int b200kv_decode_attention_layer_bf16(const B200KvAttentionLayerArgs *args,
                                        b200kv_stream stream);
 
+/* ------------------------------------------------------------------ *
+ * KV-head-sharded mode, one process per GPU: all-gather of the per-rank
+ * attention rows over NVLink peer memory in one small kernel per rank (peer
+ * stores + flags; no multicast, no library collective). No counterpart in the
+ * reference, which is single-GPU; it takes the place of an ncclAllGather of a
+ * few KiB, whose cost is launch and protocol latency.
+ *
+ * b200kv_peer_buffer_create allocates this rank's buffer (cudaMalloc:
+ * 2 x world x slot_bytes + flags, zeroed) and writes a 64-byte export
+ * (a cudaIpcMemHandle_t) that the caller passes to the other ranks by any
+ * means (e.g. an all-gather of 64 bytes over its process group).
+ * b200kv_peer_buffer_connect maps the other ranks' buffers from
+ * `exports` = world x 64 bytes in rank order. All ranks must have connected
+ * (a host barrier) before the first gather.
+ * b200kv_peer_allgather enqueues the kernel on `stream`: `bytes` (multiple of
+ * 16, <= slot_bytes) from `src` land in slot `rank` of every rank's buffer;
+ * when the kernel has run, `*gathered` (device pointer, [world][slot_bytes],
+ * valid until the call after next) holds every rank's rows. Every rank calls it
+ * the same number of times. Waits are bounded (about a second): a rank whose
+ * peers do not arrive writes B200KV_STATUS_WAIT_TIMEOUT to status[0]
+ * (optional) and returns. Not for CUDA-graph replay: the host counts the calls
+ * to pick the buffer half. world <= 8.
+ * ------------------------------------------------------------------ */
+int b200kv_peer_buffer_create(int64_t slot_bytes, int32_t world, int32_t rank,
+                              void **handle, void *export_64_bytes);
+int b200kv_peer_buffer_connect(void *handle, const void *exports);
+int b200kv_peer_allgather(void *handle, const void *src, int64_t bytes,
+                          int32_t *status, b200kv_stream stream,
+                          void **gathered);
+int b200kv_peer_buffer_destroy(void *handle);
+
 /* Timing events for the hooks above (cudaEventCreate / Destroy / ElapsedTime).
  * No counterpart in the reference library; its benches time with the same
  * CUDA events, src/benches/gemma4_bench_utils.cuh:336-370. */
