@@ -65,6 +65,10 @@ def parse_args():
                     help="replay each step from a CUDA graph captured once (auto: on for the batch-1 latency "
                          "workloads cfg1/cfg2, where the host cannot issue 3 launches per layer fast enough)")
     ap.add_argument("--layers", type=int, default=48, help="--workload layer: layers in the stack")
+    ap.add_argument("--shard", default="heads", choices=["heads", "keys"],
+                    help="cfg4 on more than one GPU: every rank holds all KV heads of a contiguous range of the keys "
+                         "and the ranks' rows are merged by log-sum-exp (keys), or every rank holds some KV heads "
+                         "of all keys and the rows are all-gathered (heads)")
     ap.add_argument("--gather", default="peer", choices=["peer", "nccl"],
                     help="cfg4 on more than one GPU: all-gather of the head outputs by the library's peer-memory "
                          "kernel (b200kv_peer_allgather) or by ncclAllGather")
@@ -185,8 +189,9 @@ class Spec:
     """Which layers one step runs and on what geometry."""
 
     def __init__(self, name, text, n_local, n_global, hkv=8, fp8=False, tight_ring=False, outliers=False,
-                 gather=False):
+                 gather=False, key_shard=None):
         self.name, self.text = name, text
+        self.key_shard = key_shard                  # (rank, ranks): this rank holds one range of the keys
         self.n_local, self.n_global = n_local, n_global
         self.hkv, self.hq = hkv, 2 * hkv           # KV / query heads held by this rank
         self.fp8, self.tight_ring, self.outliers, self.gather = fp8, tight_ring, outliers, gather
@@ -215,6 +220,16 @@ class RankWorkload:
             return t
 
         max_pos = int(ctx.max()) + total_steps + 1
+        # Key-range sharding: a rank's keys sit at local positions 0 .. C-1 of its own cache; the new token has
+        # local position C + s on every rank and absolute position shift + C + s, so the RoPE tables are
+        # entered `shift` rows further down. Only the last rank has pages for the new rows: on the others the
+        # position is unmapped, nothing is appended, and q is still prepared at the absolute position.
+        self.rope_shift, self.owns_new_rows = 0, True
+        if spec.key_shard:
+            me, shards = spec.key_shard
+            self.rope_shift = (shards - 1) * int(ctx[0])
+            self.owns_new_rows = me == shards - 1
+            max_pos += self.rope_shift
         self.g_cfg = self.l_cfg = None
         if ng:
             # global layers: linear cache, one pool, permuted block table
@@ -228,6 +243,8 @@ class RankWorkload:
                 table[b, :pages_b[b]] = pool[cur:cur + pages_b[b]]
                 cur += int(pages_b[b])
             self.g_cfg = kv.make_kv_config(ng, self.g_pages, PAGE, self.g_mpps, B, HKV, D, 0)
+            if not self.owns_new_rows:
+                table[:, (int(ctx[0]) + PAGE - 1) // PAGE:] = -1
             self.g_table = torch.from_numpy(table).to(dev)
             gc, gs = kv.fill_rope_tables(max_pos, D // 2, 1000000.0, D)
             self.g_cos, self.g_sin = torch.from_numpy(gc).to(dev), torch.from_numpy(gs).to(dev)
@@ -281,9 +298,13 @@ class RankWorkload:
             import torch.distributed as dist
 
             self.out_all = torch.empty((self.world, L, B, HQ, D), dtype=torch.bfloat16, device=dev)
+            self.gather_checked = True          # nothing to check against on the nccl arm
             if args.gather == "peer":
                 self.out_bytes = self.out.numel() * 2
-                self.peer = kv.PeerBuffer(self.out_bytes, self.world, int(os.environ.get("RANK", "0")))
+                slot = self.out_bytes               # the gathered view is then exactly [world][rows][D]
+                if spec.key_shard:
+                    slot = (self.out_bytes + self.lse.numel() * 4 + 15) // 16 * 16
+                self.peer = kv.PeerBuffer(slot, self.world, int(os.environ.get("RANK", "0")))
                 mine = torch.tensor(list(self.peer.export), dtype=torch.uint8, device=dev)
                 everyone = torch.empty(self.world * 64, dtype=torch.uint8, device=dev)
                 dist.all_gather_into_tensor(everyone, mine)
@@ -294,7 +315,8 @@ class RankWorkload:
         # per-step metadata, resident: position of the appended token and length after the append
         steps = np.arange(total_steps, dtype=np.int64)[:, None]
         self.pos_all = torch.from_numpy((ctx[None, :] + steps).astype(np.int32)).to(dev)
-        self.len_all = torch.from_numpy((ctx[None, :] + steps + 1).astype(np.int32)).to(dev)
+        lengths = ctx[None, :] + steps + 1 if self.owns_new_rows else ctx[None, :] + 0 * steps
+        self.len_all = torch.from_numpy(lengths.astype(np.int32)).to(dev)
 
         balanced_ok = HKV == 8 and B <= 1024
         self.g_split, self.g_nsplit = kv.plan_splits_total(B, int(ctx.max()) + total_steps,
@@ -335,8 +357,9 @@ class RankWorkload:
             a.softmax_scale = 1.0 / math.sqrt(D)
             a.raw_q, a.raw_k, a.raw_v = self.raw_q[i].data_ptr(), self.raw_k[i].data_ptr(), self.raw_v[i].data_ptr()
             a.q_norm_weight, a.k_norm_weight = self.q_w.data_ptr(), self.k_w.data_ptr()
-            a.cos = (self.g_cos if is_global else self.l_cos).data_ptr()
-            a.sin = (self.g_sin if is_global else self.l_sin).data_ptr()
+            rope_offset = self.rope_shift * (D // 2) * 4 if is_global else 0
+            a.cos = (self.g_cos if is_global else self.l_cos).data_ptr() + rope_offset
+            a.sin = (self.g_sin if is_global else self.l_sin).data_ptr() + rope_offset
             a.batch_count, a.q_heads, a.rotary_dim, a.norm_mode = B, HQ, D, kv.NORM_RSQRT_APPROX
             a.status = self.status.data_ptr()
         self.timed_layer = max((i for i in range(L) if self.layer_is_global(i)), default=L - 1)
@@ -418,34 +441,56 @@ class RankWorkload:
             assert s == self.graph_next, "graph replay walks consecutive steps"
             self.graph.replay()
             self.graph_next += 1
-            if self.spec.gather and self.world > 1:
-                import torch.distributed as dist
-
-                if self.peer is not None:
-                    self.gathered_ptr = self.peer.allgather(self.out, self.out_bytes, status=self.status,
-                                                            stream=self.stream)
-                else:
-                    dist.all_gather_into_tensor(self.out_all, self.out)
+            self._exchange()
             return
         self._launch_step(self.pos_all[s].data_ptr(), self.len_all[s].data_ptr(), s if events else None, self.stream)
-        if self.spec.gather and self.world > 1:
-            # KV-head sharding: every rank holds all heads' outputs after the step
-            import torch.distributed as dist
+        self._exchange()
 
-            if self.peer is None:
-                dist.all_gather_into_tensor(self.out_all, self.out)
-                return
-            self.gathered_ptr = self.peer.allgather(self.out, self.out_bytes, status=self.status, stream=self.stream)
-            if not self.gather_checked:          # once, in the warm-up: the same rows as NCCL's all-gather
+    def _exchange(self):
+        """The step's exchange between the ranks (cfg4 on more than one GPU). KV-head sharding: all-gather of the
+        head outputs, after which every rank holds all heads' rows. Key-range sharding: every rank's rows and
+        log-sum-exp are exchanged and merged, after which `out` / `lse` hold the full attention on every rank."""
+        if not (self.spec.gather and self.world > 1):
+            return
+        import torch.distributed as dist
+
+        torch = self.torch
+        rows = self.out.numel() // D
+        if self.spec.key_shard:
+            if self.peer is None or not self.gather_checked:
+                # ncclAllGather of rows and log-sum-exp, merge with torch ops (the --gather nccl arm, and once in
+                # the warm-up the check of the peer kernel's merge)
+                all_out = torch.empty((self.world, rows, D), dtype=torch.bfloat16, device=self.out.device)
+                all_lse = torch.empty((self.world, rows), dtype=torch.float32, device=self.out.device)
+                dist.all_gather_into_tensor(all_out, self.out.view(rows, D))
+                dist.all_gather_into_tensor(all_lse, self.lse.view(rows))
+                weight = torch.softmax(all_lse, dim=0)
+                merged = (weight[:, :, None] * all_out.float()).sum(0)
+                if self.peer is None:
+                    self.out.view(rows, D).copy_(merged)
+                    self.lse.view(rows).copy_(torch.logsumexp(all_lse, dim=0))
+                    return
+            self.peer.merge_attention(self.out, self.lse, self.out, self.lse, rows, D, status=self.status,
+                                      stream=self.stream)
+            if not self.gather_checked:
                 self.gather_checked = True
-                dist.all_gather_into_tensor(self.out_all, self.out)
-                got = self.torch.empty_like(self.out_all)
-                cudart = ctypes.CDLL("libcudart.so.12")
-                cudart.cudaMemcpy.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int]
-                self.torch.cuda.synchronize()
-                rc = cudart.cudaMemcpy(got.data_ptr(), self.gathered_ptr, got.numel() * 2, 3)
-                assert rc == 0 and self.torch.equal(got.view(self.torch.int16), self.out_all.view(self.torch.int16)), \
-                    "peer all-gather differs from ncclAllGather"
+                err = (self.out.view(rows, D).float() - merged).abs().max().item()
+                assert err <= 2.0 ** -7 * max(1.0, merged.abs().max().item()), f"peer merge differs: {err}"
+            return
+        if self.peer is None:
+            dist.all_gather_into_tensor(self.out_all, self.out)
+            return
+        self.gathered_ptr = self.peer.allgather(self.out, self.out_bytes, status=self.status, stream=self.stream)
+        if not self.gather_checked:          # once, in the warm-up: the same rows as NCCL's all-gather
+            self.gather_checked = True
+            dist.all_gather_into_tensor(self.out_all, self.out)
+            got = torch.empty_like(self.out_all)
+            cudart = ctypes.CDLL("libcudart.so.12")
+            cudart.cudaMemcpy.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int]
+            torch.cuda.synchronize()
+            rc = cudart.cudaMemcpy(got.data_ptr(), self.gathered_ptr, got.numel() * 2, 3)
+            assert rc == 0 and torch.equal(got.view(torch.int16), self.out_all.view(torch.int16)), \
+                "peer all-gather differs from ncclAllGather"
 
     def _launch_step(self, pos: int, length: int, s, stream: int):
         kv = self.kv
@@ -486,7 +531,7 @@ class RankWorkload:
 
     def bytes_for_step(self, s: int) -> tuple[int, int]:
         sp = self.spec
-        after = self.ctx + s + 1
+        after = self.ctx + s + 1 if self.owns_new_rows else self.ctx
         total = (sp.n_local * layer_step_bytes(after, WINDOW, sp.hkv, sp.e_kv)
                  + sp.n_global * layer_step_bytes(after, 0, sp.hkv, sp.e_kv))
         timed_window = 0 if sp.n_global else WINDOW
@@ -666,7 +711,18 @@ def plan_workload(args, world: int, rank: int):
         if 8 % world:
             raise SystemExit("cfg4 shards 8 KV heads: --gpus must divide 8")
         ctx_all = np.array([131072], dtype=np.int64)
-        return (Spec(name, WORKLOADS[name], 0, 1, hkv=8 // world, outliers=True, gather=True), ctx_all, ctx_all,
+        shards = args.emulate_world if (world == 1 and args.emulate_world > 1) else world   # tuning aid: one rank's share
+        if args.shard == "keys" and shards > 1:
+            if 131072 % (shards * PAGE):
+                raise SystemExit("cfg4 --shard keys: the ranks must divide 131072 / 16 pages")
+            me = rank if world > 1 else args.emulate_rank
+            mine = np.array([131072 // shards], dtype=np.int64)
+            return (Spec(name, WORKLOADS[name], 0, 1, outliers=True, gather=world > 1, key_shard=(me, shards)),
+                    ctx_all, mine,
+                    f"key-range-sharded x{shards} (all 8 KV heads of {131072 // shards} keys per rank), rows merged by "
+                    "log-sum-exp" + (" in one peer-store kernel per rank over NVLink (b200kv_peer_merge_attention)"
+                                     if args.gather == "peer" else " after two ncclAllGather calls"), "strong")
+        return (Spec(name, WORKLOADS[name], 0, 1, hkv=8 // shards, outliers=True, gather=True), ctx_all, ctx_all,
                 f"KV-head-sharded x{world} ({8 // world} KV heads per rank), all-gather of head outputs: "
                 + ("one peer-store kernel per rank over NVLink (b200kv_peer_allgather)" if args.gather == "peer"
                    else "ncclAllGather"),

@@ -200,6 +200,7 @@ _SIGNATURES = {
     "b200kv_peer_buffer_create": (c_int, [c_int64, c_int32, c_int32, POINTER(_P), _P]),
     "b200kv_peer_buffer_connect": (c_int, [_P, _P]),
     "b200kv_peer_allgather": (c_int, [_P, _P, c_int64, _P, _P, POINTER(_P)]),
+    "b200kv_peer_merge_attention": (c_int, [_P, _P, _P, _P, _P, c_int32, c_int32, _P, _P]),
     "b200kv_peer_buffer_destroy": (c_int, [_P]),
     "b200kv_timer_create": (c_int, [POINTER(_P)]),
     "b200kv_timer_destroy": (c_int, [_P]),
@@ -552,6 +553,12 @@ class PeerBuffer:
                                                     ctypes.byref(out))
         _check(code, "b200kv_peer_allgather", check)
         return out.value or 0
+
+    def merge_attention(self, merged_out, merged_lse, out, lse, rows: int, head_dim: int, status=None, stream=None,
+                        check: bool = True) -> int:
+        code = load_library().b200kv_peer_merge_attention(self._handle, _ptr(merged_out), _ptr(merged_lse), _ptr(out),
+                                                          _ptr(lse), rows, head_dim, _ptr(status), _stream(stream))
+        return _check(code, "b200kv_peer_merge_attention", check)
 
     def close(self):
         if self._handle:

@@ -1160,6 +1160,17 @@ int b200kv_peer_allgather(void *handle, const void *src, int64_t bytes,
                                 static_cast<cudaStream_t>(stream), gathered);
 }
 
+int b200kv_peer_merge_attention(void *handle, b200kv_bf16 *merged_out,
+                                float *merged_lse, const b200kv_bf16 *out,
+                                const float *lse, int32_t rows, int32_t head_dim,
+                                int32_t *status, b200kv_stream stream) {
+  using bf = __nv_bfloat16;
+  return b200kv::peer_merge_attention(
+      handle, reinterpret_cast<bf *>(merged_out), merged_lse,
+      reinterpret_cast<const bf *>(out), lse, rows, head_dim, status,
+      static_cast<cudaStream_t>(stream));
+}
+
 int b200kv_peer_buffer_destroy(void *handle) {
   return b200kv::peer_buffer_destroy(handle);
 }

@@ -149,6 +149,14 @@ cudaError_t peer_buffer_connect(void *handle, const void *exports);
 cudaError_t peer_allgather(void *handle, const void *src, int64_t bytes,
                            int32_t *status, cudaStream_t stream,
                            void **gathered);
+// Key-range sharding: every rank passes its normalised rows `out`
+// [rows][head_dim] bf16 with their log-sum-exp `lse` [rows]; every rank gets
+// the merged rows (merged_out may be `out`) and, optionally, the merged lse.
+// slot_bytes >= rows * (head_dim * 2 + 4); rows <= 64.
+cudaError_t peer_merge_attention(void *handle, __nv_bfloat16 *merged_out,
+                                 float *merged_lse, const __nv_bfloat16 *out,
+                                 const float *lse, int32_t rows, int32_t head_dim,
+                                 int32_t *status, cudaStream_t stream);
 cudaError_t peer_buffer_destroy(void *handle);
 
 struct PrefillPrepArgs {

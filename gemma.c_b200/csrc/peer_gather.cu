@@ -15,6 +15,12 @@
 // peer's flag of call e + 1 to get past call e + 1), so half (e & 1) is never
 // overwritten while a peer still reads call e.
 //
+// The same kernel can finish a key-range-sharded attention (every rank holds
+// all heads but only a range of the keys): each rank contributes its
+// normalised rows and their log-sum-exp, and after the wait every rank merges
+// them, out = sum_r exp(lse_r - LSE) out_r with LSE = log sum_r exp(lse_r) --
+// the combine of src/gemma4_flash_attention_decode.cu:881-977 one level up.
+//
 // No counterpart in the reference (single GPU). Every wait is bounded; a rank
 // whose peers do not show up within about a second records
 // B200KV_STATUS_WAIT_TIMEOUT and returns.
@@ -30,6 +36,7 @@ namespace {
 
 constexpr int kMaxPeers = 8;
 constexpr int kGatherThreads = 256;
+constexpr int kMaxMergeRows = 64;
 
 struct PeerGatherParams {
   const uint4 *src;
@@ -41,6 +48,15 @@ struct PeerGatherParams {
   int32_t rank;
   int32_t world;
   int32_t *status;
+  // optional second segment of 4-byte words, stored behind the packs
+  const uint32_t *src_words;
+  int32_t words;
+  // optional merge (merge_rows > 0): the packs are [merge_rows][merge_dim] bf16
+  // rows, the words their fp32 log-sum-exp
+  int32_t merge_rows;
+  int32_t merge_dim;
+  __nv_bfloat16 *merged_out;
+  float *merged_lse;
 };
 
 __device__ __forceinline__ void store_release_sys(uint32_t *addr, uint32_t v) {
@@ -68,6 +84,10 @@ __global__ void __launch_bounds__(kGatherThreads) peer_allgather_kernel(
     for (int64_t i = threadIdx.x; i < p.packs; i += kGatherThreads) {
       dst[i] = p.src[i];
     }
+    uint32_t *dst_words = reinterpret_cast<uint32_t *>(dst + p.packs);
+    for (int i = threadIdx.x; i < p.words; i += kGatherThreads) {
+      dst_words[i] = p.src_words[i];
+    }
   }
   __threadfence_system();
   __syncthreads();
@@ -87,6 +107,52 @@ __global__ void __launch_bounds__(kGatherThreads) peer_allgather_kernel(
   }
   __syncthreads();
   if (threadIdx.x == 0) *p.epoch = e;
+  if (p.merge_rows <= 0) return;
+
+  // Merge of the ranks' partial attention rows. The slots were written by
+  // other GPUs: read them past L1 (a line of the same half may be cached from
+  // two calls ago).
+  __shared__ float s_weight[kMaxMergeRows][kMaxPeers];
+  const uint4 *mine = p.data[p.rank] + half * p.slot_packs;
+  for (int row = threadIdx.x; row < p.merge_rows; row += kGatherThreads) {
+    float lse[kMaxPeers];
+    float top = -INFINITY;
+    for (int r = 0; r < p.world; ++r) {
+      const float *words =
+          reinterpret_cast<const float *>(mine + r * p.slot_packs + p.packs);
+      lse[r] = __ldcg(words + row);
+      top = fmaxf(top, lse[r]);
+    }
+    float sum = 0.0f;
+    for (int r = 0; r < p.world; ++r) {
+      lse[r] = (top == -INFINITY) ? 0.0f : expf(lse[r] - top);
+      sum += lse[r];
+    }
+    for (int r = 0; r < p.world; ++r) {
+      s_weight[row][r] = sum > 0.0f ? lse[r] / sum : 0.0f;
+    }
+    if (p.merged_lse != nullptr) {
+      p.merged_lse[row] = sum > 0.0f ? top + logf(sum) : -INFINITY;
+    }
+  }
+  __syncthreads();
+  const int pairs = p.merge_rows * p.merge_dim / 2;
+  for (int i = threadIdx.x; i < pairs; i += kGatherThreads) {
+    const int row = (2 * i) / p.merge_dim;
+    float lo = 0.0f, hi = 0.0f;
+    for (int r = 0; r < p.world; ++r) {
+      const uint32_t *rows =
+          reinterpret_cast<const uint32_t *>(mine + r * p.slot_packs);
+      const uint32_t v = __ldcg(rows + i);
+      const float w = s_weight[row][r];
+      if (w != 0.0f) {  // a rank without keys may hold anything
+        lo = fmaf(w, bf16_lo(v), lo);
+        hi = fmaf(w, bf16_hi(v), hi);
+      }
+    }
+    const __nv_bfloat162 packed = __floats2bfloat162_rn(lo, hi);
+    reinterpret_cast<__nv_bfloat162 *>(p.merged_out)[i] = packed;
+  }
 }
 
 struct PeerBuffer {
@@ -152,16 +218,11 @@ cudaError_t peer_buffer_connect(void *handle, const void *exports) {
   return cudaSuccess;
 }
 
-cudaError_t peer_allgather(void *handle, const void *src, int64_t bytes,
-                           int32_t *status, cudaStream_t stream,
-                           void **gathered) {
-  PeerBuffer *b = static_cast<PeerBuffer *>(handle);
-  if (b == nullptr || !b->connected || src == nullptr || bytes <= 0 ||
-      bytes % 16 != 0 || bytes > b->slot_bytes ||
-      (reinterpret_cast<uintptr_t>(src) & 15u) != 0) {
-    return cudaErrorInvalidValue;
-  }
-  PeerGatherParams p = {};
+namespace {
+
+cudaError_t launch_gather(PeerBuffer *b, PeerGatherParams p, const void *src,
+                          int64_t bytes, int32_t *status, cudaStream_t stream,
+                          void **gathered) {
   p.src = static_cast<const uint4 *>(src);
   p.packs = bytes / 16;
   p.slot_packs = b->slot_bytes / 16;
@@ -181,6 +242,43 @@ cudaError_t peer_allgather(void *handle, const void *src, int64_t bytes,
     *gathered = b->base + int64_t(b->calls & 1u) * b->world * b->slot_bytes;
   }
   return cudaSuccess;
+}
+
+}  // namespace
+
+cudaError_t peer_allgather(void *handle, const void *src, int64_t bytes,
+                           int32_t *status, cudaStream_t stream,
+                           void **gathered) {
+  PeerBuffer *b = static_cast<PeerBuffer *>(handle);
+  if (b == nullptr || !b->connected || src == nullptr || bytes <= 0 ||
+      bytes % 16 != 0 || bytes > b->slot_bytes ||
+      (reinterpret_cast<uintptr_t>(src) & 15u) != 0) {
+    return cudaErrorInvalidValue;
+  }
+  return launch_gather(b, PeerGatherParams{}, src, bytes, status, stream, gathered);
+}
+
+cudaError_t peer_merge_attention(void *handle, __nv_bfloat16 *merged_out,
+                                 float *merged_lse, const __nv_bfloat16 *out,
+                                 const float *lse, int32_t rows, int32_t head_dim,
+                                 int32_t *status, cudaStream_t stream) {
+  PeerBuffer *b = static_cast<PeerBuffer *>(handle);
+  const int64_t bytes = int64_t(rows) * head_dim * 2;
+  if (b == nullptr || !b->connected || merged_out == nullptr || out == nullptr ||
+      lse == nullptr || rows <= 0 || rows > kMaxMergeRows || head_dim <= 0 ||
+      bytes % 16 != 0 || bytes + int64_t(rows) * 4 > b->slot_bytes ||
+      (reinterpret_cast<uintptr_t>(out) & 15u) != 0 ||
+      (reinterpret_cast<uintptr_t>(merged_out) & 3u) != 0) {
+    return cudaErrorInvalidValue;
+  }
+  PeerGatherParams p = {};
+  p.src_words = reinterpret_cast<const uint32_t *>(lse);
+  p.words = rows;
+  p.merge_rows = rows;
+  p.merge_dim = head_dim;
+  p.merged_out = merged_out;
+  p.merged_lse = merged_lse;
+  return launch_gather(b, p, out, bytes, status, stream, nullptr);
 }
 
 cudaError_t peer_buffer_destroy(void *handle) {

@@ -622,6 +622,19 @@ int b200kv_peer_buffer_connect(void *handle, const void *exports);
 int b200kv_peer_allgather(void *handle, const void *src, int64_t bytes,
                           int32_t *status, b200kv_stream stream,
                           void **gathered);
+/* Key-range sharding (every rank holds all KV heads of a range of the keys and
+ * attends the full query over it): the same kernel exchanges each rank's
+ * normalised rows `out` [rows, head_dim] bf16 with their log-sum-exp `lse`
+ * [rows] fp32 and, after the wait, merges them on every rank,
+ *   merged = sum_r exp(lse_r - LSE) out_r,  LSE = log sum_r exp(lse_r)
+ * (the combine of src/gemma4_flash_attention_decode.cu:881-977 across ranks;
+ * a rank without live keys has lse = -inf and weight 0). `merged_out` may be
+ * `out`; `merged_lse` is optional. rows <= 64,
+ * slot_bytes >= rows * (head_dim * 2 + 4). */
+int b200kv_peer_merge_attention(void *handle, b200kv_bf16 *merged_out,
+                                float *merged_lse, const b200kv_bf16 *out,
+                                const float *lse, int32_t rows, int32_t head_dim,
+                                int32_t *status, b200kv_stream stream);
 int b200kv_peer_buffer_destroy(void *handle);
 
 /* Timing events for the hooks above (cudaEventCreate / Destroy / ElapsedTime).

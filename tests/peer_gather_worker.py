@@ -47,7 +47,35 @@ def main():
     got = read_device(ptrs[-1], world * slot // 4, np.int32).reshape(world, slot // 4)[:, :256]
     assert status[0].item() == 0
     assert all((got[r] == 100 * 39 + r).all() for r in range(world))
+    # key-range merge: every rank's rows and log-sum-exp against the double-precision merge
+    rows, dim = 16, 256
+    mbuf = kv.PeerBuffer((rows * (dim * 2 + 4) + 15) // 16 * 16, world, rank)
+    mine = torch.tensor(list(mbuf.export), dtype=torch.uint8, device="cuda")
+    dist.all_gather_into_tensor(everyone, mine)
+    mbuf.connect(bytes(everyone.cpu().tolist()))
     dist.barrier()
+    for it in range(10):
+        gen.manual_seed(7000 + 10 * it + rank)
+        out = torch.randn(rows, dim, device="cuda", generator=gen).bfloat16()
+        lse = torch.randn(rows, device="cuda", generator=gen) * 4
+        if it % 3 == 0 and rank == world - 1:
+            lse[5] = float("-inf")                      # this rank saw no key of that row
+        all_out = torch.empty(world, rows, dim, dtype=torch.bfloat16, device="cuda")
+        all_lse = torch.empty(world, rows, dtype=torch.float32, device="cuda")
+        dist.all_gather_into_tensor(all_out, out)
+        dist.all_gather_into_tensor(all_lse, lse)
+        merged, merged_lse = torch.empty_like(out), torch.empty_like(lse)
+        mbuf.merge_attention(merged, merged_lse, out, lse, rows, dim, status=status)
+        torch.cuda.synchronize()
+        assert status[0].item() == 0
+        w = torch.softmax(all_lse.double(), dim=0)                              # [world, rows]
+        want = (w[:, :, None] * all_out.double()).sum(0)
+        want_lse = torch.logsumexp(all_lse.double(), dim=0)
+        err = (merged.double() - want).abs().max().item()
+        assert err <= 2.0 ** -7 * max(1.0, want.abs().max().item()), f"rank {rank} merge {it}: {err}"
+        assert (merged_lse.double() - want_lse).abs().max().item() <= 1e-4
+    dist.barrier()
+    mbuf.close()
     buf.close()
     if rank == 0:
         print("PEER_GATHER_OK", world)

@@ -34,6 +34,28 @@ def test_single_rank_gather_copies_and_alternates_halves(kv):
     buf.close()
 
 
+def test_single_rank_merge_is_the_identity(kv):
+    """One rank: weight exp(lse - lse) = 1, so the merged rows are the rows; a row without keys (-inf) gives 0."""
+    rows, dim = 16, 256
+    buf = kv.PeerBuffer(rows * (dim * 2 + 4) + 12, 1, 0) if (rows * (dim * 2 + 4) + 12) % 16 == 0 else \
+        kv.PeerBuffer((rows * (dim * 2 + 4) + 15) // 16 * 16, 1, 0)
+    out = torch.randn(rows, dim, device="cuda").bfloat16()
+    lse = torch.randn(rows, device="cuda") * 5
+    lse[3] = float("-inf")
+    merged = torch.full_like(out, float("nan"))
+    merged_lse = torch.full_like(lse, float("nan"))
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    for _ in range(3):
+        buf.merge_attention(merged, merged_lse, out, lse, rows, dim, status=status)
+    torch.cuda.synchronize()
+    assert status[0].item() == 0
+    keep = [r for r in range(rows) if r != 3]
+    assert torch.equal(merged[keep].view(torch.int16), out[keep].view(torch.int16))
+    assert (merged[3] == 0).all() and merged_lse[3].item() == float("-inf")
+    assert torch.equal(merged_lse[keep], lse[keep])
+    buf.close()
+
+
 def test_gather_argument_checks(kv):
     buf = kv.PeerBuffer(1024, 1, 0)
     src = torch.zeros(1024, dtype=torch.int32, device="cuda")
@@ -57,3 +79,48 @@ def test_two_or_more_ranks_against_nccl():
     proc = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=str(REPO))
     assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-4000:]
     assert f"PEER_GATHER_OK {world}" in proc.stdout
+
+
+def test_key_range_shards_merge_to_the_unsharded_attention(kv, orc):
+    """Key-range sharding on one GPU: the keys of a sequence are attended in two pieces (the second piece through
+    a page table that starts at its first page, so its keys sit at local positions 0..), and the pieces' rows
+    and log-sum-exp merged as b200kv_peer_merge_attention merges them equal the attention over all keys."""
+    from tests import helpers
+    from tests.gpu_util import dev, host_u16
+    from tests.helpers import ATTN_MAX_ABS, ATTN_MAX_REL, LSE_MAX_ABS, attention_error
+
+    HQ, D, total, cut = 16, 256, 2000, 1024
+    case = helpers.make_attn_case(77, [total], window=0, outlier_frac=0.01)
+    cfg = kv.make_kv_config(*case.cfg)
+    mpps = case.cfg[3]
+    tables = [case.page_table, np.concatenate([case.page_table[:, cut // 16:],
+                                               np.full((1, cut // 16), -1, np.int32)], axis=1)]
+    lengths = [cut, total - cut]
+    assert tables[1].shape == (1, mpps)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    ns = kv.plan_balanced(1, sms)
+    dq, dk, dv = dev(case.q), dev(case.cache_k), dev(case.cache_v)
+    pm = torch.zeros(HQ * ns, dtype=torch.float32, device="cuda")
+    pl, pacc = pm.clone(), torch.zeros(HQ * ns * D, dtype=torch.float32, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    outs, lses = [], []
+    for table, length in zip(tables, lengths):
+        out = torch.zeros((1, HQ, D), dtype=torch.int16, device="cuda")
+        lse = torch.zeros((1, HQ), dtype=torch.float32, device="cuda")
+        kv.decode_attention(out, lse, dq, dk, dv, cfg, dev(table), dev(np.array([length], np.int32)), 0, case.scale,
+                            0, ns, 1, HQ, pm, pl, pacc, status)
+        torch.cuda.synchronize()
+        outs.append(orc.bf16_to_f32(host_u16(out)).reshape(HQ, D).astype(np.float64))
+        lses.append(lse.cpu().numpy().reshape(HQ).astype(np.float64))
+    assert status[0].item() == 0
+    lse_all = np.stack(lses)
+    top = lse_all.max(0)
+    weight = np.exp(lse_all - top)
+    weight /= weight.sum(0)
+    merged = (weight[:, :, None] * np.stack(outs)).sum(0)
+    merged_lse = top + np.log(np.exp(lse_all - top).sum(0))
+    ref, ref_lse = orc.decode_attention_f64(case.q, case.cache_k, case.cache_v, case.page_table,
+                                            np.array([total], np.int32), case.cfg, 0, case.scale, 1, HQ)
+    max_abs, max_rel = attention_error(orc.f32_to_bf16(merged.astype(np.float32)), ref)
+    assert max_abs <= ATTN_MAX_ABS and max_rel <= ATTN_MAX_REL, (max_abs, max_rel)
+    assert np.abs(merged_lse - ref_lse.reshape(HQ)).max() <= LSE_MAX_ABS
