@@ -5,7 +5,10 @@ Two ways the path shards, neither of which the single-GPU reference has:
     sequences and no collective is on the data path;
   * by KV head: heads are independent until the output row is assembled; rank r owns KV heads
     [r * H/N, (r + 1) * H/N) and their query heads, holds a cache with num_heads = H/N, and the step ends with
-    an all-gather of the per-head outputs.
+    an all-gather of the per-head outputs;
+  * by key range: rank r owns all heads of the pages of positions [r * C, (r + 1) * C) of one long sequence,
+    attends the full query over them, and the ranks' normalised rows are merged with their log-sum-exp
+    (b200kv_peer_merge_attention does the exchange and the merge on the GPUs).
 """
 from __future__ import annotations
 
@@ -47,3 +50,34 @@ def slice_query_heads(q: np.ndarray, q_heads: int, kv_heads: int, world: int, ra
     group = q_heads // kv_heads
     lo, hi = kv_head_range(kv_heads, world, rank)
     return np.ascontiguousarray(np.asarray(q)[:, lo * group:hi * group, :])
+
+
+def key_range_page_table(page_table: np.ndarray, seq_len: int, page_size: int, world: int, rank: int):
+    """Rank's view of one sequence's page table for key-range sharding: the pages of its positions moved to the
+    front (local positions start at 0), the rest unmapped. Returns (table, local length, first absolute
+    position). The keys are dealt in whole pages, the last rank takes the remainder."""
+    table = np.asarray(page_table, dtype=np.int32)
+    pages = -(-int(seq_len) // page_size)
+    per = -(-pages // world)
+    lo, hi = min(rank * per, pages), min((rank + 1) * per, pages)
+    out = np.full_like(table, -1)
+    out[:, :hi - lo] = table[:, lo:hi]
+    first = lo * page_size
+    length = max(0, min(int(seq_len), hi * page_size) - first)
+    return out, length, first
+
+
+def merge_attention_rows(outs, lses):
+    """The merge of b200kv_peer_merge_attention on the host: outs [ranks, rows, dim], lses [ranks, rows]
+    (natural log; -inf for a rank without keys). Returns (rows [rows, dim] float64, lse [rows])."""
+    outs = np.asarray(outs, dtype=np.float64)
+    lses = np.asarray(lses, dtype=np.float64)
+    top = lses.max(axis=0)
+    safe = np.where(np.isfinite(top), top, 0.0)
+    weight = np.exp(lses - safe)
+    total = weight.sum(axis=0)
+    norm = np.where(total > 0, total, 1.0)
+    merged = ((weight / norm)[:, :, None] * np.where(weight[:, :, None] > 0, outs, 0.0)).sum(axis=0)
+    with np.errstate(divide="ignore"):
+        lse = np.where(total > 0, safe + np.log(norm), -np.inf)
+    return merged, lse

@@ -147,3 +147,38 @@ def test_host_argument_rejection_needs_no_device(kv):
     assert kv.decode_append(None, 16, 16, good, 16, 16, 0, 16, 16, 16, 16, 16, 16, 16, 1, 16, 256, stream=0, check=False) == 1
     assert kv.decode_append(16, 16, 16, good, 16, 16, 0, 16, 16, 16, 16, 16, 16, 16, 1, 16, 100, stream=0, check=False) == 1
     assert kv.decode_append(16, 16, 16, good, 16, 16, 0, 16, 16, 16, 16, 16, 16, 16, 0, 16, 256, stream=0, check=False) == 0
+
+
+def test_projection_and_peer_argument_rejection_needs_no_device(kv):
+    """The decode projections and the peer-memory exchange reject bad host arguments before any CUDA call;
+    zero rows is a success without a launch."""
+    a = kv.IngressArgs()
+    assert kv.decode_ingress(a, stream=0, check=False) == 0
+    a.batch_count, a.hidden_size, a.cols, a.q_width, a.k_width = 1, 3840, 8192, 4096, 2048
+    assert kv.decode_ingress(a, stream=0, check=False) == 1                      # null pointers
+    a.raw_qkv = a.x = a.input_norm_weight = a.qkv_proj_col_major = 4096
+    a.hidden_size = 4096
+    assert kv.decode_ingress(a, stream=0, check=False) == 1                      # hidden size the kernel is not built for
+    a.hidden_size, a.x = 3840, 4100
+    assert kv.decode_ingress(a, stream=0, check=False) == 1                      # misaligned row
+    a.x, a.q_width, a.k_width = 4096, 8192, 2048
+    assert kv.decode_ingress(a, stream=0, check=False) == 1                      # q + k wider than the projection
+    e = kv.EgressArgs()
+    assert kv.decode_egress(e, stream=0, check=False) == 0
+    e.batch_count, e.hidden_size, e.attention_width = 1, 3840, 4096
+    assert kv.decode_egress(e, stream=0, check=False) == 1                       # null pointers
+    for name, _ in kv.EgressArgs._fields_[:10]:
+        setattr(e, name, 4096)
+    e.attention_width = 1024
+    assert kv.decode_egress(e, stream=0, check=False) == 1                       # width other than 4096 / 8192
+    e.attention_width, e.ffn_x, e.pre_ffn_norm_weight = 4096, 4096, None
+    assert kv.decode_egress(e, stream=0, check=False) == 1                       # ffn_x without its norm weight
+    layer = kv.AttentionLayerArgs()
+    layer.kv.batch_count = 1
+    assert kv.decode_attention_layer(layer, stream=0, check=False) == 1          # no geometry, no scratch
+    with pytest.raises(kv.CudaError):
+        kv.PeerBuffer(1000, 2, 0)                                                # slot not a multiple of 16
+    with pytest.raises(kv.CudaError):
+        kv.PeerBuffer(1024, 2, 2)                                                # rank outside the world
+    with pytest.raises(kv.CudaError):
+        kv.PeerBuffer(1024, 9, 0)                                                # more than 8 ranks

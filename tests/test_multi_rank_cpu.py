@@ -5,7 +5,10 @@ put back together must equal the single-rank oracle result.
     balanced, and the union of the ranks' outputs is the full batch's output, bit for bit;
   * KV-head sharding (all-gather of head outputs): each rank attends over a cache that holds only its heads,
     the all-gathered rows equal the 8-head result bit for bit, and the fused append on the head slices writes
-    the same bytes as the full append.
+    the same bytes as the full append;
+  * key-range sharding (exchange of rows + log-sum-exp, merge): each rank attends the full query over its pages
+    of one long sequence through a page table that starts at its first page; the merged rows equal the
+    attention over all keys within double-precision rounding.
 The per-rank arithmetic is the CPU oracle here (no GPU in this suite); the GPU suite checks the kernels for
 the same head counts (8, 4, 2, 1).
 """
@@ -89,14 +92,30 @@ def _worker(rank: int, world: int, port: int, result_dir: str):
         flag = torch.tensor([int(append_ok)])
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
 
+        # ---- by key range ---------------------------------------------------------------------------
+        kcase = make_attn_case(903, [1500], window=0, outlier_frac=0.01)
+        ktable, klen, _ = sharding.key_range_page_table(kcase.page_table, 1500, kcase.cfg[2], world, rank)
+        kout, klse = orc.decode_attention_f64(kcase.q, kcase.cache_k, kcase.cache_v, ktable,
+                                              np.array([klen], np.int32), kcase.cfg, 0, kcase.scale, 1, 16)
+        rows_all = [torch.empty((1, 16, 256), dtype=torch.float32) for _ in range(world)]
+        lse_all = [torch.empty((1, 16), dtype=torch.float32) for _ in range(world)]
+        dist.all_gather(rows_all, torch.from_numpy(kout))
+        dist.all_gather(lse_all, torch.from_numpy(klse))
+        merged, merged_lse = sharding.merge_attention_rows(
+            np.stack([t.numpy().reshape(16, 256) for t in rows_all]), np.stack([t.numpy().reshape(16) for t in lse_all]))
+
         if rank == 0:
+            kref, kref_lse = orc.decode_attention_f64(kcase.q, kcase.cache_k, kcase.cache_v, kcase.page_table,
+                                                      kcase.seq_lengths, kcase.cfg, 0, kcase.scale, 1, 16)
+            key_err = float(np.abs(merged - kref.reshape(16, 256)).max())
+            key_lse_err = float(np.abs(merged_lse - kref_lse.reshape(16)).max())
             ref, _ = orc.decode_attention_f64(case.q, case.cache_k, case.cache_v, case.page_table, case.seq_lengths,
                                               case.cfg, 0, case.scale, case.batch, 16)
             href, _ = orc.decode_attention_f64(hcase.q, hcase.cache_k, hcase.cache_v, hcase.page_table,
                                                hcase.seq_lengths, hcase.cfg, 0, hcase.scale, 2, 16)
             np.savez(os.path.join(result_dir, "result.npz"), owner=owner.numpy(), loads=loads.numpy(),
                      seq_equal=np.array_equal(full.numpy(), ref), head_equal=np.array_equal(head_rows.numpy(), href),
-                     append_ok=int(flag.item()))
+                     append_ok=int(flag.item()), key_err=key_err, key_lse_err=key_lse_err)
     finally:
         dist.destroy_process_group()
 
@@ -111,6 +130,7 @@ def test_two_gloo_ranks_reassemble_the_single_rank_result(tmp_path):
     assert bool(r["seq_equal"])
     assert bool(r["head_equal"])
     assert int(r["append_ok"]) == 1
+    assert float(r["key_err"]) <= 1e-5 and float(r["key_lse_err"]) <= 1e-4     # fp32 rows, fp64 merge
 
 
 def test_sharding_helpers(kv):
@@ -123,6 +143,14 @@ def test_sharding_helpers(kv):
         assert sorted(i for s in shards for i in s) == list(range(64))
         loads = [int(ctx[s].sum()) for s in shards]
         assert max(loads) - min(loads) <= ctx.max()
+    table = np.arange(10, dtype=np.int32)[None, :] + 100
+    t0, n0, f0 = sharding.key_range_page_table(table, 150, 16, 4, 0)
+    t3, n3, f3 = sharding.key_range_page_table(table, 150, 16, 4, 3)
+    assert (n0, f0, list(t0[0, :3]), t0[0, 3]) == (48, 0, [100, 101, 102], -1)
+    assert (n3, f3, t3[0, 0], t3[0, 1]) == (6, 144, 109, -1)
+    rows, lse = sharding.merge_attention_rows(np.ones((2, 3, 4)), np.array([[0.0, -np.inf, -np.inf], [0.0, 1.0, -np.inf]]))
+    assert np.allclose(rows[0], 1.0) and np.allclose(rows[1], 1.0) and np.all(rows[2] == 0.0)
+    assert np.isclose(lse[0], np.log(2.0)) and np.isclose(lse[1], 1.0) and np.isneginf(lse[2])
     assert sharding.kv_head_range(8, 4, 3) == (6, 8)
     with pytest.raises(ValueError):
         sharding.kv_head_range(8, 3, 0)
