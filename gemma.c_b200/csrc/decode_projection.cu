@@ -285,6 +285,18 @@ decode_projection_kernel(const ProjParams p) {
         __threadfence_block();
         armed = n + 1;
       }
+      // Leave only when every copy this thread issued has landed: a CTA must
+      // not exit (a consumer may have given up on a wait) with bulk copies
+      // still writing into its shared memory. The last kProjStages stages are
+      // the ones that can still be in flight; nothing re-arms their barriers.
+      const int issued = armed;
+      for (int n = max(0, issued - kProjStages); n < issued; ++n) {
+        if (!mbar_wait_bounded(smem_u32(&full_bar[n % kProjStages]),
+                               uint32_t(n / kProjStages) & 1u)) {
+          set_status(p.status, B200KV_STATUS_WAIT_TIMEOUT);
+          break;
+        }
+      }
     }
     return;
   }
