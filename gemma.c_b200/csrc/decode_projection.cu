@@ -366,16 +366,21 @@ decode_projection_kernel(const ProjParams p) {
   }
 
   if constexpr (kEgress) {
-    // The CTA that finishes a row last norms it and adds the residual.
-    __threadfence();
+    // The CTA that finishes a row last norms it and adds the residual. One
+    // acquire-release ticket at device scope: the barrier before it orders the
+    // CTA's column stores ahead of the release, the barrier after it orders the
+    // acquire ahead of the last CTA's loads of everyone's columns.
     named_barrier_sync(1, kProjConsumerThreads);
     if (thread == 0) {
-      const unsigned int done = atomicAdd(p.ticket + row, 1u);
+      unsigned int done;
+      asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;"
+                   : "=r"(done)
+                   : "l"(p.ticket + row)
+                   : "memory");
       last_flag = (done == gridDim.x - 1) ? 1u : 0u;
     }
     named_barrier_sync(1, kProjConsumerThreads);
     if (last_flag == 0u) return;
-    __threadfence();
     uint4 o = make_uint4(0, 0, 0, 0);
     const int64_t base = int64_t(row) * kProjHidden;
     if (thread < kProjHiddenPacks) {

@@ -117,6 +117,21 @@ def test_egress_matches_the_oracle_bit_for_bit(kv, orc, rows, width):
             assert np.array_equal(g[r], w), (name, r, int((g[r] != w).sum()))
 
 
+def test_egress_many_calls_in_a_row_stay_exact(kv, orc):
+    """The tail runs in whichever CTA finishes last and reads what all the others wrote: 150 launches back to
+    back, outputs poisoned in between, every result the oracle's bits."""
+    rows, width = 2, 4096
+    case = _egress_case(77, rows, width)
+    want = [orc.decode_egress(case["attn"][r], case["w_o"], case["w_post"], case["w_pre"], case["x"][r])
+            for r in range(rows)]
+    ticket = torch.zeros(rows, dtype=torch.int32, device="cuda")
+    for _ in range(15):
+        got = _run_egress(kv, case, rows, width, kv.NORM_IEEE, ticket=ticket, calls=10)
+        for r in range(rows):
+            for g, w in zip(got, want[r]):
+                assert np.array_equal(g[r], w)
+
+
 def test_egress_without_ffn_x_leaves_it_alone(kv, orc):
     case = _egress_case(31, 1, 4096)
     got = _run_egress(kv, case, 1, 4096, kv.NORM_IEEE, with_ffn_x=False)
