@@ -182,16 +182,22 @@ def test_default_mode_equals_the_reference_kernels(kv, global_geometry):
         assert np.array_equal(g[0], host_u16(w)), (name, int((g[0] != host_u16(w)).sum()))
 
 
-@pytest.mark.parametrize("rows,window", [(1, 1024), (3, 0)])
-def test_attention_layer_chain(kv, orc, rows, window):
+@pytest.mark.parametrize("rows,window,native_global", [(1, 1024, False), (3, 0, False), (2, 0, True)])
+def test_attention_layer_chain(kv, orc, rows, window, native_global):
     """Layer input -> FFN input in one call. Oracle: ingress, append, double-precision attention (tolerance),
-    then egress from the attention rows the GPU produced (so the last stage is again compared bit for bit)."""
-    HQ, H, D = 16, 8, 256
-    cols, q_width, k_width = 8192, 4096, 2048
+    then egress from the attention rows the GPU produced (so the last stage is again compared bit for bit).
+    native_global: the reference's global-layer geometry, 16 query heads on one KV head of 512 dims, rotary on
+    the first 128, no V projection (V from raw K) -- 8704 projection columns, O projection of width 8192."""
+    HQ, H, D, ROT = (16, 1, 512, 128) if native_global else (16, 8, 256, 256)
+    q_width, k_width = HQ * D, H * D
+    cols = q_width + k_width * (1 if native_global else 2)
+    scale = 1.0 / np.sqrt(D)
     rng = np.random.default_rng(500 + rows)
     start = np.array([700, 33, 1500][:rows], np.int32) if window == 0 else np.array([1500][:rows], np.int32)
     acase = helpers.make_append_case(41 + rows, start, window=window, ring_pages=None if window == 0 else 65,
-                                     max_pos=int(start.max()) + 2)
+                                     max_pos=int(start.max()) + 2, kv_heads=H, q_heads=HQ, head_dim=D,
+                                     rotary_dim=ROT, has_v=not native_global,
+                                     theta=1.0e6 if native_global else 1.0e4)
     cfg_t = acase.cfg
     cfg = kv.make_kv_config(*cfg_t)
     elems = cfg_t[0] * cfg_t[1] * cfg_t[2] * cfg_t[5] * cfg_t[6]
@@ -222,16 +228,16 @@ def test_attention_layer_chain(kv, orc, rows, window):
     s.partial_m, s.partial_l, s.partial_acc = pm.data_ptr(), pl.data_ptr(), pacc.data_ptr()
     s.cache_k, s.cache_v, s.cache_config = d["ck"].data_ptr(), d["cv"].data_ptr(), cfg
     s.page_table, s.token_position, s.seq_lengths = d["table"].data_ptr(), d["pos"].data_ptr(), d["length"].data_ptr()
-    s.cache_layer, s.split_size, s.num_splits, s.softmax_scale = 0, 0, num_splits, 1.0 / 16.0
+    s.cache_layer, s.split_size, s.num_splits, s.softmax_scale = 0, 0, num_splits, scale
     s.q_norm_weight, s.k_norm_weight, s.cos, s.sin = (d["qw"].data_ptr(), d["kw"].data_ptr(), d["cos"].data_ptr(),
                                                      d["sin"].data_ptr())
-    s.batch_count, s.q_heads, s.rotary_dim, s.norm_mode, s.status = rows, HQ, D, kv.NORM_IEEE, status.data_ptr()
+    s.batch_count, s.q_heads, s.rotary_dim, s.norm_mode, s.status = rows, HQ, ROT, kv.NORM_IEEE, status.data_ptr()
     a.attention_x, a.attention_input_norm_weight = d["x"].data_ptr(), d["w_in"].data_ptr()
     a.attention_qkv_proj_col_major, a.attention_o_proj_col_major = d["w"].data_ptr(), d["w_o"].data_ptr()
     a.attention_post_norm_weight, a.attention_pre_ffn_norm_weight = d["w_post"].data_ptr(), d["w_pre"].data_ptr()
     a.raw_qkv = raw.data_ptr()
     a.residual_out, a.normed_out, a.ffn_residual, a.ffn_x = (t.data_ptr() for t in outs)
-    a.ticket, a.hidden_size, a.has_v_projection = ticket.data_ptr(), HIDDEN, 1
+    a.ticket, a.hidden_size, a.has_v_projection = ticket.data_ptr(), HIDDEN, 0 if native_global else 1
     kv.decode_attention_layer(a)
     torch.cuda.synchronize()
     assert status[0].item() == 0
@@ -239,13 +245,13 @@ def test_attention_layer_chain(kv, orc, rows, window):
     raw_rows = np.stack([orc.decode_ingress(icase["x"][r], icase["w_in"], icase["w"])[0] for r in range(rows)])
     rq = np.ascontiguousarray(raw_rows[:, :q_width]).reshape(rows, HQ, D)
     rk = np.ascontiguousarray(raw_rows[:, q_width:q_width + k_width]).reshape(rows, H, D)
-    rv = np.ascontiguousarray(raw_rows[:, q_width + k_width:]).reshape(rows, H, D)
+    rv = None if native_global else np.ascontiguousarray(raw_rows[:, q_width + k_width:]).reshape(rows, H, D)
     qp = np.zeros((rows, HQ, D), np.uint16)
     orc.decode_append(qp, ck, cv, cfg_t, acase.page_table, start, 0, rq, rk, rv, acase.q_w, acase.k_w, acase.cos,
-                      acase.sin, rows, HQ, D)
+                      acase.sin, rows, HQ, ROT)
     assert np.array_equal(host_u16(q), qp.reshape(-1))
     assert np.array_equal(host_u16(d["ck"]), ck) and np.array_equal(host_u16(d["cv"]), cv)
-    ref, _ = orc.decode_attention_f64(qp, ck, cv, acase.page_table, length, cfg_t, 0, 1.0 / 16.0, rows, HQ)
+    ref, _ = orc.decode_attention_f64(qp, ck, cv, acase.page_table, length, cfg_t, 0, scale, rows, HQ)
     max_abs, max_rel = attention_error(host_u16(out), ref)
     assert max_abs <= ATTN_MAX_ABS and max_rel <= ATTN_MAX_REL, (max_abs, max_rel)
     attn = host_u16(out).reshape(rows, q_width)
