@@ -152,3 +152,71 @@ cudaError_t gemma4_runtime_prepare_prefill(Gemma4RuntimeState *state,
 // src/gemma4_runtime.cu:276-341
 cudaError_t gemma4_runtime_prepare_decode_step(Gemma4RuntimeState *state,
                                                cudaStream_t stream);
+
+// The attention half of gemma4_decode_megakernel_flash_attention_layer_bf16
+// (src/gemma4_flash_attention_decode.cu:1122-1157), called from the layer loop
+// of gemma4_decode_megakernel (src/gemma4_decode_megakernel.cu:172-183) with
+// the reference's own per-layer argument struct: `LayerArgs` is any type with
+// the attention_* / residual_out / normed_out / ffn_residual / ffn_x members of
+// Gemma4DecodeMegakernelLayerArgs (src/gemma4_megakernel.cuh:32-66), which this
+// header therefore does not need to see. Enqueues input norm + QKV projection,
+// append + decode attention + combine, O projection + post-attention norm +
+// residual + pre-FFN norm on `stream`; the caller's FFN launch follows.
+// `raw_qkv_scratch`: 8704 bf16 per row (the reference reuses attention_out /
+// attention_q for it; here it is a buffer of its own); `ticket`: uint32 per
+// row, zero before the first call. Geometry as the reference derives it from
+// the cache config: 8 KV heads x 256 (sliding, own V projection, rotary 256) or
+// 1 KV head x 512 (global, V from raw K, rotary 128), 16 query heads.
+template <class LayerArgs>
+inline cudaError_t gemma4_b200kv_decode_attention_layer(
+    const LayerArgs &args, __nv_bfloat16 *raw_qkv_scratch, uint32_t *ticket,
+    int32_t batch_count, cudaStream_t stream, int32_t *status = nullptr) {
+  const Gemma4KvCacheConfig &cfg = args.attention_cache_config;
+  const bool global_geometry = cfg.head_dim == 512 && cfg.num_heads == 1;
+  if (!global_geometry && !(cfg.head_dim == 256 && cfg.num_heads == 8)) {
+    return cudaErrorInvalidValue;  // as the reference's dispatch, decode.cu:1126-1156
+  }
+  auto bits = [](auto *p) {
+    return reinterpret_cast<b200kv_bf16 *>(const_cast<__nv_bfloat16 *>(p));
+  };
+  B200KvAttentionLayerArgs a = {};
+  a.kv.q = bits(args.attention_q);
+  a.kv.out = bits(args.attention_out);
+  a.kv.partial_m = args.attention_partial_m;
+  a.kv.partial_l = args.attention_partial_l;
+  a.kv.partial_acc = args.attention_partial_acc;
+  a.kv.cache_k = bits(args.attention_cache_k);
+  a.kv.cache_v = bits(args.attention_cache_v);
+  a.kv.cache_config = cfg;
+  a.kv.page_table = args.attention_page_table;
+  a.kv.token_position = args.attention_token_position;
+  a.kv.seq_lengths = args.attention_seq_lengths;
+  a.kv.cache_layer = args.attention_cache_layer;
+  a.kv.split_size = args.attention_split_size;
+  a.kv.num_splits = args.attention_num_splits;
+  a.kv.softmax_scale = args.attention_softmax_scale;
+  a.kv.q_norm_weight = bits(args.attention_q_norm_weight);
+  a.kv.k_norm_weight = bits(args.attention_k_norm_weight);
+  a.kv.cos = args.attention_cos;
+  a.kv.sin = args.attention_sin;
+  a.kv.batch_count = batch_count;
+  a.kv.q_heads = 16;
+  a.kv.rotary_dim = global_geometry ? 128 : 256;
+  a.kv.norm_mode = B200KV_NORM_RSQRT_APPROX;
+  a.kv.status = status;
+  a.attention_x = bits(args.attention_x);
+  a.attention_input_norm_weight = bits(args.attention_input_norm_weight);
+  a.attention_qkv_proj_col_major = bits(args.attention_qkv_proj_col_major);
+  a.attention_o_proj_col_major = bits(args.attention_o_proj_col_major);
+  a.attention_post_norm_weight = bits(args.attention_post_norm_weight);
+  a.attention_pre_ffn_norm_weight = bits(args.attention_pre_ffn_norm_weight);
+  a.raw_qkv = bits(raw_qkv_scratch);
+  a.residual_out = bits(args.residual_out);
+  a.normed_out = bits(args.normed_out);
+  a.ffn_residual = bits(args.ffn_residual);
+  a.ffn_x = bits(args.ffn_x);
+  a.ticket = ticket;
+  a.hidden_size = 3840;
+  a.has_v_projection = global_geometry ? 0 : 1;
+  return static_cast<cudaError_t>(b200kv_decode_attention_layer_bf16(&a, stream));
+}

@@ -182,3 +182,21 @@ def test_projection_and_peer_argument_rejection_needs_no_device(kv):
         kv.PeerBuffer(1024, 2, 2)                                                # rank outside the world
     with pytest.raises(kv.CudaError):
         kv.PeerBuffer(1024, 9, 0)                                                # more than 8 ranks
+
+
+def test_cpp_header_binds_a_reference_shaped_layer_struct(kv, tmp_path):
+    """include/gemma4_b200kv.hpp from a C++ translation unit: a struct with the member names of the reference's
+    Gemma4DecodeMegakernelLayerArgs goes through the header's binding template and links against the library."""
+    import shutil
+
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    repo = kv.library_path().parents[2]
+    exe = tmp_path / "megakernel_binding"
+    lib_dir = kv.library_path().parent
+    build = subprocess.run([nvcc, "-std=c++17", "-I", str(repo / "include"), str(repo / "tests" / "cpp" / "megakernel_binding.cu"),
+                            "-L", str(lib_dir), "-lgemma4_b200kv", "-Xlinker", "-rpath", "-Xlinker", str(lib_dir),
+                            "-o", str(exe)], capture_output=True, text=True)
+    assert build.returncode == 0, build.stdout + build.stderr
+    run = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert run.returncode == 0, run.stdout + run.stderr
+    assert run.stdout.split() == ["1", "1", "0"]
