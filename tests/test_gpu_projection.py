@@ -79,6 +79,29 @@ def test_ingress_small_and_odd_column_counts(kv, orc):
         assert np.array_equal(raw, want), cols
 
 
+def test_projection_edge_values(kv, orc):
+    """A layer input of zeros (the norm's scale is rsqrt(eps), every sum is +0), and inputs of large magnitude
+    (sums near the top of bf16's exponent range): still the oracle's bits, ingress and egress."""
+    cols, q_width, k_width = 8192, 4096, 2048
+    case = _ingress_case(900, 1, cols)
+    case["x"] = np.zeros_like(case["x"])
+    raw, _ = _run_ingress(kv, case, 1, cols, q_width, k_width, kv.NORM_IEEE)
+    assert not raw.any()
+    big = _ingress_case(901, 1, cols)
+    big["x"] = helpers.bf16_normal(np.random.default_rng(5), (1, HIDDEN), std=3.0e4)
+    big["w"] = helpers.bf16_normal(np.random.default_rng(6), (cols, HIDDEN), std=40.0)
+    raw, _ = _run_ingress(kv, big, 1, cols, q_width, k_width, kv.NORM_IEEE)
+    want, _ = orc.decode_ingress(big["x"][0], big["w_in"], big["w"])
+    assert np.array_equal(raw, want) and np.abs(orc.bf16_to_f32(want)).max() > 1.0e3
+    ecase = _egress_case(902, 1, 4096)
+    ecase["attn"] = np.zeros_like(ecase["attn"])          # O projection of zeros: the residual passes through
+    got = _run_egress(kv, ecase, 1, 4096, kv.NORM_IEEE)
+    want = orc.decode_egress(ecase["attn"][0], ecase["w_o"], ecase["w_post"], ecase["w_pre"], ecase["x"][0])
+    for g, w in zip(got, want):
+        assert np.array_equal(g[0], w)
+    assert not got[0].any() and np.array_equal(got[2][0], ecase["x"][0])
+
+
 def _egress_case(seed, rows, width):
     rng = np.random.default_rng(seed)
     return dict(attn=helpers.bf16_normal(rng, (rows, width)), w_o=_weights(rng, HIDDEN, width),
