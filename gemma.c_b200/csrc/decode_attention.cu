@@ -103,6 +103,7 @@ __global__ __launch_bounds__(T::kThreads, T::kCtasPerSm) void decode_split_kerne
                           reinterpret_cast<const uint8_t *>(p.cache_v),
                           p.page_table, p.layer};
     bool ok = true;
+    PageEntryCache page_cache;
     int issued = 0;  // chunks whose full barrier has been armed
     for (int c = 0; c < nchunks; ++c) {
       const int stage = c % kStages;
@@ -113,7 +114,8 @@ __global__ __launch_bounds__(T::kThreads, T::kCtasPerSm) void decode_split_kerne
       }
       const int base = a0 + c * ST;
       producer_fill_stage<T>(ring, src, cfg, batch, base, max(split_begin, base),
-                             min(split_end, base + ST), stage, policy, lane);
+                             min(split_end, base + ST), stage, policy, lane,
+                             &page_cache);
       issued = c + 1;
     }
     // Hold the CTA until every copy this warp issued has landed.

@@ -244,6 +244,7 @@ __global__ __launch_bounds__(T::kThreads, T::kCtasPerSm) void decode_balanced_ke
                           p.page_table, p.layer};
     bool ok = true;
     bool waited = false;
+    PageEntryCache page_cache;
     int it = 0;  // stages armed so far, across all pieces of the range
     int b = b_start, flat = r0;
     Segment seg;
@@ -274,7 +275,8 @@ __global__ __launch_bounds__(T::kThreads, T::kCtasPerSm) void decode_balanced_ke
                                   stage, policy, lane);
         } else {
           producer_fill_stage<T>(ring, src, cfg, seg.b, base, max(seg.pos0, base),
-                                 min(seg.pos1, base + ST), stage, policy, lane);
+                                 min(seg.pos1, base + ST), stage, policy, lane,
+                                 &page_cache);
         }
       }
     }

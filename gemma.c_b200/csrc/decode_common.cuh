@@ -123,12 +123,36 @@ struct KvSource {
 // (all inside [base, base + kStageTokens)); a token sits in slot position -
 // base. One lane per page segment resolves the page table and issues the two
 // bulk copies; lane 0 publishes the token mask and arms the full barrier.
+// The page-table entry a lane resolved last. A stage is shorter than a page,
+// so consecutive stages mostly need the same entry; without this every stage
+// starts with a dependent global load (about a microsecond on a miss), which
+// is what bounded a CTA that streams only a few stages.
+struct PageEntryCache {
+  int batch = -1;
+  int logical_page = -1;
+  int physical = -1;
+};
+
 template <class T>
 __device__ __forceinline__ void producer_fill_stage(
     const Ring<T> &ring, const KvSource &src, const Gemma4KvCacheConfig &cfg,
-    int batch, int base, int c0, int c1, int stage, uint64_t policy, int lane) {
+    int batch, int base, int c0, int c1, int stage, uint64_t policy, int lane,
+    PageEntryCache *cache = nullptr) {
   const int ps = cfg.page_size;
-  const int64_t table_row = int64_t(batch) * cfg.max_pages_per_seq;
+  auto resolve = [&](int lp) {
+    if (cache != nullptr && cache->batch == batch && cache->logical_page == lp) {
+      return cache->physical;
+    }
+    const int slot = lp % cfg.max_pages_per_seq;
+    const int phys =
+        __ldg(src.page_table + int64_t(batch) * cfg.max_pages_per_seq + slot);
+    if (cache != nullptr) {
+      cache->batch = batch;
+      cache->logical_page = lp;
+      cache->physical = phys;
+    }
+    return phys;
+  };
   const int first_page = c0 / ps;
   const int nseg = (c1 - 1) / ps - first_page + 1;
   const uint32_t k_dst = ring.k_stage(stage);
@@ -142,8 +166,7 @@ __device__ __forceinline__ void producer_fill_stage(
       const int lp = first_page + seg;
       const int s0 = max(c0, lp * ps);
       const int s1 = min(c1, (lp + 1) * ps);
-      const int slot = lp % cfg.max_pages_per_seq;
-      const int phys = __ldg(src.page_table + table_row + slot);
+      const int phys = resolve(lp);
       if (phys >= 0 && phys < cfg.num_pages) {
         const int n = s1 - s0;
         my_bytes += uint32_t(n) * T::kRowBytes;
@@ -171,8 +194,7 @@ __device__ __forceinline__ void producer_fill_stage(
       const int lp = first_page + seg;
       const int s0 = max(c0, lp * ps);
       const int s1 = min(c1, (lp + 1) * ps);
-      const int slot = lp % cfg.max_pages_per_seq;
-      const int phys = __ldg(src.page_table + table_row + slot);
+      const int phys = resolve(lp);
       if (phys >= 0 && phys < cfg.num_pages) {
         const int64_t off =
             cache_offset(cfg, src.layer, phys, s0 - lp * ps, 0, 0);
