@@ -18,7 +18,7 @@ constexpr int kMaxBalancedBatch = 1024;  // live-key prefix sums live in smem
 // shared memory, which is what lets a CTA of the next layer-step's kernel (and
 // a waiting combine CTA) share an SM with a CTA of this one.
 constexpr int kSmallBalancedBatch = 64;
-constexpr int kMinKeysPerCta = 16;       // below this a CTA is all latency
+constexpr int kMinKeysPerCta = 8;        // below this a CTA is all latency
 
 struct BalancedParams {
   __nv_bfloat16 *out;
