@@ -561,6 +561,17 @@ __global__ __launch_bounds__(kThreads, 1) void prefill_attention_sm100_kernel(
     }
 
     // ---- the last P V, then O / l as bf16
+    // A parity wait cannot tell phase t from phase t - 2. The last thing this
+    // warp knows about the P V barrier is that tile tiles - 3 is done (the
+    // scores of the last tile were issued after it); P V of tile tiles - 2 may
+    // still be running, and a wait for the parity of tile tiles - 1 alone would
+    // then pass at once -- with the last two P V unfinished, O incomplete and
+    // the V tile, where the row sums go, about to be refilled. So: one phase
+    // at a time.
+    if (ok && tiles >= 2) {
+      ok = wait(bar_pv_done, uint32_t(tiles - 2) & 1u, 5);
+      ok = __all_sync(0xffffffffu, ok);
+    }
     if (ok) {
       ok = wait(bar_pv_done, uint32_t(tiles - 1) & 1u, 5);
       ok = __all_sync(0xffffffffu, ok);

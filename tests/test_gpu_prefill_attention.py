@@ -179,6 +179,27 @@ def test_prefill_attention_repeats_without_a_wait_running_out(kv, geom, batch, s
             assert torch.equal(out, first)
 
 
+def test_prefill_attention_last_tiles_are_waited_for(kv):
+    """1500 calls on prompts whose last query block is the longest CTA and the first one launched (cold loads):
+    the final wait of the softmax warps must cover the last two P V products, not just the parity of the last
+    (it passed early about once in 2000 calls before it waited one phase at a time; the symptom was one block of
+    rows divided by an incomplete row sum). Every call must give the first call's bits."""
+    rng = np.random.default_rng(5)
+    batch, seq, window = 3, 700, 0
+    q, k, v = _rows(rng, batch, seq, **SLIDING)
+    H, HKV, D = SLIDING["q_heads"], SLIDING["kv_heads"], SLIDING["head_dim"]
+    dq, dk, dv = dev(q), dev(k), dev(v)
+    first = None
+    for _ in range(1500):
+        out = torch.full((batch * seq, H, D), 0x7FC0, dtype=torch.int16, device="cuda")
+        kv.prefill_attention(out, dq, dk, dv, batch, seq, H, HKV, D, window, D ** -0.5)
+        if first is None:
+            first = out
+        else:
+            assert torch.equal(out, first)
+    assert kv.prefill_attention_fault() == 0
+
+
 @pytest.mark.parametrize("geom,batch,seq,window", [(SLIDING, 2, 1500, 1024), (GLOBAL, 1, 1300, 0)])
 def test_prefill_attention_long_prompt_against_torch_fp32(kv, orc, geom, batch, seq, window):
     """Prompts too long for the double-precision host oracle in a test: plain fp32 torch attention on the same
