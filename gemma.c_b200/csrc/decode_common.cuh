@@ -153,10 +153,43 @@ __device__ __forceinline__ void producer_fill_stage(
     }
     return phys;
   };
-  const int first_page = c0 / ps;
-  const int nseg = (c1 - 1) / ps - first_page + 1;
   const uint32_t k_dst = ring.k_stage(stage);
   const uint32_t v_dst = k_dst + T::kStageTensorBytes;
+
+  if constexpr (T::kRowBytes >= 4096 && T::kStageTokens <= kWarpSize) {
+    // Wide rows (all 8 KV heads: 4 KiB per token and tensor): one lane per
+    // token, one copy per token and tensor. A CTA that streams only a few
+    // stages is bound by how fast its copies come in, and that grows with the
+    // number of copies in flight, not with their size.
+    const int pos = c0 + lane;
+    const bool mine = pos < c1;
+    const int lp = mine ? pos / ps : 0;
+    const int phys = mine ? resolve(lp) : -1;
+    const bool valid = mine && phys >= 0 && phys < cfg.num_pages;
+    const uint32_t live = __ballot_sync(0xffffffffu, valid);
+    if (lane == 0) {
+      ring.masks()[stage] = static_cast<unsigned long long>(live) << (c0 - base);
+      if (live != 0u) {
+        mbar_arrive_expect_tx(ring.full_bar(stage),
+                              2u * uint32_t(__popc(live)) * T::kRowBytes);
+      } else {
+        mbar_arrive(ring.full_bar(stage));
+      }
+    }
+    __syncwarp();
+    if (valid) {
+      const int64_t off = cache_offset(cfg, src.layer, phys, pos - lp * ps, 0, 0);
+      const uint32_t dst_off = uint32_t(pos - base) * T::kRowBytes;
+      bulk_load_hint(k_dst + dst_off, src.cache_k + off * T::kElemBytes,
+                     T::kRowBytes, ring.full_bar(stage), policy);
+      bulk_load_hint(v_dst + dst_off, src.cache_v + off * T::kElemBytes,
+                     T::kRowBytes, ring.full_bar(stage), policy);
+    }
+    return;
+  }
+
+  const int first_page = c0 / ps;
+  const int nseg = (c1 - 1) / ps - first_page + 1;
 
   unsigned long long my_mask = 0;
   uint32_t my_bytes = 0;
