@@ -265,3 +265,37 @@ def test_bounded_wait_reports_instead_of_hanging(kv):
     d = DeviceCase(kv, case)
     out, lse, _ = d.run(64, 4)
     assert kv.STATUS_WAIT_TIMEOUT == 1
+
+
+@pytest.mark.parametrize("name,seq_lens,window,kvh,dim,split", [
+    ("balanced batch 1 ring", [1500], 1024, 8, 256, 0),
+    ("balanced ragged", [700, 33, 1500, 64, 260, 1024, 2000, 90], 0, 8, 256, 0),
+    ("fixed splits, 2 KV heads", [3000, 70, 1024, 513], 0, 2, 256, 128),
+    ("16 query heads on one KV head of 512", [4096], 0, 1, 512, 0),
+])
+def test_launches_back_to_back_give_the_same_bits(kv, name, seq_lens, window, kvh, dim, split):
+    """300 launches enqueued without a host synchronisation in between (each may start under its predecessor's
+    tail: programmatic dependent launch) on the same inputs and the same scratch: every output the first one's
+    bits, no wait running out."""
+    hq = 16 if kvh in (8, 1) else 2 * kvh
+    case = make_attn_case(11, seq_lens, window=window, kv_heads=kvh, q_heads=hq, head_dim=dim)
+    B = len(seq_lens)
+    cfg = kv.make_kv_config(*case.cfg)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    live = max(min(s, window) if window else s for s in seq_lens)
+    ns = kv.plan_balanced(B, sms) if split == 0 else -(-live // split)
+    d = [dev(x) for x in (case.q, case.cache_k, case.cache_v, case.page_table, case.seq_lengths)]
+    pm = torch.zeros(B * hq * ns, device="cuda")
+    pl, pacc = pm.clone(), torch.zeros(B * hq * ns * dim, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    outs = []
+    for _ in range(300):
+        out = torch.full((B, hq, dim), 0x7FC0, dtype=torch.int16, device="cuda")
+        lse = torch.zeros(B, hq, device="cuda")
+        kv.decode_attention(out, lse, d[0], d[1], d[2], cfg, d[3], d[4], 0, case.scale, split, ns, B, hq, pm, pl, pacc,
+                            status)
+        outs.append((out, lse))
+    torch.cuda.synchronize()
+    assert status[0].item() == 0
+    for out, lse in outs[1:]:
+        assert torch.equal(out, outs[0][0]) and torch.equal(lse, outs[0][1]), name
