@@ -283,3 +283,84 @@ def test_attention_layer_chain(kv, orc, rows, window, native_global):
         want = orc.decode_egress(attn[r], ecase["w_o"], ecase["w_post"], ecase["w_pre"], icase["x"][r])
         for name, g, w in zip(("residual_out", "normed_out", "ffn_residual", "ffn_x"), got, want):
             assert np.array_equal(g[r], w), (name, r, int((g[r] != w).sum()))
+
+
+def test_attention_layer_against_the_reference_phases_end_to_end(kv, orc):
+    """The whole attention half of a decode layer, this library's one call against the reference's own four
+    phases run one after the other on the same GPU (input norm + projection, fused append, split attention +
+    reduce at its default split of 20, O projection + norms): raw rows, prepared q and the appended cache rows
+    bit for bit (default norm mode = the reference's arithmetic); attention rows within the bf16 band; the
+    layer outputs, which inherit the attention rows' last-bit differences through a 4096-term sum, within 2^-6
+    of the reference's values (relative to max(|a|, |b|, 1))."""
+    ref = _ref()
+    HQ, H, D, cols, q_width, k_width = 16, 8, 256, 8192, 4096, 2048
+    rng = np.random.default_rng(77)
+    start = np.array([1500], np.int32)
+    acase = helpers.make_append_case(91, start, window=1024, ring_pages=65, max_pos=1502)
+    cfg_t = acase.cfg
+    cfg = kv.make_kv_config(*cfg_t)
+    elems = cfg_t[0] * cfg_t[1] * cfg_t[2] * cfg_t[5] * cfg_t[6]
+    ck = orc.f32_to_bf16(rng.standard_normal(elems, dtype=np.float32))
+    cv = orc.f32_to_bf16(rng.standard_normal(elems, dtype=np.float32))
+    icase, ecase = _ingress_case(801, 1, cols), _egress_case(802, 1, q_width)
+    length = (start + 1).astype(np.int32)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    num_splits = kv.plan_balanced(1, sms)
+    shared = {n: dev(v) for n, v in dict(table=acase.page_table, pos=start, length=length, qw=acase.q_w, kw=acase.k_w,
+                                         cos=acase.cos, sin=acase.sin, x=icase["x"], w_in=icase["w_in"], w=icase["w"],
+                                         w_o=ecase["w_o"], w_post=ecase["w_post"], w_pre=ecase["w_pre"]).items()}
+
+    def fresh():
+        return dict(ck=dev(ck), cv=dev(cv), q=_poison(1, HQ, D), out=_poison(1, HQ, D), raw=_poison(cols),
+                    outs=[_poison(HIDDEN) for _ in range(4)])
+
+    mine, theirs = fresh(), fresh()
+    pm = torch.zeros(HQ * num_splits, dtype=torch.float32, device="cuda")
+    pl, pacc = pm.clone(), torch.zeros(HQ * num_splits * D, dtype=torch.float32, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    ticket = torch.zeros(1, dtype=torch.int32, device="cuda")
+    a = kv.AttentionLayerArgs()
+    s = a.kv
+    s.q, s.out, s.lse = mine["q"].data_ptr(), mine["out"].data_ptr(), None
+    s.partial_m, s.partial_l, s.partial_acc = pm.data_ptr(), pl.data_ptr(), pacc.data_ptr()
+    s.cache_k, s.cache_v, s.cache_config = mine["ck"].data_ptr(), mine["cv"].data_ptr(), cfg
+    s.page_table, s.token_position, s.seq_lengths = (shared["table"].data_ptr(), shared["pos"].data_ptr(),
+                                                     shared["length"].data_ptr())
+    s.cache_layer, s.split_size, s.num_splits, s.softmax_scale = 0, 0, num_splits, 1.0 / 16.0
+    s.q_norm_weight, s.k_norm_weight, s.cos, s.sin = (shared["qw"].data_ptr(), shared["kw"].data_ptr(),
+                                                     shared["cos"].data_ptr(), shared["sin"].data_ptr())
+    s.batch_count, s.q_heads, s.rotary_dim, s.norm_mode, s.status = 1, HQ, D, kv.NORM_RSQRT_APPROX, status.data_ptr()
+    a.attention_x, a.attention_input_norm_weight = shared["x"].data_ptr(), shared["w_in"].data_ptr()
+    a.attention_qkv_proj_col_major, a.attention_o_proj_col_major = shared["w"].data_ptr(), shared["w_o"].data_ptr()
+    a.attention_post_norm_weight, a.attention_pre_ffn_norm_weight = shared["w_post"].data_ptr(), shared["w_pre"].data_ptr()
+    a.raw_qkv = mine["raw"].data_ptr()
+    a.residual_out, a.normed_out, a.ffn_residual, a.ffn_x = (t.data_ptr() for t in mine["outs"])
+    a.ticket, a.hidden_size, a.has_v_projection = ticket.data_ptr(), HIDDEN, 1
+    kv.decode_attention_layer(a)
+    torch.cuda.synchronize()
+    assert status[0].item() == 0
+
+    scratch = _poison(HIDDEN)
+    assert ref.decode_ingress(theirs["raw"], scratch, shared["x"], shared["w_in"], shared["w"], False) == 0
+    raw = theirs["raw"]
+    assert ref.decode_append(theirs["q"], theirs["ck"], theirs["cv"], cfg_t, shared["table"], shared["pos"], 0,
+                             raw[:q_width], raw[q_width:q_width + k_width], raw[q_width + k_width:], shared["qw"],
+                             shared["kw"], shared["cos"], shared["sin"], 1) == 0
+    splits = -(-1024 // 20)
+    rpm = torch.zeros(HQ * splits, dtype=torch.float32, device="cuda")
+    rpl, rpacc = rpm.clone(), torch.zeros(HQ * splits * D, dtype=torch.float32, device="cuda")
+    assert ref.decode_attention(theirs["out"], rpm, rpl, rpacc, theirs["q"], theirs["ck"], theirs["cv"],
+                                shared["table"], shared["length"], cfg_t, 0, 1.0 / 16.0, 20, splits, 1) == 0
+    assert ref.decode_egress(*theirs["outs"], theirs["out"].view(-1), shared["w_o"], shared["w_post"],
+                             shared["w_pre"], shared["x"], False) == 0
+    torch.cuda.synchronize()
+
+    assert torch.equal(mine["raw"], theirs["raw"])
+    assert torch.equal(mine["q"], theirs["q"])
+    assert torch.equal(mine["ck"], theirs["ck"]) and torch.equal(mine["cv"], theirs["cv"])
+    max_abs, max_rel = attention_error(host_u16(mine["out"]), orc.bf16_to_f32(host_u16(theirs["out"])))
+    assert max_abs <= ATTN_MAX_ABS and max_rel <= ATTN_MAX_REL, (max_abs, max_rel)
+    for name, m, t in zip(("residual_out", "normed_out", "ffn_residual", "ffn_x"), mine["outs"], theirs["outs"]):
+        x, y = orc.bf16_to_f32(host_u16(m)).astype(np.float64), orc.bf16_to_f32(host_u16(t)).astype(np.float64)
+        rel = np.abs(x - y) / np.maximum(np.maximum(np.abs(x), np.abs(y)), 1.0)
+        assert rel.max() <= 2.0 ** -6, (name, rel.max())
