@@ -202,6 +202,11 @@ _SIGNATURES = {
     "b200kv_peer_allgather": (c_int, [_P, _P, c_int64, _P, _P, POINTER(_P)]),
     "b200kv_peer_merge_attention": (c_int, [_P, _P, _P, _P, _P, c_int32, c_int32, _P, _P]),
     "b200kv_peer_buffer_destroy": (c_int, [_P]),
+    "b200kv_peer_buffer_set_wait_clocks": (c_int, [_P, c_int64]),
+    "b200kv_peer_buffer_reset": (c_int, [_P]),
+    "b200kv_peer_buffer_create_loopback": (c_int, [c_int64, c_int32, c_int32, POINTER(_P)]),
+    "b200kv_peer_buffer_post": (c_int, [_P, c_int32, ctypes.c_uint32, _P]),
+    "b200kv_bounded_wait_selftest": (c_int, [c_int64, _P, _P, _P]),
     "b200kv_timer_create": (c_int, [POINTER(_P)]),
     "b200kv_timer_destroy": (c_int, [_P]),
     "b200kv_timer_record": (c_int, [_P, _P]),
@@ -534,13 +539,29 @@ class PeerBuffer:
     """This rank's side of the peer-memory all-gather (b200kv_peer_*): `export` is the 64 bytes the other
     ranks need; connect() takes all ranks' exports in rank order (bytes of length 64 * world)."""
 
-    def __init__(self, slot_bytes: int, world: int, rank: int):
+    def __init__(self, slot_bytes: int, world: int, rank: int, loopback: bool = False):
         self.world, self.rank, self.slot_bytes = world, rank, slot_bytes
         self._handle = c_void_p()
+        if loopback:       # one-GPU stand-in: the peers are local buffers nobody writes (b200kv_peer_buffer_post)
+            _check(load_library().b200kv_peer_buffer_create_loopback(slot_bytes, world, rank, ctypes.byref(self._handle)),
+                   "b200kv_peer_buffer_create_loopback", True)
+            self.export = b""
+            return
         buf = ctypes.create_string_buffer(64)
         _check(load_library().b200kv_peer_buffer_create(slot_bytes, world, rank, ctypes.byref(self._handle), buf),
                "b200kv_peer_buffer_create", True)
         self.export = bytes(buf.raw)
+
+    def set_wait_clocks(self, clocks: int):
+        _check(load_library().b200kv_peer_buffer_set_wait_clocks(self._handle, clocks),
+               "b200kv_peer_buffer_set_wait_clocks", True)
+
+    def post(self, from_rank: int, epoch: int, stream=None):
+        _check(load_library().b200kv_peer_buffer_post(self._handle, from_rank, epoch, _stream(stream)),
+               "b200kv_peer_buffer_post", True)
+
+    def reset(self):
+        _check(load_library().b200kv_peer_buffer_reset(self._handle), "b200kv_peer_buffer_reset", True)
 
     def connect(self, exports: bytes):
         assert len(exports) == 64 * self.world
@@ -564,6 +585,11 @@ class PeerBuffer:
         if self._handle:
             load_library().b200kv_peer_buffer_destroy(self._handle)
             self._handle = c_void_p()
+
+
+def bounded_wait_selftest(clock_limit: int, status, waited_clocks=None, stream=None, check: bool = True) -> int:
+    code = load_library().b200kv_bounded_wait_selftest(clock_limit, _ptr(status), _ptr(waited_clocks), _stream(stream))
+    return _check(code, "b200kv_bounded_wait_selftest", check)
 
 
 class Timer:

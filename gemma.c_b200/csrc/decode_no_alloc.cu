@@ -44,7 +44,8 @@ float *g_device_address[kMaxDevices] = {};
 
 // Device address of the array on the current device. The first call on a
 // device asks the runtime for it (which may load the module); later calls
-// read the cached pointer.
+// read the cached pointer. The pointer belongs to the device's primary
+// context and is not refreshed: it does not survive cudaDeviceReset.
 cudaError_t static_scratch_address(float **out) {
   int device = -1;
   cudaError_t st = cudaGetDevice(&device);

@@ -175,7 +175,6 @@ cudaError_t gemma4_runtime_state_init_geometry(
 
   *state = Gemma4RuntimeState();
   Gemma4RuntimeState &s = *state;
-  s.geometry = g;
   s.batch_size = batch_size;
   s.max_seq_len = max_seq_len;
   s.page_size = page_size;
@@ -331,8 +330,11 @@ cudaError_t gemma4_runtime_prepare_decode_step(Gemma4RuntimeState *state,
 // extern "C" boundary
 // ===========================================================================
 
+// The C handle: the reference-layout state plus the geometry it was created
+// with (kept here, outside the struct gemma.c code shares with the library).
 struct B200KvRuntimeState {
   Gemma4RuntimeState state;
+  B200KvRuntimeGeometry geometry;
 };
 
 // ===========================================================================
@@ -613,9 +615,9 @@ int b200kv_runtime_state_create(B200KvRuntimeState **out, int32_t batch_size,
   *out = nullptr;
   B200KvRuntimeState *handle = new (std::nothrow) B200KvRuntimeState();
   if (handle == nullptr) return cudaErrorMemoryAllocation;
+  handle->geometry = geometry != nullptr ? *geometry : default_geometry();
   const cudaError_t st = gemma4_runtime_state_init_geometry(
-      &handle->state, batch_size, max_seq_len, page_size,
-      geometry != nullptr ? *geometry : default_geometry(),
+      &handle->state, batch_size, max_seq_len, page_size, handle->geometry,
       static_cast<cudaStream_t>(stream));
   if (st != cudaSuccess) {
     delete handle;
@@ -1173,6 +1175,33 @@ int b200kv_peer_merge_attention(void *handle, b200kv_bf16 *merged_out,
 
 int b200kv_peer_buffer_destroy(void *handle) {
   return b200kv::peer_buffer_destroy(handle);
+}
+
+int b200kv_peer_buffer_create_loopback(int64_t slot_bytes, int32_t world,
+                                       int32_t rank, void **handle) {
+  if (handle == nullptr) return cudaErrorInvalidValue;
+  return b200kv::peer_buffer_create_loopback(slot_bytes, world, rank, handle);
+}
+
+int b200kv_peer_buffer_set_wait_clocks(void *handle, int64_t clocks) {
+  return b200kv::peer_buffer_set_wait_clocks(handle, clocks);
+}
+
+int b200kv_peer_buffer_post(void *handle, int32_t from_rank, uint32_t epoch,
+                            b200kv_stream stream) {
+  return b200kv::peer_buffer_post(handle, from_rank, epoch,
+                                  static_cast<cudaStream_t>(stream));
+}
+
+int b200kv_peer_buffer_reset(void *handle) {
+  return b200kv::peer_buffer_reset(handle);
+}
+
+int b200kv_bounded_wait_selftest(int64_t clock_limit, int32_t *d_status,
+                                 int64_t *d_waited_clocks, b200kv_stream stream) {
+  return b200kv::bounded_wait_selftest(
+      clock_limit, d_status, reinterpret_cast<long long *>(d_waited_clocks),
+      static_cast<cudaStream_t>(stream));
 }
 
 int b200kv_timer_create(void **event) {

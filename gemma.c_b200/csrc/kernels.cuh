@@ -158,6 +158,19 @@ cudaError_t peer_merge_attention(void *handle, __nv_bfloat16 *merged_out,
                                  const float *lse, int32_t rows, int32_t head_dim,
                                  int32_t *status, cudaStream_t stream);
 cudaError_t peer_buffer_destroy(void *handle);
+// One-GPU stand-in (every peer's buffer is a local allocation nobody writes),
+// the wait limit of later calls, a flag posted from the host in a peer's name,
+// and the re-synchronisation after a rank missed a call (peer_gather.cu).
+cudaError_t peer_buffer_create_loopback(int64_t slot_bytes, int world, int rank,
+                                        void **handle);
+cudaError_t peer_buffer_set_wait_clocks(void *handle, long long clocks);
+cudaError_t peer_buffer_post(void *handle, int from_rank, uint32_t epoch,
+                             cudaStream_t stream);
+cudaError_t peer_buffer_reset(void *handle);
+// One warp waits on an mbarrier that nothing arrives at, with the bounded wait
+// every kernel of the library uses, for `clock_limit` SM clocks (bounded_wait.cu).
+cudaError_t bounded_wait_selftest(long long clock_limit, int32_t *status,
+                                  long long *waited_clocks, cudaStream_t stream);
 
 struct PrefillPrepArgs {
   __nv_bfloat16 *q_prepared = nullptr;

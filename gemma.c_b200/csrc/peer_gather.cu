@@ -48,6 +48,7 @@ struct PeerGatherParams {
   int32_t rank;
   int32_t world;
   int32_t *status;
+  long long wait_clocks;       // how long a thread waits for its peer's flag
   // optional second segment of 4-byte words, stored behind the packs
   const uint32_t *src_words;
   int32_t words;
@@ -98,7 +99,7 @@ __global__ void __launch_bounds__(kGatherThreads) peer_allgather_kernel(
     const uint32_t *mine = p.flags[p.rank] + half + r;
     const long long start = clock64();
     while (int32_t(load_acquire_sys(mine) - e) < 0) {
-      if (clock64() - start > kWaitClockLimit) {
+      if (clock64() - start > p.wait_clocks) {
         set_status(p.status, B200KV_STATUS_WAIT_TIMEOUT);
         break;
       }
@@ -162,7 +163,9 @@ struct PeerBuffer {
   unsigned char *base = nullptr;          // own allocation
   unsigned char *peer[kMaxPeers] = {};    // mapped bases (peer[rank] == base)
   bool connected = false;
+  bool loopback = false;                  // peers are local allocations (one-GPU stand-in)
   uint32_t calls = 0;                     // host mirror of the device epoch
+  long long wait_clocks = kWaitClockLimit;
 };
 
 int64_t data_bytes(const PeerBuffer &b) { return 2 * int64_t(b.world) * b.slot_bytes; }
@@ -234,6 +237,7 @@ cudaError_t launch_gather(PeerBuffer *b, PeerGatherParams p, const void *src,
   p.rank = b->rank;
   p.world = b->world;
   p.status = status;
+  p.wait_clocks = b->wait_clocks;
   const cudaError_t st = launch_pdl(peer_allgather_kernel, dim3(1),
                                     dim3(kGatherThreads), 0, stream, p);
   if (st != cudaSuccess) return st;
@@ -281,13 +285,70 @@ cudaError_t peer_merge_attention(void *handle, __nv_bfloat16 *merged_out,
   return launch_gather(b, p, out, bytes, status, stream, nullptr);
 }
 
+cudaError_t peer_buffer_create_loopback(int64_t slot_bytes, int world, int rank,
+                                        void **handle) {
+  unsigned char unused[64];
+  const cudaError_t st = peer_buffer_create(slot_bytes, world, rank, handle, unused);
+  if (st != cudaSuccess) return st;
+  PeerBuffer *b = static_cast<PeerBuffer *>(*handle);
+  b->loopback = true;
+  for (int r = 0; r < world; ++r) {
+    if (r == rank) continue;
+    cudaError_t e = cudaMalloc(&b->peer[r], size_t(total_bytes(*b)));
+    if (e == cudaSuccess) e = cudaMemset(b->peer[r], 0, size_t(total_bytes(*b)));
+    if (e != cudaSuccess) {
+      peer_buffer_destroy(b);
+      *handle = nullptr;
+      return e;
+    }
+  }
+  b->connected = true;
+  return cudaDeviceSynchronize();
+}
+
+cudaError_t peer_buffer_set_wait_clocks(void *handle, long long clocks) {
+  PeerBuffer *b = static_cast<PeerBuffer *>(handle);
+  if (b == nullptr || clocks <= 0) return cudaErrorInvalidValue;
+  b->wait_clocks = clocks;
+  return cudaSuccess;
+}
+
+cudaError_t peer_buffer_post(void *handle, int from_rank, uint32_t epoch,
+                             cudaStream_t stream) {
+  PeerBuffer *b = static_cast<PeerBuffer *>(handle);
+  if (b == nullptr || from_rank < 0 || from_rank >= b->world) {
+    return cudaErrorInvalidValue;
+  }
+  uint32_t *flags = reinterpret_cast<uint32_t *>(b->base + flag_offset(*b));
+  for (int half = 0; half < 2; ++half) {
+    const cudaError_t st =
+        cudaMemcpyAsync(flags + half * b->world + from_rank, &epoch, sizeof(epoch),
+                        cudaMemcpyHostToDevice, stream);
+    if (st != cudaSuccess) return st;
+  }
+  return cudaStreamSynchronize(stream);  // `epoch` is a stack variable
+}
+
+cudaError_t peer_buffer_reset(void *handle) {
+  PeerBuffer *b = static_cast<PeerBuffer *>(handle);
+  if (b == nullptr) return cudaErrorInvalidValue;
+  cudaError_t st = cudaDeviceSynchronize();
+  if (st == cudaSuccess) {
+    st = cudaMemset(b->base + flag_offset(*b), 0, 256);  // flags and the epoch
+  }
+  if (st == cudaSuccess) st = cudaDeviceSynchronize();
+  if (st == cudaSuccess) b->calls = 0;
+  return st;
+}
+
 cudaError_t peer_buffer_destroy(void *handle) {
   PeerBuffer *b = static_cast<PeerBuffer *>(handle);
   if (b == nullptr) return cudaSuccess;
   cudaError_t first = cudaSuccess;
   for (int r = 0; r < b->world; ++r) {
     if (r != b->rank && b->peer[r] != nullptr) {
-      const cudaError_t st = cudaIpcCloseMemHandle(b->peer[r]);
+      const cudaError_t st = b->loopback ? cudaFree(b->peer[r])
+                                         : cudaIpcCloseMemHandle(b->peer[r]);
       if (first == cudaSuccess) first = st;
     }
   }

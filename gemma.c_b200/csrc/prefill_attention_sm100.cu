@@ -251,7 +251,11 @@ struct Barriers {
   // at tile it (it waits for V as well), and a single barrier would then be two
   // phases ahead of its reader.
   uint64_t p_full[2];
-  uint64_t pv_done;     // P V done: S[b] (the weights) and the V tile are free, O is stable
+  // P V of the tile in S[b] done: S[b] (the weights) and the V tile are free, O is
+  // stable. One barrier per buffer, like p_full: each then completes once per
+  // two tiles, so a waiter that has seen tile t - 2 (same buffer) complete is
+  // exactly one phase behind tile t and a parity wait cannot alias.
+  uint64_t pv_done[2];
 };
 
 struct SmallState {
@@ -308,7 +312,7 @@ __global__ __launch_bounds__(kThreads, 1) void prefill_attention_sm100_kernel(
   const uint32_t bar_v_full = smem_u32(&s_bars.v_full);
   const uint32_t bar_s_full = smem_u32(&s_bars.s_full[0]);    // + 8 b
   const uint32_t bar_p_full = smem_u32(&s_bars.p_full[0]);    // + 8 b
-  const uint32_t bar_pv_done = smem_u32(&s_bars.pv_done);
+  const uint32_t bar_pv_done = smem_u32(&s_bars.pv_done[0]);  // + 8 b
   if (tid == 0) {
     mbar_init(bar_q_full, 1);
     mbar_init(bar_k_full, 1);
@@ -318,6 +322,7 @@ __global__ __launch_bounds__(kThreads, 1) void prefill_attention_sm100_kernel(
     mbar_init(bar_p_full, kSoftmaxWarps);
     mbar_init(bar_p_full + 8, kSoftmaxWarps);
     mbar_init(bar_pv_done, 1);
+    mbar_init(bar_pv_done + 8, 1);
     small.abort = 0;
     mbar_fence_init();
   }
@@ -392,7 +397,10 @@ __global__ __launch_bounds__(kThreads, 1) void prefill_attention_sm100_kernel(
     if (lane == 0) {
       int issued = 0;
       for (int it = 0; it < tiles; ++it) {
-        if (it > 0 && !wait(bar_pv_done, uint32_t(it - 1) & 1u, 3)) break;
+        if (it > 0 && !wait(bar_pv_done + 8u * uint32_t((it - 1) & 1),
+                            uint32_t((it - 1) >> 1) & 1u, 3)) {
+          break;
+        }
         mbar_arrive_expect_tx(bar_v_full, T::kVBytes);
 #pragma unroll
         for (int blk = 0; blk < kDv / 64; ++blk) {
@@ -438,7 +446,7 @@ __global__ __launch_bounds__(kThreads, 1) void prefill_attention_sm100_kernel(
                            umma_desc(s_v + uint32_t(j) * 2048u, T::kKBlockBytes >> 4, 64),
                            kIdescPV, accumulate || j > 0);
         }
-        umma_commit(bar_pv_done);
+        umma_commit(bar_pv_done + 8u * uint32_t(buf));
       };
       bool ok = wait(bar_q_full, 0, 4) && wait(bar_k_full, 0, 4);
       if (ok) {
@@ -451,7 +459,9 @@ __global__ __launch_bounds__(kThreads, 1) void prefill_attention_sm100_kernel(
           // the weights of tile it - 1, is no longer read
           const int n = it + 1;
           ok = wait(bar_k_full, uint32_t(n) & 1u, 4);
-          if (ok && n >= 2) ok = wait(bar_pv_done, uint32_t(n - 2) & 1u, 4);
+          if (ok && n >= 2) {
+            ok = wait(bar_pv_done + 8u * uint32_t(n & 1), uint32_t((n - 2) >> 1) & 1u, 4);
+          }
           if (!ok) break;
           tc_fence_after();
           issue_qk(n & 1);
@@ -474,6 +484,12 @@ __global__ __launch_bounds__(kThreads, 1) void prefill_attention_sm100_kernel(
     float m_ref = -INFINITY;  // the maximum this row's weights are scaled by
     float l_run = 0.0f;       // this thread's quarter of the row's denominator
     bool ok = true;
+    // The four warps that share 32 rows meet at a named barrier once per tile and
+    // once at the end. Each decides for itself when to give up a wait, so one may
+    // leave the loop while a sibling still passes the same wait; a warp that has
+    // given up therefore makes up the arrivals it skipped (below), and no sibling
+    // is left alone at the barrier on its way to the common exit.
+    int row_syncs = 0;
     for (int it = 0; it < tiles; ++it) {
       const int tile = tile_lo + it;
       const int buf = it & 1;
@@ -510,6 +526,7 @@ __global__ __launch_bounds__(kThreads, 1) void prefill_attention_sm100_kernel(
           __float2bfloat16_rn(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale);
       s_max[buf][quarter][row_in] = m_mine;
       named_barrier_sync(row_barrier, 128);
+      ++row_syncs;
       const float m_tile = fmaxf(fmaxf(__bfloat162float(s_max[buf][0][row_in]),
                                        __bfloat162float(s_max[buf][1][row_in])),
                                  fmaxf(__bfloat162float(s_max[buf][2][row_in]),
@@ -539,7 +556,7 @@ __global__ __launch_bounds__(kThreads, 1) void prefill_attention_sm100_kernel(
       // the columns of O if any of its rows must, once P V of the previous tile
       // no longer adds to them
       if (it > 0 && __any_sync(0xffffffffu, factor != 1.0f)) {
-        ok = wait(bar_pv_done, uint32_t(it - 1) & 1u, 2);
+        ok = wait(bar_pv_done + 8u * uint32_t((it - 1) & 1), uint32_t((it - 1) >> 1) & 1u, 2);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
@@ -561,19 +578,17 @@ __global__ __launch_bounds__(kThreads, 1) void prefill_attention_sm100_kernel(
     }
 
     // ---- the last P V, then O / l as bf16
-    // A parity wait cannot tell phase t from phase t - 2. The last thing this
-    // warp knows about the P V barrier is that tile tiles - 3 is done (the
-    // scores of the last tile were issued after it); P V of tile tiles - 2 may
-    // still be running, and a wait for the parity of tile tiles - 1 alone would
-    // then pass at once -- with the last two P V unfinished, O incomplete and
-    // the V tile, where the row sums go, about to be refilled. So: one phase
-    // at a time.
+    // P V of the last two tiles may both still be running: wait for each on its
+    // own buffer's barrier. The warp has seen tile tiles - 3 complete (the last
+    // tile's scores were issued after it) and P V products complete in order, so
+    // on either barrier the awaited phase is the one right after a phase the
+    // warp knows to be complete.
     if (ok && tiles >= 2) {
-      ok = wait(bar_pv_done, uint32_t(tiles - 2) & 1u, 5);
+      ok = wait(bar_pv_done + 8u * uint32_t((tiles - 2) & 1), uint32_t((tiles - 2) >> 1) & 1u, 5);
       ok = __all_sync(0xffffffffu, ok);
     }
     if (ok) {
-      ok = wait(bar_pv_done, uint32_t(tiles - 1) & 1u, 5);
+      ok = wait(bar_pv_done + 8u * uint32_t((tiles - 1) & 1), uint32_t((tiles - 1) >> 1) & 1u, 5);
       ok = __all_sync(0xffffffffu, ok);
     }
     if (ok) {
@@ -583,6 +598,7 @@ __global__ __launch_bounds__(kThreads, 1) void prefill_attention_sm100_kernel(
       float *row_sum = reinterpret_cast<float *>(smem_raw + T::kQBytes + T::kKBytes);
       row_sum[quarter * kBlockM + row_in] = l_run;
       named_barrier_sync(row_barrier, 128);
+      ++row_syncs;
       const float l_row = (row_sum[row_in] + row_sum[kBlockM + row_in]) +
                           (row_sum[2 * kBlockM + row_in] + row_sum[3 * kBlockM + row_in]);
       const float inv = l_row > 0.0f ? 1.0f / l_row : 0.0f;
@@ -609,6 +625,8 @@ __global__ __launch_bounds__(kThreads, 1) void prefill_attention_sm100_kernel(
         }
       }
     }
+    // gave up somewhere above (ok is warp-uniform): the arrivals still owed
+    for (; row_syncs < tiles + 1; ++row_syncs) named_barrier_sync(row_barrier, 128);
   }
   tc_fence_before();
   __syncthreads();

@@ -401,11 +401,18 @@ enum {
  * no cudaMalloc, cudaFree or other allocating call.
  *   - Refused with cudaErrorInvalidValue (and a line on stderr) when
  *     2 * round_up(batch*q_heads*num_splits, 64) * 4
- *       + batch*q_heads*num_splits*head_dim*4 bytes exceed that size;
- *     num_splits == 1 needs no scratch and is always accepted.
+ *       + batch*q_heads*num_splits*head_dim*4 bytes exceed that size.
+ *     With fixed splits (split_size > 0) num_splits == 1 needs no scratch and
+ *     is never refused for size; the balanced partition (split_size == 0)
+ *     always works through scratch, so it needs num_splits >= 2 (take it from
+ *     b200kv_plan_balanced) and returns cudaErrorInvalidValue for 1.
  *   - The first call on each device looks the array's device address up
- *     (cudaGetSymbolAddress, with that device current); make that first call
- *     before any stream capture begins.
+ *     (cudaGetSymbolAddress, with that device current) and keeps it for the
+ *     life of the process; make that first call before any stream capture
+ *     begins. The kept address belongs to the device's primary context: after
+ *     cudaDeviceReset (or anything else that destroys that context) it is
+ *     stale, so a process that resets a device must not call this entry point
+ *     on it afterwards.
  *   - All calls on a device share the array and it keeps the last call's
  *     contents. Nothing needs clearing between calls, but calls whose kernels
  *     may overlap on the GPU race on it: keep them on one stream.
@@ -636,6 +643,38 @@ int b200kv_peer_merge_attention(void *handle, b200kv_bf16 *merged_out,
                                 const float *lse, int32_t rows, int32_t head_dim,
                                 int32_t *status, b200kv_stream stream);
 int b200kv_peer_buffer_destroy(void *handle);
+
+/* Failure handling of the exchange. No counterpart in the reference.
+ * b200kv_peer_buffer_set_wait_clocks: how many SM clocks later calls wait for a
+ * peer's flag before they give up with B200KV_STATUS_WAIT_TIMEOUT (default
+ * 2^31, about a second).
+ * After a call timed out (a peer died, hung, or skipped a call) the ranks'
+ * call counters no longer agree and later gathers would pair the wrong buffer
+ * halves. b200kv_peer_buffer_reset brings a rank back to "no call made yet"
+ * (synchronises the device, clears its flags and counter): every surviving
+ * rank calls it, with a host-side barrier before and after, and the next
+ * matched call gathers correctly again.
+ * b200kv_peer_buffer_create_loopback / b200kv_peer_buffer_post are a one-GPU
+ * stand-in for bring-up and tests: the other ranks' buffers are local
+ * allocations that nobody writes, and _post stores `epoch` into this rank's
+ * flags (both halves) in the name of rank `from_rank`, as that rank's kernel
+ * would -- so a wait can be seen to run out (nothing posted) and to succeed
+ * (posted) without a second GPU. */
+int b200kv_peer_buffer_set_wait_clocks(void *handle, int64_t clocks);
+int b200kv_peer_buffer_reset(void *handle);
+int b200kv_peer_buffer_create_loopback(int64_t slot_bytes, int32_t world,
+                                       int32_t rank, void **handle);
+int b200kv_peer_buffer_post(void *handle, int32_t from_rank, uint32_t epoch,
+                            b200kv_stream stream);
+
+/* Self-test of the bounded wait all kernels of the library share: one warp
+ * waits, with that helper, on an mbarrier nothing arrives at, for clock_limit
+ * SM clocks (1 .. 2^28), then writes B200KV_STATUS_WAIT_TIMEOUT to d_status[0]
+ * (if it is 0) and the clocks it waited to *d_waited_clocks (optional) and
+ * returns normally: the give-up path exercised without a fault. No counterpart
+ * in the reference, whose kernels do not wait on one another. */
+int b200kv_bounded_wait_selftest(int64_t clock_limit, int32_t *d_status,
+                                 int64_t *d_waited_clocks, b200kv_stream stream);
 
 /* Timing events for the hooks above (cudaEventCreate / Destroy / ElapsedTime).
  * No counterpart in the reference library; its benches time with the same

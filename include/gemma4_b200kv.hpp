@@ -1,18 +1,36 @@
 // C++ host interface of libgemma4_b200kv.so, source-compatible with the
 // declarations a gemma.c translation unit gets from
-//   src/gemma4_kv_cache.cuh:9-66   (config, offset, page helpers, cache write)
-//   src/gemma4_runtime.cuh:12-64   (Gemma4RuntimeState and its four functions)
+//   src/gemma4_kv_cache.cuh:9-66        (config, offset, page helpers, cache write)
+//   src/gemma4_runtime.cuh:12-64        (Gemma4RuntimeState and its four functions)
+//   src/gemma4_flash_attention.cuh:9-45 (prompt attention entry points)
 // so that code written against those headers builds against this one and
-// links to the B200 library instead of gemma4_kv_cache.cu / gemma4_runtime.cu.
+// links to the B200 library instead of gemma4_kv_cache.cu / gemma4_runtime.cu /
+// gemma4_flash_attention_prefill.cu. Two ways to use it:
+//   * instead of the reference's headers: include it directly, or put
+//     include/compat (files named like the reference's, forwarding here) ahead
+//     of gemma.c's src/ on the include path;
+//   * on top of them, in a translation unit that already sees gemma.c's own
+//     headers (anything inside gemma.c's src/, e.g. the decode layer loop):
+//     define GEMMA4_B200KV_USE_REFERENCE_HEADERS before including it; the types
+//     and functions then come from the reference's headers and this file only
+//     adds the layout checks and the library's extra entry points.
 #pragma once
 
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <stddef.h>
 #include <stdint.h>
 #include <vector>
 
 #define GEMMA4_KV_CACHE_CONFIG_DEFINED
+#define GEMMA4_B200KV_TYPED_CACHE_WRITE
+#if defined(GEMMA4_B200KV_USE_REFERENCE_HEADERS)
+#include "gemma4_flash_attention.cuh"
+#include "gemma4_kv_cache.cuh"
+#include "gemma4_runtime.cuh"
+#include "gemma4_b200kv.h"
+#else
 struct Gemma4KvCacheConfig {
   int32_t num_layers;
   int32_t num_pages;
@@ -24,7 +42,6 @@ struct Gemma4KvCacheConfig {
   int32_t window_size;
 };
 
-#define GEMMA4_B200KV_TYPED_CACHE_WRITE
 #include "gemma4_b200kv.h"
 
 // src/gemma4_kv_cache.cuh:55-66, same symbol as the C declaration.
@@ -97,9 +114,10 @@ int32_t gemma4_kv_cache_ensure_range(std::vector<int32_t> &page_table,
                                      int32_t batch, int32_t first_position,
                                      int32_t token_count);
 
-// src/gemma4_runtime.cuh:12-42. Member names, types and order are the
-// reference's; `geometry` is appended so one owner can also hold caches of a
-// non-default shape.
+// src/gemma4_runtime.cuh:12-42: the same members, types, order and default
+// initialisers, nothing added, so that an object a gemma.c translation unit
+// built against the reference's header has exactly the size and layout the
+// library writes (static_asserts below).
 struct Gemma4RuntimeState {
   int32_t batch_size = 0;
   int32_t max_seq_len = 0;
@@ -130,15 +148,31 @@ struct Gemma4RuntimeState {
   std::vector<int32_t> h_seq_lengths;
   std::vector<int32_t> h_token_batch;
   std::vector<int32_t> h_token_position;
-
-  B200KvRuntimeGeometry geometry = {};
 };
+
+#endif  // GEMMA4_B200KV_USE_REFERENCE_HEADERS
+
+// The reference's layout on an LP64 host: four int32, two 32-byte configs,
+// thirteen pointers, seven std::vector (three pointers each).
+static_assert(sizeof(Gemma4KvCacheConfig) == 32, "src/gemma4_kv_cache.cuh:9-18");
+static_assert(offsetof(Gemma4RuntimeState, sliding_cache_config) == 16 &&
+                  offsetof(Gemma4RuntimeState, global_cache_config) == 48 &&
+                  offsetof(Gemma4RuntimeState, sliding_cache_k) == 80 &&
+                  offsetof(Gemma4RuntimeState, sliding_page_table) == 112 &&
+                  offsetof(Gemma4RuntimeState, global_sin) == 176 &&
+                  offsetof(Gemma4RuntimeState, h_sliding_page_table) == 184 &&
+                  offsetof(Gemma4RuntimeState, h_token_position) ==
+                      184 + 6 * sizeof(std::vector<int32_t>) &&
+                  sizeof(Gemma4RuntimeState) ==
+                      184 + 7 * sizeof(std::vector<int32_t>),
+              "Gemma4RuntimeState must keep the layout of src/gemma4_runtime.cuh:12-42");
 
 // src/gemma4_runtime.cu:95-234. `state` must be zero-initialised or freed.
 cudaError_t gemma4_runtime_state_init(Gemma4RuntimeState *state,
                                       int32_t batch_size, int32_t max_seq_len,
                                       int32_t page_size, cudaStream_t stream);
-// Same, for caches of another geometry.
+// Same, for caches of another geometry (the state does not record it: the two
+// cache configs carry everything the other functions need).
 cudaError_t gemma4_runtime_state_init_geometry(
     Gemma4RuntimeState *state, int32_t batch_size, int32_t max_seq_len,
     int32_t page_size, const B200KvRuntimeGeometry &geometry,

@@ -15,8 +15,8 @@ CUTLASS="${CUTLASS_INCLUDE:-$(python -c 'import flashinfer, os; print(os.path.jo
 mkdir -p "$OUT"
 STAMP="$OUT/build.stamp"
 KEY="$(cat "$HERE/ref_harness.cu" "$HERE/build_ref.sh" "$REF/gemma4_flash_attention_decode.cu" "$REF/gemma4_flash_attention_prefill.cu" "$REF/gemma4_kv_cache.cu" "$REF/gemma4_rmsnorm.cu" "$REF/gemma4_rope.cu" | sha256sum | cut -d' ' -f1)"
-if [ -f "$OUT/libgemma4_ref.so" ] && [ -f "$STAMP" ] && [ "$(cat "$STAMP")" = "$KEY" ]; then exit 0; fi
 ARCH="-gencode arch=compute_100a,code=sm_100a"
+if ! { [ -f "$OUT/libgemma4_ref.so" ] && [ -f "$STAMP" ] && [ "$(cat "$STAMP")" = "$KEY" ]; }; then
 COMMON="-std=c++17 -O3 $ARCH -rdc=true -Xcompiler -fPIC -I$REF -I$CUTLASS"
 FAST="--expt-relaxed-constexpr --expt-extended-lambda --use_fast_math"
 $NVCC $COMMON $FAST -c "$HERE/ref_harness.cu" -o "$OUT/ref_harness.o"
@@ -28,3 +28,27 @@ $NVCC $COMMON -c "$REF/gemma4_kv_cache.cu" -o "$OUT/gemma4_kv_cache.o"
 $NVCC $ARCH -Xcompiler -fPIC -shared "$OUT/ref_harness.o" "$OUT/gemma4_flash_attention_prefill.o" "$OUT/gemma4_rmsnorm.o" "$OUT/gemma4_rope.o" "$OUT/gemma4_kv_cache.o" -o "$OUT/libgemma4_ref.so"
 echo "$KEY" > "$STAMP"
 echo "built $OUT/libgemma4_ref.so"
+fi
+
+# The drop-in proof: the reference's own test programs, unchanged, compiled against the library's stand-in headers
+# (include/compat ahead of the reference's src/) and linked to libgemma4_b200kv.so -- no reference object in the
+# link -- plus tests/cpp/megakernel_layer.cu, which includes the reference's real gemma4_megakernel.cuh. They run
+# on the GPU (tests/test_gpu_reference_boundary.py). Needs the library built first (gemma.c_b200/build.py).
+REPO="$(cd "$HERE/.." && pwd)"
+LIBDIR="$REPO/gemma.c_b200/_build"
+TESTS="$(cd "$REF/../tests" 2>/dev/null && pwd || true)"
+if [ -f "$LIBDIR/libgemma4_b200kv.so" ] && [ -n "$TESTS" ] && [ -f "$TESTS/test_kv_cache.cu" ]; then
+  TKEY="$(cat "$HERE/build_ref.sh" "$REPO"/include/*.h* "$REPO"/include/compat/*.cuh "$REPO/tests/cpp/megakernel_layer.cu" \
+          "$TESTS/test_kv_cache.cu" "$TESTS/test_runtime_state.cu" "$TESTS/test_flash_attention.cu" \
+          "$REF/gemma4_megakernel.cuh" "$REF/gemma4.h" | sha256sum | cut -d' ' -f1)"
+  TSTAMP="$OUT/boundary.stamp"
+  if ! { [ -f "$OUT/ref_test_kv_cache" ] && [ -f "$OUT/megakernel_layer" ] && [ -f "$TSTAMP" ] && [ "$(cat "$TSTAMP")" = "$TKEY" ]; }; then
+    LINK="-L$LIBDIR -lgemma4_b200kv -Xlinker -rpath -Xlinker \$ORIGIN/../../gemma.c_b200/_build"
+    for t in test_kv_cache test_runtime_state test_flash_attention; do
+      $NVCC -std=c++17 -O2 $ARCH -I"$REPO/include/compat" -I"$REPO/include" -I"$REF" "$TESTS/$t.cu" $LINK -o "$OUT/ref_$t"
+    done
+    $NVCC -std=c++17 -O2 $ARCH -I"$REF" -I"$REPO/include" "$REPO/tests/cpp/megakernel_layer.cu" $LINK -o "$OUT/megakernel_layer"
+    echo "$TKEY" > "$TSTAMP"
+    echo "built $OUT/ref_test_{kv_cache,runtime_state,flash_attention} and $OUT/megakernel_layer"
+  fi
+fi

@@ -1,10 +1,20 @@
 // Compile-and-link check of include/gemma4_b200kv.hpp from a translation unit shaped like the reference's
-// src/gemma4_decode_megakernel.cu: a per-layer argument struct with the member names of
-// Gemma4DecodeMegakernelLayerArgs (src/gemma4_megakernel.cuh:32-66, restated here with the attention half only)
-// is handed to the header's binding template. Run by tests/test_host_api.py; needs no GPU: the arguments are
-// rejected on the host (null pointers / unknown geometry) before anything is launched.
+// src/gemma4_decode_megakernel.cu. With -DB200KV_TEST_WITH_GEMMA_C (and gemma.c's src/ on the include path) the
+// per-layer argument struct is the reference's own Gemma4DecodeMegakernelLayerArgs from its gemma4_megakernel.cuh
+// and the library's header sits on top of the reference's headers; without it, a struct with the same member
+// names (src/gemma4_megakernel.cuh:32-66, the attention half) stands in. Either is handed to the header's binding
+// template. Run by tests/test_host_api.py; needs no GPU: the arguments are rejected on the host (null pointers /
+// unknown geometry) before anything is launched. (tests/cpp/megakernel_layer.cu runs a real layer on the GPU.)
 #include <cstdio>
 
+#ifdef B200KV_TEST_WITH_GEMMA_C
+#include "gemma4_megakernel.cuh"
+#define GEMMA4_B200KV_USE_REFERENCE_HEADERS
+#include "gemma4_b200kv.hpp"
+using LayerArgs = Gemma4DecodeMegakernelLayerArgs;
+// an object laid out by the reference's header, initialised and freed by the library
+static_assert(sizeof(Gemma4RuntimeState) == 184 + 7 * sizeof(std::vector<int32_t>), "layout");
+#else
 #include "gemma4_b200kv.hpp"
 
 struct LayerArgs {
@@ -38,6 +48,7 @@ struct LayerArgs {
   const float *attention_cos = nullptr;
   const float *attention_sin = nullptr;
 };
+#endif
 
 int main() {
   LayerArgs args;

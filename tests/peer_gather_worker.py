@@ -75,6 +75,27 @@ def main():
         assert err <= 2.0 ** -7 * max(1.0, want.abs().max().item()), f"rank {rank} merge {it}: {err}"
         assert (merged_lse.double() - want_lse).abs().max().item() <= 1e-4
     dist.barrier()
+    # A rank misses a call (between steps, nothing of its own in flight): the others' waits run out after the
+    # short limit set here, they report B200KV_STATUS_WAIT_TIMEOUT and return; every rank then resets its buffer
+    # between two host barriers and the next matched call gathers correctly again.
+    torch.cuda.synchronize()
+    buf.set_wait_clocks(1 << 24)
+    src = torch.full((256,), 7000 + rank, dtype=torch.int32, device="cuda")
+    if rank != world - 1:
+        buf.allgather(src, 1024, status=status)
+        torch.cuda.synchronize()
+        assert status[0].item() == kv.STATUS_WAIT_TIMEOUT, f"rank {rank}: expected the wait to run out"
+        status.zero_()
+    dist.barrier()
+    buf.reset()
+    dist.barrier()
+    for it in range(3):
+        src = torch.full((256,), 8000 + 10 * it + rank, dtype=torch.int32, device="cuda")
+        ptr = buf.allgather(src, 1024, status=status)
+        got = read_device(ptr, world * slot // 4, np.int32).reshape(world, slot // 4)[:, :256]
+        assert status[0].item() == 0, f"rank {rank}: wait ran out after the reset"
+        assert all((got[r] == 8000 + 10 * it + r).all() for r in range(world)), f"rank {rank}: rows after reset"
+    dist.barrier()
     mbuf.close()
     buf.close()
     if rank == 0:

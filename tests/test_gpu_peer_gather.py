@@ -70,6 +70,52 @@ def test_gather_argument_checks(kv):
         kv.PeerBuffer(1024, 9, 0)                            # more than 8 ranks
 
 
+def test_wait_for_an_absent_rank_runs_out_and_the_next_call_works(kv):
+    """The give-up path of the exchange, seen to run: a two-rank buffer on one GPU whose rank 1 is a local
+    stand-in that nobody drives. With a short limit (2^22 SM clocks, a few milliseconds) rank 0's call waits for
+    rank 1's flag, gives up, writes B200KV_STATUS_WAIT_TIMEOUT and returns normally; after the flag is posted in
+    rank 1's name the next call finds it, leaves the status at 0 and has copied this rank's rows. Nothing
+    faults, traps or hangs; the same context keeps working."""
+    buf = kv.PeerBuffer(4096, 2, 0, loopback=True)
+    buf.set_wait_clocks(1 << 22)
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    src = torch.arange(1024, dtype=torch.int32, device="cuda")
+    start = torch.cuda.Event(enable_timing=True)
+    end = torch.cuda.Event(enable_timing=True)
+    start.record()
+    buf.allgather(src, 4096, status=status)
+    end.record()
+    torch.cuda.synchronize()
+    assert status[0].item() == kv.STATUS_WAIT_TIMEOUT
+    assert start.elapsed_time(end) < 500.0                    # gave up promptly (the default limit is a second)
+    status.zero_()
+    buf.post(1, 1000)                                          # "rank 1" announces itself for every call to come
+    for it in range(3):
+        src = torch.arange(it, it + 1024, dtype=torch.int32, device="cuda")
+        ptr = buf.allgather(src, 4096, status=status)
+        got = read_device(ptr, 1024, np.int32)                # slot 0 of the gathered buffer = this rank's rows
+        assert np.array_equal(got, src.cpu().numpy())
+    assert status[0].item() == 0
+    # an ordinary one-rank gather on the same device afterwards
+    one = kv.PeerBuffer(4096, 1, 0)
+    ptr = one.allgather(src, 4096, status=status)
+    assert np.array_equal(read_device(ptr, 1024, np.int32), src.cpu().numpy()) and status[0].item() == 0
+    one.close()
+    buf.close()
+
+
+def test_reset_returns_a_buffer_to_its_first_call(kv):
+    buf = kv.PeerBuffer(1024, 1, 0)
+    src = torch.arange(256, dtype=torch.int32, device="cuda")
+    first = buf.allgather(src, 1024)
+    buf.allgather(src, 1024)
+    buf.allgather(src, 1024)
+    buf.reset()
+    assert buf.allgather(src, 1024) == first                  # the half the very first call used
+    assert np.array_equal(read_device(first, 256, np.int32), src.cpu().numpy())
+    buf.close()
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs with peer access")
 def test_two_or_more_ranks_against_nccl():
     world = min(torch.cuda.device_count(), 8)

@@ -184,19 +184,59 @@ def test_projection_and_peer_argument_rejection_needs_no_device(kv):
         kv.PeerBuffer(1024, 9, 0)                                                # more than 8 ranks
 
 
-def test_cpp_header_binds_a_reference_shaped_layer_struct(kv, tmp_path):
-    """include/gemma4_b200kv.hpp from a C++ translation unit: a struct with the member names of the reference's
-    Gemma4DecodeMegakernelLayerArgs goes through the header's binding template and links against the library."""
+def _compile_and_run_binding(kv, tmp_path, extra):
     import shutil
 
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     repo = kv.library_path().parents[2]
     exe = tmp_path / "megakernel_binding"
     lib_dir = kv.library_path().parent
-    build = subprocess.run([nvcc, "-std=c++17", "-I", str(repo / "include"), str(repo / "tests" / "cpp" / "megakernel_binding.cu"),
+    build = subprocess.run([nvcc, "-std=c++17", *extra, "-I", str(repo / "include"),
+                            str(repo / "tests" / "cpp" / "megakernel_binding.cu"),
                             "-L", str(lib_dir), "-lgemma4_b200kv", "-Xlinker", "-rpath", "-Xlinker", str(lib_dir),
                             "-o", str(exe)], capture_output=True, text=True)
     assert build.returncode == 0, build.stdout + build.stderr
     run = subprocess.run([str(exe)], capture_output=True, text=True)
     assert run.returncode == 0, run.stdout + run.stderr
     assert run.stdout.split() == ["1", "1", "0"]
+
+
+def test_cpp_header_binds_a_reference_shaped_layer_struct(kv, tmp_path):
+    """include/gemma4_b200kv.hpp from a C++ translation unit: a struct with the member names of the reference's
+    Gemma4DecodeMegakernelLayerArgs goes through the header's binding template and links against the library."""
+    _compile_and_run_binding(kv, tmp_path, [])
+
+
+def _gemma_c_src():
+    import os
+
+    src = os.environ.get("GEMMA_REF_SRC") or str(Path(__file__).resolve().parents[2] / "reference" / "src")
+    return src if Path(src, "gemma4_megakernel.cuh").is_file() else None
+
+
+@pytest.mark.skipif(_gemma_c_src() is None, reason="gemma.c sources not mounted")
+def test_cpp_header_sits_on_top_of_the_reference_headers(kv, tmp_path):
+    """The same translation unit with the reference's real gemma4_megakernel.cuh (which pulls in its own
+    gemma4_runtime.cuh and gemma4_kv_cache.cuh): the library's header adds its entry points on top without
+    redefining a type, its layout static_asserts hold for the reference's structs, and the reference's
+    Gemma4DecodeMegakernelLayerArgs binds."""
+    _compile_and_run_binding(kv, tmp_path, ["-DB200KV_TEST_WITH_GEMMA_C", "-I", _gemma_c_src()])
+
+
+@pytest.mark.skipif(_gemma_c_src() is None, reason="gemma.c sources not mounted")
+def test_reference_tests_compile_against_the_stand_in_headers(kv, tmp_path):
+    """The reference's own test programs, unchanged, compile against include/compat (ahead of the reference's src/
+    on the include path) and link to the library alone -- every symbol they need is exported with the
+    reference's signature. They run on a GPU in tests/test_gpu_reference_boundary.py."""
+    import shutil
+
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    repo = kv.library_path().parents[2]
+    lib_dir = kv.library_path().parent
+    tests = Path(_gemma_c_src()).parent / "tests"
+    for name in ("test_kv_cache", "test_runtime_state"):
+        build = subprocess.run([nvcc, "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a",
+                                "-I", str(repo / "include" / "compat"), "-I", str(repo / "include"),
+                                "-I", _gemma_c_src(), str(tests / f"{name}.cu"), "-L", str(lib_dir),
+                                "-lgemma4_b200kv", "-o", str(tmp_path / name)], capture_output=True, text=True)
+        assert build.returncode == 0, name + "\n" + build.stdout + build.stderr

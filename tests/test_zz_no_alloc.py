@@ -66,6 +66,25 @@ def test_static_scratch_matches_caller_scratch_on_two_calls_in_a_row(kv, orc):
     _run_both(kv, orc, third, 128, 1)                 # single split: no scratch at all
 
 
+def test_static_scratch_on_the_balanced_partition_and_the_wide_head_geometry(kv, orc):
+    """The library's default partition (split_size 0: key ranges balanced over a fixed grid, one scratch slot
+    per CTA and sequence boundary) and the 16-query-heads-on-one-KV-head-of-512 geometry through the shared
+    array, each twice in a row and interleaved, against the caller-scratch entry point and the oracle. With
+    split_size 0 a single split is refused: that partition always needs its scratch."""
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    ragged = make_attn_case(505, [3000, 17, 1500, 260], window=0)
+    wide = make_attn_case(506, [2100, 40], window=0, kv_heads=1, q_heads=16, head_dim=512)
+    ring = make_attn_case(507, [1500], window=1024)
+    for case in (ragged, wide, ragged, wide, ring, ring):
+        _run_both(kv, orc, case, 0, kv.plan_balanced(case.batch, sms))
+    cfg = kv.make_kv_config(*ring.cfg)
+    out = torch.zeros((1, 16, 256), dtype=torch.int16, device="cuda")
+    code = kv.decode_attention_static_scratch(out, None, dev(ring.q), dev(ring.cache_k), dev(ring.cache_v), cfg,
+                                              dev(ring.page_table), dev(ring.seq_lengths), 0, ring.scale, 0, 1, 1, 16,
+                                              check=False)
+    assert code == kv.CUDA_ERROR_INVALID_VALUE
+
+
 def test_static_scratch_refuses_what_does_not_fit(kv, capfd):
     case = make_attn_case(504, [64], window=0)
     cfg = kv.make_kv_config(*case.cfg)
