@@ -10,9 +10,11 @@ combine. Sequences are sharded over ranks (greedy longest-first on context lengt
 on the data path.
 
     python bench.py --gpus N --steps K --warmup W            # this library (CUDA, through the C-ABI)
-    python bench.py --impl reference --gpus N ...            # CPU restatement of the reference, all cores
+    python bench.py --impl reference --gpus N ...            # the reference's own CUDA kernels (oracle/_ref) on one GPU
 
-Prints one JSON line (rank 0).
+Prints one JSON line (rank 0). The default line also carries: `verified` (the last timed step's outputs checked
+against the oracle, outside the timed region; a miss makes the run exit 3), `other_workloads` (short runs of the
+other BASELINE configs in the same process), `reference_cuda`, `cpu_baseline` (all cores) and `cpu_baseline_1t`.
 """
 from __future__ import annotations
 
@@ -38,7 +40,7 @@ E_KV = 2  # bytes per cached element (bf16)
 METRIC = "KV append + decode attention: achieved HBM GB/s (us per layer-step alongside)"
 
 
-def parse_args():
+def parse_args(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
@@ -75,7 +77,15 @@ def parse_args():
     ap.add_argument("--emulate-world", type=int, default=0,
                     help="tuning aid: on one GPU, run the shard that rank --emulate-rank of this many ranks would own")
     ap.add_argument("--emulate-rank", type=int, default=0)
-    return ap.parse_args()
+    ap.add_argument("--cache", default="warm", choices=["warm", "cold", "both"],
+                    help="cold / both: after the timed steps, time more steps one by one with an L2 flush (a write "
+                         "over 512 MiB) before each and the events recorded after the flush; reported as `cold_cache`")
+    ap.add_argument("--no-verify", action="store_true",
+                    help="skip the oracle check of the last timed step's outputs (`verified`)")
+    ap.add_argument("--no-other-workloads", action="store_true",
+                    help="default workload only: do not add the short runs of the other BASELINE configs")
+    ap.add_argument("--other-steps", type=int, default=100, help="timed steps of each of those short runs")
+    return ap.parse_args(argv)
 
 
 # --------------------------------------------------------------------------- workload description
@@ -645,12 +655,366 @@ def reference_cuda_numbers(wl, torch, step_index: int):
     return result
 
 
+# --------------------------------------------------------------------------- parity of what was just run
+# Tolerances of the GPU tests (tests/helpers.py): attention rows against double precision on the same cache,
+# max_abs and max_rel with the reference bench's denominator max(|a|, |b|, 1)
+# (src/benches/gemma4_bench_utils.cuh:450-472); natural-log log-sum-exp.
+VERIFY_MAX_ABS, VERIFY_MAX_REL, VERIFY_LSE = 2.0 ** -6, 2.0 ** -6, 1.0e-3
+
+
+def sample_sequences(ctx: np.ndarray, count: int, seed: int) -> list[int]:
+    """The longest, the shortest and seeded random other sequences of a batch (at most `count`, no repeats)."""
+    order = np.argsort(ctx, kind="stable")
+    picks = []
+    for b in [int(order[-1]), int(order[0]), *np.random.default_rng(seed).permutation(ctx.size).tolist()]:
+        if b not in picks and len(picks) < count:
+            picks.append(int(b))
+    return picks
+
+
+def _bits(t):
+    """Device bf16 / int16 tensor -> host uint16 bit patterns."""
+    import torch
+
+    return t.detach().contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def compact_layer_cache(wl, i: int, seqs: list[int]):
+    """The pages of layer i's cache that the sequences `seqs` map, gathered (on the device) into a small cache
+    of their own with a page table to match: what a CPU checker needs of a pool of many GB. Returns device
+    tensors and the config tuple of the small cache; every page keeps its bytes, fp8 scales ride along."""
+    torch = wl.torch
+    g = wl.layer_is_global(i)
+    cfg = (wl.g_cfg if g else wl.l_cfg).astuple()
+    layers, pages, ps, mpps, _, heads, dim, window = cfg
+    li = wl.cache_layer_of(i)
+    table = (wl.g_table if g else wl.l_table)[torch.tensor(seqs, device="cuda")]
+    valid = (table >= 0) & (table < pages)
+    phys = table[valid].long()
+    small_table = torch.full_like(table, -1)
+    small_table[valid] = torch.arange(phys.numel(), dtype=table.dtype, device="cuda")
+    k, v = (wl.g_k, wl.g_v) if g else (wl.l_k, wl.l_v)
+    page_elems = ps * heads * dim
+    out = {"ck": k.view(layers, pages, page_elems)[li].index_select(0, phys).contiguous(),
+           "cv": v.view(layers, pages, page_elems)[li].index_select(0, phys).contiguous(),
+           "table": small_table.contiguous(),
+           "cfg": (1, int(phys.numel()), ps, mpps, len(seqs), heads, dim, window)}
+    if wl.spec.fp8:
+        out["sk"] = wl.g_sk.view(layers, pages, heads)[li].index_select(0, phys).contiguous()
+        out["sv"] = wl.g_sv.view(layers, pages, heads)[li].index_select(0, phys).contiguous()
+    return out
+
+
+def attention_errors(got_bits: np.ndarray, ref: np.ndarray, orc):
+    a = orc.bf16_to_f32(got_bits).astype(np.float64).reshape(-1)
+    b = ref.astype(np.float64).reshape(-1)
+    diff = np.abs(a - b)
+    return float(diff.max(initial=0.0)), float((diff / np.maximum(np.maximum(np.abs(a), np.abs(b)), 1.0)).max(initial=0.0))
+
+
+def bf16_steps_apart(a: np.ndarray, b: np.ndarray):
+    """(elements that differ, largest distance in bf16 steps) between two arrays of bf16 bit patterns."""
+    def ordered(x):            # sign-magnitude bits -> integers that order like the values
+        x = x.astype(np.int32)
+        return np.where(x & 0x8000, 0x8000 - x, x)
+    d = np.abs(ordered(a.reshape(-1)) - ordered(b.reshape(-1)))
+    return int((d != 0).sum()), int(d.max(initial=0))
+
+
+def verify_step(wl, s: int, count: int = 4, layers=None, seqs=None) -> dict:
+    """Checks what step `s` -- the step that ran last -- left on the device, for a sample of this rank's
+    sequences (the longest, the shortest, random others; `count` in all, or `seqs`) on the timed (global) layer
+    and on the first sliding layer (or `layers`), against the CPU oracle (test infrastructure, never timed):
+      * attention rows and log-sum-exp against double precision over the same cache and prepared q;
+      * the prepared q and the appended K/V rows against the oracle's fused append (IEEE square root and
+        divide; the library's default mode uses rsqrt.approx like the reference's GPU code, so single elements
+        may sit one bf16 step away: counted, bounded) and, where the reference's own append kernel is built
+        (oracle/_ref, same arithmetic as the default mode), against that kernel bit for bit.
+    Runs outside every timed region. Returns the figures and "ok"."""
+    from oracle import binding as orc
+
+    orc.build()
+    torch, sp = wl.torch, wl.spec
+    torch.cuda.synchronize()
+    if seqs is None:
+        seqs = sample_sequences(wl.ctx, count, 7 + s)
+    if layers is None:
+        layers = [i for i in (wl.timed_layer, 0) if 0 <= i < wl.L]
+        layers = list(dict.fromkeys(layers))
+    idx = torch.tensor(seqs, device="cuda")
+    n = len(seqs)
+    lens = wl.len_all[s][idx].cpu().numpy().astype(np.int32)
+    pos = wl.pos_all[s][idx].cpu().numpy().astype(np.int32)
+    res = {"step": int(s), "sequences": [int(b) for b in seqs], "layers": [], "rows": 0, "max_abs": 0.0, "max_rel": 0.0,
+           "lse_max_abs": 0.0, "cache_rows_exact": None, "append_vs_ieee_oracle": {"elements": 0, "one_step_off": 0,
+                                                                                 "max_steps": 0}}
+    ok = int(wl.status[0].item()) == 0
+    ref_lib = None
+    if not sp.fp8 and sp.hkv == 8 and not sp.key_shard:
+        try:
+            from oracle import ref_binding
+
+            ref_lib = ref_binding if ref_binding.available() else None
+        except OSError:
+            ref_lib = None
+    for i in layers:
+        g = wl.layer_is_global(i)
+        c = compact_layer_cache(wl, i, seqs)
+        cfg = c["cfg"]
+        table = c["table"].cpu().numpy().astype(np.int32)
+        q = _bits(wl.q_prepared[i][idx])
+        got = _bits(wl.out[i][idx])
+        got_lse = wl.lse[i][idx].cpu().numpy()
+        scale = 1.0 / math.sqrt(D)
+        if sp.fp8:
+            ck, cv = c["ck"].cpu().numpy(), c["cv"].cpu().numpy()
+            ref, ref_lse = orc.fp8_decode_attention_f64(q, ck.reshape(-1), cv.reshape(-1), c["sk"].cpu().numpy().reshape(-1),
+                                                        c["sv"].cpu().numpy().reshape(-1), table, lens, cfg, 0, scale, n, sp.hq)
+        else:
+            ck, cv = _bits(c["ck"]).reshape(-1), _bits(c["cv"]).reshape(-1)
+            ref, ref_lse = orc.decode_attention_f64(q, ck, cv, table, lens, cfg, 0, scale, n, sp.hq)
+        max_abs, max_rel = attention_errors(got, ref, orc)
+        finite = np.isfinite(ref_lse)
+        lse_err = float(np.abs(got_lse[finite] - ref_lse[finite]).max(initial=0.0))
+        ok = ok and max_abs <= VERIFY_MAX_ABS and max_rel <= VERIFY_MAX_REL and lse_err <= VERIFY_LSE \
+            and bool(np.array_equal(np.isfinite(got_lse), finite))
+        entry = {"layer": int(i), "kind": "global" if g else "sliding", "keys": [int(min(x, WINDOW)) if not g else int(x)
+                                                                               for x in lens],
+                 "max_abs": max_abs, "max_rel": max_rel, "lse_max_abs": lse_err}
+        res["rows"] += n * sp.hq
+        res["max_abs"], res["max_rel"] = max(res["max_abs"], max_abs), max(res["max_rel"], max_rel)
+        res["lse_max_abs"] = max(res["lse_max_abs"], lse_err)
+        if not sp.fp8 and not sp.key_shard:
+            # the append of this step: prepared q and the new cache rows
+            rq, rk, rv = _bits(wl.raw_q[i][idx]), _bits(wl.raw_k[i][idx]), _bits(wl.raw_v[i][idx])
+            cos_t, sin_t = ((wl.g_cos, wl.g_sin) if g else (wl.l_cos, wl.l_sin))
+            cos, sin = cos_t.cpu().numpy(), sin_t.cpu().numpy()
+            qp = np.zeros((n, sp.hq, D), np.uint16)
+            ck2, cv2 = ck.copy(), cv.copy()
+            orc.decode_append(qp, ck2, cv2, cfg, table, pos, 0, rq.reshape(n, sp.hq, D), rk.reshape(n, sp.hkv, D),
+                              rv.reshape(n, sp.hkv, D), _bits(wl.q_w), _bits(wl.k_w), cos, sin, n, sp.hq, D)
+            off = [bf16_steps_apart(qp, q), bf16_steps_apart(ck2, ck), bf16_steps_apart(cv2, cv)]
+            elements = n * (sp.hq + 2 * sp.hkv) * D
+            differing, steps = sum(o[0] for o in off), max(o[1] for o in off)
+            a = res["append_vs_ieee_oracle"]
+            a["elements"] += elements
+            a["one_step_off"] += differing
+            a["max_steps"] = max(a["max_steps"], steps)
+            ok = ok and steps <= 1 and differing <= 0.02 * elements
+            if ref_lib is not None:
+                # the reference's own fused append kernel on a copy of the same pages: it rewrites the new rows,
+                # and nothing may change
+                ckd, cvd = c["ck"].clone(), c["cv"].clone()
+                qpd = torch.zeros_like(wl.q_prepared[i][idx])
+                rc = ref_lib.decode_append(qpd, ckd, cvd, cfg, c["table"], wl.pos_all[s][idx].contiguous(), 0,
+                                           wl.raw_q[i][idx].contiguous(), wl.raw_k[i][idx].contiguous(),
+                                           wl.raw_v[i][idx].contiguous(), wl.q_w, wl.k_w, cos_t, sin_t, n)
+                torch.cuda.synchronize()
+                exact = (rc == 0 and torch.equal(ckd, c["ck"]) and torch.equal(cvd, c["cv"])
+                         and torch.equal(qpd.view(torch.int16), wl.q_prepared[i][idx].view(torch.int16)))
+                entry["append_equals_reference_kernel"] = bool(exact)
+                res["cache_rows_exact"] = bool(exact) if res["cache_rows_exact"] is None else (res["cache_rows_exact"] and exact)
+                ok = ok and exact
+        res["layers"].append(entry)
+    if res["cache_rows_exact"] is None and res["append_vs_ieee_oracle"]["elements"]:
+        res["cache_rows_exact"] = res["append_vs_ieee_oracle"]["one_step_off"] == 0
+        res["cache_checker"] = "host oracle (IEEE 1/sqrt); the reference's append kernel was not available"
+    elif res["cache_rows_exact"] is not None:
+        res["cache_checker"] = "the reference's own fused append kernel (oracle/_ref) on the same pages, bit for bit"
+    res["tolerance"] = {"max_abs": VERIFY_MAX_ABS, "max_rel": VERIFY_MAX_REL, "lse_max_abs": VERIFY_LSE,
+                        "append": "host oracle: at most one bf16 step on under 2 % of elements; reference kernel: exact"}
+    res["ok"] = bool(ok)
+    return res
+
+
 def run_reference_arm(args):
-    """CPU restatement of the reference's path on all host cores; each step is one global layer-step over
-    a bounded sample of the workload's sequences."""
+    """`--impl reference`: the reference's own implementation of the path on the same workload. gemma.c has no CPU
+    implementation of it -- its KV path is CUDA only -- so the arm runs the reference's own CUDA kernels, built
+    for sm_100a from its unchanged sources (oracle/_ref, oracle/build_ref.sh), when that library and a GPU are
+    there: fused append phase, split phase and reduce phase at the reference's split size of 20 keys
+    (src/gemma4.h:24), layer by layer. The reference is single-GPU (decode requires batch 1 and one device,
+    src/gemma4_decode_megakernel.cu:143): under torchrun rank 0 alone runs the whole batch on its GPU and the
+    other ranks exit. Without that library (or a GPU) it falls back to the CPU port of the same phases."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    from oracle import ref_binding as ref
+
+    gpu = False
+    try:
+        import torch
+
+        gpu = torch.cuda.is_available()
+    except ImportError:
+        torch = None
+    if gpu and ref.available() and args.workload == "cfg3":
+        run_reference_cuda_arm(args, torch, ref)
+    else:
+        run_reference_cpu_arm(args, "no GPU" if not gpu else ("oracle/_ref not built" if not ref.available()
+                                                              else f"workload {args.workload}"))
+
+
+def run_reference_cuda_arm(args, torch, ref):
+    """The default workload (BASELINE configs[2]) through the reference's CUDA phases on one GPU. Nothing of the
+    B200 library is loaded: caches, tables and metadata are built with torch and the oracle's host helpers."""
+    from oracle import binding as orc
+
+    orc.build()
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    dev = "cuda"
+    sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
+    ctx = context_lengths(args)
+    B = int(ctx.size)
+    split = 20                                            # GEMMA4_SLIDING_DECODE_SPLIT_SIZE, src/gemma4.h:24
+    e2e_warm = 2
+    e2e_steps = min(args.e2e_steps, 5)
+    total = args.warmup + args.steps + e2e_warm + e2e_steps
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(args.seed)
+    rng = np.random.default_rng(args.seed)
+
+    def normal_bf16(n):
+        t = torch.empty(n, dtype=torch.bfloat16, device=dev)
+        t.normal_(generator=gen)
+        return t
+
+    pages_b = (ctx + total + PAGE) // PAGE
+    g_pages, g_mpps = int(pages_b.sum()), int(pages_b.max())
+    table = np.full((B, g_mpps), -1, dtype=np.int32)
+    pool = rng.permutation(g_pages).astype(np.int32)
+    cur = 0
+    for b in range(B):
+        table[b, :pages_b[b]] = pool[cur:cur + pages_b[b]]
+        cur += int(pages_b[b])
+    n_local, n_global = 5, 1
+    l_mpps = (WINDOW + PAGE - 1 + PAGE - 1) // PAGE
+    g_cfg = (n_global, g_pages, PAGE, g_mpps, B, HKV, D, 0)
+    l_cfg = (n_local, B * l_mpps, PAGE, l_mpps, B, HKV, D, WINDOW)
+    g_table = torch.from_numpy(table).to(dev)
+    l_table = torch.from_numpy(rng.permutation(B * l_mpps).astype(np.int32).reshape(B, l_mpps)).to(dev)
+    elems = lambda c: c[0] * c[1] * c[2] * c[5] * c[6]
+    g_k, g_v = normal_bf16(elems(g_cfg)), normal_bf16(elems(g_cfg))
+    l_k, l_v = normal_bf16(elems(l_cfg)), normal_bf16(elems(l_cfg))
+    max_pos = int(ctx.max()) + total + 1
+    g_cos, g_sin = (torch.from_numpy(t).to(dev) for t in orc.fill_rope_tables(max_pos, D // 2, 1000000.0, D))
+    l_cos, l_sin = (torch.from_numpy(t).to(dev) for t in orc.fill_rope_tables(max_pos, D // 2, 10000.0, D))
+    w = torch.empty(2, D, dtype=torch.float32, device=dev).normal_(1.0, 0.05, generator=gen).to(torch.bfloat16)
+    L = n_local + n_global
+    row = (HQ + 2 * HKV) * D
+    raw = normal_bf16(L * B * row).view(L, B, row)
+    raw_host = torch.empty((L, B, row), dtype=torch.bfloat16).pin_memory()
+    raw_host.copy_(raw)
+    raw_q = torch.empty((L, B, HQ * D), dtype=torch.bfloat16, device=dev)
+    raw_k = torch.empty((L, B, HKV * D), dtype=torch.bfloat16, device=dev)
+    raw_v = torch.empty((L, B, HKV * D), dtype=torch.bfloat16, device=dev)
+
+    def unpack():
+        q, k, v = raw.split([HQ * D, HKV * D, HKV * D], dim=2)
+        raw_q.copy_(q); raw_k.copy_(k); raw_v.copy_(v)
+
+    unpack()
+    q_prepared = torch.empty((L, B, HQ, D), dtype=torch.bfloat16, device=dev)
+    out = torch.empty((L, B, HQ, D), dtype=torch.bfloat16, device=dev)
+    out_host = torch.empty((L, B, HQ, D), dtype=torch.bfloat16).pin_memory()
+    steps_i = np.arange(total, dtype=np.int64)[:, None]
+    pos_all = torch.from_numpy((ctx[None, :] + steps_i).astype(np.int32)).to(dev)
+    len_all = torch.from_numpy((ctx[None, :] + steps_i + 1).astype(np.int32)).to(dev)
+    g_nsplit = -(-(int(ctx.max()) + total) // split)
+    l_nsplit = -(-WINDOW // split)
+    rows = B * HQ * max(g_nsplit, l_nsplit)
+    pm = torch.empty(rows, dtype=torch.float32, device=dev)
+    pl = torch.empty(rows, dtype=torch.float32, device=dev)
+    pacc = torch.empty(rows * D, dtype=torch.float32, device=dev)
+    is_global = [(i + 1) % 6 == 0 for i in range(L)]       # five sliding layers, then one global (src/gemma4.h:105-108)
+    scale = 1.0 / math.sqrt(D)
+
+    def step(s):
+        n_l = n_g = 0
+        for i in range(L):
+            g = is_global[i]
+            cfg, ck, cv, tab = (g_cfg, g_k, g_v, g_table) if g else (l_cfg, l_k, l_v, l_table)
+            cos, sin = (g_cos, g_sin) if g else (l_cos, l_sin)
+            li = n_g if g else n_l
+            rc = ref.decode_append(q_prepared[i], ck, cv, cfg, tab, pos_all[s], li, raw_q[i], raw_k[i], raw_v[i],
+                                   w[0], w[1], cos, sin, B)
+            rc2 = ref.decode_attention(out[i], pm, pl, pacc, q_prepared[i], ck, cv, tab, len_all[s], cfg, li, scale,
+                                       split, g_nsplit if g else l_nsplit, B)
+            if rc or rc2:
+                raise RuntimeError(f"reference kernel launch failed: {rc} {rc2}")
+            n_g, n_l = n_g + int(g), n_l + int(not g)
+
+    def bytes_of(s):
+        after = ctx + s + 1
+        return n_local * layer_step_bytes(after, WINDOW) + n_global * layer_step_bytes(after, 0)
+
+    sampler.mark("load_begin")
+    s = 0
+    for _ in range(args.warmup):
+        step(s); s += 1
+    torch.cuda.synchronize()
+    sampler.mark("timed_begin")
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    first = s
+    marks[0].record()
+    for i in range(args.steps):
+        step(s); s += 1
+        marks[i + 1].record()
+    torch.cuda.synchronize()
+    sampler.mark("timed_end")
+    ms = marks[0].elapsed_time(marks[-1])
+    step_bytes = sum(bytes_of(i) for i in range(first, first + args.steps))
+
+    def step_e2e(s):
+        raw.copy_(raw_host, non_blocking=True)
+        unpack()
+        step(s)
+        out_host.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(e2e_warm):
+        step_e2e(s); s += 1
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    first_e = s
+    e0.record()
+    for _ in range(e2e_steps):
+        step_e2e(s); s += 1
+    e1.record()
+    torch.cuda.synchronize()
+    e2e_ms = e0.elapsed_time(e1)
+    e2e_bytes = sum(bytes_of(i) for i in range(first_e, first_e + e2e_steps))
+    sampler.mark("load_end")
+    clocks = sampler.stop()
+    value = step_bytes / (ms * 1e-3) / 1e9
+    threads = orc.hardware_threads()
+    cpu = cpu_layer_step_sample(ctx, threads, min(args.cpu_seconds, 5.0))
+    cfg_line = workload_config(args, 1, "B200 (one GPU)", "single GPU: the reference does not shard", L)
+    cfg_line["launch"] = "stream launches: fused append phase, split phase, reduce phase per layer"
+    cfg_line["split_size"] = split
+    line = {
+        "impl": "reference", "reference_class": "cuda",
+        "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus, "gpus_used": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": cfg_line,
+        "us_per_layer_step": ms * 1e3 / (args.steps * L), "step_ms_stats": step_stats(marks),
+        "e2e": {"value": e2e_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
+                "h2d_bytes_per_step": int(raw_host.numel() * 2), "d2h_bytes_per_step": int(out_host.numel() * 2),
+                "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
+        "cpu_baseline": {"value": cpu["gbps"], "unit": "GB/s", "cores": threads, "kind": "port",
+                         "sample": f"global layer-step over the first {cpu['sequences']} sequences ({cpu['keys']} keys), "
+                                   f"{cpu['runs']} passes, oracle port on all host threads; shown beside, not the arm's value"},
+        "gpu_launches": 3 * L * args.steps,
+        "kernels": "phase_decode_q_paged_kv_norm_rope, phase_decode_paged_grouped_split, phase_decode_paged_reduce of "
+                   "src/gemma4_flash_attention_decode.cu:305-375,692-977, compiled unchanged for sm_100a",
+        "clocks": clocks,
+        "note": "gemma.c has no CPU implementation of this path; this arm is its own CUDA code on one B200"
+                + ("" if args.gpus == 1 else f" (single-GPU reference: rank 0 ran all {B} sequences on one GPU of the {args.gpus})"),
+    }
+    print(json.dumps(line))
+
+
+def run_reference_cpu_arm(args, why: str):
+    """Fallback of the reference arm: the CPU port of the reference's phases on all host cores; each step is
+    one global layer-step over a bounded sample of the workload's sequences."""
     from oracle import binding as orc
 
     orc.build()
@@ -668,14 +1032,14 @@ def run_reference_arm(args):
     desc = (f"global layer-step (append + split attention + reduce) over the first {sample['sequences']} "
             f"sequences ({sample['keys']} keys) of the workload, {sample['runs']} passes per step")
     line = {
-        "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus,
+        "impl": "reference", "reference_class": "cpu", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs / len(times) * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": workload_config(args, 1, "cpu"),
         "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port", "sample": desc},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
-        "note": "the reference has no CPU implementation of this path; this is the oracle port of its CUDA "
+        "note": f"the reference's CUDA kernels could not be run here ({why}); this is the oracle port of its CUDA "
                 "phases (oracle/kv_oracle.cpp) on all host threads",
     }
     print(json.dumps(line))
@@ -1207,54 +1571,21 @@ def run_prefill(args, kv, torch, sampler):
 
 
 # --------------------------------------------------------------------------- main arm
-def main():
-    args = parse_args()
-    if args.impl == "reference":
-        run_reference_arm(args)
-        return
+L2_FLUSH_BYTES = 512 << 20      # four times the 126 MB L2 of a B200
 
-    import torch
-    import torch.distributed as dist
 
-    from __graft_entry__ import load_package
-
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if world != args.gpus and world > 1:
-        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
-    torch.cuda.set_device(local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-
-    kv = load_package()
-    kv.load_library(build_if_missing=False)
-    sampler = ClockSampler(local_rank) if rank == 0 else None   # started early: nvidia-smi takes a second to come up
-
-    if args.workload == "prefill":
-        if world > 1:
-            raise SystemExit("--workload prefill is a one-GPU line")
-        run_prefill(args, kv, torch, sampler)
-        return
-    if args.workload == "layer":
-        if world > 1:
-            raise SystemExit("--workload layer is a one-GPU line")
-        run_layer(args, kv, torch, sampler)
-        return
-    if args.workload == "native_global":
-        if world > 1:
-            raise SystemExit("--workload native_global is a one-GPU line")
-        run_native_global(args, kv, torch, sampler)
-        return
+def measure_workload(args, kv, torch, dist, world, rank, sampler=None, verify=True, extras=True):
+    """Builds one workload on this rank, runs warm-up + timed + end-to-end + probe steps and returns the JSON
+    line as a dict on rank 0 (None elsewhere). `verify`: check the last timed step's outputs against the
+    oracle. `extras`: the reference's CUDA kernels and the CPU baselines beside the number (rank 0, one GPU)."""
     spec, ctx_all, ctx, parallelism, scaling = plan_workload(args, world, rank)
     if args.emulate_world > 1 and world == 1 and args.workload in ("cfg3", "cfg5"):
         ctx = ctx_all[shard_sequences(ctx_all, args.emulate_world)[args.emulate_rank]]
     e2e_warm = 3
     use_graph = args.graph == "on" or (args.graph == "auto" and args.workload in ("cfg1", "cfg2"))
     probe_steps = 11                        # steps after the timed regions that carry the per-kernel events
-    total_steps = args.warmup + args.steps + e2e_warm + args.e2e_steps + probe_steps
+    cold_steps = min(args.steps, 50) if args.cache in ("cold", "both") else 0
+    total_steps = args.warmup + args.steps + cold_steps + e2e_warm + args.e2e_steps + probe_steps
     wl = RankWorkload(kv, torch, ctx, total_steps, args.seed + 1000 * rank, args, spec)
     torch.cuda.synchronize()
 
@@ -1289,6 +1620,36 @@ def main():
     attn_bytes = statistics.mean(wl.bytes_for_step(i)[1] for i in range(first_timed, first_timed + args.steps))
     status = int(wl.status[0].item())
 
+    # parity of what the timed region just produced (host work, outside every timed region)
+    verified = None
+    if verify:
+        verified = verify_step(wl, s - 1) if not spec.key_shard else {
+            "ok": True, "skipped": "key-range sharding: a rank holds a slice of the keys, the merged rows are "
+                                   "checked against ncclAllGather + a torch merge in the warm-up instead"}
+
+    # cold cache: an L2 flush (a write over four times the L2) before every timed iteration, the events recorded
+    # after the flush -- the reference bench's contract (src/benches/gemma4_kv_cache_bench.cu:60-112,187-195)
+    cold = None
+    if cold_steps:
+        flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device="cuda")
+        begin = [torch.cuda.Event(enable_timing=True) for _ in range(cold_steps)]
+        end = [torch.cuda.Event(enable_timing=True) for _ in range(cold_steps)]
+        first_cold = s
+        for i in range(cold_steps):
+            flush.fill_(i & 0xFF)
+            begin[i].record()
+            wl.step(s)
+            s += 1
+            end[i].record()
+        barrier()
+        ms = np.array([begin[i].elapsed_time(end[i]) for i in range(cold_steps)])
+        cold_bytes = statistics.mean(wl.bytes_for_step(i)[0] for i in range(first_cold, first_cold + cold_steps))
+        cold = {"steps": cold_steps, "ms_per_step_median": float(np.median(ms)), "ms_per_step_min": float(ms.min()),
+                "ms_per_step_max": float(ms.max()), "us_per_layer_step": float(np.median(ms)) * 1e3 / wl.L,
+                "GBps": cold_bytes / (float(np.median(ms)) * 1e-3) / 1e9,
+                "flush": f"{L2_FLUSH_BYTES >> 20} MiB written before every step, events after the flush"}
+        del flush
+
     # end to end through host buffers
     for _ in range(e2e_warm):
         wl.step_e2e(s)
@@ -1314,12 +1675,16 @@ def main():
         s += 1
     torch.cuda.synchronize()
     attn_ms = [wl.ev_begin[i].elapsed_ms(wl.ev_end[i]) for i in range(probe0 + 3, probe0 + probe_steps)]
+    clocks = None
     if sampler:
         sampler.mark("load_end")
         clocks = sampler.stop()
 
+    v_ok = 1.0 if (verified is None or verified.get("ok")) else 0.0
     stats = torch.tensor([elapsed_ms, e2e_ms, -float(step_bytes), -float(e2e_bytes), float(status),
-                          statistics.mean(attn_ms)], dtype=torch.float64, device="cuda")
+                          statistics.mean(attn_ms), -v_ok, (verified or {}).get("max_abs", 0.0),
+                          (verified or {}).get("lse_max_abs", 0.0), cold["ms_per_step_median"] if cold else 0.0],
+                         dtype=torch.float64, device="cuda")
     if world > 1:
         mx = stats.clone()
         dist.all_reduce(mx, op=dist.ReduceOp.MAX)
@@ -1327,80 +1692,199 @@ def main():
         dist.all_reduce(sm_, op=dist.ReduceOp.SUM)
         elapsed_ms, e2e_ms, status = mx[0].item(), mx[1].item(), int(mx[4].item())
         step_bytes, e2e_bytes = -sm_[2].item(), -sm_[3].item()
+        if verified is not None:
+            verified["all_ranks_ok"] = bool(-mx[6].item() >= 1.0)
+            verified["max_abs_over_ranks"], verified["lse_max_abs_over_ranks"] = mx[7].item(), mx[8].item()
+            verified["ok"] = verified["all_ranks_ok"]
+        if cold:
+            cold["ms_per_step_median_max_over_ranks"] = mx[9].item()
+    launches = wl.launches_per_step * args.steps
+    splits = {"global": [wl.g_split, wl.g_nsplit], "local": [wl.l_split, wl.l_nsplit]}
+    timed_split = wl.layers[wl.timed_layer].split_size
+    ref_cuda = None
+    if rank == 0 and extras and not args.no_reference_cuda and world == 1:
+        try:
+            ref_cuda = reference_cuda_numbers(wl, torch, first_timed)
+        except Exception as exc:  # the second checker must never cost the bench line
+            ref_cuda = {"error": repr(exc)}
+    n_layers, n_global, fp8 = wl.L, spec.n_global, spec.fp8
+    if wl.peer is not None:
+        wl.peer.close()
+    del wl
+    torch.cuda.empty_cache()
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
-        return
+        return None
 
-    peaks_path = REPO / "MEASURED_PEAKS.json"
-    if peaks_path.exists():
-        peak, peak_src = float(json.loads(peaks_path.read_text())["hbm_gbs"]), "MEASURED_PEAKS.json hbm_gbs"
-    else:
-        peak, peak_src = 6650.0, "fallback 6.65 TB/s (MEASURED_PEAKS.json absent)"
-
+    peak, peak_src = hbm_peak()
     value = step_bytes / (elapsed_ms * 1e-3) / 1e9
-    layer_steps = args.steps * wl.L
     attn_achieved = attn_bytes / (statistics.mean(attn_ms) * 1e-3) / 1e9
     line = {
         "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
         "scaling": scaling, "vs_baseline": None, "dtype": ("fp8 e4m3 cache; scores e4m3 tensor-core MMA (query hi+lo) with fp32 accumulate, P*V fp16 per 8 keys into fp32"
-                                                            if spec.fp8 else "bf16"),
+                                                            if fp8 else "bf16"),
         "data": "synthetic",
-        "config": workload_config(args, world, "B200", parallelism, wl.L),
-        "us_per_layer_step": elapsed_ms * 1e3 / layer_steps,
+        "config": workload_config(args, world, "B200", parallelism, n_layers),
+        "us_per_layer_step": elapsed_ms * 1e3 / (args.steps * n_layers),
         "us_global_layer_attention": statistics.mean(attn_ms) * 1e3,
         "step_ms_stats": step_stats(marks),
         "frac_of_hbm_peak": value / (peak * world),
         "roofline": {
             "bound": "hbm",
-            "kernel": ("decode_balanced_kernel" if wl.layers[wl.timed_layer].split_size == 0 or spec.fp8
-                       else "decode_split_kernel") + " + combine, "
-                      + ("global" if spec.n_global else "sliding") + " layer (rank 0)",
+            "kernel": ("decode_balanced_kernel" if timed_split == 0 or fp8 else "decode_split_kernel") + " + combine, "
+                      + ("global" if n_global else "sliding") + " layer (rank 0)",
             "achieved": attn_achieved, "peak": peak, "unit": "GB/s", "frac": attn_achieved / peak,
             "traffic": None, "peak_source": peak_src,
             "algorithmic_bytes_per_launch": attn_bytes, "avg_launch_ms": statistics.mean(attn_ms),
         },
         "e2e": {
             "value": e2e_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
-            "h2d_bytes_per_step": int(wl.raw_host.numel() * 2), "d2h_bytes_per_step": int(wl.out_host.numel() * 2),
+            "h2d_bytes_per_step": int(n_layers * ctx.size * (spec.hq + 2 * spec.hkv) * D * 2),
+            "d2h_bytes_per_step": int(n_layers * ctx.size * spec.hq * D * 2),
             "steps": args.e2e_steps, "ms_per_step": e2e_ms / args.e2e_steps,
             "note": "per rank, rank 0's copy sizes; host buffers are pinned, copies and a stream sync are inside "
                     "the timed region every step",
         },
-        "gpu_launches": wl.launches_per_step * args.steps,
-        "splits": {"global": [wl.g_split, wl.g_nsplit], "local": [wl.l_split, wl.l_nsplit]},
+        "gpu_launches": launches,
+        "splits": splits,
         "device_status": status,
         "clocks": clocks,
     }
+    if verified is not None:
+        line["verified"] = verified
+    if cold is not None:
+        line["cold_cache"] = cold
     traffic_path = REPO / "profiles" / "decode_balanced_traffic.json"
     if traffic_path.exists():
         try:
             t = json.loads(traffic_path.read_text())
-            t = t.get("fp8", t) if spec.fp8 else t
+            t = t.get("fp8", t) if fp8 else t
             line["roofline"]["traffic"] = t["dram_bytes_per_algorithmic_byte"] * attn_bytes
             line["roofline"]["traffic_source"] = t.get("source")
         except (ValueError, KeyError):
             pass
-    if not args.no_reference_cuda and world == 1:
-        try:
-            ref_cuda = reference_cuda_numbers(wl, torch, first_timed)
-        except Exception as exc:  # the second checker must never cost the bench line
-            ref_cuda = {"error": repr(exc)}
-        if ref_cuda is not None:
-            line["reference_cuda"] = ref_cuda
-    if not args.no_cpu_baseline and world == 1:
+    if ref_cuda is not None:
+        line["reference_cuda"] = ref_cuda
+    if extras and not args.no_cpu_baseline and world == 1:
         threads = os.cpu_count() or 1
-        base = cpu_layer_step_sample(ctx_all, threads, args.cpu_seconds)
-        line["cpu_baseline"] = {
-            "value": base["gbps"], "unit": "GB/s", "cores": threads, "kind": "port",
-            "sample": f"global layer-step over the first {base['sequences']} sequences ({base['keys']} keys) of the "
-                      f"batch, repeated {base['runs']}x, {base['seconds']:.2f} s of host time, oracle port on all "
-                      f"host threads",
-        }
-    print(json.dumps(line))
+        for key, n_threads, seconds in (("cpu_baseline", threads, args.cpu_seconds),
+                                        ("cpu_baseline_1t", 1, args.cpu_seconds)):
+            base = cpu_layer_step_sample(ctx_all, n_threads, seconds, max_keys=131072 if n_threads > 1 else 32768)
+            line[key] = {
+                "value": base["gbps"], "unit": "GB/s", "cores": n_threads, "kind": "port",
+                "us_per_layer_step_of_sample": base["us_per_layer_step"],
+                "sample": f"global layer-step over the first {base['sequences']} sequences ({base['keys']} keys) of the "
+                          f"batch, repeated {base['runs']}x, {base['seconds']:.2f} s of host time, oracle port on "
+                          + (f"all {n_threads} host threads" if n_threads > 1 else "one host thread"),
+            }
+    return line
+
+
+def summary_of(line: dict) -> dict:
+    """The figures of a secondary workload that go into the main line's `other_workloads`."""
+    peak = line["roofline"]["peak"]
+    out = {
+        "workload": line["config"]["workload"], "parallelism": line["config"]["parallelism"],
+        "launch": line["config"]["launch"], "n_gpus": line["n_gpus"], "steps": line["steps"], "warmup": line["warmup"],
+        "us_per_layer_step": line["us_per_layer_step"], "ms_per_step": line["ms_per_step"], "GBps": line["value"],
+        "frac_of_hbm_peak_x_gpus": line["value"] / (peak * line["n_gpus"]),
+        "dominant_kernel": {k: line["roofline"][k] for k in ("kernel", "achieved", "frac", "avg_launch_ms",
+                                                             "algorithmic_bytes_per_launch")},
+        "e2e_GBps": line["e2e"]["value"], "device_status": line["device_status"], "dtype": line["dtype"],
+        "step_ms_stats": line["step_ms_stats"],
+    }
+    for key in ("verified", "cold_cache", "reference_cuda"):
+        if key in line:
+            out[key] = line[key]
+    if isinstance(out.get("verified"), dict):         # the short form: figures, not the per-layer list
+        out["verified"] = {k: v for k, v in out["verified"].items() if k not in ("layers", "sequences", "tolerance")}
+    return out
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import copy
+
+    import torch
+    import torch.distributed as dist
+
+    from __graft_entry__ import load_package
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    kv = load_package()
+    kv.load_library(build_if_missing=False)
+    sampler = ClockSampler(local_rank) if rank == 0 else None   # started early: nvidia-smi takes a second to come up
+
+    if args.workload in ("prefill", "layer", "native_global"):
+        if world > 1:
+            raise SystemExit(f"--workload {args.workload} is a one-GPU line")
+        {"prefill": run_prefill, "layer": run_layer, "native_global": run_native_global}[args.workload](
+            args, kv, torch, sampler)
+        return
+
+    line = measure_workload(args, kv, torch, dist, world, rank, sampler, verify=not args.no_verify)
+
+    # The other BASELINE configs, short runs in the same process (default workload only): batch-1 latency cases on
+    # one GPU; the long single sequence KV-head-sharded with the peer all-gather (and ncclAllGather beside it) and
+    # the fp8 batch sequence-sharded on as many GPUs as this run has.
+    others = []
+    if args.workload == "cfg3" and not args.no_other_workloads and not args.emulate_world:
+        plan = []
+        if world == 1:
+            plan += [("cfg1", {"cache": "both"}), ("cfg2", {"cache": "both"})]
+        if 8 % world == 0:
+            plan += [("cfg4", {"gather": "peer"})]
+            if world > 1:
+                plan += [("cfg4", {"gather": "nccl"})]
+        plan += [("cfg5", {})]
+        for name, extra in plan:
+            sub = copy.copy(args)
+            sub.workload, sub.seqs = name, 0
+            sub.steps = max(20, min(args.steps, args.other_steps))
+            sub.warmup = max(3, min(args.warmup, 10))
+            sub.e2e_steps = min(args.e2e_steps, 5)
+            sub.cache = "warm"
+            sub.no_cpu_baseline = True
+            for k, v in extra.items():
+                setattr(sub, k, v)
+            try:
+                got = measure_workload(sub, kv, torch, dist, world, rank, None, verify=not args.no_verify)
+            except Exception as exc:          # a secondary workload must never cost the main line
+                got = None
+                if rank == 0:
+                    others.append({"workload": WORKLOADS[name], "error": repr(exc)})
+            if got is not None:
+                entry = summary_of(got)
+                if name == "cfg4" and world > 1:
+                    entry["exchange"] = extra["gather"]
+                others.append(entry)
+    if rank == 0:
+        if others:
+            line["other_workloads"] = others
+        print(json.dumps(line))
+    failed = False
+    if rank == 0:
+        checks = [line.get("verified")] + [o.get("verified") for o in others]
+        failed = any(isinstance(c, dict) and not c.get("ok", True) for c in checks)
     if world > 1:
         dist.destroy_process_group()
+    if failed:
+        print("bench.py: outputs of a timed step are outside the parity band (see `verified`)", file=sys.stderr)
+        sys.exit(3)
 
 
 if __name__ == "__main__":

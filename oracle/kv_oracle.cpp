@@ -764,10 +764,14 @@ void orc_decode_attention_f64(float *out_f32, float *lse, const uint16_t *q,
   const OrcKvConfig &c = *cfg;
   const int D = c.head_dim;
   const int G = q_heads / c.num_heads;
-  for (int b = 0; b < batch_count; ++b) {
+  // rows are independent: one (sequence, query head) per work item, on all host
+  // threads; the arithmetic of a row does not depend on the thread count
+  parallel_for(orc_hardware_threads(), batch_count * q_heads, [&](int unit) {
+    const int b = unit / q_heads;
     const int seq_len = seq_lengths[b];
     const LiveRange r = live_range(c, seq_len, 1);
-    for (int qh = 0; qh < q_heads; ++qh) {
+    {
+      const int qh = unit - b * q_heads;
       const int kvh = qh / G;
       const int64_t row = int64_t(b) * q_heads + qh;
       std::vector<double> scores;
@@ -790,7 +794,7 @@ void orc_decode_attention_f64(float *out_f32, float *lse, const uint16_t *q,
       if (scores.empty()) {
         for (int d = 0; d < D; ++d) out_f32[row * D + d] = 0.0f;
         lse[row] = -std::numeric_limits<float>::infinity();
-        continue;
+        return;
       }
       const double M = *std::max_element(scores.begin(), scores.end());
       double L = 0.0;
@@ -806,7 +810,7 @@ void orc_decode_attention_f64(float *out_f32, float *lse, const uint16_t *q,
       for (int d = 0; d < D; ++d) out_f32[row * D + d] = float(acc[d] / L);
       lse[row] = float(M + std::log(L));
     }
-  }
+  });
 }
 
 int64_t orc_fp8_k_index(const OrcKvConfig *cfg, int32_t layer, int32_t page,
@@ -903,10 +907,12 @@ void orc_fp8_decode_attention_f64(float *out_f32, float *lse,
   const OrcKvConfig &c = *cfg;
   const int D = c.head_dim;
   const int G = q_heads / c.num_heads;
-  for (int b = 0; b < batch_count; ++b) {
+  parallel_for(orc_hardware_threads(), batch_count * q_heads, [&](int unit) {
+    const int b = unit / q_heads;
     const int seq_len = seq_lengths[b];
     const LiveRange r = live_range(c, seq_len, 1);
-    for (int qh = 0; qh < q_heads; ++qh) {
+    {
+      const int qh = unit - b * q_heads;
       const int kvh = qh / G;
       const int64_t row = int64_t(b) * q_heads + qh;
       std::vector<double> scores, vscale;
@@ -935,7 +941,7 @@ void orc_fp8_decode_attention_f64(float *out_f32, float *lse,
       if (scores.empty()) {
         for (int d = 0; d < D; ++d) out_f32[row * D + d] = 0.0f;
         lse[row] = -std::numeric_limits<float>::infinity();
-        continue;
+        return;
       }
       const double M = *std::max_element(scores.begin(), scores.end());
       double L = 0.0;
@@ -952,7 +958,7 @@ void orc_fp8_decode_attention_f64(float *out_f32, float *lse,
       for (int d = 0; d < D; ++d) out_f32[row * D + d] = float(acc[d] / L);
       lse[row] = float(M + std::log(L));
     }
-  }
+  });
 }
 
 double orc_layer_step_timed(int32_t threads, uint16_t *out,
