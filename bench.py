@@ -80,6 +80,9 @@ def parse_args(argv=None):
     ap.add_argument("--cache", default="warm", choices=["warm", "cold", "both"],
                     help="cold / both: after the timed steps, time more steps one by one with an L2 flush (a write "
                          "over 512 MiB) before each and the events recorded after the flush; reported as `cold_cache`")
+    ap.add_argument("--no-tickets", action="store_true",
+                    help="do not hand the layer-step its tickets: small jobs then run as fused attention + combine "
+                         "(two launches) instead of the one-launch form")
     ap.add_argument("--no-verify", action="store_true",
                     help="skip the oracle check of the last timed step's outputs (`verified`)")
     ap.add_argument("--no-other-workloads", action="store_true",
@@ -347,6 +350,8 @@ class RankWorkload:
         self.pl = torch.empty(rows, dtype=torch.float32, device=dev)
         self.pacc = torch.empty(rows * D, dtype=torch.float32, device=dev)
 
+        # tickets of the one-launch layer-step (zero before the first call, left zero by every call)
+        self.ticket = torch.zeros(B * HKV, dtype=torch.int32, device=dev)
         self.layers = (kv.LayerStepArgs * L)()
         self.ev_begin = [kv.Timer() for _ in range(total_steps)]
         self.ev_end = [kv.Timer() for _ in range(total_steps)]
@@ -372,18 +377,18 @@ class RankWorkload:
             a.sin = (self.g_sin if is_global else self.l_sin).data_ptr() + rope_offset
             a.batch_count, a.q_heads, a.rotary_dim, a.norm_mode = B, HQ, D, kv.NORM_RSQRT_APPROX
             a.status = self.status.data_ptr()
+            a.ticket = None if args.no_tickets else self.ticket.data_ptr()
         self.timed_layer = max((i for i in range(L) if self.layer_is_global(i)), default=L - 1)
         self.stream = torch.cuda.current_stream().cuda_stream
         self.launches_per_step = 0
+        self.kernels_per_layer = []
         for i in range(L):
-            g = self.layer_is_global(i)
-            split, nsplit = (self.g_split, self.g_nsplit) if g else (self.l_split, self.l_nsplit)
-            fused = (split == 0 and not spec.fp8 and spec.hkv == 8 and B <= 1024
-                     and os.environ.get("B200KV_FUSED_LAYER_STEP", "1") != "0")
-            if fused:
-                self.launches_per_step += 2          # balanced kernel with the append inside, combine
+            if spec.fp8:
+                n = 3                                   # fp8 append, balanced attention, combine
             else:
-                self.launches_per_step += 2 if (nsplit == 1 and split > 0) else 3   # append, split[, combine]
+                n = kv.layer_step_launches(self.layers[i])
+            self.kernels_per_layer.append(n)
+            self.launches_per_step += n
         if self.peer is not None:
             self.launches_per_step += 1              # the peer-memory all-gather kernel
 
@@ -1701,6 +1706,10 @@ def measure_workload(args, kv, torch, dist, world, rank, sampler=None, verify=Tr
     launches = wl.launches_per_step * args.steps
     splits = {"global": [wl.g_split, wl.g_nsplit], "local": [wl.l_split, wl.l_nsplit]}
     timed_split = wl.layers[wl.timed_layer].split_size
+    timed_kernels = wl.kernels_per_layer[wl.timed_layer]
+    timed_kernel = ("decode_pagetile_kernel (append, attention and merge in one launch)" if timed_kernels == 1 else
+                    ("decode_balanced_kernel" if timed_split == 0 or spec.fp8 else "decode_split_kernel") + " + combine")
+    kernels_per_layer = list(wl.kernels_per_layer)
     ref_cuda = None
     if rank == 0 and extras and not args.no_reference_cuda and world == 1:
         try:
@@ -1731,8 +1740,7 @@ def measure_workload(args, kv, torch, dist, world, rank, sampler=None, verify=Tr
         "frac_of_hbm_peak": value / (peak * world),
         "roofline": {
             "bound": "hbm",
-            "kernel": ("decode_balanced_kernel" if timed_split == 0 or fp8 else "decode_split_kernel") + " + combine, "
-                      + ("global" if n_global else "sliding") + " layer (rank 0)",
+            "kernel": timed_kernel + ", " + ("global" if n_global else "sliding") + " layer (rank 0)",
             "achieved": attn_achieved, "peak": peak, "unit": "GB/s", "frac": attn_achieved / peak,
             "traffic": None, "peak_source": peak_src,
             "algorithmic_bytes_per_launch": attn_bytes, "avg_launch_ms": statistics.mean(attn_ms),
@@ -1746,6 +1754,7 @@ def measure_workload(args, kv, torch, dist, world, rank, sampler=None, verify=Tr
                     "the timed region every step",
         },
         "gpu_launches": launches,
+        "kernels_per_layer_step": kernels_per_layer,
         "splits": splits,
         "device_status": status,
         "clocks": clocks,

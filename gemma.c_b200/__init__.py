@@ -106,6 +106,7 @@ class LayerStepArgs(ctypes.Structure):
         ("rotary_dim", c_int32), ("norm_mode", c_int32),
         ("status", c_void_p),
         ("event_before_attention", c_void_p), ("event_after_attention", c_void_p),
+        ("ticket", c_void_p),
     ]
 
 
@@ -194,6 +195,10 @@ _SIGNATURES = {
     "b200kv_plan_splits_total": (None, [c_int32, c_int32, c_int64, c_int32, c_int32, POINTER(c_int32), POINTER(c_int32)]),
     "b200kv_decode_layer_step_bf16": (c_int, [POINTER(LayerStepArgs), _P]),
     "b200kv_decode_step_bf16": (c_int, [POINTER(LayerStepArgs), c_int32, _P]),
+    "b200kv_decode_layer_step_tiled_bf16": (c_int, [POINTER(LayerStepArgs), _P]),
+    "b200kv_layer_step_launches": (c_int32, [POINTER(LayerStepArgs)]),
+    "b200kv_decode_attention_tiled_bf16": (c_int, [_P, _P, _P, _P, _P, KvConfig, _P, _P, c_int32, c_float, c_int32,
+                                                  c_int32, c_int32, _P, _P, _P, _P, _P, _P]),
     "b200kv_decode_ingress_bf16": (c_int, [POINTER(IngressArgs), _P]),
     "b200kv_decode_egress_bf16": (c_int, [POINTER(EgressArgs), _P]),
     "b200kv_decode_attention_layer_bf16": (c_int, [POINTER(AttentionLayerArgs), _P]),
@@ -512,6 +517,27 @@ def decode_attention_static_scratch(out, lse, q_prepared, cache_k, cache_v, cfg:
 def decode_layer_step(args: LayerStepArgs, stream=None, check: bool = True) -> int:
     code = load_library().b200kv_decode_layer_step_bf16(ctypes.byref(args), _stream(stream))
     return _check(code, "b200kv_decode_layer_step_bf16", check)
+
+
+def layer_step_launches(args: LayerStepArgs) -> int:
+    return load_library().b200kv_layer_step_launches(ctypes.byref(args))
+
+
+def decode_layer_step_tiled(args: LayerStepArgs, stream=None, check: bool = True) -> int:
+    """The layer-step as one launch of the per-(sequence, KV head, key range) kernel; needs args.ticket."""
+    code = load_library().b200kv_decode_layer_step_tiled_bf16(ctypes.byref(args), _stream(stream))
+    return _check(code, "b200kv_decode_layer_step_tiled_bf16", check)
+
+
+def decode_attention_tiled(out, lse, q_prepared, cache_k, cache_v, cfg: KvConfig, page_table, seq_lengths,
+                           cache_layer: int, softmax_scale: float, num_splits: int, batch_count: int, q_heads: int,
+                           partial_m, partial_l, partial_acc, ticket, status=None, stream=None,
+                           check: bool = True) -> int:
+    code = load_library().b200kv_decode_attention_tiled_bf16(
+        _ptr(out), _ptr(lse), _ptr(q_prepared), _ptr(cache_k), _ptr(cache_v), cfg, _ptr(page_table),
+        _ptr(seq_lengths), cache_layer, softmax_scale, num_splits, batch_count, q_heads, _ptr(partial_m),
+        _ptr(partial_l), _ptr(partial_acc), _ptr(ticket), _ptr(status), _stream(stream))
+    return _check(code, "b200kv_decode_attention_tiled_bf16", check)
 
 
 def decode_step(layers, layer_count: int, stream=None, check: bool = True) -> int:

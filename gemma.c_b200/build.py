@@ -18,7 +18,7 @@ BUILD_DIR = PKG_DIR / "_build"
 LIB_PATH = BUILD_DIR / "libgemma4_b200kv.so"
 STAMP_PATH = BUILD_DIR / "libgemma4_b200kv.sha256"
 
-SOURCES = ["decode_attention.cu", "decode_balanced.cu", "decode_gqa16.cu", "decode_no_alloc.cu", "decode_projection.cu", "peer_gather.cu", "bounded_wait.cu", "append_prep.cu", "prefill_attention.cu", "prefill_attention_sm100.cu", "fp8_cache.cu", "host_api.cu"]
+SOURCES = ["decode_attention.cu", "decode_balanced.cu", "decode_pagetile.cu", "decode_gqa16.cu", "decode_no_alloc.cu", "decode_projection.cu", "peer_gather.cu", "bounded_wait.cu", "append_prep.cu", "prefill_attention.cu", "prefill_attention_sm100.cu", "fp8_cache.cu", "host_api.cu"]
 NVCC_FLAGS = [
     "-std=c++17",
     "-O3",

@@ -1,0 +1,772 @@
+// Decode layer-step by (sequence, KV head, range of key tiles), in ONE launch.
+//
+// The balanced kernel (decode_balanced.cu) gives every CTA the rows of all
+// eight KV heads of its keys and leaves the merge of the CTAs' partials to a
+// second launch. That is the right shape when a launch streams hundreds of MB.
+// For small jobs -- a sliding-window layer of a few sequences, a batch-1 layer,
+// the share of one rank of a sharded batch -- the fixed costs decide: sixteen
+// partial rows per CTA (16 KiB against the 32 KiB of keys a small CTA streams),
+// a second kernel that waits for the first, and query rows prepared again for
+// every sequence a range touches. Here:
+//
+//  * A CTA owns one KV head of one sequence over a contiguous range of its live
+//    keys. Its two query rows are prepared once. The head's rows are 512-byte
+//    slices of the cache's 4 KiB token rows; a TMA tensor map over
+//    [dim][head][page offset][page] fetches the slices of up to 16 tokens of a
+//    page as one tile (cp.async.bulk.tensor.4d, completion on an mbarrier, no
+//    multicast), two tiles per 32-token stage and tensor, three stages.
+//  * Eight consumer warps take four tokens of a stage each (the arithmetic of
+//    decode_common.cuh), merge their running (m, l, acc) through the idle ring
+//    at the end, and the CTA leaves ONE partial of two rows (2 KiB).
+//  * The last CTA of a (sequence, head) to arrive -- a ticket per pair, taken
+//    with a fence on either side -- merges that pair's partials and writes the
+//    two output rows and their log-sum-exp: what phase_decode_paged_reduce does
+//    behind a grid-wide barrier (src/gemma4_flash_attention_decode.cu:881-977),
+//    without a second launch. A pair with a single range writes its rows
+//    directly.
+//  * The step's append is fused as in the balanced kernel: warps 0..3 prepare
+//    the two query rows and, in the CTA whose range holds the new position,
+//    the K and V row (prep_common.cuh: the append kernel's arithmetic, so the
+//    same bits); the new row is patched into the stage the tile arrived in and
+//    written to the cache after the wait for the preceding kernel.
+//
+// Works for any number of KV heads (the caches of KV-head-sharded ranks
+// included). Ranges are cut per sequence, so it is chosen when the live keys of
+// the sequences are equal by construction (sliding windows) or there is one
+// sequence; ragged batches stay on the balanced partition.
+//
+// Programmatic dependent launch follows decode_balanced.cu: before its
+// griddepcontrol.wait a CTA reads lengths, positions, page-table entries, raw
+// projections (unless they come from the preceding kernel) and key tiles older
+// than the page of the previous step's newest key; everything it writes
+// (prepared q, cache rows, partials, tickets, outputs) and the newest tiles
+// come after. The dependent launch is released by a warp that has itself waited
+// for the preceding kernel, so at most two kernels are in flight.
+#include <cuda.h>
+
+#include <algorithm>
+#include <cstdlib>
+#include <cstring>
+
+#include "balanced_partition.cuh"
+#include "decode_common.cuh"
+#include "kernels.cuh"
+#include "prep_common.cuh"
+
+namespace b200kv {
+
+namespace {
+
+using TileTraits = DecodeTraits<256, 1, 2, 8>;  // one head: 8 warps x 4 tokens
+constexpr int kTileStage = TileTraits::kStageTokens;  // 32 tokens
+constexpr int kMaxTileTokens = 16;                    // tokens of one TMA tile
+constexpr int kMaxRanges = 296;                       // partials per (sequence, head)
+// Above this many sequences a sliding-window layer is a bandwidth job and stays
+// on the balanced partition (see decode_pagetile_preferred).
+constexpr int kPagetileMaxBatch = 32;
+constexpr int kTileConsumerThreads = TileTraits::kConsumerWarps * kWarpSize;
+// 8 consumer warps, the producer warp, and a warp that does nothing but wait
+// for the preceding kernel and then release the next one (see the kernel).
+constexpr int kTileThreads = TileTraits::kThreads + kWarpSize;
+constexpr int kTileExtraBytes = 4 * 512 + 64;  // q rows, new K/V rows, flags
+constexpr int kTileSmemBytes = TileTraits::kRingBytes + kTileExtraBytes;
+static_assert(TileTraits::kRingBytes % 128 == 0, "rows behind the ring stay aligned");
+static_assert(2 * (kTileSmemBytes + 1024) <= 228 * 1024, "two CTAs per SM");
+
+struct TileParams {
+  __nv_bfloat16 *out;
+  float *lse;
+  const __nv_bfloat16 *q;  // attention only: the prepared q
+  __nv_bfloat16 *cache_k;  // fused: the new rows are written here
+  __nv_bfloat16 *cache_v;
+  Gemma4KvCacheConfig cfg;
+  const int32_t *page_table;
+  const int32_t *seq_lengths;
+  int32_t layer;
+  float scale_log2;
+  int32_t batch_count;
+  int32_t q_heads;
+  float *partial_m;
+  float *partial_l;
+  float *partial_acc;
+  uint32_t *ticket;     // [batch * kv_heads], zero between launches
+  int32_t ranges;       // key ranges (CTAs) per sequence and head
+  int32_t tile_tokens;  // tokens of one TMA tile: min(page_size, 16)
+  int32_t *status;
+  // fused modes
+  const __nv_bfloat16 *raw_q;
+  const __nv_bfloat16 *raw_k;
+  const __nv_bfloat16 *raw_v;
+  const __nv_bfloat16 *q_norm_weight;
+  const __nv_bfloat16 *k_norm_weight;
+  const float *cos;
+  const float *sin;
+  const int32_t *token_position;
+  __nv_bfloat16 *q_prepared;
+  int32_t raw_from_predecessor;
+  // Non-zero: the kernels that may still be in flight when this one starts do
+  // not write this layer's cache (they belong to another layer's step), so no
+  // tile has to wait for them.
+  int32_t cache_settled;
+};
+
+// One tile: the 512-byte slices of head `head` for `tile_tokens` tokens of a
+// page, starting at offset `offset` (a multiple of the tile size). The inner
+// coordinate is 0, so the 16-byte rule of TMA starts holds by construction.
+__device__ __forceinline__ void tma_load_tile(uint32_t dst, const CUtensorMap *map,
+                                              int head, int offset, int page,
+                                              uint32_t bar, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      ".L2::cache_hint [%0], [%1, {%2, %3, %4, %5}], [%6], %7;" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(0), "r"(head), "r"(offset), "r"(page),
+      "r"(bar), "l"(policy)
+      : "memory");
+}
+
+template <int kMode>
+__global__ __launch_bounds__(kTileThreads, 2) void decode_pagetile_kernel(
+    TileParams p, const __grid_constant__ CUtensorMap map_k,
+    const __grid_constant__ CUtensorMap map_v) {
+  using T = TileTraits;
+  constexpr int D = 256;
+  constexpr int ST = kTileStage;
+  constexpr bool kFused = kMode != kAttentionOnly;
+  constexpr bool kIeee = kMode == kFusedIeee;
+  extern __shared__ __align__(128) uint8_t smem[];
+  __nv_bfloat16 *s_q = reinterpret_cast<__nv_bfloat16 *>(smem + T::kRingBytes);  // [2][256]
+  __nv_bfloat16 *s_new = s_q + 2 * D;  // [2][256]: the new K row, the new V row
+  volatile int *s_flag = reinterpret_cast<volatile int *>(s_new + 2 * D);  // abort, last
+
+  const int warp = int(threadIdx.x) >> 5;
+  const int lane = int(threadIdx.x) & 31;
+  const Gemma4KvCacheConfig &cfg = p.cfg;
+  const int H = cfg.num_heads;
+  const int bid = int(blockIdx.x);
+  const int h = bid % H;
+  const int r = (bid / H) % p.ranges;
+  const int b = bid / (H * p.ranges);
+
+  // Attention only: the successor (the next step's append, or anything else)
+  // waits for this whole grid before it touches a thing.
+  if constexpr (!kFused) pdl_release_successor();
+
+  const Ring<T> ring(smem);
+  if (threadIdx.x == 0) {
+    ring.init_barriers();
+    s_flag[0] = 0;
+    s_flag[1] = 0;
+  }
+  // The raw row a prep warp works on depends on nothing but (b, h): fetched
+  // first, so that it lands under the length and position loads.
+  [[maybe_unused]] float x[D / 32];
+  [[maybe_unused]] const __nv_bfloat16 *raw_row = nullptr;
+  if constexpr (kFused) {
+    if (warp < 4) {
+      const int64_t kv_src = (int64_t(b) * H + h) * D;
+      raw_row = warp < 2 ? p.raw_q + (int64_t(b) * p.q_heads + h * 2 + warp) * D
+                         : (warp == 2 || p.raw_v == nullptr ? p.raw_k + kv_src
+                                                            : p.raw_v + kv_src);
+      if (!p.raw_from_predecessor) load_head<D>(raw_row, lane, x);
+    }
+  }
+  // A short page-table row (a sliding-window ring) is fetched whole by the
+  // producer warp before the length is known, four entries per lane: one
+  // dependent round trip less before the first tile can be asked for.
+  const int mpps = cfg.max_pages_per_seq;
+  const bool small_table = mpps <= 4 * kWarpSize;
+  int table_regs[4] = {-1, -1, -1, -1};
+  if (warp == T::kConsumerWarps && small_table) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      if (lane * 4 + k < mpps) {
+        table_regs[k] = __ldg(p.page_table + int64_t(b) * mpps + lane * 4 + k);
+      }
+    }
+  }
+  const int len = __ldg(p.seq_lengths + b);
+  int new_pos = -1;
+  if constexpr (kFused) new_pos = __ldg(p.token_position + b);
+  __syncthreads();  // barriers and flags are set
+
+  // The live keys and this CTA's share of them, in chunks of one stage (32
+  // positions, aligned in position space).
+  const int first = cfg.window_size > 0 ? max(0, len - cfg.window_size) : 0;
+  const int count = max(0, len - first);
+  const int chunk_lo = first / ST;
+  const int chunks_total = count > 0 ? (len - 1) / ST - chunk_lo + 1 : 0;
+  const int r_eff = min(p.ranges, chunks_total);
+  // Ranges beyond the live chunks have nothing to do. Range 0 always stays: it
+  // writes the rows of an empty sequence and keeps "this grid is complete
+  // implies its predecessors are" (every CTA that stays waits before it exits).
+  if (r >= max(r_eff, 1)) return;
+  const int c0 = r_eff > 0 ? chunk_lo + int(int64_t(r) * chunks_total / r_eff) : 0;
+  const int c1 = r_eff > 0 ? chunk_lo + int(int64_t(r + 1) * chunks_total / r_eff) : 0;
+  const int nchunks = c1 - c0;
+  const bool new_live = kFused && new_pos >= first && new_pos < len;
+  const bool owns_new = new_live && new_pos / ST >= c0 && new_pos / ST < c1;
+  // a new position that is not a live key of the attention (lengths and
+  // positions that do not belong together): range 0 appends it all the same
+  const bool preps_kv = owns_new || (kFused && new_pos >= 0 && !new_live && r == 0);
+
+  if (warp == T::kConsumerWarps + 1) {
+    // ------------------------------ sentinel ------------------------------
+    // The next kernel may start once the kernel BEFORE this one is complete:
+    // then only this kernel's writes are still in flight, which is what the
+    // next kernel's early reads allow for (it leaves the page of this step's
+    // new key, and everything it writes, for after its own wait). A warp of its
+    // own passes that on as soon as it is true, however far this CTA's stream is.
+    if constexpr (kFused) {
+      pdl_wait_for_predecessor();
+      pdl_release_successor();
+    }
+    return;
+  }
+  if (warp == T::kConsumerWarps) {
+    // ------------------------------ producer ------------------------------
+    const uint64_t policy = l2_policy_evict_first();
+    const int tb = p.tile_tokens;
+    const int tiles = ST / tb;
+    const int ps = cfg.page_size;
+    // first position of the first page the preceding kernels may have written
+    const int newest = max(len - (kFused ? 2 : 1), 0);
+    const int fresh = (kFused && p.cache_settled) ? len : (newest / ps) * ps;
+    bool ok = true;
+    bool waited = false;
+    int cached_lp = -1, cached_phys = -1;
+    int issued = 0;
+    for (int c = 0; c < nchunks; ++c) {
+      const int base = (c0 + c) * ST;
+      if (!waited && min(len, base + ST) > fresh) {
+        pdl_wait_for_predecessor();
+        waited = true;
+      }
+      const int stage = c % kStages;
+      const int fill = c / kStages;
+      if (fill > 0 &&
+          !mbar_wait_bounded(ring.empty_bar(stage), uint32_t(fill - 1) & 1u)) {
+        ok = false;
+        break;
+      }
+      const int pos0 = base + lane * tb;
+      const int live0 = max(pos0, first);
+      const int live1 = min(pos0 + tb, len);
+      const bool mine = lane < tiles && live0 < live1;
+      int phys = -1;
+      if (small_table) {
+        const int slot = mine ? (pos0 / ps) % mpps : 0;
+        const int e0 = __shfl_sync(0xffffffffu, table_regs[0], slot >> 2);
+        const int e1 = __shfl_sync(0xffffffffu, table_regs[1], slot >> 2);
+        const int e2 = __shfl_sync(0xffffffffu, table_regs[2], slot >> 2);
+        const int e3 = __shfl_sync(0xffffffffu, table_regs[3], slot >> 2);
+        const int e = (slot & 2) ? ((slot & 1) ? e3 : e2) : ((slot & 1) ? e1 : e0);
+        phys = mine ? e : -1;
+      } else if (mine) {
+        const int lp = pos0 / ps;
+        if (lp != cached_lp) {
+          cached_phys = __ldg(p.page_table + int64_t(b) * mpps + lp % mpps);
+          cached_lp = lp;
+        }
+        phys = cached_phys;
+      }
+      const bool valid = mine && phys >= 0 && phys < cfg.num_pages;
+      const uint32_t bits =
+          valid ? ((1u << (live1 - live0)) - 1u) << (live0 - base) : 0u;
+      const uint32_t mask = __reduce_or_sync(0xffffffffu, bits);
+      const int nvalid = __popc(__ballot_sync(0xffffffffu, valid));
+      if (lane == 0) {
+        ring.masks()[stage] = mask;
+        if (nvalid > 0) {
+          mbar_arrive_expect_tx(ring.full_bar(stage),
+                                uint32_t(nvalid) * 2u * uint32_t(tb) * T::kRowBytes);
+        } else {
+          mbar_arrive(ring.full_bar(stage));
+        }
+      }
+      __syncwarp();
+      if (valid) {
+        const uint32_t dst = ring.k_stage(stage) + uint32_t(lane * tb) * T::kRowBytes;
+        const int page = p.layer * cfg.num_pages + phys;
+        tma_load_tile(dst, &map_k, h, pos0 % ps, page, ring.full_bar(stage), policy);
+        tma_load_tile(dst + T::kStageTensorBytes, &map_v, h, pos0 % ps, page,
+                      ring.full_bar(stage), policy);
+      }
+      issued = c + 1;
+    }
+    // hold the CTA until every copy this warp issued has landed
+    for (int s = 0; s < kStages && s < issued; ++s) {
+      const int fill = (issued - 1 - s) / kStages;
+      if (!mbar_wait_bounded(ring.full_bar(s), uint32_t(fill) & 1u)) ok = false;
+    }
+    if (!waited) pdl_wait_for_predecessor();
+    if (!ok && lane == 0) set_status(p.status, B200KV_STATUS_WAIT_TIMEOUT);
+    return;
+  }
+
+  // -------------------------------- consumers --------------------------------
+  // Prologue: the two query rows of this head (and, where this CTA appends, the
+  // new K and V row) into shared memory; warps 0..3 work in parallel.
+  [[maybe_unused]] int new_page = -1;
+  if constexpr (kFused) {
+    if (warp < 4) {
+      if (p.raw_from_predecessor) {
+        pdl_wait_for_predecessor();
+        load_head<D>(raw_row, lane, x);
+      }
+      __nv_bfloat16 y[D / 32];
+      if (warp < 2) {
+        if (new_pos >= 0) {
+          prep_weighted_rope_values<D, D, kIeee>(y, x, p.q_norm_weight,
+                                                 p.cos + int64_t(new_pos) * (D / 2),
+                                                 p.sin + int64_t(new_pos) * (D / 2), lane);
+          store_head<D>(s_q + warp * D, y, lane);
+        } else {  // no append for this sequence: q is what the caller left there
+          reinterpret_cast<uint4 *>(s_q + warp * D)[lane] = __ldg(
+              reinterpret_cast<const uint4 *>(
+                  p.q_prepared + (int64_t(b) * p.q_heads + h * 2 + warp) * D) +
+              lane);
+        }
+      } else if (preps_kv) {
+        // the row's page: unmapped means nothing is appended
+        // (src/gemma4_flash_attention_decode.cu:333-338)
+        const int e = __ldg(p.page_table + int64_t(b) * cfg.max_pages_per_seq +
+                            (new_pos / cfg.page_size) % cfg.max_pages_per_seq);
+        new_page = (e >= 0 && e < cfg.num_pages) ? e : -1;
+        if (warp == 2) {
+          prep_weighted_rope_values<D, D, kIeee>(y, x, p.k_norm_weight,
+                                                 p.cos + int64_t(new_pos) * (D / 2),
+                                                 p.sin + int64_t(new_pos) * (D / 2), lane);
+        } else {
+          prep_scale_free_values<D, kIeee>(y, x);
+        }
+        store_head<D>(s_new + (warp - 2) * D, y, lane);
+      }
+    }
+  } else {
+    pdl_wait_for_predecessor();  // q comes from the append
+    if (warp < 2) {
+      reinterpret_cast<uint4 *>(s_q + warp * D)[lane] = __ldg(
+          reinterpret_cast<const uint4 *>(
+              p.q + (int64_t(b) * p.q_heads + h * 2 + warp) * D) +
+          lane);
+    }
+  }
+  named_barrier_sync(1, kTileConsumerThreads);
+
+  WarpState<T> st;
+  {
+    uint4 raw[2];
+    raw[0] = reinterpret_cast<const uint4 *>(s_q)[lane];
+    raw[1] = reinterpret_cast<const uint4 *>(s_q + D)[lane];
+    st.set_q(raw, p.scale_log2);
+  }
+  st.reset();
+  bool ok = true;
+  for (int c = 0; c < nchunks; ++c) {
+    const int stage = c % kStages;
+    const int fill = c / kStages;
+    if (!mbar_wait_bounded(ring.full_bar(stage), uint32_t(fill) & 1u)) {
+      ok = false;
+      break;
+    }
+    if constexpr (kFused) {
+      // The stage that holds the new key: the tile brought whatever the cache
+      // had there; the warp that owns the token's slot replaces the row by the
+      // prepared one (no other warp reads that slot). The slot's mask bit is set
+      // exactly when its page is mapped.
+      if (owns_new && c0 + c == new_pos / ST) {
+        const int slot = new_pos % ST;
+        if (warp == slot / kTokPerWarp && ((ring.masks()[stage] >> slot) & 1ull) != 0ull) {
+          uint8_t *k_row = smem + stage * T::kStageBytes + slot * T::kRowBytes;
+          const uint4 *rows = reinterpret_cast<const uint4 *>(s_new);
+          reinterpret_cast<uint4 *>(k_row)[lane] = rows[lane];
+          reinterpret_cast<uint4 *>(k_row + T::kStageTensorBytes)[lane] = rows[32 + lane];
+          fence_proxy_async_shared();  // the next fill of the stage is a bulk copy
+          __syncwarp();
+        }
+      }
+    }
+    consume_stage<T>(st, ring, stage, 0, warp, lane);
+    __syncwarp();
+    if (lane == 0) mbar_arrive(ring.empty_bar(stage));
+  }
+  if (!ok && lane == 0) {
+    set_status(p.status, B200KV_STATUS_WAIT_TIMEOUT);
+    s_flag[0] = 1;
+  }
+
+  // Merge of the eight warps through the ring (idle once every warp is past its
+  // last stage): thread t ends with dim t of both rows.
+  float l[2];
+  st.denominators(l, lane);
+  float *x_acc = reinterpret_cast<float *>(smem);         // [8][2][256]
+  float *x_m = x_acc + T::kConsumerWarps * 2 * D;          // [8][2]
+  float *x_l = x_m + T::kConsumerWarps * 2;                // [8][2]
+  float *s_m = x_l + T::kConsumerWarps * 2;                // [kMaxRanges][2]
+  float *s_l = s_m + kMaxRanges * 2;                       // [kMaxRanges][2]
+  named_barrier_sync(1, kTileConsumerThreads);
+#pragma unroll
+  for (int g = 0; g < 2; ++g) {
+    float4 *dst = reinterpret_cast<float4 *>(x_acc + (warp * 2 + g) * D) + lane * 2;
+    dst[0] = make_float4(st.acc[g][0], st.acc[g][1], st.acc[g][2], st.acc[g][3]);
+    dst[1] = make_float4(st.acc[g][4], st.acc[g][5], st.acc[g][6], st.acc[g][7]);
+    if (lane == 0) {
+      x_m[warp * 2 + g] = st.m[g];
+      x_l[warp * 2 + g] = l[g];
+    }
+  }
+  named_barrier_sync(1, kTileConsumerThreads);
+  const int t = int(threadIdx.x);  // 0..255: the dim this thread finishes
+  float M[2], L[2], A[2];
+#pragma unroll
+  for (int g = 0; g < 2; ++g) {
+    M[g] = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < T::kConsumerWarps; ++w) M[g] = fmaxf(M[g], x_m[w * 2 + g]);
+    L[g] = 0.0f;
+    A[g] = 0.0f;
+#pragma unroll
+    for (int w = 0; w < T::kConsumerWarps; ++w) {
+      const float mw = x_m[w * 2 + g];
+      const float wt = mw == -INFINITY ? 0.0f : ex2_approx(mw - M[g]);
+      L[g] = fmaf(x_l[w * 2 + g], wt, L[g]);
+      A[g] = fmaf(x_acc[(w * 2 + g) * D + t], wt, A[g]);
+    }
+  }
+
+  // Everything below writes memory the preceding kernel may still use.
+  pdl_wait_for_predecessor();
+  if (s_flag[0] != 0) return;  // a wait ran out in this CTA: the status word says so
+
+  if constexpr (kFused) {
+    if (warp < 2 && r == 0 && new_pos >= 0) {
+      reinterpret_cast<uint4 *>(p.q_prepared +
+                                (int64_t(b) * p.q_heads + h * 2 + warp) * D)[lane] =
+          reinterpret_cast<const uint4 *>(s_q + warp * D)[lane];
+    } else if ((warp == 2 || warp == 3) && preps_kv && new_page >= 0) {
+      const int64_t off =
+          cache_offset(cfg, p.layer, new_page,
+                       new_pos - (new_pos / cfg.page_size) * cfg.page_size, h, 0);
+      __nv_bfloat16 *dst = (warp == 2 ? p.cache_k : p.cache_v) + off;
+      reinterpret_cast<uint4 *>(dst)[lane] =
+          reinterpret_cast<const uint4 *>(s_new + (warp - 2) * D)[lane];
+    }
+  }
+
+  auto write_rows = [&]() {
+#pragma unroll
+    for (int g = 0; g < 2; ++g) {
+      const int64_t row = int64_t(b) * p.q_heads + h * 2 + g;
+      const float inv = L[g] > 0.0f ? 1.0f / L[g] : 0.0f;
+      p.out[row * D + t] = __float2bfloat16_rn(A[g] * inv);
+      if (p.lse != nullptr && t == 0) {
+        p.lse[row] = L[g] > 0.0f ? (M[g] + lg2_approx(L[g])) * 0.6931471805599453f
+                                 : -INFINITY;
+      }
+    }
+  };
+  if (r_eff <= 1) {  // the only range of its (sequence, head), or no live key
+    write_rows();
+    return;
+  }
+
+  // One partial of two rows, then the ticket: the last CTA of the pair merges.
+  const int64_t pair = (int64_t(b) * H + h) * p.ranges;  // first slot of the pair
+#pragma unroll
+  for (int g = 0; g < 2; ++g) {
+    const int64_t slot = (pair + r) * 2 + g;
+    p.partial_acc[slot * D + t] = A[g];
+    if (t == 0) {
+      p.partial_m[slot] = M[g];
+      p.partial_l[slot] = L[g];
+    }
+  }
+  // The CTA's partial is complete in every thread's view after the barrier; one
+  // acq_rel atomic at GPU scope then publishes it (release: the writes the
+  // barrier ordered before it) and, for the CTA that arrives last, makes the
+  // other CTAs' partials visible (acquire).
+  named_barrier_sync(1, kTileConsumerThreads);
+  if (t == 0) {
+    uint32_t before;
+    asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], %2;"
+                 : "=r"(before)
+                 : "l"(p.ticket + int64_t(b) * H + h), "r"(1u)
+                 : "memory");
+    s_flag[1] = before == uint32_t(r_eff - 1) ? 1 : 0;
+  }
+  named_barrier_sync(1, kTileConsumerThreads);
+  if (s_flag[1] == 0) return;
+  // Merge of the pair's r_eff partials. Thread t owns four dims (t % 64) of row
+  // (t / 64) % 2 and every second partial, parity t / 128: all its loads are
+  // independent and go out together (the first eight before the weights are
+  // known). The partials were written by other SMs: read them past L1 (a line
+  // of the same scratch may sit there from an earlier launch).
+  constexpr int kPre = 8;
+  const int col = t & 63;
+  const int g = (t >> 6) & 1;
+  const int parity = t >> 7;
+  const float4 *mine = reinterpret_cast<const float4 *>(p.partial_acc) + col;
+  auto acc_of = [&](int i) {  // partial i of row g, this thread's four dims
+    return __ldcg(mine + ((pair + i) * 2 + g) * (D / 4));
+  };
+  float4 pre[kPre];
+#pragma unroll
+  for (int j = 0; j < kPre; ++j) {
+    const int i = parity + 2 * j;
+    pre[j] = i < r_eff ? acc_of(i) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  for (int i = t; i < 2 * r_eff; i += kTileConsumerThreads) {
+    s_m[i] = __ldcg(p.partial_m + pair * 2 + i);
+    s_l[i] = __ldcg(p.partial_l + pair * 2 + i);
+  }
+  named_barrier_sync(1, kTileConsumerThreads);
+  float top = -INFINITY;
+  for (int i = 0; i < r_eff; ++i) top = fmaxf(top, s_m[i * 2 + g]);
+  float sum = 0.0f;
+  for (int i = 0; i < r_eff; ++i) {
+    const float li = s_l[i * 2 + g];
+    if (li > 0.0f) sum = fmaf(li, ex2_approx(s_m[i * 2 + g] - top), sum);
+  }
+  float4 value = make_float4(0.f, 0.f, 0.f, 0.f);
+  auto add = [&](const float4 &a, int i) {
+    const float w = s_l[i * 2 + g] > 0.0f ? ex2_approx(s_m[i * 2 + g] - top) : 0.0f;
+    if (w > 0.0f) {  // a partial without mass is dropped whatever it holds
+      value.x = fmaf(a.x, w, value.x);
+      value.y = fmaf(a.y, w, value.y);
+      value.z = fmaf(a.z, w, value.z);
+      value.w = fmaf(a.w, w, value.w);
+    }
+  };
+#pragma unroll
+  for (int j = 0; j < kPre; ++j) {
+    if (parity + 2 * j < r_eff) add(pre[j], parity + 2 * j);
+  }
+  for (int i0 = parity + 2 * kPre; i0 < r_eff; i0 += 2 * kPre) {
+    float4 a[kPre];
+#pragma unroll
+    for (int j = 0; j < kPre; ++j) {
+      a[j] = i0 + 2 * j < r_eff ? acc_of(i0 + 2 * j) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int j = 0; j < kPre; ++j) {
+      if (i0 + 2 * j < r_eff) add(a[j], i0 + 2 * j);
+    }
+  }
+  // the two parities meet in shared memory (the warps' exchange area is idle)
+  float4 *x_sum = reinterpret_cast<float4 *>(x_acc);
+  if (parity == 1) x_sum[t - 128] = value;
+  named_barrier_sync(1, kTileConsumerThreads);
+  if (parity == 0) {
+    const float4 o = x_sum[t];
+    const float inv = sum > 0.0f ? 1.0f / sum : 0.0f;
+    const int64_t row = int64_t(b) * p.q_heads + h * 2 + g;
+    const __nv_bfloat162 lo =
+        __floats2bfloat162_rn((value.x + o.x) * inv, (value.y + o.y) * inv);
+    const __nv_bfloat162 hi =
+        __floats2bfloat162_rn((value.z + o.z) * inv, (value.w + o.w) * inv);
+    reinterpret_cast<uint2 *>(p.out + row * D)[col] =
+        make_uint2(*reinterpret_cast<const uint32_t *>(&lo),
+                   *reinterpret_cast<const uint32_t *>(&hi));
+    if (p.lse != nullptr && col == 0) {
+      p.lse[row] = sum > 0.0f ? (top + lg2_approx(sum)) * 0.6931471805599453f : -INFINITY;
+    }
+  }
+  if (t == 0) p.ticket[int64_t(b) * H + h] = 0u;  // ready for the next launch
+}
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                   const cuuint64_t *, const cuuint64_t *,
+                                   const cuuint32_t *, const cuuint32_t *,
+                                   CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void *ptr = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault,
+                                &result) != cudaSuccess ||
+        result != cudaDriverEntryPointSuccess) {
+      return EncodeTiledFn(nullptr);
+    }
+    return reinterpret_cast<EncodeTiledFn>(ptr);
+  }();
+  return fn;
+}
+
+// The cache as [dim][head][page offset][layer * pages + page] bf16 with tiles of
+// (256 dims, one head, tile_tokens offsets, one page): 512-byte rows, dense in
+// shared memory.
+bool make_cache_map(CUtensorMap *map, const __nv_bfloat16 *base,
+                    const Gemma4KvCacheConfig &c, int tile_tokens) {
+  EncodeTiledFn encode = encode_tiled_fn();
+  if (encode == nullptr) return false;
+  const cuuint64_t row = cuuint64_t(c.head_dim) * 2;
+  const cuuint64_t dims[4] = {cuuint64_t(c.head_dim), cuuint64_t(c.num_heads),
+                              cuuint64_t(c.page_size),
+                              cuuint64_t(c.num_layers) * cuuint64_t(c.num_pages)};
+  const cuuint64_t strides[3] = {row, row * c.num_heads, row * c.num_heads * c.page_size};
+  const cuuint32_t box[4] = {cuuint32_t(c.head_dim), 1, cuuint32_t(tile_tokens), 1};
+  const cuuint32_t elem_strides[4] = {1, 1, 1, 1};
+  return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
+                const_cast<__nv_bfloat16 *>(base), dims, strides, box, elem_strides,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int tile_tokens_of(int page_size) {
+  const int tb = std::min(page_size, kMaxTileTokens);
+  // tiles tile a page and a stage: 32 % tb == 0 and page_size % tb == 0
+  if (tb < 2 || kTileStage % tb != 0 || page_size % tb != 0) return 0;
+  return tb;
+}
+
+// B200KV_PAGETILE: "0" never, "1" wherever the geometry allows, unset: the
+// built-in choice (pagetile_preferred).
+int pagetile_override() {
+  static const int mode = [] {
+    const char *v = std::getenv("B200KV_PAGETILE");
+    if (v == nullptr) return -1;
+    return std::strcmp(v, "0") == 0 ? 0 : 1;
+  }();
+  return mode;
+}
+
+// B200KV_PAGETILE_RANGES=n: tuning aid, n key ranges per (sequence, head).
+int pagetile_ranges_override() {
+  static const int n = [] {
+    const char *v = std::getenv("B200KV_PAGETILE_RANGES");
+    return v == nullptr ? 0 : std::atoi(v);
+  }();
+  return n;
+}
+
+template <int kMode>
+cudaError_t launch_pagetile(const TileParams &p, const CUtensorMap &map_k,
+                            const CUtensorMap &map_v, cudaStream_t stream) {
+  cudaError_t st = cudaFuncSetAttribute(decode_pagetile_kernel<kMode>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        kTileSmemBytes);
+  if (st != cudaSuccess) return st;
+  const int64_t ctas = int64_t(p.batch_count) * p.ranges * p.cfg.num_heads;
+  return launch_pdl(decode_pagetile_kernel<kMode>, dim3(unsigned(ctas)),
+                    dim3(kTileThreads), kTileSmemBytes, stream, p, map_k, map_v);
+}
+
+}  // namespace
+
+bool decode_pagetile_supported(const Gemma4KvCacheConfig &c, int q_heads,
+                               int batch_count) {
+  return c.head_dim == 256 && c.num_heads >= 1 && c.num_heads <= 64 &&
+         q_heads == 2 * c.num_heads && tile_tokens_of(c.page_size) > 0 &&
+         batch_count >= 1 && int64_t(batch_count) * c.num_heads <= (1 << 20);
+}
+
+bool decode_pagetile_preferred(const Gemma4KvCacheConfig &c, int q_heads,
+                               int batch_count, bool has_ticket) {
+  if (!has_ticket || !decode_pagetile_supported(c, q_heads, batch_count)) return false;
+  const int forced = pagetile_override();
+  if (forced >= 0) return forced == 1;
+  // Ranges are cut per sequence: chosen where the sequences' live keys are equal
+  // by construction (a sliding window) or there is one sequence; small jobs only
+  // -- a big batch is bandwidth-bound and streams best through the balanced
+  // partition. With fewer than 8 KV heads (the cache of a KV-head-sharded rank)
+  // a long linear context has too few (sequence, head) pairs: each pair's last
+  // CTA would merge hundreds of partials alone, and the fixed-split kernels with
+  // their parallel combine are faster (measured: 38 against 52 us on the
+  // one-head share of 131072 keys).
+  if (c.window_size > 0) return batch_count <= kPagetileMaxBatch;
+  return batch_count == 1 && c.num_heads == 8;
+}
+
+cudaError_t decode_layer_step_pagetile_bf16(const AppendArgs *ap, const DecodeArgs &a,
+                                            uint32_t *ticket, cudaStream_t stream) {
+  const Gemma4KvCacheConfig &c = a.cfg;
+  cudaError_t st = validate_decode_args(a);
+  if (st != cudaSuccess) return st;
+  if (ap != nullptr) {
+    st = validate_append_args(*ap);
+    if (st != cudaSuccess) return st;
+    if (ap->rotary_dim != 256 || ap->q_heads != a.q_heads ||
+        ap->batch_count != a.batch_count || ap->cache_layer != a.layer ||
+        ap->page_table != a.page_table || ap->q_prepared != a.q ||
+        ap->cache_k != a.cache_k || ap->cache_v != a.cache_v ||
+        std::memcmp(&ap->cfg, &c, sizeof(c)) != 0 ||
+        (reinterpret_cast<uintptr_t>(ap->q_prepared) & 15u) != 0) {
+      return cudaErrorInvalidValue;
+    }
+  }
+  if (ticket == nullptr || !decode_pagetile_supported(c, a.q_heads, a.batch_count)) {
+    return cudaErrorInvalidValue;
+  }
+  int device = 0, sm_count = 0;
+  st = cudaGetDevice(&device);
+  if (st != cudaSuccess) return st;
+  st = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
+  if (st != cudaSuccess) return st;
+
+  TileParams p = {};
+  p.out = a.out;
+  p.lse = a.lse;
+  p.q = a.q;
+  p.cache_k = const_cast<__nv_bfloat16 *>(a.cache_k);
+  p.cache_v = const_cast<__nv_bfloat16 *>(a.cache_v);
+  p.cfg = c;
+  p.page_table = a.page_table;
+  p.seq_lengths = a.seq_lengths;
+  p.layer = a.layer;
+  p.scale_log2 = a.softmax_scale * 1.4426950408889634f;
+  p.batch_count = a.batch_count;
+  p.q_heads = a.q_heads;
+  p.partial_m = a.partial_m;
+  p.partial_l = a.partial_l;
+  p.partial_acc = a.partial_acc;
+  p.ticket = ticket;
+  p.status = a.status;
+  p.tile_tokens = tile_tokens_of(c.page_size);
+  // Ranges per (sequence, head): enough CTAs for two per SM, no more than the
+  // scratch holds (batch * q_heads * num_splits rows = two rows per range) or
+  // the chunks a sequence can have.
+  const int64_t pairs = int64_t(a.batch_count) * c.num_heads;
+  const int64_t span = c.window_size > 0 ? int64_t(c.window_size)
+                                         : int64_t(c.max_pages_per_seq) * c.page_size;
+  const int64_t max_chunks = span / kTileStage + 2;
+  // ... and at least two chunks per CTA where a sequence is that long: a CTA's
+  // fixed cost (prologue, merge of its warps, its partial) is that of a chunk or
+  // two, and every further partial lengthens the last CTA's merge.
+  int64_t ranges = std::max<int64_t>(1, (2 * int64_t(sm_count)) / pairs);
+  ranges = std::min<int64_t>({ranges, int64_t(kMaxRanges), std::max<int64_t>(1, max_chunks / 2),
+                              std::max<int64_t>(1, a.num_splits)});
+  if (pagetile_ranges_override() > 0) {
+    ranges = std::min<int64_t>({int64_t(pagetile_ranges_override()), int64_t(kMaxRanges),
+                                std::max<int64_t>(1, a.num_splits)});
+  }
+  if (ranges > 1 && (a.partial_m == nullptr || a.partial_l == nullptr ||
+                     a.partial_acc == nullptr)) {
+    return cudaErrorInvalidValue;
+  }
+  p.ranges = int32_t(ranges);
+  CUtensorMap map_k, map_v;
+  if (!make_cache_map(&map_k, a.cache_k, c, p.tile_tokens) ||
+      !make_cache_map(&map_v, a.cache_v, c, p.tile_tokens)) {
+    return cudaErrorInvalidValue;
+  }
+  if (ap == nullptr) return launch_pagetile<kAttentionOnly>(p, map_k, map_v, stream);
+  p.raw_q = ap->q;
+  p.raw_k = ap->k;
+  p.raw_v = ap->v;
+  p.q_norm_weight = ap->q_norm_weight;
+  p.k_norm_weight = ap->k_norm_weight;
+  p.cos = ap->cos;
+  p.sin = ap->sin;
+  p.token_position = ap->token_position;
+  p.q_prepared = ap->q_prepared;
+  p.raw_from_predecessor = ap->raw_from_predecessor ? 1 : 0;
+  p.cache_settled = ap->cache_settled ? 1 : 0;
+  return ap->norm_mode == B200KV_NORM_IEEE
+             ? launch_pagetile<kFusedIeee>(p, map_k, map_v, stream)
+             : launch_pagetile<kFusedApprox>(p, map_k, map_v, stream);
+}
+
+}  // namespace b200kv

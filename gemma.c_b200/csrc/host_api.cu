@@ -947,7 +947,8 @@ namespace {
 // raw_from_predecessor: the raw rows come from the kernel enqueued just before
 // (the attention-layer call's QKV projection), not from an earlier step.
 int layer_step(const B200KvLayerStepArgs *s, bool raw_from_predecessor,
-               b200kv_stream stream) {
+               b200kv_stream stream, bool force_tiled = false,
+               bool cache_settled = false) {
   if (s == nullptr) return cudaErrorInvalidValue;
   using bf = __nv_bfloat16;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -971,6 +972,7 @@ int layer_step(const B200KvLayerStepArgs *s, bool raw_from_predecessor,
   a.rotary_dim = s->rotary_dim;
   a.norm_mode = s->norm_mode;
   a.raw_from_predecessor = raw_from_predecessor;
+  a.cache_settled = cache_settled;
 
   b200kv::DecodeArgs d;
   d.out = reinterpret_cast<bf *>(s->out);
@@ -992,6 +994,30 @@ int layer_step(const B200KvLayerStepArgs *s, bool raw_from_predecessor,
   d.partial_acc = s->partial_acc;
   d.status = s->status;
 
+  // Small jobs: one launch for append + attention + merge, a CTA per (sequence,
+  // KV head, key range) (decode_pagetile.cu); needs the caller's tickets.
+  if (force_tiled && (s->batch_count <= 0 || s->split_size != 0 ||
+                      s->rotary_dim != 256 || s->ticket == nullptr)) {
+    return cudaErrorInvalidValue;
+  }
+  if (force_tiled ||
+      (s->batch_count > 0 && s->split_size == 0 && s->rotary_dim == 256 &&
+       fused_layer_step_enabled() &&
+       b200kv::decode_pagetile_preferred(d.cfg, d.q_heads, d.batch_count,
+                                         s->ticket != nullptr))) {
+    if (s->event_before_attention != nullptr) {
+      B200KV_TRY(cudaEventRecord(
+          static_cast<cudaEvent_t>(s->event_before_attention), st));
+    }
+    const cudaError_t st_tile =
+        b200kv::decode_layer_step_pagetile_bf16(&a, d, s->ticket, st);
+    if (st_tile != cudaSuccess) return st_tile;
+    if (s->event_after_attention != nullptr) {
+      B200KV_TRY(cudaEventRecord(
+          static_cast<cudaEvent_t>(s->event_after_attention), st));
+    }
+    return cudaSuccess;
+  }
   // One launch for append + attention where the balanced kernel can do both
   // (the reference's decode_megakernel_fused_layer_kernel is one launch too,
   // src/gemma4_flash_attention_decode.cu:1004-1031). The profiling hooks then
@@ -1037,11 +1063,75 @@ int b200kv_decode_layer_step_bf16(const B200KvLayerStepArgs *s,
   return layer_step(s, false, stream);
 }
 
+int32_t b200kv_layer_step_launches(const B200KvLayerStepArgs *s) {
+  if (s == nullptr || s->batch_count <= 0) return 0;
+  const Gemma4KvCacheConfig &c = s->cache_config;
+  if (s->split_size == 0 && s->rotary_dim == 256 && fused_layer_step_enabled() &&
+      b200kv::decode_pagetile_preferred(c, s->q_heads, s->batch_count,
+                                        s->ticket != nullptr)) {
+    return 1;
+  }
+  if (s->split_size == 0 && fused_layer_step_enabled() && s->rotary_dim == 256 &&
+      b200kv::decode_balanced_supported(c, s->q_heads, s->batch_count)) {
+    return 2;  // fused attention kernel + combine
+  }
+  return (s->split_size > 0 && s->num_splits == 1) ? 2 : 3;  // append, attention[, combine]
+}
+
+int b200kv_decode_layer_step_tiled_bf16(const B200KvLayerStepArgs *s,
+                                        b200kv_stream stream) {
+  return layer_step(s, false, stream, true);
+}
+
+int b200kv_decode_attention_tiled_bf16(
+    b200kv_bf16 *d_out, float *d_lse, const b200kv_bf16 *d_q_prepared,
+    const b200kv_bf16 *d_cache_k, const b200kv_bf16 *d_cache_v,
+    Gemma4KvCacheConfig cache_config, const int32_t *d_page_table,
+    const int32_t *d_seq_lengths, int32_t cache_layer, float softmax_scale,
+    int32_t num_splits, int32_t batch_count, int32_t q_heads, float *d_partial_m,
+    float *d_partial_l, float *d_partial_acc, uint32_t *d_ticket,
+    int32_t *d_status, b200kv_stream stream) {
+  using bf = __nv_bfloat16;
+  b200kv::DecodeArgs d;
+  d.out = reinterpret_cast<bf *>(d_out);
+  d.lse = d_lse;
+  d.q = reinterpret_cast<const bf *>(d_q_prepared);
+  d.cache_k = reinterpret_cast<const bf *>(d_cache_k);
+  d.cache_v = reinterpret_cast<const bf *>(d_cache_v);
+  d.cfg = cache_config;
+  d.page_table = d_page_table;
+  d.seq_lengths = d_seq_lengths;
+  d.layer = cache_layer;
+  d.softmax_scale = softmax_scale;
+  d.split_size = 0;
+  d.num_splits = num_splits;
+  d.batch_count = batch_count;
+  d.q_heads = q_heads;
+  d.partial_m = d_partial_m;
+  d.partial_l = d_partial_l;
+  d.partial_acc = d_partial_acc;
+  d.status = d_status;
+  return b200kv::decode_layer_step_pagetile_bf16(
+      nullptr, d, d_ticket, static_cast<cudaStream_t>(stream));
+}
+
 int b200kv_decode_step_bf16(const B200KvLayerStepArgs *layers,
                             int32_t layer_count, b200kv_stream stream) {
   if (layers == nullptr || layer_count < 0) return cudaErrorInvalidValue;
   for (int32_t i = 0; i < layer_count; ++i) {
-    const int st = b200kv_decode_layer_step_bf16(layers + i, stream);
+    // From the second layer on, what can still be in flight when a layer's
+    // kernel starts is the step of the layer before it (the kernels here let at
+    // most their direct predecessor's launches overlap them). If that is another
+    // cache layer, nothing in flight writes this layer's cache rows.
+    bool settled = false;
+    if (i > 0) {
+      const B200KvLayerStepArgs &p = layers[i - 1];
+      const B200KvLayerStepArgs &c = layers[i];
+      const bool same_k = p.cache_k == c.cache_k && p.cache_layer == c.cache_layer;
+      const bool same_v = p.cache_v == c.cache_v && p.cache_layer == c.cache_layer;
+      settled = !same_k && !same_v && p.batch_count > 0;
+    }
+    const int st = layer_step(layers + i, false, stream, false, settled);
     if (st != cudaSuccess) return st;
   }
   return cudaSuccess;

@@ -80,6 +80,12 @@ struct AppendArgs {
   // rows before it waits for its predecessor unless this is set. The append
   // kernels wait before anything else.
   bool raw_from_predecessor = false;
+  // The launches that can still be running when this layer-step's kernel starts
+  // (with programmatic dependent launch: the one or two before it on the stream)
+  // are layer-steps of ANOTHER cache layer: none of them writes a row of this
+  // layer's cache, so the kernel need not hold back the page of the newest key.
+  // Only the one-launch layer-step (decode_pagetile.cu) makes use of it.
+  bool cache_settled = false;
 };
 
 cudaError_t decode_append_bf16(const AppendArgs &args, cudaStream_t stream);
@@ -97,6 +103,21 @@ bool decode_fused_supported(const AppendArgs &append, const DecodeArgs &decode);
 cudaError_t decode_layer_step_fused_bf16(const AppendArgs &append,
                                          const DecodeArgs &decode,
                                          cudaStream_t stream);
+
+// One layer-step (or, with append == nullptr, the attention alone) in a single
+// launch: a CTA per (sequence, KV head, key range), TMA tiles of one head's rows,
+// the ranges' partials merged by the last CTA of each (sequence, head) through
+// `ticket` (uint32 [batch * kv_heads], zero between launches). decode_pagetile.cu.
+// _supported: the geometry the kernel is built for (head_dim 256, two query
+// heads per KV head, page sizes that tile into 32); _preferred: where the layer-
+// step picks it over the balanced partition.
+bool decode_pagetile_supported(const Gemma4KvCacheConfig &cfg, int q_heads,
+                               int batch_count);
+bool decode_pagetile_preferred(const Gemma4KvCacheConfig &cfg, int q_heads,
+                               int batch_count, bool has_ticket);
+cudaError_t decode_layer_step_pagetile_bf16(const AppendArgs *append,
+                                            const DecodeArgs &decode,
+                                            uint32_t *ticket, cudaStream_t stream);
 
 // Decode projections either side of the KV path (decode_projection.cu), rows of
 // one token each; hidden size 3840. Weights are column-major: output column c

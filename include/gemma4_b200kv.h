@@ -501,14 +501,59 @@ typedef struct B200KvLayerStepArgs {
    * right before and after that launch and its combine. */
   void *event_before_attention;
   void *event_after_attention;
+  /* Optional: uint32 [batch_count * cache_config.num_heads], zero before the
+   * first call; every call leaves it zero again (unless a bounded wait ran
+   * out, which `status` reports). With it, and split_size == 0, small jobs --
+   * a sliding-window layer of up to 32 sequences, or one sequence on a linear
+   * cache of 8 KV heads (head_dim 256, two query heads per KV head, rotary_dim
+   * 256) -- run as ONE launch: a CTA per (sequence, KV head, key
+   * range) fetches that head's rows as TMA tiles, and the last CTA of each
+   * (sequence, head) to finish merges the ranges' partials, the job of the
+   * reference's grid-wide barrier + reduce phase
+   * (src/gemma4_flash_attention_decode.cu:1017-1031). Results as without it,
+   * within the summation order of the partials. Calls that may overlap on the
+   * GPU need tickets (and scratch) of their own. */
+  uint32_t *ticket;
 } B200KvLayerStepArgs;
 
 int b200kv_decode_layer_step_bf16(const B200KvLayerStepArgs *args,
                                   b200kv_stream stream);
 
+/* How many kernels b200kv_decode_layer_step_bf16 would launch for these
+ * arguments (1: the one-launch form; 2: fused attention + combine, or append +
+ * a single-split attention; 3: append, split attention, combine). */
+int32_t b200kv_layer_step_launches(const B200KvLayerStepArgs *args);
+
+/* The one-launch form chosen explicitly (see `ticket` above): the same
+ * layer-step through the per-(sequence, KV head, key range) kernel whatever
+ * the batch size; cudaErrorInvalidValue without a ticket, with split_size != 0,
+ * or for a geometry it is not built for (head_dim 256, q_heads == 2 * KV heads,
+ * rotary_dim 256, a page size of 2, 4, 8 or a multiple of 16). Key ranges are
+ * cut per sequence, so very uneven lengths leave CTAs idle; the default entry
+ * point picks the balanced partition there. num_splits still sizes the scratch
+ * (two rows per key range and head). */
+int b200kv_decode_layer_step_tiled_bf16(const B200KvLayerStepArgs *args,
+                                        b200kv_stream stream);
+/* The attention alone in that form, on rows already appended and a q already
+ * prepared: arguments of b200kv_decode_attention_bf16 with the balanced
+ * partition's num_splits, plus the tickets. */
+int b200kv_decode_attention_tiled_bf16(
+    b200kv_bf16 *d_out, float *d_lse, const b200kv_bf16 *d_q_prepared,
+    const b200kv_bf16 *d_cache_k, const b200kv_bf16 *d_cache_v,
+    Gemma4KvCacheConfig cache_config, const int32_t *d_page_table,
+    const int32_t *d_seq_lengths, int32_t cache_layer, float softmax_scale,
+    int32_t num_splits, int32_t batch_count, int32_t q_heads, float *d_partial_m,
+    float *d_partial_l, float *d_partial_acc, uint32_t *d_ticket,
+    int32_t *d_status, b200kv_stream stream);
+
 /* One decode step over `layer_count` layers, enqueued in order on `stream`:
  * the layer loop of gemma4_decode_megakernel, src/gemma4_decode_megakernel.cu:172-183,
- * restricted to the KV path (the caller supplies each layer's projections). */
+ * restricted to the KV path (the caller supplies each layer's projections).
+ * Consecutive entries are expected to be different cache layers (caches that
+ * do not overlap in memory), as in the model: a layer's kernel then streams
+ * all of its keys under the tail of the layer before it. Two consecutive
+ * entries with the same cache_k / cache_v and cache_layer are detected and
+ * handled like separate b200kv_decode_layer_step_bf16 calls. */
 int b200kv_decode_step_bf16(const B200KvLayerStepArgs *layers,
                             int32_t layer_count, b200kv_stream stream);
 

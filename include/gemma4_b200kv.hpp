@@ -197,8 +197,10 @@ cudaError_t gemma4_runtime_prepare_decode_step(Gemma4RuntimeState *state,
 // append + decode attention + combine, O projection + post-attention norm +
 // residual + pre-FFN norm on `stream`; the caller's FFN launch follows.
 // `raw_qkv_scratch`: 8704 bf16 per row (the reference reuses attention_out /
-// attention_q for it; here it is a buffer of its own); `ticket`: uint32 per
-// row, zero before the first call. Geometry as the reference derives it from
+// attention_q for it; here it is a buffer of its own); `ticket`: uint32
+// [batch_count * (1 + KV heads)], zero before the first call and left zero by
+// every call (one word per row for the O projection's last-CTA epilogue, then
+// one per row and KV head for the one-launch attention). Geometry as the reference derives it from
 // the cache config: 8 KV heads x 256 (sliding, own V projection, rotary 256) or
 // 1 KV head x 512 (global, V from raw K, rotary 128), 16 query heads.
 template <class LayerArgs>
@@ -238,6 +240,7 @@ inline cudaError_t gemma4_b200kv_decode_attention_layer(
   a.kv.rotary_dim = global_geometry ? 128 : 256;
   a.kv.norm_mode = B200KV_NORM_RSQRT_APPROX;
   a.kv.status = status;
+  a.kv.ticket = ticket != nullptr ? ticket + batch_count : nullptr;
   a.attention_x = bits(args.attention_x);
   a.attention_input_norm_weight = bits(args.attention_input_norm_weight);
   a.attention_qkv_proj_col_major = bits(args.attention_qkv_proj_col_major);

@@ -1,7 +1,10 @@
 """The one-launch layer-step (append fused into the balanced decode kernel) through
 b200kv_decode_layer_step_bf16, against (a) the two-launch form on a second copy of the same state --
 caches, prepared q, attention rows and LSE must be the same bits -- and (b) the CPU oracle: cache bytes
-and prepared q exact, attention within the stated bf16 tolerance.
+and prepared q exact, attention within the stated bf16 tolerance. A third copy of the state runs the same
+steps through b200kv_decode_layer_step_tiled_bf16 (a CTA per sequence, KV head and key range; partials
+merged by the last CTA through tickets): caches and prepared q the same bits again, attention rows within
+the tolerance (another summation order), tickets back at zero after every step.
 
 Covers: sliding ring that wraps every few steps, linear cache, ragged batch, a sequence that is not
 appended (position -1), an unmapped page, lengths that do not contain the new position (the row is
@@ -60,6 +63,8 @@ def _run_steps(kv, orc, *, window, ring_pages, start, steps, norm_mode, has_v=Tr
     num_splits = kv.plan_balanced(B, sms)
     fused = _State(kv, acase, ck, cv, num_splits)
     plain = _State(kv, acase, ck, cv, num_splits)
+    tiled = _State(kv, acase, ck, cv, num_splits)
+    ticket = torch.zeros(B * H, dtype=torch.int32, device="cuda")
     table, qw, kw_ = dev(acase.page_table), dev(acase.q_w), dev(acase.k_w)
     cos, sin = dev(acase.cos), dev(acase.sin)
     scale = 1.0 / 16.0
@@ -86,6 +91,12 @@ def _run_steps(kv, orc, *, window, ring_pages, start, steps, norm_mode, has_v=Tr
         a.status = fused.status.data_ptr()
         kv.decode_layer_step(a)
 
+        a.q, a.out, a.lse = tiled.q.data_ptr(), tiled.out.data_ptr(), tiled.lse.data_ptr()
+        a.partial_m, a.partial_l, a.partial_acc = tiled.pm.data_ptr(), tiled.pl.data_ptr(), tiled.pacc.data_ptr()
+        a.cache_k, a.cache_v = tiled.ck.data_ptr(), tiled.cv.data_ptr()
+        a.status, a.ticket = tiled.status.data_ptr(), ticket.data_ptr()
+        kv.decode_layer_step_tiled(a)
+
         kv.decode_append(plain.q, plain.ck, plain.cv, cfg, table, dpos, 0, dq, dk, dv, qw, kw_, cos, sin, B, HQ, D,
                          norm_mode)
         kv.decode_attention(plain.out, plain.lse, plain.q, plain.ck, plain.cv, cfg, table, dlen, 0, scale, 0,
@@ -97,6 +108,14 @@ def _run_steps(kv, orc, *, window, ring_pages, start, steps, norm_mode, has_v=Tr
         assert torch.equal(fused.q, plain.q), t
         assert torch.equal(fused.out, plain.out), t
         assert torch.equal(fused.lse.view(torch.int32), plain.lse.view(torch.int32)), t
+        assert tiled.status[0].item() == 0 and not ticket.any(), t
+        assert torch.equal(tiled.ck, plain.ck) and torch.equal(tiled.cv, plain.cv), t
+        assert torch.equal(tiled.q, plain.q), t
+        max_abs, max_rel = attention_error(host_u16(tiled.out), orc.bf16_to_f32(host_u16(plain.out)))
+        assert max_abs <= ATTN_MAX_ABS and max_rel <= ATTN_MAX_REL, (t, max_abs, max_rel)
+        la, lb = tiled.lse.cpu().numpy(), plain.lse.cpu().numpy()
+        assert np.array_equal(np.isfinite(la), np.isfinite(lb)), t
+        assert np.abs(la[np.isfinite(la)] - lb[np.isfinite(lb)]).max(initial=0.0) <= LSE_MAX_ABS, t
 
         if norm_mode == kv.NORM_IEEE:            # the host oracle states the IEEE arithmetic
             qp = qp_host.copy()
@@ -109,8 +128,9 @@ def _run_steps(kv, orc, *, window, ring_pages, start, steps, norm_mode, has_v=Tr
                 assert np.array_equal(host_u16(fused.ck), ck) and np.array_equal(host_u16(fused.cv), cv), t
                 assert np.array_equal(host_u16(fused.q), qp.reshape(-1)), t
                 ref, ref_lse = orc.decode_attention_f64(qp, ck, cv, acase.page_table, length, cfg_t, 0, scale, B, HQ)
-                max_abs, max_rel = attention_error(host_u16(fused.out), ref)
-                assert max_abs <= ATTN_MAX_ABS and max_rel <= ATTN_MAX_REL, (t, max_abs, max_rel)
+                for which in (fused, tiled):
+                    max_abs, max_rel = attention_error(host_u16(which.out), ref)
+                    assert max_abs <= ATTN_MAX_ABS and max_rel <= ATTN_MAX_REL, (t, max_abs, max_rel)
                 got_lse = fused.lse.cpu().numpy()
                 fin = np.isfinite(ref_lse)
                 assert np.array_equal(np.isneginf(got_lse), np.isneginf(ref_lse))
