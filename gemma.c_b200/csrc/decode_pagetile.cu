@@ -64,6 +64,7 @@ constexpr int kMaxRanges = 296;                       // partials per (sequence,
 // Above this many sequences a sliding-window layer is a bandwidth job and stays
 // on the balanced partition (see decode_pagetile_preferred).
 constexpr int kPagetileMaxBatch = 32;
+constexpr int kPagetileMaxLinearKeys = 32768;
 constexpr int kTileConsumerThreads = TileTraits::kConsumerWarps * kWarpSize;
 // 8 consumer warps, the producer warp, and a warp that does nothing but wait
 // for the preceding kernel and then release the next one (see the kernel).
@@ -362,18 +363,12 @@ __global__ __launch_bounds__(kTileThreads, 2) void decode_pagetile_kernel(
   }
   st.reset();
   bool ok = true;
-  for (int c = 0; c < nchunks; ++c) {
-    const int stage = c % kStages;
-    const int fill = c / kStages;
-    if (!mbar_wait_bounded(ring.full_bar(stage), uint32_t(fill) & 1u)) {
-      ok = false;
-      break;
-    }
+  // The stage that holds the new key: the tile brought whatever the cache had
+  // there; the warp that owns the token's slot replaces the row by the prepared
+  // one (no other warp reads that slot). The slot's mask bit is set exactly when
+  // its page is mapped.
+  auto patch_new_row = [&](int c, int stage) {
     if constexpr (kFused) {
-      // The stage that holds the new key: the tile brought whatever the cache
-      // had there; the warp that owns the token's slot replaces the row by the
-      // prepared one (no other warp reads that slot). The slot's mask bit is set
-      // exactly when its page is mapped.
       if (owns_new && c0 + c == new_pos / ST) {
         const int slot = new_pos % ST;
         if (warp == slot / kTokPerWarp && ((ring.masks()[stage] >> slot) & 1ull) != 0ull) {
@@ -386,6 +381,14 @@ __global__ __launch_bounds__(kTileThreads, 2) void decode_pagetile_kernel(
         }
       }
     }
+  };
+  for (int c = 0; c < nchunks; ++c) {
+    const int stage = c % kStages;
+    if (!mbar_wait_bounded(ring.full_bar(stage), uint32_t(c / kStages) & 1u)) {
+      ok = false;
+      break;
+    }
+    patch_new_row(c, stage);
     consume_stage<T>(st, ring, stage, 0, warp, lane);
     __syncwarp();
     if (lane == 0) mbar_arrive(ring.empty_bar(stage));
@@ -501,7 +504,7 @@ __global__ __launch_bounds__(kTileThreads, 2) void decode_pagetile_kernel(
   // independent and go out together (the first eight before the weights are
   // known). The partials were written by other SMs: read them past L1 (a line
   // of the same scratch may sit there from an earlier launch).
-  constexpr int kPre = 8;
+  constexpr int kPre = 16;
   const int col = t & 63;
   const int g = (t >> 6) & 1;
   const int parity = t >> 7;
@@ -515,21 +518,10 @@ __global__ __launch_bounds__(kTileThreads, 2) void decode_pagetile_kernel(
     const int i = parity + 2 * j;
     pre[j] = i < r_eff ? acc_of(i) : make_float4(0.f, 0.f, 0.f, 0.f);
   }
-  for (int i = t; i < 2 * r_eff; i += kTileConsumerThreads) {
-    s_m[i] = __ldcg(p.partial_m + pair * 2 + i);
-    s_l[i] = __ldcg(p.partial_l + pair * 2 + i);
-  }
-  named_barrier_sync(1, kTileConsumerThreads);
   float top = -INFINITY;
-  for (int i = 0; i < r_eff; ++i) top = fmaxf(top, s_m[i * 2 + g]);
   float sum = 0.0f;
-  for (int i = 0; i < r_eff; ++i) {
-    const float li = s_l[i * 2 + g];
-    if (li > 0.0f) sum = fmaf(li, ex2_approx(s_m[i * 2 + g] - top), sum);
-  }
   float4 value = make_float4(0.f, 0.f, 0.f, 0.f);
-  auto add = [&](const float4 &a, int i) {
-    const float w = s_l[i * 2 + g] > 0.0f ? ex2_approx(s_m[i * 2 + g] - top) : 0.0f;
+  auto add = [&value](const float4 &a, float w) {
     if (w > 0.0f) {  // a partial without mass is dropped whatever it holds
       value.x = fmaf(a.x, w, value.x);
       value.y = fmaf(a.y, w, value.y);
@@ -537,19 +529,51 @@ __global__ __launch_bounds__(kTileThreads, 2) void decode_pagetile_kernel(
       value.w = fmaf(a.w, w, value.w);
     }
   };
+  if (r_eff <= kWarpSize) {
+    // Up to 32 partials: lane i of every warp holds partial i's (m, l) of the
+    // warp's row; maximum, weights and denominator by shuffles, no shared memory.
+    const float mi = lane < r_eff ? __ldcg(p.partial_m + (pair + lane) * 2 + g) : -INFINITY;
+    const float li = lane < r_eff ? __ldcg(p.partial_l + (pair + lane) * 2 + g) : 0.0f;
+    top = mi;
 #pragma unroll
-  for (int j = 0; j < kPre; ++j) {
-    if (parity + 2 * j < r_eff) add(pre[j], parity + 2 * j);
-  }
-  for (int i0 = parity + 2 * kPre; i0 < r_eff; i0 += 2 * kPre) {
-    float4 a[kPre];
+    for (int o = 16; o > 0; o >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, o));
+    const float wi = li > 0.0f ? ex2_approx(mi - top) : 0.0f;
+    sum = li * wi;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
 #pragma unroll
     for (int j = 0; j < kPre; ++j) {
-      a[j] = i0 + 2 * j < r_eff ? acc_of(i0 + 2 * j) : make_float4(0.f, 0.f, 0.f, 0.f);
+      const float w = __shfl_sync(0xffffffffu, wi, (parity + 2 * j) & 31);
+      if (parity + 2 * j < r_eff) add(pre[j], w);
     }
+  } else {
+    for (int i = t; i < 2 * r_eff; i += kTileConsumerThreads) {
+      s_m[i] = __ldcg(p.partial_m + pair * 2 + i);
+      s_l[i] = __ldcg(p.partial_l + pair * 2 + i);
+    }
+    named_barrier_sync(1, kTileConsumerThreads);
+    for (int i = 0; i < r_eff; ++i) top = fmaxf(top, s_m[i * 2 + g]);
+    for (int i = 0; i < r_eff; ++i) {
+      const float li = s_l[i * 2 + g];
+      if (li > 0.0f) sum = fmaf(li, ex2_approx(s_m[i * 2 + g] - top), sum);
+    }
+    auto weight = [&](int i) {
+      return s_l[i * 2 + g] > 0.0f ? ex2_approx(s_m[i * 2 + g] - top) : 0.0f;
+    };
 #pragma unroll
     for (int j = 0; j < kPre; ++j) {
-      if (i0 + 2 * j < r_eff) add(a[j], i0 + 2 * j);
+      if (parity + 2 * j < r_eff) add(pre[j], weight(parity + 2 * j));
+    }
+    for (int i0 = parity + 2 * kPre; i0 < r_eff; i0 += 2 * kPre) {
+      float4 a[kPre];
+#pragma unroll
+      for (int j = 0; j < kPre; ++j) {
+        a[j] = i0 + 2 * j < r_eff ? acc_of(i0 + 2 * j) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int j = 0; j < kPre; ++j) {
+        if (i0 + 2 * j < r_eff) add(a[j], weight(i0 + 2 * j));
+      }
     }
   }
   // the two parities meet in shared memory (the warps' exchange area is idle)
@@ -677,7 +701,10 @@ bool decode_pagetile_preferred(const Gemma4KvCacheConfig &c, int q_heads,
   // their parallel combine are faster (measured: 38 against 52 us on the
   // one-head share of 131072 keys).
   if (c.window_size > 0) return batch_count <= kPagetileMaxBatch;
-  return batch_count == 1 && c.num_heads == 8;
+  // one sequence on a linear cache: up to kPagetileMaxLinearKeys of capacity; a
+  // longer context is a bandwidth job again (131072 keys: 169 us balanced, 171 here)
+  return batch_count == 1 && c.num_heads == 8 &&
+         int64_t(c.max_pages_per_seq) * c.page_size <= kPagetileMaxLinearKeys;
 }
 
 cudaError_t decode_layer_step_pagetile_bf16(const AppendArgs *ap, const DecodeArgs &a,
@@ -738,6 +765,9 @@ cudaError_t decode_layer_step_pagetile_bf16(const AppendArgs *ap, const DecodeAr
   int64_t ranges = std::max<int64_t>(1, (2 * int64_t(sm_count)) / pairs);
   ranges = std::min<int64_t>({ranges, int64_t(kMaxRanges), std::max<int64_t>(1, max_chunks / 2),
                               std::max<int64_t>(1, a.num_splits)});
+  // up to 32 partials per pair are merged in one round of loads; a few more
+  // ranges than that do not pay for the second round
+  if (ranges > 32 && ranges < 48) ranges = 32;
   if (pagetile_ranges_override() > 0) {
     ranges = std::min<int64_t>({int64_t(pagetile_ranges_override()), int64_t(kMaxRanges),
                                 std::max<int64_t>(1, a.num_splits)});

@@ -505,8 +505,8 @@ typedef struct B200KvLayerStepArgs {
    * first call; every call leaves it zero again (unless a bounded wait ran
    * out, which `status` reports). With it, and split_size == 0, small jobs --
    * a sliding-window layer of up to 32 sequences, or one sequence on a linear
-   * cache of 8 KV heads (head_dim 256, two query heads per KV head, rotary_dim
-   * 256) -- run as ONE launch: a CTA per (sequence, KV head, key
+   * cache of 8 KV heads with room for at most 32768 keys (head_dim 256, two
+   * query heads per KV head, rotary_dim 256) -- run as ONE launch: a CTA per (sequence, KV head, key
    * range) fetches that head's rows as TMA tiles, and the last CTA of each
    * (sequence, head) to finish merges the ranges' partials, the job of the
    * reference's grid-wide barrier + reduce phase
