@@ -498,6 +498,7 @@ def decode_attention(out, lse, q_prepared, cache_k, cache_v, cfg: KvConfig, page
 
 
 STATIC_SCRATCH_BYTES = 16 << 20
+TICKETS_PER_HEAD = 11            # B200KV_TICKETS_PER_HEAD: words of LayerStepArgs.ticket per sequence and KV head
 
 
 def decode_attention_static_scratch(out, lse, q_prepared, cache_k, cache_v, cfg: KvConfig, page_table, seq_lengths,

@@ -60,7 +60,9 @@ namespace {
 using TileTraits = DecodeTraits<256, 1, 2, 8>;  // one head: 8 warps x 4 tokens
 constexpr int kTileStage = TileTraits::kStageTokens;  // 32 tokens
 constexpr int kMaxTileTokens = 16;                    // tokens of one TMA tile
-constexpr int kMaxRanges = 296;                       // partials per (sequence, head)
+constexpr int kMergeGroup = 32;      // partials one CTA merges in one round of loads
+constexpr int kMaxMergeGroups = B200KV_TICKETS_PER_HEAD - 1;  // groups per (sequence, head)
+constexpr int kMaxRanges = kMergeGroup * kMaxMergeGroups;  // key ranges per (sequence, head)
 // Above this many sequences a sliding-window layer is a bandwidth job and stays
 // on the balanced partition (see decode_pagetile_preferred).
 constexpr int kPagetileMaxBatch = 32;
@@ -90,7 +92,7 @@ struct TileParams {
   float *partial_m;
   float *partial_l;
   float *partial_acc;
-  uint32_t *ticket;     // [batch * kv_heads], zero between launches
+  uint32_t *ticket;     // [batch * kv_heads * B200KV_TICKETS_PER_HEAD], zero between launches
   int32_t ranges;       // key ranges (CTAs) per sequence and head
   int32_t tile_tokens;  // tokens of one TMA tile: min(page_size, 16)
   int32_t *status;
@@ -405,8 +407,6 @@ __global__ __launch_bounds__(kTileThreads, 2) void decode_pagetile_kernel(
   float *x_acc = reinterpret_cast<float *>(smem);         // [8][2][256]
   float *x_m = x_acc + T::kConsumerWarps * 2 * D;          // [8][2]
   float *x_l = x_m + T::kConsumerWarps * 2;                // [8][2]
-  float *s_m = x_l + T::kConsumerWarps * 2;                // [kMaxRanges][2]
-  float *s_l = s_m + kMaxRanges * 2;                       // [kMaxRanges][2]
   named_barrier_sync(1, kTileConsumerThreads);
 #pragma unroll
   for (int g = 0; g < 2; ++g) {
@@ -484,56 +484,51 @@ __global__ __launch_bounds__(kTileThreads, 2) void decode_pagetile_kernel(
       p.partial_l[slot] = L[g];
     }
   }
-  // The CTA's partial is complete in every thread's view after the barrier; one
-  // acq_rel atomic at GPU scope then publishes it (release: the writes the
-  // barrier ordered before it) and, for the CTA that arrives last, makes the
-  // other CTAs' partials visible (acquire).
-  named_barrier_sync(1, kTileConsumerThreads);
-  if (t == 0) {
-    uint32_t before;
-    asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], %2;"
-                 : "=r"(before)
-                 : "l"(p.ticket + int64_t(b) * H + h), "r"(1u)
-                 : "memory");
-    s_flag[1] = before == uint32_t(r_eff - 1) ? 1 : 0;
-  }
-  named_barrier_sync(1, kTileConsumerThreads);
-  if (s_flag[1] == 0) return;
-  // Merge of the pair's r_eff partials. Thread t owns four dims (t % 64) of row
-  // (t / 64) % 2 and every second partial, parity t / 128: all its loads are
-  // independent and go out together (the first eight before the weights are
-  // known). The partials were written by other SMs: read them past L1 (a line
-  // of the same scratch may sit there from an earlier launch).
-  constexpr int kPre = 16;
+  // A ticket: the CTA's writes are complete in every thread's view after the
+  // barrier; one acq_rel atomic at GPU scope then publishes them (release: the
+  // writes the barrier ordered before it) and, for the CTA that arrives last,
+  // makes the other CTAs' writes visible (acquire). True in the last arriver.
+  auto last_to_arrive = [&](uint32_t *counter, int expected) {
+    named_barrier_sync(1, kTileConsumerThreads);
+    if (t == 0) {
+      uint32_t before;
+      asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], %2;"
+                   : "=r"(before)
+                   : "l"(counter), "r"(1u)
+                   : "memory");
+      s_flag[1] = before == uint32_t(expected - 1) ? 1 : 0;
+    }
+    named_barrier_sync(1, kTileConsumerThreads);
+    return s_flag[1] != 0;
+  };
+  // Merge of up to 32 partials at slots first, first + stride, ... Thread t owns
+  // four dims (t % 64) of row (t / 64) % 2 and every second partial, parity
+  // t / 128: all its loads are independent and go out together, before the
+  // weights are known. Lane i of every warp holds partial i's (m, l) of the
+  // warp's row: maximum, weights and denominator by shuffles. The partials were
+  // written by other SMs: read them past L1 (a line of the same scratch may sit
+  // there from an earlier launch). Afterwards the threads of parity 0 hold the
+  // merged (top, sum, value) of their row and dims.
+  constexpr int kPre = kMergeGroup / 2;
   const int col = t & 63;
   const int g = (t >> 6) & 1;
   const int parity = t >> 7;
-  const float4 *mine = reinterpret_cast<const float4 *>(p.partial_acc) + col;
-  auto acc_of = [&](int i) {  // partial i of row g, this thread's four dims
-    return __ldcg(mine + ((pair + i) * 2 + g) * (D / 4));
-  };
-  float4 pre[kPre];
-#pragma unroll
-  for (int j = 0; j < kPre; ++j) {
-    const int i = parity + 2 * j;
-    pre[j] = i < r_eff ? acc_of(i) : make_float4(0.f, 0.f, 0.f, 0.f);
-  }
   float top = -INFINITY;
   float sum = 0.0f;
   float4 value = make_float4(0.f, 0.f, 0.f, 0.f);
-  auto add = [&value](const float4 &a, float w) {
-    if (w > 0.0f) {  // a partial without mass is dropped whatever it holds
-      value.x = fmaf(a.x, w, value.x);
-      value.y = fmaf(a.y, w, value.y);
-      value.z = fmaf(a.z, w, value.z);
-      value.w = fmaf(a.w, w, value.w);
+  float4 *x_sum = reinterpret_cast<float4 *>(x_acc);  // the warps' exchange area is idle
+  auto merge = [&](int64_t first, int stride, int count) {
+    const float4 *mine = reinterpret_cast<const float4 *>(p.partial_acc) + col;
+    float4 pre[kPre];
+#pragma unroll
+    for (int j = 0; j < kPre; ++j) {
+      const int i = parity + 2 * j;
+      pre[j] = i < count ? __ldcg(mine + ((first + int64_t(i) * stride) * 2 + g) * (D / 4))
+                         : make_float4(0.f, 0.f, 0.f, 0.f);
     }
-  };
-  if (r_eff <= kWarpSize) {
-    // Up to 32 partials: lane i of every warp holds partial i's (m, l) of the
-    // warp's row; maximum, weights and denominator by shuffles, no shared memory.
-    const float mi = lane < r_eff ? __ldcg(p.partial_m + (pair + lane) * 2 + g) : -INFINITY;
-    const float li = lane < r_eff ? __ldcg(p.partial_l + (pair + lane) * 2 + g) : 0.0f;
+    const int64_t ml = (first + int64_t(lane) * stride) * 2 + g;
+    const float mi = lane < count ? __ldcg(p.partial_m + ml) : -INFINITY;
+    const float li = lane < count ? __ldcg(p.partial_l + ml) : 0.0f;
     top = mi;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, o));
@@ -541,61 +536,75 @@ __global__ __launch_bounds__(kTileThreads, 2) void decode_pagetile_kernel(
     sum = li * wi;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    value = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
     for (int j = 0; j < kPre; ++j) {
       const float w = __shfl_sync(0xffffffffu, wi, (parity + 2 * j) & 31);
-      if (parity + 2 * j < r_eff) add(pre[j], w);
+      if (parity + 2 * j < count && w > 0.0f) {  // a partial without mass is dropped
+        value.x = fmaf(pre[j].x, w, value.x);
+        value.y = fmaf(pre[j].y, w, value.y);
+        value.z = fmaf(pre[j].z, w, value.z);
+        value.w = fmaf(pre[j].w, w, value.w);
+      }
     }
-  } else {
-    for (int i = t; i < 2 * r_eff; i += kTileConsumerThreads) {
-      s_m[i] = __ldcg(p.partial_m + pair * 2 + i);
-      s_l[i] = __ldcg(p.partial_l + pair * 2 + i);
-    }
+    named_barrier_sync(1, kTileConsumerThreads);  // x_sum is free (a merge before this one)
+    if (parity == 1) x_sum[t - 128] = value;
     named_barrier_sync(1, kTileConsumerThreads);
-    for (int i = 0; i < r_eff; ++i) top = fmaxf(top, s_m[i * 2 + g]);
-    for (int i = 0; i < r_eff; ++i) {
-      const float li = s_l[i * 2 + g];
-      if (li > 0.0f) sum = fmaf(li, ex2_approx(s_m[i * 2 + g] - top), sum);
+    if (parity == 0) {
+      const float4 o = x_sum[t];
+      value.x += o.x;
+      value.y += o.y;
+      value.z += o.z;
+      value.w += o.w;
     }
-    auto weight = [&](int i) {
-      return s_l[i * 2 + g] > 0.0f ? ex2_approx(s_m[i * 2 + g] - top) : 0.0f;
-    };
-#pragma unroll
-    for (int j = 0; j < kPre; ++j) {
-      if (parity + 2 * j < r_eff) add(pre[j], weight(parity + 2 * j));
-    }
-    for (int i0 = parity + 2 * kPre; i0 < r_eff; i0 += 2 * kPre) {
-      float4 a[kPre];
-#pragma unroll
-      for (int j = 0; j < kPre; ++j) {
-        a[j] = i0 + 2 * j < r_eff ? acc_of(i0 + 2 * j) : make_float4(0.f, 0.f, 0.f, 0.f);
-      }
-#pragma unroll
-      for (int j = 0; j < kPre; ++j) {
-        if (i0 + 2 * j < r_eff) add(a[j], weight(i0 + 2 * j));
+  };
+  auto write_merged_rows = [&]() {
+    if (parity == 0) {
+      const float inv = sum > 0.0f ? 1.0f / sum : 0.0f;
+      const int64_t row = int64_t(b) * p.q_heads + h * 2 + g;
+      const __nv_bfloat162 lo = __floats2bfloat162_rn(value.x * inv, value.y * inv);
+      const __nv_bfloat162 hi = __floats2bfloat162_rn(value.z * inv, value.w * inv);
+      reinterpret_cast<uint2 *>(p.out + row * D)[col] =
+          make_uint2(*reinterpret_cast<const uint32_t *>(&lo),
+                     *reinterpret_cast<const uint32_t *>(&hi));
+      if (p.lse != nullptr && col == 0) {
+        p.lse[row] = sum > 0.0f ? (top + lg2_approx(sum)) * 0.6931471805599453f : -INFINITY;
       }
     }
+  };
+  // Tickets: one word per (sequence, head) for the pair, then kMaxMergeGroups
+  // words per pair for its groups of kMergeGroup ranges.
+  uint32_t *pair_ticket = p.ticket + (int64_t(b) * H + h);
+  const int groups = div_up(r_eff, kMergeGroup);
+  if (groups == 1) {
+    if (!last_to_arrive(pair_ticket, r_eff)) return;
+    merge(pair, 1, r_eff);
+    write_merged_rows();
+    if (t == 0) *pair_ticket = 0u;  // ready for the next launch
+    return;
   }
-  // the two parities meet in shared memory (the warps' exchange area is idle)
-  float4 *x_sum = reinterpret_cast<float4 *>(x_acc);
-  if (parity == 1) x_sum[t - 128] = value;
-  named_barrier_sync(1, kTileConsumerThreads);
-  if (parity == 0) {
-    const float4 o = x_sum[t];
-    const float inv = sum > 0.0f ? 1.0f / sum : 0.0f;
-    const int64_t row = int64_t(b) * p.q_heads + h * 2 + g;
-    const __nv_bfloat162 lo =
-        __floats2bfloat162_rn((value.x + o.x) * inv, (value.y + o.y) * inv);
-    const __nv_bfloat162 hi =
-        __floats2bfloat162_rn((value.z + o.z) * inv, (value.w + o.w) * inv);
-    reinterpret_cast<uint2 *>(p.out + row * D)[col] =
-        make_uint2(*reinterpret_cast<const uint32_t *>(&lo),
-                   *reinterpret_cast<const uint32_t *>(&hi));
-    if (p.lse != nullptr && col == 0) {
-      p.lse[row] = sum > 0.0f ? (top + lg2_approx(sum)) * 0.6931471805599453f : -INFINITY;
+  // More than 32 ranges (long contexts on few heads): the last CTA of each group
+  // of 32 merges the group into the group's first slot, the last group to finish
+  // merges the groups. One CTA never reads more than 32 + groups partials.
+  const int group = r / kMergeGroup;
+  const int group_size = min(kMergeGroup, r_eff - group * kMergeGroup);
+  uint32_t *group_ticket = p.ticket + int64_t(p.batch_count) * H +
+                           (int64_t(b) * H + h) * kMaxMergeGroups + group;
+  if (!last_to_arrive(group_ticket, group_size)) return;
+  const int64_t group_slot = pair + int64_t(group) * kMergeGroup;
+  merge(group_slot, 1, group_size);
+  if (parity == 0) {  // every partial of the group has been read: its first slot takes the sum
+    reinterpret_cast<float4 *>(p.partial_acc)[(group_slot * 2 + g) * (D / 4) + col] = value;
+    if (col == 0) {
+      p.partial_m[group_slot * 2 + g] = top;
+      p.partial_l[group_slot * 2 + g] = sum;
     }
   }
-  if (t == 0) p.ticket[int64_t(b) * H + h] = 0u;  // ready for the next launch
+  if (t == 0) *group_ticket = 0u;
+  if (!last_to_arrive(pair_ticket, groups)) return;
+  merge(pair, kMergeGroup, groups);
+  write_merged_rows();
+  if (t == 0) *pair_ticket = 0u;
 }
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
@@ -695,15 +704,14 @@ bool decode_pagetile_preferred(const Gemma4KvCacheConfig &c, int q_heads,
   // Ranges are cut per sequence: chosen where the sequences' live keys are equal
   // by construction (a sliding window) or there is one sequence; small jobs only
   // -- a big batch is bandwidth-bound and streams best through the balanced
-  // partition. With fewer than 8 KV heads (the cache of a KV-head-sharded rank)
-  // a long linear context has too few (sequence, head) pairs: each pair's last
-  // CTA would merge hundreds of partials alone, and the fixed-split kernels with
-  // their parallel combine are faster (measured: 38 against 52 us on the
-  // one-head share of 131072 keys).
+  // partition.
   if (c.window_size > 0) return batch_count <= kPagetileMaxBatch;
-  // one sequence on a linear cache: up to kPagetileMaxLinearKeys of capacity; a
-  // longer context is a bandwidth job again (131072 keys: 169 us balanced, 171 here)
-  return batch_count == 1 && c.num_heads == 8 &&
+  if (batch_count != 1) return false;
+  // One sequence on a linear cache. Fewer than 8 KV heads (the cache of a
+  // KV-head-sharded rank): the alternative is three launches of the fixed-split
+  // kernels. 8 heads: up to kPagetileMaxLinearKeys of capacity; a longer context
+  // is a bandwidth job again (131072 keys: 169 us balanced, 171 here).
+  return c.num_heads < 8 ||
          int64_t(c.max_pages_per_seq) * c.page_size <= kPagetileMaxLinearKeys;
 }
 

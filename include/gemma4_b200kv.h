@@ -473,6 +473,10 @@ void b200kv_plan_splits_total(int32_t batch_count, int32_t max_live_keys,
  * The environment variable B200KV_FUSED_LAYER_STEP=0 (read once) keeps the two
  * launches apart, for comparison.
  * ------------------------------------------------------------------ */
+/* Words of the layer-step's `ticket` buffer per sequence and KV head: one for
+ * the (sequence, head) pair and one per group of 32 key ranges. */
+#define B200KV_TICKETS_PER_HEAD 11
+
 typedef struct B200KvLayerStepArgs {
   b200kv_bf16 *q;                 /* out: prepared q [batch, q_heads, head_dim] */
   b200kv_bf16 *out;               /* out: attention [batch, q_heads, head_dim] */
@@ -501,12 +505,14 @@ typedef struct B200KvLayerStepArgs {
    * right before and after that launch and its combine. */
   void *event_before_attention;
   void *event_after_attention;
-  /* Optional: uint32 [batch_count * cache_config.num_heads], zero before the
-   * first call; every call leaves it zero again (unless a bounded wait ran
+  /* Optional: uint32 [batch_count * cache_config.num_heads *
+   * B200KV_TICKETS_PER_HEAD], zero before the first call; every call leaves
+   * it zero again (unless a bounded wait ran
    * out, which `status` reports). With it, and split_size == 0, small jobs --
    * a sliding-window layer of up to 32 sequences, or one sequence on a linear
-   * cache of 8 KV heads with room for at most 32768 keys (head_dim 256, two
-   * query heads per KV head, rotary_dim 256) -- run as ONE launch: a CTA per (sequence, KV head, key
+   * cache (with 8 KV heads: one with room for at most 32768 keys; with fewer,
+   * the cache of a KV-head-sharded rank, any) (head_dim 256, two query heads
+   * per KV head, rotary_dim 256) -- run as ONE launch: a CTA per (sequence, KV head, key
    * range) fetches that head's rows as TMA tiles, and the last CTA of each
    * (sequence, head) to finish merges the ranges' partials, the job of the
    * reference's grid-wide barrier + reduce phase

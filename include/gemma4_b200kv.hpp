@@ -198,9 +198,9 @@ cudaError_t gemma4_runtime_prepare_decode_step(Gemma4RuntimeState *state,
 // residual + pre-FFN norm on `stream`; the caller's FFN launch follows.
 // `raw_qkv_scratch`: 8704 bf16 per row (the reference reuses attention_out /
 // attention_q for it; here it is a buffer of its own); `ticket`: uint32
-// [batch_count * (1 + KV heads)], zero before the first call and left zero by
-// every call (one word per row for the O projection's last-CTA epilogue, then
-// one per row and KV head for the one-launch attention). Geometry as the reference derives it from
+// [batch_count * (1 + KV heads * B200KV_TICKETS_PER_HEAD)], zero before the
+// first call and left zero by every call (one word per row for the O
+// projection's last-CTA epilogue, then the one-launch attention's tickets). Geometry as the reference derives it from
 // the cache config: 8 KV heads x 256 (sliding, own V projection, rotary 256) or
 // 1 KV head x 512 (global, V from raw K, rotary 128), 16 query heads.
 template <class LayerArgs>

@@ -122,8 +122,8 @@ int main(int argc, char **argv) {
   CHECK(cudaMalloc(&pm, size_t(kQHeads) * num_splits * 4));
   CHECK(cudaMalloc(&pl, size_t(kQHeads) * num_splits * 4));
   CHECK(cudaMalloc(&pacc, size_t(kQHeads) * num_splits * kDim * 4));
-  CHECK(cudaMalloc(&ticket, (1 + kHeads) * 4));  // one row: O projection + one word per KV head
-  CHECK(cudaMemset(ticket, 0, (1 + kHeads) * 4));
+  CHECK(cudaMalloc(&ticket, (1 + kHeads * B200KV_TICKETS_PER_HEAD) * 4));  // one row: O projection + the attention's tickets
+  CHECK(cudaMemset(ticket, 0, (1 + kHeads * B200KV_TICKETS_PER_HEAD) * 4));
   CHECK(cudaMalloc(&status, 16));
   CHECK(cudaMemset(status, 0, 16));
 

@@ -11,8 +11,8 @@ the CPU oracle with bench.verify_step -- the check the benchmark itself runs aft
   * configs[4]: 32 x 8192 keys in an FP8 e4m3 cache filled by quantise-on-append, fused-dequant decode against the
     double-precision oracle over the same quantised bytes and against the bf16 rows they were made from.
 Tolerances: tests/helpers.py (attention 2^-6 abs / rel, log-sum-exp 1e-3), FP8 vs bf16 0.05 / 5e-3; appended rows:
-bit-exact against the reference's own append kernel where it is built, at most one bf16 step from the IEEE host
-oracle otherwise.
+bit-exact against the reference's own append kernel where it is built; against the IEEE host oracle no element
+further than one bf16 step at its magnitude (the library's default norm mode is rsqrt.approx, like the reference's).
 """
 from __future__ import annotations
 
@@ -50,7 +50,7 @@ def _assert_verified(res):
     assert res["ok"], res
     assert res["max_abs"] <= ATTN_MAX_ABS and res["max_rel"] <= ATTN_MAX_REL and res["lse_max_abs"] <= LSE_MAX_ABS
     a = res["append_vs_ieee_oracle"]
-    assert a["max_steps"] <= 1 and a["one_step_off"] <= 0.02 * max(a["elements"], 1)
+    assert a["beyond_one_step"] == 0 and a["differing"] <= 0.02 * max(a["elements"], 1)
     if "reference's own" in res.get("cache_checker", ""):
         assert res["cache_rows_exact"] is True
 

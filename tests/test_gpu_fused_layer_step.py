@@ -64,7 +64,7 @@ def _run_steps(kv, orc, *, window, ring_pages, start, steps, norm_mode, has_v=Tr
     fused = _State(kv, acase, ck, cv, num_splits)
     plain = _State(kv, acase, ck, cv, num_splits)
     tiled = _State(kv, acase, ck, cv, num_splits)
-    ticket = torch.zeros(B * H, dtype=torch.int32, device="cuda")
+    ticket = torch.zeros(B * H * kv.TICKETS_PER_HEAD, dtype=torch.int32, device="cuda")
     table, qw, kw_ = dev(acase.page_table), dev(acase.q_w), dev(acase.k_w)
     cos, sin = dev(acase.cos), dev(acase.sin)
     scale = 1.0 / 16.0

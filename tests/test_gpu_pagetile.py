@@ -25,7 +25,7 @@ def _run(kv, case, num_splits, poison=float("nan"), repeat=1):
     rows = B * H * num_splits
     pm = torch.full((rows,), poison, dtype=torch.float32, device="cuda")
     pl, pacc = pm.clone(), torch.full((rows * D,), poison, dtype=torch.float32, device="cuda")
-    ticket = torch.zeros(B * case.cfg[5], dtype=torch.int32, device="cuda")
+    ticket = torch.zeros(B * case.cfg[5] * kv.TICKETS_PER_HEAD, dtype=torch.int32, device="cuda")
     status = torch.zeros(4, dtype=torch.int32, device="cuda")
     outs = []
     for _ in range(repeat):
@@ -80,7 +80,9 @@ def test_tiled_unmapped_pages_empty_rows_and_stale_scratch(kv, orc):
 @pytest.mark.parametrize("name,kw", [
     ("batch 1 ring", dict(seq_lens=[1500], window=1024)),
     ("eight sequences, ring", dict(seq_lens=[1500, 1024, 4000, 1025, 1100, 9000, 2048, 1030], window=1024)),
-    ("one KV head of a long sequence", dict(seq_lens=[20000], window=0, kv_heads=1, q_heads=2)),
+    ("one KV head of a long sequence", dict(seq_lens=[20000], window=0, kv_heads=1, q_heads=2)),      # 296 ranges: ten groups
+    ("four KV heads of a long sequence", dict(seq_lens=[9000], window=0, kv_heads=4, q_heads=8)),     # 74 ranges: three groups
+    ("eight KV heads, 40 ranges asked for", dict(seq_lens=[5000], window=0)),
 ])
 def test_tiled_launches_back_to_back_give_the_same_bits(kv, orc, name, kw):
     """200 launches enqueued without a host synchronisation, every one free to start under its predecessor's tail,
@@ -95,7 +97,7 @@ def test_tiled_rejects_what_it_is_not_built_for(kv):
     case = make_attn_case(3, [40], window=0, page_size=1)
     cfg = kv.make_kv_config(*case.cfg)
     buf = torch.zeros(16 * 4 * 256, dtype=torch.float32, device="cuda")
-    ticket = torch.zeros(8, dtype=torch.int32, device="cuda")
+    ticket = torch.zeros(8 * kv.TICKETS_PER_HEAD, dtype=torch.int32, device="cuda")
     out = torch.zeros((1, 16, 256), dtype=torch.int16, device="cuda")
     args = (out, None, dev(case.q), dev(case.cache_k), dev(case.cache_v), cfg, dev(case.page_table),
             dev(case.seq_lengths), 0, case.scale, 4, 1, 16, buf, buf, buf)
@@ -132,7 +134,7 @@ def test_decode_step_over_the_layers_of_one_cache(kv, orc, window, start):
     ns = kv.plan_balanced(B, sms)
     pm = torch.full((B * HQ * ns,), float("nan"), dtype=torch.float32, device="cuda")
     pl, pacc = pm.clone(), torch.full((B * HQ * ns * D,), float("nan"), dtype=torch.float32, device="cuda")
-    ticket = torch.zeros(B * H, dtype=torch.int32, device="cuda")
+    ticket = torch.zeros(B * H * kv.TICKETS_PER_HEAD, dtype=torch.int32, device="cuda")
     status = torch.zeros(4, dtype=torch.int32, device="cuda")
     table, qw, kw_, cos, sin = (dev(x) for x in (acase.page_table, acase.q_w, acase.k_w, acase.cos, acase.sin))
     raws = [[helpers.bf16_normal(rng, (B, n, D)) for n in (HQ, H, H)] for _ in range(steps * L)]
