@@ -212,6 +212,10 @@ _SIGNATURES = {
     "b200kv_peer_buffer_create_loopback": (c_int, [c_int64, c_int32, c_int32, POINTER(_P)]),
     "b200kv_peer_buffer_post": (c_int, [_P, c_int32, ctypes.c_uint32, _P]),
     "b200kv_bounded_wait_selftest": (c_int, [c_int64, _P, _P, _P]),
+    "b200kv_shard_sequences": (c_int32, [_P, c_int32, c_int32, _P]),
+    "b200kv_kv_head_range": (c_int32, [c_int32, c_int32, c_int32, POINTER(c_int32), POINTER(c_int32)]),
+    "b200kv_key_range_page_table": (c_int32, [_P, c_int32, c_int32, c_int32, c_int32, c_int32, _P, POINTER(c_int32),
+                                             POINTER(c_int32)]),
     "b200kv_timer_create": (c_int, [POINTER(_P)]),
     "b200kv_timer_destroy": (c_int, [_P]),
     "b200kv_timer_record": (c_int, [_P, _P]),

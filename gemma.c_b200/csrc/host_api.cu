@@ -1294,6 +1294,65 @@ int b200kv_bounded_wait_selftest(int64_t clock_limit, int32_t *d_status,
       static_cast<cudaStream_t>(stream));
 }
 
+// ---------------------------------------------------------------------------
+// Partition of the path over the GPUs of a node (host bookkeeping only).
+// ---------------------------------------------------------------------------
+int32_t b200kv_shard_sequences(const int64_t *h_live_keys, int32_t sequences,
+                               int32_t world, int32_t *h_owner) {
+  if (h_live_keys == nullptr || h_owner == nullptr || sequences < 0 || world <= 0) {
+    return -1;
+  }
+  // greedy, longest first: every sequence goes to the rank with the least keys
+  std::vector<int32_t> order(static_cast<size_t>(sequences));
+  for (int32_t i = 0; i < sequences; ++i) order[size_t(i)] = i;
+  std::stable_sort(order.begin(), order.end(), [&](int32_t a, int32_t b) {
+    return h_live_keys[a] > h_live_keys[b];
+  });
+  std::vector<int64_t> load(static_cast<size_t>(world), 0);
+  for (const int32_t i : order) {
+    const int32_t r =
+        int32_t(std::min_element(load.begin(), load.end()) - load.begin());
+    h_owner[i] = r;
+    load[size_t(r)] += h_live_keys[i];
+  }
+  return 0;
+}
+
+int32_t b200kv_kv_head_range(int32_t kv_heads, int32_t world, int32_t rank,
+                             int32_t *first_head, int32_t *head_count) {
+  if (kv_heads <= 0 || world <= 0 || rank < 0 || rank >= world ||
+      kv_heads % world != 0 || first_head == nullptr || head_count == nullptr) {
+    return -1;
+  }
+  *head_count = kv_heads / world;
+  *first_head = rank * *head_count;
+  return 0;
+}
+
+int32_t b200kv_key_range_page_table(const int32_t *h_page_table,
+                                    int32_t max_pages_per_seq, int32_t seq_len,
+                                    int32_t page_size, int32_t world, int32_t rank,
+                                    int32_t *h_rank_table, int32_t *local_length,
+                                    int32_t *first_position) {
+  if (h_page_table == nullptr || h_rank_table == nullptr || max_pages_per_seq <= 0 ||
+      seq_len < 0 || page_size <= 0 || world <= 0 || rank < 0 || rank >= world) {
+    return -1;
+  }
+  const int32_t pages = std::min(b200kv::div_up(seq_len, page_size), max_pages_per_seq);
+  const int32_t per = b200kv::div_up(pages, world);
+  const int32_t lo = std::min(rank * per, pages);
+  const int32_t hi = std::min((rank + 1) * per, pages);
+  for (int32_t i = 0; i < max_pages_per_seq; ++i) {
+    h_rank_table[i] = i < hi - lo ? h_page_table[lo + i] : -1;
+  }
+  const int32_t first = lo * page_size;
+  if (local_length != nullptr) {
+    *local_length = std::max(0, std::min(seq_len, hi * page_size) - first);
+  }
+  if (first_position != nullptr) *first_position = first;
+  return 0;
+}
+
 int b200kv_timer_create(void **event) {
   if (event == nullptr) return cudaErrorInvalidValue;
   cudaEvent_t ev = nullptr;

@@ -1,4 +1,6 @@
-"""Host-side partition of the KV path over the GPUs of one node (numpy only, no device code).
+"""Host-side partition of the KV path over the GPUs of one node: numpy front end of the library's C entry points
+(b200kv_shard_sequences, b200kv_kv_head_range, b200kv_key_range_page_table; no device code) plus the array slicing
+the tests and the bench need around them.
 
 Two ways the path shards, neither of which the single-GPU reference has:
   * by sequence: sequences are independent (own pages, own length, own output rows); each rank owns whole
@@ -12,27 +14,29 @@ Two ways the path shards, neither of which the single-GPU reference has:
 """
 from __future__ import annotations
 
+import ctypes
+
 import numpy as np
+
+from . import load_library
 
 
 def shard_sequences(live_keys, world: int) -> list[list[int]]:
-    """Greedy longest-first partition of sequence indices over `world` ranks by live key count."""
-    keys = np.asarray(live_keys, dtype=np.int64)
+    """Greedy longest-first partition of sequence indices over `world` ranks by live key count
+    (b200kv_shard_sequences); a rank's list is in the order the sequences were dealt."""
+    keys = np.ascontiguousarray(live_keys, dtype=np.int64)
+    owner = np.empty(keys.size, dtype=np.int32)
+    if load_library().b200kv_shard_sequences(keys.ctypes.data, keys.size, world, owner.ctypes.data) != 0:
+        raise ValueError("b200kv_shard_sequences rejected its arguments")
     order = np.argsort(-keys, kind="stable")
-    load = [0] * world
-    shards: list[list[int]] = [[] for _ in range(world)]
-    for i in order:
-        r = int(np.argmin(load))
-        shards[r].append(int(i))
-        load[r] += int(keys[i])
-    return shards
+    return [[int(i) for i in order if owner[i] == r] for r in range(world)]
 
 
 def kv_head_range(kv_heads: int, world: int, rank: int) -> tuple[int, int]:
-    if kv_heads % world:
+    first, count = ctypes.c_int32(), ctypes.c_int32()
+    if load_library().b200kv_kv_head_range(kv_heads, world, rank, ctypes.byref(first), ctypes.byref(count)) != 0:
         raise ValueError(f"{kv_heads} KV heads do not divide over {world} ranks")
-    per = kv_heads // world
-    return rank * per, (rank + 1) * per
+    return first.value, first.value + count.value
 
 
 def slice_cache_heads(cache: np.ndarray, cfg: tuple, world: int, rank: int):
@@ -56,15 +60,15 @@ def key_range_page_table(page_table: np.ndarray, seq_len: int, page_size: int, w
     """Rank's view of one sequence's page table for key-range sharding: the pages of its positions moved to the
     front (local positions start at 0), the rest unmapped. Returns (table, local length, first absolute
     position). The keys are dealt in whole pages, the last rank takes the remainder."""
-    table = np.asarray(page_table, dtype=np.int32)
-    pages = -(-int(seq_len) // page_size)
-    per = -(-pages // world)
-    lo, hi = min(rank * per, pages), min((rank + 1) * per, pages)
-    out = np.full_like(table, -1)
-    out[:, :hi - lo] = table[:, lo:hi]
-    first = lo * page_size
-    length = max(0, min(int(seq_len), hi * page_size) - first)
-    return out, length, first
+    table = np.ascontiguousarray(page_table, dtype=np.int32)
+    assert table.ndim == 2 and table.shape[0] == 1, "one sequence"
+    out = np.empty_like(table)
+    length, first = ctypes.c_int32(), ctypes.c_int32()
+    rc = load_library().b200kv_key_range_page_table(table.ctypes.data, table.shape[1], int(seq_len), page_size, world,
+                                                    rank, out.ctypes.data, ctypes.byref(length), ctypes.byref(first))
+    if rc != 0:
+        raise ValueError("b200kv_key_range_page_table rejected its arguments")
+    return out, length.value, first.value
 
 
 def merge_attention_rows(outs, lses):

@@ -727,6 +727,42 @@ int b200kv_peer_buffer_post(void *handle, int32_t from_rank, uint32_t epoch,
 int b200kv_bounded_wait_selftest(int64_t clock_limit, int32_t *d_status,
                                  int64_t *d_waited_clocks, b200kv_stream stream);
 
+/* ------------------------------------------------------------------ *
+ * Host bookkeeping of the three ways the path shards over the GPUs of a node
+ * (one process per GPU). No counterpart in the reference, which is single-GPU
+ * and batch 1 (src/gemma4_decode_megakernel.cu:143). All return 0, or -1 for
+ * arguments that make no sense; none touches a device.
+ *
+ * b200kv_shard_sequences: sequences are independent units (own pages, own
+ * length, own output rows), so whole sequences are dealt to ranks and no
+ * collective is on the data path. Greedy, longest first by h_live_keys[i]
+ * (min(length, window) for sliding caches); h_owner[i] receives sequence i's
+ * rank. The largest and smallest rank load differ by at most one sequence.
+ *
+ * b200kv_kv_head_range: KV heads are independent until the output row is
+ * assembled; rank r holds caches with num_heads = kv_heads / world for heads
+ * [*first_head, *first_head + *head_count) and their query heads, and the
+ * step ends with b200kv_peer_allgather of the head outputs. kv_heads must be a
+ * multiple of world.
+ *
+ * b200kv_key_range_page_table: one long sequence split by key range; rank r
+ * holds all KV heads of a contiguous run of the sequence's pages. Writes the
+ * rank's view of the one-row page table (its pages moved to the front, so that
+ * its keys sit at local positions 0 .. *local_length - 1; the rest -1) and the
+ * absolute position of its first key (the offset by which the RoPE tables are
+ * entered for the new token's row). Pages are dealt whole, the last rank takes
+ * the remainder; the ranks' rows are merged with b200kv_peer_merge_attention.
+ * ------------------------------------------------------------------ */
+int32_t b200kv_shard_sequences(const int64_t *h_live_keys, int32_t sequences,
+                               int32_t world, int32_t *h_owner);
+int32_t b200kv_kv_head_range(int32_t kv_heads, int32_t world, int32_t rank,
+                             int32_t *first_head, int32_t *head_count);
+int32_t b200kv_key_range_page_table(const int32_t *h_page_table,
+                                    int32_t max_pages_per_seq, int32_t seq_len,
+                                    int32_t page_size, int32_t world, int32_t rank,
+                                    int32_t *h_rank_table, int32_t *local_length,
+                                    int32_t *first_position);
+
 /* Timing events for the hooks above (cudaEventCreate / Destroy / ElapsedTime).
  * No counterpart in the reference library; its benches time with the same
  * CUDA events, src/benches/gemma4_bench_utils.cuh:336-370. */

@@ -240,3 +240,33 @@ def test_reference_tests_compile_against_the_stand_in_headers(kv, tmp_path):
                                 "-I", _gemma_c_src(), str(tests / f"{name}.cu"), "-L", str(lib_dir),
                                 "-lgemma4_b200kv", "-o", str(tmp_path / name)], capture_output=True, text=True)
         assert build.returncode == 0, name + "\n" + build.stdout + build.stderr
+
+
+def test_partition_helpers_of_the_c_abi(kv):
+    """b200kv_shard_sequences / b200kv_kv_head_range / b200kv_key_range_page_table called directly: every sequence
+    owned once, rank loads within one sequence of each other, heads dealt in equal runs, a key range's page-table
+    view starts at local position 0; arguments that make no sense return -1."""
+    import ctypes
+
+    lib = kv.load_library()
+    rng = np.random.default_rng(4)
+    keys = rng.integers(512, 32769, size=64).astype(np.int64)
+    for world in (1, 2, 4, 8):
+        owner = np.full(64, -1, np.int32)
+        assert lib.b200kv_shard_sequences(keys.ctypes.data, 64, world, owner.ctypes.data) == 0
+        assert owner.min() == 0 and owner.max() == world - 1
+        loads = np.array([keys[owner == r].sum() for r in range(world)])
+        assert loads.max() - loads.min() <= keys.max()
+    assert lib.b200kv_shard_sequences(keys.ctypes.data, 64, 0, owner.ctypes.data) == -1
+    first, count = ctypes.c_int32(), ctypes.c_int32()
+    assert lib.b200kv_kv_head_range(8, 4, 3, ctypes.byref(first), ctypes.byref(count)) == 0
+    assert (first.value, count.value) == (6, 2)
+    assert lib.b200kv_kv_head_range(8, 3, 0, ctypes.byref(first), ctypes.byref(count)) == -1
+    table = (np.arange(10, dtype=np.int32) + 100)
+    out = np.zeros(10, np.int32)
+    length, start = ctypes.c_int32(), ctypes.c_int32()
+    assert lib.b200kv_key_range_page_table(table.ctypes.data, 10, 150, 16, 4, 3, out.ctypes.data,
+                                           ctypes.byref(length), ctypes.byref(start)) == 0
+    assert (length.value, start.value, out[0], out[1]) == (6, 144, 109, -1)
+    assert lib.b200kv_key_range_page_table(table.ctypes.data, 10, 150, 16, 4, 4, out.ctypes.data,
+                                           ctypes.byref(length), ctypes.byref(start)) == -1
