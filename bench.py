@@ -380,6 +380,9 @@ class RankWorkload:
             a.batch_count, a.q_heads, a.rotary_dim, a.norm_mode = B, HQ, D, kv.NORM_RSQRT_APPROX
             a.status = self.status.data_ptr()
             a.ticket = None if args.no_tickets else self.ticket.data_ptr()
+            # KV-head sharding with the library's exchange: the step itself ends with the all-gather
+            # (inside the one-launch kernel where the step runs as that, a gather kernel behind it otherwise)
+            a.peer_gather = self.peer.handle if (self.peer is not None and not spec.key_shard) else None
         self.timed_layer = max((i for i in range(L) if self.layer_is_global(i)), default=L - 1)
         self.stream = torch.cuda.current_stream().cuda_stream
         self.launches_per_step = 0
@@ -391,8 +394,8 @@ class RankWorkload:
                 n = kv.layer_step_launches(self.layers[i])
             self.kernels_per_layer.append(n)
             self.launches_per_step += n
-        if self.peer is not None:
-            self.launches_per_step += 1              # the peer-memory all-gather kernel
+        if self.peer is not None and spec.key_shard:
+            self.launches_per_step += 1              # the peer-memory merge kernel (key-range sharding)
 
     def layer_is_global(self, i: int) -> bool:
         nl, ng = self.spec.n_local, self.spec.n_global
@@ -505,7 +508,7 @@ class RankWorkload:
         if self.peer is None:
             dist.all_gather_into_tensor(self.out_all, self.out)
             return
-        self.gathered_ptr = self.peer.allgather(self.out, self.out_bytes, status=self.status, stream=self.stream)
+        self.gathered_ptr = self.peer.gathered()          # the step's own exchange has been enqueued with it
         if not self.gather_checked:          # once, in the warm-up: the same rows as NCCL's all-gather
             self.gather_checked = True
             dist.all_gather_into_tensor(self.out_all, self.out)
@@ -1128,9 +1131,11 @@ def workload_config(args, world, where, parallelism=None, layers=None):
         "parallelism": parallelism or f"x{world}",
         "partition": args.partition,
         "where": where,
-        "launch": ("one CUDA graph replay per step" + (" (cfg1: sixteen one-kernel steps per replay)"
-                                                         if args.workload == "cfg1" else "")
-                   if (args.graph == "on" or (args.graph == "auto" and args.workload in ("cfg1", "cfg2")))
+        "launch": ("one CUDA graph replay per step" + (" (sixteen one-kernel steps per replay)"
+                                                         if args.workload in ("cfg1", "cfg4") else "")
+                   if (args.graph == "on" or (args.graph == "auto" and (args.workload in ("cfg1", "cfg2") or (
+                       args.workload == "cfg4" and world > 1 and args.gather == "peer" and args.shard == "heads"
+                       and not args.no_tickets))))
                    else "stream launches (programmatic dependent launch between kernels)"),
     }
     if args.workload == "cfg3":
@@ -1606,6 +1611,11 @@ def measure_workload(args, kv, torch, dist, world, rank, sampler=None, verify=Tr
         ctx = ctx_all[shard_sequences(ctx_all, args.emulate_world)[args.emulate_rank]]
     e2e_warm = 3
     use_graph = args.graph == "on" or (args.graph == "auto" and args.workload in ("cfg1", "cfg2"))
+    # the KV-head-sharded long context with the exchange inside the step's kernel: replayed from a graph as well,
+    # so that the ranks' launches do not drift against each other under the hosts' jitter
+    if args.graph == "auto" and args.workload == "cfg4" and world > 1 and args.gather == "peer" \
+            and not spec.key_shard and not args.no_tickets:
+        use_graph = True
     probe_steps = 11                        # steps after the timed regions that carry the per-kernel events
     # a one-layer step is a single kernel: sixteen steps per replayed graph (see RankWorkload.enable_graph)
     steps_per_graph = 16 if (use_graph and spec.n_local + spec.n_global == 1) else 1

@@ -107,6 +107,7 @@ class LayerStepArgs(ctypes.Structure):
         ("status", c_void_p),
         ("event_before_attention", c_void_p), ("event_after_attention", c_void_p),
         ("ticket", c_void_p),
+        ("peer_gather", c_void_p),
     ]
 
 
@@ -209,6 +210,7 @@ _SIGNATURES = {
     "b200kv_peer_buffer_destroy": (c_int, [_P]),
     "b200kv_peer_buffer_set_wait_clocks": (c_int, [_P, c_int64]),
     "b200kv_peer_buffer_reset": (c_int, [_P]),
+    "b200kv_peer_buffer_gathered": (c_int, [_P, POINTER(_P)]),
     "b200kv_peer_buffer_create_loopback": (c_int, [c_int64, c_int32, c_int32, POINTER(_P)]),
     "b200kv_peer_buffer_post": (c_int, [_P, c_int32, ctypes.c_uint32, _P]),
     "b200kv_bounded_wait_selftest": (c_int, [c_int64, _P, _P, _P]),
@@ -590,6 +592,18 @@ class PeerBuffer:
     def post(self, from_rank: int, epoch: int, stream=None):
         _check(load_library().b200kv_peer_buffer_post(self._handle, from_rank, epoch, _stream(stream)),
                "b200kv_peer_buffer_post", True)
+
+    @property
+    def handle(self) -> int:
+        """The raw handle, for LayerStepArgs.peer_gather."""
+        return self._handle.value
+
+    def gathered(self) -> int:
+        """Device address of what the most recent gather delivered ([world][slot_bytes])."""
+        out = c_void_p()
+        _check(load_library().b200kv_peer_buffer_gathered(self._handle, ctypes.byref(out)),
+               "b200kv_peer_buffer_gathered", True)
+        return out.value or 0
 
     def reset(self):
         _check(load_library().b200kv_peer_buffer_reset(self._handle), "b200kv_peer_buffer_reset", True)

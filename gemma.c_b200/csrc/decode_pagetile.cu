@@ -111,6 +111,9 @@ struct TileParams {
   // not write this layer's cache (they belong to another layer's step), so no
   // tile has to wait for them.
   int32_t cache_settled;
+  // The all-gather of the output rows over peer memory, finished by this kernel
+  // (world == 0: none). The rows of this rank are [batch, q_heads, 256] bf16.
+  PeerEpilogue peer;
 };
 
 // One tile: the 512-byte slices of head `head` for `tile_tokens` tokens of a
@@ -125,6 +128,15 @@ __device__ __forceinline__ void tma_load_tile(uint32_t dst, const CUtensorMap *m
       "l"(reinterpret_cast<uint64_t>(map)), "r"(0), "r"(head), "r"(offset), "r"(page),
       "r"(bar), "l"(policy)
       : "memory");
+}
+
+__device__ __forceinline__ void st_release_sys(uint32_t *addr, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *addr) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
 }
 
 template <int kMode>
@@ -456,34 +468,6 @@ __global__ __launch_bounds__(kTileThreads, 2) void decode_pagetile_kernel(
     }
   }
 
-  auto write_rows = [&]() {
-#pragma unroll
-    for (int g = 0; g < 2; ++g) {
-      const int64_t row = int64_t(b) * p.q_heads + h * 2 + g;
-      const float inv = L[g] > 0.0f ? 1.0f / L[g] : 0.0f;
-      p.out[row * D + t] = __float2bfloat16_rn(A[g] * inv);
-      if (p.lse != nullptr && t == 0) {
-        p.lse[row] = L[g] > 0.0f ? (M[g] + lg2_approx(L[g])) * 0.6931471805599453f
-                                 : -INFINITY;
-      }
-    }
-  };
-  if (r_eff <= 1) {  // the only range of its (sequence, head), or no live key
-    write_rows();
-    return;
-  }
-
-  // One partial of two rows, then the ticket: the last CTA of the pair merges.
-  const int64_t pair = (int64_t(b) * H + h) * p.ranges;  // first slot of the pair
-#pragma unroll
-  for (int g = 0; g < 2; ++g) {
-    const int64_t slot = (pair + r) * 2 + g;
-    p.partial_acc[slot * D + t] = A[g];
-    if (t == 0) {
-      p.partial_m[slot] = M[g];
-      p.partial_l[slot] = L[g];
-    }
-  }
   // A ticket: the CTA's writes are complete in every thread's view after the
   // barrier; one acq_rel atomic at GPU scope then publishes them (release: the
   // writes the barrier ordered before it) and, for the CTA that arrives last,
@@ -501,6 +485,82 @@ __global__ __launch_bounds__(kTileThreads, 2) void decode_pagetile_kernel(
     named_barrier_sync(1, kTileConsumerThreads);
     return s_flag[1] != 0;
   };
+  auto write_rows = [&]() {
+#pragma unroll
+    for (int g = 0; g < 2; ++g) {
+      const int64_t row = int64_t(b) * p.q_heads + h * 2 + g;
+      const float inv = L[g] > 0.0f ? 1.0f / L[g] : 0.0f;
+      p.out[row * D + t] = __float2bfloat16_rn(A[g] * inv);
+      if (p.lse != nullptr && t == 0) {
+        p.lse[row] = L[g] > 0.0f ? (M[g] + lg2_approx(L[g])) * 0.6931471805599453f
+                                 : -INFINITY;
+      }
+    }
+  };
+  // The exchange that may follow: a final CTA stores its two rows into this
+  // rank's slot of every rank's gather buffer (plain peer stores over NVLink, no
+  // multicast); the last final CTA on this GPU -- a counter next to the flags --
+  // fences, publishes the call's epoch to every peer and waits, bounded, until
+  // every peer's epoch has arrived here. "This kernel is complete" then means
+  // "every rank's rows are in this GPU's buffer", without another launch.
+  const PeerEpilogue &peer = p.peer;
+  const uint32_t epoch = peer.world > 0 ? *peer.epoch + 1u : 0u;
+  const int64_t half = int64_t(epoch & 1u) * peer.world;
+  auto peer_store = [&](int64_t row, int word, uint2 v) {  // 8 bytes of a row of this rank
+    for (int rk = 0; rk < peer.world; ++rk) {
+      uint2 *dst = reinterpret_cast<uint2 *>(peer.data[rk] + (half + peer.rank) * peer.slot_packs);
+      dst[row * (D / 4) + word] = v;
+    }
+  };
+  auto peer_finish = [&]() {  // all threads of the consumer warps call it
+    if (peer.world <= 0) return;
+    __threadfence_system();
+    if (!last_to_arrive(peer.done, p.batch_count * H)) return;
+    if (t < peer.world) {
+      __threadfence_system();
+      st_release_sys(peer.flags[t] + half + peer.rank, epoch);
+      const uint32_t *mine = peer.flags[peer.rank] + half + t;
+      const long long start = clock64();
+      while (int32_t(ld_acquire_sys(mine) - epoch) < 0) {
+        if (clock64() - start > peer.wait_clocks) {
+          set_status(p.status, B200KV_STATUS_WAIT_TIMEOUT);
+          break;
+        }
+        __nanosleep(100);
+      }
+    }
+    named_barrier_sync(1, kTileConsumerThreads);
+    if (t == 0) {
+      *peer.epoch = epoch;
+      *peer.done = 0u;
+    }
+  };
+  if (r_eff <= 1) {  // the only range of its (sequence, head), or no live key
+    write_rows();
+    for (int rk = 0; rk < peer.world; ++rk) {  // the same two rows for the peers, a dim per thread
+      __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(
+          peer.data[rk] + (half + peer.rank) * peer.slot_packs);
+#pragma unroll
+      for (int g = 0; g < 2; ++g) {
+        const float inv = L[g] > 0.0f ? 1.0f / L[g] : 0.0f;
+        dst[(int64_t(b) * p.q_heads + h * 2 + g) * D + t] = __float2bfloat16_rn(A[g] * inv);
+      }
+    }
+    peer_finish();
+    return;
+  }
+
+  // One partial of two rows, then the ticket: the last CTA of the pair merges.
+  const int64_t pair = (int64_t(b) * H + h) * p.ranges;  // first slot of the pair
+#pragma unroll
+  for (int g = 0; g < 2; ++g) {
+    const int64_t slot = (pair + r) * 2 + g;
+    p.partial_acc[slot * D + t] = A[g];
+    if (t == 0) {
+      p.partial_m[slot] = M[g];
+      p.partial_l[slot] = L[g];
+    }
+  }
   // Merge of up to 32 partials at slots first, first + stride, ... Thread t owns
   // four dims (t % 64) of row (t / 64) % 2 and every second partial, parity
   // t / 128: all its loads are independent and go out together, before the
@@ -564,9 +624,10 @@ __global__ __launch_bounds__(kTileThreads, 2) void decode_pagetile_kernel(
       const int64_t row = int64_t(b) * p.q_heads + h * 2 + g;
       const __nv_bfloat162 lo = __floats2bfloat162_rn(value.x * inv, value.y * inv);
       const __nv_bfloat162 hi = __floats2bfloat162_rn(value.z * inv, value.w * inv);
-      reinterpret_cast<uint2 *>(p.out + row * D)[col] =
-          make_uint2(*reinterpret_cast<const uint32_t *>(&lo),
-                     *reinterpret_cast<const uint32_t *>(&hi));
+      const uint2 packed = make_uint2(*reinterpret_cast<const uint32_t *>(&lo),
+                                      *reinterpret_cast<const uint32_t *>(&hi));
+      reinterpret_cast<uint2 *>(p.out + row * D)[col] = packed;
+      peer_store(row, col, packed);
       if (p.lse != nullptr && col == 0) {
         p.lse[row] = sum > 0.0f ? (top + lg2_approx(sum)) * 0.6931471805599453f : -INFINITY;
       }
@@ -581,6 +642,7 @@ __global__ __launch_bounds__(kTileThreads, 2) void decode_pagetile_kernel(
     merge(pair, 1, r_eff);
     write_merged_rows();
     if (t == 0) *pair_ticket = 0u;  // ready for the next launch
+    peer_finish();
     return;
   }
   // More than 32 ranges (long contexts on few heads): the last CTA of each group
@@ -605,6 +667,7 @@ __global__ __launch_bounds__(kTileThreads, 2) void decode_pagetile_kernel(
   merge(pair, kMergeGroup, groups);
   write_merged_rows();
   if (t == 0) *pair_ticket = 0u;
+  peer_finish();
 }
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
@@ -716,7 +779,8 @@ bool decode_pagetile_preferred(const Gemma4KvCacheConfig &c, int q_heads,
 }
 
 cudaError_t decode_layer_step_pagetile_bf16(const AppendArgs *ap, const DecodeArgs &a,
-                                            uint32_t *ticket, cudaStream_t stream) {
+                                            uint32_t *ticket, cudaStream_t stream,
+                                            const PeerEpilogue *peer) {
   const Gemma4KvCacheConfig &c = a.cfg;
   cudaError_t st = validate_decode_args(a);
   if (st != cudaSuccess) return st;
@@ -760,6 +824,7 @@ cudaError_t decode_layer_step_pagetile_bf16(const AppendArgs *ap, const DecodeAr
   p.ticket = ticket;
   p.status = a.status;
   p.tile_tokens = tile_tokens_of(c.page_size);
+  if (peer != nullptr) p.peer = *peer;
   // Ranges per (sequence, head): enough CTAs for two per SM, no more than the
   // scratch holds (batch * q_heads * num_splits rows = two rows per range) or
   // the chunks a sequence can have.

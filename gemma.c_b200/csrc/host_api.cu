@@ -944,6 +944,16 @@ void b200kv_plan_splits(int32_t batch_count, int32_t max_live_keys,
 
 namespace {
 
+// The exchange of a layer-step that did not run as the one-launch kernel: the
+// stand-alone all-gather kernel behind the step's last launch.
+int gather_after(const B200KvLayerStepArgs *s, cudaStream_t st) {
+  if (s->peer_gather == nullptr) return cudaSuccess;
+  return b200kv::peer_allgather(
+      s->peer_gather, s->out,
+      int64_t(s->batch_count) * s->q_heads * s->cache_config.head_dim * 2, s->status,
+      st, nullptr);
+}
+
 // raw_from_predecessor: the raw rows come from the kernel enqueued just before
 // (the attention-layer call's QKV projection), not from an earlier step.
 int layer_step(const B200KvLayerStepArgs *s, bool raw_from_predecessor,
@@ -1009,8 +1019,14 @@ int layer_step(const B200KvLayerStepArgs *s, bool raw_from_predecessor,
       B200KV_TRY(cudaEventRecord(
           static_cast<cudaEvent_t>(s->event_before_attention), st));
     }
-    const cudaError_t st_tile =
-        b200kv::decode_layer_step_pagetile_bf16(&a, d, s->ticket, st);
+    b200kv::PeerEpilogue peer = {};
+    if (s->peer_gather != nullptr) {
+      B200KV_TRY(b200kv::peer_epilogue_begin(
+          s->peer_gather, int64_t(s->batch_count) * s->q_heads * d.cfg.head_dim * 2,
+          &peer));
+    }
+    const cudaError_t st_tile = b200kv::decode_layer_step_pagetile_bf16(
+        &a, d, s->ticket, st, s->peer_gather != nullptr ? &peer : nullptr);
     if (st_tile != cudaSuccess) return st_tile;
     if (s->event_after_attention != nullptr) {
       B200KV_TRY(cudaEventRecord(
@@ -1034,7 +1050,7 @@ int layer_step(const B200KvLayerStepArgs *s, bool raw_from_predecessor,
       B200KV_TRY(cudaEventRecord(
           static_cast<cudaEvent_t>(s->event_after_attention), st));
     }
-    return cudaSuccess;
+    return gather_after(s, st);
   }
   // Two launches: stream order makes the appended row visible to the attention
   // kernel, the job the grid-wide barrier does inside the reference's fused
@@ -1051,7 +1067,7 @@ int layer_step(const B200KvLayerStepArgs *s, bool raw_from_predecessor,
     B200KV_TRY(cudaEventRecord(
         static_cast<cudaEvent_t>(s->event_after_attention), st));
   }
-  return cudaSuccess;
+  return gather_after(s, st);
 }
 
 }  // namespace
@@ -1069,13 +1085,14 @@ int32_t b200kv_layer_step_launches(const B200KvLayerStepArgs *s) {
   if (s->split_size == 0 && s->rotary_dim == 256 && fused_layer_step_enabled() &&
       b200kv::decode_pagetile_preferred(c, s->q_heads, s->batch_count,
                                         s->ticket != nullptr)) {
-    return 1;
+    return 1;  // the exchange, if any, is part of it
   }
+  const int32_t gather = s->peer_gather != nullptr ? 1 : 0;  // the stand-alone gather kernel
   if (s->split_size == 0 && fused_layer_step_enabled() && s->rotary_dim == 256 &&
       b200kv::decode_balanced_supported(c, s->q_heads, s->batch_count)) {
-    return 2;  // fused attention kernel + combine
+    return 2 + gather;  // fused attention kernel + combine
   }
-  return (s->split_size > 0 && s->num_splits == 1) ? 2 : 3;  // append, attention[, combine]
+  return ((s->split_size > 0 && s->num_splits == 1) ? 2 : 3) + gather;  // append, attention[, combine]
 }
 
 int b200kv_decode_layer_step_tiled_bf16(const B200KvLayerStepArgs *s,
@@ -1285,6 +1302,10 @@ int b200kv_peer_buffer_post(void *handle, int32_t from_rank, uint32_t epoch,
 
 int b200kv_peer_buffer_reset(void *handle) {
   return b200kv::peer_buffer_reset(handle);
+}
+
+int b200kv_peer_buffer_gathered(void *handle, void **gathered) {
+  return b200kv::peer_buffer_gathered(handle, gathered);
 }
 
 int b200kv_bounded_wait_selftest(int64_t clock_limit, int32_t *d_status,

@@ -115,9 +115,28 @@ bool decode_pagetile_supported(const Gemma4KvCacheConfig &cfg, int q_heads,
                                int batch_count);
 bool decode_pagetile_preferred(const Gemma4KvCacheConfig &cfg, int q_heads,
                                int batch_count, bool has_ticket);
+// What the one-launch layer-step needs to finish with the all-gather of its
+// output rows over peer memory (peer_gather.cu holds the buffers; world == 0:
+// no exchange): every final CTA stores its rows into slot `rank` of every rank's
+// buffer, the last of them on this GPU publishes the epoch flag to the peers and
+// waits (bounded) for theirs.
+struct PeerEpilogue {
+  uint4 *data[8];      // rank r's gathered buffer [2][world][slot_packs]
+  uint32_t *flags[8];  // rank r's flags [2][world]
+  uint32_t *epoch;     // this rank's call counter
+  uint32_t *done;      // this rank's count of finished (sequence, head) pairs, zero between calls
+  int64_t slot_packs;
+  long long wait_clocks;
+  int32_t rank;
+  int32_t world;
+};
+// Fills `out` from a peer buffer handle for a call that gathers `bytes` per
+// rank and counts the call; cudaErrorInvalidValue if it does not fit.
+cudaError_t peer_epilogue_begin(void *handle, int64_t bytes, PeerEpilogue *out);
 cudaError_t decode_layer_step_pagetile_bf16(const AppendArgs *append,
                                             const DecodeArgs &decode,
-                                            uint32_t *ticket, cudaStream_t stream);
+                                            uint32_t *ticket, cudaStream_t stream,
+                                            const PeerEpilogue *peer = nullptr);
 
 // Decode projections either side of the KV path (decode_projection.cu), rows of
 // one token each; hidden size 3840. Weights are column-major: output column c
@@ -188,6 +207,8 @@ cudaError_t peer_buffer_set_wait_clocks(void *handle, long long clocks);
 cudaError_t peer_buffer_post(void *handle, int from_rank, uint32_t epoch,
                              cudaStream_t stream);
 cudaError_t peer_buffer_reset(void *handle);
+// The half of the gathered buffer the most recent call filled ([world][slot_bytes]).
+cudaError_t peer_buffer_gathered(void *handle, void **gathered);
 // One warp waits on an mbarrier that nothing arrives at, with the bounded wait
 // every kernel of the library uses, for `clock_limit` SM clocks (bounded_wait.cu).
 cudaError_t bounded_wait_selftest(long long clock_limit, int32_t *status,

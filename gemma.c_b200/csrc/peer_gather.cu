@@ -306,6 +306,35 @@ cudaError_t peer_buffer_create_loopback(int64_t slot_bytes, int world, int rank,
   return cudaDeviceSynchronize();
 }
 
+cudaError_t peer_epilogue_begin(void *handle, int64_t bytes, PeerEpilogue *out) {
+  PeerBuffer *b = static_cast<PeerBuffer *>(handle);
+  if (b == nullptr || out == nullptr || !b->connected || bytes <= 0 || bytes % 16 != 0 ||
+      bytes > b->slot_bytes) {
+    return cudaErrorInvalidValue;
+  }
+  *out = PeerEpilogue{};
+  for (int r = 0; r < b->world; ++r) {
+    out->data[r] = reinterpret_cast<uint4 *>(b->peer[r]);
+    out->flags[r] = reinterpret_cast<uint32_t *>(b->peer[r] + flag_offset(*b));
+  }
+  uint32_t *own = reinterpret_cast<uint32_t *>(b->base + flag_offset(*b));
+  out->epoch = own + 2 * kMaxPeers;
+  out->done = own + 2 * kMaxPeers + 1;
+  out->slot_packs = b->slot_bytes / 16;
+  out->wait_clocks = b->wait_clocks;
+  out->rank = b->rank;
+  out->world = b->world;
+  b->calls += 1;
+  return cudaSuccess;
+}
+
+cudaError_t peer_buffer_gathered(void *handle, void **gathered) {
+  PeerBuffer *b = static_cast<PeerBuffer *>(handle);
+  if (b == nullptr || gathered == nullptr) return cudaErrorInvalidValue;
+  *gathered = b->base + int64_t(b->calls & 1u) * b->world * b->slot_bytes;
+  return cudaSuccess;
+}
+
 cudaError_t peer_buffer_set_wait_clocks(void *handle, long long clocks) {
   PeerBuffer *b = static_cast<PeerBuffer *>(handle);
   if (b == nullptr || clocks <= 0) return cudaErrorInvalidValue;

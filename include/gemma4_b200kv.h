@@ -520,6 +520,17 @@ typedef struct B200KvLayerStepArgs {
    * within the summation order of the partials. Calls that may overlap on the
    * GPU need tickets (and scratch) of their own. */
   uint32_t *ticket;
+  /* Optional, KV-head-sharded mode: a connected handle of
+   * b200kv_peer_buffer_create. The step then ends with the all-gather of `out`
+   * ([batch, q_heads, head_dim] of this rank, <= the handle's slot_bytes) over
+   * peer memory, as if b200kv_peer_allgather(handle, out, ...) followed it; read
+   * the result with b200kv_peer_buffer_gathered. Where the step runs as the
+   * one-launch kernel the exchange is part of that kernel: the CTA that
+   * finishes a (sequence, head) stores its rows into this rank's slot on every
+   * GPU, the last of them publishes the flag and waits (bounded, see `status`)
+   * for the peers' -- compute and collective in one launch. Every rank makes
+   * the call with the same batch and head counts. */
+  void *peer_gather;
 } B200KvLayerStepArgs;
 
 int b200kv_decode_layer_step_bf16(const B200KvLayerStepArgs *args,
@@ -712,6 +723,9 @@ int b200kv_peer_buffer_destroy(void *handle);
  * would -- so a wait can be seen to run out (nothing posted) and to succeed
  * (posted) without a second GPU. */
 int b200kv_peer_buffer_set_wait_clocks(void *handle, int64_t clocks);
+/* Device pointer to what the most recent gather through `handle` delivered
+ * ([world][slot_bytes]; valid until the call after next). */
+int b200kv_peer_buffer_gathered(void *handle, void **gathered);
 int b200kv_peer_buffer_reset(void *handle);
 int b200kv_peer_buffer_create_loopback(int64_t slot_bytes, int32_t world,
                                        int32_t rank, void **handle);

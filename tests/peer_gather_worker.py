@@ -75,6 +75,72 @@ def main():
         assert err <= 2.0 ** -7 * max(1.0, want.abs().max().item()), f"rank {rank} merge {it}: {err}"
         assert (merged_lse.double() - want_lse).abs().max().item() <= 1e-4
     dist.barrier()
+    # The sharded layer-step itself: every rank holds 8 / world KV heads of one sequence's cache, runs the step
+    # with the exchange inside it (LayerStepArgs.peer_gather) and must end up with the attention rows of ALL heads:
+    # compared with the double-precision attention over the unsharded cache.
+    if 8 % world == 0:
+        from oracle import binding as orc
+        from tests import helpers
+        from tests.helpers import ATTN_MAX_ABS, attention_error
+        from gemma_c_b200 import sharding
+
+        orc.build()
+        HQ, H, D, steps = 16, 8, 256, 3
+        start = np.array([6000], np.int32)
+        acase = helpers.make_append_case(77, start, window=0, ring_pages=None, max_pos=int(start[0]) + steps + 1)
+        cfg_t = acase.cfg
+        rng = np.random.default_rng(123)                      # the same cache on every rank
+        elems = cfg_t[0] * cfg_t[1] * cfg_t[2] * cfg_t[5] * cfg_t[6]
+        ck = orc.f32_to_bf16(rng.standard_normal(elems, dtype=np.float32))
+        cv = orc.f32_to_bf16(rng.standard_normal(elems, dtype=np.float32))
+        h_local = H // world
+        my_k, my_cfg = sharding.slice_cache_heads(ck, cfg_t, world, rank)
+        my_v, _ = sharding.slice_cache_heads(cv, cfg_t, world, rank)
+        lo, hi = sharding.kv_head_range(H, world, rank)
+        dev = lambda a: torch.from_numpy(np.ascontiguousarray(a).view(np.int16) if a.dtype == np.uint16 else np.ascontiguousarray(a)).cuda()
+        sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+        ns = kv.plan_balanced(1, sms)
+        hq_local = 2 * h_local
+        dck, dcv = dev(my_k), dev(my_v)
+        dq = torch.zeros((1, hq_local, D), dtype=torch.int16, device="cuda")
+        dout = torch.zeros_like(dq)
+        pm = torch.zeros(hq_local * ns, dtype=torch.float32, device="cuda")
+        pl, pacc = pm.clone(), torch.zeros(hq_local * ns * D, dtype=torch.float32, device="cuda")
+        ticket = torch.zeros(h_local * kv.TICKETS_PER_HEAD, dtype=torch.int32, device="cuda")
+        step_buf = kv.PeerBuffer(hq_local * D * 2, world, rank)
+        mine = torch.tensor(list(step_buf.export), dtype=torch.uint8, device="cuda")
+        dist.all_gather_into_tensor(everyone, mine)
+        step_buf.connect(bytes(everyone.cpu().tolist()))
+        dist.barrier()
+        table, qw, kw_, cos, sin = (dev(x) for x in (acase.page_table, acase.q_w, acase.k_w, acase.cos, acase.sin))
+        qp_full = np.zeros((1, HQ, D), np.uint16)
+        for t in range(steps):
+            raw = [helpers.bf16_normal(rng, (1, n, D)) for n in (HQ, H, H)]       # same rows on every rank
+            pos, length = (start + t).astype(np.int32), (start + t + 1).astype(np.int32)
+            rq, rk, rv = dev(raw[0][:, 2 * lo:2 * hi]), dev(raw[1][:, lo:hi]), dev(raw[2][:, lo:hi])
+            dpos, dlen = dev(pos), dev(length)
+            a = kv.LayerStepArgs()
+            a.q, a.out, a.lse = dq.data_ptr(), dout.data_ptr(), None
+            a.partial_m, a.partial_l, a.partial_acc = pm.data_ptr(), pl.data_ptr(), pacc.data_ptr()
+            a.cache_k, a.cache_v, a.cache_config = dck.data_ptr(), dcv.data_ptr(), kv.make_kv_config(*my_cfg)
+            a.page_table, a.token_position, a.seq_lengths = table.data_ptr(), dpos.data_ptr(), dlen.data_ptr()
+            a.cache_layer, a.split_size, a.num_splits, a.softmax_scale = 0, 0, ns, 1.0 / 16.0
+            a.raw_q, a.raw_k, a.raw_v = rq.data_ptr(), rk.data_ptr(), rv.data_ptr()
+            a.q_norm_weight, a.k_norm_weight, a.cos, a.sin = qw.data_ptr(), kw_.data_ptr(), cos.data_ptr(), sin.data_ptr()
+            a.batch_count, a.q_heads, a.rotary_dim, a.norm_mode = 1, hq_local, D, kv.NORM_IEEE
+            a.status, a.ticket, a.peer_gather = status.data_ptr(), ticket.data_ptr(), step_buf.handle
+            assert kv.layer_step_launches(a) == 1, "the sharded step runs as the one-launch kernel"
+            kv.decode_layer_step(a)
+            torch.cuda.synchronize()
+            assert status[0].item() == 0 and not ticket.any(), f"rank {rank} step {t}"
+            got = read_device(step_buf.gathered(), world * hq_local * D // 2, np.int32).view(np.uint16)
+            orc.decode_append(qp_full, ck, cv, cfg_t, acase.page_table, pos, 0, raw[0], raw[1], raw[2], acase.q_w,
+                              acase.k_w, acase.cos, acase.sin, 1, HQ, D)
+            ref, _ = orc.decode_attention_f64(qp_full, ck, cv, acase.page_table, length, cfg_t, 0, 1.0 / 16.0, 1, HQ)
+            max_abs, _ = attention_error(got, ref)             # rank-major slots = head order
+            assert max_abs <= ATTN_MAX_ABS, f"rank {rank} step {t}: gathered rows differ from the unsharded attention: {max_abs}"
+        dist.barrier()
+        step_buf.close()
     # A rank misses a call (between steps, nothing of its own in flight): the others' waits run out after the
     # short limit set here, they report B200KV_STATUS_WAIT_TIMEOUT and return; every rank then resets its buffer
     # between two host barriers and the next matched call gathers correctly again.

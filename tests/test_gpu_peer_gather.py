@@ -170,3 +170,69 @@ def test_key_range_shards_merge_to_the_unsharded_attention(kv, orc):
     max_abs, max_rel = attention_error(orc.f32_to_bf16(merged.astype(np.float32)), ref)
     assert max_abs <= ATTN_MAX_ABS and max_rel <= ATTN_MAX_REL, (max_abs, max_rel)
     assert np.abs(merged_lse - ref_lse.reshape(HQ)).max() <= LSE_MAX_ABS
+
+
+def _layer_step_args(kv, case, acase, d, num_splits, ticket, status, peer):
+    a = kv.LayerStepArgs()
+    a.q, a.out, a.lse = d["q"].data_ptr(), d["out"].data_ptr(), None
+    a.partial_m, a.partial_l, a.partial_acc = d["pm"].data_ptr(), d["pl"].data_ptr(), d["pacc"].data_ptr()
+    a.cache_k, a.cache_v, a.cache_config = d["ck"].data_ptr(), d["cv"].data_ptr(), kv.make_kv_config(*acase.cfg)
+    a.page_table, a.token_position, a.seq_lengths = d["table"].data_ptr(), d["pos"].data_ptr(), d["len"].data_ptr()
+    a.cache_layer, a.split_size, a.num_splits, a.softmax_scale = 0, 0, num_splits, 1.0 / 16.0
+    a.raw_q, a.raw_k, a.raw_v = d["rq"].data_ptr(), d["rk"].data_ptr(), d["rv"].data_ptr()
+    a.q_norm_weight, a.k_norm_weight, a.cos, a.sin = (d["qw"].data_ptr(), d["kw"].data_ptr(), d["cos"].data_ptr(),
+                                                      d["sin"].data_ptr())
+    a.batch_count, a.q_heads, a.rotary_dim, a.norm_mode = acase.token_position.size, acase.q_heads, 256, kv.NORM_IEEE
+    a.status, a.ticket, a.peer_gather = status.data_ptr(), ticket.data_ptr(), peer.handle
+    return a
+
+
+@pytest.mark.parametrize("name,start,window,heads", [
+    ("one sequence, ring, 8 heads: one launch", [1500], 1024, 8),
+    ("one sequence, linear, 2 heads (a sharded rank): one launch, grouped merge", [9000], 0, 2),
+    ("forty sequences: balanced kernel + combine + gather kernel", list(range(100, 140)), 64, 8),
+])
+def test_layer_step_ends_with_the_gather(kv, orc, name, start, window, heads):
+    """LayerStepArgs.peer_gather on one rank: after the step the gather buffer holds the step's attention rows,
+    call after call (the halves alternate), whether the exchange ran inside the one-launch kernel or as the
+    gather kernel behind a step of several launches."""
+    from tests import helpers
+    from tests.gpu_util import dev, host_u16
+
+    rng = np.random.default_rng(5)
+    start = np.asarray(start, np.int32)
+    B, HQ, D = start.size, 2 * heads, 256
+    acase = helpers.make_append_case(9, start, window=window, ring_pages=None, max_pos=int(start.max()) + 4,
+                                     kv_heads=heads, q_heads=HQ)
+    cfg_t = acase.cfg
+    elems = cfg_t[0] * cfg_t[1] * cfg_t[2] * cfg_t[5] * cfg_t[6]
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    ns = kv.plan_balanced(B, sms)
+    d = dict(ck=dev(orc.f32_to_bf16(rng.standard_normal(elems, dtype=np.float32))),
+             cv=dev(orc.f32_to_bf16(rng.standard_normal(elems, dtype=np.float32))),
+             q=torch.zeros((B, HQ, D), dtype=torch.int16, device="cuda"),
+             out=torch.zeros((B, HQ, D), dtype=torch.int16, device="cuda"),
+             pm=torch.zeros(B * HQ * ns, dtype=torch.float32, device="cuda"),
+             pl=torch.zeros(B * HQ * ns, dtype=torch.float32, device="cuda"),
+             pacc=torch.zeros(B * HQ * ns * D, dtype=torch.float32, device="cuda"),
+             table=dev(acase.page_table), qw=dev(acase.q_w), kw=dev(acase.k_w), cos=dev(acase.cos), sin=dev(acase.sin),
+             rq=dev(acase.q), rk=dev(acase.k), rv=dev(acase.v))
+    ticket = torch.zeros(B * heads * kv.TICKETS_PER_HEAD, dtype=torch.int32, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    peer = kv.PeerBuffer(B * HQ * D * 2, 1, 0)
+    seen = []
+    for t in range(3):
+        d["pos"], d["len"] = dev((start + t).astype(np.int32)), dev((start + t + 1).astype(np.int32))
+        a = _layer_step_args(kv, None, acase, d, ns, ticket, status, peer)
+        expected_launches = 1 if B == 1 else 3
+        assert kv.layer_step_launches(a) == expected_launches, name
+        kv.decode_layer_step(a)
+        torch.cuda.synchronize()
+        assert status[0].item() == 0 and not ticket.any()
+        ptr = peer.gathered()
+        seen.append(ptr)
+        got = read_device(ptr, B * HQ * D // 2, np.int32).view(np.uint16)
+        assert np.array_equal(got, host_u16(d["out"])), (name, t)
+        assert host_u16(d["out"]).any()
+    assert seen[0] != seen[1] and seen[0] == seen[2]
+    peer.close()
