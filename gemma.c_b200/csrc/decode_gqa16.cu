@@ -23,6 +23,7 @@
 
 #include "balanced_partition.cuh"
 #include "kernels.cuh"
+#include "mma_common.cuh"
 
 namespace b200kv {
 
@@ -60,40 +61,9 @@ __device__ __forceinline__ uint32_t gqa16_row_offset(int key) {
          uint32_t(key & 1) * Gqa16Traits::kRowBytes;
 }
 
-__device__ __forceinline__ void mma_bf16_m16n8k16(float (&d)[4], uint32_t a0,
-                                                  uint32_t a1, uint32_t a2,
-                                                  uint32_t a3, uint32_t b0,
-                                                  uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 "
-      "{%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
-      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
-  asm volatile(
-      "ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-      : "r"(addr));
-}
-
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4],
-                                                  uint32_t addr) {
-  asm volatile(
-      "ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-      : "r"(addr));
-}
-
 __device__ __forceinline__ void consumer_barrier() {
   asm volatile("bar.sync 1, %0;" ::"n"(Gqa16Traits::kConsumerWarps * 32)
                : "memory");
-}
-
-__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
-  const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<const uint32_t *>(&h);
 }
 
 struct Gqa16Ring {

@@ -15,8 +15,14 @@
 //    [dim][head][page offset][page] fetches the slices of up to 16 tokens of a
 //    page as one tile (cp.async.bulk.tensor.4d, completion on an mbarrier, no
 //    multicast), two tiles per 32-token stage and tensor, three stages.
-//  * Eight consumer warps take four tokens of a stage each (the arithmetic of
-//    decode_common.cuh), merge their running (m, l, acc) through the idle ring
+//  * Pages of 8 tokens or more: the stage's arithmetic runs on the tensor cores
+//    (bf16 mma.sync m16n8k16; see consume_half_mma). The tiles come in through a
+//    five-dimensional view of the cache that lays a tile down as four blocks of
+//    64 dims with the 128-byte swizzle, so that ldmatrix reads them without bank
+//    conflicts; stages alternate between two groups of four warps, a warp per
+//    (key half, output-dim half). Smaller pages: eight consumer warps take four
+//    tokens of a stage each (the scalar arithmetic of decode_common.cuh).
+//    Either way the warps merge their running (m, l, acc) through the idle ring
 //    at the end, and the CTA leaves ONE partial of two rows (2 KiB).
 //  * The last CTA of a (sequence, head) to arrive -- a ticket per pair, taken
 //    with a fence on either side -- merges that pair's partials and writes the
@@ -51,6 +57,7 @@
 #include "balanced_partition.cuh"
 #include "decode_common.cuh"
 #include "kernels.cuh"
+#include "mma_common.cuh"
 #include "prep_common.cuh"
 
 namespace b200kv {
@@ -71,7 +78,18 @@ constexpr int kTileConsumerThreads = TileTraits::kConsumerWarps * kWarpSize;
 // 8 consumer warps, the producer warp, and a warp that does nothing but wait
 // for the preceding kernel and then release the next one (see the kernel).
 constexpr int kTileThreads = TileTraits::kThreads + kWarpSize;
-constexpr int kTileExtraBytes = 4 * 512 + 64;  // q rows, new K/V rows, flags
+// The tensor-core variant keeps its two q rows 16 bytes further apart than a
+// row is long, so that the ldmatrix that replicates them over eight matrix rows
+// reads two bank groups instead of one.
+constexpr int kQStrideMma = 256 + 8;
+constexpr int kTileExtraBytes = 2 * kQStrideMma * 2 + 2 * 512 + 64;  // q rows, new K/V rows, flags
+// Shared-memory layout of a TMA tile (tile_tokens tokens of one head, K or V) in
+// the tensor-core variant: four blocks of 64 dims, each [tile_tokens][128 bytes],
+// written by one TMA copy with the 128-byte swizzle (the 16-byte chunk c of
+// token row r lands at chunk c ^ (r % 8)), so that the eight rows of an ldmatrix
+// tile fall into eight different bank groups. The tiles of a stage follow one
+// another as in the scalar variant (tile_tokens * 512 bytes each).
+constexpr int kMmaMinTileTokens = 8;  // a block is then a whole number of swizzle atoms
 constexpr int kTileSmemBytes = TileTraits::kRingBytes + kTileExtraBytes;
 static_assert(TileTraits::kRingBytes % 128 == 0, "rows behind the ring stay aligned");
 static_assert(2 * (kTileSmemBytes + 1024) <= 228 * 1024, "two CTAs per SM");
@@ -130,6 +148,26 @@ __device__ __forceinline__ void tma_load_tile(uint32_t dst, const CUtensorMap *m
       : "memory");
 }
 
+// The same tile through the five-dimensional view [64 dims][page offset]
+// [block of 64 dims][head][page] (tensor-core variant): the copy lays the four
+// blocks of the tile down one after the other, 128-byte rows, swizzled.
+__device__ __forceinline__ void tma_load_tile_blocked(uint32_t dst, const CUtensorMap *map,
+                                                      int head, int offset, int page,
+                                                      uint32_t bar, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      ".L2::cache_hint [%0], [%1, {%2, %3, %4, %5, %6}], [%7], %8;" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(0), "r"(offset), "r"(0), "r"(head), "r"(page),
+      "r"(bar), "l"(policy)
+      : "memory");
+}
+
+// The descriptor of a tensor map is fetched on first use; asking for it at the
+// start of the kernel takes that round trip off the first tile.
+__device__ __forceinline__ void prefetch_tensor_map(const CUtensorMap *map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+
 __device__ __forceinline__ void st_release_sys(uint32_t *addr, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
 }
@@ -139,7 +177,166 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *addr) {
   return v;
 }
 
-template <int kMode>
+// ---------------------------------------------------------------------------
+// Tensor-core arithmetic of one stage (kMma). Four warps share a stage: warp
+// (kh, dh) scores the 16 keys of half kh against the two query rows and
+// accumulates P * V for the 128 dims of half dh. Both contractions are written
+// so that nothing has to move between lanes in between:
+//
+//   S [16 x 16] = Q8 [16 x 256] * K^T: the 16 rows of the A operand are the two
+//     query rows over and over (row i is query i % 2), the B operand comes
+//     straight from the K rows by ldmatrix. Thread (g, t) then holds the scores
+//     of query g % 2 against keys 2t, 2t + 1, 2t + 8, 2t + 9 -- which is exactly
+//     the B fragment of
+//   O^T [128 x 8] += V^T [128 x 16] * P^T [16 x 8]: column n of P^T is query
+//     n % 2; V^T comes from the V rows by ldmatrix.trans; thread (g, t) ends
+//     with dims g, g + 8 (of each 16-dim tile) of both queries.
+//
+// The running maximum and sum are per query as in decode_common.cuh (exp2
+// domain); P is rounded to bf16 for the second contraction, the sum adds the
+// unrounded weights.
+// ---------------------------------------------------------------------------
+struct MmaLane {
+  uint32_t row;     // byte offset of this lane's ldmatrix row (block 0) inside a stage's K rows,
+                    // with the swizzle term of the lane's chunk already applied
+  uint32_t block;   // bytes from one 64-dim block of a tile to the next
+  uint32_t q_addr;  // its row of the q matrices: query lane % 2, chunk lane / 8
+  int key0;         // first of its four keys within the half: 2 (lane % 4)
+  int own;          // the query its scores belong to: (lane / 4) % 2
+  // Address of the lane's row for the 16-dim step `step` (0..3) of block `blk`:
+  // chunk 2 step + sel lands at chunk (2 step + sel) ^ (token % 8), and since
+  // 2 step and sel share no bit, that is (2 step) ^ (sel ^ token % 8).
+  __device__ __forceinline__ uint32_t at(uint32_t tensor, int blk, int step) const {
+    return (tensor + uint32_t(blk) * block + row) ^ uint32_t(step << 5);
+  }
+  __device__ MmaLane(int lane, int kh, int tile_tokens, uint32_t q_base) {
+    const int key = kh * 16 + ((lane >> 4) << 3) + (lane & 7);
+    const uint32_t sel = uint32_t(lane >> 3) & 1u;
+    block = uint32_t(tile_tokens) * 128u;
+    row = uint32_t(key / tile_tokens) * uint32_t(tile_tokens) * 512u +
+          uint32_t(key % tile_tokens) * 128u + ((sel ^ uint32_t(key & 7)) << 4);
+    q_addr = q_base + uint32_t(lane & 1) * uint32_t(kQStrideMma * 2) +
+             uint32_t(lane >> 3) * 16u;
+    key0 = (lane & 3) * 2;
+    own = (lane >> 2) & 1;
+  }
+};
+
+struct MmaState {
+  float acc[8][4];  // tile j: dims 16 j + g (queries 0, 1), 16 j + g + 8 (queries 0, 1)
+  float m[2];       // running maxima of the two queries, exp2 domain
+  float l_lane;     // running sum of this lane's own weights (query `own`)
+  __device__ __forceinline__ void reset() {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[j][i] = 0.0f;
+    }
+    m[0] = m[1] = -INFINITY;
+    l_lane = 0.0f;
+  }
+};
+
+// k_tensor: shared address of the stage's K rows (V rows follow at
+// kStageTensorBytes), 1024-byte aligned; mask16: live keys of the half (not
+// zero). Fragments are fetched one round ahead of the MMAs that use them: the
+// asm statements are volatile, so the order written here is the order issued.
+__device__ __forceinline__ void consume_half_mma(MmaState &st, const MmaLane &ln,
+                                                 uint32_t k_tensor, uint32_t mask16,
+                                                 int dh, float scale_log2) {
+  float s[2][2][4];  // [parity of the 16-dim step][8-key tile][fragment]
+#pragma unroll
+  for (int a = 0; a < 2; ++a) {
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) s[a][b][i] = 0.0f;
+    }
+  }
+  uint32_t qa[2][4], kb[2][2][4];
+  auto fetch_round = [&](int kp, int buf) {  // the 16-dim steps 2 kp, 2 kp + 1
+    ldmatrix_x4(qa[buf], ln.q_addr + uint32_t(kp) * 64u);
+    ldmatrix_x4(kb[buf][0], ln.at(k_tensor, kp >> 1, (2 * kp) & 3));
+    ldmatrix_x4(kb[buf][1], ln.at(k_tensor, kp >> 1, (2 * kp + 1) & 3));
+  };
+  fetch_round(0, 0);
+#pragma unroll
+  for (int kp = 0; kp < 8; ++kp) {
+    const int cur = kp & 1;
+    if (kp + 1 < 8) fetch_round(kp + 1, cur ^ 1);
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      mma_bf16_m16n8k16(s[j][0], qa[cur][2 * j], qa[cur][2 * j], qa[cur][2 * j + 1],
+                        qa[cur][2 * j + 1], kb[cur][j][0], kb[cur][j][1]);
+      mma_bf16_m16n8k16(s[j][1], qa[cur][2 * j], qa[cur][2 * j], qa[cur][2 * j + 1],
+                        qa[cur][2 * j + 1], kb[cur][j][2], kb[cur][j][3]);
+    }
+  }
+  // the first V fragments travel under the softmax
+  const uint32_t v_tensor = k_tensor + TileTraits::kStageTensorBytes;
+  uint32_t va[2][4];
+  ldmatrix_x4_trans(va[0], ln.at(v_tensor, dh * 2, 0));
+  ldmatrix_x4_trans(va[1], ln.at(v_tensor, dh * 2, 1));
+
+  float sc[4];
+  sc[0] = (s[0][0][0] + s[1][0][0]) * scale_log2;  // key key0
+  sc[1] = (s[0][0][1] + s[1][0][1]) * scale_log2;  // key key0 + 1
+  sc[2] = (s[0][1][0] + s[1][1][0]) * scale_log2;  // key key0 + 8
+  sc[3] = (s[0][1][1] + s[1][1][1]) * scale_log2;  // key key0 + 9
+  const uint32_t mine = mask16 >> ln.key0;  // bits 0, 1, 8, 9: this lane's keys
+  if ((mine & 0x001u) == 0u) sc[0] = -INFINITY;
+  if ((mine & 0x002u) == 0u) sc[1] = -INFINITY;
+  if ((mine & 0x100u) == 0u) sc[2] = -INFINITY;
+  if ((mine & 0x200u) == 0u) sc[3] = -INFINITY;
+  float tile_max = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
+  tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 1));
+  tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 2));
+  const float other_max = __shfl_xor_sync(0xffffffffu, tile_max, 4);
+  const float new_m0 = fmaxf(st.m[0], ln.own == 0 ? tile_max : other_max);
+  const float new_m1 = fmaxf(st.m[1], ln.own == 0 ? other_max : tile_max);
+  if (new_m0 > st.m[0] || new_m1 > st.m[1]) {
+    const float corr0 = ex2_approx(st.m[0] - new_m0);
+    const float corr1 = ex2_approx(st.m[1] - new_m1);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      st.acc[j][0] *= corr0;
+      st.acc[j][1] *= corr1;
+      st.acc[j][2] *= corr0;
+      st.acc[j][3] *= corr1;
+    }
+    st.l_lane *= (ln.own == 0 ? corr0 : corr1);
+    st.m[0] = new_m0;
+    st.m[1] = new_m1;
+  }
+  const float m_own = ln.own == 0 ? st.m[0] : st.m[1];
+  float pr[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) pr[i] = ex2_approx(sc[i] - m_own);
+  st.l_lane += (pr[0] + pr[1]) + (pr[2] + pr[3]);
+  const uint32_t pb0 = pack_bf16x2(pr[0], pr[1]);
+  const uint32_t pb1 = pack_bf16x2(pr[2], pr[3]);
+
+  // A dead key's V row may hold anything (0 * NaN would poison the sums): its
+  // elements are cleared where the half is not complete.
+  const bool partial = mask16 != 0xffffu;
+  const uint32_t keep0 = ((mine & 0x001u) ? 0x0000ffffu : 0u) | ((mine & 0x002u) ? 0xffff0000u : 0u);
+  const uint32_t keep1 = ((mine & 0x100u) ? 0x0000ffffu : 0u) | ((mine & 0x200u) ? 0xffff0000u : 0u);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {  // dims dh * 128 + 16 j ...
+    const int cur = j & 1;
+    uint32_t a0 = va[cur][0], a1 = va[cur][1], a2 = va[cur][2], a3 = va[cur][3];
+    if (j + 2 < 8) ldmatrix_x4_trans(va[cur], ln.at(v_tensor, dh * 2 + ((j + 2) >> 2), (j + 2) & 3));
+    if (partial) {
+      a0 &= keep0;
+      a1 &= keep0;
+      a2 &= keep1;
+      a3 &= keep1;
+    }
+    mma_bf16_m16n8k16(st.acc[j], a0, a1, a2, a3, pb0, pb1);
+  }
+}
+
+template <int kMode, bool kMma>
 __global__ __launch_bounds__(kTileThreads, 2) void decode_pagetile_kernel(
     TileParams p, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v) {
@@ -148,9 +345,13 @@ __global__ __launch_bounds__(kTileThreads, 2) void decode_pagetile_kernel(
   constexpr int ST = kTileStage;
   constexpr bool kFused = kMode != kAttentionOnly;
   constexpr bool kIeee = kMode == kFusedIeee;
-  extern __shared__ __align__(128) uint8_t smem[];
-  __nv_bfloat16 *s_q = reinterpret_cast<__nv_bfloat16 *>(smem + T::kRingBytes);  // [2][256]
-  __nv_bfloat16 *s_new = s_q + 2 * D;  // [2][256]: the new K row, the new V row
+  constexpr int kQStride = kMma ? kQStrideMma : D;  // elements between the two q rows
+  // partial states the CTA's warps leave for the merge: one per warp, or one per
+  // (group of four warps, key half)
+  constexpr int kStates = kMma ? 4 : T::kConsumerWarps;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  __nv_bfloat16 *s_q = reinterpret_cast<__nv_bfloat16 *>(smem + T::kRingBytes);  // [2][kQStride]
+  __nv_bfloat16 *s_new = s_q + 2 * kQStride;  // [2][256]: the new K row, the new V row
   volatile int *s_flag = reinterpret_cast<volatile int *>(s_new + 2 * D);  // abort, last
 
   const int warp = int(threadIdx.x) >> 5;
@@ -188,6 +389,10 @@ __global__ __launch_bounds__(kTileThreads, 2) void decode_pagetile_kernel(
   // A short page-table row (a sliding-window ring) is fetched whole by the
   // producer warp before the length is known, four entries per lane: one
   // dependent round trip less before the first tile can be asked for.
+  if (warp == T::kConsumerWarps && lane == 0) {
+    prefetch_tensor_map(&map_k);
+    prefetch_tensor_map(&map_v);
+  }
   const int mpps = cfg.max_pages_per_seq;
   const bool small_table = mpps <= 4 * kWarpSize;
   int table_regs[4] = {-1, -1, -1, -1};
@@ -300,11 +505,17 @@ __global__ __launch_bounds__(kTileThreads, 2) void decode_pagetile_kernel(
       }
       __syncwarp();
       if (valid) {
-        const uint32_t dst = ring.k_stage(stage) + uint32_t(lane * tb) * T::kRowBytes;
         const int page = p.layer * cfg.num_pages + phys;
-        tma_load_tile(dst, &map_k, h, pos0 % ps, page, ring.full_bar(stage), policy);
-        tma_load_tile(dst + T::kStageTensorBytes, &map_v, h, pos0 % ps, page,
-                      ring.full_bar(stage), policy);
+        const uint32_t dst = ring.k_stage(stage) + uint32_t(lane * tb) * T::kRowBytes;
+        if constexpr (kMma) {
+          tma_load_tile_blocked(dst, &map_k, h, pos0 % ps, page, ring.full_bar(stage), policy);
+          tma_load_tile_blocked(dst + T::kStageTensorBytes, &map_v, h, pos0 % ps, page,
+                                ring.full_bar(stage), policy);
+        } else {
+          tma_load_tile(dst, &map_k, h, pos0 % ps, page, ring.full_bar(stage), policy);
+          tma_load_tile(dst + T::kStageTensorBytes, &map_v, h, pos0 % ps, page,
+                        ring.full_bar(stage), policy);
+        }
       }
       issued = c + 1;
     }
@@ -334,9 +545,9 @@ __global__ __launch_bounds__(kTileThreads, 2) void decode_pagetile_kernel(
           prep_weighted_rope_values<D, D, kIeee>(y, x, p.q_norm_weight,
                                                  p.cos + int64_t(new_pos) * (D / 2),
                                                  p.sin + int64_t(new_pos) * (D / 2), lane);
-          store_head<D>(s_q + warp * D, y, lane);
+          store_head<D>(s_q + warp * kQStride, y, lane);
         } else {  // no append for this sequence: q is what the caller left there
-          reinterpret_cast<uint4 *>(s_q + warp * D)[lane] = __ldg(
+          reinterpret_cast<uint4 *>(s_q + warp * kQStride)[lane] = __ldg(
               reinterpret_cast<const uint4 *>(
                   p.q_prepared + (int64_t(b) * p.q_heads + h * 2 + warp) * D) +
               lane);
@@ -360,7 +571,7 @@ __global__ __launch_bounds__(kTileThreads, 2) void decode_pagetile_kernel(
   } else {
     pdl_wait_for_predecessor();  // q comes from the append
     if (warp < 2) {
-      reinterpret_cast<uint4 *>(s_q + warp * D)[lane] = __ldg(
+      reinterpret_cast<uint4 *>(s_q + warp * kQStride)[lane] = __ldg(
           reinterpret_cast<const uint4 *>(
               p.q + (int64_t(b) * p.q_heads + h * 2 + warp) * D) +
           lane);
@@ -368,68 +579,149 @@ __global__ __launch_bounds__(kTileThreads, 2) void decode_pagetile_kernel(
   }
   named_barrier_sync(1, kTileConsumerThreads);
 
-  WarpState<T> st;
-  {
-    uint4 raw[2];
-    raw[0] = reinterpret_cast<const uint4 *>(s_q)[lane];
-    raw[1] = reinterpret_cast<const uint4 *>(s_q + D)[lane];
-    st.set_q(raw, p.scale_log2);
-  }
-  st.reset();
   bool ok = true;
-  // The stage that holds the new key: the tile brought whatever the cache had
-  // there; the warp that owns the token's slot replaces the row by the prepared
-  // one (no other warp reads that slot). The slot's mask bit is set exactly when
-  // its page is mapped.
-  auto patch_new_row = [&](int c, int stage) {
-    if constexpr (kFused) {
-      if (owns_new && c0 + c == new_pos / ST) {
-        const int slot = new_pos % ST;
-        if (warp == slot / kTokPerWarp && ((ring.masks()[stage] >> slot) & 1ull) != 0ull) {
-          uint8_t *k_row = smem + stage * T::kStageBytes + slot * T::kRowBytes;
-          const uint4 *rows = reinterpret_cast<const uint4 *>(s_new);
-          reinterpret_cast<uint4 *>(k_row)[lane] = rows[lane];
-          reinterpret_cast<uint4 *>(k_row + T::kStageTensorBytes)[lane] = rows[32 + lane];
-          fence_proxy_async_shared();  // the next fill of the stage is a bulk copy
-          __syncwarp();
+  float *x_acc = reinterpret_cast<float *>(smem);  // [kStates][2][256], in the idle ring
+  float *x_m = x_acc + kStates * 2 * D;            // [kStates][2]
+  float *x_l = x_m + kStates * 2;                  // [kStates][2]
+  if constexpr (kMma) {
+    // Chunks alternate between the two groups of four warps; within a group,
+    // warp (kh, dh) takes key half kh and output-dim half dh of the stage. Every
+    // warp waits for and releases every stage, its group's or not: a warp that
+    // skipped the other group's stages could meet a barrier two phases on, and a
+    // parity wait cannot tell that from the phase it is waiting for.
+    const int qd = warp >> 2;
+    const int kh = (warp >> 1) & 1;
+    const int dh = warp & 1;
+    const MmaLane ln(lane, kh, p.tile_tokens, smem_u32(s_q));
+    MmaState st;
+    st.reset();
+    if ((ring.base & 1023u) != 0u) {  // the swizzle is a function of the address
+      ok = false;
+    }
+    for (int c = 0; ok && c < nchunks; ++c) {
+      const int stage = c % kStages;
+      if (!mbar_wait_bounded(ring.full_bar(stage), uint32_t(c / kStages) & 1u)) {
+        ok = false;
+        break;
+      }
+      if ((c & 1) != qd) {  // the other group's stage
+        if (lane == 0) mbar_arrive(ring.empty_bar(stage));
+        continue;
+      }
+      const uint32_t mask = uint32_t(ring.masks()[stage]);
+      if constexpr (kFused) {
+        // The stage that holds the new key: the tile brought whatever the cache
+        // had there. Both warps that read the key's half replace the row by the
+        // prepared one before they read it -- the same bytes twice, so neither
+        // has to wait for the other. The slot's mask bit is set exactly when its
+        // page is mapped.
+        if (owns_new && c0 + c == new_pos / ST) {
+          const int slot = new_pos % ST;
+          if (kh == slot / 16 && ((mask >> slot) & 1u) != 0u) {
+            const uint4 *rows = reinterpret_cast<const uint4 *>(s_new);
+            const int tb = p.tile_tokens;  // chunk lane of the row: block lane / 8, swizzled
+            uint8_t *k_row = smem + stage * T::kStageBytes + (slot / tb) * tb * T::kRowBytes +
+                             (lane >> 3) * tb * 128 + (slot % tb) * 128 +
+                             (((lane & 7) ^ (slot & 7)) << 4);
+            *reinterpret_cast<uint4 *>(k_row) = rows[lane];
+            *reinterpret_cast<uint4 *>(k_row + T::kStageTensorBytes) = rows[32 + lane];
+            fence_proxy_async_shared();  // the next fill of the stage is a bulk copy
+            __syncwarp();
+          }
         }
       }
+      const uint32_t mask16 = (mask >> (kh * 16)) & 0xffffu;
+      if (mask16 != 0u) {
+        consume_half_mma(st, ln, ring.k_stage(stage), mask16, dh, p.scale_log2);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(ring.empty_bar(stage));
     }
-  };
-  for (int c = 0; c < nchunks; ++c) {
-    const int stage = c % kStages;
-    if (!mbar_wait_bounded(ring.full_bar(stage), uint32_t(c / kStages) & 1u)) {
-      ok = false;
-      break;
+    if (!ok && lane == 0) {
+      set_status(p.status, B200KV_STATUS_WAIT_TIMEOUT);
+      s_flag[0] = 1;
     }
-    patch_new_row(c, stage);
-    consume_stage<T>(st, ring, stage, 0, warp, lane);
-    __syncwarp();
-    if (lane == 0) mbar_arrive(ring.empty_bar(stage));
-  }
-  if (!ok && lane == 0) {
-    set_status(p.status, B200KV_STATUS_WAIT_TIMEOUT);
-    s_flag[0] = 1;
-  }
-
-  // Merge of the eight warps through the ring (idle once every warp is past its
-  // last stage): thread t ends with dim t of both rows.
-  float l[2];
-  st.denominators(l, lane);
-  float *x_acc = reinterpret_cast<float *>(smem);         // [8][2][256]
-  float *x_m = x_acc + T::kConsumerWarps * 2 * D;          // [8][2]
-  float *x_l = x_m + T::kConsumerWarps * 2;                // [8][2]
-  named_barrier_sync(1, kTileConsumerThreads);
+    // The warp's state into the exchange area: the two dim halves of a (group,
+    // key half) make one partial state.
+    float l = st.l_lane + __shfl_xor_sync(0xffffffffu, st.l_lane, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    named_barrier_sync(1, kTileConsumerThreads);  // every warp is past its last stage
+    const int state = qd * 2 + kh;
+    const int g8 = lane >> 2;
 #pragma unroll
-  for (int g = 0; g < 2; ++g) {
-    float4 *dst = reinterpret_cast<float4 *>(x_acc + (warp * 2 + g) * D) + lane * 2;
-    dst[0] = make_float4(st.acc[g][0], st.acc[g][1], st.acc[g][2], st.acc[g][3]);
-    dst[1] = make_float4(st.acc[g][4], st.acc[g][5], st.acc[g][6], st.acc[g][7]);
-    if (lane == 0) {
-      x_m[warp * 2 + g] = st.m[g];
-      x_l[warp * 2 + g] = l[g];
+    for (int j = 0; j < 8; ++j) {
+      if ((j & 3) == (lane & 3)) {  // the four lanes of a row hold copies: one tile each
+        const int dim = dh * 128 + 16 * j + g8;
+        x_acc[(state * 2 + 0) * D + dim] = st.acc[j][0];
+        x_acc[(state * 2 + 1) * D + dim] = st.acc[j][1];
+        x_acc[(state * 2 + 0) * D + dim + 8] = st.acc[j][2];
+        x_acc[(state * 2 + 1) * D + dim + 8] = st.acc[j][3];
+      }
+    }
+    if (dh == 0 && (lane == 0 || lane == 4)) {  // lane 4 g scores query g
+      x_m[state * 2 + g8] = g8 == 0 ? st.m[0] : st.m[1];
+      x_l[state * 2 + g8] = l;
+    }
+  } else {
+    WarpState<T> st;
+    {
+      uint4 raw[2];
+      raw[0] = reinterpret_cast<const uint4 *>(s_q)[lane];
+      raw[1] = reinterpret_cast<const uint4 *>(s_q + D)[lane];
+      st.set_q(raw, p.scale_log2);
+    }
+    st.reset();
+    // The stage that holds the new key: the tile brought whatever the cache had
+    // there; the warp that owns the token's slot replaces the row by the prepared
+    // one (no other warp reads that slot). The slot's mask bit is set exactly when
+    // its page is mapped.
+    auto patch_new_row = [&](int c, int stage) {
+      if constexpr (kFused) {
+        if (owns_new && c0 + c == new_pos / ST) {
+          const int slot = new_pos % ST;
+          if (warp == slot / kTokPerWarp && ((ring.masks()[stage] >> slot) & 1ull) != 0ull) {
+            uint8_t *k_row = smem + stage * T::kStageBytes + slot * T::kRowBytes;
+            const uint4 *rows = reinterpret_cast<const uint4 *>(s_new);
+            reinterpret_cast<uint4 *>(k_row)[lane] = rows[lane];
+            reinterpret_cast<uint4 *>(k_row + T::kStageTensorBytes)[lane] = rows[32 + lane];
+            fence_proxy_async_shared();  // the next fill of the stage is a bulk copy
+            __syncwarp();
+          }
+        }
+      }
+    };
+    for (int c = 0; c < nchunks; ++c) {
+      const int stage = c % kStages;
+      if (!mbar_wait_bounded(ring.full_bar(stage), uint32_t(c / kStages) & 1u)) {
+        ok = false;
+        break;
+      }
+      patch_new_row(c, stage);
+      consume_stage<T>(st, ring, stage, 0, warp, lane);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(ring.empty_bar(stage));
+    }
+    if (!ok && lane == 0) {
+      set_status(p.status, B200KV_STATUS_WAIT_TIMEOUT);
+      s_flag[0] = 1;
+    }
+    // The warps' states into the ring (idle once every warp is past its last
+    // stage).
+    float l[2];
+    st.denominators(l, lane);
+    named_barrier_sync(1, kTileConsumerThreads);
+#pragma unroll
+    for (int g = 0; g < 2; ++g) {
+      float4 *dst = reinterpret_cast<float4 *>(x_acc + (warp * 2 + g) * D) + lane * 2;
+      dst[0] = make_float4(st.acc[g][0], st.acc[g][1], st.acc[g][2], st.acc[g][3]);
+      dst[1] = make_float4(st.acc[g][4], st.acc[g][5], st.acc[g][6], st.acc[g][7]);
+      if (lane == 0) {
+        x_m[warp * 2 + g] = st.m[g];
+        x_l[warp * 2 + g] = l[g];
+      }
     }
   }
+  // Merge of the states: thread t ends with dim t of both rows.
   named_barrier_sync(1, kTileConsumerThreads);
   const int t = int(threadIdx.x);  // 0..255: the dim this thread finishes
   float M[2], L[2], A[2];
@@ -437,11 +729,11 @@ __global__ __launch_bounds__(kTileThreads, 2) void decode_pagetile_kernel(
   for (int g = 0; g < 2; ++g) {
     M[g] = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < T::kConsumerWarps; ++w) M[g] = fmaxf(M[g], x_m[w * 2 + g]);
+    for (int w = 0; w < kStates; ++w) M[g] = fmaxf(M[g], x_m[w * 2 + g]);
     L[g] = 0.0f;
     A[g] = 0.0f;
 #pragma unroll
-    for (int w = 0; w < T::kConsumerWarps; ++w) {
+    for (int w = 0; w < kStates; ++w) {
       const float mw = x_m[w * 2 + g];
       const float wt = mw == -INFINITY ? 0.0f : ex2_approx(mw - M[g]);
       L[g] = fmaf(x_l[w * 2 + g], wt, L[g]);
@@ -457,7 +749,7 @@ __global__ __launch_bounds__(kTileThreads, 2) void decode_pagetile_kernel(
     if (warp < 2 && r == 0 && new_pos >= 0) {
       reinterpret_cast<uint4 *>(p.q_prepared +
                                 (int64_t(b) * p.q_heads + h * 2 + warp) * D)[lane] =
-          reinterpret_cast<const uint4 *>(s_q + warp * D)[lane];
+          reinterpret_cast<const uint4 *>(s_q + warp * kQStride)[lane];
     } else if ((warp == 2 || warp == 3) && preps_kv && new_page >= 0) {
       const int64_t off =
           cache_offset(cfg, p.layer, new_page,
@@ -692,12 +984,29 @@ EncodeTiledFn encode_tiled_fn() {
 
 // The cache as [dim][head][page offset][layer * pages + page] bf16 with tiles of
 // (256 dims, one head, tile_tokens offsets, one page): 512-byte rows, dense in
-// shared memory.
+// shared memory. Swizzled (the tensor-core variant): boxes of 64 dims, 128-byte
+// rows with the 128-byte swizzle.
 bool make_cache_map(CUtensorMap *map, const __nv_bfloat16 *base,
-                    const Gemma4KvCacheConfig &c, int tile_tokens) {
+                    const Gemma4KvCacheConfig &c, int tile_tokens, bool swizzled) {
   EncodeTiledFn encode = encode_tiled_fn();
   if (encode == nullptr) return false;
   const cuuint64_t row = cuuint64_t(c.head_dim) * 2;
+  if (swizzled) {
+    // [64 dims][page offset][block of 64 dims][head][layer * pages + page]: a box of
+    // (64, tile_tokens, 4, 1, 1) is the tile as four blocks of 128-byte rows.
+    const cuuint64_t dims[5] = {64, cuuint64_t(c.page_size), cuuint64_t(c.head_dim) / 64,
+                                cuuint64_t(c.num_heads),
+                                cuuint64_t(c.num_layers) * cuuint64_t(c.num_pages)};
+    const cuuint64_t strides[4] = {row * c.num_heads, 128, row,
+                                   row * c.num_heads * c.page_size};
+    const cuuint32_t box[5] = {64, cuuint32_t(tile_tokens), cuuint32_t(c.head_dim) / 64, 1, 1};
+    const cuuint32_t elem_strides[5] = {1, 1, 1, 1, 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5,
+                  const_cast<__nv_bfloat16 *>(base), dims, strides, box, elem_strides,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  }
   const cuuint64_t dims[4] = {cuuint64_t(c.head_dim), cuuint64_t(c.num_heads),
                               cuuint64_t(c.page_size),
                               cuuint64_t(c.num_layers) * cuuint64_t(c.num_pages)};
@@ -738,16 +1047,32 @@ int pagetile_ranges_override() {
   return n;
 }
 
-template <int kMode>
-cudaError_t launch_pagetile(const TileParams &p, const CUtensorMap &map_k,
-                            const CUtensorMap &map_v, cudaStream_t stream) {
-  cudaError_t st = cudaFuncSetAttribute(decode_pagetile_kernel<kMode>,
+// B200KV_PAGETILE_MMA=0: tuning aid, the scalar arithmetic for every page size.
+bool pagetile_mma_allowed() {
+  static const bool allowed = [] {
+    const char *v = std::getenv("B200KV_PAGETILE_MMA");
+    return v == nullptr || std::strcmp(v, "0") != 0;
+  }();
+  return allowed;
+}
+
+template <int kMode, bool kMma>
+cudaError_t launch_pagetile_variant(const TileParams &p, const CUtensorMap &map_k,
+                                    const CUtensorMap &map_v, cudaStream_t stream) {
+  cudaError_t st = cudaFuncSetAttribute(decode_pagetile_kernel<kMode, kMma>,
                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         kTileSmemBytes);
   if (st != cudaSuccess) return st;
   const int64_t ctas = int64_t(p.batch_count) * p.ranges * p.cfg.num_heads;
-  return launch_pdl(decode_pagetile_kernel<kMode>, dim3(unsigned(ctas)),
+  return launch_pdl(decode_pagetile_kernel<kMode, kMma>, dim3(unsigned(ctas)),
                     dim3(kTileThreads), kTileSmemBytes, stream, p, map_k, map_v);
+}
+
+template <int kMode>
+cudaError_t launch_pagetile(const TileParams &p, bool mma, const CUtensorMap &map_k,
+                            const CUtensorMap &map_v, cudaStream_t stream) {
+  return mma ? launch_pagetile_variant<kMode, true>(p, map_k, map_v, stream)
+             : launch_pagetile_variant<kMode, false>(p, map_k, map_v, stream);
 }
 
 }  // namespace
@@ -850,12 +1175,15 @@ cudaError_t decode_layer_step_pagetile_bf16(const AppendArgs *ap, const DecodeAr
     return cudaErrorInvalidValue;
   }
   p.ranges = int32_t(ranges);
+  // Tiles of at least 8 tokens go through the tensor cores (swizzled rows);
+  // smaller pages keep the scalar arithmetic.
+  const bool mma = p.tile_tokens >= kMmaMinTileTokens && pagetile_mma_allowed();
   CUtensorMap map_k, map_v;
-  if (!make_cache_map(&map_k, a.cache_k, c, p.tile_tokens) ||
-      !make_cache_map(&map_v, a.cache_v, c, p.tile_tokens)) {
+  if (!make_cache_map(&map_k, a.cache_k, c, p.tile_tokens, mma) ||
+      !make_cache_map(&map_v, a.cache_v, c, p.tile_tokens, mma)) {
     return cudaErrorInvalidValue;
   }
-  if (ap == nullptr) return launch_pagetile<kAttentionOnly>(p, map_k, map_v, stream);
+  if (ap == nullptr) return launch_pagetile<kAttentionOnly>(p, mma, map_k, map_v, stream);
   p.raw_q = ap->q;
   p.raw_k = ap->k;
   p.raw_v = ap->v;
@@ -868,8 +1196,8 @@ cudaError_t decode_layer_step_pagetile_bf16(const AppendArgs *ap, const DecodeAr
   p.raw_from_predecessor = ap->raw_from_predecessor ? 1 : 0;
   p.cache_settled = ap->cache_settled ? 1 : 0;
   return ap->norm_mode == B200KV_NORM_IEEE
-             ? launch_pagetile<kFusedIeee>(p, map_k, map_v, stream)
-             : launch_pagetile<kFusedApprox>(p, map_k, map_v, stream);
+             ? launch_pagetile<kFusedIeee>(p, mma, map_k, map_v, stream)
+             : launch_pagetile<kFusedApprox>(p, mma, map_k, map_v, stream);
 }
 
 }  // namespace b200kv

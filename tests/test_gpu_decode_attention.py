@@ -75,6 +75,7 @@ CASES = {
     "mixed_batch_ring": dict(seq_lens=[5000, 90, 1024, 1023, 1025], window=1024),
     "page64": dict(seq_lens=[1000, 65], window=0, page_size=64),
     "page4": dict(seq_lens=[77, 31], window=0, page_size=4),
+    "page8": dict(seq_lens=[333, 50], window=0, page_size=8),
     "page1": dict(seq_lens=[40], window=0, page_size=1),
     "outliers": dict(seq_lens=[3000], window=0, outlier_frac=0.01),
     "layer1_of_3": dict(seq_lens=[500, 33], window=0, layers=3, layer=1),
