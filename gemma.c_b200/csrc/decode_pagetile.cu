@@ -129,6 +129,10 @@ struct TileParams {
   // not write this layer's cache (they belong to another layer's step), so no
   // tile has to wait for them.
   int32_t cache_settled;
+  // Non-zero: the next kernel may start as soon as this one runs (the caller has
+  // checked that what the next kernel reads before its own wait is written by
+  // none of the kernels that can then be in flight).
+  int32_t release_early;
   // The all-gather of the output rows over peer memory, finished by this kernel
   // (world == 0: none). The rows of this rank are [batch, q_heads, 256] bf16.
   PeerEpilogue peer;
@@ -436,8 +440,11 @@ __global__ __launch_bounds__(kTileThreads, 2) void decode_pagetile_kernel(
     // next kernel's early reads allow for (it leaves the page of this step's
     // new key, and everything it writes, for after its own wait). A warp of its
     // own passes that on as soon as it is true, however far this CTA's stream is.
+    // (With release_early the caller has made sure that the next kernel's early
+    // reads allow for deeper overlap, and the release comes at once. The order
+    // of completion stays a chain either way: every CTA waits before it exits.)
     if constexpr (kFused) {
-      pdl_wait_for_predecessor();
+      if (p.release_early == 0) pdl_wait_for_predecessor();
       pdl_release_successor();
     }
     return;
@@ -1195,6 +1202,7 @@ cudaError_t decode_layer_step_pagetile_bf16(const AppendArgs *ap, const DecodeAr
   p.q_prepared = ap->q_prepared;
   p.raw_from_predecessor = ap->raw_from_predecessor ? 1 : 0;
   p.cache_settled = ap->cache_settled ? 1 : 0;
+  p.release_early = ap->release_early ? 1 : 0;
   return ap->norm_mode == B200KV_NORM_IEEE
              ? launch_pagetile<kFusedIeee>(p, mma, map_k, map_v, stream)
              : launch_pagetile<kFusedApprox>(p, mma, map_k, map_v, stream);

@@ -956,9 +956,17 @@ int gather_after(const B200KvLayerStepArgs *s, cudaStream_t st) {
 
 // raw_from_predecessor: the raw rows come from the kernel enqueued just before
 // (the attention-layer call's QKV projection), not from an earlier step.
+// Whether layer_step() gives this layer-step to the one-launch kernel.
+bool takes_one_launch_kernel(const B200KvLayerStepArgs *s) {
+  return s->batch_count > 0 && s->split_size == 0 && s->rotary_dim == 256 &&
+         fused_layer_step_enabled() &&
+         b200kv::decode_pagetile_preferred(s->cache_config, s->q_heads, s->batch_count,
+                                           s->ticket != nullptr);
+}
+
 int layer_step(const B200KvLayerStepArgs *s, bool raw_from_predecessor,
                b200kv_stream stream, bool force_tiled = false,
-               bool cache_settled = false) {
+               bool cache_settled = false, bool release_early = false) {
   if (s == nullptr) return cudaErrorInvalidValue;
   using bf = __nv_bfloat16;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -983,6 +991,7 @@ int layer_step(const B200KvLayerStepArgs *s, bool raw_from_predecessor,
   a.norm_mode = s->norm_mode;
   a.raw_from_predecessor = raw_from_predecessor;
   a.cache_settled = cache_settled;
+  a.release_early = release_early;
 
   b200kv::DecodeArgs d;
   d.out = reinterpret_cast<bf *>(s->out);
@@ -1010,11 +1019,7 @@ int layer_step(const B200KvLayerStepArgs *s, bool raw_from_predecessor,
                       s->rotary_dim != 256 || s->ticket == nullptr)) {
     return cudaErrorInvalidValue;
   }
-  if (force_tiled ||
-      (s->batch_count > 0 && s->split_size == 0 && s->rotary_dim == 256 &&
-       fused_layer_step_enabled() &&
-       b200kv::decode_pagetile_preferred(d.cfg, d.q_heads, d.batch_count,
-                                         s->ticket != nullptr))) {
+  if (force_tiled || takes_one_launch_kernel(s)) {
     if (s->event_before_attention != nullptr) {
       B200KV_TRY(cudaEventRecord(
           static_cast<cudaEvent_t>(s->event_before_attention), st));
@@ -1135,21 +1140,41 @@ int b200kv_decode_attention_tiled_bf16(
 int b200kv_decode_step_bf16(const B200KvLayerStepArgs *layers,
                             int32_t layer_count, b200kv_stream stream) {
   if (layers == nullptr || layer_count < 0) return cudaErrorInvalidValue;
-  for (int32_t i = 0; i < layer_count; ++i) {
-    // From the second layer on, what can still be in flight when a layer's
-    // kernel starts is the step of the layer before it (the kernels here let at
-    // most their direct predecessor's launches overlap them). If that is another
-    // cache layer, nothing in flight writes this layer's cache rows.
-    bool settled = false;
-    if (i > 0) {
-      const B200KvLayerStepArgs &p = layers[i - 1];
-      const B200KvLayerStepArgs &c = layers[i];
+  // How many of the entries right before entry j work on caches other than
+  // entry j's (K and V both), counting back to the first that shares one.
+  auto distinct_before = [&](int32_t j) {
+    const B200KvLayerStepArgs &c = layers[j];
+    int32_t n = 0;
+    for (int32_t i = j - 1; i >= 0; --i, ++n) {
+      const B200KvLayerStepArgs &p = layers[i];
       const bool same_k = p.cache_k == c.cache_k && p.cache_layer == c.cache_layer;
       const bool same_v = p.cache_v == c.cache_v && p.cache_layer == c.cache_layer;
-      settled = !same_k && !same_v && p.batch_count > 0;
+      if (same_k || same_v || p.batch_count <= 0) break;
     }
-    const int st = layer_step(layers + i, false, stream, false, settled);
+    return n;
+  };
+  // An entry's kernel normally lets the next entry's kernel start once its own
+  // predecessor is complete, so that a starting kernel overlaps one unfinished
+  // launch. A run of one-launch layer-steps on different cache layers can do
+  // better: entry i releases entry i + 1 at once when every launch that can then
+  // still be in flight -- the entries of the run so far -- works on another
+  // cache than entry i + 1. The first entry never does (what precedes it is not
+  // known here), and a run is cut after kMaxEarlyRun entries, which bounds the
+  // launches in flight whatever their size.
+  constexpr int32_t kMaxEarlyRun = 6;
+  int32_t run = 0;  // early releases in a row up to the entry before this one
+  for (int32_t i = 0; i < layer_count; ++i) {
+    const int32_t in_flight = 1 + run;  // unfinished launches entry i can meet
+    const bool settled = i > 0 && distinct_before(i) >= in_flight;
+    bool early = false;
+    if (i >= 1 && i + 1 < layer_count && run < kMaxEarlyRun &&
+        layers[i].peer_gather == nullptr && layers[i + 1].peer_gather == nullptr &&
+        takes_one_launch_kernel(layers + i) && takes_one_launch_kernel(layers + i + 1)) {
+      early = distinct_before(i + 1) >= in_flight + 1;
+    }
+    const int st = layer_step(layers + i, false, stream, false, settled, early);
     if (st != cudaSuccess) return st;
+    run = early ? run + 1 : 0;
   }
   return cudaSuccess;
 }

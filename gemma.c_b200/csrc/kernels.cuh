@@ -86,6 +86,13 @@ struct AppendArgs {
   // layer's cache, so the kernel need not hold back the page of the newest key.
   // Only the one-launch layer-step (decode_pagetile.cu) makes use of it.
   bool cache_settled = false;
+  // Let the launch behind this one start as soon as this one runs, instead of
+  // when this one's own predecessor is complete. The caller vouches for the
+  // launch behind: it is a one-launch layer-step with cache_settled set, and
+  // cache_settled holds for it against every launch that can then still be in
+  // flight when it starts (see b200kv_decode_step_bf16). Only the one-launch
+  // layer-step makes use of it.
+  bool release_early = false;
 };
 
 cudaError_t decode_append_bf16(const AppendArgs &args, cudaStream_t stream);
