@@ -445,6 +445,19 @@ class RankWorkload:
         self.graph_first = self.graph_next = first_step
 
         def launch_all(stream):
+            if self.L == 1 and k > 1 and not self.spec.fp8:
+                # the k steps of the one layer as ONE b200kv_decode_step_bf16 call: the library then knows that
+                # they are consecutive steps of one cache layer and keeps their launches overlapped
+                steps = (type(self.layers[0]) * k)()
+                for j in range(k):
+                    steps[j] = self.layers[0]
+                    steps[j].token_position = self.step_state[0, j].data_ptr()
+                    steps[j].seq_lengths = self.step_state[1, j].data_ptr()
+                    steps[j].event_before_attention = None
+                    steps[j].event_after_attention = None
+                self.graph_entries = steps
+                self.kv.decode_step(steps, k, stream=stream)
+                return
             for j in range(k):
                 self._launch_step(self.step_state[0, j].data_ptr(), self.step_state[1, j].data_ptr(), None, stream)
 
@@ -1083,6 +1096,21 @@ WORKLOADS = {
 }
 
 
+def replays_graph(args, world: int) -> bool:
+    """Whether the steps are replayed from a CUDA graph: the batch-1 workloads, and the KV-head-sharded long
+    context with the one-launch kernel (on several GPUs with the exchange inside the kernel, or one rank's share
+    emulated on one GPU) -- sixteen consecutive steps of the one layer per graph, handed to the library as one
+    b200kv_decode_step_bf16 call, so that the ranks' launches do not drift against each other under the hosts'
+    jitter and the library can keep the steps' launches overlapped."""
+    if args.graph != "auto":
+        return args.graph == "on"
+    if args.workload in ("cfg1", "cfg2"):
+        return True
+    sharded = world > 1 or args.emulate_world > 1
+    return (args.workload == "cfg4" and sharded and args.shard == "heads" and not args.no_tickets
+            and (args.gather == "peer" or world == 1))
+
+
 def plan_workload(args, world: int, rank: int):
     """Returns (spec, all context lengths, this rank's context lengths, parallelism text, scaling)."""
     name = args.workload
@@ -1133,9 +1161,7 @@ def workload_config(args, world, where, parallelism=None, layers=None):
         "where": where,
         "launch": ("one CUDA graph replay per step" + (" (sixteen one-kernel steps per replay)"
                                                          if args.workload in ("cfg1", "cfg4") else "")
-                   if (args.graph == "on" or (args.graph == "auto" and (args.workload in ("cfg1", "cfg2") or (
-                       args.workload == "cfg4" and world > 1 and args.gather == "peer" and args.shard == "heads"
-                       and not args.no_tickets))))
+                   if replays_graph(args, world)
                    else "stream launches (programmatic dependent launch between kernels)"),
     }
     if args.workload == "cfg3":
@@ -1610,12 +1636,7 @@ def measure_workload(args, kv, torch, dist, world, rank, sampler=None, verify=Tr
     if args.emulate_world > 1 and world == 1 and args.workload in ("cfg3", "cfg5"):
         ctx = ctx_all[shard_sequences(ctx_all, args.emulate_world)[args.emulate_rank]]
     e2e_warm = 3
-    use_graph = args.graph == "on" or (args.graph == "auto" and args.workload in ("cfg1", "cfg2"))
-    # the KV-head-sharded long context with the exchange inside the step's kernel: replayed from a graph as well,
-    # so that the ranks' launches do not drift against each other under the hosts' jitter
-    if args.graph == "auto" and args.workload == "cfg4" and world > 1 and args.gather == "peer" \
-            and not spec.key_shard and not args.no_tickets:
-        use_graph = True
+    use_graph = replays_graph(args, world)
     probe_steps = 11                        # steps after the timed regions that carry the per-kernel events
     # a one-layer step is a single kernel: sixteen steps per replayed graph (see RankWorkload.enable_graph)
     steps_per_graph = 16 if (use_graph and spec.n_local + spec.n_global == 1) else 1

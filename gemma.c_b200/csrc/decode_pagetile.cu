@@ -125,10 +125,11 @@ struct TileParams {
   const int32_t *token_position;
   __nv_bfloat16 *q_prepared;
   int32_t raw_from_predecessor;
-  // Non-zero: the kernels that may still be in flight when this one starts do
-  // not write this layer's cache (they belong to another layer's step), so no
-  // tile has to wait for them.
-  int32_t cache_settled;
+  // How many of the kernels that may still be in flight when this one starts
+  // are decode steps of this cache layer (each appends the position before the
+  // next one's): the tiles of that many positions before the new one wait for
+  // the preceding kernel. 0: none writes this layer's cache, no tile waits.
+  int32_t steps_in_flight;
   // Non-zero: the next kernel may start as soon as this one runs (the caller has
   // checked that what the next kernel reads before its own wait is written by
   // none of the kernels that can then be in flight).
@@ -456,8 +457,10 @@ __global__ __launch_bounds__(kTileThreads, 2) void decode_pagetile_kernel(
     const int tiles = ST / tb;
     const int ps = cfg.page_size;
     // first position of the first page the preceding kernels may have written
-    const int newest = max(len - (kFused ? 2 : 1), 0);
-    const int fresh = (kFused && p.cache_settled) ? len : (newest / ps) * ps;
+    // (fused: the steps in flight wrote the positions len - 2 down to
+    // len - 1 - steps_in_flight; attention only: the append before wrote len - 1)
+    const int newest = max(len - 1 - (kFused ? p.steps_in_flight : 0), 0);
+    const int fresh = (kFused && p.steps_in_flight == 0) ? len : (newest / ps) * ps;
     bool ok = true;
     bool waited = false;
     int cached_lp = -1, cached_phys = -1;
@@ -1167,7 +1170,11 @@ cudaError_t decode_layer_step_pagetile_bf16(const AppendArgs *ap, const DecodeAr
   // ... and at least two chunks per CTA where a sequence is that long: a CTA's
   // fixed cost (prologue, merge of its warps, its partial) is that of a chunk or
   // two, and every further partial lengthens the last CTA's merge.
-  int64_t ranges = std::max<int64_t>(1, (2 * int64_t(sm_count)) / pairs);
+  // (a launch of a run of overlapping launches: one CTA per SM, so that the next
+  // launch of the run streams beside this one instead of waiting for its CTAs
+  // to leave -- a CTA stays until the launch before its own is complete)
+  const int64_t grid_target = (ap != nullptr && ap->chained ? 1 : 2) * int64_t(sm_count);
+  int64_t ranges = std::max<int64_t>(1, grid_target / pairs);
   ranges = std::min<int64_t>({ranges, int64_t(kMaxRanges), std::max<int64_t>(1, max_chunks / 2),
                               std::max<int64_t>(1, a.num_splits)});
   // up to 32 partials per pair are merged in one round of loads; a few more
@@ -1201,7 +1208,7 @@ cudaError_t decode_layer_step_pagetile_bf16(const AppendArgs *ap, const DecodeAr
   p.token_position = ap->token_position;
   p.q_prepared = ap->q_prepared;
   p.raw_from_predecessor = ap->raw_from_predecessor ? 1 : 0;
-  p.cache_settled = ap->cache_settled ? 1 : 0;
+  p.steps_in_flight = std::max(0, ap->steps_in_flight);
   p.release_early = ap->release_early ? 1 : 0;
   return ap->norm_mode == B200KV_NORM_IEEE
              ? launch_pagetile<kFusedIeee>(p, mma, map_k, map_v, stream)

@@ -966,7 +966,8 @@ bool takes_one_launch_kernel(const B200KvLayerStepArgs *s) {
 
 int layer_step(const B200KvLayerStepArgs *s, bool raw_from_predecessor,
                b200kv_stream stream, bool force_tiled = false,
-               bool cache_settled = false, bool release_early = false) {
+               int32_t steps_in_flight = 1, bool release_early = false,
+               bool chained = false) {
   if (s == nullptr) return cudaErrorInvalidValue;
   using bf = __nv_bfloat16;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -990,8 +991,9 @@ int layer_step(const B200KvLayerStepArgs *s, bool raw_from_predecessor,
   a.rotary_dim = s->rotary_dim;
   a.norm_mode = s->norm_mode;
   a.raw_from_predecessor = raw_from_predecessor;
-  a.cache_settled = cache_settled;
+  a.steps_in_flight = steps_in_flight;
   a.release_early = release_early;
+  a.chained = chained;
 
   b200kv::DecodeArgs d;
   d.out = reinterpret_cast<bf *>(s->out);
@@ -1140,39 +1142,39 @@ int b200kv_decode_attention_tiled_bf16(
 int b200kv_decode_step_bf16(const B200KvLayerStepArgs *layers,
                             int32_t layer_count, b200kv_stream stream) {
   if (layers == nullptr || layer_count < 0) return cudaErrorInvalidValue;
-  // How many of the entries right before entry j work on caches other than
-  // entry j's (K and V both), counting back to the first that shares one.
-  auto distinct_before = [&](int32_t j) {
+  auto same_cache = [&](int32_t i, int32_t j) {
+    const B200KvLayerStepArgs &p = layers[i];
     const B200KvLayerStepArgs &c = layers[j];
-    int32_t n = 0;
-    for (int32_t i = j - 1; i >= 0; --i, ++n) {
-      const B200KvLayerStepArgs &p = layers[i];
-      const bool same_k = p.cache_k == c.cache_k && p.cache_layer == c.cache_layer;
-      const bool same_v = p.cache_v == c.cache_v && p.cache_layer == c.cache_layer;
-      if (same_k || same_v || p.batch_count <= 0) break;
-    }
-    return n;
+    return (p.cache_k == c.cache_k || p.cache_v == c.cache_v) && p.cache_layer == c.cache_layer;
   };
   // An entry's kernel normally lets the next entry's kernel start once its own
-  // predecessor is complete, so that a starting kernel overlaps one unfinished
-  // launch. A run of one-launch layer-steps on different cache layers can do
-  // better: entry i releases entry i + 1 at once when every launch that can then
-  // still be in flight -- the entries of the run so far -- works on another
-  // cache than entry i + 1. The first entry never does (what precedes it is not
-  // known here), and a run is cut after kMaxEarlyRun entries, which bounds the
-  // launches in flight whatever their size.
+  // predecessor is complete, so that a starting kernel meets one unfinished
+  // launch. A run of one-launch layer-steps does better: entry i releases entry
+  // i + 1 at once, and entry i + 1 is told how many of the launches it can then
+  // meet -- the entries of the run so far -- are earlier decode steps of its own
+  // cache layer, whose newest rows it must not read before they are complete.
+  // (Entries that name the same cache layer are consecutive decode steps, in
+  // order: each appends the position after its predecessor's.) The first entry
+  // never releases early (what precedes it is not known here) and allows for one
+  // step of its own layer in flight; a run is cut after kMaxEarlyRun entries,
+  // which bounds the launches in flight whatever their size.
   constexpr int32_t kMaxEarlyRun = 6;
   int32_t run = 0;  // early releases in a row up to the entry before this one
   for (int32_t i = 0; i < layer_count; ++i) {
     const int32_t in_flight = 1 + run;  // unfinished launches entry i can meet
-    const bool settled = i > 0 && distinct_before(i) >= in_flight;
-    bool early = false;
-    if (i >= 1 && i + 1 < layer_count && run < kMaxEarlyRun &&
-        layers[i].peer_gather == nullptr && layers[i + 1].peer_gather == nullptr &&
-        takes_one_launch_kernel(layers + i) && takes_one_launch_kernel(layers + i + 1)) {
-      early = distinct_before(i + 1) >= in_flight + 1;
+    int32_t mine = 0;                   // ... of which decode steps of its cache layer
+    for (int32_t k = 1; k <= in_flight; ++k) {
+      if (i - k < 0 || layers[i - k].batch_count <= 0 || same_cache(i - k, i)) ++mine;
     }
-    const int st = layer_step(layers + i, false, stream, false, settled, early);
+    const bool early = i >= 1 && i + 1 < layer_count && run < kMaxEarlyRun &&
+                       takes_one_launch_kernel(layers + i) &&
+                       takes_one_launch_kernel(layers + i + 1);
+    // part of a run: released early, releasing early, or the run's first entry
+    const bool chained =
+        early || run > 0 ||
+        (i + 2 < layer_count && takes_one_launch_kernel(layers + i) &&
+         takes_one_launch_kernel(layers + i + 1) && takes_one_launch_kernel(layers + i + 2));
+    const int st = layer_step(layers + i, false, stream, false, mine, early, chained);
     if (st != cudaSuccess) return st;
     run = early ? run + 1 : 0;
   }

@@ -80,19 +80,26 @@ struct AppendArgs {
   // rows before it waits for its predecessor unless this is set. The append
   // kernels wait before anything else.
   bool raw_from_predecessor = false;
-  // The launches that can still be running when this layer-step's kernel starts
-  // (with programmatic dependent launch: the one or two before it on the stream)
-  // are layer-steps of ANOTHER cache layer: none of them writes a row of this
-  // layer's cache, so the kernel need not hold back the page of the newest key.
-  // Only the one-launch layer-step (decode_pagetile.cu) makes use of it.
-  bool cache_settled = false;
+  // How many of the launches that can still be running when this layer-step's
+  // kernel starts (with programmatic dependent launch: the ones just before it
+  // on the stream) are decode steps of THIS cache layer. Each of them appends
+  // the position before the next one's, so the kernel holds back the pages of
+  // the newest `steps_in_flight` positions before its own until its predecessor
+  // is complete, and streams everything older at once. 0: none of them writes a
+  // row of this layer's cache (they are layer-steps of other cache layers).
+  // Only the one-launch layer-step (decode_pagetile.cu) makes use of it; the
+  // other kernels allow for one such step.
+  int32_t steps_in_flight = 1;
   // Let the launch behind this one start as soon as this one runs, instead of
   // when this one's own predecessor is complete. The caller vouches for the
-  // launch behind: it is a one-launch layer-step with cache_settled set, and
-  // cache_settled holds for it against every launch that can then still be in
-  // flight when it starts (see b200kv_decode_step_bf16). Only the one-launch
-  // layer-step makes use of it.
+  // launch behind: it is a one-launch layer-step whose steps_in_flight covers
+  // every launch that can then still be in flight when it starts (see
+  // b200kv_decode_step_bf16). Only the one-launch layer-step makes use of it.
   bool release_early = false;
+  // This launch is one of a run whose launches overlap one another that way:
+  // the grid is then sized for one CTA per SM instead of two, so that two
+  // launches of the run fit on the GPU side by side.
+  bool chained = false;
 };
 
 cudaError_t decode_append_bf16(const AppendArgs &args, cudaStream_t stream);

@@ -566,11 +566,15 @@ int b200kv_decode_attention_tiled_bf16(
 /* One decode step over `layer_count` layers, enqueued in order on `stream`:
  * the layer loop of gemma4_decode_megakernel, src/gemma4_decode_megakernel.cu:172-183,
  * restricted to the KV path (the caller supplies each layer's projections).
- * Consecutive entries are expected to be different cache layers (caches that
- * do not overlap in memory), as in the model: a layer's kernel then streams
- * all of its keys under the tail of the layer before it. Two consecutive
- * entries with the same cache_k / cache_v and cache_layer are detected and
- * handled like separate b200kv_decode_layer_step_bf16 calls. */
+ * Entries are either different cache layers (caches that do not overlap in
+ * memory), as in the model -- a layer's kernel then streams all of its keys
+ * under the tails of the layers before it -- or, where two entries name the same
+ * cache_k / cache_v and cache_layer, consecutive decode steps of that layer in
+ * order (each appends the position after the one its predecessor appended, for
+ * every sequence): the later step then leaves the pages of the positions its
+ * unfinished predecessors write until they are complete. Several steps of one
+ * layer in one call are the way to keep a one-layer decode loop's launches
+ * overlapped. */
 int b200kv_decode_step_bf16(const B200KvLayerStepArgs *layers,
                             int32_t layer_count, b200kv_stream stream);
 
