@@ -175,3 +175,79 @@ def test_decode_step_over_the_layers_of_one_cache(kv, orc, window, start):
             assert max_abs <= ATTN_MAX_ABS and max_rel <= ATTN_MAX_REL, (t, i, max_abs, max_rel)
             assert np.abs(lse[t, i].cpu().numpy() - ref_lse).max() <= LSE_MAX_ABS
     assert np.array_equal(host_u16(dck), ck) and np.array_equal(host_u16(dcv), cv)
+
+
+@pytest.mark.parametrize("name,window,ring_pages,start,order", [
+    ("one layer, linear cache", 0, None, [300], "steps"),
+    ("one layer, ring with slack", 64, 5, [100, 7], "steps"),
+    ("one layer, tight ring", 64, 4, [130, 64], "steps"),
+    ("two layers in turn", 64, 5, [100, 7], "alternate"),
+])
+def test_decode_step_with_consecutive_steps_of_a_layer_in_one_call(kv, orc, name, window, ring_pages, start, order):
+    """b200kv_decode_step_bf16 with entries that name the same cache layer: they are consecutive decode steps, the
+    library lets their launches overlap (a later step starts while earlier ones still run, streams its old keys
+    and holds back the pages the unfinished steps write). Fourteen steps of one layer in one call -- on a linear
+    cache, a ring with slack and a tight ring, where the newest row lands in the slot of a key that an unfinished
+    predecessor still reads -- and seven steps of two layers in turn. Every entry: cache rows and prepared q the
+    oracle's bits (IEEE mode), attention within the tolerance."""
+    from tests import helpers
+
+    HQ, H, D = 16, 8, 256
+    L = 1 if order == "steps" else 2
+    steps = 14 if order == "steps" else 7
+    rng = np.random.default_rng(17)
+    start = np.asarray(start, np.int32)
+    B = start.size
+    acase = helpers.make_append_case(5, start, window=window, ring_pages=ring_pages, layers=L,
+                                     max_pos=int(start.max()) + steps + 1)
+    cfg_t = acase.cfg
+    cfg = kv.make_kv_config(*cfg_t)
+    elems = cfg_t[0] * cfg_t[1] * cfg_t[2] * cfg_t[5] * cfg_t[6]
+    ck = orc.f32_to_bf16(rng.standard_normal(elems, dtype=np.float32))
+    cv = orc.f32_to_bf16(rng.standard_normal(elems, dtype=np.float32))
+    dck, dcv = dev(ck), dev(cv)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    ns = kv.plan_balanced(B, sms)
+    pm = torch.full((B * HQ * ns,), float("nan"), dtype=torch.float32, device="cuda")
+    pl, pacc = pm.clone(), torch.full((B * HQ * ns * D,), float("nan"), dtype=torch.float32, device="cuda")
+    ticket = torch.zeros(B * H * kv.TICKETS_PER_HEAD, dtype=torch.int32, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    table, qw, kw_, cos, sin = (dev(x) for x in (acase.page_table, acase.q_w, acase.k_w, acase.cos, acase.sin))
+    entries = [(t, i) for t in range(steps) for i in range(L)]           # (step, layer), in launch order
+    raws = [[helpers.bf16_normal(rng, (B, n, D)) for n in (HQ, H, H)] for _ in entries]
+    draws = [[dev(x) for x in r] for r in raws]
+    pos_all = [dev((start + t).astype(np.int32)) for t in range(steps)]
+    len_all = [dev((start + t + 1).astype(np.int32)) for t in range(steps)]
+    n = len(entries)
+    q = torch.zeros((n, B, HQ, D), dtype=torch.int16, device="cuda")
+    out = torch.zeros_like(q)
+    lse = torch.zeros((n, B, HQ), dtype=torch.float32, device="cuda")
+    layers = (kv.LayerStepArgs * n)()
+    for e, (t, i) in enumerate(entries):
+        a = layers[e]
+        a.q, a.out, a.lse = q[e].data_ptr(), out[e].data_ptr(), lse[e].data_ptr()
+        a.partial_m, a.partial_l, a.partial_acc = pm.data_ptr(), pl.data_ptr(), pacc.data_ptr()
+        a.cache_k, a.cache_v, a.cache_config = dck.data_ptr(), dcv.data_ptr(), cfg
+        a.page_table, a.token_position, a.seq_lengths = table.data_ptr(), pos_all[t].data_ptr(), len_all[t].data_ptr()
+        a.cache_layer, a.split_size, a.num_splits, a.softmax_scale = i, 0, ns, 1.0 / 16.0
+        r = draws[e]
+        a.raw_q, a.raw_k, a.raw_v = r[0].data_ptr(), r[1].data_ptr(), r[2].data_ptr()
+        a.q_norm_weight, a.k_norm_weight, a.cos, a.sin = qw.data_ptr(), kw_.data_ptr(), cos.data_ptr(), sin.data_ptr()
+        a.batch_count, a.q_heads, a.rotary_dim, a.norm_mode = B, HQ, D, kv.NORM_IEEE
+        a.status, a.ticket = status.data_ptr(), ticket.data_ptr()
+        assert kv.layer_step_launches(a) == 1
+    kv.decode_step(layers, n)
+    torch.cuda.synchronize()
+    assert status[0].item() == 0 and not ticket.any()
+    for e, (t, i) in enumerate(entries):
+        pos, length = (start + t).astype(np.int32), (start + t + 1).astype(np.int32)
+        qp = np.zeros((B, HQ, D), np.uint16)
+        r = raws[e]
+        orc.decode_append(qp, ck, cv, cfg_t, acase.page_table, pos, i, r[0], r[1], r[2], acase.q_w, acase.k_w,
+                          acase.cos, acase.sin, B, HQ, D)
+        assert np.array_equal(host_u16(q[e]), qp.reshape(-1)), (name, t, i)
+        ref, ref_lse = orc.decode_attention_f64(qp, ck, cv, acase.page_table, length, cfg_t, i, 1.0 / 16.0, B, HQ)
+        max_abs, max_rel = attention_error(host_u16(out[e]), ref)
+        assert max_abs <= ATTN_MAX_ABS and max_rel <= ATTN_MAX_REL, (name, t, i, max_abs, max_rel)
+        assert np.abs(lse[e].cpu().numpy() - ref_lse).max() <= LSE_MAX_ABS
+    assert np.array_equal(host_u16(dck), ck) and np.array_equal(host_u16(dcv), cv)
