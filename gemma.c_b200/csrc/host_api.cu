@@ -1139,44 +1139,78 @@ int b200kv_decode_attention_tiled_bf16(
       nullptr, d, d_ticket, static_cast<cudaStream_t>(stream));
 }
 
+namespace {
+
+// An entry's kernel normally lets the next entry's kernel start once its own
+// predecessor is complete, so that a starting kernel meets one unfinished
+// launch. A run of one-launch layer-steps does better: entry i releases entry
+// i + 1 at once, and entry i + 1 is told how many of the launches it can then
+// meet -- the entries of the run so far -- are earlier decode steps of its own
+// cache layer, whose newest rows it must not read before they are complete.
+// (Entries that name the same cache layer are consecutive decode steps, in
+// order: each appends the position after its predecessor's.) The first entry
+// never releases early (what precedes it is not known here) and allows for one
+// step of its own layer in flight; a run is cut after kMaxEarlyRun entries,
+// which bounds the launches in flight whatever their size.
+constexpr int32_t kMaxEarlyRun = 6;
+
+struct StepPlan {
+  int32_t steps_in_flight;  // unfinished launches entry i can meet that are steps of its cache layer
+  bool release_early;       // its kernel releases the next entry's at once
+  bool chained;             // part of a run: sized for one CTA per SM
+};
+
+// Plan of entry i given the early releases in a row up to entry i - 1.
+StepPlan plan_entry(const B200KvLayerStepArgs *layers, int32_t layer_count, int32_t i,
+                    int32_t run) {
+  auto same_cache = [&](int32_t a, int32_t b) {
+    const B200KvLayerStepArgs &p = layers[a];
+    const B200KvLayerStepArgs &c = layers[b];
+    return (p.cache_k == c.cache_k || p.cache_v == c.cache_v) && p.cache_layer == c.cache_layer;
+  };
+  StepPlan plan = {};
+  const int32_t in_flight = 1 + run;  // unfinished launches entry i can meet
+  for (int32_t k = 1; k <= in_flight; ++k) {
+    if (i - k < 0 || layers[i - k].batch_count <= 0 || same_cache(i - k, i)) {
+      ++plan.steps_in_flight;
+    }
+  }
+  plan.release_early = i >= 1 && i + 1 < layer_count && run < kMaxEarlyRun &&
+                       takes_one_launch_kernel(layers + i) &&
+                       takes_one_launch_kernel(layers + i + 1);
+  // part of a run: released early, releasing early, or the run's first entry
+  plan.chained = plan.release_early || run > 0 ||
+                 (i + 2 < layer_count && takes_one_launch_kernel(layers + i) &&
+                  takes_one_launch_kernel(layers + i + 1) &&
+                  takes_one_launch_kernel(layers + i + 2));
+  return plan;
+}
+
+}  // namespace
+
 int b200kv_decode_step_bf16(const B200KvLayerStepArgs *layers,
                             int32_t layer_count, b200kv_stream stream) {
   if (layers == nullptr || layer_count < 0) return cudaErrorInvalidValue;
-  auto same_cache = [&](int32_t i, int32_t j) {
-    const B200KvLayerStepArgs &p = layers[i];
-    const B200KvLayerStepArgs &c = layers[j];
-    return (p.cache_k == c.cache_k || p.cache_v == c.cache_v) && p.cache_layer == c.cache_layer;
-  };
-  // An entry's kernel normally lets the next entry's kernel start once its own
-  // predecessor is complete, so that a starting kernel meets one unfinished
-  // launch. A run of one-launch layer-steps does better: entry i releases entry
-  // i + 1 at once, and entry i + 1 is told how many of the launches it can then
-  // meet -- the entries of the run so far -- are earlier decode steps of its own
-  // cache layer, whose newest rows it must not read before they are complete.
-  // (Entries that name the same cache layer are consecutive decode steps, in
-  // order: each appends the position after its predecessor's.) The first entry
-  // never releases early (what precedes it is not known here) and allows for one
-  // step of its own layer in flight; a run is cut after kMaxEarlyRun entries,
-  // which bounds the launches in flight whatever their size.
-  constexpr int32_t kMaxEarlyRun = 6;
   int32_t run = 0;  // early releases in a row up to the entry before this one
   for (int32_t i = 0; i < layer_count; ++i) {
-    const int32_t in_flight = 1 + run;  // unfinished launches entry i can meet
-    int32_t mine = 0;                   // ... of which decode steps of its cache layer
-    for (int32_t k = 1; k <= in_flight; ++k) {
-      if (i - k < 0 || layers[i - k].batch_count <= 0 || same_cache(i - k, i)) ++mine;
-    }
-    const bool early = i >= 1 && i + 1 < layer_count && run < kMaxEarlyRun &&
-                       takes_one_launch_kernel(layers + i) &&
-                       takes_one_launch_kernel(layers + i + 1);
-    // part of a run: released early, releasing early, or the run's first entry
-    const bool chained =
-        early || run > 0 ||
-        (i + 2 < layer_count && takes_one_launch_kernel(layers + i) &&
-         takes_one_launch_kernel(layers + i + 1) && takes_one_launch_kernel(layers + i + 2));
-    const int st = layer_step(layers + i, false, stream, false, mine, early, chained);
+    const StepPlan plan = plan_entry(layers, layer_count, i, run);
+    const int st = layer_step(layers + i, false, stream, false, plan.steps_in_flight,
+                              plan.release_early, plan.chained);
     if (st != cudaSuccess) return st;
-    run = early ? run + 1 : 0;
+    run = plan.release_early ? run + 1 : 0;
+  }
+  return cudaSuccess;
+}
+
+int b200kv_decode_step_plan(const B200KvLayerStepArgs *layers, int32_t layer_count,
+                            int32_t *steps_in_flight, int32_t *release_early) {
+  if (layers == nullptr || layer_count < 0) return cudaErrorInvalidValue;
+  int32_t run = 0;
+  for (int32_t i = 0; i < layer_count; ++i) {
+    const StepPlan plan = plan_entry(layers, layer_count, i, run);
+    if (steps_in_flight != nullptr) steps_in_flight[i] = plan.steps_in_flight;
+    if (release_early != nullptr) release_early[i] = plan.release_early ? 1 : 0;
+    run = plan.release_early ? run + 1 : 0;
   }
   return cudaSuccess;
 }

@@ -577,6 +577,16 @@ int b200kv_decode_attention_tiled_bf16(
  * overlapped. */
 int b200kv_decode_step_bf16(const B200KvLayerStepArgs *layers,
                             int32_t layer_count, b200kv_stream stream);
+/* What b200kv_decode_step_bf16 would tell each entry's launch, without
+ * launching anything (host only; either output may be NULL):
+ * steps_in_flight[i] -- how many of the launches that can still be running
+ * when entry i's kernel starts are taken to be earlier decode steps of entry
+ * i's own cache layer (0: none of them writes that cache), release_early[i]
+ * -- whether entry i's kernel lets entry i + 1's start at once. Entries that
+ * do not run as the one-launch layer-step neither release early nor are
+ * released early. */
+int b200kv_decode_step_plan(const B200KvLayerStepArgs *layers, int32_t layer_count,
+                            int32_t *steps_in_flight, int32_t *release_early);
 
 /* ------------------------------------------------------------------ *
  * The steps either side of the KV path inside the reference's fused decode

@@ -270,3 +270,51 @@ def test_partition_helpers_of_the_c_abi(kv):
     assert (length.value, start.value, out[0], out[1]) == (6, 144, 109, -1)
     assert lib.b200kv_key_range_page_table(table.ctypes.data, 10, 150, 16, 4, 4, out.ctypes.data,
                                            ctypes.byref(length), ctypes.byref(start)) == -1
+
+
+def _step_entries(kv, specs):
+    """LayerStepArgs array for the planning call; specs: (cache pointer, cache layer, batch, window) per entry.
+    Nothing is dereferenced by b200kv_decode_step_plan, so the pointers are just distinct numbers."""
+    arr = (kv.LayerStepArgs * len(specs))()
+    for a, (cache, layer, batch, window) in zip(arr, specs):
+        pages = 64 if window else 2048
+        a.cache_config = kv.make_kv_config(4, max(batch, 1) * pages, 16, pages, max(batch, 1), 8, 256, window)
+        a.cache_k, a.cache_v, a.cache_layer = cache, cache + 0x1000, layer
+        a.batch_count, a.q_heads, a.rotary_dim, a.split_size, a.num_splits = batch, 16, 256, 0, 37
+        a.ticket = 0x7000
+    return arr
+
+
+def test_decode_step_plan_of_runs(kv):
+    """The host logic behind b200kv_decode_step_bf16 (no device involved). Layers of a model in order: from the
+    second entry on nothing in flight writes an entry's cache, entries release their successor at once, and a run
+    is cut after six early releases. Steps of one layer: every entry allows for as many steps of its own layer in
+    flight as the run is long. An entry that is not a one-launch layer-step ends the run on both sides."""
+    n = 48
+    held, early = kv.decode_step_plan(_step_entries(kv, [(0x100000, i % 4, 1, 1024) for i in range(n)]), n)
+    assert held[0] == 1 and held[1:4] == [0, 0, 0]
+    held, early = kv.decode_step_plan(_step_entries(kv, [(0x100000 * (i + 1), 0, 1, 1024) for i in range(n)]), n)
+    assert held == [1] + [0] * (n - 1)
+    assert early == [i % 7 != 0 and i + 1 < n for i in range(n)]
+
+    n = 16                                               # sixteen steps of ONE layer (a one-layer decode loop)
+    held, early = kv.decode_step_plan(_step_entries(kv, [(0x100000, 0, 1, 0)] * n), n)
+    assert early == [i % 7 != 0 and i + 1 < n for i in range(n)]
+    assert held == [1, 1, 2, 3, 4, 5, 6, 7, 1, 2, 3, 4, 5, 6, 7, 1]
+
+    n = 8                                                # two layers in turn
+    held, early = kv.decode_step_plan(_step_entries(kv, [(0x100000, i % 2, 2, 1024) for i in range(n)]), n)
+    assert held == [1, 0, 1, 1, 2, 2, 3, 3]
+    assert early == [False, True, True, True, True, True, True, False]
+
+    specs = [(0x100000 * (i + 1), 0, 1, 1024) for i in range(6)]
+    specs[3] = (0x900000, 0, 64, 1024)                   # 64 sequences: the balanced kernel's job
+    held, early = kv.decode_step_plan(_step_entries(kv, specs), 6)
+    assert early == [False, True, False, False, True, False]
+    assert held == [1, 0, 0, 0, 0, 0]
+    arr = _step_entries(kv, [(0x100000 * (i + 1), 0, 1, 1024) for i in range(4)])
+    for a in arr:
+        a.ticket = None                                  # without tickets nothing runs as one launch
+    held, early = kv.decode_step_plan(arr, 4)
+    assert early == [False] * 4 and held == [1, 0, 0, 0]
+    assert kv.decode_step_plan(arr, 0) == ([], [])
