@@ -15,6 +15,7 @@
 #include "kernels.cuh"
 #include "prep_common.cuh"
 
+#include <algorithm>
 #include <type_traits>
 
 namespace b200kv {
@@ -79,83 +80,259 @@ __global__ void decode_append_kernel(AppendArgs a) {
   }
 }
 
-// grid (rows). The q_heads + 2 * kv_heads rows of a token are dealt to the
-// warps two at a time (for 16 + 8 + 8 rows and 16 warps: one query head and one
-// K or V head each). Global memory is touched with 128-bit accesses only: a
-// warp loads both of its rows up front, passes each through a shared-memory row
-// to get the arithmetic's ownership (lane l holds elements l + 32 i, which
-// fixes the order of the sum of squares) and back; the RoPE factors of the
-// token and the norm weights sit in registers. With 2-byte accesses and the
-// tables re-read per head the kernel was bound by L1 transactions (32 per KB
-// moved) at 0.39 of the HBM peak.
+// ---------------------------------------------------------------------------
+// Whole-prompt prep. grid (rows): a CTA per token; its q_heads + 2 * kv_heads
+// head rows are dealt to the warps in PAIRS of the same kind (two query heads,
+// two K heads, two V heads; a last odd head pairs with nothing).
+//
+// The arithmetic's ownership -- lane l holds elements l + 32 i, which fixes the
+// order of the sum of squares and so the bits of the scale -- is not the order
+// the rows lie in memory. Global memory is touched with 128-bit accesses only;
+// the transposition goes through shared memory, and what made the first
+// versions issue-bound (2-byte accesses: 32 L1 transactions per KB moved, 0.39 of
+// the HBM peak; then sixteen 2-byte shared accesses and one scalar fp32 operation
+// per element and step: 250 warp instructions per KB, 0.50) is halved twice:
+//   * the two rows of a pair are interleaved element by element (byte permutes
+//     on the 128-bit packs), so that every 32-bit shared-memory word holds one
+//     element of each row: a lane reads its elements of BOTH rows with D / 32
+//     word loads and writes both results with D / 32 word stores;
+//   * the arithmetic runs on both rows at once in packed fp32 pairs
+//     (fma.rn.f32x2 / mul.rn{.ftz}.f32x2: each half is the scalar operation with
+//     the same rounding, so the bits are those of prep_common.cuh), and results
+//     are rounded and packed two at a time (cvt.rn.bf16x2.f32).
+// Shared-memory words are laid out so that neither side conflicts: a pack's
+// eight words go to two regions (elements 0..3 and 4..7 of the pack, 16 bytes
+// per lane and region), the second region 16 words off a multiple of 32.
+// ---------------------------------------------------------------------------
+using f32x2 = unsigned long long;  // two fp32: low half = first row of the pair
+
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 v, float &lo, float &hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2 fma2_rn(f32x2 a, f32x2 b, f32x2 c) {
+  f32x2 r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ f32x2 mul2_rn(f32x2 a, f32x2 b) {
+  f32x2 r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+// The prep multiplications (flush-to-zero in the approx mode, see mul_prep).
+template <bool kIeee>
+__device__ __forceinline__ f32x2 mul2_prep(f32x2 a, f32x2 b) {
+  f32x2 r;
+  if constexpr (kIeee) {
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  } else {
+    asm("mul.rn.ftz.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  }
+  return r;
+}
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t r;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+  return r;
+}
+// bf16 pair from two floats: low half <- lo.
+__device__ __forceinline__ uint32_t cvt_bf16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+template <int D>
+struct PairLayout {
+  static constexpr int kRegion = D / 2 + 16;  // words; the second region starts here
+  static constexpr int kWords = D + 16;
+  // word of element e of the interleaved pair
+  __device__ static int word(int e) {
+    return ((e & 7) >> 2) * kRegion + (e >> 3) * 4 + (e & 3);
+  }
+};
+
+// rsqrt(mean of squares + eps) of one row from its warp-wide sum of squares.
+template <int D, bool kIeee>
+__device__ __forceinline__ float rms_scale_of(float ss) {
+  const float t = __fadd_rn(__fdiv_rn(ss, float(D)), kRmsEps);
+  if constexpr (kIeee) {
+    return __fdiv_rn(1.0f, __fsqrt_rn(t));
+  } else {
+    return rsqrtf(t);
+  }
+}
+
+// What a warp needs to know about pair `pr` of a token: kind 0 query heads, 1 K
+// heads, 2 V heads; whether the pair has a second row; where its rows lie.
+struct PrepPair {
+  int kind;
+  bool second;
+  const __nv_bfloat16 *src;
+  __nv_bfloat16 *dst;
+};
+
+template <int D>
+__device__ __forceinline__ PrepPair prep_pair_of(const PrefillPrepArgs &a, int64_t row, int pr,
+                                                 int pq, int pk) {
+  PrepPair p;
+  p.kind = pr < pq ? 0 : (pr < pq + pk ? 1 : 2);
+  const int h0 = 2 * (p.kind == 0 ? pr : (p.kind == 1 ? pr - pq : pr - pq - pk));
+  p.second = h0 + 1 < (p.kind == 0 ? a.q_heads : a.kv_heads);
+  p.src = p.kind == 0
+              ? a.q + (row * a.q_heads + h0) * D
+              : ((p.kind == 1 || a.v == nullptr ? a.k : a.v) + (row * a.kv_heads + h0) * D);
+  p.dst = p.kind == 0 ? a.q_prepared + (row * a.q_heads + h0) * D
+                      : ((p.kind == 1 ? a.k_prepared : a.v_prepared) +
+                         (row * a.kv_heads + h0) * D);
+  return p;
+}
+
+// Up to 8 warps of two pairs each, four CTAs per SM: the kernel lives on loads in
+// flight (a token's rows, then its position's RoPE factors), so the rows of a
+// warp's first pair are asked for before anything else and the next pair's as
+// soon as the current one is in shared memory.
+constexpr int kPrepWarps = 8;
+
 template <int D, int ROT, bool kIeee>
-__global__ void prefill_prep_kernel(PrefillPrepArgs a) {
+__global__ __launch_bounds__(kPrepWarps * 32, D == 256 ? 4 : 2) void prefill_prep_kernel(PrefillPrepArgs a) {
+  constexpr int E = D / 32;          // elements per lane and row
   constexpr int kVecs = D / 8 / 32;  // 128-bit packs per lane and row
-  __shared__ __align__(16) __nv_bfloat16 s_rows[16][D];
+  constexpr int kPairs = ROT / 64;   // rotated (lo, hi) element pairs per lane
+  using L = PairLayout<D>;
+  __shared__ __align__(16) uint32_t s_pairs[kPrepWarps][L::kWords];
   const int64_t row = blockIdx.x;
   const int warp = int(threadIdx.x) >> 5;
   const int lane = int(threadIdx.x) & 31;
+  const int warps = int(blockDim.x) >> 5;
+  // pairs: of query heads, then of K heads, then of V heads
+  const int pq = (a.q_heads + 1) / 2;
+  const int pk = (a.kv_heads + 1) / 2;
+  const int pairs = pq + 2 * pk;
+  if (warp >= pairs) return;
+
+  uint4 pa[kVecs], pb[kVecs];
+  auto fetch = [&](const PrepPair &p) {
+#pragma unroll
+    for (int v = 0; v < kVecs; ++v) {
+      pa[v] = __ldg(reinterpret_cast<const uint4 *>(p.src) + lane + 32 * v);
+      pb[v] = p.second ? __ldg(reinterpret_cast<const uint4 *>(p.src + D) + lane + 32 * v)
+                       : make_uint4(0u, 0u, 0u, 0u);
+    }
+  };
+  PrepPair cur = prep_pair_of<D>(a, row, warp, pq, pk);
+  fetch(cur);
   const int position = __ldg(a.token_position + row);
   if (position < 0) return;
-  const int warps = int(blockDim.x) >> 5;
-  const int tasks = a.q_heads + 2 * a.kv_heads;  // q heads, then K heads, then V heads
-  // Source / destination row of a task; V tasks read raw K when there is no V
-  // projection.
-  auto source = [&](int task) -> const __nv_bfloat16 * {
-    if (task < a.q_heads) return a.q + (row * a.q_heads + task) * D;
-    const int kv = task - a.q_heads;
-    if (kv < a.kv_heads) return a.k + (row * a.kv_heads + kv) * D;
-    const int64_t off = (row * a.kv_heads + (kv - a.kv_heads)) * D;
-    return (a.v != nullptr ? a.v : a.k) + off;
-  };
-  auto destination = [&](int task) -> __nv_bfloat16 * {
-    if (task < a.q_heads) return a.q_prepared + (row * a.q_heads + task) * D;
-    const int kv = task - a.q_heads;
-    if (kv < a.kv_heads) return a.k_prepared + (row * a.kv_heads + kv) * D;
-    return a.v_prepared + (row * a.kv_heads + (kv - a.kv_heads)) * D;
-  };
-  PrepTables<D, ROT> tables;
-  tables.load_rope(a.cos + int64_t(position) * (ROT / 2),
-                   a.sin + int64_t(position) * (ROT / 2), lane);
-  __nv_bfloat16 *mine = s_rows[warp];
-  auto finish = [&](int task, const uint4 (&packs)[kVecs]) {
+
+  // RoPE factors of the token for this lane's rotated elements
+  float rc[kPairs], rs[kPairs];
+  {
+    const float *cos_row = a.cos + int64_t(position) * (ROT / 2);
+    const float *sin_row = a.sin + int64_t(position) * (ROT / 2);
+#pragma unroll
+    for (int i = 0; i < kPairs; ++i) {
+      rc[i] = __ldg(cos_row + lane + i * 32);
+      rs[i] = __ldg(sin_row + lane + i * 32);
+    }
+  }
+  uint32_t *mine = s_pairs[warp];
+  // this lane's words of the interleaved pair: element lane + 32 i
+  const int word0 = ((lane & 7) >> 2) * L::kRegion + (lane >> 3) * 4 + (lane & 3);  // + 16 i
+
+  for (int pr = warp; pr < pairs; pr += warps) {
+    // 1. both rows, interleaved, into shared memory; then the next pair's rows are asked for
 #pragma unroll
     for (int v = 0; v < kVecs; ++v) {
-      reinterpret_cast<uint4 *>(mine)[lane + 32 * v] = packs[v];
+      const int pv = lane + 32 * v;
+      reinterpret_cast<uint4 *>(mine)[pv] =
+          make_uint4(prmt(pa[v].x, pb[v].x, 0x5410u), prmt(pa[v].x, pb[v].x, 0x7632u),
+                     prmt(pa[v].y, pb[v].y, 0x5410u), prmt(pa[v].y, pb[v].y, 0x7632u));
+      reinterpret_cast<uint4 *>(mine + L::kRegion)[pv] =
+          make_uint4(prmt(pa[v].z, pb[v].z, 0x5410u), prmt(pa[v].z, pb[v].z, 0x7632u),
+                     prmt(pa[v].w, pb[v].w, 0x5410u), prmt(pa[v].w, pb[v].w, 0x7632u));
+    }
+    const PrepPair now = cur;
+    if (pr + warps < pairs) {
+      cur = prep_pair_of<D>(a, row, pr + warps, pq, pk);
+      fetch(cur);
+    }
+    // the norm weights of this lane's elements (query and K rows)
+    float w[E];
+    if (now.kind != 2) {
+      const __nv_bfloat16 *weight = now.kind == 0 ? a.q_norm_weight : a.k_norm_weight;
+#pragma unroll
+      for (int i = 0; i < E; ++i) w[i] = __bfloat162float(__ldg(weight + lane + i * 32));
     }
     __syncwarp();
-    float x[D / 32];
-    load_head<D>(mine, lane, x);
-    __nv_bfloat16 y[D / 32];
-    if (task < a.q_heads + a.kv_heads) {
-      tables.load_weight(task < a.q_heads ? a.q_norm_weight : a.k_norm_weight, lane);
-      prep_weighted_rope_tables<D, ROT, kIeee>(y, x, tables);
+    // 2. this lane's elements of both rows; sums of squares in the reference's order
+    f32x2 x[E];
+    f32x2 ss = pack2(0.0f, 0.0f);
+#pragma unroll
+    for (int i = 0; i < E; ++i) {
+      const uint32_t wd = mine[word0 + 16 * i];
+      x[i] = pack2(__uint_as_float(wd << 16), __uint_as_float(wd & 0xffff0000u));
+      ss = fma2_rn(x[i], x[i], ss);
+    }
+    float ss_a, ss_b;
+    unpack2(ss, ss_a, ss_b);
+#pragma unroll
+    for (int offset = 16; offset > 0; offset /= 2) {
+      ss_a = __fadd_rn(ss_a, __shfl_xor_sync(0xffffffffu, ss_a, offset));
+      ss_b = __fadd_rn(ss_b, __shfl_xor_sync(0xffffffffu, ss_b, offset));
+    }
+    const f32x2 scale2 = pack2(rms_scale_of<D, kIeee>(ss_a), rms_scale_of<D, kIeee>(ss_b));
+    // 3. norm (+ weight, + rotation), rounded and packed per element of the pair;
+    // a lane's words are its own: they take the results
+    if (now.kind == 2) {
+#pragma unroll
+      for (int i = 0; i < E; ++i) {
+        float ya, yb;
+        unpack2(mul2_prep<kIeee>(x[i], scale2), ya, yb);
+        mine[word0 + 16 * i] = cvt_bf16x2(ya, yb);
+      }
     } else {
-      prep_scale_free_values<D, kIeee>(y, x);
+#pragma unroll
+      for (int i = 0; i < E; ++i) {
+        x[i] = mul2_prep<kIeee>(mul2_prep<kIeee>(x[i], scale2), pack2(w[i], w[i]));
+      }
+#pragma unroll
+      for (int i = 0; i < kPairs; ++i) {  // lo' = lo c - hi s, hi' = hi c + lo s
+        const f32x2 lo = x[i];
+        const f32x2 hi = x[i + kPairs];
+        const f32x2 c2 = pack2(rc[i], rc[i]);
+        x[i] = fma2_rn(hi, pack2(-rs[i], -rs[i]), mul2_rn(lo, c2));
+        x[i + kPairs] = fma2_rn(lo, pack2(rs[i], rs[i]), mul2_rn(hi, c2));
+      }
+#pragma unroll
+      for (int i = 0; i < E; ++i) {
+        float ya, yb;
+        unpack2(x[i], ya, yb);
+        mine[word0 + 16 * i] = cvt_bf16x2(ya, yb);
+      }
     }
     __syncwarp();
-    store_head<D>(mine, y, lane);
-    __syncwarp();
-    uint4 *dst = reinterpret_cast<uint4 *>(destination(task));
+    // 4. de-interleave and out
 #pragma unroll
     for (int v = 0; v < kVecs; ++v) {
-      dst[lane + 32 * v] = reinterpret_cast<const uint4 *>(mine)[lane + 32 * v];
+      const int pv = lane + 32 * v;
+      const uint4 w0 = reinterpret_cast<const uint4 *>(mine)[pv];
+      const uint4 w1 = reinterpret_cast<const uint4 *>(mine + L::kRegion)[pv];
+      reinterpret_cast<uint4 *>(now.dst)[pv] =
+          make_uint4(prmt(w0.x, w0.y, 0x5410u), prmt(w0.z, w0.w, 0x5410u),
+                     prmt(w1.x, w1.y, 0x5410u), prmt(w1.z, w1.w, 0x5410u));
+      if (now.second) {
+        reinterpret_cast<uint4 *>(now.dst + D)[pv] =
+            make_uint4(prmt(w0.x, w0.y, 0x7632u), prmt(w0.z, w0.w, 0x7632u),
+                       prmt(w1.x, w1.y, 0x7632u), prmt(w1.z, w1.w, 0x7632u));
+      }
     }
-    __syncwarp();
-  };
-  for (int t0 = warp; t0 < tasks; t0 += 2 * warps) {
-    const int t1 = t0 + warps;
-    uint4 p0[kVecs], p1[kVecs];
-    const uint4 *s0 = reinterpret_cast<const uint4 *>(source(t0));
-#pragma unroll
-    for (int v = 0; v < kVecs; ++v) p0[v] = __ldg(s0 + lane + 32 * v);
-    if (t1 < tasks) {
-      const uint4 *s1 = reinterpret_cast<const uint4 *>(source(t1));
-#pragma unroll
-      for (int v = 0; v < kVecs; ++v) p1[v] = __ldg(s1 + lane + 32 * v);
-    }
-    finish(t0, p0);
-    if (t1 < tasks) finish(t1, p1);
+    __syncwarp();  // the next pair's packs overwrite the words
   }
 }
 
@@ -283,7 +460,9 @@ cudaError_t prefill_prep_bf16(const PrefillPrepArgs &a, cudaStream_t stream) {
       reinterpret_cast<uintptr_t>(a.k_prepared) |
       reinterpret_cast<uintptr_t>(a.v_prepared);
   if ((align & 15u) != 0) return cudaErrorInvalidValue;  // rows move as 128-bit packs
-  const int warps = a.q_heads < 16 ? a.q_heads : 16;
+  // pairs of head rows per token; two pairs per warp where there are that many
+  const int pairs = (a.q_heads + 1) / 2 + 2 * ((a.kv_heads + 1) / 2);
+  const int warps = std::max(1, std::min(kPrepWarps, (pairs + 1) / 2));
   return dispatch_geometry(
       a.head_dim, a.rotary_dim, a.norm_mode, [&](auto d, auto rot, auto ieee) {
         prefill_prep_kernel<decltype(d)::value, decltype(rot)::value,
