@@ -96,7 +96,9 @@ def test_decode_layer_through_the_reference_structs(kv, orc, tmp_path):
     outs = [torch.zeros(HID, dtype=torch.int16, device="cuda") for _ in range(4)]
     pm = torch.zeros(HQ * num_splits, dtype=torch.float32, device="cuda")
     pl, pacc = pm.clone(), torch.zeros(HQ * num_splits * D, dtype=torch.float32, device="cuda")
-    ticket = torch.zeros(1, dtype=torch.int32, device="cuda")
+    # one word for the O projection's row, then the attention's tickets: the layout the C++ entry point hands
+    # on (include/gemma4_b200kv.hpp), so that both runs take the one-launch attention kernel
+    ticket = torch.zeros(1 + 8 * kv.TICKETS_PER_HEAD, dtype=torch.int32, device="cuda")
     st = torch.zeros(4, dtype=torch.int32, device="cuda")
     a = kv.AttentionLayerArgs()
     s = a.kv
@@ -108,6 +110,7 @@ def test_decode_layer_through_the_reference_structs(kv, orc, tmp_path):
     s.q_norm_weight, s.k_norm_weight, s.cos, s.sin = (d["q_w"].data_ptr(), d["k_w"].data_ptr(), d["cos"].data_ptr(),
                                                      d["sin"].data_ptr())
     s.batch_count, s.q_heads, s.rotary_dim, s.norm_mode, s.status = 1, HQ, D, kv.NORM_RSQRT_APPROX, st.data_ptr()
+    s.ticket = ticket.data_ptr() + 4
     a.attention_x, a.attention_input_norm_weight = d["x"].data_ptr(), d["w_in"].data_ptr()
     a.attention_qkv_proj_col_major, a.attention_o_proj_col_major = d["w_qkv"].data_ptr(), d["w_o"].data_ptr()
     a.attention_post_norm_weight, a.attention_pre_ffn_norm_weight = d["w_post"].data_ptr(), d["w_pre"].data_ptr()
