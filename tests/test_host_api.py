@@ -318,3 +318,14 @@ def test_decode_step_plan_of_runs(kv):
     held, early = kv.decode_step_plan(arr, 4)
     assert early == [False] * 4 and held == [1, 0, 0, 0]
     assert kv.decode_step_plan(arr, 0) == ([], [])
+
+
+def test_device_phase_header_compiles_into_a_kernel_of_its_own(tmp_path):
+    """include/gemma4_b200kv_device.cuh is header-only: the cooperative harness kernel that calls its three
+    phases builds with nvcc for sm_100a without the library (no GPU needed here; the GPU test runs it)."""
+    from tests.gpu_util import build_device_phases_harness
+
+    lib = build_device_phases_harness(force=True)
+    assert lib.exists() and lib.stat().st_size > 0
+    exported = subprocess.run(["nm", "-D", "--defined-only", str(lib)], capture_output=True, text=True).stdout
+    assert "device_phases_layer_step" in exported
