@@ -251,3 +251,79 @@ def test_decode_step_with_consecutive_steps_of_a_layer_in_one_call(kv, orc, name
         assert max_abs <= ATTN_MAX_ABS and max_rel <= ATTN_MAX_REL, (name, t, i, max_abs, max_rel)
         assert np.abs(lse[e].cpu().numpy() - ref_lse).max() <= LSE_MAX_ABS
     assert np.array_equal(host_u16(dck), ck) and np.array_equal(host_u16(dcv), cv)
+
+
+@pytest.mark.parametrize("name,window,ring_pages,start,L,steps", [
+    ("one layer, tight ring of 1024 (configs[0])", 1024, 64, [1024], 1, 32),
+    ("one layer, linear", 0, None, [3000], 1, 32),
+    ("six layers in turn", 1024, 65, [1500], 6, 6),
+])
+def test_runs_of_overlapping_launches_repeat_bit_for_bit(kv, orc, name, window, ring_pages, start, L, steps):
+    """The same decode steps enqueued as runs (sixteen entries per b200kv_decode_step_bf16 call: launches start
+    while their predecessors still run) twenty times over from the same initial cache: the same output bits and
+    cache bytes every time, a clean status, tickets back at zero -- and the same cache bytes and prepared q as
+    the steps enqueued one call at a time (the rows may differ in the last bit: runs cut the key ranges
+    differently)."""
+    import ctypes
+
+    from tests import helpers
+
+    HQ, H, D = 16, 8, 256
+    rng = np.random.default_rng(5)
+    start = np.asarray(start, np.int32)
+    B = start.size
+    acase = helpers.make_append_case(5, start, window=window, ring_pages=ring_pages, layers=L,
+                                     max_pos=int(start.max()) + steps + 1)
+    cfg_t = acase.cfg
+    cfg = kv.make_kv_config(*cfg_t)
+    elems = cfg_t[0] * cfg_t[1] * cfg_t[2] * cfg_t[5] * cfg_t[6]
+    ck0 = orc.f32_to_bf16(rng.standard_normal(elems, dtype=np.float32))
+    cv0 = orc.f32_to_bf16(rng.standard_normal(elems, dtype=np.float32))
+    ns = kv.plan_balanced(B, torch.cuda.get_device_properties(0).multi_processor_count)
+    table, qw, kw_, cos, sin = (dev(x) for x in (acase.page_table, acase.q_w, acase.k_w, acase.cos, acase.sin))
+    entries = [(t, i) for t in range(steps) for i in range(L)]
+    n = len(entries)
+    draws = [[dev(helpers.bf16_normal(rng, (B, m, D))) for m in (HQ, H, H)] for _ in entries]
+    pos_all = [dev((start + t).astype(np.int32)) for t in range(steps)]
+    len_all = [dev((start + t + 1).astype(np.int32)) for t in range(steps)]
+
+    def once(per_call):
+        dck, dcv = dev(ck0), dev(cv0)
+        pm = torch.full((B * HQ * ns,), float("nan"), dtype=torch.float32, device="cuda")
+        pl, pacc = pm.clone(), torch.full((B * HQ * ns * D,), float("nan"), dtype=torch.float32, device="cuda")
+        ticket = torch.zeros(B * H * kv.TICKETS_PER_HEAD, dtype=torch.int32, device="cuda")
+        status = torch.zeros(4, dtype=torch.int32, device="cuda")
+        q = torch.zeros((n, B, HQ, D), dtype=torch.int16, device="cuda")
+        out = torch.zeros_like(q)
+        lse = torch.zeros((n, B, HQ), dtype=torch.float32, device="cuda")
+        layers = (kv.LayerStepArgs * n)()
+        for e, (t, i) in enumerate(entries):
+            a = layers[e]
+            a.q, a.out, a.lse = q[e].data_ptr(), out[e].data_ptr(), lse[e].data_ptr()
+            a.partial_m, a.partial_l, a.partial_acc = pm.data_ptr(), pl.data_ptr(), pacc.data_ptr()
+            a.cache_k, a.cache_v, a.cache_config = dck.data_ptr(), dcv.data_ptr(), cfg
+            a.page_table, a.token_position, a.seq_lengths = (table.data_ptr(), pos_all[t].data_ptr(),
+                                                             len_all[t].data_ptr())
+            a.cache_layer, a.split_size, a.num_splits, a.softmax_scale = i, 0, ns, 1.0 / 16.0
+            r = draws[e]
+            a.raw_q, a.raw_k, a.raw_v = r[0].data_ptr(), r[1].data_ptr(), r[2].data_ptr()
+            a.q_norm_weight, a.k_norm_weight, a.cos, a.sin = (qw.data_ptr(), kw_.data_ptr(), cos.data_ptr(),
+                                                              sin.data_ptr())
+            a.batch_count, a.q_heads, a.rotary_dim, a.norm_mode = B, HQ, D, kv.NORM_RSQRT_APPROX
+            a.status, a.ticket = status.data_ptr(), ticket.data_ptr()
+        size = ctypes.sizeof(kv.LayerStepArgs)
+        for e0 in range(0, n, per_call):
+            m = min(per_call, n - e0)
+            kv.decode_step((kv.LayerStepArgs * m).from_address(ctypes.addressof(layers) + e0 * size), m)
+        torch.cuda.synchronize()
+        assert status[0].item() == 0 and not ticket.any(), name
+        return out, lse.view(torch.int32), q, dck, dcv
+
+    single = once(1)
+    first = once(16)
+    assert all(torch.equal(a, b) for a, b in zip(first[2:], single[2:])), name       # q and caches
+    worst = (first[0].view(torch.bfloat16).float() - single[0].view(torch.bfloat16).float()).abs().max().item()
+    assert worst <= 2.0 ** -9, (name, worst)
+    for _ in range(19):
+        again = once(16)
+        assert all(torch.equal(a, b) for a, b in zip(again, first)), name
