@@ -487,6 +487,17 @@ class RankWorkload:
         self._launch_step(self.pos_all[s].data_ptr(), self.len_all[s].data_ptr(), s if events else None, self.stream)
         self._exchange()
 
+    def step_direct(self, s: int):
+        """One decode step launched on the stream even when a graph has been captured (the cold-cache timing of
+        a workload whose graph holds several steps); skip_replayed_steps() afterwards keeps the graph in step."""
+        self._launch_step(self.pos_all[s].data_ptr(), self.len_all[s].data_ptr(), None, self.stream)
+        self._exchange()
+
+    def skip_replayed_steps(self, count: int):
+        assert count % self.steps_per_graph == 0 and (self.graph_next - self.graph_first) % self.steps_per_graph == 0
+        self.step_state.add_(count)
+        self.graph_next += count
+
     def _exchange(self):
         """The step's exchange between the ranks (cfg4 on more than one GPU). KV-head sharding: all-gather of the
         head outputs, after which every rank holds all heads' rows. Key-range sharding: every rank's rows and
@@ -1096,10 +1107,14 @@ WORKLOADS = {
 }
 
 
+# One-layer workloads put this many consecutive steps into one graph: what a replay of configs[1] holds (48 layers).
+ONE_LAYER_STEPS_PER_GRAPH = 48
+
+
 def replays_graph(args, world: int) -> bool:
     """Whether the steps are replayed from a CUDA graph: the batch-1 workloads, and the KV-head-sharded long
     context with the one-launch kernel (on several GPUs with the exchange inside the kernel, or one rank's share
-    emulated on one GPU) -- sixteen consecutive steps of the one layer per graph, handed to the library as one
+    emulated on one GPU) -- ONE_LAYER_STEPS_PER_GRAPH consecutive steps of the one layer per graph, handed to the library as one
     b200kv_decode_step_bf16 call, so that the ranks' launches do not drift against each other under the hosts'
     jitter and the library can keep the steps' launches overlapped."""
     if args.graph != "auto":
@@ -1159,7 +1174,7 @@ def workload_config(args, world, where, parallelism=None, layers=None):
         "parallelism": parallelism or f"x{world}",
         "partition": args.partition,
         "where": where,
-        "launch": ("one CUDA graph replay per step" + (" (sixteen one-kernel steps per replay)"
+        "launch": ("one CUDA graph replay per step" + (f" ({ONE_LAYER_STEPS_PER_GRAPH} one-kernel steps per replay)"
                                                          if args.workload in ("cfg1", "cfg4") else "")
                    if replays_graph(args, world)
                    else "stream launches (programmatic dependent launch between kernels)"),
@@ -1638,13 +1653,18 @@ def measure_workload(args, kv, torch, dist, world, rank, sampler=None, verify=Tr
     e2e_warm = 3
     use_graph = replays_graph(args, world)
     probe_steps = 11                        # steps after the timed regions that carry the per-kernel events
-    # a one-layer step is a single kernel: sixteen steps per replayed graph (see RankWorkload.enable_graph)
-    steps_per_graph = 16 if (use_graph and spec.n_local + spec.n_global == 1) else 1
+    # a one-layer step is a single kernel: as many steps per replayed graph as configs[1] has layer-steps
+    # per replay (see RankWorkload.enable_graph)
+    steps_per_graph = ONE_LAYER_STEPS_PER_GRAPH if (use_graph and spec.n_local + spec.n_global == 1) else 1
     if steps_per_graph > 1:
         args = copy.copy(args)
         args.warmup = -(-args.warmup // steps_per_graph) * steps_per_graph
         args.steps = -(-args.steps // steps_per_graph) * steps_per_graph
     cold_steps = min(args.steps, 50) if args.cache in ("cold", "both") else 0
+    if cold_steps and steps_per_graph > 1:
+        # cold steps are timed one by one, so they are launched directly, not replayed; a whole number of graphs'
+        # worth of them keeps the replays that follow in step
+        cold_steps = steps_per_graph
     total_steps = args.warmup + args.steps + cold_steps + e2e_warm + args.e2e_steps + probe_steps
     wl = RankWorkload(kv, torch, ctx, total_steps, args.seed + 1000 * rank, args, spec)
     torch.cuda.synchronize()
@@ -1700,9 +1720,14 @@ def measure_workload(args, kv, torch, dist, world, rank, sampler=None, verify=Tr
         for i in range(cold_steps):
             flush.fill_(i & 0xFF)
             begin[i].record()
-            wl.step(s)
+            if steps_per_graph > 1:
+                wl.step_direct(s)
+            else:
+                wl.step(s)
             s += 1
             end[i].record()
+        if steps_per_graph > 1:
+            wl.skip_replayed_steps(cold_steps)
         barrier()
         ms = np.array([begin[i].elapsed_time(end[i]) for i in range(cold_steps)])
         cold_bytes = statistics.mean(wl.bytes_for_step(i)[0] for i in range(first_cold, first_cold + cold_steps))

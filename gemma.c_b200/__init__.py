@@ -196,7 +196,8 @@ _SIGNATURES = {
     "b200kv_plan_splits_total": (None, [c_int32, c_int32, c_int64, c_int32, c_int32, POINTER(c_int32), POINTER(c_int32)]),
     "b200kv_decode_layer_step_bf16": (c_int, [POINTER(LayerStepArgs), _P]),
     "b200kv_decode_step_bf16": (c_int, [POINTER(LayerStepArgs), c_int32, _P]),
-    "b200kv_decode_step_plan": (c_int, [POINTER(LayerStepArgs), c_int32, POINTER(c_int32), POINTER(c_int32)]),
+    "b200kv_decode_step_plan": (c_int, [POINTER(LayerStepArgs), c_int32, POINTER(c_int32), POINTER(c_int32),
+                                        POINTER(c_int32)]),
     "b200kv_decode_layer_step_tiled_bf16": (c_int, [POINTER(LayerStepArgs), _P]),
     "b200kv_layer_step_launches": (c_int32, [POINTER(LayerStepArgs)]),
     "b200kv_decode_attention_tiled_bf16": (c_int, [_P, _P, _P, _P, _P, KvConfig, _P, _P, c_int32, c_float, c_int32,
@@ -554,13 +555,17 @@ def decode_step(layers, layer_count: int, stream=None, check: bool = True) -> in
     return _check(code, "b200kv_decode_step_bf16", check)
 
 
-def decode_step_plan(layers, layer_count: int) -> tuple[list[int], list[bool]]:
+def decode_step_plan(layers, layer_count: int, forwarded: bool = False):
     """What decode_step would tell each entry's launch (host only): per entry the number of unfinished launches
-    taken to be earlier steps of its own cache layer, and whether its kernel releases the next entry's at once."""
+    taken to be earlier steps of its own cache layer, and whether its kernel releases the next entry's at once;
+    with `forwarded` also for how many of those steps the kernel prepares the appended rows itself."""
     held = (c_int32 * max(layer_count, 1))()
     early = (c_int32 * max(layer_count, 1))()
-    _check(load_library().b200kv_decode_step_plan(layers, layer_count, held, early), "b200kv_decode_step_plan", True)
-    return list(held)[:layer_count], [bool(x) for x in list(early)[:layer_count]]
+    fwd = (c_int32 * max(layer_count, 1))()
+    _check(load_library().b200kv_decode_step_plan(layers, layer_count, held, early, fwd), "b200kv_decode_step_plan",
+           True)
+    out = (list(held)[:layer_count], [bool(x) for x in list(early)[:layer_count]])
+    return out + (list(fwd)[:layer_count],) if forwarded else out
 
 
 def decode_ingress(args: IngressArgs, stream=None, check: bool = True) -> int:

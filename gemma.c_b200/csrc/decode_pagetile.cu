@@ -82,7 +82,11 @@ constexpr int kTileThreads = TileTraits::kThreads + kWarpSize;
 // row is long, so that the ldmatrix that replicates them over eight matrix rows
 // reads two bank groups instead of one.
 constexpr int kQStrideMma = 256 + 8;
-constexpr int kTileExtraBytes = 2 * kQStrideMma * 2 + 2 * 512 + 64;  // q rows, new K/V rows, flags
+// Rows of unfinished earlier steps of the same cache layer that a step prepares
+// itself instead of waiting for them to reach the cache (TileParams::fwd_*).
+constexpr int kMaxForward = AppendArgs::kMaxForward;
+// q rows, new K/V rows, flags, forwarded K/V rows and their positions
+constexpr int kTileExtraBytes = 2 * kQStrideMma * 2 + 2 * 512 + 64 + kMaxForward * 1024 + 32;
 // Shared-memory layout of a TMA tile (tile_tokens tokens of one head, K or V) in
 // the tensor-core variant: four blocks of 64 dims, each [tile_tokens][128 bytes],
 // written by one TMA copy with the 128-byte swizzle (the 16-byte chunk c of
@@ -130,6 +134,14 @@ struct TileParams {
   // next one's): the tiles of that many positions before the new one wait for
   // the preceding kernel. 0: none writes this layer's cache, no tile waits.
   int32_t steps_in_flight;
+  // With fwd_count == steps_in_flight no tile waits either: the K / V rows those
+  // steps append are prepared here from their raw rows (fwd_k, fwd_v; V from K
+  // where fwd_v is null) at their positions (fwd_pos, per sequence; negative: the
+  // step did not append for that sequence), nearest step first.
+  int32_t fwd_count;
+  const __nv_bfloat16 *fwd_k[kMaxForward];
+  const __nv_bfloat16 *fwd_v[kMaxForward];
+  const int32_t *fwd_pos[kMaxForward];
   // Non-zero: the next kernel may start as soon as this one runs (the caller has
   // checked that what the next kernel reads before its own wait is written by
   // none of the kernels that can then be in flight).
@@ -358,6 +370,9 @@ __global__ __launch_bounds__(kTileThreads, 2) void decode_pagetile_kernel(
   __nv_bfloat16 *s_q = reinterpret_cast<__nv_bfloat16 *>(smem + T::kRingBytes);  // [2][kQStride]
   __nv_bfloat16 *s_new = s_q + 2 * kQStride;  // [2][256]: the new K row, the new V row
   volatile int *s_flag = reinterpret_cast<volatile int *>(s_new + 2 * D);  // abort, last
+  // forwarded rows [step][K row, V row][256] and the position of each (-1: not in this CTA's range)
+  __nv_bfloat16 *s_fwd = s_new + 2 * D + 32;
+  volatile int *s_fwd_pos = reinterpret_cast<volatile int *>(s_fwd + kMaxForward * 2 * D);
 
   const int warp = int(threadIdx.x) >> 5;
   const int lane = int(threadIdx.x) & 31;
@@ -460,7 +475,9 @@ __global__ __launch_bounds__(kTileThreads, 2) void decode_pagetile_kernel(
     // (fused: the steps in flight wrote the positions len - 2 down to
     // len - 1 - steps_in_flight; attention only: the append before wrote len - 1)
     const int newest = max(len - 1 - (kFused ? p.steps_in_flight : 0), 0);
-    const int fresh = (kFused && p.steps_in_flight == 0) ? len : (newest / ps) * ps;
+    const int fresh = (kFused && (p.steps_in_flight == 0 || p.fwd_count >= p.steps_in_flight))
+                          ? len
+                          : (newest / ps) * ps;
     bool ok = true;
     bool waited = false;
     int cached_lp = -1, cached_phys = -1;
@@ -578,6 +595,37 @@ __global__ __launch_bounds__(kTileThreads, 2) void decode_pagetile_kernel(
         store_head<D>(s_new + (warp - 2) * D, y, lane);
       }
     }
+    // Rows of the unfinished steps before this one that fall into this CTA's
+    // range: prepared here like the new row (task 2 j is step j's K row, 2 j + 1
+    // its V row; warps 4..7 start on them while warps 0..3 prepare q, K and V).
+    if (p.fwd_count > 0) {
+#pragma unroll
+      for (int j = 0; j < kMaxForward; ++j) {
+        if (j >= p.fwd_count) break;
+#pragma unroll
+        for (int kind = 0; kind < 2; ++kind) {
+          if (((2 * j + kind + 4) & 7) != warp) continue;
+          const int pos = __ldg(p.fwd_pos[j] + b);
+          const bool here = pos >= first && pos < len && pos / ST >= c0 && pos / ST < c1;
+          if (kind == 0 && lane == 0) s_fwd_pos[j] = here ? pos : -1;
+          if (!here) continue;
+          const __nv_bfloat16 *src =
+              (kind == 0 || p.fwd_v[j] == nullptr ? p.fwd_k[j] : p.fwd_v[j]) +
+              (int64_t(b) * H + h) * D;
+          float xf[D / 32];
+          load_head<D>(src, lane, xf);
+          __nv_bfloat16 yf[D / 32];
+          if (kind == 0) {
+            prep_weighted_rope_values<D, D, kIeee>(yf, xf, p.k_norm_weight,
+                                                   p.cos + int64_t(pos) * (D / 2),
+                                                   p.sin + int64_t(pos) * (D / 2), lane);
+          } else {
+            prep_scale_free_values<D, kIeee>(yf, xf);
+          }
+          store_head<D>(s_fwd + (2 * j + kind) * D, yf, lane);
+        }
+      }
+    }
   } else {
     pdl_wait_for_predecessor();  // q comes from the append
     if (warp < 2) {
@@ -625,10 +673,10 @@ __global__ __launch_bounds__(kTileThreads, 2) void decode_pagetile_kernel(
         // prepared one before they read it -- the same bytes twice, so neither
         // has to wait for the other. The slot's mask bit is set exactly when its
         // page is mapped.
-        if (owns_new && c0 + c == new_pos / ST) {
-          const int slot = new_pos % ST;
+        auto patch = [&](int pos, const __nv_bfloat16 *kv_rows) {
+          const int slot = pos % ST;
           if (kh == slot / 16 && ((mask >> slot) & 1u) != 0u) {
-            const uint4 *rows = reinterpret_cast<const uint4 *>(s_new);
+            const uint4 *rows = reinterpret_cast<const uint4 *>(kv_rows);
             const int tb = p.tile_tokens;  // chunk lane of the row: block lane / 8, swizzled
             uint8_t *k_row = smem + stage * T::kStageBytes + (slot / tb) * tb * T::kRowBytes +
                              (lane >> 3) * tb * 128 + (slot % tb) * 128 +
@@ -638,6 +686,12 @@ __global__ __launch_bounds__(kTileThreads, 2) void decode_pagetile_kernel(
             fence_proxy_async_shared();  // the next fill of the stage is a bulk copy
             __syncwarp();
           }
+        };
+        if (owns_new && c0 + c == new_pos / ST) patch(new_pos, s_new);
+        // ... and so do the rows the unfinished steps before this one append
+        for (int j = 0; j < p.fwd_count; ++j) {
+          const int pos = s_fwd_pos[j];
+          if (pos >= 0 && pos / ST == c0 + c) patch(pos, s_fwd + 2 * j * D);
         }
       }
       const uint32_t mask16 = (mask >> (kh * 16)) & 0xffffu;
@@ -687,16 +741,21 @@ __global__ __launch_bounds__(kTileThreads, 2) void decode_pagetile_kernel(
     // its page is mapped.
     auto patch_new_row = [&](int c, int stage) {
       if constexpr (kFused) {
-        if (owns_new && c0 + c == new_pos / ST) {
-          const int slot = new_pos % ST;
+        auto patch = [&](int pos, const __nv_bfloat16 *kv_rows) {
+          const int slot = pos % ST;
           if (warp == slot / kTokPerWarp && ((ring.masks()[stage] >> slot) & 1ull) != 0ull) {
             uint8_t *k_row = smem + stage * T::kStageBytes + slot * T::kRowBytes;
-            const uint4 *rows = reinterpret_cast<const uint4 *>(s_new);
+            const uint4 *rows = reinterpret_cast<const uint4 *>(kv_rows);
             reinterpret_cast<uint4 *>(k_row)[lane] = rows[lane];
             reinterpret_cast<uint4 *>(k_row + T::kStageTensorBytes)[lane] = rows[32 + lane];
             fence_proxy_async_shared();  // the next fill of the stage is a bulk copy
             __syncwarp();
           }
+        };
+        if (owns_new && c0 + c == new_pos / ST) patch(new_pos, s_new);
+        for (int j = 0; j < p.fwd_count; ++j) {  // rows of the unfinished steps before this one
+          const int pos = s_fwd_pos[j];
+          if (pos >= 0 && pos / ST == c0 + c) patch(pos, s_fwd + 2 * j * D);
         }
       }
     };
@@ -1209,6 +1268,13 @@ cudaError_t decode_layer_step_pagetile_bf16(const AppendArgs *ap, const DecodeAr
   p.q_prepared = ap->q_prepared;
   p.raw_from_predecessor = ap->raw_from_predecessor ? 1 : 0;
   p.steps_in_flight = std::max(0, ap->steps_in_flight);
+  p.fwd_count = std::min<int32_t>(std::max(0, ap->forward_count), kMaxForward);
+  for (int j = 0; j < p.fwd_count; ++j) {
+    if (ap->forward_k[j] == nullptr || ap->forward_position[j] == nullptr) return cudaErrorInvalidValue;
+    p.fwd_k[j] = ap->forward_k[j];
+    p.fwd_v[j] = ap->forward_v[j];
+    p.fwd_pos[j] = ap->forward_position[j];
+  }
   p.release_early = ap->release_early ? 1 : 0;
   return ap->norm_mode == B200KV_NORM_IEEE
              ? launch_pagetile<kFusedIeee>(p, mma, map_k, map_v, stream)

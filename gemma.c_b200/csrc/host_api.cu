@@ -964,10 +964,22 @@ bool takes_one_launch_kernel(const B200KvLayerStepArgs *s) {
                                            s->ticket != nullptr);
 }
 
+// What b200kv_decode_step_bf16 tells an entry's launch about its place in a run
+// of overlapping launches (see plan_entry below). Default: a launch on its own.
+struct StepPlan {
+  int32_t steps_in_flight = 1;  // unfinished launches entry i can meet that are steps of its cache layer
+  bool release_early = false;   // its kernel releases the next entry's at once
+  bool chained = false;         // part of a run: sized for one CTA per SM
+  // the entries (nearest first) whose appended rows entry i prepares itself
+  // instead of waiting for them; either all steps_in_flight of them or none
+  int32_t forward_count = 0;
+  int32_t forward_entry[b200kv::AppendArgs::kMaxForward] = {};
+};
+
 int layer_step(const B200KvLayerStepArgs *s, bool raw_from_predecessor,
                b200kv_stream stream, bool force_tiled = false,
-               int32_t steps_in_flight = 1, bool release_early = false,
-               bool chained = false) {
+               const StepPlan &plan = StepPlan(),
+               const B200KvLayerStepArgs *entries = nullptr) {
   if (s == nullptr) return cudaErrorInvalidValue;
   using bf = __nv_bfloat16;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -991,9 +1003,18 @@ int layer_step(const B200KvLayerStepArgs *s, bool raw_from_predecessor,
   a.rotary_dim = s->rotary_dim;
   a.norm_mode = s->norm_mode;
   a.raw_from_predecessor = raw_from_predecessor;
-  a.steps_in_flight = steps_in_flight;
-  a.release_early = release_early;
-  a.chained = chained;
+  a.steps_in_flight = plan.steps_in_flight;
+  a.release_early = plan.release_early;
+  a.chained = plan.chained;
+  if (entries != nullptr) {
+    a.forward_count = plan.forward_count;
+    for (int32_t j = 0; j < plan.forward_count; ++j) {
+      const B200KvLayerStepArgs &e = entries[plan.forward_entry[j]];
+      a.forward_k[j] = reinterpret_cast<const bf *>(e.raw_k);
+      a.forward_v[j] = reinterpret_cast<const bf *>(e.raw_v);
+      a.forward_position[j] = e.token_position;
+    }
+  }
 
   b200kv::DecodeArgs d;
   d.out = reinterpret_cast<bf *>(s->out);
@@ -1146,19 +1167,26 @@ namespace {
 // launch. A run of one-launch layer-steps does better: entry i releases entry
 // i + 1 at once, and entry i + 1 is told how many of the launches it can then
 // meet -- the entries of the run so far -- are earlier decode steps of its own
-// cache layer, whose newest rows it must not read before they are complete.
-// (Entries that name the same cache layer are consecutive decode steps, in
-// order: each appends the position after its predecessor's.) The first entry
-// never releases early (what precedes it is not known here) and allows for one
-// step of its own layer in flight; a run is cut after kMaxEarlyRun entries,
-// which bounds the launches in flight whatever their size.
+// cache layer, whose newest rows are not in the cache yet. (Entries that name
+// the same cache layer are consecutive decode steps, in order: each appends the
+// position after its predecessor's.) Where all of those steps are entries of
+// this call, the kernel is given their raw K / V rows and positions and prepares
+// the rows itself; otherwise it leaves their pages until its predecessor is
+// complete. The first entry never releases early (what precedes it is not known
+// here) and allows for one step of its own layer in flight; a run is cut after
+// kMaxEarlyRun entries, which bounds the launches in flight whatever their size.
 constexpr int32_t kMaxEarlyRun = 6;
+static_assert(kMaxEarlyRun + 1 <= b200kv::AppendArgs::kMaxForward, "every step in flight can be forwarded");
 
-struct StepPlan {
-  int32_t steps_in_flight;  // unfinished launches entry i can meet that are steps of its cache layer
-  bool release_early;       // its kernel releases the next entry's at once
-  bool chained;             // part of a run: sized for one CTA per SM
-};
+// B200KV_MAX_EARLY_RUN=n (0..6): tuning aid, shorter runs.
+int32_t max_early_run() {
+  static const int32_t n = [] {
+    const char *v = std::getenv("B200KV_MAX_EARLY_RUN");
+    if (v == nullptr) return kMaxEarlyRun;
+    return std::min(kMaxEarlyRun, std::max(0, std::atoi(v)));
+  }();
+  return n;
+}
 
 // Plan of entry i given the early releases in a row up to entry i - 1.
 StepPlan plan_entry(const B200KvLayerStepArgs *layers, int32_t layer_count, int32_t i,
@@ -1168,14 +1196,30 @@ StepPlan plan_entry(const B200KvLayerStepArgs *layers, int32_t layer_count, int3
     const B200KvLayerStepArgs &c = layers[b];
     return (p.cache_k == c.cache_k || p.cache_v == c.cache_v) && p.cache_layer == c.cache_layer;
   };
-  StepPlan plan = {};
+  StepPlan plan;
+  plan.steps_in_flight = 0;
   const int32_t in_flight = 1 + run;  // unfinished launches entry i can meet
+  bool all_known = true;
   for (int32_t k = 1; k <= in_flight; ++k) {
-    if (i - k < 0 || layers[i - k].batch_count <= 0 || same_cache(i - k, i)) {
+    if (i - k < 0 || layers[i - k].batch_count <= 0) {
+      ++plan.steps_in_flight;  // not known here: taken to be a step of this layer
+      all_known = false;
+    } else if (same_cache(i - k, i)) {
+      const B200KvLayerStepArgs &e = layers[i - k];
+      const B200KvLayerStepArgs &c = layers[i];
+      if (plan.steps_in_flight < b200kv::AppendArgs::kMaxForward && e.raw_k != nullptr &&
+          e.token_position != nullptr && e.batch_count == c.batch_count &&
+          e.k_norm_weight == c.k_norm_weight && e.cos == c.cos && e.sin == c.sin &&
+          e.norm_mode == c.norm_mode && e.page_table == c.page_table) {
+        plan.forward_entry[plan.steps_in_flight] = i - k;
+      } else {
+        all_known = false;
+      }
       ++plan.steps_in_flight;
     }
   }
-  plan.release_early = i >= 1 && i + 1 < layer_count && run < kMaxEarlyRun &&
+  plan.forward_count = all_known && takes_one_launch_kernel(layers + i) ? plan.steps_in_flight : 0;
+  plan.release_early = i >= 1 && i + 1 < layer_count && run < max_early_run() &&
                        takes_one_launch_kernel(layers + i) &&
                        takes_one_launch_kernel(layers + i + 1);
   // part of a run: released early, releasing early, or the run's first entry
@@ -1194,8 +1238,7 @@ int b200kv_decode_step_bf16(const B200KvLayerStepArgs *layers,
   int32_t run = 0;  // early releases in a row up to the entry before this one
   for (int32_t i = 0; i < layer_count; ++i) {
     const StepPlan plan = plan_entry(layers, layer_count, i, run);
-    const int st = layer_step(layers + i, false, stream, false, plan.steps_in_flight,
-                              plan.release_early, plan.chained);
+    const int st = layer_step(layers + i, false, stream, false, plan, layers);
     if (st != cudaSuccess) return st;
     run = plan.release_early ? run + 1 : 0;
   }
@@ -1203,13 +1246,15 @@ int b200kv_decode_step_bf16(const B200KvLayerStepArgs *layers,
 }
 
 int b200kv_decode_step_plan(const B200KvLayerStepArgs *layers, int32_t layer_count,
-                            int32_t *steps_in_flight, int32_t *release_early) {
+                            int32_t *steps_in_flight, int32_t *release_early,
+                            int32_t *forwarded) {
   if (layers == nullptr || layer_count < 0) return cudaErrorInvalidValue;
   int32_t run = 0;
   for (int32_t i = 0; i < layer_count; ++i) {
     const StepPlan plan = plan_entry(layers, layer_count, i, run);
     if (steps_in_flight != nullptr) steps_in_flight[i] = plan.steps_in_flight;
     if (release_early != nullptr) release_early[i] = plan.release_early ? 1 : 0;
+    if (forwarded != nullptr) forwarded[i] = plan.forward_count;
     run = plan.release_early ? run + 1 : 0;
   }
   return cudaSuccess;

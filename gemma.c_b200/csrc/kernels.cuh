@@ -100,6 +100,17 @@ struct AppendArgs {
   // the grid is then sized for one CTA per SM instead of two, so that two
   // launches of the run fit on the GPU side by side.
   bool chained = false;
+  // The raw K / V rows (nullptr V: derived from raw K) and positions of the
+  // `forward_count` decode steps of this cache layer just before this one,
+  // nearest first. With forward_count == steps_in_flight the kernel does not
+  // wait for those steps' rows to reach the cache: it prepares them itself from
+  // the same inputs (the same arithmetic, so the same bits) and puts them where
+  // the tiles of the cache would have brought them.
+  static constexpr int kMaxForward = 7;
+  int32_t forward_count = 0;
+  const __nv_bfloat16 *forward_k[kMaxForward] = {};
+  const __nv_bfloat16 *forward_v[kMaxForward] = {};
+  const int32_t *forward_position[kMaxForward] = {};
 };
 
 cudaError_t decode_append_bf16(const AppendArgs &args, cudaStream_t stream);

@@ -571,22 +571,28 @@ int b200kv_decode_attention_tiled_bf16(
  * under the tails of the layers before it -- or, where two entries name the same
  * cache_k / cache_v and cache_layer, consecutive decode steps of that layer in
  * order (each appends the position after the one its predecessor appended, for
- * every sequence): the later step then leaves the pages of the positions its
- * unfinished predecessors write until they are complete. Several steps of one
- * layer in one call are the way to keep a one-layer decode loop's launches
- * overlapped. */
+ * every sequence): the later step then does not read the rows its unfinished
+ * predecessors append from the cache -- it prepares them itself from those
+ * entries' raw rows (the same arithmetic, the same bits), or, where a
+ * predecessor is not an entry of this call, leaves their pages until it is
+ * complete. Several steps of one layer in one call are the way to keep a
+ * one-layer decode loop's launches overlapped. */
 int b200kv_decode_step_bf16(const B200KvLayerStepArgs *layers,
                             int32_t layer_count, b200kv_stream stream);
 /* What b200kv_decode_step_bf16 would tell each entry's launch, without
- * launching anything (host only; either output may be NULL):
+ * launching anything (host only; every output may be NULL):
  * steps_in_flight[i] -- how many of the launches that can still be running
  * when entry i's kernel starts are taken to be earlier decode steps of entry
  * i's own cache layer (0: none of them writes that cache), release_early[i]
- * -- whether entry i's kernel lets entry i + 1's start at once. Entries that
- * do not run as the one-launch layer-step neither release early nor are
- * released early. */
+ * -- whether entry i's kernel lets entry i + 1's start at once, forwarded[i]
+ * -- for how many of those earlier steps entry i's kernel prepares the
+ * appended rows itself from their raw rows instead of waiting for them to reach
+ * the cache (all of them when they are entries of this call, else none).
+ * Entries that do not run as the one-launch layer-step neither release early
+ * nor are released early. */
 int b200kv_decode_step_plan(const B200KvLayerStepArgs *layers, int32_t layer_count,
-                            int32_t *steps_in_flight, int32_t *release_early);
+                            int32_t *steps_in_flight, int32_t *release_early,
+                            int32_t *forwarded);
 
 /* ------------------------------------------------------------------ *
  * The steps either side of the KV path inside the reference's fused decode

@@ -281,7 +281,7 @@ def _step_entries(kv, specs):
         a.cache_config = kv.make_kv_config(4, max(batch, 1) * pages, 16, pages, max(batch, 1), 8, 256, window)
         a.cache_k, a.cache_v, a.cache_layer = cache, cache + 0x1000, layer
         a.batch_count, a.q_heads, a.rotary_dim, a.split_size, a.num_splits = batch, 16, 256, 0, 37
-        a.ticket = 0x7000
+        a.ticket, a.raw_k, a.token_position = 0x7000, 0x5000, 0x6000
     return arr
 
 
@@ -298,13 +298,17 @@ def test_decode_step_plan_of_runs(kv):
     assert early == [i % 7 != 0 and i + 1 < n for i in range(n)]
 
     n = 16                                               # sixteen steps of ONE layer (a one-layer decode loop)
-    held, early = kv.decode_step_plan(_step_entries(kv, [(0x100000, 0, 1, 0)] * n), n)
+    held, early, fwd = kv.decode_step_plan(_step_entries(kv, [(0x100000, 0, 1, 0)] * n), n, forwarded=True)
     assert early == [i % 7 != 0 and i + 1 < n for i in range(n)]
     assert held == [1, 1, 2, 3, 4, 5, 6, 7, 1, 2, 3, 4, 5, 6, 7, 1]
+    # the first entry's predecessor is not an entry of the call: its rows cannot be prepared here
+    assert fwd == [0] + held[1:]
 
     n = 8                                                # two layers in turn
-    held, early = kv.decode_step_plan(_step_entries(kv, [(0x100000, i % 2, 2, 1024) for i in range(n)]), n)
+    held, early, fwd = kv.decode_step_plan(_step_entries(kv, [(0x100000, i % 2, 2, 1024) for i in range(n)]), n,
+                                           forwarded=True)
     assert held == [1, 0, 1, 1, 2, 2, 3, 3]
+    assert fwd == [0, 0, 1, 1, 2, 2, 3, 3]
     assert early == [False, True, True, True, True, True, True, False]
 
     specs = [(0x100000 * (i + 1), 0, 1, 1024) for i in range(6)]
