@@ -46,8 +46,19 @@
 // projections (unless they come from the preceding kernel) and key tiles older
 // than the page of the previous step's newest key; everything it writes
 // (prepared q, cache rows, partials, tickets, outputs) and the newest tiles
-// come after. The dependent launch is released by a warp that has itself waited
-// for the preceding kernel, so at most two kernels are in flight.
+// come after. By default the dependent launch is released by a warp that has
+// itself waited for the preceding kernel, so at most two kernels are in flight.
+//
+// Runs (b200kv_decode_step_bf16 decides, see host_api.cu): a kernel may be told
+// to release the next launch at once (release_early), and is told how many of
+// the launches it can then meet are earlier decode steps of its own cache layer
+// (steps_in_flight; 0 = layer-steps of other layers only, no tile waits). The
+// rows those steps append are not in the cache yet: the kernel either gets their
+// raw K / V rows and positions and prepares them itself (fwd_*, patched into the
+// stages like its own new row), or holds back the tiles of those positions
+// until the preceding kernel is complete. Completion stays a chain -- every CTA
+// waits for the preceding kernel before it writes or leaves -- which is what
+// scratch, tickets, outputs and the slots of a tight ring rely on.
 #include <cuda.h>
 
 #include <algorithm>
