@@ -333,3 +333,37 @@ def test_device_phase_header_compiles_into_a_kernel_of_its_own(tmp_path):
     assert lib.exists() and lib.stat().st_size > 0
     exported = subprocess.run(["nm", "-D", "--defined-only", str(lib)], capture_output=True, text=True).stdout
     assert "device_phases_layer_step" in exported
+
+
+@pytest.mark.skipif(_gemma_c_src() is None, reason="gemma.c sources not mounted")
+def test_device_phase_header_inside_a_gemma_c_translation_unit(tmp_path):
+    """include/gemma4_b200kv_device.cuh in a translation unit that has the reference's own headers (the situation
+    of its decode megakernel): with GEMMA4_B200KV_USE_REFERENCE_HEADERS the library's header declares no type
+    of its own, and a kernel that calls the three phases with the reference's Gemma4KvCacheConfig compiles."""
+    import shutil
+
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    repo = Path(__file__).resolve().parents[1]
+    src = tmp_path / "phases_in_gemma_c.cu"
+    src.write_text('''
+#include "gemma4_kv_cache.cuh"   // gemma.c's own
+#include "gemma4_b200kv_device.cuh"
+__global__ void layer(__nv_bfloat16 *q_prepared, __nv_bfloat16 *cache_k, __nv_bfloat16 *cache_v,
+                      __nv_bfloat16 *out, float *pm, float *pl, float *pacc, Gemma4KvCacheConfig cfg,
+                      const int32_t *table, const int32_t *pos, const int32_t *len, const __nv_bfloat16 *q,
+                      const __nv_bfloat16 *k, const __nv_bfloat16 *v, const __nv_bfloat16 *w, const float *cs) {
+  extern __shared__ float smem[];
+  b200kv_device::append_phase(q_prepared, cache_k, cache_v, cfg, table, pos, 0, q, k, v, w, w, cs, cs, 16,
+                              int(blockIdx.x), int(blockIdx.y), int(threadIdx.x), int(blockDim.x));
+  b200kv_device::split_phase(pm, pl, pacc, out, nullptr, q_prepared, cache_k, cache_v, cfg, table, len, 0,
+                             0.0625f, 20, 4, 16, int(blockIdx.x), int(blockIdx.y), int(blockIdx.z), smem,
+                             int(threadIdx.x), int(blockDim.x));
+  b200kv_device::reduce_phase(out, nullptr, pm, pl, pacc, cfg, len, 20, 4, 16, int(blockIdx.x),
+                              int(blockIdx.y), int(threadIdx.x), int(blockDim.x));
+}
+''')
+    build = subprocess.run([nvcc, "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-c",
+                            "-DGEMMA4_B200KV_USE_REFERENCE_HEADERS", "-I", _gemma_c_src(), "-I",
+                            str(repo / "include"), str(src), "-o", str(tmp_path / "phases.o")],
+                           capture_output=True, text=True)
+    assert build.returncode == 0, build.stdout + build.stderr
