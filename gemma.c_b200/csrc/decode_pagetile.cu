@@ -417,13 +417,13 @@ __global__ __launch_bounds__(kTileThreads, 2) void decode_pagetile_kernel(
       if (!p.raw_from_predecessor) load_head<D>(raw_row, lane, x);
     }
   }
-  // A short page-table row (a sliding-window ring) is fetched whole by the
-  // producer warp before the length is known, four entries per lane: one
-  // dependent round trip less before the first tile can be asked for.
   if (warp == T::kConsumerWarps && lane == 0) {
     prefetch_tensor_map(&map_k);
     prefetch_tensor_map(&map_v);
   }
+  // A short page-table row (a sliding-window ring) is fetched whole by the
+  // producer warp before the length is known, four entries per lane: one
+  // dependent round trip less before the first tile can be asked for.
   const int mpps = cfg.max_pages_per_seq;
   const bool small_table = mpps <= 4 * kWarpSize;
   int table_regs[4] = {-1, -1, -1, -1};
