@@ -40,6 +40,12 @@ __device__ __forceinline__ uint8_t enc_e4m3(float x) {
   return static_cast<uint8_t>(__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3));
 }
 
+// Two values to two codes in one conversion (low byte <- lo), the same rounding
+// and saturation as enc_e4m3.
+__device__ __forceinline__ uint32_t enc_e4m3x2(float lo, float hi) {
+  return uint32_t(__nv_cvt_float2_to_fp8x2(make_float2(lo, hi), __NV_SATFINITE, __NV_E4M3));
+}
+
 __device__ __forceinline__ float dec_e4m3(uint8_t b) {
   const __half_raw h = __nv_cvt_fp8_to_halfraw(b, __NV_E4M3);
   return __half2float(*reinterpret_cast<const __half *>(&h));
@@ -216,9 +222,9 @@ __device__ __forceinline__ void fp8_store_rows_from_memory(
         uint32_t out[2] = {0u, 0u};
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          const uint32_t lo = enc_e4m3(__fdiv_rn(bf16_lo(u[k]), s_new));
-          const uint32_t hi = enc_e4m3(__fdiv_rn(bf16_hi(u[k]), s_new));
-          out[k >> 1] |= (lo | (hi << 8)) << (16 * (k & 1));
+          out[k >> 1] |= enc_e4m3x2(__fdiv_rn(bf16_lo(u[k]), s_new),
+                                    __fdiv_rn(bf16_hi(u[k]), s_new))
+                         << (16 * (k & 1));
         }
         // byte offset of elements 8 * lane .. + 7 inside the 256-byte row
         const int granule = kIsK ? ((lane >> 1) ^ ((r & 1) << 2)) : (lane >> 1);
